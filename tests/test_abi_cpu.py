@@ -1,0 +1,129 @@
+"""No-GPU checks of the boundary: the shared library loads and exports every symbol the header declares,
+struct layouts match the header, host-side mirrors behave like the reference's traits."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _header_symbols():
+    text = open(os.path.join(ROOT, "include", "phoenix_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(phx_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    import __graft_entry__ as ge
+    ge.build()
+    from x_algorithm_b200 import _lib
+    syms = _header_symbols()
+    assert len(syms) >= 25
+    for s in syms:
+        assert hasattr(_lib.lib, s), f"{s} declared in the header but not exported"
+        assert s in _lib.SIGNATURES, f"{s} has no ctypes signature"
+    assert sorted(_lib.SIGNATURES) == syms
+
+
+def test_struct_layouts_match_header():
+    from x_algorithm_b200 import _lib
+    assert C.sizeof(_lib.HashFamily) == 8 * 4 + 8 * 4 + 8 + 8 + 4 + 4
+    assert C.sizeof(_lib.ModelConfig) == 17 * 4 + 5 * 4 + 4 * C.sizeof(_lib.HashFamily)
+    assert C.sizeof(_lib.BlendSpec) == 8 + 32 * 4 + 32 * 8 + 16 - 4 + 4   # int + pad, src, weight, two doubles
+    assert C.sizeof(_lib.RankBatch) == 8 + 6 * 8 and C.sizeof(_lib.RankOut) == 24
+
+
+def test_config_matches_oracle_layout():
+    import x_algorithm_b200 as px
+    from oracle import phoenix_oracle as po
+    for h in (2, 4):
+        cfg = px.PhoenixConfig(num_hashes=h, table_size=1 << 14)
+        lay = po.ModelConfig(num_hashes=h, table_size=1 << 14).hash_layout()
+        for got, want in zip(cfg.families(), (lay.user, lay.item, lay.author, lay.ip)):
+            assert list(got.scales) == list(want.scales) and list(got.biases) == list(want.biases)
+            assert got.modulus == want.modulus and got.table_size == want.table_size
+        assert cfg.table_rows == lay.total_rows
+    assert px.PhoenixConfig(emb_size=512).ffn_size == 2048 == po.ModelConfig(emb_size=512).ffn_size
+
+
+def test_blend_spec_matches_oracle():
+    import x_algorithm_b200 as px
+    from oracle import phoenix_oracle as po
+    ow = po.make_blend_weights(1)
+    ospec = po.blend_spec_from_weights(ow, po.HEAD_NAMES_19, 19)
+    spec = px.blend_spec_from_weights(px.ValueModelWeights(w=dict(ow.w)), px.HEAD_NAMES_19, 19)
+    assert spec.num_terms == len(ospec.src) == 20
+    assert list(spec.src[:20]) == ospec.src.tolist() and list(spec.weight[:20]) == ospec.weight.tolist()
+    assert spec.total_sum == ospec.total_sum and spec.negative_sum == ospec.negative_sum
+    assert px.HEAD_NAMES_19 == po.HEAD_NAMES_19
+
+
+class _FakeEngine:
+    """Stands in for the native engine: deterministic outputs, optional failure."""
+
+    def __init__(self, cfg, fail=False):
+        self.cfg, self.fail, self.calls = cfg, fail, 0
+
+    def rank(self, inp):
+        import x_algorithm_b200 as px
+        self.calls += 1
+        if self.fail:
+            raise px.PhoenixError(2, "device lost")
+        B, Cn = inp.cand_post_ids.shape
+        lp = np.log(np.clip((inp.cand_post_ids % 97 + 1)[..., None] / 100.0 * np.ones(self.cfg.num_actions), 1e-6, 1)).astype(np.float32)
+        cont = (inp.cand_author_ids % 30)[..., None].astype(np.float32)
+        return px.RankOutputs(lp, cont, (inp.cand_post_ids % 97 + 1) / 100.0 + 0.001)
+
+
+def test_scorer_contract_mirrors_reference_trait():
+    import x_algorithm_b200 as px
+    from x_algorithm_b200.plugin import HistoryItem
+    cfg = px.PhoenixConfig(num_candidates=4, max_batch=2, history_len=3)
+    sc = px.PhoenixScorer(_FakeEngine(cfg), px.HEAD_NAMES_19)
+    hist = [HistoryItem(10 + i, 20 + i, 1, 1) for i in range(5)] + [HistoryItem(0, 5, 1, 1)]
+    q = px.Query(user_id=1, history=hist)
+    cands = [px.Candidate(post_id=100 + i, author_id=7 + i) for i in range(11)]   # 3 chunks -> 2 engine calls
+    res = sc.run(q, cands)
+    assert len(res) == 11 and all(not isinstance(r, str) for r in res)
+    assert [r.post_id for r in res] == [c.post_id for c in cands]                 # order and length preserved
+    assert sc.engine.calls == 2
+    assert abs(res[0].phoenix_scores["favorite"] - ((100 % 97 + 1) / 100.0)) < 1e-6
+    sc.update_all(cands, res)
+    assert cands[3].weighted_score == res[3].weighted_score and cands[3].phoenix_scores is res[3].phoenix_scores
+    # most recent S history items, zero entries dropped
+    inp = sc._inputs(q, [cands[:4]])
+    assert inp.hist_post_ids[0].tolist() == [12, 13, 14]
+    # engine failure -> an error string for every candidate, no exception (phoenix_scorer.rs:131-134)
+    bad = px.PhoenixScorer(_FakeEngine(cfg, fail=True), px.HEAD_NAMES_19)
+    res = bad.run(q, cands)
+    assert len(res) == 11 and all(isinstance(r, str) and "Phoenix prediction failed" in r for r in res)
+    before = [c.weighted_score for c in cands]
+    bad.update_all(cands, res)
+    assert [c.weighted_score for c in cands] == before                            # only Ok results are applied
+    # missing scoring sequence -> default candidates (phoenix_scorer.rs:107-109)
+    res = sc.run(px.Query(history=None), cands)
+    assert len(res) == 11 and all(r.phoenix_scores is None for r in res)
+    assert not sc.enable(px.Query(has_cached_posts=True)) and not sc.enable(px.Query(kill_switch=True))
+
+    class Short(px.PhoenixScorer):
+        def score(self, query, candidates):
+            return super().score(query, candidates)[:-1]
+
+    res = Short(_FakeEngine(cfg), px.HEAD_NAMES_19).run(q, cands)                 # scorer.rs:29-44
+    assert res == ["Scorer length_mismatch expected=11 got=10"] * 11
+
+
+def test_source_contract():
+    import x_algorithm_b200 as px
+
+    class FakeRetriever:
+        def retrieve_for_history(self, tower, history, k):
+            return np.array([0.9, 0.8, 0.7], np.float32), np.array([2, 0, 1])
+
+    src = px.PhoenixSource(None, FakeRetriever(), np.array([11, 0, 33]), np.array([1, 2, 3]))
+    out = src.run(px.Query(history=[]))
+    assert [(c.post_id, c.author_id) for c in out] == [(33, 3), (11, 1)]          # row with post id 0 dropped
+    assert src.run(px.Query(history=None)) == "PhoenixSource: missing retrieval_sequence"

@@ -1,0 +1,248 @@
+"""GPU parity: the CUDA path (through the C ABI) against the CPU oracle on the same seeded inputs.
+Integer / byte work is bit exact; bf16 floating point is within 2e-2 relative (L2) of the oracle,
+the tolerance the workload definition states."""
+import ctypes as C
+import math
+import os
+
+import numpy as np
+import pytest
+
+from oracle import phoenix_oracle as po
+from helpers import make_pair, rel_l2, to_inputs
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch
+    return torch
+
+
+def test_hash_bit_exact_all_families(torch):
+    ocfg, w, rows_fn, eng = make_pair()
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "hash_golden.npz"))
+    ids = np.concatenate([g["ids"], po.make_batch(ocfg, 64, seed=5, zipf_s=1.1).cand_post_ids.ravel()])
+    lay = ocfg.hash_layout()
+    want = [lay.user_hash(ids), lay.item_hash(ids), lay.author_hash(ids), lay.ip_hash(ids)]
+    d_ids = torch.from_numpy(ids).cuda()
+    for fam in range(4):
+        out = torch.empty((ids.size, 2), dtype=torch.int32, device="cuda")
+        eng.hash_ids_device(fam, d_ids, ids.size, out)
+        eng.sync()
+        np.testing.assert_array_equal(out.cpu().numpy(), want[fam])
+    # the reference function's own outputs for the item family at this bucket count
+    np.testing.assert_array_equal(want[1][: g["ids"].size] - lay.offset_item * (want[1][: g["ids"].size] != 0),
+                                  g[f"item_{1 << 17}"])
+    eng.close()
+
+
+@pytest.mark.parametrize("emb,hashes", [(128, 2), (256, 4), (512, 2)])
+def test_gather_sum_bit_exact(torch, emb, hashes):
+    ocfg, w, rows_fn, eng = make_pair(emb_size=emb, num_hashes=hashes, num_q_heads=emb // 32, num_kv_heads=emb // 32,
+                                      table_size=1 << 14)
+    ids = po.make_batch(ocfg, 32, seed=3, zipf_s=1.1).cand_post_ids.ravel()
+    ids[:5] = [0, 1, -7, (1 << 40) - 1, 12345]
+    lay = ocfg.hash_layout()
+    want = po.gather_sum(rows_fn(lay.item_hash(ids)))
+    want[0] = po.gather_sum(rows_fn(np.zeros((1, hashes), np.int32)))[0]   # id 0 -> row 0 for every hash
+    d_ids = torch.from_numpy(ids).cuda()
+    out = torch.empty((ids.size, emb), dtype=torch.int16, device="cuda")
+    eng.gather_sum_device(1, d_ids, ids.size, out)
+    eng.sync()
+    np.testing.assert_array_equal(out.cpu().numpy().view(np.uint16), want)
+    eng.close()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 384, 128), (1000, 128, 512), (4096, 1536, 512),
+                                   (2048, 512, 2048), (77, 2048, 512)])
+@pytest.mark.parametrize("epi", [0, 1, 2])
+def test_gemm_tcgen05_vs_fp32(torch, M, N, K, epi):
+    from x_algorithm_b200.engine import gemm
+    gen = torch.Generator(device="cpu").manual_seed(M + N + K + epi)
+    a = (torch.randn(M, K, generator=gen) * 0.5).to(torch.bfloat16).cuda()
+    wt = (torch.randn(N, K, generator=gen) * 0.05).to(torch.bfloat16).cuda()
+    r = (torch.randn(M, N, generator=gen)).to(torch.bfloat16).cuda() if epi == 1 else None
+    ref = a.float() @ wt.float().t()
+    ref = ref.to(torch.bfloat16).float()
+    if epi == 1:
+        ref = ref + r.float()
+    elif epi == 2:
+        ref = torch.nn.functional.gelu(ref, approximate="tanh")
+    ref = ref.to(torch.bfloat16).float()
+    for impl in (0, 1):
+        c, ms = gemm(a, wt, r, epilogue=epi, impl=impl)
+        err = rel_l2(c.float().cpu().numpy(), ref.cpu().numpy())
+        assert err < 4e-3, (impl, err)
+        # elementwise: at most one bf16 ulp apart almost everywhere
+        d = (c.float() - ref).abs()
+        assert float((d > 0.02 * ref.abs() + 1e-2).float().mean()) < 1e-4, impl
+
+
+@pytest.mark.parametrize("dh,S,Cn,H", [(32, 32, 8, 4), (64, 128, 64, 2), (128, 96, 40, 2), (64, 200, 56, 3)])
+@pytest.mark.parametrize("cap", [(-1.0, 0), (30.0, 1), (30.0, 2)])
+def test_ranker_attention_vs_oracle(torch, dh, S, Cn, H, cap):
+    from x_algorithm_b200.engine import ranker_attention
+    B, T = 3, S + Cn
+    rng = np.random.default_rng(dh + S)
+    q, k, v = (po.bf16_round(rng.standard_normal((B, T, H, dh)).astype(np.float32)) for _ in range(3))
+    pad = np.ones((B, T), bool)
+    pad[1, S // 2:S] = False; pad[1, T - 3:] = False        # ragged history and candidates
+    pad[2, :S] = False                                       # no history at all: candidates see only themselves
+    seg = po.attention_segment_ids(pad, S)
+    sm = math.sqrt(128.0) / dh
+    method = {0: "soft_sign", 1: "soft_sign", 2: "tanh"}[cap[1]]
+    want = po.bf16_round(po.masked_attention(q, k, v, po.ranker_mask(seg), sm, cap[0], method, po._Rounder("bf16")))
+    tq, tk, tv = (torch.from_numpy(x).to(torch.bfloat16).cuda() for x in (q, k, v))
+    out, ms = ranker_attention(tq, tk, tv, torch.from_numpy(seg).cuda(), S, sm, cap[0], cap[1])
+    got = out.float().cpu().numpy()
+    assert rel_l2(got, want) < 1e-2
+    assert np.abs(got - want).max() < 0.05
+    assert (got[seg == 0] == 0).all()                        # padded queries -> zeros
+    # candidate isolation: perturbing one candidate's k,v changes only that candidate's output
+    k2, v2 = k.copy(), v.copy()
+    k2[0, S + 1] += 1.0; v2[0, S + 1] -= 1.0
+    out2, _ = ranker_attention(tq, torch.from_numpy(k2).to(torch.bfloat16).cuda(),
+                               torch.from_numpy(v2).to(torch.bfloat16).cuda(), torch.from_numpy(seg).cuda(), S, sm,
+                               cap[0], cap[1])
+    got2 = out2.float().cpu().numpy()
+    keep = np.ones(T, bool); keep[S + 1] = False
+    np.testing.assert_array_equal(got[0, keep], got2[0, keep])
+    assert not np.array_equal(got[0, S + 1], got2[0, S + 1])
+
+
+def _forward_case(ocfg, w, rows_fn, eng, batch, ragged):
+    b = po.make_batch(ocfg, batch, seed=2, ragged=ragged)
+    taps = {}
+    lp, cont, logits = po.rank_forward(ocfg, w, rows_fn, b, taps)
+    wt = po.make_blend_weights(1)
+    spec = po.blend_spec_from_weights(wt, po.HEAD_NAMES_19, ocfg.num_actions)
+    import x_algorithm_b200 as px
+    pw = px.ValueModelWeights(w=dict(wt.w))
+    eng.set_blend(px.blend_spec_from_weights(pw, px.HEAD_NAMES_19, ocfg.num_actions))
+    res = eng.rank(to_inputs(b))
+    return b, taps, lp, cont, logits, spec, res
+
+
+@pytest.mark.parametrize("ragged", [False, True])
+def test_rank_forward_cfg0_vs_oracle(torch, ragged, monkeypatch):
+    monkeypatch.setenv("PHX_DEBUG_TAPS", "1")
+    ocfg, w, rows_fn, eng = make_pair(max_batch=16)
+    B, T, H = 16, ocfg.seq_len, ocfg.num_hashes
+    b, taps, lp, cont, logits, spec, res = _forward_case(ocfg, w, rows_fn, eng, B, ragged)
+    # integer / byte stages: bit exact
+    hashes = eng.debug_read("hashes", (B, T, 2 * H), np.int32)
+    want_h = np.concatenate([np.concatenate([taps["hist_post"], taps["hist_author"]], axis=2),
+                             np.concatenate([taps["cand_post"], taps["cand_author"]], axis=2)], axis=1)
+    np.testing.assert_array_equal(hashes, want_h)
+    tokens = eng.debug_read("tokens", (B, T, ocfg.emb_size), np.uint16)
+    np.testing.assert_array_equal(tokens, np.concatenate([taps["hist_tok"], taps["cand_tok"]], axis=1))
+    # floating point: 2e-2 relative on logits-derived outputs, valid candidates only
+    valid = b.cand_post_ids != 0
+    assert rel_l2(res.log_probs[valid], lp[valid]) < TOL
+    assert rel_l2(res.continuous[valid], cont[valid]) < TOL
+    # against the fp32 path of the oracle as well
+    ocfg32 = po.ModelConfig(compute="fp32")
+    lp32, cont32, _ = po.rank_forward(ocfg32, w, rows_fn, b)
+    assert rel_l2(res.log_probs[valid], lp32[valid]) < TOL
+    # blend: exact arithmetic given the engine's own head outputs (f64, same order)
+    want_s = po.blend_scores(spec, res.log_probs, res.continuous)
+    np.testing.assert_allclose(res.scores[valid], want_s[valid], rtol=1e-12, atol=1e-15)
+    assert rel_l2(res.scores[valid], po.blend_scores(spec, lp, cont)[valid]) < 5e-2
+    eng.close()
+
+
+@pytest.mark.parametrize("opts", [dict(qk_norm=True), dict(primer_norm=True), dict(attn_logit_cap=20.0),
+                                  dict(attn_logit_cap=20.0, attn_logit_cap_method="tanh", final_logit_cap=10.0),
+                                  dict(rotary=False), dict(emb_size=256, num_q_heads=4, num_kv_heads=4, key_size=64,
+                                                           history_len=48, num_candidates=24, num_layers=3)])
+def test_rank_forward_options_vs_oracle(torch, opts):
+    ocfg, w, rows_fn, eng = make_pair(max_batch=4, **opts)
+    b, taps, lp, cont, logits, spec, res = _forward_case(ocfg, w, rows_fn, eng, 4, True)
+    valid = b.cand_post_ids != 0
+    assert rel_l2(res.log_probs[valid], lp[valid]) < TOL, opts
+    assert rel_l2(res.continuous[valid], cont[valid]) < TOL, opts
+    eng.close()
+
+
+def test_simt_gemm_path_matches_tcgen05(torch, monkeypatch):
+    """The cross-check GEMM and the tcgen05 GEMM give the same forward (accumulation order aside)."""
+    ocfg, w, rows_fn, eng = make_pair(max_batch=4)
+    b = po.make_batch(ocfg, 4, seed=9)
+    r1 = eng.rank(to_inputs(b))
+    eng.close()
+    monkeypatch.setenv("PHX_GEMM", "simt")
+    ocfg, w, rows_fn, eng2 = make_pair(max_batch=4)
+    r2 = eng2.rank(to_inputs(b))
+    eng2.close()
+    assert rel_l2(r1.log_probs, r2.log_probs) < 5e-3
+
+
+def test_engine_errors_are_statuses(torch):
+    import x_algorithm_b200 as px
+    with pytest.raises(px.PhoenixError) as ei:
+        px.PhoenixEngine(px.PhoenixConfig(key_size=48), 0)
+    assert ei.value.status == 1
+    eng = px.PhoenixEngine(px.PhoenixConfig(max_batch=2), 0)
+    ocfg = po.ModelConfig()
+    with pytest.raises(px.PhoenixError) as ei:          # weights not loaded
+        eng.rank(to_inputs(po.make_batch(ocfg, 2)))
+    assert ei.value.status == 6 and "not loaded" in ei.value.message
+    eng.load_weights(po.make_weights(ocfg, 0))
+    with pytest.raises(px.PhoenixError) as ei:          # batch beyond capacity
+        eng.rank(to_inputs(po.make_batch(ocfg, 3)))
+    assert ei.value.status == 5
+    out = eng.rank(to_inputs(po.make_batch(ocfg, 2)))   # the engine stays usable after errors
+    assert np.isfinite(out.log_probs).all()
+    eng.close()
+
+
+def test_user_tower_and_topk_vs_oracle(torch):
+    from x_algorithm_b200.retrieval import CorpusShard, Retriever
+    ocfg, w, rows_fn, eng = make_pair(max_batch=8, emb_size=128, num_candidates=0, history_len=32)
+    b = po.make_batch(po.ModelConfig(history_len=32, num_candidates=1), 8, seed=4, ragged=True)
+    want_users = po.user_tower(ocfg, w, rows_fn, b)
+    dev = [torch.from_numpy(x).cuda() for x in (b.hist_post_ids, b.hist_author_ids, b.hist_actions, b.hist_surfaces)]
+    users = torch.empty((8, 128), dtype=torch.float32, device="cuda")
+    eng.user_tower_device(8, *dev, users)
+    eng.sync()
+    got_users = users.cpu().numpy()
+    ok = b.hist_post_ids[:, 0] != 0
+    assert rel_l2(got_users[ok], want_users[ok]) < TOL
+    # top-k: exact id sets and order (ties -> lower id) for the engine's own user vectors
+    N, k = 50_000, 100
+    shards = [CorpusShard(N // 2, 128, row_offset=0, max_queries=8, max_k=k),
+              CorpusShard(N - N // 2, 128, row_offset=N // 2, max_queries=8, max_k=k)]
+    for s in shards:
+        s.fill_synthetic(11)
+    corpus = po.synthetic_corpus_rows(np.arange(N), 128, 11)
+    sc = po.corpus_scores(got_users, corpus)
+    want_s, want_i = po.top_k(sc, k)
+    got_s, got_i = Retriever(shards).retrieve(users, k)
+    np.testing.assert_array_equal(got_i.cpu().numpy(), want_i)
+    np.testing.assert_array_equal(got_s.cpu().numpy(), want_s)
+    for s in shards:
+        s.close()
+    eng.close()
+
+
+def test_topk_large_shard_uses_pivot_path(torch):
+    """A shard larger than the survivor capacity goes through the sampled pivot; result still exact."""
+    from x_algorithm_b200.retrieval import CorpusShard
+    N, k, B, dim = 400_000, 64, 20, 64
+    sh = CorpusShard(N, dim, row_offset=1000, max_queries=B, max_k=k)
+    sh.fill_synthetic(5)
+    rng = np.random.default_rng(0)
+    u = rng.standard_normal((B, dim)).astype(np.float32)
+    u /= np.linalg.norm(u, axis=1, keepdims=True)
+    users = torch.from_numpy(u).cuda()
+    sc = torch.empty((B, k), dtype=torch.float32, device="cuda"); ids = torch.empty((B, k), dtype=torch.int64, device="cuda")
+    sh.topk_device(users, B, k, sc, ids)
+    sh.sync()
+    corpus = po.synthetic_corpus_rows(np.arange(1000, 1000 + N), dim, 5)
+    want_s, want_i = po.top_k(po.corpus_scores(u, corpus), k, row_offset=1000)
+    np.testing.assert_array_equal(ids.cpu().numpy(), want_i)
+    np.testing.assert_array_equal(sc.cpu().numpy(), want_s)
+    sh.close()

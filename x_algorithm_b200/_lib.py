@@ -1,0 +1,104 @@
+"""ctypes binding of libphoenix_b200.so (the C ABI declared in include/phoenix_b200.h).
+
+There is no fallback: if the shared library is missing or does not load, importing this module
+raises, and every operator of the package fails with it."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libphoenix_b200.so")
+
+PHX_MAX_HASHES = 4
+PHX_MAX_BLEND_TERMS = 32
+STATUS_NAMES = {0: "PHX_OK", 1: "PHX_E_ARG", 2: "PHX_E_CUDA", 3: "PHX_E_NCCL", 4: "PHX_E_TIMEOUT",
+                5: "PHX_E_CAPACITY", 6: "PHX_E_STATE"}
+
+
+class HashFamily(C.Structure):
+    _fields_ = [("scales", C.c_int64 * PHX_MAX_HASHES), ("biases", C.c_int64 * PHX_MAX_HASHES),
+                ("modulus", C.c_int64), ("table_size", C.c_int64), ("num_hashes", C.c_int32), ("_pad", C.c_int32)]
+
+
+class ModelConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in (
+        "emb_size", "num_layers", "num_q_heads", "num_kv_heads", "key_size", "ffn_size", "history_len",
+        "num_candidates", "max_batch", "num_actions", "num_continuous", "num_action_types", "num_surfaces",
+        "rotary", "qk_norm", "primer_norm", "cap_method")] + [(n, C.c_float) for n in (
+        "attn_logit_cap", "final_logit_cap", "rms_eps", "rope_base", "dwell_norm_scale")] + [
+        ("user", HashFamily), ("item", HashFamily), ("author", HashFamily), ("ip", HashFamily)]
+
+
+class BlendSpec(C.Structure):
+    _fields_ = [("num_terms", C.c_int32), ("src", C.c_int32 * PHX_MAX_BLEND_TERMS),
+                ("weight", C.c_double * PHX_MAX_BLEND_TERMS), ("total_sum", C.c_double), ("negative_sum", C.c_double)]
+
+
+class RankBatch(C.Structure):
+    _fields_ = [("batch", C.c_int32), ("_pad", C.c_int32), ("hist_post_ids", C.c_void_p),
+                ("hist_author_ids", C.c_void_p), ("hist_actions", C.c_void_p), ("hist_surfaces", C.c_void_p),
+                ("cand_post_ids", C.c_void_p), ("cand_author_ids", C.c_void_p)]
+
+
+class RankOut(C.Structure):
+    _fields_ = [("log_probs", C.c_void_p), ("continuous", C.c_void_p), ("scores", C.c_void_p)]
+
+
+# every symbol include/phoenix_b200.h declares: name -> (restype, argtypes)
+_P = C.c_void_p
+SIGNATURES = {
+    "phx_engine_create": (C.c_int32, [C.POINTER(ModelConfig), C.c_int32, C.POINTER(_P)]),
+    "phx_engine_destroy": (None, [_P]),
+    "phx_last_error": (C.c_char_p, [_P]),
+    "phx_global_error": (C.c_char_p, []),
+    "phx_load_param": (C.c_int32, [_P, C.c_char_p, _P, C.c_int64, C.c_int64]),
+    "phx_table_upload": (C.c_int32, [_P, C.c_int64, C.c_int64, _P]),
+    "phx_table_fill_synthetic": (C.c_int32, [_P, C.c_uint32, C.c_float]),
+    "phx_set_blend": (C.c_int32, [_P, C.POINTER(BlendSpec)]),
+    "phx_rank_forward": (C.c_int32, [_P, C.POINTER(RankBatch), C.POINTER(RankOut)]),
+    "phx_rank_forward_device": (C.c_int32, [_P, C.POINTER(RankBatch), C.POINTER(RankOut)]),
+    "phx_sync": (C.c_int32, [_P]),
+    "phx_last_device_ms": (C.c_int32, [_P, C.POINTER(C.c_float)]),
+    "phx_last_launch_count": (C.c_int32, [_P, C.POINTER(C.c_int32)]),
+    "phx_mark": (C.c_int32, [_P, C.c_int32]),
+    "phx_elapsed_ms": (C.c_int32, [_P, C.c_int32, C.c_int32, C.POINTER(C.c_float)]),
+    "phx_profile_enable": (C.c_int32, [_P, C.c_int32]),
+    "phx_profile_read": (C.c_int32, [_P, C.POINTER(C.c_float), C.POINTER(C.c_int32)]),
+    "phx_debug_read": (C.c_int32, [_P, C.c_char_p, _P, C.c_size_t]),
+    "phx_hash_ids_device": (C.c_int32, [_P, C.c_int32, _P, C.c_int64, _P]),
+    "phx_gather_sum_device": (C.c_int32, [_P, C.c_int32, _P, C.c_int64, _P]),
+    "phx_ranker_attention_device": (C.c_int32, [C.c_int32, _P, _P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32,
+                                                C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_float, C.c_int32,
+                                                C.POINTER(C.c_float)]),
+    "phx_gemm_device": (C.c_int32, [C.c_int32, _P, _P, _P, _P, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                    C.POINTER(C.c_float)]),
+    "phx_user_tower_device": (C.c_int32, [_P, C.POINTER(RankBatch), _P]),
+    "phx_corpus_create": (C.c_int32, [C.c_int32, C.c_int64, C.c_int32, C.c_int64, C.c_int32, C.c_int32, C.POINTER(_P)]),
+    "phx_corpus_destroy": (None, [_P]),
+    "phx_corpus_upload": (C.c_int32, [_P, C.c_int64, C.c_int64, _P]),
+    "phx_corpus_fill_synthetic": (C.c_int32, [_P, C.c_uint32]),
+    "phx_corpus_topk_device": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, _P, _P]),
+    "phx_topk_merge_device": (C.c_int32, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, _P, _P]),
+    "phx_corpus_sync": (C.c_int32, [_P]),
+    "phx_corpus_last_device_ms": (C.c_int32, [_P, C.POINTER(C.c_float)]),
+    "phx_corpus_last_error": (C.c_char_p, [_P]),
+}
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python -m x_algorithm_b200.build` (nvcc, sm_100a). "
+        "This package has no CPU or PyTorch fallback.")
+
+lib = C.CDLL(LIB_PATH)
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)  # AttributeError here = the library does not export a declared symbol
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+class PhoenixError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"{STATUS_NAMES.get(status, status)}: {message}")
+        self.status = status
+        self.message = message

@@ -1,0 +1,110 @@
+"""Model configuration mirroring the reference's TransformerConfig / RecsysAttentionConfig / HashKeys
+(phoenix/xrex/configs/xrecsys.py:1051-1090, phoenix/xrex/models/recsys_embedding.py:175-248)."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List
+
+from . import _lib
+
+
+@dataclass
+class HashFamilySpec:
+    scales: List[int]
+    biases: List[int]
+    modulus: int
+    table_size: int
+
+    def to_c(self) -> _lib.HashFamily:
+        f = _lib.HashFamily()
+        for i, (s, b) in enumerate(zip(self.scales, self.biases)):
+            f.scales[i], f.biases[i] = s, b
+        f.modulus, f.table_size, f.num_hashes = self.modulus, self.table_size, len(self.scales)
+        return f
+
+
+# HashKeys defaults of the reference (recsys_embedding.py:176-197)
+_REF = {
+    "user": ([196742702, 1852108266], [1935840681, 167407236], 2_859_568_897),
+    "item": ([2161410491, 1754358832], [1935840681, 167407236], 2_361_375_383),
+    "author": ([371965780, 328930218], [139686260, 37755056], 631_860_353),
+    "ip": ([529_482_163, 1_327_604_891], [742_961_053, 318_205_477], 1_073_741_789),
+}
+
+
+def default_family(name: str, table_size: int, num_hashes: int = 2) -> HashFamilySpec:
+    """The reference's constants for `name`; beyond two hashes the list is extended with the other
+    families' constants in the fixed order item, author, user, ip."""
+    sc, bi, mod = (list(x) if isinstance(x, list) else x for x in _REF[name])
+    pool_s = _REF["item"][0] + _REF["author"][0] + _REF["user"][0] + _REF["ip"][0]
+    pool_b = _REF["item"][1] + _REF["author"][1] + _REF["user"][1] + _REF["ip"][1]
+    k = 0
+    while len(sc) < num_hashes:
+        if pool_s[k] not in sc:
+            sc.append(pool_s[k]); bi.append(pool_b[k])
+        k += 1
+    return HashFamilySpec(sc[:num_hashes], bi[:num_hashes], mod, table_size)
+
+
+@dataclass
+class PhoenixConfig:
+    emb_size: int = 128
+    num_layers: int = 2
+    num_q_heads: int = 4
+    num_kv_heads: int = 4
+    key_size: int = 32
+    widening_factor: float = 4.0
+    history_len: int = 32
+    num_candidates: int = 8
+    max_batch: int = 16
+    num_actions: int = 19
+    num_continuous: int = 1
+    num_action_types: int = 8
+    num_surfaces: int = 4
+    num_hashes: int = 2
+    table_size: int = 1 << 17
+    user_table_size: int = -1   # -1: same as table_size
+    ip_table_size: int = -1
+    rotary: bool = True
+    qk_norm: bool = False
+    primer_norm: bool = False
+    attn_logit_cap: float = -1.0
+    attn_logit_cap_method: str = "soft_sign"
+    final_logit_cap: float = 0.0
+    rms_eps: float = 1e-5
+    rope_base: float = 10000.0
+    dwell_norm_scale: float = 30.0
+
+    @property
+    def ffn_size(self) -> int:  # phoenix/xrex/utils/utils.py:37-52
+        f = int(self.widening_factor * self.emb_size)
+        return ((f + 31) // 32) * 32
+
+    @property
+    def seq_len(self) -> int:
+        return self.history_len + self.num_candidates
+
+    def families(self):
+        ut = self.table_size if self.user_table_size < 0 else self.user_table_size
+        it = self.table_size if self.ip_table_size < 0 else self.ip_table_size
+        return (default_family("user", ut, self.num_hashes), default_family("item", self.table_size, self.num_hashes),
+                default_family("author", self.table_size, self.num_hashes), default_family("ip", it, self.num_hashes))
+
+    @property
+    def table_rows(self) -> int:
+        u, i, a, p = self.families()
+        return 65 + u.table_size + i.table_size + a.table_size + p.table_size
+
+    def to_c(self) -> _lib.ModelConfig:
+        c = _lib.ModelConfig()
+        for n in ("emb_size", "num_layers", "num_q_heads", "num_kv_heads", "key_size", "history_len", "num_candidates",
+                  "max_batch", "num_actions", "num_continuous", "num_action_types", "num_surfaces"):
+            setattr(c, n, int(getattr(self, n)))
+        c.ffn_size = self.ffn_size
+        c.rotary, c.qk_norm, c.primer_norm = int(self.rotary), int(self.qk_norm), int(self.primer_norm)
+        c.cap_method = {"soft_sign": 1, "tanh": 2}[self.attn_logit_cap_method] if self.attn_logit_cap > 0 else 0
+        c.attn_logit_cap, c.final_logit_cap = self.attn_logit_cap, self.final_logit_cap
+        c.rms_eps, c.rope_base, c.dwell_norm_scale = self.rms_eps, self.rope_base, self.dwell_norm_scale
+        u, i, a, p = self.families()
+        c.user, c.item, c.author, c.ip = u.to_c(), i.to_c(), a.to_c(), p.to_c()
+        return c

@@ -1,0 +1,162 @@
+// Shared declarations of the Phoenix B200 engine (sm_100a only).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <string>
+
+#include "../../include/phoenix_b200.h"
+
+namespace phx {
+
+typedef __nv_bfloat16 bf16;
+
+// ---- error plumbing ---------------------------------------------------------------------------
+void set_global_error(const std::string& msg);
+
+#define PHX_CUDA_TRY(call, errstr)                                                               \
+  do {                                                                                           \
+    cudaError_t _e = (call);                                                                     \
+    if (_e != cudaSuccess) {                                                                     \
+      (errstr) = std::string(#call) + ": " + cudaGetErrorString(_e) + " (" + __FILE__ + ":" +    \
+                 std::to_string(__LINE__) + ")";                                                 \
+      return PHX_E_CUDA;                                                                         \
+    }                                                                                            \
+  } while (0)
+
+// ---- bf16 <-> f32 on device -------------------------------------------------------------------
+__device__ __forceinline__ float bf2f(bf16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ bf16 f2bf(float x) { return __float2bfloat16_rn(x); }
+__device__ __forceinline__ float round_bf(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+__device__ __forceinline__ uint32_t pack_bf2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float2 unpack_bf2(uint32_t u) {
+  __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);
+  return __bfloat1622float2(v);
+}
+
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+  const float c = 0.7978845608028654f;  // sqrt(2/pi)
+  float inner = c * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(inner));
+}
+
+// ---- GEMM ---------------------------------------------------------------------------------------
+enum GemmEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GELU = 2 };
+
+// One GEMM problem bound to fixed buffers: C[M,N] = epi(A[M,K] @ Wt[N,K]^T).  The tensor maps
+// are encoded once for (pointer, rows_max) and reused for every M <= rows_max.
+struct GemmPlan {
+  CUtensorMap map_a;
+  CUtensorMap map_b;
+  const bf16* A = nullptr;
+  const bf16* Wt = nullptr;
+  int64_t rows_max = 0;
+  int N = 0, K = 0, BN = 0;
+  bool ready = false;
+};
+
+phx_status gemm_plan_create(GemmPlan* plan, const bf16* A, const bf16* Wt, int64_t rows_max, int N, int K,
+                            std::string& err);
+// Launch on `stream`.  `R` is the residual (EPI_RESIDUAL) or null.  `err_flag` is a device int the
+// kernel sets to 1 when a bounded wait ran out.
+phx_status gemm_launch(const GemmPlan& plan, bf16* C, const bf16* R, int64_t M, int epilogue, int* err_flag,
+                       int num_sms, cudaStream_t stream, std::string& err);
+// Plain SIMT GEMM with the same epilogues (debug / cross-check path, selected by PHX_GEMM=simt).
+phx_status gemm_simt_launch(const bf16* A, const bf16* Wt, bf16* C, const bf16* R, int64_t M, int N, int K,
+                            int epilogue, cudaStream_t stream, std::string& err);
+
+// ---- embedding ----------------------------------------------------------------------------------
+struct HashFamilyDev {
+  long long scales[PHX_MAX_HASHES];
+  long long biases[PHX_MAX_HASHES];
+  long long modulus;
+  long long buckets_m1;  // table_size - 1
+  int offset;            // region offset in the unified table
+  int num_hashes;
+};
+
+struct TokenBuildArgs {
+  const long long* hist_post;
+  const long long* hist_author;
+  const int* hist_actions;
+  const int* hist_surfaces;
+  const long long* cand_post;
+  const long long* cand_author;
+  const bf16* table;
+  long long table_rows;
+  const bf16* action_table;
+  const bf16* surface_table;
+  int num_action_types, num_surfaces;
+  HashFamilyDev item, author;
+  int B, S, C, D;
+  float input_scale;
+  bf16* x;         // [B,T,D] scaled tokens
+  bf16* tokens;    // optional [B,T,D] unscaled gather-sum output
+  int* hashes;     // optional [B,T,2H]
+  int* seg;        // [B,T] 1 / -1 / 0
+};
+phx_status build_tokens_launch(const TokenBuildArgs& a, cudaStream_t stream, std::string& err);
+phx_status hash_ids_launch(const HashFamilyDev& fam, const long long* ids, long long n, int* out, cudaStream_t stream,
+                           std::string& err);
+phx_status gather_sum_launch(const HashFamilyDev& fam, const bf16* table, long long table_rows, int D,
+                             const long long* ids, long long n, bf16* out, cudaStream_t stream, std::string& err);
+phx_status table_fill_launch(bf16* table, long long row0, long long rows, int width, uint32_t seed, float amp,
+                             cudaStream_t stream, std::string& err);
+phx_status corpus_fill_launch(bf16* rows_ptr, long long global_row0, long long rows, int dim, uint32_t seed,
+                              cudaStream_t stream, std::string& err);
+
+// ---- elementwise --------------------------------------------------------------------------------
+// y = bf16(norm(x) * gain); with `res` non-null y = bf16(res + bf16(norm(x) * gain)).  y may alias x or res.
+phx_status rmsnorm_launch(const bf16* x, const float* gain, bf16* y, const bf16* res, long long rows, int D, float eps,
+                          cudaStream_t stream, std::string& err);
+struct QkNormRopeArgs {
+  bf16* qkv;             // [M, qkv_width], merged layout per kv group [q_0..q_{g-1}, k, v]
+  long long M;
+  int T, Hq, Hkv, dh;
+  int pos_cap;           // position = min(t, pos_cap)
+  int rotary, qk_norm;
+  const float* q_gain;   // [Hq*dh] or null
+  const float* k_gain;   // [Hkv*dh] or null
+  const float* cos_tab;  // [pos_cap+1, dh/2]
+  const float* sin_tab;
+};
+phx_status qknorm_rope_launch(const QkNormRopeArgs& a, cudaStream_t stream, std::string& err);
+
+// ---- attention ----------------------------------------------------------------------------------
+struct AttnArgs {
+  const bf16* q; const bf16* k; const bf16* v;  // element strides below
+  long long q_tok_stride, k_tok_stride, v_tok_stride;  // between consecutive tokens
+  int q_head_stride, k_head_stride, v_head_stride;     // between consecutive heads
+  bf16* out;             // [B,T,Hq,dh] dense
+  const int* seg;        // [B,T]
+  int B, T, Hq, Hkv, dh, hist_len;
+  float sm_scale, cap;
+  int cap_method;
+};
+phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::string& err);
+
+// ---- heads + blend ------------------------------------------------------------------------------
+struct HeadsArgs {
+  const bf16* x;          // trunk output [B,T,D]
+  const float* final_gain;
+  const bf16* unembed_t;  // [V+NC, D] (transposed, K-major)
+  int B, T, S, C, D, V, NC;
+  float eps, output_scale, final_logit_cap, dwell_norm_scale;
+  phx_blend_spec blend;
+  int has_blend;
+  float* log_probs; float* continuous; double* scores;
+};
+phx_status heads_launch(const HeadsArgs& a, cudaStream_t stream, std::string& err);
+// masked mean pool + L2 normalise of final-normed history rows -> f32 [B,D]
+phx_status tower_pool_launch(const bf16* x, const float* final_gain, const int* seg, int B, int T, int D, float eps,
+                             float* users, cudaStream_t stream, std::string& err);
+
+}  // namespace phx

@@ -1,0 +1,226 @@
+// Multi-hash id -> unified-table row (phoenix/xrex/models/recsys_embedding.py:154-172, 282-331),
+// row gather (xai-recsys-engine/src/emb_table.rs:124-140) and the fixed-order fp32 combine of the
+// gathered rows into one token.  HBM-bound: one warp per token, 16-byte loads per lane, rows of one
+// token read back to back and summed in slot order so the result does not depend on the launch shape.
+#include "common.cuh"
+
+namespace phx {
+namespace {
+
+// raw = (id*scale + bias) mod M, floored (non-negative); idx = 0 if id == 0 else raw mod (buckets-1) + 1
+__device__ __forceinline__ int hash_one(long long id, long long scale, long long bias, long long modulus,
+                                        long long buckets_m1, int offset) {
+  if (id == 0) return 0;
+  // wrapping int64 arithmetic, as numba / Rust release builds do
+  long long raw = (long long)((unsigned long long)id * (unsigned long long)scale + (unsigned long long)bias);
+  long long r = raw % modulus;
+  if (r < 0) r += modulus;
+  return (int)(r % buckets_m1) + 1 + offset;
+}
+
+__device__ __forceinline__ void acc_row(float (&acc)[8], const bf16* row, int col) {
+  uint4 u = __ldg(reinterpret_cast<const uint4*>(row + col));
+  float2 a = unpack_bf2(u.x), b = unpack_bf2(u.y), c = unpack_bf2(u.z), d = unpack_bf2(u.w);
+  acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+  acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+}
+
+// One warp per token.  History token slots: post h0.., author h0.., action row, surface row;
+// candidate token slots: post h0.., author h0...  x = bf16(bf16(sum) * input_scale).
+__global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
+  const int T = a.S + a.C;
+  const long long tok = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (tok >= (long long)a.B * T) return;
+  const int b = (int)(tok / T), t = (int)(tok % T);
+  const bool is_hist = t < a.S;
+  const long long post_id = is_hist ? a.hist_post[(long long)b * a.S + t] : a.cand_post[(long long)b * a.C + (t - a.S)];
+  const long long auth_id = is_hist ? a.hist_author[(long long)b * a.S + t] : a.cand_author[(long long)b * a.C + (t - a.S)];
+  const int H = a.item.num_hashes;
+  // lanes 0..H-1 hash the post id, lanes H..2H-1 the author id
+  int my_idx = 0;
+  if (lane < H) my_idx = hash_one(post_id, a.item.scales[lane], a.item.biases[lane], a.item.modulus, a.item.buckets_m1, a.item.offset);
+  else if (lane < 2 * H) {
+    const int j = lane - H;
+    my_idx = hash_one(auth_id, a.author.scales[j], a.author.biases[j], a.author.modulus, a.author.buckets_m1, a.author.offset);
+  }
+  if (a.hashes && lane < 2 * H) a.hashes[tok * (2 * H) + lane] = my_idx;
+  const int first_post_hash = __shfl_sync(0xffffffffu, my_idx, 0);
+  if (lane == 0) a.seg[tok] = (first_post_hash != 0) ? (is_hist ? 1 : -1) : 0;
+  int act = 0, srf = 0;
+  if (is_hist) {
+    act = a.hist_actions[(long long)b * a.S + t];
+    srf = a.hist_surfaces[(long long)b * a.S + t];
+    act = act < 0 ? 0 : (act > a.num_action_types ? a.num_action_types : act);
+    srf = srf < 0 ? 0 : (srf > a.num_surfaces ? a.num_surfaces : srf);
+  }
+  for (int col = lane * 8; col < a.D; col += 256) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < 2 * H; ++j) {
+      long long idx = __shfl_sync(0xffffffffu, my_idx, j);
+      if (idx < 0 || idx >= a.table_rows) idx = 0;  // out of range -> row 0
+      acc_row(acc, a.table + idx * a.D, col);
+    }
+    if (is_hist) {
+      acc_row(acc, a.action_table + (long long)act * a.D, col);
+      acc_row(acc, a.surface_table + (long long)srf * a.D, col);
+    }
+    uint4 o;
+    if (a.tokens) {
+      o.x = pack_bf2(acc[0], acc[1]); o.y = pack_bf2(acc[2], acc[3]); o.z = pack_bf2(acc[4], acc[5]); o.w = pack_bf2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(a.tokens + tok * a.D + col) = o;
+    }
+    float s[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i] = round_bf(acc[i]) * a.input_scale;
+    o.x = pack_bf2(s[0], s[1]); o.y = pack_bf2(s[2], s[3]); o.z = pack_bf2(s[4], s[5]); o.w = pack_bf2(s[6], s[7]);
+    *reinterpret_cast<uint4*>(a.x + tok * a.D + col) = o;
+  }
+}
+
+__global__ void hash_ids_kernel(HashFamilyDev fam, const long long* __restrict__ ids, long long n, int* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n * fam.num_hashes) return;
+  const long long t = i / fam.num_hashes;
+  const int j = (int)(i % fam.num_hashes);
+  out[i] = hash_one(ids[t], fam.scales[j], fam.biases[j], fam.modulus, fam.buckets_m1, fam.offset);
+}
+
+// Stand-alone gather-sum: out[i] = bf16(sum_j table[hash_j(id_i)]) in hash order.  LANES lanes per id
+// (LANES * 8 >= D or a loop), several ids per warp for narrow rows.
+template <int LANES>
+__global__ void __launch_bounds__(256) gather_sum_kernel(HashFamilyDev fam, const bf16* __restrict__ table,
+                                                         long long table_rows, int D, const long long* __restrict__ ids,
+                                                         long long n, bf16* __restrict__ out) {
+  const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LANES;
+  const int sub = threadIdx.x % LANES;
+  if (gid >= n) return;
+  const long long id = __ldg(ids + gid);
+  long long idx[PHX_MAX_HASHES];
+#pragma unroll
+  for (int j = 0; j < PHX_MAX_HASHES; ++j) {
+    idx[j] = 0;
+    if (j < fam.num_hashes) {
+      idx[j] = hash_one(id, fam.scales[j], fam.biases[j], fam.modulus, fam.buckets_m1, fam.offset);
+      if (idx[j] < 0 || idx[j] >= table_rows) idx[j] = 0;
+    }
+  }
+  for (int col = sub * 8; col < D; col += LANES * 8) {
+    uint4 u[PHX_MAX_HASHES];
+#pragma unroll
+    for (int j = 0; j < PHX_MAX_HASHES; ++j)
+      if (j < fam.num_hashes) u[j] = __ldg(reinterpret_cast<const uint4*>(table + idx[j] * D + col));
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < PHX_MAX_HASHES; ++j) {
+      if (j < fam.num_hashes) {
+        float2 a = unpack_bf2(u[j].x), b = unpack_bf2(u[j].y), c = unpack_bf2(u[j].z), d = unpack_bf2(u[j].w);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+        acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf2(acc[0], acc[1]); o.y = pack_bf2(acc[2], acc[3]); o.z = pack_bf2(acc[4], acc[5]); o.w = pack_bf2(acc[6], acc[7]);
+    __stcs(reinterpret_cast<uint4*>(out + gid * D + col), o);
+  }
+}
+
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16; x *= 0x7FEB352Du; x ^= x >> 15; x *= 0x846CA68Bu; x ^= x >> 16;
+  return x;
+}
+__device__ __forceinline__ float synth_value(unsigned long long row, int col, int width, uint32_t seed, float scale) {
+  uint32_t x = (uint32_t)((row * (unsigned long long)width + (unsigned long long)col) & 0xFFFFFFFFull) ^ seed;
+  x = mix32(x);
+  return ((float)(x >> 16) - 32768.0f) * scale;
+}
+
+__global__ void table_fill_kernel(bf16* table, long long row0, long long rows, int width, uint32_t seed, float scale) {
+  const long long total = rows * (long long)(width / 8);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / (width / 8);
+    const int c = (int)(i % (width / 8)) * 8;
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = synth_value((unsigned long long)(row0 + r), c + k, width, seed, scale);
+    uint4 o;
+    o.x = pack_bf2(v[0], v[1]); o.y = pack_bf2(v[2], v[3]); o.z = pack_bf2(v[4], v[5]); o.w = pack_bf2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(table + r * width + c) = o;
+  }
+}
+
+// corpus rows: synthetic values rounded to bf16, fixed-order fp32 sum of squares, scaled, rounded again
+__global__ void corpus_fill_kernel(bf16* rows_ptr, long long global_row0, long long rows, int dim, uint32_t seed) {
+  for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += (long long)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int c = 0; c < dim; ++c) {
+      float v = round_bf(synth_value((unsigned long long)(global_row0 + r), c, dim, seed, 1.0f / 32768.0f));
+      acc = acc + v * v;
+    }
+    const float inv = 1.0f / sqrtf(fmaxf(acc, 1e-12f));
+    for (int c = 0; c < dim; c += 8) {
+      float v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        v[k] = round_bf(synth_value((unsigned long long)(global_row0 + r), c + k, dim, seed, 1.0f / 32768.0f)) * inv;
+      uint4 o;
+      o.x = pack_bf2(v[0], v[1]); o.y = pack_bf2(v[2], v[3]); o.z = pack_bf2(v[4], v[5]); o.w = pack_bf2(v[6], v[7]);
+      *reinterpret_cast<uint4*>(rows_ptr + r * dim + c) = o;
+    }
+  }
+}
+
+}  // namespace
+
+phx_status build_tokens_launch(const TokenBuildArgs& a, cudaStream_t stream, std::string& err) {
+  if (a.D % 8 != 0 || a.item.num_hashes != a.author.num_hashes || 2 * a.item.num_hashes > 32) {
+    err = "build_tokens: D must be a multiple of 8 and hash counts must match";
+    return PHX_E_ARG;
+  }
+  const long long toks = (long long)a.B * (a.S + a.C);
+  if (toks == 0) return PHX_OK;
+  const int warps = 8;
+  build_tokens_kernel<<<(unsigned)((toks + warps - 1) / warps), warps * 32, 0, stream>>>(a);
+  PHX_CUDA_TRY(cudaGetLastError(), err);
+  return PHX_OK;
+}
+
+phx_status hash_ids_launch(const HashFamilyDev& fam, const long long* ids, long long n, int* out, cudaStream_t stream,
+                           std::string& err) {
+  const long long total = n * fam.num_hashes;
+  if (total == 0) return PHX_OK;
+  hash_ids_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(fam, ids, n, out);
+  PHX_CUDA_TRY(cudaGetLastError(), err);
+  return PHX_OK;
+}
+
+phx_status gather_sum_launch(const HashFamilyDev& fam, const bf16* table, long long table_rows, int D,
+                             const long long* ids, long long n, bf16* out, cudaStream_t stream, std::string& err) {
+  if (D % 8 != 0) { err = "gather_sum: D must be a multiple of 8"; return PHX_E_ARG; }
+  if (n == 0) return PHX_OK;
+  if (D <= 128) {
+    gather_sum_kernel<16><<<(unsigned)((n * 16 + 255) / 256), 256, 0, stream>>>(fam, table, table_rows, D, ids, n, out);
+  } else {
+    gather_sum_kernel<32><<<(unsigned)((n * 32 + 255) / 256), 256, 0, stream>>>(fam, table, table_rows, D, ids, n, out);
+  }
+  PHX_CUDA_TRY(cudaGetLastError(), err);
+  return PHX_OK;
+}
+
+phx_status table_fill_launch(bf16* table, long long row0, long long rows, int width, uint32_t seed, float amp,
+                             cudaStream_t stream, std::string& err) {
+  if (rows == 0) return PHX_OK;
+  table_fill_kernel<<<148 * 8, 256, 0, stream>>>(table, row0, rows, width, seed, amp / 32768.0f);
+  PHX_CUDA_TRY(cudaGetLastError(), err);
+  return PHX_OK;
+}
+
+phx_status corpus_fill_launch(bf16* rows_ptr, long long global_row0, long long rows, int dim, uint32_t seed,
+                              cudaStream_t stream, std::string& err) {
+  if (rows == 0) return PHX_OK;
+  corpus_fill_kernel<<<148 * 8, 256, 0, stream>>>(rows_ptr, global_row0, rows, dim, seed);
+  PHX_CUDA_TRY(cudaGetLastError(), err);
+  return PHX_OK;
+}
+
+}  // namespace phx

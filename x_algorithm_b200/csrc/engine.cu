@@ -1,0 +1,737 @@
+// C ABI of the Phoenix B200 engine (include/phoenix_b200.h): owns weights, the unified embedding
+// table and work space, and sequences the kernels of one ranking forward / user-tower pass on one
+// stream.  Mirrors the model runner's gather -> forward -> reply sequence
+// (phoenix/xrex/inference/model_runner.py:4141-4222) and the model's forward
+// (phoenix/xrex/models/recsys_model.py:6082-6224 -> 4734-4883, transformer.py:461-618).
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <map>
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+
+namespace phx {
+
+static std::mutex g_err_mu;
+static std::string g_err = "";
+void set_global_error(const std::string& msg) {
+  std::lock_guard<std::mutex> lk(g_err_mu);
+  g_err = msg;
+}
+
+static inline uint16_t f32_to_bf16_bits(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x40);  // NaN
+  uint32_t r = ((u >> 16) & 1u) + 0x7FFFu;
+  return (uint16_t)((u + r) >> 16);
+}
+static inline float bf16_bits_to_f32(uint16_t b) {
+  uint32_t u = (uint32_t)b << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+struct Layer {
+  float* pre_attn_norm = nullptr;
+  float* pre_ffn_norm = nullptr;
+  float* post_attn_norm = nullptr;
+  float* post_ffn_norm = nullptr;
+  float* q_norm = nullptr;
+  float* k_norm = nullptr;
+  bf16* w_qkv_t = nullptr;   // [QW, D]
+  bf16* w_out_t = nullptr;   // [D, HD]
+  bf16* w_up_t = nullptr;    // [F, D]
+  bf16* w_down_t = nullptr;  // [D, F]
+  GemmPlan p_qkv, p_out, p_up, p_down;
+};
+
+}  // namespace phx
+
+using namespace phx;
+
+struct phx_engine {
+  phx_model_config cfg;
+  int device = 0;
+  int num_sms = 148;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  std::string err;
+  bool use_simt_gemm = false;
+
+  // dimensions
+  int D, S, C, T, Hq, Hkv, dh, F, QW, HD, V, NC;
+  long long table_rows = 0;
+  long long max_tokens = 0;
+
+  // parameters
+  bf16* table = nullptr;
+  bf16* action_table = nullptr;
+  bf16* surface_table = nullptr;
+  float* final_norm = nullptr;
+  bf16* unembed_t = nullptr;  // [V+NC, D]
+  std::vector<Layer> layers;
+  std::map<std::string, bool> loaded;
+  float *cos_tab = nullptr, *sin_tab = nullptr;
+  phx_blend_spec blend;
+  bool has_blend = false;
+
+  // work space
+  bf16 *x = nullptr, *hbuf = nullptr, *qkv = nullptr, *attn = nullptr, *ffn = nullptr, *tmp = nullptr, *tokens = nullptr;
+  int* seg = nullptr;
+  int* hashes = nullptr;
+  int* err_flag = nullptr;
+  // staging for the host-buffer entry point
+  void* in_stage_dev = nullptr;
+  void* in_stage_host = nullptr;
+  size_t in_stage_bytes = 0;
+  float* lp_dev = nullptr; float* cont_dev = nullptr; double* score_dev = nullptr;
+  float* lp_host = nullptr; float* cont_host = nullptr; double* score_host = nullptr;
+
+  int last_batch = 0;
+  int last_launches = 0;
+  bool debug_taps = false;
+
+  // optional per-kernel-class timing (phx_profile_enable): events around every launch
+  bool profile = false;
+  std::vector<std::pair<int, std::pair<cudaEvent_t, cudaEvent_t>>> prof_events;  // (class, (start, stop))
+  size_t prof_used = 0;
+  cudaEvent_t marks[4] = {nullptr, nullptr, nullptr, nullptr};
+};
+
+namespace {
+enum KernelClass { KC_TOKENS = 0, KC_NORM = 1, KC_GEMM = 2, KC_ROPE = 3, KC_ATTN = 4, KC_HEADS = 5, KC_COUNT = 6 };
+struct ProfScope {
+  phx_engine* e; cudaEvent_t stop = nullptr;
+  ProfScope(phx_engine* e_, int cls) : e(e_) {
+    if (!e->profile) return;
+    if (e->prof_used == e->prof_events.size()) {
+      cudaEvent_t a, b; cudaEventCreate(&a); cudaEventCreate(&b);
+      e->prof_events.push_back({cls, {a, b}});
+    }
+    auto& pe = e->prof_events[e->prof_used++];
+    pe.first = cls;
+    cudaEventRecord(pe.second.first, e->stream);
+    stop = pe.second.second;
+  }
+  ~ProfScope() { if (stop) cudaEventRecord(stop, e->stream); }
+};
+}  // namespace
+
+namespace {
+
+template <typename Tp>
+phx_status dev_alloc(phx_engine* e, Tp** p, size_t count) {
+  PHX_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(p), count * sizeof(Tp)), e->err);
+  return PHX_OK;
+}
+
+HashFamilyDev to_dev(const phx_hash_family& f, int offset) {
+  HashFamilyDev d;
+  for (int i = 0; i < PHX_MAX_HASHES; ++i) { d.scales[i] = f.scales[i]; d.biases[i] = f.biases[i]; }
+  d.modulus = f.modulus;
+  d.buckets_m1 = f.table_size - 1;
+  d.offset = offset;
+  d.num_hashes = f.num_hashes;
+  return d;
+}
+
+// region offsets of the unified table: phoenix/xrex/models/recsys_embedding.py:234-248
+void region_offsets(const phx_model_config& c, long long* user, long long* item, long long* author, long long* ip,
+                    long long* total) {
+  *user = 1 + 64;
+  *item = *user + c.user.table_size;
+  *author = *item + c.item.table_size;
+  *ip = *author + c.author.table_size;
+  *total = *ip + c.ip.table_size;
+}
+
+phx_status check_cfg(const phx_model_config& c, std::string& err) {
+  auto bad = [&](const char* m) { err = std::string("config: ") + m; return PHX_E_ARG; };
+  if (c.emb_size <= 0 || c.emb_size % 64 != 0) return bad("emb_size must be a positive multiple of 64");
+  if (c.key_size != 32 && c.key_size != 64 && c.key_size != 128) return bad("key_size must be 32, 64 or 128");
+  if (c.num_q_heads <= 0 || c.num_kv_heads <= 0 || c.num_q_heads % c.num_kv_heads != 0) return bad("head counts");
+  if (c.ffn_size <= 0 || c.ffn_size % 64 != 0) return bad("ffn_size must be a positive multiple of 64");
+  if (c.num_layers <= 0 || c.history_len <= 0 || c.num_candidates < 0 || c.max_batch <= 0) return bad("sizes");
+  if (c.num_actions < 0 || c.num_continuous < 0 || c.num_actions + c.num_continuous > 32) return bad("at most 32 heads");
+  if (c.num_candidates > 0 && c.num_actions + c.num_continuous == 0) return bad("ranking engine needs heads");
+  const phx_hash_family* fams[4] = {&c.user, &c.item, &c.author, &c.ip};
+  for (auto f : fams) {
+    if (f->num_hashes < 0 || f->num_hashes > PHX_MAX_HASHES) return bad("num_hashes out of range");
+    if (f->table_size < 0 || (f->num_hashes > 0 && (f->table_size < 2 || f->modulus <= 0))) return bad("hash family");
+  }
+  if (c.item.num_hashes <= 0 || c.item.num_hashes != c.author.num_hashes) return bad("item/author hash counts must match");
+  if (c.cap_method < 0 || c.cap_method > 2) return bad("cap_method");
+  return PHX_OK;
+}
+
+phx_status upload_f32(phx_engine* e, float** dst, const float* host, size_t n, bool round_bf16) {
+  std::vector<float> tmp(host, host + n);
+  if (round_bf16) for (auto& v : tmp) v = bf16_bits_to_f32(f32_to_bf16_bits(v));
+  if (!*dst) { phx_status s = dev_alloc(e, dst, n); if (s) return s; }
+  PHX_CUDA_TRY(cudaMemcpy(*dst, tmp.data(), n * sizeof(float), cudaMemcpyHostToDevice), e->err);
+  return PHX_OK;
+}
+// host [rows, cols] f32 (in, out) -> device bf16; transposed to [cols, rows] when `transpose`
+phx_status upload_bf16(phx_engine* e, bf16** dst, const float* host, int64_t rows, int64_t cols, bool transpose) {
+  std::vector<uint16_t> tmp((size_t)rows * cols);
+  if (transpose) {
+    for (int64_t r = 0; r < rows; ++r)
+      for (int64_t c = 0; c < cols; ++c) tmp[(size_t)c * rows + r] = f32_to_bf16_bits(host[(size_t)r * cols + c]);
+  } else {
+    for (size_t i = 0; i < tmp.size(); ++i) tmp[i] = f32_to_bf16_bits(host[i]);
+  }
+  if (!*dst) { phx_status s = dev_alloc(e, dst, tmp.size()); if (s) return s; }
+  PHX_CUDA_TRY(cudaMemcpy(*dst, tmp.data(), tmp.size() * 2, cudaMemcpyHostToDevice), e->err);
+  return PHX_OK;
+}
+
+phx_status do_gemm(phx_engine* e, const GemmPlan& p, bf16* Cc, const bf16* R, int64_t M, int epi) {
+  ProfScope ps(e, KC_GEMM);
+  e->last_launches++;
+  if (e->use_simt_gemm) return gemm_simt_launch(p.A, p.Wt, Cc, R, M, p.N, p.K, epi, e->stream, e->err);
+  return gemm_launch(p, Cc, R, M, epi, e->err_flag, e->num_sms, e->stream, e->err);
+}
+
+bool params_complete(phx_engine* e, bool need_heads) {
+  std::vector<std::string> need = {"action_table", "surface_table", "final_norm"};
+  if (need_heads) {
+    if (e->V > 0) need.push_back("unembed");
+    if (e->NC > 0) need.push_back("cont_unembed");
+  }
+  for (int l = 0; l < e->cfg.num_layers; ++l) {
+    std::string p = "layer" + std::to_string(l) + ".";
+    for (const char* n : {"pre_attn_norm", "w_qkv", "w_out", "pre_ffn_norm", "w_up", "w_down"}) need.push_back(p + n);
+    if (e->cfg.qk_norm) { need.push_back(p + "q_norm"); need.push_back(p + "k_norm"); }
+    if (e->cfg.primer_norm) { need.push_back(p + "post_attn_norm"); need.push_back(p + "post_ffn_norm"); }
+  }
+  for (auto& n : need)
+    if (!e->loaded.count(n)) { e->err = "parameter not loaded: " + n; return false; }
+  return true;
+}
+
+// trunk over `Tt` tokens per request (history + candidates, or history only for the tower)
+phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len) {
+  const long long M = (long long)B * Tt;
+  const phx_model_config& c = e->cfg;
+  const float sm_scale = sqrtf(128.0f) / (float)c.key_size;  // phoenix/xrex/models/scaling.py:46-47
+  phx_status s;
+  for (int l = 0; l < c.num_layers; ++l) {
+    Layer& L = e->layers[l];
+    { ProfScope ps(e, KC_NORM);
+    if ((s = rmsnorm_launch(e->x, L.pre_attn_norm, e->hbuf, nullptr, M, e->D, c.rms_eps, e->stream, e->err))) return s; }
+    e->last_launches++;
+    if ((s = do_gemm(e, L.p_qkv, e->qkv, nullptr, M, EPI_STORE))) return s;
+    if (c.rotary || c.qk_norm) {
+      QkNormRopeArgs qa;
+      qa.qkv = e->qkv; qa.M = M; qa.T = Tt; qa.Hq = e->Hq; qa.Hkv = e->Hkv; qa.dh = e->dh; qa.pos_cap = pos_cap;
+      qa.rotary = c.rotary; qa.qk_norm = c.qk_norm; qa.q_gain = L.q_norm; qa.k_gain = L.k_norm;
+      qa.cos_tab = e->cos_tab; qa.sin_tab = e->sin_tab;
+      { ProfScope ps(e, KC_ROPE); if ((s = qknorm_rope_launch(qa, e->stream, e->err))) return s; }
+      e->last_launches++;
+    }
+    AttnArgs aa;
+    const int g = e->Hq / e->Hkv;
+    aa.q = e->qkv; aa.k = e->qkv + (long long)g * e->dh; aa.v = e->qkv + (long long)(g + 1) * e->dh;
+    aa.q_tok_stride = aa.k_tok_stride = aa.v_tok_stride = e->QW;
+    // q head h sits at column ((h / g) * (g + 2) + h % g) * dh; for g == 1 that is h * 3 * dh.  The kernel
+    // takes a constant head stride, so grouped-query layouts are handled by the (g + 2) * dh stride of kv
+    // heads and require g == 1 for q here.
+    aa.q_head_stride = (g + 2) * e->dh; aa.k_head_stride = (g + 2) * e->dh; aa.v_head_stride = (g + 2) * e->dh;
+    aa.out = e->attn; aa.seg = e->seg; aa.B = B; aa.T = Tt; aa.Hq = e->Hq; aa.Hkv = e->Hkv; aa.dh = e->dh;
+    aa.hist_len = hist_len; aa.sm_scale = sm_scale; aa.cap = c.attn_logit_cap;
+    aa.cap_method = (c.attn_logit_cap > 0.f) ? c.cap_method : 0;
+    { ProfScope ps(e, KC_ATTN); if ((s = ranker_attention_launch(aa, e->stream, e->err))) return s; }
+    e->last_launches++;
+    if (c.primer_norm) {
+      // x = x + post_attn_norm(out(attn)) (transformer.py:531-541)
+      if ((s = do_gemm(e, L.p_out, e->tmp, nullptr, M, EPI_STORE))) return s;
+      { ProfScope ps(e, KC_NORM); if ((s = rmsnorm_launch(e->tmp, L.post_attn_norm, e->x, e->x, M, e->D, c.rms_eps, e->stream, e->err))) return s; }
+      e->last_launches++;
+    } else {
+      if ((s = do_gemm(e, L.p_out, e->x, e->x, M, EPI_RESIDUAL))) return s;
+    }
+    { ProfScope ps(e, KC_NORM); if ((s = rmsnorm_launch(e->x, L.pre_ffn_norm, e->hbuf, nullptr, M, e->D, c.rms_eps, e->stream, e->err))) return s; }
+    e->last_launches++;
+    if ((s = do_gemm(e, L.p_up, e->ffn, nullptr, M, EPI_GELU))) return s;
+    if (c.primer_norm) {
+      if ((s = do_gemm(e, L.p_down, e->tmp, nullptr, M, EPI_STORE))) return s;
+      { ProfScope ps(e, KC_NORM); if ((s = rmsnorm_launch(e->tmp, L.post_ffn_norm, e->x, e->x, M, e->D, c.rms_eps, e->stream, e->err))) return s; }
+      e->last_launches++;
+    } else {
+      if ((s = do_gemm(e, L.p_down, e->x, e->x, M, EPI_RESIDUAL))) return s;
+    }
+  }
+  return PHX_OK;
+}
+
+phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc) {
+  long long ou, oi, oa, oip, tot;
+  region_offsets(e->cfg, &ou, &oi, &oa, &oip, &tot);
+  TokenBuildArgs ta;
+  ta.hist_post = (const long long*)bd->hist_post_ids; ta.hist_author = (const long long*)bd->hist_author_ids;
+  ta.hist_actions = bd->hist_actions; ta.hist_surfaces = bd->hist_surfaces;
+  ta.cand_post = (const long long*)bd->cand_post_ids; ta.cand_author = (const long long*)bd->cand_author_ids;
+  ta.table = e->table; ta.table_rows = e->table_rows;
+  ta.action_table = e->action_table; ta.surface_table = e->surface_table;
+  ta.num_action_types = e->cfg.num_action_types; ta.num_surfaces = e->cfg.num_surfaces;
+  ta.item = to_dev(e->cfg.item, (int)oi); ta.author = to_dev(e->cfg.author, (int)oa);
+  ta.B = B; ta.S = e->S; ta.C = Cc; ta.D = e->D;
+  ta.input_scale = sqrtf((float)e->D);  // scaling.py:40-41
+  ta.x = e->x; ta.tokens = e->debug_taps ? e->tokens : nullptr; ta.hashes = e->debug_taps ? e->hashes : nullptr;
+  ta.seg = e->seg;
+  e->last_launches++;
+  ProfScope ps(e, KC_TOKENS);
+  return build_tokens_launch(ta, e->stream, e->err);
+}
+
+phx_status check_err_flag(phx_engine* e) {
+  int flag = 0;
+  PHX_CUDA_TRY(cudaMemcpy(&flag, e->err_flag, sizeof(int), cudaMemcpyDeviceToHost), e->err);
+  if (flag != 0) {
+    cudaMemset(e->err_flag, 0, sizeof(int));
+    e->err = "a bounded device-side wait ran out (GEMM pipeline)";
+    return PHX_E_TIMEOUT;
+  }
+  return PHX_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* phx_global_error(void) { return g_err.c_str(); }
+const char* phx_last_error(const phx_engine* e) { return e ? e->err.c_str() : g_err.c_str(); }
+
+phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_engine** out) {
+  if (!cfg || !out) { set_global_error("phx_engine_create: null argument"); return PHX_E_ARG; }
+  std::string err;
+  phx_status s = check_cfg(*cfg, err);
+  if (s) { set_global_error(err); return s; }
+  phx_engine* e = new phx_engine();
+  e->cfg = *cfg; e->device = device;
+  auto fail = [&](phx_status st) { set_global_error(e->err); phx_engine_destroy(e); return st; };
+  if (cudaSetDevice(device) != cudaSuccess) { e->err = "cudaSetDevice failed"; return fail(PHX_E_CUDA); }
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { e->err = "cudaGetDeviceProperties failed"; return fail(PHX_E_CUDA); }
+  if (prop.major != 10) { e->err = "this library is built for sm_100a (B200) only"; return fail(PHX_E_ARG); }
+  e->num_sms = prop.multiProcessorCount;
+  const char* gi = getenv("PHX_GEMM");
+  e->use_simt_gemm = gi && strcmp(gi, "simt") == 0;
+  const char* dt = getenv("PHX_DEBUG_TAPS");
+  e->debug_taps = dt && dt[0] == '1';
+  e->D = cfg->emb_size; e->S = cfg->history_len; e->C = cfg->num_candidates; e->T = e->S + e->C;
+  e->Hq = cfg->num_q_heads; e->Hkv = cfg->num_kv_heads; e->dh = cfg->key_size; e->F = cfg->ffn_size;
+  e->QW = (e->Hq + 2 * e->Hkv) * e->dh; e->HD = e->Hq * e->dh; e->V = cfg->num_actions; e->NC = cfg->num_continuous;
+  if (e->Hq != e->Hkv) { e->err = "grouped-query attention is not supported by this build (num_q_heads must equal num_kv_heads)"; return fail(PHX_E_ARG); }
+  long long ou, oi, oa, oip, tot;
+  region_offsets(*cfg, &ou, &oi, &oa, &oip, &tot);
+  e->table_rows = tot;
+  e->max_tokens = (long long)cfg->max_batch * e->T;
+  const long long M = e->max_tokens;
+#define TRY(x) do { phx_status _s = (x); if (_s) return fail(_s); } while (0)
+#define CU(x) do { cudaError_t _c = (x); if (_c != cudaSuccess) { e->err = std::string(#x) + ": " + cudaGetErrorString(_c); return fail(PHX_E_CUDA); } } while (0)
+  CU(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
+  CU(cudaEventCreate(&e->ev0)); CU(cudaEventCreate(&e->ev1));
+  TRY(dev_alloc(e, &e->table, (size_t)tot * e->D));
+  CU(cudaMemset(e->table, 0, (size_t)tot * e->D * 2));
+  TRY(dev_alloc(e, &e->x, (size_t)M * e->D));
+  TRY(dev_alloc(e, &e->hbuf, (size_t)M * e->D));
+  TRY(dev_alloc(e, &e->qkv, (size_t)M * e->QW));
+  TRY(dev_alloc(e, &e->attn, (size_t)M * e->HD));
+  TRY(dev_alloc(e, &e->ffn, (size_t)M * e->F));
+  TRY(dev_alloc(e, &e->seg, (size_t)M));
+  if (cfg->primer_norm) TRY(dev_alloc(e, &e->tmp, (size_t)M * e->D));
+  if (e->debug_taps) {
+    TRY(dev_alloc(e, &e->tokens, (size_t)M * e->D));
+    TRY(dev_alloc(e, &e->hashes, (size_t)M * 2 * cfg->item.num_hashes));
+  }
+  TRY(dev_alloc(e, &e->err_flag, 1));
+  CU(cudaMemset(e->err_flag, 0, sizeof(int)));
+  // RoPE tables: angle = pos * base^(-2j/dh), positions 0..S (layers.py:52-60)
+  {
+    const int half = e->dh / 2, npos = e->S + 1;
+    std::vector<float> ct((size_t)npos * half), st((size_t)npos * half);
+    for (int j = 0; j < half; ++j) {
+      const float expo = (float)(2 * j) / (float)e->dh;
+      const float inv_freq = 1.0f / powf(cfg->rope_base, expo);
+      for (int p = 0; p < npos; ++p) {
+        const float ang = (float)p * inv_freq;
+        ct[(size_t)p * half + j] = cosf(ang);
+        st[(size_t)p * half + j] = sinf(ang);
+      }
+    }
+    TRY(dev_alloc(e, &e->cos_tab, ct.size())); TRY(dev_alloc(e, &e->sin_tab, st.size()));
+    CU(cudaMemcpy(e->cos_tab, ct.data(), ct.size() * 4, cudaMemcpyHostToDevice));
+    CU(cudaMemcpy(e->sin_tab, st.data(), st.size() * 4, cudaMemcpyHostToDevice));
+  }
+  e->layers.resize(cfg->num_layers);
+  for (auto& L : e->layers) {
+    TRY(dev_alloc(e, &L.w_qkv_t, (size_t)e->QW * e->D));
+    TRY(dev_alloc(e, &L.w_out_t, (size_t)e->D * e->HD));
+    TRY(dev_alloc(e, &L.w_up_t, (size_t)e->F * e->D));
+    TRY(dev_alloc(e, &L.w_down_t, (size_t)e->D * e->F));
+    TRY(gemm_plan_create(&L.p_qkv, e->hbuf, L.w_qkv_t, M, e->QW, e->D, e->err));
+    TRY(gemm_plan_create(&L.p_out, e->attn, L.w_out_t, M, e->D, e->HD, e->err));
+    TRY(gemm_plan_create(&L.p_up, e->hbuf, L.w_up_t, M, e->F, e->D, e->err));
+    TRY(gemm_plan_create(&L.p_down, e->ffn, L.w_down_t, M, e->D, e->F, e->err));
+  }
+  if (e->V + e->NC > 0) TRY(dev_alloc(e, &e->unembed_t, (size_t)(e->V + e->NC) * e->D));
+  // staging for the host entry point
+  {
+    const size_t B = cfg->max_batch;
+    e->in_stage_bytes = B * ((size_t)e->S * (8 + 8 + 4 + 4) + (size_t)e->C * 16);
+    CU(cudaMalloc(&e->in_stage_dev, e->in_stage_bytes));
+    CU(cudaMallocHost(&e->in_stage_host, e->in_stage_bytes));
+    const size_t rows = B * (size_t)(e->C > 0 ? e->C : 1);
+    TRY(dev_alloc(e, &e->lp_dev, rows * (e->V > 0 ? e->V : 1)));
+    TRY(dev_alloc(e, &e->cont_dev, rows * (e->NC > 0 ? e->NC : 1)));
+    TRY(dev_alloc(e, &e->score_dev, rows));
+    CU(cudaMallocHost(reinterpret_cast<void**>(&e->lp_host), rows * (e->V > 0 ? e->V : 1) * 4));
+    CU(cudaMallocHost(reinterpret_cast<void**>(&e->cont_host), rows * (e->NC > 0 ? e->NC : 1) * 4));
+    CU(cudaMallocHost(reinterpret_cast<void**>(&e->score_host), rows * 8));
+  }
+#undef TRY
+#undef CU
+  *out = e;
+  return PHX_OK;
+}
+
+void phx_engine_destroy(phx_engine* e) {
+  if (!e) return;
+  cudaSetDevice(e->device);
+  if (e->stream) cudaStreamSynchronize(e->stream);
+  auto fr = [](void* p) { if (p) cudaFree(p); };
+  fr(e->table); fr(e->action_table); fr(e->surface_table); fr(e->final_norm); fr(e->unembed_t);
+  for (auto& L : e->layers) {
+    fr(L.pre_attn_norm); fr(L.pre_ffn_norm); fr(L.post_attn_norm); fr(L.post_ffn_norm); fr(L.q_norm); fr(L.k_norm);
+    fr(L.w_qkv_t); fr(L.w_out_t); fr(L.w_up_t); fr(L.w_down_t);
+  }
+  fr(e->cos_tab); fr(e->sin_tab); fr(e->x); fr(e->hbuf); fr(e->qkv); fr(e->attn); fr(e->ffn); fr(e->tmp); fr(e->tokens);
+  fr(e->seg); fr(e->hashes); fr(e->err_flag); fr(e->in_stage_dev); fr(e->lp_dev); fr(e->cont_dev); fr(e->score_dev);
+  if (e->in_stage_host) cudaFreeHost(e->in_stage_host);
+  if (e->lp_host) cudaFreeHost(e->lp_host);
+  if (e->cont_host) cudaFreeHost(e->cont_host);
+  if (e->score_host) cudaFreeHost(e->score_host);
+  if (e->ev0) cudaEventDestroy(e->ev0);
+  if (e->ev1) cudaEventDestroy(e->ev1);
+  for (auto& pe : e->prof_events) { cudaEventDestroy(pe.second.first); cudaEventDestroy(pe.second.second); }
+  for (auto m : e->marks) if (m) cudaEventDestroy(m);
+  if (e->stream) cudaStreamDestroy(e->stream);
+  delete e;
+}
+
+phx_status phx_load_param(phx_engine* e, const char* name, const float* host, int64_t rows, int64_t cols) {
+  if (!e || !name || !host) return PHX_E_ARG;
+  cudaSetDevice(e->device);
+  const std::string n(name);
+  auto shape = [&](int64_t r, int64_t c) {
+    if (rows == r && cols == c) return true;
+    e->err = "phx_load_param(" + n + "): expected [" + std::to_string(r) + "," + std::to_string(c) + "], got [" +
+             std::to_string(rows) + "," + std::to_string(cols) + "]";
+    return false;
+  };
+  phx_status s = PHX_E_ARG;
+  if (n == "action_table") { if (!shape(e->cfg.num_action_types + 1, e->D)) return PHX_E_ARG; s = upload_bf16(e, &e->action_table, host, rows, cols, false); }
+  else if (n == "surface_table") { if (!shape(e->cfg.num_surfaces + 1, e->D)) return PHX_E_ARG; s = upload_bf16(e, &e->surface_table, host, rows, cols, false); }
+  else if (n == "final_norm") { if (!shape(1, e->D)) return PHX_E_ARG; s = upload_f32(e, &e->final_norm, host, e->D, true); }
+  else if (n == "unembed" || n == "cont_unembed") {
+    const bool cont = n == "cont_unembed";
+    const int nout = cont ? e->NC : e->V;
+    if (!shape(e->D, nout)) return PHX_E_ARG;
+    std::vector<uint16_t> tmp((size_t)nout * e->D);
+    for (int r = 0; r < e->D; ++r) for (int c = 0; c < nout; ++c) tmp[(size_t)c * e->D + r] = f32_to_bf16_bits(host[(size_t)r * nout + c]);
+    cudaError_t ce = cudaMemcpy(e->unembed_t + (size_t)(cont ? e->V : 0) * e->D, tmp.data(), tmp.size() * 2, cudaMemcpyHostToDevice);
+    if (ce != cudaSuccess) { e->err = cudaGetErrorString(ce); return PHX_E_CUDA; }
+    s = PHX_OK;
+  } else if (n.rfind("layer", 0) == 0) {
+    const size_t dot = n.find('.');
+    if (dot == std::string::npos) { e->err = "unknown parameter " + n; return PHX_E_ARG; }
+    const int l = atoi(n.substr(5, dot - 5).c_str());
+    if (l < 0 || l >= (int)e->layers.size()) { e->err = "layer index out of range: " + n; return PHX_E_ARG; }
+    Layer& L = e->layers[l];
+    const std::string f = n.substr(dot + 1);
+    if (f == "pre_attn_norm") { if (!shape(1, e->D)) return PHX_E_ARG; s = upload_f32(e, &L.pre_attn_norm, host, e->D, true); }
+    else if (f == "pre_ffn_norm") { if (!shape(1, e->D)) return PHX_E_ARG; s = upload_f32(e, &L.pre_ffn_norm, host, e->D, true); }
+    else if (f == "post_attn_norm") { if (!shape(1, e->D)) return PHX_E_ARG; s = upload_f32(e, &L.post_attn_norm, host, e->D, true); }
+    else if (f == "post_ffn_norm") { if (!shape(1, e->D)) return PHX_E_ARG; s = upload_f32(e, &L.post_ffn_norm, host, e->D, true); }
+    else if (f == "q_norm") { if (!shape(1, e->HD)) return PHX_E_ARG; s = upload_f32(e, &L.q_norm, host, e->HD, true); }
+    else if (f == "k_norm") { if (!shape(1, e->Hkv * e->dh)) return PHX_E_ARG; s = upload_f32(e, &L.k_norm, host, e->Hkv * e->dh, true); }
+    else if (f == "w_qkv") { if (!shape(e->D, e->QW)) return PHX_E_ARG; s = upload_bf16(e, &L.w_qkv_t, host, rows, cols, true); }
+    else if (f == "w_out") { if (!shape(e->HD, e->D)) return PHX_E_ARG; s = upload_bf16(e, &L.w_out_t, host, rows, cols, true); }
+    else if (f == "w_up") { if (!shape(e->D, e->F)) return PHX_E_ARG; s = upload_bf16(e, &L.w_up_t, host, rows, cols, true); }
+    else if (f == "w_down") { if (!shape(e->F, e->D)) return PHX_E_ARG; s = upload_bf16(e, &L.w_down_t, host, rows, cols, true); }
+    else { e->err = "unknown parameter " + n; return PHX_E_ARG; }
+  } else { e->err = "unknown parameter " + n; return PHX_E_ARG; }
+  if (s == PHX_OK) e->loaded[n] = true;
+  return s;
+}
+
+phx_status phx_table_upload(phx_engine* e, int64_t row0, int64_t nrows, const uint16_t* host_bf16) {
+  if (!e || !host_bf16 || row0 < 0 || nrows < 0 || row0 + nrows > e->table_rows) { if (e) e->err = "phx_table_upload: range"; return PHX_E_ARG; }
+  cudaSetDevice(e->device);
+  PHX_CUDA_TRY(cudaMemcpy(e->table + row0 * e->D, host_bf16, (size_t)nrows * e->D * 2, cudaMemcpyHostToDevice), e->err);
+  return PHX_OK;
+}
+
+phx_status phx_table_fill_synthetic(phx_engine* e, uint32_t seed, float amp) {
+  if (!e) return PHX_E_ARG;
+  cudaSetDevice(e->device);
+  phx_status s = table_fill_launch(e->table, 0, e->table_rows, e->D, seed, amp, e->stream, e->err);
+  if (s) return s;
+  PHX_CUDA_TRY(cudaStreamSynchronize(e->stream), e->err);
+  return PHX_OK;
+}
+
+phx_status phx_set_blend(phx_engine* e, const phx_blend_spec* spec) {
+  if (!e || !spec || spec->num_terms < 0 || spec->num_terms > PHX_MAX_BLEND_TERMS) { if (e) e->err = "phx_set_blend: bad spec"; return PHX_E_ARG; }
+  for (int i = 0; i < spec->num_terms; ++i)
+    if (spec->src[i] < 0 || spec->src[i] >= e->V + e->NC) { e->err = "phx_set_blend: term source out of range"; return PHX_E_ARG; }
+  e->blend = *spec; e->has_blend = true;
+  return PHX_OK;
+}
+
+phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* bd, const phx_rank_out* od) {
+  if (!e || !bd || !od) return PHX_E_ARG;
+  if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
+  if (bd->batch < 0 || bd->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
+  if (!params_complete(e, true)) return PHX_E_STATE;
+  cudaSetDevice(e->device);
+  const int B = bd->batch;
+  e->last_batch = B; e->last_launches = 0; e->prof_used = 0;
+  if (B == 0) return PHX_OK;
+  PHX_CUDA_TRY(cudaEventRecord(e->ev0, e->stream), e->err);
+  phx_status s;
+  if ((s = build_tokens(e, bd, B, e->C))) return s;
+  if ((s = run_trunk(e, B, e->T, e->S, e->S))) return s;
+  HeadsArgs ha;
+  ha.x = e->x; ha.final_gain = e->final_norm; ha.unembed_t = e->unembed_t;
+  ha.B = B; ha.T = e->T; ha.S = e->S; ha.C = e->C; ha.D = e->D; ha.V = e->V; ha.NC = e->NC;
+  ha.eps = e->cfg.rms_eps; ha.output_scale = 2.0f * sqrtf(512.0f / (float)e->D);  // scaling.py:43-44
+  ha.final_logit_cap = e->cfg.final_logit_cap; ha.dwell_norm_scale = e->cfg.dwell_norm_scale;
+  ha.has_blend = e->has_blend ? 1 : 0;
+  if (e->has_blend) ha.blend = e->blend; else memset(&ha.blend, 0, sizeof(ha.blend));
+  ha.log_probs = od->log_probs; ha.continuous = od->continuous; ha.scores = od->scores;
+  { ProfScope ps(e, KC_HEADS); if ((s = heads_launch(ha, e->stream, e->err))) return s; }
+  e->last_launches++;
+  PHX_CUDA_TRY(cudaEventRecord(e->ev1, e->stream), e->err);
+  return PHX_OK;
+}
+
+phx_status phx_rank_forward(phx_engine* e, const phx_rank_batch* bh, const phx_rank_out* oh) {
+  if (!e || !bh || !oh) return PHX_E_ARG;
+  if (bh->batch < 0 || bh->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
+  cudaSetDevice(e->device);
+  const size_t B = bh->batch, S = e->S, C = e->C;
+  if (B == 0) return PHX_OK;
+  // pack the six input arrays into one pinned block -> one H2D copy
+  uint8_t* hp = (uint8_t*)e->in_stage_host;
+  uint8_t* dp = (uint8_t*)e->in_stage_dev;
+  size_t off = 0;
+  phx_rank_batch bd; bd.batch = bh->batch; bd._pad = 0;
+  auto put = [&](const void* src, size_t bytes) { memcpy(hp + off, src, bytes); const void* d = dp + off; off += bytes; return d; };
+  bd.hist_post_ids = (const int64_t*)put(bh->hist_post_ids, B * S * 8);
+  bd.hist_author_ids = (const int64_t*)put(bh->hist_author_ids, B * S * 8);
+  bd.cand_post_ids = (const int64_t*)put(bh->cand_post_ids, B * C * 8);
+  bd.cand_author_ids = (const int64_t*)put(bh->cand_author_ids, B * C * 8);
+  bd.hist_actions = (const int32_t*)put(bh->hist_actions, B * S * 4);
+  bd.hist_surfaces = (const int32_t*)put(bh->hist_surfaces, B * S * 4);
+  PHX_CUDA_TRY(cudaMemcpyAsync(dp, hp, off, cudaMemcpyHostToDevice, e->stream), e->err);
+  phx_rank_out od; od.log_probs = e->lp_dev; od.continuous = e->cont_dev; od.scores = e->score_dev;
+  phx_status s = phx_rank_forward_device(e, &bd, &od);
+  if (s) return s;
+  const size_t rows = B * C;
+  if (oh->log_probs) PHX_CUDA_TRY(cudaMemcpyAsync(e->lp_host, e->lp_dev, rows * e->V * 4, cudaMemcpyDeviceToHost, e->stream), e->err);
+  if (oh->continuous) PHX_CUDA_TRY(cudaMemcpyAsync(e->cont_host, e->cont_dev, rows * e->NC * 4, cudaMemcpyDeviceToHost, e->stream), e->err);
+  if (oh->scores && e->has_blend) PHX_CUDA_TRY(cudaMemcpyAsync(e->score_host, e->score_dev, rows * 8, cudaMemcpyDeviceToHost, e->stream), e->err);
+  PHX_CUDA_TRY(cudaStreamSynchronize(e->stream), e->err);
+  if (oh->log_probs) memcpy(oh->log_probs, e->lp_host, rows * e->V * 4);
+  if (oh->continuous) memcpy(oh->continuous, e->cont_host, rows * e->NC * 4);
+  if (oh->scores && e->has_blend) memcpy(oh->scores, e->score_host, rows * 8);
+  return check_err_flag(e);
+}
+
+phx_status phx_sync(phx_engine* e) {
+  if (!e) return PHX_E_ARG;
+  cudaSetDevice(e->device);
+  PHX_CUDA_TRY(cudaStreamSynchronize(e->stream), e->err);
+  return check_err_flag(e);
+}
+
+phx_status phx_last_device_ms(phx_engine* e, float* ms) {
+  if (!e || !ms) return PHX_E_ARG;
+  PHX_CUDA_TRY(cudaEventSynchronize(e->ev1), e->err);
+  PHX_CUDA_TRY(cudaEventElapsedTime(ms, e->ev0, e->ev1), e->err);
+  return PHX_OK;
+}
+
+phx_status phx_profile_enable(phx_engine* e, int32_t on) {
+  if (!e) return PHX_E_ARG;
+  e->profile = on != 0;
+  e->prof_used = 0;
+  return PHX_OK;
+}
+
+phx_status phx_profile_read(phx_engine* e, float* ms_by_class, int32_t* launches_by_class) {
+  if (!e || !ms_by_class || !launches_by_class) return PHX_E_ARG;
+  cudaSetDevice(e->device);
+  PHX_CUDA_TRY(cudaStreamSynchronize(e->stream), e->err);
+  for (int i = 0; i < KC_COUNT; ++i) { ms_by_class[i] = 0.f; launches_by_class[i] = 0; }
+  for (size_t i = 0; i < e->prof_used; ++i) {
+    float ms = 0.f;
+    PHX_CUDA_TRY(cudaEventElapsedTime(&ms, e->prof_events[i].second.first, e->prof_events[i].second.second), e->err);
+    ms_by_class[e->prof_events[i].first] += ms;
+    launches_by_class[e->prof_events[i].first] += 1;
+  }
+  return PHX_OK;
+}
+
+phx_status phx_mark(phx_engine* e, int32_t slot) {
+  if (!e || slot < 0 || slot > 3) return PHX_E_ARG;
+  cudaSetDevice(e->device);
+  if (!e->marks[slot]) PHX_CUDA_TRY(cudaEventCreate(&e->marks[slot]), e->err);
+  PHX_CUDA_TRY(cudaEventRecord(e->marks[slot], e->stream), e->err);
+  return PHX_OK;
+}
+
+phx_status phx_elapsed_ms(phx_engine* e, int32_t from_slot, int32_t to_slot, float* ms) {
+  if (!e || !ms || from_slot < 0 || from_slot > 3 || to_slot < 0 || to_slot > 3 || !e->marks[from_slot] || !e->marks[to_slot]) return PHX_E_ARG;
+  PHX_CUDA_TRY(cudaEventSynchronize(e->marks[to_slot]), e->err);
+  PHX_CUDA_TRY(cudaEventElapsedTime(ms, e->marks[from_slot], e->marks[to_slot]), e->err);
+  return PHX_OK;
+}
+
+phx_status phx_last_launch_count(phx_engine* e, int32_t* n) {
+  if (!e || !n) return PHX_E_ARG;
+  *n = e->last_launches;
+  return PHX_OK;
+}
+
+phx_status phx_debug_read(phx_engine* e, const char* what, void* host, size_t nbytes) {
+  if (!e || !what || !host) return PHX_E_ARG;
+  cudaSetDevice(e->device);
+  const std::string w(what);
+  const size_t M = (size_t)e->last_batch * e->T;
+  const void* src = nullptr; size_t avail = 0;
+  if (w == "hidden") { src = e->x; avail = M * e->D * 2; }
+  else if (w == "seg") { src = e->seg; avail = M * 4; }
+  else if (w == "attn") { src = e->attn; avail = M * e->HD * 2; }
+  else if (w == "qkv") { src = e->qkv; avail = M * e->QW * 2; }
+  else if (w == "tokens" && e->debug_taps) { src = e->tokens; avail = M * e->D * 2; }
+  else if (w == "hashes" && e->debug_taps) { src = e->hashes; avail = M * 2 * e->cfg.item.num_hashes * 4; }
+  else { e->err = "phx_debug_read: unknown tap (tokens / hashes need PHX_DEBUG_TAPS=1): " + w; return PHX_E_ARG; }
+  if (nbytes > avail) { e->err = "phx_debug_read: more bytes requested than the tap holds"; return PHX_E_ARG; }
+  PHX_CUDA_TRY(cudaStreamSynchronize(e->stream), e->err);
+  PHX_CUDA_TRY(cudaMemcpy(host, src, nbytes, cudaMemcpyDeviceToHost), e->err);
+  return PHX_OK;
+}
+
+phx_status phx_hash_ids_device(phx_engine* e, int32_t family, const int64_t* ids_dev, int64_t n, int32_t* out_dev) {
+  if (!e || family < 0 || family > 3 || n < 0) return PHX_E_ARG;
+  cudaSetDevice(e->device);
+  long long off[5];
+  region_offsets(e->cfg, &off[0], &off[1], &off[2], &off[3], &off[4]);
+  const phx_hash_family* fams[4] = {&e->cfg.user, &e->cfg.item, &e->cfg.author, &e->cfg.ip};
+  return hash_ids_launch(to_dev(*fams[family], (int)off[family]), (const long long*)ids_dev, n, out_dev, e->stream, e->err);
+}
+
+phx_status phx_gather_sum_device(phx_engine* e, int32_t family, const int64_t* ids_dev, int64_t n, uint16_t* out_dev) {
+  if (!e || family < 0 || family > 3 || n < 0) return PHX_E_ARG;
+  cudaSetDevice(e->device);
+  long long off[5];
+  region_offsets(e->cfg, &off[0], &off[1], &off[2], &off[3], &off[4]);
+  const phx_hash_family* fams[4] = {&e->cfg.user, &e->cfg.item, &e->cfg.author, &e->cfg.ip};
+  PHX_CUDA_TRY(cudaEventRecord(e->ev0, e->stream), e->err);
+  phx_status s = gather_sum_launch(to_dev(*fams[family], (int)off[family]), e->table, e->table_rows, e->D,
+                                   (const long long*)ids_dev, n, (bf16*)out_dev, e->stream, e->err);
+  if (s) return s;
+  PHX_CUDA_TRY(cudaEventRecord(e->ev1, e->stream), e->err);
+  return PHX_OK;
+}
+
+phx_status phx_user_tower_device(phx_engine* e, const phx_rank_batch* bd, float* users_dev) {
+  if (!e || !bd || !users_dev) return PHX_E_ARG;
+  if (bd->batch < 0 || bd->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
+  if (!params_complete(e, false)) return PHX_E_STATE;
+  cudaSetDevice(e->device);
+  const int B = bd->batch;
+  e->last_batch = B; e->last_launches = 0; e->prof_used = 0;
+  if (B == 0) return PHX_OK;
+  PHX_CUDA_TRY(cudaEventRecord(e->ev0, e->stream), e->err);
+  phx_status s;
+  // history only: tokens laid out [B, S]; every valid token is "history" so attention is full among them
+  if ((s = build_tokens(e, bd, B, 0))) return s;
+  if ((s = run_trunk(e, B, e->S, e->S, e->S))) return s;
+  { ProfScope ps(e, KC_HEADS); if ((s = tower_pool_launch(e->x, e->final_norm, e->seg, B, e->S, e->D, e->cfg.rms_eps, users_dev, e->stream, e->err))) return s; }
+  e->last_launches++;
+  PHX_CUDA_TRY(cudaEventRecord(e->ev1, e->stream), e->err);
+  return PHX_OK;
+}
+
+phx_status phx_ranker_attention_device(int32_t device, const uint16_t* q, const uint16_t* k, const uint16_t* v,
+                                       const int32_t* seg, uint16_t* out, int32_t B, int32_t T, int32_t Hq,
+                                       int32_t Hkv, int32_t dh, int32_t hist_len, float sm_scale, float cap,
+                                       int32_t cap_method, float* device_ms) {
+  std::string err;
+  if (cudaSetDevice(device) != cudaSuccess) { set_global_error("cudaSetDevice failed"); return PHX_E_CUDA; }
+  AttnArgs aa;
+  aa.q = (const bf16*)q; aa.k = (const bf16*)k; aa.v = (const bf16*)v;
+  aa.q_tok_stride = (long long)Hq * dh; aa.k_tok_stride = aa.v_tok_stride = (long long)Hkv * dh;
+  aa.q_head_stride = aa.k_head_stride = aa.v_head_stride = dh;
+  aa.out = (bf16*)out; aa.seg = seg; aa.B = B; aa.T = T; aa.Hq = Hq; aa.Hkv = Hkv; aa.dh = dh; aa.hist_len = hist_len;
+  aa.sm_scale = sm_scale; aa.cap = cap; aa.cap_method = cap > 0.f ? cap_method : 0;
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0); cudaEventCreate(&e1);
+  cudaEventRecord(e0, 0);
+  phx_status s = ranker_attention_launch(aa, 0, err);
+  cudaEventRecord(e1, 0);
+  cudaError_t ce = cudaEventSynchronize(e1);
+  if (s == PHX_OK && ce != cudaSuccess) { err = cudaGetErrorString(ce); s = PHX_E_CUDA; }
+  if (s == PHX_OK && device_ms) cudaEventElapsedTime(device_ms, e0, e1);
+  cudaEventDestroy(e0); cudaEventDestroy(e1);
+  if (s) set_global_error(err);
+  return s;
+}
+
+phx_status phx_gemm_device(int32_t device, const uint16_t* A, const uint16_t* Wt, const uint16_t* R, uint16_t* C,
+                           int64_t M, int32_t N, int32_t K, int32_t epilogue, int32_t impl, float* device_ms) {
+  std::string err;
+  if (cudaSetDevice(device) != cudaSuccess) { set_global_error("cudaSetDevice failed"); return PHX_E_CUDA; }
+  cudaDeviceProp prop;
+  cudaGetDeviceProperties(&prop, device);
+  int* flag = nullptr;
+  if (cudaMalloc(&flag, sizeof(int)) != cudaSuccess) { set_global_error("cudaMalloc failed"); return PHX_E_CUDA; }
+  cudaMemset(flag, 0, sizeof(int));
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0); cudaEventCreate(&e1);
+  phx_status s = PHX_OK;
+  if (impl == 1) {
+    cudaEventRecord(e0, 0);
+    s = gemm_simt_launch((const bf16*)A, (const bf16*)Wt, (bf16*)C, (const bf16*)R, M, N, K, epilogue, 0, err);
+    cudaEventRecord(e1, 0);
+  } else {
+    GemmPlan plan;
+    s = gemm_plan_create(&plan, (const bf16*)A, (const bf16*)Wt, M, N, K, err);
+    cudaEventRecord(e0, 0);
+    if (s == PHX_OK) s = gemm_launch(plan, (bf16*)C, (const bf16*)R, M, epilogue, flag, prop.multiProcessorCount, 0, err);
+    cudaEventRecord(e1, 0);
+  }
+  cudaError_t ce = cudaEventSynchronize(e1);
+  if (s == PHX_OK && ce != cudaSuccess) { err = cudaGetErrorString(ce); s = PHX_E_CUDA; }
+  if (s == PHX_OK && device_ms) cudaEventElapsedTime(device_ms, e0, e1);
+  int hflag = 0;
+  if (s == PHX_OK) {
+    cudaMemcpy(&hflag, flag, sizeof(int), cudaMemcpyDeviceToHost);
+    if (hflag) { err = "a bounded device-side wait ran out (GEMM pipeline)"; s = PHX_E_TIMEOUT; }
+  }
+  cudaFree(flag);
+  cudaEventDestroy(e0); cudaEventDestroy(e1);
+  if (s) set_global_error(err);
+  return s;
+}
+
+}  // extern "C"

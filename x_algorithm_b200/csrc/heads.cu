@@ -1,0 +1,177 @@
+// Final RMSNorm of the candidate rows, the action and continuous heads, the server's log-sigmoid
+// and the value-model blend in one pass (phoenix/xrex/models/recsys_model.py:4792-4843, 3557-3560,
+// 3756-3846, 712-733; phoenix/xrex/inference/model_runner.py:4474; xai-value-model/scoring.rs:67-73,
+// 112-120, 282-291).  One warp per candidate row; the (V+NC) x D head matrix sits in shared memory.
+// Also the user-tower pooling (recsys_two_tower_model.py:2187-2200).
+#include "common.cuh"
+
+namespace phx {
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+constexpr int MAX_OUT = 32;  // V + NC
+
+__global__ void __launch_bounds__(256) heads_kernel(HeadsArgs a) {
+  extern __shared__ __align__(16) uint8_t hsm[];
+  bf16* sw = reinterpret_cast<bf16*>(hsm);  // [(V+NC), D]
+  const int NO = a.V + a.NC;
+  for (int i = threadIdx.x * 8; i < NO * a.D; i += blockDim.x * 8)
+    *reinterpret_cast<uint4*>(sw + i) = *reinterpret_cast<const uint4*>(a.unembed_t + i);
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const long long nrows = (long long)a.B * a.C;
+  for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < nrows;
+       r += (long long)gridDim.x * (blockDim.x >> 5)) {
+    const int b = (int)(r / a.C), c = (int)(r % a.C);
+    const bf16* xr = a.x + ((long long)b * a.T + a.S + c) * a.D;
+    float ss = 0.f;
+    for (int k = lane * 8; k < a.D; k += 256) {
+      uint4 u = *reinterpret_cast<const uint4*>(xr + k);
+      float2 p0 = unpack_bf2(u.x), p1 = unpack_bf2(u.y), p2 = unpack_bf2(u.z), p3 = unpack_bf2(u.w);
+      ss += p0.x * p0.x + p0.y * p0.y + p1.x * p1.x + p1.y * p1.y + p2.x * p2.x + p2.y * p2.y + p3.x * p3.x + p3.y * p3.y;
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)a.D + a.eps);
+    float acc[MAX_OUT];
+#pragma unroll
+    for (int j = 0; j < MAX_OUT; ++j) acc[j] = 0.f;
+    for (int k = lane * 8; k < a.D; k += 256) {
+      uint4 u = *reinterpret_cast<const uint4*>(xr + k);
+      float xv[8];
+      float2 p0 = unpack_bf2(u.x), p1 = unpack_bf2(u.y), p2 = unpack_bf2(u.z), p3 = unpack_bf2(u.w);
+      xv[0] = p0.x; xv[1] = p0.y; xv[2] = p1.x; xv[3] = p1.y; xv[4] = p2.x; xv[5] = p2.y; xv[6] = p3.x; xv[7] = p3.y;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) xv[i] = round_bf(xv[i] * rstd * a.final_gain[k + i]);  // normed row is bf16
+#pragma unroll
+      for (int j = 0; j < MAX_OUT; ++j) {
+        if (j < NO) {
+          uint4 w = *reinterpret_cast<const uint4*>(sw + j * a.D + k);
+          float2 w0 = unpack_bf2(w.x), w1 = unpack_bf2(w.y), w2 = unpack_bf2(w.z), w3 = unpack_bf2(w.w);
+          acc[j] += xv[0] * w0.x + xv[1] * w0.y + xv[2] * w1.x + xv[3] * w1.y + xv[4] * w2.x + xv[5] * w2.y + xv[6] * w3.x + xv[7] * w3.y;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < MAX_OUT; ++j)
+      if (j < NO) acc[j] = warp_sum(acc[j]);
+    // every lane now holds all outputs; lane j finishes output j
+    float mine = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAX_OUT; ++j)
+      if (j == lane) mine = acc[j];
+    float value = 0.f;  // probability (f32 log-prob kept separately) or continuous prediction
+    float logp = 0.f;
+    if (lane < a.V) {
+      float lg = round_bf(round_bf(mine) * a.output_scale);
+      if (a.final_logit_cap > 0.f) lg = round_bf(a.final_logit_cap * tanhf(lg / a.final_logit_cap));
+      logp = fminf(lg, 0.f) - log1pf(expf(-fabsf(lg)));  // log_sigmoid in fp32
+      if (a.log_probs) a.log_probs[r * a.V + lane] = logp;
+    } else if (lane < NO) {
+      float cl = round_bf(mine);
+      float sg = round_bf(1.0f / (1.0f + expf(-cl)));
+      value = round_bf(sg * a.dwell_norm_scale);
+      if (a.continuous) a.continuous[r * a.NC + (lane - a.V)] = value;
+    }
+    if (a.has_blend && a.scores) {
+      // exp(ln p as f32 -> f64) like the client side; terms summed left to right in f64 by lane 0
+      double col = (lane < a.V) ? exp((double)logp) : (double)value;
+      double s = 0.0;
+      for (int i = 0; i < a.blend.num_terms; ++i) {
+        const int src = a.blend.src[i];
+        double cv = __shfl_sync(0xffffffffu, col, src);
+        s = s + cv * a.blend.weight[i];
+      }
+      if (lane == 0) {
+        double out;
+        if (a.blend.total_sum == 0.0) out = s > 0.0 ? s : 0.0;
+        else if (s < 0.0) out = (s + a.blend.negative_sum) / a.blend.total_sum * 0.001;
+        else out = s + 0.001;
+        a.scores[r] = out;
+      }
+    }
+  }
+}
+
+// users[b] = l2norm(mean over valid t of final_norm(x[b,t])), fp32; one CTA per user, one thread per column
+__global__ void tower_pool_kernel(const bf16* __restrict__ x, const float* __restrict__ gain, const int* __restrict__ seg,
+                                  int T, int D, float eps, float* __restrict__ users) {
+  extern __shared__ float psm[];  // [T] rstd (0 for invalid) + reduction scratch
+  float* rstd = psm;
+  float* red = psm + T;
+  const int b = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int t = warp; t < T; t += nw) {
+    const bf16* xr = x + ((long long)b * T + t) * D;
+    float ss = 0.f;
+    for (int k = lane; k < D; k += 32) { float v = bf2f(xr[k]); ss += v * v; }
+    ss = warp_sum(ss);
+    if (lane == 0) rstd[t] = (seg[(long long)b * T + t] != 0) ? rsqrtf(ss / (float)D + eps) : 0.f;
+  }
+  __syncthreads();
+  float cnt = 0.f;
+  for (int t = 0; t < T; ++t) cnt += (rstd[t] != 0.f) ? 1.f : 0.f;
+  float sq = 0.f;
+  float vals[8];  // D <= 8 * blockDim.x
+  int nv = 0;
+  for (int k = threadIdx.x; k < D; k += blockDim.x, ++nv) {
+    float acc = 0.f;
+    const float gk = gain[k];
+    for (int t = 0; t < T; ++t) {  // fixed order over positions
+      if (rstd[t] != 0.f) acc = acc + round_bf(bf2f(x[((long long)b * T + t) * D + k]) * rstd[t] * gk);
+    }
+    const float rep = acc / fmaxf(cnt, 1.0f);
+    vals[nv] = rep;
+    sq += rep * rep;
+  }
+  sq = warp_sum(sq);
+  if (lane == 0) red[warp] = sq;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < nw; ++w) tot += red[w];
+  const float inv = 1.0f / sqrtf(fmaxf(tot, 1e-12f));
+  nv = 0;
+  for (int k = threadIdx.x; k < D; k += blockDim.x, ++nv) users[(long long)b * D + k] = vals[nv] * inv;
+}
+
+}  // namespace
+
+phx_status heads_launch(const HeadsArgs& a, cudaStream_t stream, std::string& err) {
+  const int NO = a.V + a.NC;
+  if (NO > MAX_OUT || a.D % 8 != 0) { err = "heads: V + NC must be <= 32 and D a multiple of 8"; return PHX_E_ARG; }
+  if (a.has_blend) {
+    for (int i = 0; i < a.blend.num_terms; ++i)
+      if (a.blend.src[i] < 0 || a.blend.src[i] >= NO) { err = "heads: blend term source out of range"; return PHX_E_ARG; }
+  }
+  const long long rows = (long long)a.B * a.C;
+  if (rows == 0) return PHX_OK;
+  const size_t smem = (size_t)NO * a.D * sizeof(bf16);
+  static bool attr_set = false;
+  if (!attr_set && smem > 48 * 1024) {
+    PHX_CUDA_TRY(cudaFuncSetAttribute(heads_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), err);
+    attr_set = true;
+  }
+  if (smem > 200 * 1024) { err = "heads: head matrix does not fit shared memory"; return PHX_E_CAPACITY; }
+  long long blocks = (rows + 7) / 8;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  heads_kernel<<<(unsigned)blocks, 256, smem, stream>>>(a);
+  PHX_CUDA_TRY(cudaGetLastError(), err);
+  return PHX_OK;
+}
+
+phx_status tower_pool_launch(const bf16* x, const float* final_gain, const int* seg, int B, int T, int D, float eps,
+                             float* users, cudaStream_t stream, std::string& err) {
+  if (B == 0) return PHX_OK;
+  int threads = 256;
+  if (D > 8 * threads) { err = "tower_pool: D too large"; return PHX_E_CAPACITY; }
+  const size_t smem = (size_t)(T + 32) * sizeof(float);
+  tower_pool_kernel<<<B, threads, smem, stream>>>(x, final_gain, seg, T, D, eps, users);
+  PHX_CUDA_TRY(cudaGetLastError(), err);
+  return PHX_OK;
+}
+
+}  // namespace phx

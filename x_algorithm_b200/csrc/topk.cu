@@ -1,0 +1,522 @@
+// Exhaustive dot-product top-k over a corpus shard without materialising the score matrix
+// (reference: users_bf16 @ posts^T -> bf16 scores -> top_k_by_key,
+// phoenix/xrex/models/recsys_two_tower_model.py:2455-2516, phoenix/xrex/cuda/top_k_by_key/).
+//
+//   1. sample pass   every `stride`-th 64-row tile is scored; per user and 16-row group the maximum
+//                    score is kept; the pivot of a user is the j-th largest group maximum, with j
+//                    chosen so that about 3k corpus rows are expected at or above it
+//   2. collect pass  the whole shard is scored once (corpus read once from HBM, scores live only in
+//                    registers); rows with bf16(score) >= pivot are appended to the user's survivor
+//                    list as 64-bit keys  ordered(score) << 32 | ~global_row
+//   3. select        per user an MSB-first radix select finds the k-th largest key (keys are unique,
+//                    so exactly k survive), the k keys are sorted in shared memory and written out
+// Ordering by the 64-bit key is (score descending, row ascending): the definitional top-k with ties
+// broken by the lower id (jax.lax.top_k, cuda/top_k_by_key/__init__.py:78-80).  The result is exact
+// whenever the survivor list holds at least k and at most `cap` rows; otherwise the call reports
+// PHX_E_CAPACITY instead of returning a wrong answer.
+#include <math.h>
+
+#include <vector>
+
+#include "common.cuh"
+
+namespace phx {
+namespace {
+
+constexpr int TILE_ROWS = 64;
+constexpr int SCAN_THREADS = 256;
+constexpr int SEL_THREADS = 1024;
+
+__device__ __forceinline__ uint32_t ordered32(float f) {
+  if (f == 0.f) f = 0.f;  // -0 -> +0
+  uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float from_ordered32(uint32_t o) {
+  uint32_t u = (o & 0x80000000u) ? (o & 0x7FFFFFFFu) : ~o;
+  return __uint_as_float(u);
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
+  int sz = pred ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void users_to_bf16_kernel(const float* __restrict__ users, bf16* __restrict__ out, int B, int Bpad, int dim) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= Bpad * dim) return;
+  const int b = i / dim;
+  out[i] = (b < B) ? f2bf(users[i]) : f2bf(0.f);
+}
+
+struct ScanArgs {
+  const bf16* corpus;      // [rows, dim]
+  const bf16* users;       // [Bpad, dim] bf16
+  long long rows;
+  long long row_offset;    // global id of local row 0
+  int dim, B, Bpad;
+  int stride;              // MODE 0: score tiles t with t % stride == 0
+  float* gmax;             // MODE 0: [B][n_groups] group maxima
+  long long n_groups;      // sampled groups per user
+  const float* pivot;      // MODE 1: [B]
+  unsigned long long* surv;  // MODE 1: [B][cap]
+  int* counts;             // MODE 1: [B]
+  int cap;
+};
+
+// NT = n-tiles (8 users each) per warp; a CTA covers 2 * NT * 8 users x 64 corpus rows per tile
+template <int NT, int MODE>
+__global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
+  extern __shared__ __align__(16) uint8_t ssm[];
+  const int LD = a.dim + 8;
+  bf16* s_users = reinterpret_cast<bf16*>(ssm);                    // [Bpad][LD]
+  bf16* s_tile = s_users + (size_t)a.Bpad * LD;                    // [2][TILE_ROWS][LD]
+  float* s_pivot = reinterpret_cast<float*>(s_tile + 2 * TILE_ROWS * LD);  // [Bpad]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int mt = warp & 3, half = warp >> 2;
+  const int chunks_per_row = a.dim / 8;
+
+  for (int c = threadIdx.x; c < a.Bpad * chunks_per_row; c += SCAN_THREADS) {
+    const int r = c / chunks_per_row, dc = (c % chunks_per_row) * 8;
+    *reinterpret_cast<uint4*>(&s_users[r * LD + dc]) = *reinterpret_cast<const uint4*>(a.users + (size_t)r * a.dim + dc);
+  }
+  if (MODE == 1)
+    for (int u = threadIdx.x; u < a.Bpad; u += SCAN_THREADS) s_pivot[u] = (u < a.B) ? a.pivot[u] : INFINITY;
+
+  const long long n_tiles = (a.rows + TILE_ROWS - 1) / TILE_ROWS;
+  const long long step = (long long)gridDim.x * (MODE == 0 ? a.stride : 1);
+  const long long first = (long long)blockIdx.x * (MODE == 0 ? a.stride : 1);
+
+  auto load_tile = [&](long long tile, int buf) {
+    const long long r0 = tile * TILE_ROWS;
+    bf16* dst = s_tile + (size_t)buf * TILE_ROWS * LD;
+    for (int c = threadIdx.x; c < TILE_ROWS * chunks_per_row; c += SCAN_THREADS) {
+      const int r = c / chunks_per_row, dc = (c % chunks_per_row) * 8;
+      const bool ok = (r0 + r) < a.rows;
+      const bf16* src = a.corpus + (size_t)(ok ? (r0 + r) : 0) * a.dim + dc;
+      cp_async16((uint32_t)__cvta_generic_to_shared(dst + r * LD + dc), src, ok);
+    }
+    cp_async_commit();
+  };
+
+  int buf = 0;
+  if (first < n_tiles) load_tile(first, 0);
+  for (long long tile = first; tile < n_tiles; tile += step) {
+    const long long next = tile + step;
+    if (next < n_tiles) { load_tile(next, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncthreads();
+    const bf16* tl = s_tile + (size_t)buf * TILE_ROWS * LD;
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+    for (int ks = 0; ks < a.dim / 16; ++ks) {
+      uint32_t af[4];
+      ldmatrix_x4(af, (uint32_t)__cvta_generic_to_shared(tl + (mt * 16 + (lane & 15)) * LD + ks * 16 + ((lane >> 4) << 3)));
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const bf16* up = s_users + ((half * NT + j) * 8 + g) * LD + ks * 16 + 2 * t4;
+        mma_16816(acc[j], af, *reinterpret_cast<const uint32_t*>(up), *reinterpret_cast<const uint32_t*>(up + 8));
+      }
+    }
+    const long long row_a = tile * TILE_ROWS + mt * 16 + g, row_b = row_a + 8;
+    if (MODE == 0) {
+      // 16-row group maximum per user (rows past the end count as -inf)
+      const long long grp = (tile / a.stride) * 4 + mt;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        float m0 = fmaxf(row_a < a.rows ? round_bf(acc[j][0]) : -INFINITY, row_b < a.rows ? round_bf(acc[j][2]) : -INFINITY);
+        float m1 = fmaxf(row_a < a.rows ? round_bf(acc[j][1]) : -INFINITY, row_b < a.rows ? round_bf(acc[j][3]) : -INFINITY);
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+          m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
+          m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
+        }
+        if (g == 0) {
+          const int u0 = (half * NT + j) * 8 + 2 * t4;
+          if (u0 < a.B) a.gmax[(size_t)u0 * a.n_groups + grp] = m0;
+          if (u0 + 1 < a.B) a.gmax[(size_t)(u0 + 1) * a.n_groups + grp] = m1;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const int u0 = (half * NT + j) * 8 + 2 * t4;
+        const float2 pv = *reinterpret_cast<const float2*>(&s_pivot[u0]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float v = round_bf(acc[j][e]);
+          const float p = (e & 1) ? pv.y : pv.x;
+          const long long row = (e & 2) ? row_b : row_a;
+          if (v >= p && row < a.rows) {
+            const int u = u0 + (e & 1);
+            const int slot = atomicAdd(&a.counts[u], 1);
+            if (slot < a.cap)
+              a.surv[(size_t)u * a.cap + slot] =
+                  ((unsigned long long)ordered32(v) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)(a.row_offset + row));
+          }
+        }
+      }
+    }
+    __syncthreads();
+    buf ^= 1;
+  }
+}
+
+// ---- MSB-first radix select of the k-th largest 64-bit key among n (one CTA) ------------------------
+__device__ unsigned long long radix_kth_largest(const unsigned long long* keys, int n, int k, int* s_hist,
+                                                unsigned long long* s_bcast) {
+  unsigned long long prefix = 0, mask = 0;
+  int remaining = k;
+  for (int shift = 56; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) s_hist[i] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const unsigned long long v = keys[i];
+      if ((v & mask) == prefix) atomicAdd(&s_hist[(int)((v >> shift) & 0xFF)], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int cum = 0, d = 255;
+      for (; d > 0; --d) {
+        if (cum + s_hist[d] >= remaining) break;
+        cum += s_hist[d];
+      }
+      s_bcast[0] = (unsigned long long)d;
+      s_bcast[1] = (unsigned long long)(remaining - cum);
+    }
+    __syncthreads();
+    const unsigned long long d = s_bcast[0];
+    remaining = (int)s_bcast[1];
+    prefix |= d << shift;
+    mask |= 0xFFull << shift;
+    __syncthreads();
+  }
+  return prefix;  // the k-th largest key itself
+}
+
+__device__ void bitonic_sort_desc(unsigned long long* s, int n_pow2) {
+  for (int size = 2; size <= n_pow2; size <<= 1) {
+    for (int strd = size >> 1; strd > 0; strd >>= 1) {
+      __syncthreads();
+      for (int i = threadIdx.x; i < n_pow2 / 2; i += blockDim.x) {
+        const int lo = 2 * i - (i & (strd - 1));
+        const int hi = lo + strd;
+        const bool desc = ((lo & size) == 0);
+        const unsigned long long x = s[lo], y = s[hi];
+        if ((x < y) == desc) { s[lo] = y; s[hi] = x; }
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// pivot[u] = j-th largest of gmax[u][0..n_groups); j <= 0 or j > n_groups -> -inf
+__global__ void __launch_bounds__(SEL_THREADS) pivot_kernel(const float* __restrict__ gmax, long long n_groups, int j,
+                                                            float* __restrict__ pivot) {
+  __shared__ int s_hist[256];  // two 256-bin passes over the 16 significant bits
+  __shared__ int s_sel[2];
+  const int u = blockIdx.x;
+  if (j <= 0 || j > n_groups) { if (threadIdx.x == 0) pivot[u] = -INFINITY; return; }
+  const float* gm = gmax + (size_t)u * n_groups;
+  // values are bf16-representable: the top 16 bits of the ordered key carry everything
+  uint32_t prefix = 0, mask = 0;
+  int remaining = j;
+  for (int shift = 24; shift >= 16; shift -= 8) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) s_hist[i] = 0;
+    __syncthreads();
+    for (long long i = threadIdx.x; i < n_groups; i += blockDim.x) {
+      const uint32_t v = ordered32(gm[i]);
+      if ((v & mask) == prefix) atomicAdd(&s_hist[(v >> shift) & 0xFF], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int cum = 0, d = 255;
+      for (; d > 0; --d) { if (cum + s_hist[d] >= remaining) break; cum += s_hist[d]; }
+      s_sel[0] = d; s_sel[1] = remaining - cum;
+    }
+    __syncthreads();
+    prefix |= (uint32_t)s_sel[0] << shift;
+    mask |= 0xFFu << shift;
+    remaining = s_sel[1];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) pivot[u] = from_ordered32(prefix);
+}
+
+// keys[u][0..n_u) -> top k sorted; n_u = min(counts[u], cap) or fixed_n.  status[0] |= 1 on underflow, 2 on overflow
+__global__ void __launch_bounds__(SEL_THREADS) select_kernel(const unsigned long long* __restrict__ keys, const int* counts,
+                                                             int fixed_n, int cap, int k, int kpow2,
+                                                             float* __restrict__ out_scores, long long* __restrict__ out_ids,
+                                                             int* status) {
+  extern __shared__ __align__(16) uint8_t selsm[];
+  unsigned long long* s_keys = reinterpret_cast<unsigned long long*>(selsm);  // [kpow2]
+  __shared__ int s_hist[256];
+  __shared__ unsigned long long s_bcast[2];
+  __shared__ int s_fill;
+  const int u = blockIdx.x;
+  int n = counts ? counts[u] : fixed_n;
+  if (counts && n > cap) { if (threadIdx.x == 0) atomicOr(status, 2); n = cap; }
+  if (n < k) {
+    if (threadIdx.x == 0) atomicOr(status, 1);
+    for (int i = threadIdx.x; i < k; i += blockDim.x) { out_scores[(size_t)u * k + i] = -INFINITY; out_ids[(size_t)u * k + i] = -1; }
+    return;
+  }
+  const unsigned long long* ku = keys + (size_t)u * cap;
+  const unsigned long long kth = radix_kth_largest(ku, n, k, s_hist, s_bcast);
+  if (threadIdx.x == 0) s_fill = 0;
+  for (int i = threadIdx.x; i < kpow2; i += blockDim.x) s_keys[i] = 0ull;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const unsigned long long v = ku[i];
+    if (v >= kth) { const int slot = atomicAdd(&s_fill, 1); if (slot < kpow2) s_keys[slot] = v; }
+  }
+  __syncthreads();
+  bitonic_sort_desc(s_keys, kpow2);
+  for (int i = threadIdx.x; i < k; i += blockDim.x) {
+    const unsigned long long v = s_keys[i];
+    out_scores[(size_t)u * k + i] = from_ordered32((uint32_t)(v >> 32));
+    out_ids[(size_t)u * k + i] = (long long)(0xFFFFFFFFu - (uint32_t)(v & 0xFFFFFFFFull));
+  }
+}
+
+// [P][B][k] (score, id) lists -> keys[B][P*k]
+__global__ void merge_keys_kernel(const float* __restrict__ scores, const long long* __restrict__ ids, int P, int B, int k,
+                                  unsigned long long* __restrict__ keys) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)P * B * k) return;
+  const int p = (int)(i / ((long long)B * k));
+  const int b = (int)((i / k) % B);
+  const int j = (int)(i % k);
+  const long long id = ids[i];
+  unsigned long long key = 0ull;  // empty slot (id < 0) sorts last
+  if (id >= 0) key = ((unsigned long long)ordered32(scores[i]) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)id);
+  keys[((size_t)b * P + p) * k + j] = key;
+}
+
+int next_pow2(int v) { int p = 1; while (p < v) p <<= 1; return p; }
+
+}  // namespace
+}  // namespace phx
+
+using namespace phx;
+
+struct phx_corpus {
+  int device = 0;
+  long long rows = 0, row_offset = 0;
+  int dim = 0, max_queries = 0, max_k = 0, cap = 0;
+  int num_sms = 148;
+  bf16* data = nullptr;
+  bf16* users_bf = nullptr;
+  float* gmax = nullptr;
+  long long gmax_elems = 0;
+  float* pivot = nullptr;
+  unsigned long long* surv = nullptr;
+  unsigned long long* merge_keys = nullptr;
+  size_t merge_keys_elems = 0;
+  int* counts = nullptr;
+  int* status = nullptr;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  std::string err;
+};
+
+namespace {
+
+template <int NT>
+phx_status launch_scan(phx_corpus* c, const ScanArgs& a, int mode, int grid, size_t smem) {
+  if (mode == 0) {
+    PHX_CUDA_TRY(cudaFuncSetAttribute(scan_kernel<NT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), c->err);
+    scan_kernel<NT, 0><<<grid, SCAN_THREADS, smem, c->stream>>>(a);
+  } else {
+    PHX_CUDA_TRY(cudaFuncSetAttribute(scan_kernel<NT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), c->err);
+    scan_kernel<NT, 1><<<grid, SCAN_THREADS, smem, c->stream>>>(a);
+  }
+  PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  return PHX_OK;
+}
+
+phx_status run_scan(phx_corpus* c, const ScanArgs& a, int mode, int grid) {
+  const size_t smem = ((size_t)a.Bpad + 2 * TILE_ROWS) * (a.dim + 8) * 2 + (size_t)a.Bpad * 4;
+  if (smem > 200 * 1024) { c->err = "topk: query batch x dim does not fit shared memory"; return PHX_E_CAPACITY; }
+  if (a.Bpad == 16) return launch_scan<1>(c, a, mode, grid, smem);
+  if (a.Bpad == 64) return launch_scan<4>(c, a, mode, grid, smem);
+  return launch_scan<16>(c, a, mode, grid, smem);
+}
+
+}  // namespace
+
+extern "C" {
+
+phx_status phx_corpus_create(int32_t device, int64_t rows, int32_t dim, int64_t row_offset, int32_t max_queries,
+                             int32_t max_k, phx_corpus** out) {
+  if (!out || rows <= 0 || dim <= 0 || dim % 16 != 0 || dim > 512 || max_queries <= 0 || max_queries > 256 ||
+      max_k <= 0 || max_k > 4096 || row_offset < 0 || rows + row_offset > 0xFFFFFFFFll) {
+    set_global_error("phx_corpus_create: bad argument (dim % 16 == 0, <= 256 queries, k <= 4096, global rows < 2^32)");
+    return PHX_E_ARG;
+  }
+  phx_corpus* c = new phx_corpus();
+  c->device = device; c->rows = rows; c->dim = dim; c->row_offset = row_offset; c->max_queries = max_queries; c->max_k = max_k;
+  c->cap = 64 * max_k > 32768 ? 64 * max_k : 32768;
+  auto fail = [&](const std::string& m) { set_global_error(m); phx_corpus_destroy(c); return PHX_E_CUDA; };
+  if (cudaSetDevice(device) != cudaSuccess) return fail("cudaSetDevice failed");
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return fail("cudaGetDeviceProperties failed");
+  c->num_sms = prop.multiProcessorCount;
+#define CU(x) do { cudaError_t _e = (x); if (_e != cudaSuccess) return fail(std::string(#x) + ": " + cudaGetErrorString(_e)); } while (0)
+  CU(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+  CU(cudaEventCreate(&c->ev0)); CU(cudaEventCreate(&c->ev1));
+  CU(cudaMalloc(&c->data, (size_t)rows * dim * 2));
+  CU(cudaMalloc(&c->users_bf, (size_t)256 * dim * 2));
+  const long long n_tiles = (rows + TILE_ROWS - 1) / TILE_ROWS;
+  c->gmax_elems = (long long)max_queries * n_tiles * 4;  // stride 1 worst case
+  // the sample never needs more than ~ (64 * j) groups; bound the buffer at 64M floats
+  if (c->gmax_elems > (64ll << 20)) c->gmax_elems = 64ll << 20;
+  CU(cudaMalloc(&c->gmax, (size_t)c->gmax_elems * 4));
+  CU(cudaMalloc(&c->pivot, 256 * 4));
+  CU(cudaMalloc(&c->surv, (size_t)max_queries * c->cap * 8));
+  CU(cudaMalloc(&c->counts, 256 * 4));
+  CU(cudaMalloc(&c->status, 4));
+  CU(cudaMemset(c->status, 0, 4));
+#undef CU
+  *out = c;
+  return PHX_OK;
+}
+
+void phx_corpus_destroy(phx_corpus* c) {
+  if (!c) return;
+  cudaSetDevice(c->device);
+  if (c->stream) cudaStreamSynchronize(c->stream);
+  auto fr = [](void* p) { if (p) cudaFree(p); };
+  fr(c->data); fr(c->users_bf); fr(c->gmax); fr(c->pivot); fr(c->surv); fr(c->merge_keys); fr(c->counts); fr(c->status);
+  if (c->ev0) cudaEventDestroy(c->ev0);
+  if (c->ev1) cudaEventDestroy(c->ev1);
+  if (c->stream) cudaStreamDestroy(c->stream);
+  delete c;
+}
+
+const char* phx_corpus_last_error(const phx_corpus* c) { return c ? c->err.c_str() : phx_global_error(); }
+
+phx_status phx_corpus_upload(phx_corpus* c, int64_t row0, int64_t nrows, const uint16_t* host_bf16) {
+  if (!c || !host_bf16 || row0 < 0 || nrows < 0 || row0 + nrows > c->rows) { if (c) c->err = "phx_corpus_upload: range"; return PHX_E_ARG; }
+  cudaSetDevice(c->device);
+  PHX_CUDA_TRY(cudaMemcpy(c->data + row0 * c->dim, host_bf16, (size_t)nrows * c->dim * 2, cudaMemcpyHostToDevice), c->err);
+  return PHX_OK;
+}
+
+phx_status phx_corpus_fill_synthetic(phx_corpus* c, uint32_t seed) {
+  if (!c) return PHX_E_ARG;
+  cudaSetDevice(c->device);
+  phx_status s = corpus_fill_launch(c->data, c->row_offset, c->rows, c->dim, seed, c->stream, c->err);
+  if (s) return s;
+  PHX_CUDA_TRY(cudaStreamSynchronize(c->stream), c->err);
+  return PHX_OK;
+}
+
+phx_status phx_corpus_topk_device(phx_corpus* c, const float* users_dev, int32_t B, int32_t k, float* scores_dev,
+                                  int64_t* ids_dev) {
+  if (!c || !users_dev || !scores_dev || !ids_dev) return PHX_E_ARG;
+  if (B <= 0 || B > c->max_queries || k <= 0 || k > c->max_k) { c->err = "topk: B or k exceeds what the corpus was created for"; return PHX_E_CAPACITY; }
+  if (k > c->rows) { c->err = "topk: k exceeds the shard's rows"; return PHX_E_ARG; }
+  cudaSetDevice(c->device);
+  const int Bpad = B <= 16 ? 16 : (B <= 64 ? 64 : 256);
+  PHX_CUDA_TRY(cudaEventRecord(c->ev0, c->stream), c->err);
+  users_to_bf16_kernel<<<(Bpad * c->dim + 255) / 256, 256, 0, c->stream>>>(users_dev, c->users_bf, B, Bpad, c->dim);
+  PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  PHX_CUDA_TRY(cudaMemsetAsync(c->counts, 0, 256 * 4, c->stream), c->err);
+
+  ScanArgs a;
+  a.corpus = c->data; a.users = c->users_bf; a.rows = c->rows; a.row_offset = c->row_offset; a.dim = c->dim; a.B = B; a.Bpad = Bpad;
+  a.stride = 1; a.gmax = c->gmax; a.n_groups = 0; a.pivot = c->pivot; a.surv = c->surv; a.counts = c->counts; a.cap = c->cap;
+  const long long n_tiles = (c->rows + TILE_ROWS - 1) / TILE_ROWS;
+  int j = 0;
+  if (c->rows > c->cap) {
+    // sample every stride-th tile so that about 48 of the wanted ~3k rows fall into the sample
+    const double want = 3.0 * k;
+    long long stride = (long long)(want / 48.0);
+    if (stride < 1) stride = 1;
+    long long sampled_tiles = (n_tiles + stride - 1) / stride;
+    while (sampled_tiles * 4 * (long long)B > c->gmax_elems) { stride *= 2; sampled_tiles = (n_tiles + stride - 1) / stride; }
+    a.stride = (int)stride;
+    a.n_groups = sampled_tiles * 4;
+    // per-row tail fraction f = want / rows; a 16-row group exceeds the level with 1 - (1-f)^16
+    const double f = want / (double)c->rows;
+    const double qg = 1.0 - pow(1.0 - (f < 0.5 ? f : 0.5), 16.0);
+    j = (int)ceil(qg * (double)a.n_groups);
+    if (j < 1) j = 1;
+    int grid = (int)(sampled_tiles < c->num_sms * 2 ? sampled_tiles : c->num_sms * 2);
+    phx_status s = run_scan(c, a, 0, grid);
+    if (s) return s;
+  }
+  pivot_kernel<<<B, SEL_THREADS, 0, c->stream>>>(c->gmax, a.n_groups, j, c->pivot);
+  PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  {
+    int grid = (int)(n_tiles < c->num_sms * 2 ? n_tiles : c->num_sms * 2);
+    phx_status s = run_scan(c, a, 1, grid);
+    if (s) return s;
+  }
+  const int kp2 = next_pow2(k);
+  select_kernel<<<B, SEL_THREADS, (size_t)kp2 * 8, c->stream>>>(c->surv, c->counts, 0, c->cap, k, kp2, scores_dev,
+                                                               (long long*)ids_dev, c->status);
+  PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  PHX_CUDA_TRY(cudaEventRecord(c->ev1, c->stream), c->err);
+  return PHX_OK;
+}
+
+phx_status phx_topk_merge_device(phx_corpus* c, const float* scores_dev, const int64_t* ids_dev, int32_t P, int32_t B,
+                                 int32_t k, float* out_scores_dev, int64_t* out_ids_dev) {
+  if (!c || !scores_dev || !ids_dev || !out_scores_dev || !out_ids_dev || P <= 0 || B <= 0 || k <= 0 || k > 4096) return PHX_E_ARG;
+  cudaSetDevice(c->device);
+  const size_t need = (size_t)P * B * k;
+  if (need > c->merge_keys_elems) {
+    if (c->merge_keys) cudaFree(c->merge_keys);
+    c->merge_keys = nullptr;
+    PHX_CUDA_TRY(cudaMalloc(&c->merge_keys, need * 8), c->err);
+    c->merge_keys_elems = need;
+  }
+  merge_keys_kernel<<<(unsigned)((need + 255) / 256), 256, 0, c->stream>>>(scores_dev, (const long long*)ids_dev, P, B, k, c->merge_keys);
+  PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  const int kp2 = next_pow2(k);
+  select_kernel<<<B, SEL_THREADS, (size_t)kp2 * 8, c->stream>>>(c->merge_keys, nullptr, P * k, P * k, k, kp2, out_scores_dev,
+                                                               (long long*)out_ids_dev, c->status);
+  PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  return PHX_OK;
+}
+
+phx_status phx_corpus_sync(phx_corpus* c) {
+  if (!c) return PHX_E_ARG;
+  cudaSetDevice(c->device);
+  PHX_CUDA_TRY(cudaStreamSynchronize(c->stream), c->err);
+  int st = 0;
+  PHX_CUDA_TRY(cudaMemcpy(&st, c->status, 4, cudaMemcpyDeviceToHost), c->err);
+  if (st != 0) {
+    cudaMemset(c->status, 0, 4);
+    c->err = std::string("topk: survivor list ") + ((st & 2) ? "overflowed its capacity" : "held fewer than k rows") +
+             " (pivot estimate off for this corpus); result withheld";
+    return PHX_E_CAPACITY;
+  }
+  return PHX_OK;
+}
+
+phx_status phx_corpus_last_device_ms(phx_corpus* c, float* ms) {
+  if (!c || !ms) return PHX_E_ARG;
+  PHX_CUDA_TRY(cudaEventSynchronize(c->ev1), c->err);
+  PHX_CUDA_TRY(cudaEventElapsedTime(ms, c->ev0, c->ev1), c->err);
+  return PHX_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,197 @@
+"""Python face of the engine: owns a phx_engine handle and moves numpy / torch buffers through the
+C ABI.  Mirrors the model runner's per-batch sequence (phoenix/xrex/inference/model_runner.py:4141-4222):
+featurised ids in, log-probabilities / continuous predictions / weighted scores out."""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Dict, Optional
+
+import numpy as np
+
+from . import _lib
+from ._lib import PhoenixError, lib
+from .config import PhoenixConfig
+
+
+@dataclass
+class RankInputs:
+    """One batch of requests (id 0 = padding, history front-filled): the buffers of the reference's
+    RankingBatchPrep (xai-recsys-engine/src/python.rs:1394-1440) with raw ids instead of hashes."""
+    hist_post_ids: np.ndarray      # int64 [B,S]
+    hist_author_ids: np.ndarray    # int64 [B,S]
+    hist_actions: np.ndarray       # int32 [B,S]
+    hist_surfaces: np.ndarray      # int32 [B,S]
+    cand_post_ids: np.ndarray      # int64 [B,C]
+    cand_author_ids: np.ndarray    # int64 [B,C]
+
+    @property
+    def batch(self) -> int:
+        return int(self.hist_post_ids.shape[0])
+
+
+@dataclass
+class RankOutputs:
+    log_probs: np.ndarray    # f32 [B,C,V]
+    continuous: np.ndarray   # f32 [B,C,NC]
+    scores: Optional[np.ndarray]  # f64 [B,C] or None when no blend is set
+
+
+def _ptr(a) -> int:
+    if a is None:
+        return 0
+    if isinstance(a, np.ndarray):
+        return a.ctypes.data
+    return int(a.data_ptr())  # torch tensor
+
+
+class PhoenixEngine:
+    def __init__(self, cfg: PhoenixConfig, device: int = 0):
+        self.cfg = cfg
+        self.device = device
+        self._h = C.c_void_p()
+        self._ccfg = cfg.to_c()
+        st = lib.phx_engine_create(C.byref(self._ccfg), device, C.byref(self._h))
+        if st != 0:
+            raise PhoenixError(st, lib.phx_global_error().decode())
+        self._has_blend = False
+
+    # -- plumbing ------------------------------------------------------------------------------
+    def _check(self, st: int):
+        if st != 0:
+            raise PhoenixError(st, lib.phx_last_error(self._h).decode())
+
+    def close(self):
+        if self._h:
+            lib.phx_engine_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- parameters ----------------------------------------------------------------------------
+    def load_weights(self, weights: Dict[str, np.ndarray]):
+        for name, arr in weights.items():
+            a = np.ascontiguousarray(arr, dtype=np.float32)
+            rows, cols = (1, a.shape[0]) if a.ndim == 1 else a.shape
+            self._check(lib.phx_load_param(self._h, name.encode(), a.ctypes.data, rows, cols))
+
+    def table_upload(self, row0: int, rows_bf16_bits: np.ndarray):
+        a = np.ascontiguousarray(rows_bf16_bits, dtype=np.uint16)
+        self._check(lib.phx_table_upload(self._h, row0, a.shape[0], a.ctypes.data))
+
+    def table_fill_synthetic(self, seed: int, amp: float):
+        self._check(lib.phx_table_fill_synthetic(self._h, seed, amp))
+
+    def set_blend(self, spec: _lib.BlendSpec):
+        self._check(lib.phx_set_blend(self._h, C.byref(spec)))
+        self._has_blend = True
+
+    # -- ranking ---------------------------------------------------------------------------------
+    def _batch_struct(self, B, hp, ha, act, srf, cp, ca) -> _lib.RankBatch:
+        b = _lib.RankBatch()
+        b.batch = B
+        b.hist_post_ids, b.hist_author_ids, b.hist_actions, b.hist_surfaces = _ptr(hp), _ptr(ha), _ptr(act), _ptr(srf)
+        b.cand_post_ids, b.cand_author_ids = _ptr(cp), _ptr(ca)
+        return b
+
+    def rank(self, inp: RankInputs) -> RankOutputs:
+        """Host buffers in, host buffers out (copies inside the call)."""
+        cfg, B = self.cfg, inp.batch
+        arrs = [np.ascontiguousarray(inp.hist_post_ids, np.int64), np.ascontiguousarray(inp.hist_author_ids, np.int64),
+                np.ascontiguousarray(inp.hist_actions, np.int32), np.ascontiguousarray(inp.hist_surfaces, np.int32),
+                np.ascontiguousarray(inp.cand_post_ids, np.int64), np.ascontiguousarray(inp.cand_author_ids, np.int64)]
+        assert arrs[0].shape == (B, cfg.history_len) and arrs[4].shape == (B, cfg.num_candidates)
+        lp = np.empty((B, cfg.num_candidates, cfg.num_actions), np.float32)
+        cont = np.empty((B, cfg.num_candidates, cfg.num_continuous), np.float32)
+        sc = np.empty((B, cfg.num_candidates), np.float64) if self._has_blend else None
+        b = self._batch_struct(B, *arrs)
+        o = _lib.RankOut(_ptr(lp), _ptr(cont), _ptr(sc))
+        self._check(lib.phx_rank_forward(self._h, C.byref(b), C.byref(o)))
+        return RankOutputs(lp, cont, sc)
+
+    def rank_device(self, B, hp, ha, act, srf, cp, ca, lp, cont, sc=None):
+        """Device tensors (torch) in and out; asynchronous on the engine's stream."""
+        b = self._batch_struct(B, hp, ha, act, srf, cp, ca)
+        o = _lib.RankOut(_ptr(lp), _ptr(cont), _ptr(sc))
+        self._check(lib.phx_rank_forward_device(self._h, C.byref(b), C.byref(o)))
+
+    def user_tower_device(self, B, hp, ha, act, srf, users):
+        b = self._batch_struct(B, hp, ha, act, srf, None, None)
+        self._check(lib.phx_user_tower_device(self._h, C.byref(b), _ptr(users)))
+
+    def sync(self):
+        self._check(lib.phx_sync(self._h))
+
+    def last_device_ms(self) -> float:
+        ms = C.c_float()
+        self._check(lib.phx_last_device_ms(self._h, C.byref(ms)))
+        return float(ms.value)
+
+    def last_launch_count(self) -> int:
+        n = C.c_int32()
+        self._check(lib.phx_last_launch_count(self._h, C.byref(n)))
+        return int(n.value)
+
+    def mark(self, slot: int):
+        self._check(lib.phx_mark(self._h, slot))
+
+    def elapsed_ms(self, a: int, b: int) -> float:
+        ms = C.c_float()
+        self._check(lib.phx_elapsed_ms(self._h, a, b, C.byref(ms)))
+        return float(ms.value)
+
+    KERNEL_CLASSES = ("tokens", "rmsnorm", "gemm", "qknorm_rope", "attention", "heads")
+
+    def profile_enable(self, on: bool):
+        self._check(lib.phx_profile_enable(self._h, int(on)))
+
+    def profile_read(self):
+        ms = (C.c_float * 6)()
+        n = (C.c_int32 * 6)()
+        self._check(lib.phx_profile_read(self._h, ms, n))
+        return {k: (float(ms[i]), int(n[i])) for i, k in enumerate(self.KERNEL_CLASSES)}
+
+    def debug_read(self, what: str, shape, dtype) -> np.ndarray:
+        out = np.empty(shape, dtype)
+        self._check(lib.phx_debug_read(self._h, what.encode(), out.ctypes.data, out.nbytes))
+        return out
+
+    # -- stand-alone operators ---------------------------------------------------------------------
+    def hash_ids_device(self, family: int, ids, n: int, out):
+        self._check(lib.phx_hash_ids_device(self._h, family, _ptr(ids), n, _ptr(out)))
+
+    def gather_sum_device(self, family: int, ids, n: int, out):
+        self._check(lib.phx_gather_sum_device(self._h, family, _ptr(ids), n, _ptr(out)))
+
+
+def ranker_attention(q, k, v, seg, hist_len: int, sm_scale: float, cap: float = -1.0, cap_method: int = 0,
+                     device: int = 0):
+    """Candidate-isolated attention on torch bf16 tensors [B,T,H,dh]; returns (out, device_ms)."""
+    import torch
+    B, T, Hq, dh = q.shape
+    out = torch.empty_like(q)
+    ms = C.c_float()
+    torch.cuda.synchronize()
+    st = lib.phx_ranker_attention_device(device, _ptr(q), _ptr(k), _ptr(v), _ptr(seg), _ptr(out), B, T, Hq,
+                                         k.shape[2], dh, hist_len, sm_scale, cap, cap_method, C.byref(ms))
+    if st != 0:
+        raise PhoenixError(st, lib.phx_global_error().decode())
+    return out, float(ms.value)
+
+
+def gemm(a, wt, residual=None, epilogue: int = 0, impl: int = 0, device: int = 0):
+    """epilogue(A[M,K] @ Wt[N,K]^T) on torch bf16 tensors; returns (C, device_ms)."""
+    import torch
+    M, K = a.shape
+    N = wt.shape[0]
+    c = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    ms = C.c_float()
+    torch.cuda.synchronize()
+    st = lib.phx_gemm_device(device, _ptr(a), _ptr(wt), _ptr(residual), _ptr(c), M, N, K, epilogue, impl, C.byref(ms))
+    if st != 0:
+        raise PhoenixError(st, lib.phx_global_error().decode())
+    return c, float(ms.value)

@@ -1,0 +1,180 @@
+"""Scorer / Source plugins over the engine, mirroring the reference's plugin traits
+(candidate-pipeline/scorer.rs:9-64, candidate-pipeline/source.rs:11-42) and the two Phoenix plugins
+(home-mixer/scorers/phoenix_scorer.rs:80-185, home-mixer/scorers/phoenix_scores_ranking_scorer.rs:15-35,
+home-mixer/sources/phoenix_source.rs:103-150).
+
+Contract kept from the traits: `score` returns exactly one result per candidate, in input order; a
+failed engine call turns into an error string for every candidate and never raises; `run` replaces a
+wrong-length result by `length_mismatch` errors; `update_all` applies only the successful results."""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+
+from ._lib import PhoenixError
+from .engine import PhoenixEngine, RankInputs
+
+
+@dataclass
+class HistoryItem:
+    post_id: int
+    author_id: int
+    action: int        # 1..num_action_types
+    surface: int       # 1..num_surfaces
+
+
+@dataclass
+class Query:
+    """The part of ScoredPostsQuery the Phoenix plugins read: the user's scoring sequence."""
+    user_id: int = 0
+    history: Optional[List[HistoryItem]] = None     # scoring_sequence / retrieval_sequence; None = absent
+    has_cached_posts: bool = False
+    kill_switch: bool = False
+    top_k: int = 1000
+
+
+@dataclass
+class Candidate:
+    post_id: int = 0
+    author_id: int = 0
+    phoenix_scores: Optional[Dict[str, float]] = None   # head name -> probability (dwell_time: seconds)
+    weighted_score: Optional[float] = None
+    score: Optional[float] = None
+
+
+Result = Union[Candidate, str]   # Ok(candidate) | Err(message)
+
+
+class Scorer:
+    def enable(self, query: Query) -> bool:
+        return True
+
+    def score(self, query: Query, candidates: Sequence[Candidate]) -> List[Result]:
+        raise NotImplementedError
+
+    def update(self, candidate: Candidate, scored: Candidate) -> None:
+        raise NotImplementedError
+
+    def run(self, query: Query, candidates: Sequence[Candidate]) -> List[Result]:
+        scored = self.score(query, candidates)
+        if len(scored) == len(candidates):
+            return scored
+        msg = f"Scorer length_mismatch expected={len(candidates)} got={len(scored)}"
+        return [msg] * len(candidates)
+
+    def update_all(self, candidates: Sequence[Candidate], scored: Sequence[Result]) -> None:
+        for c, s in zip(candidates, scored):
+            if not isinstance(s, str):
+                self.update(c, s)
+
+
+class PhoenixScorer(Scorer):
+    """Ranks one request's candidates in chunks of the engine's candidate capacity.  Fills
+    `phoenix_scores` (probabilities = exp(ln p), the client-side conversion of
+    home-mixer/candidate_pipeline/performance_tests.rs:516-521) and, when a blend is set on the engine,
+    `weighted_score` / `score` (phoenix_scores_ranking_scorer.rs:15-35)."""
+
+    def __init__(self, engine: PhoenixEngine, head_names: Sequence[str], cont_names: Sequence[str] = ("dwell_time",)):
+        self.engine = engine
+        self.head_names = list(head_names)
+        self.cont_names = list(cont_names)
+
+    def enable(self, query: Query) -> bool:
+        return not query.has_cached_posts and not query.kill_switch
+
+    def _inputs(self, query: Query, chunks: List[Sequence[Candidate]]) -> RankInputs:
+        cfg = self.engine.cfg
+        B, S, C = len(chunks), cfg.history_len, cfg.num_candidates
+        hp = np.zeros((B, S), np.int64); ha = np.zeros((B, S), np.int64)
+        act = np.zeros((B, S), np.int32); srf = np.zeros((B, S), np.int32)
+        cp = np.zeros((B, C), np.int64); ca = np.zeros((B, C), np.int64)
+        # most recent S items, front-filled, entries without post or author skipped
+        # (phoenix/crates/common/xai-recsys/src/util.rs:1495-1503)
+        hist = [h for h in (query.history or []) if h.post_id != 0 and h.author_id != 0][-S:]
+        for j, h in enumerate(hist):
+            hp[:, j], ha[:, j], act[:, j], srf[:, j] = h.post_id, h.author_id, h.action, h.surface
+        for i, ch in enumerate(chunks):
+            for j, c in enumerate(ch):
+                cp[i, j], ca[i, j] = c.post_id, c.author_id
+        return RankInputs(hp, ha, act, srf, cp, ca)
+
+    def score(self, query: Query, candidates: Sequence[Candidate]) -> List[Result]:
+        n = len(candidates)
+        if query.history is None:                       # phoenix_scorer.rs:107-109
+            return [Candidate() for _ in range(n)]
+        if n == 0:
+            return []
+        cfg = self.engine.cfg
+        C = cfg.num_candidates
+        chunks = [candidates[i:i + C] for i in range(0, n, C)]
+        out: List[Result] = []
+        try:
+            for g in range(0, len(chunks), cfg.max_batch):
+                group = chunks[g:g + cfg.max_batch]
+                res = self.engine.rank(self._inputs(query, group))
+                probs = np.exp(res.log_probs.astype(np.float64))
+                for i, ch in enumerate(group):
+                    for j, c in enumerate(ch):
+                        if c.post_id == 0:
+                            out.append("Phoenix prediction failed: candidate without post id")
+                            continue
+                        ps = {name: float(probs[i, j, k]) for k, name in enumerate(self.head_names)}
+                        for k, name in enumerate(self.cont_names):
+                            ps[name] = float(res.continuous[i, j, k])
+                        w = float(res.scores[i, j]) if res.scores is not None else None
+                        out.append(Candidate(post_id=c.post_id, author_id=c.author_id, phoenix_scores=ps,
+                                             weighted_score=w, score=w))
+        except PhoenixError as err:                      # phoenix_scorer.rs:131-134
+            return [f"Phoenix prediction failed: {err}"] * n
+        return out
+
+    def update(self, candidate: Candidate, scored: Candidate) -> None:
+        candidate.phoenix_scores = scored.phoenix_scores
+        if scored.weighted_score is not None:
+            candidate.weighted_score = scored.weighted_score
+            candidate.score = scored.score
+
+
+class Source:
+    def enable(self, query: Query) -> bool:
+        return True
+
+    def source(self, query: Query) -> Union[List[Candidate], str]:
+        raise NotImplementedError
+
+    def run(self, query: Query) -> Union[List[Candidate], str]:
+        return self.source(query)
+
+
+class PhoenixSource(Source):
+    """User tower + exhaustive top-k over the corpus shards of this process
+    (home-mixer/sources/phoenix_source.rs:113-150).  `post_ids` / `author_ids` map corpus rows to ids
+    like the reference's reply (phoenix/xrex/inference/model_runner.py:5332-5360); rows whose post id
+    is 0 are dropped (xai-recsys-engine/src/python.rs:846-864)."""
+
+    def __init__(self, tower: PhoenixEngine, retriever, post_ids: np.ndarray, author_ids: np.ndarray):
+        self.tower = tower
+        self.retriever = retriever
+        self.post_ids = post_ids
+        self.author_ids = author_ids
+
+    def enable(self, query: Query) -> bool:
+        return not query.has_cached_posts
+
+    def source(self, query: Query) -> Union[List[Candidate], str]:
+        if query.history is None:
+            return "PhoenixSource: missing retrieval_sequence"
+        try:
+            scores, rows = self.retriever.retrieve_for_history(self.tower, query.history, query.top_k)
+        except PhoenixError as err:
+            return f"PhoenixSource: {err}"
+        out = []
+        for s, r in zip(scores, rows):
+            pid = int(self.post_ids[r])
+            if pid == 0:
+                continue
+            out.append(Candidate(post_id=pid, author_id=int(self.author_ids[r]), score=float(s)))
+        return out

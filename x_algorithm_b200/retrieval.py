@@ -1,0 +1,120 @@
+"""Corpus shards and exhaustive dot-product top-k (phoenix/xrex/models/recsys_two_tower_model.py:
+2455-2516, 193-221; phoenix/xrex/cuda/top_k_by_key/__init__.py:56-94) over the C ABI."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Sequence
+
+import numpy as np
+
+from . import _lib
+from ._lib import PhoenixError, lib
+
+
+class CorpusShard:
+    """Rows [row_offset, row_offset + rows) of the post corpus on one device."""
+
+    def __init__(self, rows: int, dim: int, row_offset: int = 0, max_queries: int = 256, max_k: int = 1000,
+                 device: int = 0):
+        self.rows, self.dim, self.row_offset, self.device = rows, dim, row_offset, device
+        self.max_queries, self.max_k = max_queries, max_k
+        self._h = C.c_void_p()
+        st = lib.phx_corpus_create(device, rows, dim, row_offset, max_queries, max_k, C.byref(self._h))
+        if st != 0:
+            raise PhoenixError(st, lib.phx_global_error().decode())
+
+    def _check(self, st: int):
+        if st != 0:
+            raise PhoenixError(st, lib.phx_corpus_last_error(self._h).decode())
+
+    def close(self):
+        if self._h:
+            lib.phx_corpus_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def upload(self, row0: int, rows_bf16_bits: np.ndarray):
+        a = np.ascontiguousarray(rows_bf16_bits, dtype=np.uint16)
+        self._check(lib.phx_corpus_upload(self._h, row0, a.shape[0], a.ctypes.data))
+
+    def fill_synthetic(self, seed: int):
+        self._check(lib.phx_corpus_fill_synthetic(self._h, seed))
+
+    def topk_device(self, users, B: int, k: int, scores, ids):
+        """users f32 [B,dim], scores f32 [B,k], ids int64 [B,k]: torch CUDA tensors; asynchronous."""
+        self._check(lib.phx_corpus_topk_device(self._h, int(users.data_ptr()), B, k, int(scores.data_ptr()),
+                                               int(ids.data_ptr())))
+
+    def merge_device(self, scores, ids, P: int, B: int, k: int, out_scores, out_ids):
+        self._check(lib.phx_topk_merge_device(self._h, int(scores.data_ptr()), int(ids.data_ptr()), P, B, k,
+                                              int(out_scores.data_ptr()), int(out_ids.data_ptr())))
+
+    def sync(self):
+        self._check(lib.phx_corpus_sync(self._h))
+
+    def last_device_ms(self) -> float:
+        ms = C.c_float()
+        self._check(lib.phx_corpus_last_device_ms(self._h, C.byref(ms)))
+        return float(ms.value)
+
+
+class Retriever:
+    """User tower -> per-shard top-k -> merge.  With torch.distributed initialised, each rank holds one
+    shard and the per-shard lists are merged after an all-gather (the reference's shard-local top-k +
+    all_gather + top_k merge, recsys_two_tower_model.py:215-220); otherwise the local shards are merged
+    directly."""
+
+    def __init__(self, shards: Sequence[CorpusShard]):
+        self.shards = list(shards)
+
+    def retrieve(self, users, k: int):
+        import torch
+        B = users.shape[0]
+        dev = users.device
+        P = len(self.shards)
+        sc = torch.empty((P, B, k), dtype=torch.float32, device=dev)
+        ids = torch.empty((P, B, k), dtype=torch.int64, device=dev)
+        torch.cuda.synchronize()
+        for p, sh in enumerate(self.shards):
+            sh.topk_device(users, B, k, sc[p], ids[p])
+        for sh in self.shards:
+            sh.sync()
+        dist = torch.distributed
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            W = dist.get_world_size()
+            gs = torch.empty((W * P, B, k), dtype=torch.float32, device=dev)
+            gi = torch.empty((W * P, B, k), dtype=torch.int64, device=dev)
+            dist.all_gather_into_tensor(gs, sc)
+            dist.all_gather_into_tensor(gi, ids)
+            sc, ids, P = gs, gi, W * P
+        if P == 1:
+            return sc[0], ids[0]
+        out_s = torch.empty((B, k), dtype=torch.float32, device=dev)
+        out_i = torch.empty((B, k), dtype=torch.int64, device=dev)
+        torch.cuda.synchronize()
+        self.shards[0].merge_device(sc, ids, P, B, k, out_s, out_i)
+        self.shards[0].sync()
+        return out_s, out_i
+
+    def retrieve_for_history(self, tower, history, k: int):
+        import torch
+        cfg = tower.cfg
+        S = cfg.history_len
+        hist = [h for h in history if h.post_id != 0 and h.author_id != 0][-S:]
+        hp = np.zeros((1, S), np.int64); ha = np.zeros((1, S), np.int64)
+        act = np.zeros((1, S), np.int32); srf = np.zeros((1, S), np.int32)
+        for j, h in enumerate(hist):
+            hp[0, j], ha[0, j], act[0, j], srf[0, j] = h.post_id, h.author_id, h.action, h.surface
+        dev = torch.device("cuda", tower.device)
+        t = [torch.from_numpy(a).to(dev) for a in (hp, ha, act, srf)]
+        users = torch.empty((1, cfg.emb_size), dtype=torch.float32, device=dev)
+        torch.cuda.synchronize()
+        tower.user_tower_device(1, *t, users)
+        tower.sync()
+        s, i = self.retrieve(users, k)
+        return s[0].cpu().numpy(), i[0].cpu().numpy()
