@@ -150,7 +150,11 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
       pf[j >> 1][(j & 1) * 2 + 1] = pack_bf2(p[2], p[3]);
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i) l[i] = l[i] * alpha[i] + ls[i];
+    for (int i = 0; i < 2; ++i) {  // a row's 64 probabilities are spread over the 4 lanes of its quad
+      ls[i] += __shfl_xor_sync(0xffffffffu, ls[i], 1);
+      ls[i] += __shfl_xor_sync(0xffffffffu, ls[i], 2);
+      l[i] = l[i] * alpha[i] + ls[i];
+    }
 #pragma unroll
     for (int j = 0; j < DT; ++j) { o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1]; }
     // O += P V : k-steps of 16 keys, n-tiles of 8 output columns (two per ldmatrix.x4.trans)
