@@ -220,6 +220,24 @@ phx_status phx_corpus_topk_device(phx_corpus* c, const float* users_dev, int32_t
  * (strided_dataset_top_k, recsys_two_tower_model.py:215-220). */
 phx_status phx_topk_merge_device(phx_corpus* c, const float* scores_dev, const int64_t* ids_dev, int32_t P,
                                  int32_t B, int32_t k, float* out_scores_dev, int64_t* out_ids_dev);
+/* The same merge for callers that must not allocate device memory.  (No counterpart in the reference.)
+ * Some hosts of this library hand it a stream and buffers but own all device memory themselves: a
+ * custom-call handler running inside a compiler-managed step, or a serving process whose memory pool
+ * was sized up front and leaves nothing for cudaMalloc, which would also stall the device.  This entry
+ * point calls no cudaMalloc / cudaFree and no allocating library routine: its scratch (the 64-bit sort
+ * keys and a status word) is a fixed 16 MiB array inside the library image, present on every device
+ * that loads the library until the process exits.
+ *   - limit: P * B * k <= 2,097,152 keys (e.g. 8 shards x 256 queries x k = 1000); larger merges are
+ *     refused with PHX_E_CAPACITY and belong to phx_topk_merge_device;
+ *   - the first call on a device looks up the array's device address (once per device, with that
+ *     device current); make that first call before any stream capture begins;
+ *   - all calls share the one array, which keeps the previous call's contents: the entry point clears
+ *     what must start at zero itself, but two calls whose kernels overlap on the GPU (different
+ *     streams, no ordering between them) race on it; order them;
+ *   - asynchronous on `stream` (a cudaStream_t, NULL = the default stream); inputs and outputs are the
+ *     caller's device buffers, laid out as for phx_topk_merge_device. */
+phx_status phx_topk_merge_static(int32_t device, const float* scores_dev, const int64_t* ids_dev, int32_t P,
+                                 int32_t B, int32_t k, float* out_scores_dev, int64_t* out_ids_dev, void* stream);
 phx_status phx_corpus_sync(phx_corpus* c);
 phx_status phx_corpus_last_device_ms(phx_corpus* c, float* ms);
 const char* phx_corpus_last_error(const phx_corpus* c);

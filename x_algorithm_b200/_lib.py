@@ -80,6 +80,7 @@ SIGNATURES = {
     "phx_corpus_fill_synthetic": (C.c_int32, [_P, C.c_uint32]),
     "phx_corpus_topk_device": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, _P, _P]),
     "phx_topk_merge_device": (C.c_int32, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, _P, _P]),
+    "phx_topk_merge_static": (C.c_int32, [C.c_int32, _P, _P, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P]),
     "phx_corpus_sync": (C.c_int32, [_P]),
     "phx_corpus_last_device_ms": (C.c_int32, [_P, C.POINTER(C.c_float)]),
     "phx_corpus_last_error": (C.c_char_p, [_P]),

@@ -16,6 +16,7 @@
 // PHX_E_CAPACITY instead of returning a wrong answer.
 #include <math.h>
 
+#include <mutex>
 #include <vector>
 
 #include "common.cuh"
@@ -494,6 +495,69 @@ phx_status phx_topk_merge_device(phx_corpus* c, const float* scores_dev, const i
   select_kernel<<<B, SEL_THREADS, (size_t)kp2 * 8, c->stream>>>(c->merge_keys, nullptr, P * k, P * k, k, kp2, out_scores_dev,
                                                                (long long*)out_ids_dev, c->status);
   PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  return PHX_OK;
+}
+
+// ---- merge without any allocation ---------------------------------------------------------------------
+// Scratch for phx_topk_merge_static: the 64-bit sort keys of one merge and its status word live in
+// device memory that belongs to the loaded library image, not to an allocator.  Every device that
+// loads the library carries these 16 MiB until the process exits.
+#define PHX_STATIC_MERGE_MAX_KEYS (1 << 21)
+static __device__ __align__(256) unsigned long long g_static_merge_keys[PHX_STATIC_MERGE_MAX_KEYS];
+static __device__ __align__(256) int g_static_merge_status[64];
+
+namespace {
+struct StaticScratch { unsigned long long* keys = nullptr; int* status = nullptr; bool ready = false; };
+StaticScratch g_static_scratch[64];  // by device ordinal
+std::mutex g_static_mu;
+
+// In host code `g_static_merge_keys` only names the symbol; the address a kernel may use has to be asked
+// for, per device, while that device is current.
+phx_status static_scratch_for(int device, StaticScratch** out, std::string& err) {
+  if (device < 0 || device >= 64) { err = "phx_topk_merge_static: device ordinal out of range"; return PHX_E_ARG; }
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  StaticScratch& sc = g_static_scratch[device];
+  if (!sc.ready) {
+    void* pk = nullptr; void* ps = nullptr;
+    PHX_CUDA_TRY(cudaGetSymbolAddress(&pk, g_static_merge_keys), err);
+    PHX_CUDA_TRY(cudaGetSymbolAddress(&ps, g_static_merge_status), err);
+    sc.keys = static_cast<unsigned long long*>(pk);
+    sc.status = static_cast<int*>(ps);
+    sc.ready = true;
+  }
+  *out = &sc;
+  return PHX_OK;
+}
+}  // namespace
+
+phx_status phx_topk_merge_static(int32_t device, const float* scores_dev, const int64_t* ids_dev, int32_t P, int32_t B,
+                                 int32_t k, float* out_scores_dev, int64_t* out_ids_dev, void* stream) {
+  std::string err;
+  if (!scores_dev || !ids_dev || !out_scores_dev || !out_ids_dev || P <= 0 || B <= 0 || k <= 0 || k > 4096) {
+    set_global_error("phx_topk_merge_static: bad argument (P, B, k > 0, k <= 4096, non-null buffers)");
+    return PHX_E_ARG;
+  }
+  const unsigned long long need = (unsigned long long)P * (unsigned long long)B * (unsigned long long)k;
+  if (need > (unsigned long long)PHX_STATIC_MERGE_MAX_KEYS) {
+    set_global_error("phx_topk_merge_static: P*B*k = " + std::to_string(need) + " exceeds the built-in scratch of " +
+                     std::to_string((long long)PHX_STATIC_MERGE_MAX_KEYS) + " keys; use phx_topk_merge_device");
+    return PHX_E_CAPACITY;
+  }
+  if (cudaSetDevice(device) != cudaSuccess) { set_global_error("phx_topk_merge_static: cudaSetDevice failed"); return PHX_E_CUDA; }
+  StaticScratch* sc = nullptr;
+  phx_status s = static_scratch_for(device, &sc, err);
+  if (s) { set_global_error(err); return s; }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the array keeps the previous call's contents: the status word must start at zero, the keys in
+  // [0, need) are all rewritten by the first kernel
+  cudaError_t ce = cudaMemsetAsync(sc->status, 0, sizeof(int), st);
+  if (ce != cudaSuccess) { set_global_error(std::string("phx_topk_merge_static: ") + cudaGetErrorString(ce)); return PHX_E_CUDA; }
+  merge_keys_kernel<<<(unsigned)((need + 255) / 256), 256, 0, st>>>(scores_dev, (const long long*)ids_dev, P, B, k, sc->keys);
+  const int kp2 = next_pow2(k);
+  select_kernel<<<B, SEL_THREADS, (size_t)kp2 * 8, st>>>(sc->keys, nullptr, P * k, P * k, k, kp2, out_scores_dev,
+                                                         (long long*)out_ids_dev, sc->status);
+  ce = cudaGetLastError();
+  if (ce != cudaSuccess) { set_global_error(std::string("phx_topk_merge_static: ") + cudaGetErrorString(ce)); return PHX_E_CUDA; }
   return PHX_OK;
 }
 

@@ -63,6 +63,16 @@ class CorpusShard:
         return float(ms.value)
 
 
+def merge_topk_static(scores, ids, P: int, B: int, k: int, out_scores, out_ids, device: int = 0, stream: int = 0):
+    """Merge [P,B,k] per-shard lists into [B,k] without allocating device memory: the scratch is a
+    fixed array inside the library (limit P*B*k <= 2,097,152).  For callers whose device memory is
+    owned by someone else.  Torch CUDA tensors; asynchronous on `stream` (0 = default stream)."""
+    st = lib.phx_topk_merge_static(device, int(scores.data_ptr()), int(ids.data_ptr()), P, B, k,
+                                   int(out_scores.data_ptr()), int(out_ids.data_ptr()), stream)
+    if st != 0:
+        raise PhoenixError(st, lib.phx_global_error().decode())
+
+
 class Retriever:
     """User tower -> per-shard top-k -> merge.  With torch.distributed initialised, each rank holds one
     shard and the per-shard lists are merged after an all-gather (the reference's shard-local top-k +
