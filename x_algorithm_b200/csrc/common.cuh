@@ -42,20 +42,39 @@ __device__ __forceinline__ float2 unpack_bf2(uint32_t u) {
   return __bfloat1622float2(v);
 }
 
+// GELU, tanh form.  tanh.approx (one MUFU op, abs error ~5e-4) is far below the bf16 rounding applied to the
+// result, and keeps the GEMM epilogue off the critical path.
 __device__ __forceinline__ float gelu_tanh_f(float x) {
   const float c = 0.7978845608028654f;  // sqrt(2/pi)
   float inner = c * (x + 0.044715f * x * x * x);
-  return 0.5f * x * (1.0f + tanhf(inner));
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(inner));
+  return 0.5f * x * (1.0f + t);
 }
 
 // ---- GEMM ---------------------------------------------------------------------------------------
-enum GemmEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GELU = 2 };
+enum GemmEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GELU = 2, EPI_ROPE = 3 };
+
+// RoPE fused into the epilogue of the merged QKV projection: applied to the q and k head parts
+// (column part p of width dh is q or k when p % group <= g; group = g + 2, g = q heads per kv head).
+struct GemmRope {
+  const float* cos_tab;  // [pos_cap + 1, dh / 2]
+  const float* sin_tab;
+  int T;                 // tokens per request: position = min(row % T, pos_cap)
+  int pos_cap;
+  int dh;                // 32 or 64
+  int group, g;
+};
 
 // One GEMM problem bound to fixed buffers: C[M,N] = epi(A[M,K] @ Wt[N,K]^T).  The tensor maps
 // are encoded once for (pointer, rows_max) and reused for every M <= rows_max.
 struct GemmPlan {
   CUtensorMap map_a;
   CUtensorMap map_b;
+  CUtensorMap map_c;   // output map, re-encoded when the output pointer or M changes
+  CUtensorMap map_r;   // residual map, likewise
+  const bf16* c_ptr = nullptr; const bf16* r_ptr = nullptr;
+  int64_t c_rows = -1, r_rows = -1;
   const bf16* A = nullptr;
   const bf16* Wt = nullptr;
   int64_t rows_max = 0;
@@ -67,8 +86,8 @@ phx_status gemm_plan_create(GemmPlan* plan, const bf16* A, const bf16* Wt, int64
                             std::string& err);
 // Launch on `stream`.  `R` is the residual (EPI_RESIDUAL) or null.  `err_flag` is a device int the
 // kernel sets to 1 when a bounded wait ran out.
-phx_status gemm_launch(const GemmPlan& plan, bf16* C, const bf16* R, int64_t M, int epilogue, int* err_flag,
-                       int num_sms, cudaStream_t stream, std::string& err);
+phx_status gemm_launch(GemmPlan& plan, bf16* C, const bf16* R, int64_t M, int epilogue, const GemmRope* rope,
+                       int* err_flag, int num_sms, cudaStream_t stream, std::string& err);
 // Plain SIMT GEMM with the same epilogues (debug / cross-check path, selected by PHX_GEMM=simt).
 phx_status gemm_simt_launch(const bf16* A, const bf16* Wt, bf16* C, const bf16* R, int64_t M, int N, int K,
                             int epilogue, cudaStream_t stream, std::string& err);

@@ -190,11 +190,12 @@ phx_status upload_bf16(phx_engine* e, bf16** dst, const float* host, int64_t row
   return PHX_OK;
 }
 
-phx_status do_gemm(phx_engine* e, const GemmPlan& p, bf16* Cc, const bf16* R, int64_t M, int epi) {
+phx_status do_gemm(phx_engine* e, GemmPlan& p, bf16* Cc, const bf16* R, int64_t M, int epi,
+                   const GemmRope* rope = nullptr) {
   ProfScope ps(e, KC_GEMM);
   e->last_launches++;
   if (e->use_simt_gemm) return gemm_simt_launch(p.A, p.Wt, Cc, R, M, p.N, p.K, epi, e->stream, e->err);
-  return gemm_launch(p, Cc, R, M, epi, e->err_flag, e->num_sms, e->stream, e->err);
+  return gemm_launch(p, Cc, R, M, epi, rope, e->err_flag, e->num_sms, e->stream, e->err);
 }
 
 bool params_complete(phx_engine* e, bool need_heads) {
@@ -225,8 +226,17 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len) {
     { ProfScope ps(e, KC_NORM);
     if ((s = rmsnorm_launch(e->x, L.pre_attn_norm, e->hbuf, nullptr, M, e->D, c.rms_eps, e->stream, e->err))) return s; }
     e->last_launches++;
-    if ((s = do_gemm(e, L.p_qkv, e->qkv, nullptr, M, EPI_STORE))) return s;
-    if (c.rotary || c.qk_norm) {
+    // RoPE rides in the QKV epilogue unless qk-norm has to run first or the head dim is 128
+    const bool fuse_rope = c.rotary && !c.qk_norm && !e->use_simt_gemm && (e->dh == 32 || e->dh == 64);
+    if (fuse_rope) {
+      GemmRope gr;
+      gr.cos_tab = e->cos_tab; gr.sin_tab = e->sin_tab; gr.T = Tt; gr.pos_cap = pos_cap; gr.dh = e->dh;
+      gr.g = e->Hq / e->Hkv; gr.group = gr.g + 2;
+      if ((s = do_gemm(e, L.p_qkv, e->qkv, nullptr, M, EPI_ROPE, &gr))) return s;
+    } else {
+      if ((s = do_gemm(e, L.p_qkv, e->qkv, nullptr, M, EPI_STORE))) return s;
+    }
+    if (!fuse_rope && (c.rotary || c.qk_norm)) {
       QkNormRopeArgs qa;
       qa.qkv = e->qkv; qa.M = M; qa.T = Tt; qa.Hq = e->Hq; qa.Hkv = e->Hkv; qa.dh = e->dh; qa.pos_cap = pos_cap;
       qa.rotary = c.rotary; qa.qk_norm = c.qk_norm; qa.q_gain = L.q_norm; qa.k_gain = L.k_norm;
@@ -717,7 +727,8 @@ phx_status phx_gemm_device(int32_t device, const uint16_t* A, const uint16_t* Wt
     GemmPlan plan;
     s = gemm_plan_create(&plan, (const bf16*)A, (const bf16*)Wt, M, N, K, err);
     cudaEventRecord(e0, 0);
-    if (s == PHX_OK) s = gemm_launch(plan, (bf16*)C, (const bf16*)R, M, epilogue, flag, prop.multiProcessorCount, 0, err);
+    if (s == PHX_OK && (epilogue < 0 || epilogue > 2)) { err = "phx_gemm_device: epilogue must be 0, 1 or 2"; s = PHX_E_ARG; }
+    if (s == PHX_OK) s = gemm_launch(plan, (bf16*)C, (const bf16*)R, M, epilogue, nullptr, flag, prop.multiProcessorCount, 0, err);
     cudaEventRecord(e1, 0);
   }
   cudaError_t ce = cudaEventSynchronize(e1);

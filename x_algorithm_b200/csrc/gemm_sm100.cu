@@ -6,10 +6,14 @@
 //               into a ring of shared-memory stages (cp.async.bulk.tensor + mbarrier tx count)
 //   warp 1      MMA issuer: one lane issues tcgen05.mma (M=128, N=BN, K=16) x4 per stage into one
 //               of two TMEM accumulators, tcgen05.commit releases the stage / publishes the tile
-//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (each warp its 32-lane quadrant),
-//               fused epilogue (store | +residual | GELU-tanh), bf16 stores; overlaps the next
-//               tile's main loop through the second accumulator
+//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (each warp its 32-lane quadrant) in
+//               64-column slabs, fused op (store | +residual | GELU-tanh | RoPE), bf16 slab staged in
+//               swizzled shared memory and written by one TMA bulk store; the residual slab is
+//               fetched by TMA one slab ahead; overlaps the next tile's main loop through the second
+//               accumulator
 // Every mbarrier wait is bounded by wall time; on expiry the kernel raises *err_flag and unwinds.
+#include <string.h>
+
 #include "common.cuh"
 
 namespace phx {
@@ -29,7 +33,7 @@ struct Cfg {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024 alignment slack
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * (128 * 64 * 2) + BAR_BYTES + 1024;  // + 2 output slabs, +1024 alignment slack
   static constexpr int TMEM_COLS = 2 * BN;                                    // two accumulators
 };
 
@@ -132,45 +136,100 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
          | ((uint32_t)(M >> 4) << 24);   // M / 16
 }
 
-template <int EPI>
-__device__ __forceinline__ void epilogue_chunk(const uint32_t* acc, bf16* c_row, const bf16* r_row, int col0, int N) {
-  // 32 fp32 accumulators -> 32 bf16, 16-byte stores; N % 8 == 0 is guaranteed by the host
+// ---- epilogue helpers -----------------------------------------------------------------------------
+constexpr int SLAB_COLS = 64;                 // one output slab = 128 rows x 64 bf16 columns = 128-byte rows
+constexpr int SLAB_BYTES = BM * SLAB_COLS * 2;
+constexpr int EPI_THREADS = 128;
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// barrier 1 over the 128 epilogue threads, AND-reducing a per-thread flag: every thread always arrives,
+// so a role that gave up on a bounded wait can never leave the others parked here
+__device__ __forceinline__ bool epi_barrier_and(bool ok) {
+  uint32_t out;
+  asm volatile(
+      "{\n .reg .pred p, q;\n setp.ne.u32 q, %1, 0;\n bar.red.and.pred p, 1, 128, q;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(out) : "r"((uint32_t)ok) : "memory");
+  return out != 0;
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// RoPE on the q / k head parts held in one 64-column slab (layers.py:52-67, 784-788): pairs (j, j + dh/2)
+__device__ __forceinline__ void rope_slab(float (&v)[64], const GemmRope& rp, int col0, long long row) {
+  const int t = (int)(row % rp.T);
+  const int pos = t < rp.pos_cap ? t : rp.pos_cap;
+  if (rp.dh == 64) {
+    const int kind = (col0 >> 6) % rp.group;
+    if (kind > rp.g) return;  // v part
+    const float4* c4 = reinterpret_cast<const float4*>(rp.cos_tab + (long long)pos * 32);
+    const float4* s4 = reinterpret_cast<const float4*>(rp.sin_tab + (long long)pos * 32);
 #pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    int col = col0 + g * 8;
-    if (col >= N) break;
-    float v[8];
+    for (int jj = 0; jj < 8; ++jj) {
+      const float4 c = __ldg(c4 + jj), s = __ldg(s4 + jj);
+      const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {s.x, s.y, s.z, s.w};
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = round_bf(__uint_as_float(acc[g * 8 + i]));  // Linear output is bf16
-    if (EPI == EPI_RESIDUAL) {
-      uint4 rr = *reinterpret_cast<const uint4*>(r_row + col);
-      float2 a = unpack_bf2(rr.x), b = unpack_bf2(rr.y), c = unpack_bf2(rr.z), d = unpack_bf2(rr.w);
-      v[0] += a.x; v[1] += a.y; v[2] += b.x; v[3] += b.y; v[4] += c.x; v[5] += c.y; v[6] += d.x; v[7] += d.y;
-    } else if (EPI == EPI_GELU) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = gelu_tanh_f(v[i]);
+      for (int e = 0; e < 4; ++e) {
+        const int j = jj * 4 + e;
+        const float x1 = v[j], x2 = v[j + 32];
+        v[j] = x1 * cc[e] - x2 * ss[e];
+        v[j + 32] = x2 * cc[e] + x1 * ss[e];
+      }
     }
-    uint4 o;
-    o.x = pack_bf2(v[0], v[1]); o.y = pack_bf2(v[2], v[3]); o.z = pack_bf2(v[4], v[5]); o.w = pack_bf2(v[6], v[7]);
-    *reinterpret_cast<uint4*>(c_row + col) = o;
+  } else {  // dh == 32: two head parts per slab
+    const float4* c4 = reinterpret_cast<const float4*>(rp.cos_tab + (long long)pos * 16);
+    const float4* s4 = reinterpret_cast<const float4*>(rp.sin_tab + (long long)pos * 16);
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {
+      const int kind = ((col0 >> 5) + part) % rp.group;
+      if (kind > rp.g) continue;
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const float4 c = __ldg(c4 + jj), s = __ldg(s4 + jj);
+        const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = part * 32 + jj * 4 + e;
+          const float x1 = v[j], x2 = v[j + 16];
+          v[j] = x1 * cc[e] - x2 * ss[e];
+          v[j + 16] = x2 * cc[e] + x1 * ss[e];
+        }
+      }
+    }
   }
 }
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    bf16* C, const bf16* R, long long M, int N, int K, int* err_flag) {
-  // C and R may alias (in-place residual update): each thread reads its R chunk before writing the same C chunk
+                    const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_r,
+                    GemmRope rope, long long M, int N, int K, int* err_flag) {
+  // C and R may be the same buffer (in-place residual update): a slab is fetched before it is written back,
+  // and no other CTA touches the tile.
   using cfg = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
-  const uint32_t bars = smem_base + cfg::STAGES * cfg::STAGE_BYTES;
-  // barrier slots (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then the TMEM slot
+  const uint32_t slab_base = smem_base + cfg::STAGES * cfg::STAGE_BYTES;   // 2 output slabs
+  const uint32_t bars = slab_base + 2 * SLAB_BYTES;
+  // barrier slots (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], res[2]; then the TMEM slot
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (cfg::STAGES + s); };
   auto tfull_bar = [&](int a) { return bars + 8u * (2 * cfg::STAGES + a); };
   auto tempty_bar = [&](int a) { return bars + 8u * (2 * cfg::STAGES + 2 + a); };
-  const uint32_t tmem_slot = bars + 8u * (2 * cfg::STAGES + 4);
+  auto res_bar = [&](int b) { return bars + 8u * (2 * cfg::STAGES + 4 + b); };
+  const uint32_t tmem_slot = bars + 8u * (2 * cfg::STAGES + 6);
   uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -182,7 +241,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < cfg::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 128); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), EPI_THREADS); mbar_init(res_bar(a), 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(tmem_slot, cfg::TMEM_COLS);
@@ -241,30 +300,85 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
   } else {
     // ---------------- epilogue (warps 2..5) ----------------
-    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
-    uint32_t it = 0;
-    bool ok = true;
-    for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-      const int n_blk = (int)(tile % n_tiles);
-      const long long m_blk = tile / n_tiles;
-      const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
-      if (!mbar_wait(tfull_bar(acc), acc_phase, verr)) { ok = false; break; }
-      tc_fence_after();
-      const long long row = m_blk * BM + quad * 32 + lane;
-      const bool row_ok = row < M;
-      bf16* c_row = C + row * (long long)N;
-      const bf16* r_row = (EPI == EPI_RESIDUAL) ? (R + row * (long long)N) : nullptr;
-      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        const int col0 = n_blk * BN + c * 32;
-        if (row_ok && col0 < N) epilogue_chunk<EPI>(r, c_row, r_row, col0, N);
-      }
-      tc_fence_before();
-      mbar_arrive(tempty_bar(acc));
+    // Work item = one 64-column slab of a tile.  TMEM -> registers -> fused op -> swizzled shared-memory slab
+    // -> one TMA bulk store; the residual slab arrives by TMA into the same buffer one item ahead.
+    constexpr int SLABS = BN / SLAB_COLS;
+    constexpr bool RES = (EPI == EPI_RESIDUAL);
+    const int quad = warp & 3;               // TMEM lane quadrant this warp may read
+    const int row_in_tile = quad * 32 + lane;
+    const bool issuer = (warp == 2 && lane == 0);
+    const long long my_tiles = (total_tiles > blockIdx.x) ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const long long total_items = my_tiles * SLABS;
+    auto coords = [&](long long q, long long& m0, int& c0) {
+      const long long tile = blockIdx.x + (q / SLABS) * gridDim.x;
+      m0 = (tile / n_tiles) * BM;
+      c0 = (int)(tile % n_tiles) * BN + (int)(q % SLABS) * SLAB_COLS;
+    };
+    if (RES && issuer && total_items > 0) {
+      long long m0; int c0; coords(0, m0, c0);
+      mbar_expect_tx(res_bar(0), SLAB_BYTES);
+      tma_load_2d(slab_base, &map_r, res_bar(0), c0, (int)m0);
     }
+    for (long long q = 0; q < total_items; ++q) {
+      const int s = (int)(q % SLABS);
+      const uint32_t it = (uint32_t)(q / SLABS), acc = it & 1, acc_phase = (it >> 1) & 1;
+      const int buf = (int)(q & 1);
+      const uint32_t slab = slab_base + buf * SLAB_BYTES;
+      long long m0; int c0; coords(q, m0, c0);
+      if (RES && issuer) {
+        bulk_wait_read0();  // the store of item q-1 has drained the other buffer
+        if (q + 1 < total_items) {
+          long long m1; int c1; coords(q + 1, m1, c1);
+          mbar_expect_tx(res_bar(buf ^ 1), SLAB_BYTES);
+          tma_load_2d(slab_base + (buf ^ 1) * SLAB_BYTES, &map_r, res_bar(buf ^ 1), c1, (int)m1);
+        }
+      }
+      bool ok = true;
+      if (s == 0) ok = mbar_wait(tfull_bar(acc), acc_phase, verr);
+      if (RES && ok) ok = mbar_wait(res_bar(buf), (uint32_t)((q >> 1) & 1), verr);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tc_fence_after();
+        uint32_t r[64];
+        const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16) + s * SLAB_COLS;
+        tmem_ld32(taddr, r);
+        tmem_ld32(taddr + 32, r + 32);
+        if (s == SLABS - 1) { tc_fence_before(); mbar_arrive(tempty_bar(acc)); }  // accumulator drained
+        float v[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) v[i] = round_bf(__uint_as_float(r[i]));       // Linear output is bf16
+        if (EPI == EPI_GELU) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) v[i] = gelu_tanh_f(v[i]);
+        } else if (EPI == EPI_ROPE) {
+          rope_slab(v, rope, c0, m0 + row_in_tile);
+        }
+        const uint32_t row_addr = slab + row_in_tile * 128;
+        const int sw = row_in_tile & 7;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t addr = row_addr + ((uint32_t)(c ^ sw) << 4);
+          if (RES) {
+            const uint4 rr = ld_shared_v4(addr);
+            const float2 a = unpack_bf2(rr.x), b = unpack_bf2(rr.y), cc = unpack_bf2(rr.z), d = unpack_bf2(rr.w);
+            v[c * 8 + 0] += a.x; v[c * 8 + 1] += a.y; v[c * 8 + 2] += b.x; v[c * 8 + 3] += b.y;
+            v[c * 8 + 4] += cc.x; v[c * 8 + 5] += cc.y; v[c * 8 + 6] += d.x; v[c * 8 + 7] += d.y;
+          }
+          uint4 o;
+          o.x = pack_bf2(v[c * 8 + 0], v[c * 8 + 1]); o.y = pack_bf2(v[c * 8 + 2], v[c * 8 + 3]);
+          o.z = pack_bf2(v[c * 8 + 4], v[c * 8 + 5]); o.w = pack_bf2(v[c * 8 + 6], v[c * 8 + 7]);
+          st_shared_v4(addr, o);
+        }
+        fence_async_smem();
+      }
+      if (!RES && issuer) bulk_wait_read0();  // store q-1 has drained the buffer item q+1 will fill
+      if (!epi_barrier_and(ok)) break;         // uniform over the 128 epilogue threads
+      if (issuer && c0 < N) {
+        tma_store_2d(&map_c, slab, c0, (int)m0);
+        bulk_commit();
+      }
+    }
+    if (issuer) bulk_wait_all();
   }
 
   // ---------------- teardown ----------------
@@ -319,7 +433,7 @@ phx_status make_map(CUtensorMap* map, const bf16* ptr, int64_t rows, int64_t col
 }
 
 template <int BN, int EPI>
-phx_status launch_t(const GemmPlan& p, bf16* C, const bf16* R, int64_t M, int* err_flag, int num_sms,
+phx_status launch_t(const GemmPlan& p, const GemmRope& rope, int64_t M, int* err_flag, int num_sms,
                     cudaStream_t stream, std::string& err) {
   using cfg = Cfg<BN>;
   static bool attr_set = false;
@@ -331,8 +445,8 @@ phx_status launch_t(const GemmPlan& p, bf16* C, const bf16* R, int64_t M, int* e
   const long long tiles = ((M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   int grid = (int)(tiles < num_sms ? tiles : num_sms);
   if (grid <= 0) return PHX_OK;
-  gemm_tcgen05_kernel<BN, EPI><<<grid, GEMM_THREADS, cfg::SMEM_BYTES, stream>>>(p.map_a, p.map_b, C, R, M, p.N, p.K,
-                                                                               err_flag);
+  gemm_tcgen05_kernel<BN, EPI><<<grid, GEMM_THREADS, cfg::SMEM_BYTES, stream>>>(
+      p.map_a, p.map_b, p.map_c, (EPI == EPI_RESIDUAL) ? p.map_r : p.map_c, rope, M, p.N, p.K, err_flag);
   PHX_CUDA_TRY(cudaGetLastError(), err);
   return PHX_OK;
 }
@@ -382,21 +496,43 @@ phx_status gemm_plan_create(GemmPlan* plan, const bf16* A, const bf16* Wt, int64
   return PHX_OK;
 }
 
-phx_status gemm_launch(const GemmPlan& p, bf16* C, const bf16* R, int64_t M, int epilogue, int* err_flag,
-                       int num_sms, cudaStream_t stream, std::string& err) {
+phx_status gemm_launch(GemmPlan& p, bf16* C, const bf16* R, int64_t M, int epilogue, const GemmRope* rope,
+                       int* err_flag, int num_sms, cudaStream_t stream, std::string& err) {
   if (!p.ready || M > p.rows_max) { err = "gemm: plan not ready or M exceeds plan rows"; return PHX_E_ARG; }
   if (epilogue == EPI_RESIDUAL && R == nullptr) { err = "gemm: residual epilogue needs R"; return PHX_E_ARG; }
+  GemmRope rp;
+  memset(&rp, 0, sizeof(rp));
+  if (epilogue == EPI_ROPE) {
+    if (!rope || (rope->dh != 32 && rope->dh != 64) || rope->T <= 0 || p.N % rope->dh != 0) {
+      err = "gemm: the RoPE epilogue needs head dim 32 or 64";
+      return PHX_E_ARG;
+    }
+    rp = *rope;
+  }
+  // output / residual maps are [M, N] with 128 x 64 boxes; rows past M are clipped by the TMA unit
+  if (p.c_ptr != C || p.c_rows != M) {
+    phx_status s = make_map(&p.map_c, C, M, p.N, BM, err);
+    if (s != PHX_OK) return s;
+    p.c_ptr = C; p.c_rows = M;
+  }
+  if (epilogue == EPI_RESIDUAL && (p.r_ptr != R || p.r_rows != M)) {
+    phx_status s = make_map(&p.map_r, R, M, p.N, BM, err);
+    if (s != PHX_OK) return s;
+    p.r_ptr = R; p.r_rows = M;
+  }
   if (p.BN == 256) {
     switch (epilogue) {
-      case EPI_STORE: return launch_t<256, EPI_STORE>(p, C, R, M, err_flag, num_sms, stream, err);
-      case EPI_RESIDUAL: return launch_t<256, EPI_RESIDUAL>(p, C, R, M, err_flag, num_sms, stream, err);
-      case EPI_GELU: return launch_t<256, EPI_GELU>(p, C, R, M, err_flag, num_sms, stream, err);
+      case EPI_STORE: return launch_t<256, EPI_STORE>(p, rp, M, err_flag, num_sms, stream, err);
+      case EPI_RESIDUAL: return launch_t<256, EPI_RESIDUAL>(p, rp, M, err_flag, num_sms, stream, err);
+      case EPI_GELU: return launch_t<256, EPI_GELU>(p, rp, M, err_flag, num_sms, stream, err);
+      case EPI_ROPE: return launch_t<256, EPI_ROPE>(p, rp, M, err_flag, num_sms, stream, err);
     }
   } else {
     switch (epilogue) {
-      case EPI_STORE: return launch_t<128, EPI_STORE>(p, C, R, M, err_flag, num_sms, stream, err);
-      case EPI_RESIDUAL: return launch_t<128, EPI_RESIDUAL>(p, C, R, M, err_flag, num_sms, stream, err);
-      case EPI_GELU: return launch_t<128, EPI_GELU>(p, C, R, M, err_flag, num_sms, stream, err);
+      case EPI_STORE: return launch_t<128, EPI_STORE>(p, rp, M, err_flag, num_sms, stream, err);
+      case EPI_RESIDUAL: return launch_t<128, EPI_RESIDUAL>(p, rp, M, err_flag, num_sms, stream, err);
+      case EPI_GELU: return launch_t<128, EPI_GELU>(p, rp, M, err_flag, num_sms, stream, err);
+      case EPI_ROPE: return launch_t<128, EPI_ROPE>(p, rp, M, err_flag, num_sms, stream, err);
     }
   }
   err = "gemm: unknown epilogue";
