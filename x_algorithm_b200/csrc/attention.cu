@@ -3,19 +3,24 @@
 // (mask: phoenix/xrex/pallas/ranker_attention_utils.py:16-56; kernel form
 // phoenix/xrex/pallas/ranker_attention_v2.py:113-148, 183).
 //
-// The candidate x candidate block is never formed: the kernel streams only the history keys
-// through shared memory (64 keys per step) and folds the candidate's single self key in as one
-// extra online-softmax step computed as a per-row dot product.  One CTA = 64 query rows of one
-// (batch, head): 4 warps x 16 rows, Q fragments in registers, S = Q K^T and O += P V on
-// mma.sync m16n8k16 bf16 with fp32 accumulation, P rounded to bf16 before P V as the reference does.
+// The candidate x candidate block is never formed: only the history keys stream through shared memory
+// (64 keys per step, two cp.async buffers) and a candidate's single self key is folded in as one extra
+// online-softmax step computed as a per-row dot product.  One CTA = 128 query rows of one
+// (batch, head): 8 warps x 16 rows.  Everything a CTA needs at the start (Q tile, the tile's own K/V rows
+// for the self term, the first two key blocks) is requested up front with cp.async, so a history of
+// <= 128 keys costs a single round trip to L2/HBM.  S = Q K^T and O += P V run on mma.sync m16n8k16
+// bf16 with fp32 accumulation, fragments come from padded shared memory through ldmatrix, P is rounded
+// to bf16 before P V as the reference does, and the output tile is staged in shared memory so global
+// stores are full 16-byte chunks of contiguous rows.
 #include "common.cuh"
 
 namespace phx {
 namespace {
 
-constexpr int KB = 64;        // keys per step
-constexpr int QROWS = 64;     // query rows per CTA
-constexpr int ATT_THREADS = 128;
+constexpr int KB = 64;           // keys per step
+constexpr int ATT_WARPS = 8;
+constexpr int QROWS = 16 * ATT_WARPS;
+constexpr int ATT_THREADS = 32 * ATT_WARPS;
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -23,118 +28,165 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+__device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
-__device__ __forceinline__ float cap_logit(float s, float cap, int method) {
-  if (method == 1) return s / (1.0f + fabsf(s) / cap);   // soft_sign
-  if (method == 2) return cap * tanhf(s / cap);          // tanh
-  return s;
+__device__ __forceinline__ void cp16(uint32_t dst, const void* src, bool pred) {
+  const int sz = pred ? 16 : 0;  // size 0 -> the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// logits are kept in the log2 domain: value = cap(s * sm_scale) * log2(e)
+__device__ __forceinline__ float scaled_logit(float s, float sm_scale, float cap, int method) {
+  const float LOG2E = 1.4426950408889634f;
+  float v = s * sm_scale;
+  if (method == 1) v = v / (1.0f + fabsf(v) / cap);   // soft_sign
+  else if (method == 2) v = cap * tanhf(v / cap);     // tanh
+  return v * LOG2E;
 }
 
 template <int DH>
 __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs a) {
-  constexpr int LD = DH + 8;          // padded row (elements): conflict-free fragment loads
+  constexpr int LD = DH + 8;          // padded row (elements): conflict-free ldmatrix
   constexpr int KSTEPS = DH / 16;     // k-steps of Q K^T
   constexpr int DT = DH / 8;          // output n-tiles
-  __shared__ __align__(16) bf16 sk[KB * LD];
-  __shared__ __align__(16) bf16 sv[KB * LD];
-  __shared__ int skey_ok[KB];
+  constexpr int CH = DH / 8;          // 16-byte chunks per row
+  extern __shared__ __align__(16) uint8_t asm_raw[];
+  bf16* sq = reinterpret_cast<bf16*>(asm_raw);     // [QROWS][LD]  Q tile, later the output tile
+  bf16* sks = sq + QROWS * LD;                     // [QROWS][LD]  K rows of the tile's own tokens
+  bf16* svs = sks + QROWS * LD;                    // [QROWS][LD]  V rows of the tile's own tokens
+  bf16* skv = svs + QROWS * LD;                    // [2][2][KB][LD]  key-block ring: (buffer, K|V)
+  int* skey_ok = reinterpret_cast<int*>(skv + 4 * KB * LD);  // [2][KB]
 
   const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * QROWS;
   const int hk = h / (a.Hq / a.Hkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int T = a.T;
-  const float LOG2E = 1.4426950408889634f;
+  const long long tok0 = (long long)b * T;
+  const int n_hist = a.hist_len < T ? a.hist_len : T;
+  const int n_blocks = (n_hist + KB - 1) / KB;
+  const bool has_cand = (q0 + QROWS > n_hist);     // rows at or past hist_len may be candidates
 
-  // rows of this thread: r0 = q0 + warp*16 + g, r1 = r0 + 8
+  const bf16* kbase = a.k + (long long)hk * a.k_head_stride;
+  const bf16* vbase = a.v + (long long)hk * a.v_head_stride;
+
+  auto load_block = [&](int blk, int buf) {
+    bf16* dk = skv + (size_t)(buf * 2 + 0) * KB * LD;
+    bf16* dv = skv + (size_t)(buf * 2 + 1) * KB * LD;
+    for (int c = threadIdx.x; c < KB * CH; c += ATT_THREADS) {
+      const int kr = c / CH, dc = (c % CH) * 8;
+      const int key = blk * KB + kr;
+      const bool ok = key < n_hist;
+      const long long tok = tok0 + (ok ? key : 0);
+      cp16((uint32_t)__cvta_generic_to_shared(dk + kr * LD + dc), kbase + tok * a.k_tok_stride + dc, ok);
+      cp16((uint32_t)__cvta_generic_to_shared(dv + kr * LD + dc), vbase + tok * a.v_tok_stride + dc, ok);
+    }
+    if (threadIdx.x < KB) {
+      const int key = blk * KB + threadIdx.x;
+      skey_ok[buf * KB + threadIdx.x] = (key < n_hist) && (a.seg[tok0 + key] == 1);
+    }
+  };
+
+  // ---- prologue: Q tile, own K/V rows, key blocks 0 and 1 --------------------------------------------
+  for (int c = threadIdx.x; c < QROWS * CH; c += ATT_THREADS) {
+    const int r = c / CH, dc = (c % CH) * 8;
+    const bool ok = (q0 + r) < T;
+    const long long tok = tok0 + (ok ? q0 + r : 0);
+    cp16((uint32_t)__cvta_generic_to_shared(sq + r * LD + dc), a.q + tok * a.q_tok_stride + (long long)h * a.q_head_stride + dc, ok);
+    if (has_cand) {
+      cp16((uint32_t)__cvta_generic_to_shared(sks + r * LD + dc), kbase + tok * a.k_tok_stride + dc, ok);
+      cp16((uint32_t)__cvta_generic_to_shared(svs + r * LD + dc), vbase + tok * a.v_tok_stride + dc, ok);
+    }
+  }
+  if (n_blocks > 0) load_block(0, 0);
+  cp_commit();
+  if (n_blocks > 1) load_block(1, 1);
+  cp_commit();
+
   const int rq[2] = {q0 + warp * 16 + g, q0 + warp * 16 + g + 8};
   int segq[2];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) segq[i] = (rq[i] < T) ? a.seg[(long long)b * T + rq[i]] : 0;
+  for (int i = 0; i < 2; ++i) segq[i] = (rq[i] < T) ? a.seg[tok0 + rq[i]] : 0;
 
-  // Q fragments straight from global memory
+  cp_wait<1>();
+  __syncthreads();
+
   uint32_t qf[KSTEPS][4];
 #pragma unroll
-  for (int ks = 0; ks < KSTEPS; ++ks) {
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const bf16* qp = a.q + ((long long)b * T + rq[i]) * a.q_tok_stride + (long long)h * a.q_head_stride + ks * 16 + 2 * t4;
-      const bool ok = rq[i] < T;
-      qf[ks][i] = ok ? *reinterpret_cast<const uint32_t*>(qp) : 0u;
-      qf[ks][i + 2] = ok ? *reinterpret_cast<const uint32_t*>(qp + 8) : 0u;
-    }
-  }
+  for (int ks = 0; ks < KSTEPS; ++ks)
+    ldsm_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3],
+            (uint32_t)__cvta_generic_to_shared(sq + (warp * 16 + (lane & 15)) * LD + ks * 16 + ((lane >> 4) << 3)));
 
   float o[DT][4];
 #pragma unroll
   for (int j = 0; j < DT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-  const int n_hist = a.hist_len < T ? a.hist_len : T;
-  for (int k0 = 0; k0 < n_hist; k0 += KB) {
-    __syncthreads();
-    // stage K and V rows k0..k0+KB of this (batch, kv head): 16-byte chunks
-    for (int c = threadIdx.x; c < KB * (DH / 8); c += ATT_THREADS) {
-      const int kr = c / (DH / 8), dc = (c % (DH / 8)) * 8;
-      const int key = k0 + kr;
-      uint4 uk = make_uint4(0, 0, 0, 0), uv = make_uint4(0, 0, 0, 0);
-      if (key < n_hist) {
-        uk = *reinterpret_cast<const uint4*>(a.k + ((long long)b * T + key) * a.k_tok_stride + (long long)hk * a.k_head_stride + dc);
-        uv = *reinterpret_cast<const uint4*>(a.v + ((long long)b * T + key) * a.v_tok_stride + (long long)hk * a.v_head_stride + dc);
-      }
-      *reinterpret_cast<uint4*>(&sk[kr * LD + dc]) = uk;
-      *reinterpret_cast<uint4*>(&sv[kr * LD + dc]) = uv;
+  for (int blk = 0; blk < n_blocks; ++blk) {
+    const int buf = blk & 1;
+    if (blk > 0) {
+      if (blk + 1 < n_blocks) cp_wait<1>(); else cp_wait<0>();
+      __syncthreads();
     }
-    if (threadIdx.x < KB) {
-      const int key = k0 + threadIdx.x;
-      skey_ok[threadIdx.x] = (key < n_hist) && (a.seg[(long long)b * T + key] == 1);
-    }
-    __syncthreads();
+    const bf16* sk = skv + (size_t)(buf * 2 + 0) * KB * LD;
+    const bf16* sv = skv + (size_t)(buf * 2 + 1) * KB * LD;
+    const int* kok = skey_ok + buf * KB;
 
-    // S = Q K^T for 64 keys: 8 n-tiles of 8 keys
+    // S = Q K^T for 64 keys: 8 n-tiles of 8 keys, two per ldmatrix.x4
     float s[KB / 8][4];
 #pragma unroll
-    for (int j = 0; j < KB / 8; ++j) {
-      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    for (int j = 0; j < KB / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+    for (int j = 0; j < KB / 8; j += 2) {
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks) {
-        const bf16* kp = &sk[(j * 8 + g) * LD + ks * 16 + 2 * t4];
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kp);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kp + 8);
+        uint32_t b0, b1, b2, b3;
+        // lanes 0-7: keys j*8.., d ks*16; 8-15: same keys, d +8; 16-23: keys (j+1)*8.., d ks*16; 24-31: d +8
+        const int kr = j * 8 + (lane & 7) + ((lane >> 4) << 3);
+        const int kc = ks * 16 + (((lane >> 3) & 1) << 3);
+        ldsm_x4(b0, b1, b2, b3, (uint32_t)__cvta_generic_to_shared(sk + kr * LD + kc));
         mma_bf16_16816(s[j], qf[ks], b0, b1);
+        mma_bf16_16816(s[j + 1], qf[ks], b2, b3);
       }
     }
     // scale, cap, mask, block max
     float bm[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int j = 0; j < KB / 8; ++j) {
+      const int2 okp = *reinterpret_cast<const int2*>(&kok[j * 8 + 2 * t4]);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int kc = j * 8 + 2 * t4 + (e & 1);
         const int ri = e >> 1;
-        float v = cap_logit(s[j][e] * a.sm_scale, a.cap, a.cap_method);
-        const bool ok = skey_ok[kc] && segq[ri] != 0;
+        float v = scaled_logit(s[j][e], a.sm_scale, a.cap, a.cap_method);
+        const bool ok = ((e & 1) ? okp.y : okp.x) && segq[ri] != 0;
         v = ok ? v : -INFINITY;
         s[j][e] = v;
         bm[ri] = fmaxf(bm[ri], v);
       }
     }
+    float alpha[2], mn[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       bm[i] = fmaxf(bm[i], __shfl_xor_sync(0xffffffffu, bm[i], 1));
       bm[i] = fmaxf(bm[i], __shfl_xor_sync(0xffffffffu, bm[i], 2));
-    }
-    float alpha[2], mn[2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
       mn[i] = fmaxf(m[i], bm[i]);
-      alpha[i] = (mn[i] == -INFINITY) ? 1.f : exp2f((m[i] - mn[i]) * LOG2E);
+      alpha[i] = (mn[i] == -INFINITY) ? 1.f : ex2(m[i] - mn[i]);
       m[i] = mn[i];
     }
-    // P = exp(S - m); row sums in fp32 of the unrounded p; P rounded to bf16 for P V
+    // P = 2^(S - m); row sums of the unrounded p in fp32; P rounded to bf16 for P V
     uint32_t pf[KB / 16][4];
     float ls[2] = {0.f, 0.f};
 #pragma unroll
@@ -143,7 +195,7 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int ri = e >> 1;
-        p[e] = (s[j][e] == -INFINITY) ? 0.f : exp2f((s[j][e] - mn[ri]) * LOG2E);
+        p[e] = (s[j][e] == -INFINITY) ? 0.f : ex2(s[j][e] - mn[ri]);
         ls[ri] += p[e];
       }
       pf[j >> 1][(j & 1) * 2 + 0] = pack_bf2(p[0], p[1]);
@@ -163,61 +215,89 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
 #pragma unroll
       for (int jd = 0; jd < DT; jd += 2) {
         uint32_t b0, b1, b2, b3;
-        const int vr = kk * 16 + (lane & 15);
-        const int vc = jd * 8 + ((lane >> 4) << 3);
-        ldmatrix_x4_trans(b0, b1, b2, b3, (uint32_t)__cvta_generic_to_shared(&sv[vr * LD + vc]));
+        ldsm_x4_trans(b0, b1, b2, b3,
+                      (uint32_t)__cvta_generic_to_shared(sv + (kk * 16 + (lane & 15)) * LD + jd * 8 + ((lane >> 4) << 3)));
         mma_bf16_16816(o[jd], pf[kk], b0, b1);
         mma_bf16_16816(o[jd + 1], pf[kk], b2, b3);
       }
     }
-  }
-
-  // self key of candidate rows: one more online-softmax step with a per-row dot product
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const bool is_cand = segq[i] == -1;  // warp-uniform per quad only, so every lane runs the shuffles
-    float dot = 0.f;
-    const long long tok = (long long)b * T + (rq[i] < T ? rq[i] : 0);
-    const bf16* kp = a.k + tok * a.k_tok_stride + (long long)hk * a.k_head_stride;
-    if (is_cand) {
-#pragma unroll
-      for (int ks = 0; ks < KSTEPS; ++ks) {
-        const float2 qa = unpack_bf2(qf[ks][i]), qb = unpack_bf2(qf[ks][i + 2]);
-        const float2 ka = unpack_bf2(*reinterpret_cast<const uint32_t*>(kp + ks * 16 + 2 * t4));
-        const float2 kb = unpack_bf2(*reinterpret_cast<const uint32_t*>(kp + ks * 16 + 2 * t4 + 8));
-        dot += qa.x * ka.x + qa.y * ka.y + qb.x * kb.x + qb.y * kb.y;
-      }
-    }
-    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-    if (is_cand) {
-      const float sv_ = cap_logit(dot * a.sm_scale, a.cap, a.cap_method);
-      const float mn = fmaxf(m[i], sv_);
-      const float alpha = (m[i] == -INFINITY) ? 0.f : exp2f((m[i] - mn) * LOG2E);
-      const float p = exp2f((sv_ - mn) * LOG2E);
-      const float pr = round_bf(p);
-      l[i] = l[i] * alpha + p;
-      m[i] = mn;
-      const bf16* vp = a.v + tok * a.v_tok_stride + (long long)hk * a.v_head_stride;
-#pragma unroll
-      for (int j = 0; j < DT; ++j) {
-        const float2 vv = unpack_bf2(*reinterpret_cast<const uint32_t*>(vp + j * 8 + 2 * t4));
-        o[j][2 * i + 0] = o[j][2 * i + 0] * alpha + pr * vv.x;
-        o[j][2 * i + 1] = o[j][2 * i + 1] * alpha + pr * vv.y;
-      }
+    // refill this buffer with block blk+2
+    if (blk + 2 < n_blocks) {
+      __syncthreads();
+      load_block(blk + 2, buf);
+      cp_commit();
     }
   }
 
-  // normalise and store (rows with no allowed key: l == 0 -> zeros)
+  // ---- self key of candidate rows: one more online-softmax step with a per-row dot product ------------
+  if (has_cand) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const bool is_cand = segq[i] == -1;
+      const int lr = warp * 16 + g + 8 * i;  // row inside the tile
+      float dot = 0.f;
+      if (is_cand) {
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+          const float2 qa = unpack_bf2(qf[ks][i]), qb = unpack_bf2(qf[ks][i + 2]);
+          const float2 ka = unpack_bf2(*reinterpret_cast<const uint32_t*>(sks + lr * LD + ks * 16 + 2 * t4));
+          const float2 kb = unpack_bf2(*reinterpret_cast<const uint32_t*>(sks + lr * LD + ks * 16 + 2 * t4 + 8));
+          dot += qa.x * ka.x + qa.y * ka.y + qb.x * kb.x + qb.y * kb.y;
+        }
+      }
+      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+      if (is_cand) {
+        const float sv_ = scaled_logit(dot, a.sm_scale, a.cap, a.cap_method);
+        const float mn = fmaxf(m[i], sv_);
+        const float alpha = (m[i] == -INFINITY) ? 0.f : ex2(m[i] - mn);
+        const float p = ex2(sv_ - mn);
+        const float pr = round_bf(p);
+        l[i] = l[i] * alpha + p;
+        m[i] = mn;
+#pragma unroll
+        for (int j = 0; j < DT; ++j) {
+          const float2 vv = unpack_bf2(*reinterpret_cast<const uint32_t*>(svs + lr * LD + j * 8 + 2 * t4));
+          o[j][2 * i + 0] = o[j][2 * i + 0] * alpha + pr * vv.x;
+          o[j][2 * i + 1] = o[j][2 * i + 1] * alpha + pr * vv.y;
+        }
+      }
+    }
+  }
+
+  // ---- normalise, stage the warp's 16 x DH output rows in the (now free) Q tile, store 16-byte chunks --
+  // each warp only ever touched its own 16 rows of sq after the first barrier, so a warp-level sync suffices
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    if (rq[i] >= T) continue;
-    const float inv = (l[i] == 0.f) ? 0.f : 1.0f / l[i];
-    bf16* op = a.out + (((long long)b * T + rq[i]) * a.Hq + h) * DH;
+    const float inv = (l[i] == 0.f) ? 0.f : 1.0f / l[i];   // rows with no allowed key -> zeros
+    bf16* orow = sq + (warp * 16 + g + 8 * i) * LD;
 #pragma unroll
     for (int j = 0; j < DT; ++j)
-      *reinterpret_cast<uint32_t*>(op + j * 8 + 2 * t4) = pack_bf2(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
+      *reinterpret_cast<uint32_t*>(orow + j * 8 + 2 * t4) = pack_bf2(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
   }
+  __syncwarp();
+  for (int c = lane; c < 16 * CH; c += 32) {
+    const int r = c / CH, dc = (c % CH) * 8;
+    const int row = q0 + warp * 16 + r;
+    if (row < T)
+      *reinterpret_cast<uint4*>(a.out + ((tok0 + row) * a.Hq + h) * DH + dc) =
+          *reinterpret_cast<const uint4*>(sq + (warp * 16 + r) * LD + dc);
+  }
+}
+
+template <int DH>
+phx_status launch_dh(const AttnArgs& a, cudaStream_t stream, std::string& err) {
+  constexpr int LD = DH + 8;
+  const size_t smem = (size_t)(3 * QROWS + 4 * KB) * LD * 2 + 2 * KB * sizeof(int);
+  static bool attr_set = false;
+  if (!attr_set) {
+    PHX_CUDA_TRY(cudaFuncSetAttribute(ranker_attention_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), err);
+    attr_set = true;
+  }
+  dim3 grid((a.T + QROWS - 1) / QROWS, a.Hq, a.B);
+  ranker_attention_kernel<DH><<<grid, ATT_THREADS, smem, stream>>>(a);
+  PHX_CUDA_TRY(cudaGetLastError(), err);
+  return PHX_OK;
 }
 
 }  // namespace
@@ -226,15 +306,12 @@ phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::
   if (a.Hq % a.Hkv != 0) { err = "attention: Hq must be a multiple of Hkv"; return PHX_E_ARG; }
   if (a.B == 0 || a.T == 0) return PHX_OK;
   if (a.B > 65535 || a.Hq > 65535) { err = "attention: batch or head count too large for one launch"; return PHX_E_CAPACITY; }
-  dim3 grid((a.T + QROWS - 1) / QROWS, a.Hq, a.B);
   switch (a.dh) {
-    case 32: ranker_attention_kernel<32><<<grid, ATT_THREADS, 0, stream>>>(a); break;
-    case 64: ranker_attention_kernel<64><<<grid, ATT_THREADS, 0, stream>>>(a); break;
-    case 128: ranker_attention_kernel<128><<<grid, ATT_THREADS, 0, stream>>>(a); break;
+    case 32: return launch_dh<32>(a, stream, err);
+    case 64: return launch_dh<64>(a, stream, err);
+    case 128: return launch_dh<128>(a, stream, err);
     default: err = "attention: head dim must be 32, 64 or 128"; return PHX_E_ARG;
   }
-  PHX_CUDA_TRY(cudaGetLastError(), err);
-  return PHX_OK;
 }
 
 }  // namespace phx
