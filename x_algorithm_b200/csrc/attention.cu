@@ -57,7 +57,8 @@ __device__ __forceinline__ float scaled_logit(float s, float sm_scale, float cap
   return v * LOG2E;
 }
 
-template <int DH>
+// CAP = false: logits stay raw accumulators and the scale sm_scale * log2(e) is folded into the exponent's FMA
+template <int DH, bool CAP>
 __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs a) {
   constexpr int LD = DH + 8;          // padded row (elements): conflict-free ldmatrix
   constexpr int KSTEPS = DH / 16;     // k-steps of Q K^T
@@ -69,6 +70,8 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
   bf16* svs = sks + QROWS * LD;                    // [QROWS][LD]  V rows of the tile's own tokens
   bf16* skv = svs + QROWS * LD;                    // [2][2][KB][LD]  key-block ring: (buffer, K|V)
   int* skey_ok = reinterpret_cast<int*>(skv + 4 * KB * LD);  // [2][KB]
+  int* sall_ok = skey_ok + 2 * KB;                           // [2][2] per buffer and 32-key half: all keys valid history
+  const float csc = CAP ? 1.0f : a.sm_scale * 1.4426950408889634f;
 
   const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * QROWS;
   const int hk = h / (a.Hq / a.Hkv);
@@ -94,9 +97,12 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
       cp16((uint32_t)__cvta_generic_to_shared(dk + kr * LD + dc), kbase + tok * a.k_tok_stride + dc, ok);
       cp16((uint32_t)__cvta_generic_to_shared(dv + kr * LD + dc), vbase + tok * a.v_tok_stride + dc, ok);
     }
-    if (threadIdx.x < KB) {
+    if (threadIdx.x < KB) {  // warps 0 and 1
       const int key = blk * KB + threadIdx.x;
-      skey_ok[buf * KB + threadIdx.x] = (key < n_hist) && (a.seg[tok0 + key] == 1);
+      const int ok = (key < n_hist) && (a.seg[tok0 + key] == 1);
+      skey_ok[buf * KB + threadIdx.x] = ok;
+      const int all32 = __all_sync(0xffffffffu, ok);
+      if ((threadIdx.x & 31) == 0) sall_ok[buf * 2 + (threadIdx.x >> 5)] = all32;
     }
   };
 
@@ -133,7 +139,7 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
   float o[DT][4];
 #pragma unroll
   for (int j = 0; j < DT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float m[2] = {-INFINITY, -INFINITY}, mprev[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
   for (int blk = 0; blk < n_blocks; ++blk) {
     const int buf = blk & 1;
@@ -162,29 +168,37 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
         mma_bf16_16816(s[j + 1], qf[ks], b2, b3);
       }
     }
-    // scale, cap, mask, block max
+    // (cap,) key mask only where the block holds invalid keys, block max.  Padded query rows are not masked
+    // here: their output is forced to zero at the end.
+    if (CAP) {
+#pragma unroll
+      for (int j = 0; j < KB / 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[j][e] = scaled_logit(s[j][e], a.sm_scale, a.cap, a.cap_method);
+    }
+    if (!(sall_ok[buf * 2] & sall_ok[buf * 2 + 1])) {
+#pragma unroll
+      for (int j = 0; j < KB / 8; ++j) {
+        const int2 okp = *reinterpret_cast<const int2*>(&kok[j * 8 + 2 * t4]);
+        if (!okp.x) { s[j][0] = -INFINITY; s[j][2] = -INFINITY; }
+        if (!okp.y) { s[j][1] = -INFINITY; s[j][3] = -INFINITY; }
+      }
+    }
     float bm[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int j = 0; j < KB / 8; ++j) {
-      const int2 okp = *reinterpret_cast<const int2*>(&kok[j * 8 + 2 * t4]);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int ri = e >> 1;
-        float v = scaled_logit(s[j][e], a.sm_scale, a.cap, a.cap_method);
-        const bool ok = ((e & 1) ? okp.y : okp.x) && segq[ri] != 0;
-        v = ok ? v : -INFINITY;
-        s[j][e] = v;
-        bm[ri] = fmaxf(bm[ri], v);
-      }
+      bm[0] = fmaxf(bm[0], fmaxf(s[j][0], s[j][1]));
+      bm[1] = fmaxf(bm[1], fmaxf(s[j][2], s[j][3]));
     }
     float alpha[2], mn[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       bm[i] = fmaxf(bm[i], __shfl_xor_sync(0xffffffffu, bm[i], 1));
       bm[i] = fmaxf(bm[i], __shfl_xor_sync(0xffffffffu, bm[i], 2));
-      mn[i] = fmaxf(m[i], bm[i]);
-      alpha[i] = (mn[i] == -INFINITY) ? 1.f : ex2(m[i] - mn[i]);
-      m[i] = mn[i];
+      m[i] = fmaxf(m[i], bm[i] * csc);                 // running max, log2 domain
+      mn[i] = (m[i] == -INFINITY) ? 0.f : m[i];        // finite stand-in while nothing is allowed yet
+      alpha[i] = ex2(mprev[i] - mn[i]);                // -inf - finite -> 0
+      mprev[i] = m[i];
     }
     // P = 2^(S - m); row sums of the unrounded p in fp32; P rounded to bf16 for P V
     uint32_t pf[KB / 16][4];
@@ -195,7 +209,7 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int ri = e >> 1;
-        p[e] = (s[j][e] == -INFINITY) ? 0.f : ex2(s[j][e] - mn[ri]);
+        p[e] = ex2(fmaf(s[j][e], csc, -mn[ri]));      // masked logit: -inf -> 0
         ls[ri] += p[e];
       }
       pf[j >> 1][(j & 1) * 2 + 0] = pack_bf2(p[0], p[1]);
@@ -248,9 +262,9 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
       dot += __shfl_xor_sync(0xffffffffu, dot, 1);
       dot += __shfl_xor_sync(0xffffffffu, dot, 2);
       if (is_cand) {
-        const float sv_ = scaled_logit(dot, a.sm_scale, a.cap, a.cap_method);
+        const float sv_ = CAP ? scaled_logit(dot, a.sm_scale, a.cap, a.cap_method) : dot * csc;
         const float mn = fmaxf(m[i], sv_);
-        const float alpha = (m[i] == -INFINITY) ? 0.f : ex2(m[i] - mn);
+        const float alpha = ex2(m[i] - mn);             // no history yet: 2^-inf = 0
         const float p = ex2(sv_ - mn);
         const float pr = round_bf(p);
         l[i] = l[i] * alpha + p;
@@ -269,7 +283,7 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
   // each warp only ever touched its own 16 rows of sq after the first barrier, so a warp-level sync suffices
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    const float inv = (l[i] == 0.f) ? 0.f : 1.0f / l[i];   // rows with no allowed key -> zeros
+    const float inv = (l[i] == 0.f || segq[i] == 0) ? 0.f : 1.0f / l[i];   // padded rows, rows with no allowed key -> zeros
     bf16* orow = sq + (warp * 16 + g + 8 * i) * LD;
 #pragma unroll
     for (int j = 0; j < DT; ++j)
@@ -285,17 +299,17 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
   }
 }
 
-template <int DH>
+template <int DH, bool CAP>
 phx_status launch_dh(const AttnArgs& a, cudaStream_t stream, std::string& err) {
   constexpr int LD = DH + 8;
-  const size_t smem = (size_t)(3 * QROWS + 4 * KB) * LD * 2 + 2 * KB * sizeof(int);
+  const size_t smem = (size_t)(3 * QROWS + 4 * KB) * LD * 2 + (2 * KB + 4) * sizeof(int);
   static bool attr_set = false;
   if (!attr_set) {
-    PHX_CUDA_TRY(cudaFuncSetAttribute(ranker_attention_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), err);
+    PHX_CUDA_TRY(cudaFuncSetAttribute(ranker_attention_kernel<DH, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), err);
     attr_set = true;
   }
   dim3 grid((a.T + QROWS - 1) / QROWS, a.Hq, a.B);
-  ranker_attention_kernel<DH><<<grid, ATT_THREADS, smem, stream>>>(a);
+  ranker_attention_kernel<DH, CAP><<<grid, ATT_THREADS, smem, stream>>>(a);
   PHX_CUDA_TRY(cudaGetLastError(), err);
   return PHX_OK;
 }
@@ -306,10 +320,11 @@ phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::
   if (a.Hq % a.Hkv != 0) { err = "attention: Hq must be a multiple of Hkv"; return PHX_E_ARG; }
   if (a.B == 0 || a.T == 0) return PHX_OK;
   if (a.B > 65535 || a.Hq > 65535) { err = "attention: batch or head count too large for one launch"; return PHX_E_CAPACITY; }
+  const bool cap = a.cap_method != 0 && a.cap > 0.f;
   switch (a.dh) {
-    case 32: return launch_dh<32>(a, stream, err);
-    case 64: return launch_dh<64>(a, stream, err);
-    case 128: return launch_dh<128>(a, stream, err);
+    case 32: return cap ? launch_dh<32, true>(a, stream, err) : launch_dh<32, false>(a, stream, err);
+    case 64: return cap ? launch_dh<64, true>(a, stream, err) : launch_dh<64, false>(a, stream, err);
+    case 128: return cap ? launch_dh<128, true>(a, stream, err) : launch_dh<128, false>(a, stream, err);
     default: err = "attention: head dim must be 32, 64 or 128"; return PHX_E_ARG;
   }
 }
