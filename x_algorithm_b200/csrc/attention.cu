@@ -156,9 +156,9 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
 #pragma unroll
     for (int j = 0; j < KB / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
 #pragma unroll
-    for (int j = 0; j < KB / 8; j += 2) {
+    for (int ks = 0; ks < KSTEPS; ++ks) {       // k-step outermost: the 8 accumulator chains stay independent
 #pragma unroll
-      for (int ks = 0; ks < KSTEPS; ++ks) {
+      for (int j = 0; j < KB / 8; j += 2) {
         uint32_t b0, b1, b2, b3;
         // lanes 0-7: keys j*8.., d ks*16; 8-15: same keys, d +8; 16-23: keys (j+1)*8.., d ks*16; 24-31: d +8
         const int kr = j * 8 + (lane & 7) + ((lane >> 4) << 3);

@@ -82,8 +82,10 @@ struct GemmPlan {
   bool ready = false;
 };
 
+// narrow_tiles: use 128 x 128 tiles even when N is a multiple of 256 (more output slab buffers; meant for
+// residual GEMMs with a short K, which are bound by HBM rather than by the tensor pipe)
 phx_status gemm_plan_create(GemmPlan* plan, const bf16* A, const bf16* Wt, int64_t rows_max, int N, int K,
-                            std::string& err);
+                            bool narrow_tiles, std::string& err);
 // Launch on `stream`.  `R` is the residual (EPI_RESIDUAL) or null.  `err_flag` is a device int the
 // kernel sets to 1 when a bounded wait ran out.
 phx_status gemm_launch(GemmPlan& plan, bf16* C, const bf16* R, int64_t M, int epilogue, const GemmRope* rope,

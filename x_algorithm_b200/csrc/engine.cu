@@ -385,10 +385,10 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
     TRY(dev_alloc(e, &L.w_out_t, (size_t)e->D * e->HD));
     TRY(dev_alloc(e, &L.w_up_t, (size_t)e->F * e->D));
     TRY(dev_alloc(e, &L.w_down_t, (size_t)e->D * e->F));
-    TRY(gemm_plan_create(&L.p_qkv, e->hbuf, L.w_qkv_t, M, e->QW, e->D, e->err));
-    TRY(gemm_plan_create(&L.p_out, e->attn, L.w_out_t, M, e->D, e->HD, e->err));
-    TRY(gemm_plan_create(&L.p_up, e->hbuf, L.w_up_t, M, e->F, e->D, e->err));
-    TRY(gemm_plan_create(&L.p_down, e->ffn, L.w_down_t, M, e->D, e->F, e->err));
+    TRY(gemm_plan_create(&L.p_qkv, e->hbuf, L.w_qkv_t, M, e->QW, e->D, false, e->err));
+    TRY(gemm_plan_create(&L.p_out, e->attn, L.w_out_t, M, e->D, e->HD, e->HD <= 1024 && !cfg->primer_norm, e->err));
+    TRY(gemm_plan_create(&L.p_up, e->hbuf, L.w_up_t, M, e->F, e->D, false, e->err));
+    TRY(gemm_plan_create(&L.p_down, e->ffn, L.w_down_t, M, e->D, e->F, false, e->err));
   }
   if (e->V + e->NC > 0) TRY(dev_alloc(e, &e->unembed_t, (size_t)(e->V + e->NC) * e->D));
   // staging for the host entry point
@@ -725,7 +725,7 @@ phx_status phx_gemm_device(int32_t device, const uint16_t* A, const uint16_t* Wt
     cudaEventRecord(e1, 0);
   } else {
     GemmPlan plan;
-    s = gemm_plan_create(&plan, (const bf16*)A, (const bf16*)Wt, M, N, K, err);
+    s = gemm_plan_create(&plan, (const bf16*)A, (const bf16*)Wt, M, N, K, epilogue == 1 && K <= 1024, err);
     cudaEventRecord(e0, 0);
     if (s == PHX_OK && (epilogue < 0 || epilogue > 2)) { err = "phx_gemm_device: epilogue must be 0, 1 or 2"; s = PHX_E_ARG; }
     if (s == PHX_OK) s = gemm_launch(plan, (bf16*)C, (const bf16*)R, M, epilogue, nullptr, flag, prop.multiProcessorCount, 0, err);

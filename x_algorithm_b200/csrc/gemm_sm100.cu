@@ -23,17 +23,18 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
 template <int BN>
 struct Cfg {
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = 4;
+  static constexpr int NSLAB = (BN == 256) ? 2 : 6;   // output slab buffers (half per epilogue group)
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * (128 * 64 * 2) + BAR_BYTES + 1024;  // + 2 output slabs, +1024 alignment slack
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NSLAB * (128 * 64 * 2) + BAR_BYTES + 1024;  // + slabs, +1024 alignment slack
   static constexpr int TMEM_COLS = 2 * BN;                                    // two accumulators
 };
 
@@ -139,23 +140,24 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
 // ---- epilogue helpers -----------------------------------------------------------------------------
 constexpr int SLAB_COLS = 64;                 // one output slab = 128 rows x 64 bf16 columns = 128-byte rows
 constexpr int SLAB_BYTES = BM * SLAB_COLS * 2;
-constexpr int EPI_THREADS = 128;
+constexpr int EPI_THREADS = 256;
 
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-// barrier 1 over the 128 epilogue threads, AND-reducing a per-thread flag: every thread always arrives,
-// so a role that gave up on a bounded wait can never leave the others parked here
-__device__ __forceinline__ bool epi_barrier_and(bool ok) {
+// named barrier `id` over the 128 threads of one epilogue group, AND-reducing a per-thread flag: every thread
+// always arrives, so a thread that gave up on a bounded wait can never leave the others parked here
+__device__ __forceinline__ bool epi_barrier_and(bool ok, int id) {
   uint32_t out;
   asm volatile(
-      "{\n .reg .pred p, q;\n setp.ne.u32 q, %1, 0;\n bar.red.and.pred p, 1, 128, q;\n selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(out) : "r"((uint32_t)ok) : "memory");
+      "{\n .reg .pred p, q;\n setp.ne.u32 q, %1, 0;\n bar.red.and.pred p, %2, 128, q;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(out) : "r"((uint32_t)ok), "r"(id) : "memory");
   return out != 0;
 }
 __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
@@ -221,15 +223,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   using cfg = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
-  const uint32_t slab_base = smem_base + cfg::STAGES * cfg::STAGE_BYTES;   // 2 output slabs
-  const uint32_t bars = slab_base + 2 * SLAB_BYTES;
-  // barrier slots (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], res[2]; then the TMEM slot
+  const uint32_t slab_base = smem_base + cfg::STAGES * cfg::STAGE_BYTES;   // output slab buffers
+  const uint32_t bars = slab_base + cfg::NSLAB * SLAB_BYTES;
+  // barrier slots (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], res[NSLAB]; then the TMEM slot
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (cfg::STAGES + s); };
   auto tfull_bar = [&](int a) { return bars + 8u * (2 * cfg::STAGES + a); };
   auto tempty_bar = [&](int a) { return bars + 8u * (2 * cfg::STAGES + 2 + a); };
   auto res_bar = [&](int b) { return bars + 8u * (2 * cfg::STAGES + 4 + b); };
-  const uint32_t tmem_slot = bars + 8u * (2 * cfg::STAGES + 6);
+  const uint32_t tmem_slot = bars + 8u * (2 * cfg::STAGES + 4 + cfg::NSLAB);
   uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -241,7 +243,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < cfg::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), EPI_THREADS); mbar_init(res_bar(a), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), EPI_THREADS); }
+    for (int a = 0; a < cfg::NSLAB; ++a) mbar_init(res_bar(a), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(tmem_slot, cfg::TMEM_COLS);
@@ -299,80 +302,114 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else {
-    // ---------------- epilogue (warps 2..5) ----------------
-    // Work item = one 64-column slab of a tile.  TMEM -> registers -> fused op -> swizzled shared-memory slab
-    // -> one TMA bulk store; the residual slab arrives by TMA into the same buffer one item ahead.
+    // ---------------- epilogue (warps 2..9: two groups of four warps) ----------------
+    // Work item = one 64-column slab of a tile; group gidx takes the items with q % 2 == gidx and owns NB
+    // slab buffers, an issuing thread and named barrier 1 + gidx.  Per item: TMEM -> registers -> fused op
+    // -> swizzled shared-memory slab -> one TMA bulk store.  The residual slab arrives by TMA into the same
+    // buffer (up to NB - 1 items ahead, at least one) and is updated in place.
     constexpr int SLABS = BN / SLAB_COLS;
+    constexpr int NB = cfg::NSLAB / 2;
     constexpr bool RES = (EPI == EPI_RESIDUAL);
-    const int quad = warp & 3;               // TMEM lane quadrant this warp may read
+    constexpr int DIST = NB - 1;                        // residual prefetch distance (items of this group)
+    const int ew = warp - 2;
+    const int gidx = ew >> 2;
+    const int quad = warp & 3;                          // TMEM lane quadrant this warp may read
     const int row_in_tile = quad * 32 + lane;
-    const bool issuer = (warp == 2 && lane == 0);
+    const bool issuer = ((ew & 3) == 0 && lane == 0);
     const long long my_tiles = (total_tiles > blockIdx.x) ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     const long long total_items = my_tiles * SLABS;
-    auto coords = [&](long long q, long long& m0, int& c0) {
+    const long long my_items = (total_items > gidx) ? (total_items - gidx + 1) / 2 : 0;
+    const uint32_t gslab = slab_base + gidx * NB * SLAB_BYTES;
+    auto coords = [&](long long i, long long& m0, int& c0) {   // i = item index inside this group
+      const long long q = 2 * i + gidx;
       const long long tile = blockIdx.x + (q / SLABS) * gridDim.x;
       m0 = (tile / n_tiles) * BM;
       c0 = (int)(tile % n_tiles) * BN + (int)(q % SLABS) * SLAB_COLS;
     };
-    if (RES && issuer && total_items > 0) {
-      long long m0; int c0; coords(0, m0, c0);
-      mbar_expect_tx(res_bar(0), SLAB_BYTES);
-      tma_load_2d(slab_base, &map_r, res_bar(0), c0, (int)m0);
+    auto issue_res = [&](long long i) {
+      long long m1; int c1; coords(i, m1, c1);
+      const int bi = (int)(i % NB);
+      mbar_expect_tx(res_bar(gidx * NB + bi), SLAB_BYTES);
+      tma_load_2d(gslab + bi * SLAB_BYTES, &map_r, res_bar(gidx * NB + bi), c1, (int)m1);
+    };
+    if (RES && issuer) {
+      for (int i = 0; i < DIST && i < my_items; ++i) issue_res(i);
     }
-    for (long long q = 0; q < total_items; ++q) {
+    for (long long i = 0; i < my_items; ++i) {
+      const long long q = 2 * i + gidx;
       const int s = (int)(q % SLABS);
       const uint32_t it = (uint32_t)(q / SLABS), acc = it & 1, acc_phase = (it >> 1) & 1;
-      const int buf = (int)(q & 1);
-      const uint32_t slab = slab_base + buf * SLAB_BYTES;
-      long long m0; int c0; coords(q, m0, c0);
-      if (RES && issuer) {
-        bulk_wait_read0();  // the store of item q-1 has drained the other buffer
-        if (q + 1 < total_items) {
-          long long m1; int c1; coords(q + 1, m1, c1);
-          mbar_expect_tx(res_bar(buf ^ 1), SLAB_BYTES);
-          tma_load_2d(slab_base + (buf ^ 1) * SLAB_BYTES, &map_r, res_bar(buf ^ 1), c1, (int)m1);
-        }
+      const int bi = (int)(i % NB);
+      const uint32_t slab = gslab + bi * SLAB_BYTES;
+      long long m0; int c0; coords(i, m0, c0);
+      const bool first_of_tile = (s < 2);               // this group's first slab of the tile
+      const bool last_of_tile = (s + 2 >= SLABS);       // ... and its last
+      if (RES && issuer && i + DIST < my_items) {
+        // the buffer of item i + DIST was last used by item i - 1: its store must have drained
+        bulk_wait_read<0>();
+        issue_res(i + DIST);
       }
       bool ok = true;
-      if (s == 0) ok = mbar_wait(tfull_bar(acc), acc_phase, verr);
-      if (RES && ok) ok = mbar_wait(res_bar(buf), (uint32_t)((q >> 1) & 1), verr);
+      if (first_of_tile) ok = mbar_wait(tfull_bar(acc), acc_phase, verr);
+      if (RES && ok) ok = mbar_wait(res_bar(gidx * NB + bi), (uint32_t)((i / NB) & 1), verr);
       ok = __all_sync(0xffffffffu, ok);
+      const uint32_t row_addr = slab + row_in_tile * 128;
+      const int sw = row_in_tile & 7;
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16) + s * SLAB_COLS;
+      if (!RES) {
+        // the store that last read this buffer (item i - NB of this group) must have drained before it is rewritten
+        if (issuer) bulk_wait_read<NB - 1>();
+        ok = epi_barrier_and(ok, 1 + gidx);
+      }
       if (ok) {
         tc_fence_after();
-        uint32_t r[64];
-        const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16) + s * SLAB_COLS;
-        tmem_ld32(taddr, r);
-        tmem_ld32(taddr + 32, r + 32);
-        if (s == SLABS - 1) { tc_fence_before(); mbar_arrive(tempty_bar(acc)); }  // accumulator drained
-        float v[64];
+        if (EPI == EPI_ROPE) {
+          uint32_t r[64];
+          tmem_ld32(taddr, r);
+          tmem_ld32(taddr + 32, r + 32);
+          if (last_of_tile) { tc_fence_before(); mbar_arrive(tempty_bar(acc)); }
+          float v[64];
 #pragma unroll
-        for (int i = 0; i < 64; ++i) v[i] = round_bf(__uint_as_float(r[i]));       // Linear output is bf16
-        if (EPI == EPI_GELU) {
-#pragma unroll
-          for (int i = 0; i < 64; ++i) v[i] = gelu_tanh_f(v[i]);
-        } else if (EPI == EPI_ROPE) {
+          for (int k = 0; k < 64; ++k) v[k] = round_bf(__uint_as_float(r[k]));   // Linear output is bf16
           rope_slab(v, rope, c0, m0 + row_in_tile);
-        }
-        const uint32_t row_addr = slab + row_in_tile * 128;
-        const int sw = row_in_tile & 7;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint32_t addr = row_addr + ((uint32_t)(c ^ sw) << 4);
-          if (RES) {
-            const uint4 rr = ld_shared_v4(addr);
-            const float2 a = unpack_bf2(rr.x), b = unpack_bf2(rr.y), cc = unpack_bf2(rr.z), d = unpack_bf2(rr.w);
-            v[c * 8 + 0] += a.x; v[c * 8 + 1] += a.y; v[c * 8 + 2] += b.x; v[c * 8 + 3] += b.y;
-            v[c * 8 + 4] += cc.x; v[c * 8 + 5] += cc.y; v[c * 8 + 6] += d.x; v[c * 8 + 7] += d.y;
+          for (int c = 0; c < 8; ++c) {
+            uint4 o;
+            o.x = pack_bf2(v[c * 8 + 0], v[c * 8 + 1]); o.y = pack_bf2(v[c * 8 + 2], v[c * 8 + 3]);
+            o.z = pack_bf2(v[c * 8 + 4], v[c * 8 + 5]); o.w = pack_bf2(v[c * 8 + 6], v[c * 8 + 7]);
+            st_shared_v4(row_addr + ((uint32_t)(c ^ sw) << 4), o);
           }
-          uint4 o;
-          o.x = pack_bf2(v[c * 8 + 0], v[c * 8 + 1]); o.y = pack_bf2(v[c * 8 + 2], v[c * 8 + 3]);
-          o.z = pack_bf2(v[c * 8 + 4], v[c * 8 + 5]); o.w = pack_bf2(v[c * 8 + 6], v[c * 8 + 7]);
-          st_shared_v4(addr, o);
+        } else {
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {              // two 32-column halves keep the register footprint low
+            uint32_t r[32];
+            tmem_ld32(taddr + hh * 32, r);
+            if (hh == 1 && last_of_tile) { tc_fence_before(); mbar_arrive(tempty_bar(acc)); }
+            float v[32];
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+              v[k] = round_bf(__uint_as_float(r[k]));                          // Linear output is bf16
+              if (EPI == EPI_GELU) v[k] = gelu_tanh_f(v[k]);
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const uint32_t addr = row_addr + ((uint32_t)((hh * 4 + c) ^ sw) << 4);
+              if (RES) {
+                const uint4 rr = ld_shared_v4(addr);
+                const float2 a = unpack_bf2(rr.x), b = unpack_bf2(rr.y), cc = unpack_bf2(rr.z), d = unpack_bf2(rr.w);
+                v[c * 8 + 0] += a.x; v[c * 8 + 1] += a.y; v[c * 8 + 2] += b.x; v[c * 8 + 3] += b.y;
+                v[c * 8 + 4] += cc.x; v[c * 8 + 5] += cc.y; v[c * 8 + 6] += d.x; v[c * 8 + 7] += d.y;
+              }
+              uint4 o;
+              o.x = pack_bf2(v[c * 8 + 0], v[c * 8 + 1]); o.y = pack_bf2(v[c * 8 + 2], v[c * 8 + 3]);
+              o.z = pack_bf2(v[c * 8 + 4], v[c * 8 + 5]); o.w = pack_bf2(v[c * 8 + 6], v[c * 8 + 7]);
+              st_shared_v4(addr, o);
+            }
+          }
         }
         fence_async_smem();
       }
-      if (!RES && issuer) bulk_wait_read0();  // store q-1 has drained the buffer item q+1 will fill
-      if (!epi_barrier_and(ok)) break;         // uniform over the 128 epilogue threads
+      if (!epi_barrier_and(ok, 1 + gidx)) break;        // uniform over the group's 128 threads
       if (issuer && c0 < N) {
         tma_store_2d(&map_c, slab, c0, (int)m0);
         bulk_commit();
@@ -481,13 +518,14 @@ __global__ void gemm_simt_kernel(const bf16* __restrict__ A, const bf16* __restr
 }  // namespace
 
 phx_status gemm_plan_create(GemmPlan* plan, const bf16* A, const bf16* Wt, int64_t rows_max, int N, int K,
-                            std::string& err) {
+                            bool narrow_tiles, std::string& err) {
   if (N % 8 != 0 || K % 8 != 0 || N <= 0 || K <= 0 || rows_max <= 0) {
     err = "gemm: N and K must be positive multiples of 8";
     return PHX_E_ARG;
   }
   plan->A = A; plan->Wt = Wt; plan->rows_max = rows_max; plan->N = N; plan->K = K;
-  plan->BN = (N % 256 == 0) ? 256 : 128;
+  // 128-wide tiles leave room for six output slabs: deep residual prefetch for the HBM-bound short-K GEMMs
+  plan->BN = (N % 256 == 0 && !narrow_tiles) ? 256 : 128;
   phx_status s = make_map(&plan->map_a, A, rows_max, K, BM, err);
   if (s != PHX_OK) return s;
   s = make_map(&plan->map_b, Wt, N, K, plan->BN, err);

@@ -56,14 +56,18 @@ __global__ void __launch_bounds__(256) heads_kernel(HeadsArgs a) {
         }
       }
     }
+    // butterfly: 31 shuffles leave the total of output j on lane j (instead of 5 shuffles per output)
 #pragma unroll
-    for (int j = 0; j < MAX_OUT; ++j)
-      if (j < NO) acc[j] = warp_sum(acc[j]);
-    // every lane now holds all outputs; lane j finishes output j
-    float mine = 0.f;
+    for (int step = 16; step >= 1; step >>= 1) {
+      const bool upper = (lane & step) != 0;
 #pragma unroll
-    for (int j = 0; j < MAX_OUT; ++j)
-      if (j == lane) mine = acc[j];
+      for (int i = 0; i < step; ++i) {
+        const float send = upper ? acc[i] : acc[i + step];
+        const float keep = upper ? acc[i + step] : acc[i];
+        acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, step);
+      }
+    }
+    const float mine = acc[0];
     float value = 0.f;  // probability (f32 log-prob kept separately) or continuous prediction
     float logp = 0.f;
     if (lane < a.V) {
