@@ -228,10 +228,14 @@ def test_user_tower_and_topk_vs_oracle(torch):
     eng.close()
 
 
-def test_topk_large_shard_uses_pivot_path(torch):
-    """A shard larger than the survivor capacity goes through the sampled pivot; result still exact."""
+@pytest.mark.parametrize("impl,dim", [("tc", 64), ("tc", 128), ("simt", 64), ("simt", 96)])
+def test_topk_large_shard_uses_pivot_path(torch, monkeypatch, impl, dim):
+    """A shard larger than the survivor capacity goes through the sampled pivot; result still exact.
+    Both scan kernels: tcgen05 (dim 64 / 128) and the mma.sync one (any dim % 16 == 0)."""
     from x_algorithm_b200.retrieval import CorpusShard
-    N, k, B, dim = 400_000, 64, 20, 64
+    if impl == "simt":
+        monkeypatch.setenv("PHX_TOPK", "simt")
+    N, k, B = 400_000, 64, 20
     sh = CorpusShard(N, dim, row_offset=1000, max_queries=B, max_k=k)
     sh.fill_synthetic(5)
     rng = np.random.default_rng(0)

@@ -24,7 +24,8 @@ def _sources():
 
 def _digest(path: str) -> str:
     h = hashlib.sha256()
-    for dep in [path, os.path.join(CSRC, "common.cuh"), os.path.join(HERE, "..", "include", "phoenix_b200.h")]:
+    for dep in [path, os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "sm100_ptx.cuh"),
+                os.path.join(HERE, "..", "include", "phoenix_b200.h")]:
         with open(dep, "rb") as f:
             h.update(f.read())
     h.update(" ".join(FLAGS).encode())

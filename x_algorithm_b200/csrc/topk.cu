@@ -15,11 +15,14 @@
 // whenever the survivor list holds at least k and at most `cap` rows; otherwise the call reports
 // PHX_E_CAPACITY instead of returning a wrong answer.
 #include <math.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include <mutex>
 #include <vector>
 
 #include "common.cuh"
+#include "topk_scan.cuh"
 
 namespace phx {
 namespace {
@@ -331,6 +334,9 @@ struct phx_corpus {
   size_t merge_keys_elems = 0;
   int* counts = nullptr;
   int* status = nullptr;
+  int* err_flag = nullptr;       // raised by a bounded device-side wait that ran out
+  bool use_tc = false;           // tcgen05 scan (dim 64 / 128), else the mma.sync scan
+  CUtensorMap map_corpus, map_users;
   cudaStream_t stream = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   std::string err;
@@ -393,7 +399,18 @@ phx_status phx_corpus_create(int32_t device, int64_t rows, int32_t dim, int64_t 
   CU(cudaMalloc(&c->counts, 256 * 4));
   CU(cudaMalloc(&c->status, 4));
   CU(cudaMemset(c->status, 0, 4));
+  CU(cudaMalloc(&c->err_flag, 4));
+  CU(cudaMemset(c->err_flag, 0, 4));
 #undef CU
+  {
+    const char* force = getenv("PHX_TOPK");
+    c->use_tc = tc_scan_supported(dim) && prop.major == 10 && !(force && strcmp(force, "simt") == 0);
+    if (c->use_tc) {
+      std::string err;
+      phx_status s = tc_scan_make_maps(&c->map_corpus, &c->map_users, c->data, rows, dim, c->users_bf, err);
+      if (s) { set_global_error(err); phx_corpus_destroy(c); return s; }
+    }
+  }
   *out = c;
   return PHX_OK;
 }
@@ -403,7 +420,7 @@ void phx_corpus_destroy(phx_corpus* c) {
   cudaSetDevice(c->device);
   if (c->stream) cudaStreamSynchronize(c->stream);
   auto fr = [](void* p) { if (p) cudaFree(p); };
-  fr(c->data); fr(c->users_bf); fr(c->gmax); fr(c->pivot); fr(c->surv); fr(c->merge_keys); fr(c->counts); fr(c->status);
+  fr(c->data); fr(c->users_bf); fr(c->gmax); fr(c->pivot); fr(c->surv); fr(c->merge_keys); fr(c->counts); fr(c->status); fr(c->err_flag);
   if (c->ev0) cudaEventDestroy(c->ev0);
   if (c->ev1) cudaEventDestroy(c->ev1);
   if (c->stream) cudaStreamDestroy(c->stream);
@@ -434,16 +451,22 @@ phx_status phx_corpus_topk_device(phx_corpus* c, const float* users_dev, int32_t
   if (B <= 0 || B > c->max_queries || k <= 0 || k > c->max_k) { c->err = "topk: B or k exceeds what the corpus was created for"; return PHX_E_CAPACITY; }
   if (k > c->rows) { c->err = "topk: k exceeds the shard's rows"; return PHX_E_ARG; }
   cudaSetDevice(c->device);
-  const int Bpad = B <= 16 ? 16 : (B <= 64 ? 64 : 256);
+  const int Bpad = c->use_tc ? 256 : (B <= 16 ? 16 : (B <= 64 ? 64 : 256));
   PHX_CUDA_TRY(cudaEventRecord(c->ev0, c->stream), c->err);
   users_to_bf16_kernel<<<(Bpad * c->dim + 255) / 256, 256, 0, c->stream>>>(users_dev, c->users_bf, B, Bpad, c->dim);
   PHX_CUDA_TRY(cudaGetLastError(), c->err);
   PHX_CUDA_TRY(cudaMemsetAsync(c->counts, 0, 256 * 4, c->stream), c->err);
 
+  // geometry of the scan in use: tile rows, rows per maximum group
+  const int tile_rows = c->use_tc ? 128 : TILE_ROWS;
+  const double group_rows = c->use_tc ? 32.0 : 16.0;
   ScanArgs a;
   a.corpus = c->data; a.users = c->users_bf; a.rows = c->rows; a.row_offset = c->row_offset; a.dim = c->dim; a.B = B; a.Bpad = Bpad;
   a.stride = 1; a.gmax = c->gmax; a.n_groups = 0; a.pivot = c->pivot; a.surv = c->surv; a.counts = c->counts; a.cap = c->cap;
-  const long long n_tiles = (c->rows + TILE_ROWS - 1) / TILE_ROWS;
+  TcScanArgs ta;
+  ta.rows = c->rows; ta.row_offset = c->row_offset; ta.dim = c->dim; ta.B = B; ta.stride = 1; ta.gmax = c->gmax; ta.n_groups = 0;
+  ta.pivot = c->pivot; ta.surv = c->surv; ta.counts = c->counts; ta.cap = c->cap;
+  const long long n_tiles = (c->rows + tile_rows - 1) / tile_rows;
   int j = 0;
   if (c->rows > c->cap) {
     // sample every stride-th tile so that about 48 of the wanted ~3k rows fall into the sample
@@ -452,22 +475,24 @@ phx_status phx_corpus_topk_device(phx_corpus* c, const float* users_dev, int32_t
     if (stride < 1) stride = 1;
     long long sampled_tiles = (n_tiles + stride - 1) / stride;
     while (sampled_tiles * 4 * (long long)B > c->gmax_elems) { stride *= 2; sampled_tiles = (n_tiles + stride - 1) / stride; }
-    a.stride = (int)stride;
-    a.n_groups = sampled_tiles * 4;
-    // per-row tail fraction f = want / rows; a 16-row group exceeds the level with 1 - (1-f)^16
+    a.stride = ta.stride = (int)stride;
+    a.n_groups = ta.n_groups = sampled_tiles * 4;
+    // per-row tail fraction f = want / rows; a group of g rows exceeds the level with 1 - (1-f)^g
     const double f = want / (double)c->rows;
-    const double qg = 1.0 - pow(1.0 - (f < 0.5 ? f : 0.5), 16.0);
+    const double qg = 1.0 - pow(1.0 - (f < 0.5 ? f : 0.5), group_rows);
     j = (int)ceil(qg * (double)a.n_groups);
     if (j < 1) j = 1;
-    int grid = (int)(sampled_tiles < c->num_sms * 2 ? sampled_tiles : c->num_sms * 2);
-    phx_status s = run_scan(c, a, 0, grid);
+    phx_status s;
+    if (c->use_tc) s = tc_scan_launch(c->map_corpus, c->map_users, ta, 0, c->num_sms, c->err_flag, c->stream, c->err);
+    else s = run_scan(c, a, 0, (int)(sampled_tiles < c->num_sms * 2 ? sampled_tiles : c->num_sms * 2));
     if (s) return s;
   }
   pivot_kernel<<<B, SEL_THREADS, 0, c->stream>>>(c->gmax, a.n_groups, j, c->pivot);
   PHX_CUDA_TRY(cudaGetLastError(), c->err);
   {
-    int grid = (int)(n_tiles < c->num_sms * 2 ? n_tiles : c->num_sms * 2);
-    phx_status s = run_scan(c, a, 1, grid);
+    phx_status s;
+    if (c->use_tc) s = tc_scan_launch(c->map_corpus, c->map_users, ta, 1, c->num_sms, c->err_flag, c->stream, c->err);
+    else s = run_scan(c, a, 1, (int)(n_tiles < c->num_sms * 2 ? n_tiles : c->num_sms * 2));
     if (s) return s;
   }
   const int kp2 = next_pow2(k);
@@ -565,7 +590,13 @@ phx_status phx_corpus_sync(phx_corpus* c) {
   if (!c) return PHX_E_ARG;
   cudaSetDevice(c->device);
   PHX_CUDA_TRY(cudaStreamSynchronize(c->stream), c->err);
-  int st = 0;
+  int st = 0, ef = 0;
+  PHX_CUDA_TRY(cudaMemcpy(&ef, c->err_flag, 4, cudaMemcpyDeviceToHost), c->err);
+  if (ef != 0) {
+    cudaMemset(c->err_flag, 0, 4);
+    c->err = "topk: a bounded device-side wait ran out (scan pipeline)";
+    return PHX_E_TIMEOUT;
+  }
   PHX_CUDA_TRY(cudaMemcpy(&st, c->status, 4, cudaMemcpyDeviceToHost), c->err);
   if (st != 0) {
     cudaMemset(c->status, 0, 4);

@@ -1,0 +1,221 @@
+// Corpus scan of the exhaustive top-k on Blackwell tensor cores (reference: users_bf16 @ posts^T,
+// phoenix/xrex/models/recsys_two_tower_model.py:2455-2456): the score tile of 128 corpus rows x 256 queries is
+// formed in TMEM and consumed there, so the only HBM traffic is the corpus itself, read once.
+//
+// Persistent kernel, one CTA per SM, 320 threads:
+//   warp 0      TMA producer: the query matrix once (stays in shared memory), then one 128 x dim corpus tile per
+//               stage (128-byte swizzle, 64-column boxes)
+//   warp 1      MMA issuer: tcgen05.mma M=128 (corpus rows) x N=256 (queries), K=16 steps, into one of two TMEM
+//               accumulators
+//   warps 2-9   consumers: each warp reads its 32-row lane quadrant and one half of the query columns with
+//               tcgen05.ld and either appends rows whose score reaches the query's threshold to the survivor list
+//               (collect pass) or reduces the 32-row maximum per query (sample pass)
+// All mbarrier waits are bounded; on expiry *err_flag is raised and the kernel unwinds.
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+#include "topk_scan.cuh"
+
+namespace phx {
+namespace {
+
+using namespace sm100;
+
+constexpr int TC_ROWS = 128;      // corpus rows per tile
+constexpr int TC_Q = 256;         // query columns (padded)
+constexpr int TC_THREADS = 320;
+constexpr int TC_STAGES = 4;
+
+__device__ __forceinline__ uint32_t ord32(float f) {
+  if (f == 0.f) f = 0.f;  // -0 -> +0
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float unord32(uint32_t o) {
+  const uint32_t u = (o & 0x80000000u) ? (o & 0x7FFFFFFFu) : ~o;
+  return __uint_as_float(u);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+scan_tc_kernel(const __grid_constant__ CUtensorMap map_corpus, const __grid_constant__ CUtensorMap map_users,
+               TcScanArgs a, int* err_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  const int kblk = a.dim / BK;                                   // 64-column k-blocks: 1 or 2
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t users_smem = smem_base;                         // kblk x [256 x 128 B]
+  const uint32_t users_bytes = (uint32_t)kblk * TC_Q * 128;
+  const uint32_t stage_bytes = (uint32_t)kblk * TC_ROWS * 128;
+  const uint32_t stage_base = users_smem + users_bytes;
+  const uint32_t thr_smem = stage_base + TC_STAGES * stage_bytes;  // [256] float thresholds
+  const uint32_t bars = thr_smem + TC_Q * 4;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (TC_STAGES + s); };
+  auto tfull_bar = [&](int x) { return bars + 8u * (2 * TC_STAGES + x); };
+  auto tempty_bar = [&](int x) { return bars + 8u * (2 * TC_STAGES + 2 + x); };
+  const uint32_t users_bar = bars + 8u * (2 * TC_STAGES + 4);
+  const uint32_t tmem_slot = bars + 8u * (2 * TC_STAGES + 5);
+  uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+  float* s_thr = reinterpret_cast<float*>(smem_raw + (thr_smem - smem_u32(smem_raw)));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* verr = err_flag;
+  // work list: MODE 1 every tile; MODE 0 tiles 0, stride, 2*stride, ...
+  const long long n_tiles = (a.rows + TC_ROWS - 1) / TC_ROWS;
+  const long long n_work = (MODE == 0) ? (n_tiles + a.stride - 1) / a.stride : n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TC_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int x = 0; x < 2; ++x) { mbar_init(tfull_bar(x), 1); mbar_init(tempty_bar(x), 256); }
+    mbar_init(users_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (MODE == 1) {
+    // collect when acc >= thr, with thr a little below the midpoint under the pivot: a superset of
+    // { bf16(acc) >= pivot }; the exact selection happens later on the rounded scores
+    for (int u = threadIdx.x; u < TC_Q; u += TC_THREADS) {
+      float t = INFINITY;
+      if (u < a.B) {
+        const float p = a.pivot[u];
+        t = (p == -INFINITY) ? -INFINITY : p - fabsf(p) * 0.00390625f - 1e-37f;
+      }
+      s_thr[u] = t;
+    }
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(users_bar, users_bytes);
+      for (int kb = 0; kb < kblk; ++kb) tma_load_2d(users_smem + kb * TC_Q * 128, &map_users, users_bar, kb * BK, 0);
+      int stage = 0; uint32_t phase = 0;
+      for (long long w = blockIdx.x; w < n_work; w += gridDim.x) {
+        const long long tile = (MODE == 0) ? w * a.stride : w;
+        if (!mbar_wait(empty_bar(stage), phase ^ 1, verr)) break;
+        const uint32_t dst = stage_base + stage * stage_bytes;
+        mbar_expect_tx(full_bar(stage), stage_bytes);
+        for (int kb = 0; kb < kblk; ++kb)
+          tma_load_2d(dst + kb * TC_ROWS * 128, &map_corpus, full_bar(stage), kb * BK, (int)(tile * TC_ROWS));
+        if (++stage == TC_STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(TC_ROWS, TC_Q);
+      bool ok = mbar_wait(users_bar, 0, verr);
+      int stage = 0; uint32_t phase = 0, it = 0;
+      for (long long w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) {
+        const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, verr)) break;
+        if (!mbar_wait(full_bar(stage), phase, verr)) break;
+        tc_fence_after();
+        const uint32_t src = stage_base + stage * stage_bytes;
+        for (int kb = 0; kb < kblk; ++kb) {
+          const uint64_t adesc = make_smem_desc(src + kb * TC_ROWS * 128);
+          const uint64_t bdesc = make_smem_desc(users_smem + kb * TC_Q * 128);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16(tmem_base + acc * TC_Q, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+        }
+        umma_commit(empty_bar(stage));
+        umma_commit(tfull_bar(acc));
+        if (++stage == TC_STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else {
+    const int ew = warp - 2;
+    const int half = ew >> 2;        // which 128 query columns
+    const int quad = warp & 3;       // TMEM lane quadrant
+    uint32_t it = 0;
+    for (long long w = blockIdx.x; w < n_work; w += gridDim.x, ++it) {
+      const long long tile = (MODE == 0) ? w * a.stride : w;
+      const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+      bool ok = mbar_wait(tfull_bar(acc), acc_phase, verr);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const long long row = tile * TC_ROWS + quad * 32 + lane;
+      const bool row_ok = row < a.rows;
+      const uint32_t taddr = tmem_base + acc * TC_Q + ((uint32_t)(quad * 32) << 16) + half * 128;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        const int u0 = half * 128 + c * 32;
+        if (MODE == 1) {
+#pragma unroll
+          for (int k4 = 0; k4 < 8; ++k4) {
+            const float4 t4 = *reinterpret_cast<const float4*>(&s_thr[u0 + k4 * 4]);
+            const float tt[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float v = __uint_as_float(r[k4 * 4 + e]);
+              if (v >= tt[e] && row_ok) {
+                const int u = u0 + k4 * 4 + e;
+                const int slot = atomicAdd(&a.counts[u], 1);
+                if (slot < a.cap)
+                  a.surv[(size_t)u * a.cap + slot] = ((unsigned long long)ord32(round_bf(v)) << 32) |
+                                                     (unsigned long long)(0xFFFFFFFFu - (uint32_t)(a.row_offset + row));
+              }
+            }
+          }
+        } else {
+          const long long grp = w * 4 + quad;
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            const uint32_t key = row_ok ? ord32(round_bf(__uint_as_float(r[k]))) : 0x007FFFFFu;  // ordered(-inf)
+            uint32_t mx;
+            asm volatile("redux.sync.max.u32 %0, %1, 0xffffffff;" : "=r"(mx) : "r"(key));
+            const int u = u0 + k;
+            if (lane == 0 && u < a.B) a.gmax[(size_t)u * a.n_groups + grp] = unord32(mx);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  if (*verr != 0) __nanosleep(1000000);  // error path: let in-flight bulk copies land before the CTA retires
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace
+
+bool tc_scan_supported(int dim) { return dim == 64 || dim == 128; }
+
+phx_status tc_scan_make_maps(CUtensorMap* map_corpus, CUtensorMap* map_users, const bf16* corpus, long long rows, int dim,
+                             const bf16* users_bf, std::string& err) {
+  phx_status s = sm100::make_map(map_corpus, corpus, rows, dim, TC_ROWS, err);
+  if (s) return s;
+  return sm100::make_map(map_users, users_bf, TC_Q, dim, TC_Q, err);
+}
+
+phx_status tc_scan_launch(const CUtensorMap& map_corpus, const CUtensorMap& map_users, const TcScanArgs& a, int mode,
+                          int num_sms, int* err_flag, cudaStream_t stream, std::string& err) {
+  const int kblk = a.dim / BK;
+  const size_t smem = (size_t)kblk * TC_Q * 128 + (size_t)TC_STAGES * kblk * TC_ROWS * 128 + TC_Q * 4 + 256 + 1024;
+  const long long n_tiles = (a.rows + TC_ROWS - 1) / TC_ROWS;
+  const long long n_work = (mode == 0) ? (n_tiles + a.stride - 1) / a.stride : n_tiles;
+  const int grid = (int)(n_work < num_sms ? n_work : num_sms);
+  if (grid <= 0) return PHX_OK;
+  if (mode == 0) {
+    PHX_CUDA_TRY(cudaFuncSetAttribute(scan_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), err);
+    scan_tc_kernel<0><<<grid, TC_THREADS, smem, stream>>>(map_corpus, map_users, a, err_flag);
+  } else {
+    PHX_CUDA_TRY(cudaFuncSetAttribute(scan_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), err);
+    scan_tc_kernel<1><<<grid, TC_THREADS, smem, stream>>>(map_corpus, map_users, a, err_flag);
+  }
+  PHX_CUDA_TRY(cudaGetLastError(), err);
+  return PHX_OK;
+}
+
+}  // namespace phx

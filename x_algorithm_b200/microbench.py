@@ -1,0 +1,143 @@
+"""Micro-benchmarks of the stand-alone operators against their rooflines (one JSON line each).
+
+    python -m x_algorithm_b200.microbench gather  [--ids 4194304] [--log2-rows 25] [--width 256] [--hashes 4]
+    python -m x_algorithm_b200.microbench topk    [--rows 12500000] [--dim 128] [--queries 256] [--k 1000]
+    python -m x_algorithm_b200.microbench attention [--batch 64] [--heads 16] [--dh 128] [--hist 1024] [--cands 1024]
+
+gather: the multi-hash gather-sum workload (8 tables x 2^24 rows x 256 bf16 = 64 GiB, realised as the four hash
+regions of the unified table x 2^25 rows: the same 2^27 rows x 512 B), 4 hashes per id, Zipf(1.1) ids.
+Algorithmic bytes per id = H*W*2 (rows) + W*2 (out) + 8 (id).
+topk: exhaustive dot-product top-k over one corpus shard; algorithmic bytes = rows*dim*2.
+attention: candidate-isolated attention; algorithmic FLOPs = 4*dh*H*(S^2 + C*(S+1)) per batch element.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import numpy as np
+
+
+def _peaks():
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def _zipf_ids(n, seed, s=1.1):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    u = rng.random(n)
+    a, N = 1.0 - s, float(1 << 40)
+    rank = np.clip(np.floor(((N ** a - 1.0) * u + 1.0) ** (1.0 / a)).astype(np.int64), 1, (1 << 40) - 1)
+    with np.errstate(over="ignore"):
+        ids = (rank * np.int64(0x9E3779B97F4A7C15 - (1 << 64))) & np.int64((1 << 40) - 1)
+    return np.where(ids == 0, 1, ids).astype(np.int64)
+
+
+def bench_gather(a):
+    import torch
+    import x_algorithm_b200 as px
+    hbm, _, src = _peaks()
+    cfg = px.PhoenixConfig(emb_size=a.width, num_layers=1, num_q_heads=a.width // 64, num_kv_heads=a.width // 64,
+                           key_size=64, history_len=1, num_candidates=1, max_batch=1, num_hashes=a.hashes,
+                           table_size=1 << a.log2_rows)
+    eng = px.PhoenixEngine(cfg, 0)
+    eng.table_fill_synthetic(7, 1.0 / math.sqrt(a.width))
+    n = a.ids
+    sets = [torch.from_numpy(_zipf_ids(n, 100 + i)).cuda() for i in range(3)]
+    out = torch.empty((n, a.width), dtype=torch.int16, device="cuda")
+    torch.cuda.synchronize()
+    times = []
+    for it in range(a.warmup + a.iters):
+        fam = it % 4
+        eng.gather_sum_device(fam, sets[it % 3], n, out)
+        eng.sync()
+        if it >= a.warmup:
+            times.append(eng.last_device_ms())
+    ms = float(np.median(times))
+    per_id = a.hashes * a.width * 2 + a.width * 2 + 8
+    gbs = per_id * n / (ms * 1e-3) / 1e9
+    print(json.dumps(dict(op="gather_sum", ids=n, hashes=a.hashes, width=a.width, table_gib=cfg.table_rows * a.width * 2 / 2**30,
+                          ms=ms, bytes_per_id=per_id, achieved_gbs=gbs, peak_gbs=hbm, frac=gbs / hbm, peak_source=src)))
+    eng.close()
+
+
+def bench_topk(a):
+    import torch
+    from x_algorithm_b200.retrieval import CorpusShard
+    hbm, tf, src = _peaks()
+    sh = CorpusShard(a.rows, a.dim, row_offset=0, max_queries=a.queries, max_k=a.k)
+    sh.fill_synthetic(4)
+    rng = np.random.default_rng(5)
+    u = rng.standard_normal((a.queries, a.dim)).astype(np.float32)
+    u /= np.linalg.norm(u, axis=1, keepdims=True)
+    users = torch.from_numpy(u).cuda()
+    sc = torch.empty((a.queries, a.k), dtype=torch.float32, device="cuda")
+    ids = torch.empty((a.queries, a.k), dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()
+    times = []
+    for it in range(a.warmup + a.iters):
+        sh.topk_device(users, a.queries, a.k, sc, ids)
+        sh.sync()
+        if it >= a.warmup:
+            times.append(sh.last_device_ms())
+    ms = float(np.median(times))
+    gbs = a.rows * a.dim * 2 / (ms * 1e-3) / 1e9
+    tfl = 2.0 * a.queries * a.dim * a.rows / (ms * 1e-3) / 1e12
+    print(json.dumps(dict(op="corpus_topk", rows=a.rows, dim=a.dim, queries=a.queries, k=a.k, ms=ms, achieved_gbs=gbs,
+                          peak_gbs=hbm, frac=gbs / hbm, tflops=tfl, peak_source=src)))
+    sh.close()
+
+
+def bench_attention(a):
+    import torch
+    from x_algorithm_b200.engine import ranker_attention
+    _, tf, src = _peaks()
+    B, H, dh, S, Cn = a.batch, a.heads, a.dh, a.hist, a.cands
+    T = S + Cn
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q, k, v = ((torch.randn(B, T, H, dh, device="cuda", generator=g) / math.sqrt(dh)).to(torch.bfloat16) for _ in range(3))
+    seg = torch.ones((B, T), dtype=torch.int32, device="cuda")
+    seg[:, S:] = -1
+    times = []
+    for it in range(a.warmup + a.iters):
+        out, ms = ranker_attention(q, k, v, seg, S, math.sqrt(128.0) / dh)
+        if it >= a.warmup:
+            times.append(ms)
+    ms = float(np.median(times))
+    fl = 4.0 * dh * H * (S * S + Cn * (S + 1)) * B
+    print(json.dumps(dict(op="ranker_attention", batch=B, heads=H, dh=dh, hist=S, cands=Cn, ms=ms,
+                          achieved_tflops=fl / (ms * 1e-3) / 1e12, peak_tflops=tf, frac=fl / (ms * 1e-3) / 1e12 / tf,
+                          peak_source=src)))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["gather", "topk", "attention"])
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--ids", type=int, default=1 << 22)
+    ap.add_argument("--log2-rows", type=int, default=25)
+    ap.add_argument("--width", type=int, default=256)
+    ap.add_argument("--hashes", type=int, default=4)
+    ap.add_argument("--rows", type=int, default=12_500_000)
+    ap.add_argument("--dim", type=int, default=128)
+    ap.add_argument("--queries", type=int, default=256)
+    ap.add_argument("--k", type=int, default=1000)
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--dh", type=int, default=128)
+    ap.add_argument("--hist", type=int, default=1024)
+    ap.add_argument("--cands", type=int, default=1024)
+    a = ap.parse_args()
+    {"gather": bench_gather, "topk": bench_topk, "attention": bench_attention}[a.op](a)
+
+
+if __name__ == "__main__":
+    main()
