@@ -100,6 +100,8 @@ struct HashFamilyDev {
   long long biases[PHX_MAX_HASHES];
   long long modulus;
   long long buckets_m1;  // table_size - 1
+  unsigned long long magic_mod;  // floor((2^64 - 1) / modulus): division-free remainder
+  unsigned long long magic_bkt;  // floor((2^64 - 1) / buckets_m1)
   int offset;            // region offset in the unified table
   int num_hashes;
 };

@@ -7,15 +7,25 @@
 namespace phx {
 namespace {
 
+// n mod d for any unsigned 64-bit n, with magic = floor((2^64 - 1) / d): the quotient estimate mulhi(n, magic)
+// is at most 2 short, so two conditional subtractions finish the job.  (A 64-bit '%' by a run-time value costs
+// ~100 instructions; this path made the gather instruction-bound.)
+__device__ __forceinline__ unsigned long long umod_magic(unsigned long long n, unsigned long long d, unsigned long long magic) {
+  unsigned long long r = n - __umul64hi(n, magic) * d;
+  if (r >= d) r -= d;
+  if (r >= d) r -= d;
+  return r;
+}
 // raw = (id*scale + bias) mod M, floored (non-negative); idx = 0 if id == 0 else raw mod (buckets-1) + 1
-__device__ __forceinline__ int hash_one(long long id, long long scale, long long bias, long long modulus,
-                                        long long buckets_m1, int offset) {
+__device__ __forceinline__ int hash_one(long long id, long long scale, long long bias, const HashFamilyDev& f) {
   if (id == 0) return 0;
   // wrapping int64 arithmetic, as numba / Rust release builds do
-  long long raw = (long long)((unsigned long long)id * (unsigned long long)scale + (unsigned long long)bias);
-  long long r = raw % modulus;
-  if (r < 0) r += modulus;
-  return (int)(r % buckets_m1) + 1 + offset;
+  const long long raw = (long long)((unsigned long long)id * (unsigned long long)scale + (unsigned long long)bias);
+  const unsigned long long m = (unsigned long long)f.modulus;
+  unsigned long long r;
+  if (raw >= 0) r = umod_magic((unsigned long long)raw, m, f.magic_mod);
+  else r = m - 1 - umod_magic((unsigned long long)(~raw), m, f.magic_mod);   // floored: -(x+1) mod m = m-1-(x mod m)
+  return (int)umod_magic(r, (unsigned long long)f.buckets_m1, f.magic_bkt) + 1 + f.offset;
 }
 
 __device__ __forceinline__ void acc_row(float (&acc)[8], const bf16* row, int col) {
@@ -39,10 +49,10 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
   const int H = a.item.num_hashes;
   // lanes 0..H-1 hash the post id, lanes H..2H-1 the author id
   int my_idx = 0;
-  if (lane < H) my_idx = hash_one(post_id, a.item.scales[lane], a.item.biases[lane], a.item.modulus, a.item.buckets_m1, a.item.offset);
+  if (lane < H) my_idx = hash_one(post_id, a.item.scales[lane], a.item.biases[lane], a.item);
   else if (lane < 2 * H) {
     const int j = lane - H;
-    my_idx = hash_one(auth_id, a.author.scales[j], a.author.biases[j], a.author.modulus, a.author.buckets_m1, a.author.offset);
+    my_idx = hash_one(auth_id, a.author.scales[j], a.author.biases[j], a.author);
   }
   if (a.hashes && lane < 2 * H) a.hashes[tok * (2 * H) + lane] = my_idx;
   const int first_post_hash = __shfl_sync(0xffffffffu, my_idx, 0);
@@ -83,7 +93,7 @@ __global__ void hash_ids_kernel(HashFamilyDev fam, const long long* __restrict__
   if (i >= n * fam.num_hashes) return;
   const long long t = i / fam.num_hashes;
   const int j = (int)(i % fam.num_hashes);
-  out[i] = hash_one(ids[t], fam.scales[j], fam.biases[j], fam.modulus, fam.buckets_m1, fam.offset);
+  out[i] = hash_one(ids[t], fam.scales[j], fam.biases[j], fam);
 }
 
 // Stand-alone gather-sum: out[i] = bf16(sum_j table[hash_j(id_i)]) in hash order.  LANES lanes per id
@@ -94,18 +104,18 @@ __global__ void __launch_bounds__(256) gather_sum_kernel(HashFamilyDev fam, cons
                                                          long long n, bf16* __restrict__ out) {
   const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LANES;
   const int sub = threadIdx.x % LANES;
-  if (gid >= n) return;
-  const long long id = __ldg(ids + gid);
+  const bool valid = gid < n;   // no early return: the shuffles below need every lane of the warp
+  const long long id = valid ? __ldg(ids + gid) : 0;
+  // lane j of the id's lane group computes hash j; the group shares the results by shuffle
+  int mine = 0;
+  if (sub < fam.num_hashes) {
+    mine = hash_one(id, fam.scales[sub], fam.biases[sub], fam);
+    if (mine < 0 || mine >= table_rows) mine = 0;  // out of range -> row 0
+  }
   long long idx[PHX_MAX_HASHES];
 #pragma unroll
-  for (int j = 0; j < PHX_MAX_HASHES; ++j) {
-    idx[j] = 0;
-    if (j < fam.num_hashes) {
-      idx[j] = hash_one(id, fam.scales[j], fam.biases[j], fam.modulus, fam.buckets_m1, fam.offset);
-      if (idx[j] < 0 || idx[j] >= table_rows) idx[j] = 0;
-    }
-  }
-  for (int col = sub * 8; col < D; col += LANES * 8) {
+  for (int j = 0; j < PHX_MAX_HASHES; ++j) idx[j] = __shfl_sync(0xffffffffu, mine, j, LANES);
+  for (int col = sub * 8; col < D && valid; col += LANES * 8) {
     uint4 u[PHX_MAX_HASHES];
 #pragma unroll
     for (int j = 0; j < PHX_MAX_HASHES; ++j)

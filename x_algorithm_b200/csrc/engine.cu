@@ -135,6 +135,8 @@ HashFamilyDev to_dev(const phx_hash_family& f, int offset) {
   for (int i = 0; i < PHX_MAX_HASHES; ++i) { d.scales[i] = f.scales[i]; d.biases[i] = f.biases[i]; }
   d.modulus = f.modulus;
   d.buckets_m1 = f.table_size - 1;
+  d.magic_mod = f.modulus > 0 ? 0xFFFFFFFFFFFFFFFFull / (unsigned long long)f.modulus : 0;
+  d.magic_bkt = d.buckets_m1 > 0 ? 0xFFFFFFFFFFFFFFFFull / (unsigned long long)d.buckets_m1 : 0;
   d.offset = offset;
   d.num_hashes = f.num_hashes;
   return d;

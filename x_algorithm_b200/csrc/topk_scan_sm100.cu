@@ -24,6 +24,8 @@ constexpr int TC_ROWS = 128;      // corpus rows per tile
 constexpr int TC_Q = 256;         // query columns (padded)
 constexpr int TC_THREADS = 320;
 constexpr int TC_STAGES = 4;
+constexpr int QCAP = 64;          // per-warp staging queue of survivors (records of 16 bytes)
+constexpr int QFLUSH = 24;        // flush a warp's queue once it holds this many records
 
 __device__ __forceinline__ uint32_t ord32(float f) {
   if (f == 0.f) f = 0.f;  // -0 -> +0
@@ -33,6 +35,11 @@ __device__ __forceinline__ uint32_t ord32(float f) {
 __device__ __forceinline__ float unord32(uint32_t o) {
   const uint32_t u = (o & 0x80000000u) ? (o & 0x7FFFFFFFu) : ~o;
   return __uint_as_float(u);
+}
+
+__device__ __forceinline__ void append_survivor(const TcScanArgs& a, int u, unsigned long long key) {
+  const int slot = atomicAdd(&a.counts[u], 1);
+  if (slot < a.cap) a.surv[(size_t)u * a.cap + slot] = key;
 }
 
 template <int MODE>
@@ -47,7 +54,8 @@ scan_tc_kernel(const __grid_constant__ CUtensorMap map_corpus, const __grid_cons
   const uint32_t stage_bytes = (uint32_t)kblk * TC_ROWS * 128;
   const uint32_t stage_base = users_smem + users_bytes;
   const uint32_t thr_smem = stage_base + TC_STAGES * stage_bytes;  // [256] float thresholds
-  const uint32_t bars = thr_smem + TC_Q * 4;
+  const uint32_t queue_smem = thr_smem + TC_Q * 4;                 // [8 warps][QCAP] uint4 records + [8] counters
+  const uint32_t bars = queue_smem + 8 * QCAP * 16 + 64;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (TC_STAGES + s); };
   auto tfull_bar = [&](int x) { return bars + 8u * (2 * TC_STAGES + x); };
@@ -56,6 +64,9 @@ scan_tc_kernel(const __grid_constant__ CUtensorMap map_corpus, const __grid_cons
   const uint32_t tmem_slot = bars + 8u * (2 * TC_STAGES + 5);
   uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
   float* s_thr = reinterpret_cast<float*>(smem_raw + (thr_smem - smem_u32(smem_raw)));
+  uint4* s_queue = reinterpret_cast<uint4*>(smem_raw + (queue_smem - smem_u32(smem_raw)));
+  int* s_qcnt = reinterpret_cast<int*>(s_queue + 8 * QCAP);
+  if (threadIdx.x < 8) s_qcnt[threadIdx.x] = 0;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* verr = err_flag;
@@ -154,11 +165,14 @@ scan_tc_kernel(const __grid_constant__ CUtensorMap map_corpus, const __grid_cons
             for (int e = 0; e < 4; ++e) {
               const float v = __uint_as_float(r[k4 * 4 + e]);
               if (v >= tt[e] && row_ok) {
+                // stage the hit in the warp's shared-memory queue: the global append (an atomic whose result the
+                // store depends on) would stall the whole warp for a memory round trip per hit
+                const unsigned long long key = ((unsigned long long)ord32(round_bf(v)) << 32) |
+                                               (unsigned long long)(0xFFFFFFFFu - (uint32_t)(a.row_offset + row));
                 const int u = u0 + k4 * 4 + e;
-                const int slot = atomicAdd(&a.counts[u], 1);
-                if (slot < a.cap)
-                  a.surv[(size_t)u * a.cap + slot] = ((unsigned long long)ord32(round_bf(v)) << 32) |
-                                                     (unsigned long long)(0xFFFFFFFFu - (uint32_t)(a.row_offset + row));
+                const int qs = atomicAdd(&s_qcnt[ew], 1);
+                if (qs < QCAP) s_queue[ew * QCAP + qs] = make_uint4((uint32_t)key, (uint32_t)(key >> 32), (uint32_t)u, 0u);
+                else append_survivor(a, u, key);   // queue full (dense regime): append directly
               }
             }
           }
@@ -176,6 +190,27 @@ scan_tc_kernel(const __grid_constant__ CUtensorMap map_corpus, const __grid_cons
       }
       tc_fence_before();
       mbar_arrive(tempty_bar(acc));
+      if (MODE == 1) {
+        __syncwarp();
+        const int nq = s_qcnt[ew] < QCAP ? s_qcnt[ew] : QCAP;
+        if (nq >= QFLUSH) {
+          for (int i = lane; i < nq; i += 32) {
+            const uint4 rec = s_queue[ew * QCAP + i];
+            append_survivor(a, (int)rec.z, ((unsigned long long)rec.y << 32) | rec.x);
+          }
+          __syncwarp();
+          if (lane == 0) s_qcnt[ew] = 0;
+        }
+        __syncwarp();
+      }
+    }
+    if (MODE == 1) {   // drain what is left
+      __syncwarp();
+      const int nq = s_qcnt[ew] < QCAP ? s_qcnt[ew] : QCAP;
+      for (int i = lane; i < nq; i += 32) {
+        const uint4 rec = s_queue[ew * QCAP + i];
+        append_survivor(a, (int)rec.z, ((unsigned long long)rec.y << 32) | rec.x);
+      }
     }
   }
 
@@ -202,7 +237,7 @@ phx_status tc_scan_make_maps(CUtensorMap* map_corpus, CUtensorMap* map_users, co
 phx_status tc_scan_launch(const CUtensorMap& map_corpus, const CUtensorMap& map_users, const TcScanArgs& a, int mode,
                           int num_sms, int* err_flag, cudaStream_t stream, std::string& err) {
   const int kblk = a.dim / BK;
-  const size_t smem = (size_t)kblk * TC_Q * 128 + (size_t)TC_STAGES * kblk * TC_ROWS * 128 + TC_Q * 4 + 256 + 1024;
+  const size_t smem = (size_t)kblk * TC_Q * 128 + (size_t)TC_STAGES * kblk * TC_ROWS * 128 + TC_Q * 4 + 8 * QCAP * 16 + 64 + 256 + 1024;
   const long long n_tiles = (a.rows + TC_ROWS - 1) / TC_ROWS;
   const long long n_work = (mode == 0) ? (n_tiles + a.stride - 1) / a.stride : n_tiles;
   const int grid = (int)(n_work < num_sms ? n_work : num_sms);
