@@ -128,6 +128,8 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--table-log2", type=int, default=22, help="log2 buckets per hash region (smaller for profiling captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tables", default="sharded", choices=["sharded", "replicated"],
+                    help="N > 1: row-shard the embedding table over the ranks (peer loads over NVLink) or replicate it")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -150,11 +152,15 @@ def main():
     wl = dict(WORKLOAD)
     wl["table_size"] = 1 << args.table_log2
     B = args.batch
-    cfg = px.PhoenixConfig(max_batch=B, **wl)
+    sharded = world > 1 and args.tables == "sharded"
+    cfg = px.PhoenixConfig(max_batch=B, table_world=world if sharded else 1, table_rank=rank if sharded else 0, **wl)
     eng = px.PhoenixEngine(cfg, local_rank)
     ocfg = po.ModelConfig(**wl)
     eng.load_weights(po.make_weights(ocfg, WEIGHT_SEED))
     eng.table_fill_synthetic(TABLE_SEED, 1.0 / math.sqrt(cfg.emb_size))
+    if sharded:
+        from x_algorithm_b200.parallel import attach_table_shards
+        attach_table_shards(eng)
     bw = po.make_blend_weights(BLEND_SEED)
     eng.set_blend(px.blend_spec_from_weights(px.ValueModelWeights(w=dict(bw.w)), px.HEAD_NAMES_19, cfg.num_actions))
 
@@ -235,6 +241,7 @@ def main():
             vs_baseline=None, dtype="bf16", data="synthetic",
             config=dict(workload="phoenix_rank_bf16_D512_L8_H8x64_B256_S128_C512", batch_per_gpu=B, history=cfg.history_len,
                         candidates=C, table_rows=cfg.table_rows, parallelism=f"dp{world}",
+                        tables=("row-sharded over ranks, remote rows by NVLink peer loads" if sharded else "one full table per GPU"),
                         l2="working set per step (activations 1.7 GB, table 17 GB) exceeds the 126 MB L2; 4 input batches rotated"),
             e2e=dict(value=total / (e2e_ms * 1e-3), unit="candidates/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
                      ms_per_step=e2e_ms / args.steps),

@@ -76,6 +76,12 @@ typedef struct phx_model_config {
   float rope_base;
   float dwell_norm_scale;  /* recsys_model.py:712-733 */
   phx_hash_family user, item, author, ip; /* unified table regions, recsys_embedding.py:234-248 */
+  /* Row sharding of the unified table over `table_world` engines (one per GPU) in contiguous ranges, the
+   * ownership rule of the reference's row-sharded embedding (phoenix/xrex/cuda/row_emb/src/row_emb_kernel.hpp:
+   * 19-25: owner = row / rows_per_rank).  This engine allocates shard `table_rank` only and reads the other
+   * shards through peer mappings (phx_table_attach_peer*).  0 or 1 = not sharded. */
+  int32_t table_world;
+  int32_t table_rank;
 } phx_model_config;
 
 /* Weighted blend in term-list form: xai-value-model/scoring.rs:67-73, 112-120, 282-291.
@@ -142,6 +148,21 @@ phx_status phx_table_upload(phx_engine* e, int64_t row0, int64_t nrows, const ui
  * touched rows, phoenix/xrex/inference/h2d.py:418-445. */
 phx_status phx_table_fill_synthetic(phx_engine* e, uint32_t seed, float amp);
 phx_status phx_set_blend(phx_engine* e, const phx_blend_spec* spec);
+
+/* Row-sharded tables.  Replaces the reference's id / row exchange (phoenix/xrex/cuda/row_emb/src/row_emb_comm.cc:
+ * 655-743: all-to-all of ids, owner-side gather, all-to-all of rows) by direct loads from the owner's shard over
+ * NVLink inside the gather kernel: each engine exports its shard once, every other engine maps it, and the
+ * hash -> gather -> fixed-order sum kernel dereferences whichever shard owns a row.  The sum order is by hash
+ * slot and does not depend on the number of shards, so results are bit-identical to the unsharded table. */
+#define PHX_IPC_HANDLE_BYTES 64
+/* Export this engine's shard for another process (a CUDA IPC memory handle). */
+phx_status phx_table_ipc_handle(phx_engine* e, uint8_t out[PHX_IPC_HANDLE_BYTES]);
+/* Map shard `rank` exported by another process. */
+phx_status phx_table_attach_peer(phx_engine* e, int32_t rank, const uint8_t handle[PHX_IPC_HANDLE_BYTES]);
+/* Same-process variants: the device pointer of this engine's shard / attach a shard by pointer (engines of one
+ * process, devices with peer access enabled or the same device). */
+phx_status phx_table_local_ptr(phx_engine* e, void** out);
+phx_status phx_table_attach_peer_ptr(phx_engine* e, int32_t rank, const void* shard_dev);
 
 /* ---- ranking ---------------------------------------------------------------------------------- */
 

@@ -180,6 +180,48 @@ def test_simt_gemm_path_matches_tcgen05(torch, monkeypatch):
     assert rel_l2(r1.log_probs, r2.log_probs) < 5e-3
 
 
+def test_row_sharded_table_is_bit_identical(torch, monkeypatch):
+    """Two engines each hold half of the unified table and read the other half through a peer mapping (here both on
+    one device, attached by pointer; across processes the same path uses CUDA IPC handles).  Hash rows, gathered
+    sums and the whole forward are bit-identical to the single-table engine."""
+    import x_algorithm_b200 as px
+    monkeypatch.setenv("PHX_DEBUG_TAPS", "1")
+    ocfg, w, rows_fn, ref = make_pair(max_batch=4)
+    amp = 1.0 / math.sqrt(ocfg.emb_size)
+    shards = []
+    for r in range(2):
+        e = px.PhoenixEngine(px.PhoenixConfig(max_batch=4, table_world=2, table_rank=r), 0)
+        e.load_weights(w)
+        e.table_fill_synthetic(7, amp)
+        shards.append(e)
+    b = po.make_batch(ocfg, 4, seed=21, ragged=True)
+    with pytest.raises(px.PhoenixError) as ei:          # peers not attached yet
+        shards[0].rank(to_inputs(b))
+    assert ei.value.status == 6 and "not attached" in ei.value.message
+    shards[0].table_attach_peer_ptr(1, shards[1].table_local_ptr())
+    shards[1].table_attach_peer_ptr(0, shards[0].table_local_ptr())
+    want = ref.rank(to_inputs(b))
+    want_tok = ref.debug_read("tokens", (4, ocfg.seq_len, ocfg.emb_size), np.uint16)
+    for e in shards:
+        got = e.rank(to_inputs(b))
+        np.testing.assert_array_equal(e.debug_read("tokens", (4, ocfg.seq_len, ocfg.emb_size), np.uint16), want_tok)
+        np.testing.assert_array_equal(got.log_probs, want.log_probs)
+        np.testing.assert_array_equal(got.continuous, want.continuous)
+    ids = po.make_batch(ocfg, 32, seed=3, zipf_s=1.1).cand_post_ids.ravel()
+    d_ids = torch.from_numpy(ids).cuda()
+    outs = []
+    for e in [ref] + shards:
+        o = torch.empty((ids.size, ocfg.emb_size), dtype=torch.int16, device="cuda")
+        e.gather_sum_device(2, d_ids, ids.size, o)
+        e.sync()
+        outs.append(o.cpu().numpy())
+    np.testing.assert_array_equal(outs[1], outs[0]); np.testing.assert_array_equal(outs[2], outs[0])
+    want_rows = po.gather_sum(rows_fn(ocfg.hash_layout().author_hash(ids)))
+    np.testing.assert_array_equal(outs[0].view(np.uint16), want_rows)
+    for e in shards + [ref]:
+        e.close()
+
+
 def test_engine_errors_are_statuses(torch):
     import x_algorithm_b200 as px
     with pytest.raises(px.PhoenixError) as ei:

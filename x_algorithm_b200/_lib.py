@@ -27,7 +27,8 @@ class ModelConfig(C.Structure):
         "num_candidates", "max_batch", "num_actions", "num_continuous", "num_action_types", "num_surfaces",
         "rotary", "qk_norm", "primer_norm", "cap_method")] + [(n, C.c_float) for n in (
         "attn_logit_cap", "final_logit_cap", "rms_eps", "rope_base", "dwell_norm_scale")] + [
-        ("user", HashFamily), ("item", HashFamily), ("author", HashFamily), ("ip", HashFamily)]
+        ("user", HashFamily), ("item", HashFamily), ("author", HashFamily), ("ip", HashFamily),
+        ("table_world", C.c_int32), ("table_rank", C.c_int32)]
 
 
 class BlendSpec(C.Structure):
@@ -56,6 +57,10 @@ SIGNATURES = {
     "phx_table_upload": (C.c_int32, [_P, C.c_int64, C.c_int64, _P]),
     "phx_table_fill_synthetic": (C.c_int32, [_P, C.c_uint32, C.c_float]),
     "phx_set_blend": (C.c_int32, [_P, C.POINTER(BlendSpec)]),
+    "phx_table_ipc_handle": (C.c_int32, [_P, _P]),
+    "phx_table_attach_peer": (C.c_int32, [_P, C.c_int32, _P]),
+    "phx_table_local_ptr": (C.c_int32, [_P, C.POINTER(_P)]),
+    "phx_table_attach_peer_ptr": (C.c_int32, [_P, C.c_int32, _P]),
     "phx_rank_forward": (C.c_int32, [_P, C.POINTER(RankBatch), C.POINTER(RankOut)]),
     "phx_rank_forward_device": (C.c_int32, [_P, C.POINTER(RankBatch), C.POINTER(RankOut)]),
     "phx_sync": (C.c_int32, [_P]),

@@ -74,6 +74,8 @@ class PhoenixConfig:
     rms_eps: float = 1e-5
     rope_base: float = 10000.0
     dwell_norm_scale: float = 30.0
+    table_world: int = 1        # row-shard the unified table over this many engines (one per GPU)
+    table_rank: int = 0
 
     @property
     def ffn_size(self) -> int:  # phoenix/xrex/utils/utils.py:37-52
@@ -107,4 +109,5 @@ class PhoenixConfig:
         c.rms_eps, c.rope_base, c.dwell_norm_scale = self.rms_eps, self.rope_base, self.dwell_norm_scale
         u, i, a, p = self.families()
         c.user, c.item, c.author, c.ip = u.to_c(), i.to_c(), a.to_c(), p.to_c()
+        c.table_world, c.table_rank = int(self.table_world), int(self.table_rank)
         return c

@@ -106,6 +106,25 @@ struct HashFamilyDev {
   int num_hashes;
 };
 
+// The unified embedding table, possibly row-sharded over `world` devices in contiguous ranges: global row r lives
+// on shard r / rows_per_shard at local row r % rows_per_shard (the reference's row_emb ownership rule,
+// phoenix/xrex/cuda/row_emb/src/row_emb_kernel.hpp:19-25).  base[s] is a pointer this device can load from:
+// its own shard, or a peer's shard mapped over NVLink.  world == 1: one shard holding every row.
+#define PHX_MAX_SHARDS 16
+struct TableView {
+  const bf16* base[PHX_MAX_SHARDS];
+  long long total_rows;
+  unsigned int rows_per_shard;
+  int world;
+  __device__ __forceinline__ const bf16* row_ptr(long long row, int D) const {
+    if (row < 0 || row >= total_rows) row = 0;  // out of range -> row 0 (emb_table.rs:134-137)
+    if (world == 1) return base[0] + row * D;
+    const unsigned int r = (unsigned int)row;
+    const unsigned int s = r / rows_per_shard;
+    return base[s] + (long long)(r - s * rows_per_shard) * D;
+  }
+};
+
 struct TokenBuildArgs {
   const long long* hist_post;
   const long long* hist_author;
@@ -113,8 +132,7 @@ struct TokenBuildArgs {
   const int* hist_surfaces;
   const long long* cand_post;
   const long long* cand_author;
-  const bf16* table;
-  long long table_rows;
+  TableView table;
   const bf16* action_table;
   const bf16* surface_table;
   int num_action_types, num_surfaces;
@@ -129,7 +147,7 @@ struct TokenBuildArgs {
 phx_status build_tokens_launch(const TokenBuildArgs& a, cudaStream_t stream, std::string& err);
 phx_status hash_ids_launch(const HashFamilyDev& fam, const long long* ids, long long n, int* out, cudaStream_t stream,
                            std::string& err);
-phx_status gather_sum_launch(const HashFamilyDev& fam, const bf16* table, long long table_rows, int D,
+phx_status gather_sum_launch(const HashFamilyDev& fam, const TableView& table, int D,
                              const long long* ids, long long n, bf16* out, cudaStream_t stream, std::string& err);
 phx_status table_fill_launch(bf16* table, long long row0, long long rows, int width, uint32_t seed, float amp,
                              cudaStream_t stream, std::string& err);

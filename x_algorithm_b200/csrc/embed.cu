@@ -67,9 +67,8 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
   for (int col = lane * 8; col < a.D; col += 256) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int j = 0; j < 2 * H; ++j) {
-      long long idx = __shfl_sync(0xffffffffu, my_idx, j);
-      if (idx < 0 || idx >= a.table_rows) idx = 0;  // out of range -> row 0
-      acc_row(acc, a.table + idx * a.D, col);
+      const long long idx = __shfl_sync(0xffffffffu, my_idx, j);
+      acc_row(acc, a.table.row_ptr(idx, a.D), col);
     }
     if (is_hist) {
       acc_row(acc, a.action_table + (long long)act * a.D, col);
@@ -99,8 +98,8 @@ __global__ void hash_ids_kernel(HashFamilyDev fam, const long long* __restrict__
 // Stand-alone gather-sum: out[i] = bf16(sum_j table[hash_j(id_i)]) in hash order.  LANES lanes per id
 // (LANES * 8 >= D or a loop), several ids per warp for narrow rows.
 template <int LANES>
-__global__ void __launch_bounds__(256) gather_sum_kernel(HashFamilyDev fam, const bf16* __restrict__ table,
-                                                         long long table_rows, int D, const long long* __restrict__ ids,
+__global__ void __launch_bounds__(256) gather_sum_kernel(HashFamilyDev fam, TableView table, int D,
+                                                         const long long* __restrict__ ids,
                                                          long long n, bf16* __restrict__ out) {
   const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LANES;
   const int sub = threadIdx.x % LANES;
@@ -110,16 +109,15 @@ __global__ void __launch_bounds__(256) gather_sum_kernel(HashFamilyDev fam, cons
   int mine = 0;
   if (sub < fam.num_hashes) {
     mine = hash_one(id, fam.scales[sub], fam.biases[sub], fam);
-    if (mine < 0 || mine >= table_rows) mine = 0;  // out of range -> row 0
   }
-  long long idx[PHX_MAX_HASHES];
+  const bf16* rowp[PHX_MAX_HASHES];
 #pragma unroll
-  for (int j = 0; j < PHX_MAX_HASHES; ++j) idx[j] = __shfl_sync(0xffffffffu, mine, j, LANES);
+  for (int j = 0; j < PHX_MAX_HASHES; ++j) rowp[j] = table.row_ptr(__shfl_sync(0xffffffffu, mine, j, LANES), D);
   for (int col = sub * 8; col < D && valid; col += LANES * 8) {
     uint4 u[PHX_MAX_HASHES];
 #pragma unroll
     for (int j = 0; j < PHX_MAX_HASHES; ++j)
-      if (j < fam.num_hashes) u[j] = __ldg(reinterpret_cast<const uint4*>(table + idx[j] * D + col));
+      if (j < fam.num_hashes) u[j] = __ldg(reinterpret_cast<const uint4*>(rowp[j] + col));
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int j = 0; j < PHX_MAX_HASHES; ++j) {
@@ -204,14 +202,14 @@ phx_status hash_ids_launch(const HashFamilyDev& fam, const long long* ids, long 
   return PHX_OK;
 }
 
-phx_status gather_sum_launch(const HashFamilyDev& fam, const bf16* table, long long table_rows, int D,
+phx_status gather_sum_launch(const HashFamilyDev& fam, const TableView& table, int D,
                              const long long* ids, long long n, bf16* out, cudaStream_t stream, std::string& err) {
   if (D % 8 != 0) { err = "gather_sum: D must be a multiple of 8"; return PHX_E_ARG; }
   if (n == 0) return PHX_OK;
   if (D <= 128) {
-    gather_sum_kernel<16><<<(unsigned)((n * 16 + 255) / 256), 256, 0, stream>>>(fam, table, table_rows, D, ids, n, out);
+    gather_sum_kernel<16><<<(unsigned)((n * 16 + 255) / 256), 256, 0, stream>>>(fam, table, D, ids, n, out);
   } else {
-    gather_sum_kernel<32><<<(unsigned)((n * 32 + 255) / 256), 256, 0, stream>>>(fam, table, table_rows, D, ids, n, out);
+    gather_sum_kernel<32><<<(unsigned)((n * 32 + 255) / 256), 256, 0, stream>>>(fam, table, D, ids, n, out);
   }
   PHX_CUDA_TRY(cudaGetLastError(), err);
   return PHX_OK;

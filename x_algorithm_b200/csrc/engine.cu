@@ -65,7 +65,11 @@ struct phx_engine {
 
   // dimensions
   int D, S, C, T, Hq, Hkv, dh, F, QW, HD, V, NC;
-  long long table_rows = 0;
+  long long table_rows = 0;        // rows of the whole unified table
+  int table_world = 1, table_rank = 0;
+  long long shard_rows = 0;        // rows per shard (== table_rows when not sharded)
+  const bf16* shard_ptr[PHX_MAX_SHARDS] = {nullptr};   // this device's view of every shard
+  void* ipc_opened[PHX_MAX_SHARDS] = {nullptr};
   long long max_tokens = 0;
 
   // parameters
@@ -142,6 +146,20 @@ HashFamilyDev to_dev(const phx_hash_family& f, int offset) {
   return d;
 }
 
+TableView table_view(const phx_engine* e) {
+  TableView v;
+  for (int i = 0; i < PHX_MAX_SHARDS; ++i) v.base[i] = e->shard_ptr[i];
+  v.total_rows = e->table_rows;
+  v.rows_per_shard = (unsigned int)e->shard_rows;
+  v.world = e->table_world;
+  return v;
+}
+bool shards_complete(phx_engine* e) {
+  for (int i = 0; i < e->table_world; ++i)
+    if (!e->shard_ptr[i]) { e->err = "table shard " + std::to_string(i) + " is not attached (phx_table_attach_peer)"; return false; }
+  return true;
+}
+
 // region offsets of the unified table: phoenix/xrex/models/recsys_embedding.py:234-248
 void region_offsets(const phx_model_config& c, long long* user, long long* item, long long* author, long long* ip,
                     long long* total) {
@@ -168,6 +186,8 @@ phx_status check_cfg(const phx_model_config& c, std::string& err) {
   }
   if (c.item.num_hashes <= 0 || c.item.num_hashes != c.author.num_hashes) return bad("item/author hash counts must match");
   if (c.cap_method < 0 || c.cap_method > 2) return bad("cap_method");
+  if (c.table_world < 0 || c.table_world > PHX_MAX_SHARDS || (c.table_world > 1 && (c.table_rank < 0 || c.table_rank >= c.table_world)))
+    return bad("table_world / table_rank");
   return PHX_OK;
 }
 
@@ -288,7 +308,7 @@ phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc) 
   ta.hist_post = (const long long*)bd->hist_post_ids; ta.hist_author = (const long long*)bd->hist_author_ids;
   ta.hist_actions = bd->hist_actions; ta.hist_surfaces = bd->hist_surfaces;
   ta.cand_post = (const long long*)bd->cand_post_ids; ta.cand_author = (const long long*)bd->cand_author_ids;
-  ta.table = e->table; ta.table_rows = e->table_rows;
+  ta.table = table_view(e);
   ta.action_table = e->action_table; ta.surface_table = e->surface_table;
   ta.num_action_types = e->cfg.num_action_types; ta.num_surfaces = e->cfg.num_surfaces;
   ta.item = to_dev(e->cfg.item, (int)oi); ta.author = to_dev(e->cfg.author, (int)oa);
@@ -343,14 +363,19 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
   long long ou, oi, oa, oip, tot;
   region_offsets(*cfg, &ou, &oi, &oa, &oip, &tot);
   e->table_rows = tot;
+  if (tot >= (1ll << 31)) { e->err = "the unified table must have fewer than 2^31 rows"; return fail(PHX_E_ARG); }
+  e->table_world = cfg->table_world > 1 ? cfg->table_world : 1;
+  e->table_rank = cfg->table_world > 1 ? cfg->table_rank : 0;
+  e->shard_rows = (tot + e->table_world - 1) / e->table_world;
   e->max_tokens = (long long)cfg->max_batch * e->T;
   const long long M = e->max_tokens;
 #define TRY(x) do { phx_status _s = (x); if (_s) return fail(_s); } while (0)
 #define CU(x) do { cudaError_t _c = (x); if (_c != cudaSuccess) { e->err = std::string(#x) + ": " + cudaGetErrorString(_c); return fail(PHX_E_CUDA); } } while (0)
   CU(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
   CU(cudaEventCreate(&e->ev0)); CU(cudaEventCreate(&e->ev1));
-  TRY(dev_alloc(e, &e->table, (size_t)tot * e->D));
-  CU(cudaMemset(e->table, 0, (size_t)tot * e->D * 2));
+  TRY(dev_alloc(e, &e->table, (size_t)e->shard_rows * e->D));
+  CU(cudaMemset(e->table, 0, (size_t)e->shard_rows * e->D * 2));
+  e->shard_ptr[e->table_rank] = e->table;
   TRY(dev_alloc(e, &e->x, (size_t)M * e->D));
   TRY(dev_alloc(e, &e->hbuf, (size_t)M * e->D));
   TRY(dev_alloc(e, &e->qkv, (size_t)M * e->QW));
@@ -417,6 +442,7 @@ void phx_engine_destroy(phx_engine* e) {
   if (!e) return;
   cudaSetDevice(e->device);
   if (e->stream) cudaStreamSynchronize(e->stream);
+  for (auto p : e->ipc_opened) if (p) cudaIpcCloseMemHandle(p);
   auto fr = [](void* p) { if (p) cudaFree(p); };
   fr(e->table); fr(e->action_table); fr(e->surface_table); fr(e->final_norm); fr(e->unembed_t);
   for (auto& L : e->layers) {
@@ -485,17 +511,57 @@ phx_status phx_load_param(phx_engine* e, const char* name, const float* host, in
 
 phx_status phx_table_upload(phx_engine* e, int64_t row0, int64_t nrows, const uint16_t* host_bf16) {
   if (!e || !host_bf16 || row0 < 0 || nrows < 0 || row0 + nrows > e->table_rows) { if (e) e->err = "phx_table_upload: range"; return PHX_E_ARG; }
+  const long long lo = (long long)e->table_rank * e->shard_rows;
+  if (row0 < lo || row0 + nrows > lo + e->shard_rows) { e->err = "phx_table_upload: rows outside this engine's shard"; return PHX_E_ARG; }
   cudaSetDevice(e->device);
-  PHX_CUDA_TRY(cudaMemcpy(e->table + row0 * e->D, host_bf16, (size_t)nrows * e->D * 2, cudaMemcpyHostToDevice), e->err);
+  PHX_CUDA_TRY(cudaMemcpy(e->table + (row0 - lo) * e->D, host_bf16, (size_t)nrows * e->D * 2, cudaMemcpyHostToDevice), e->err);
   return PHX_OK;
 }
 
 phx_status phx_table_fill_synthetic(phx_engine* e, uint32_t seed, float amp) {
   if (!e) return PHX_E_ARG;
   cudaSetDevice(e->device);
-  phx_status s = table_fill_launch(e->table, 0, e->table_rows, e->D, seed, amp, e->stream, e->err);
+  const long long lo = (long long)e->table_rank * e->shard_rows;
+  long long mine = e->table_rows - lo;
+  if (mine > e->shard_rows) mine = e->shard_rows;
+  if (mine < 0) mine = 0;
+  phx_status s = table_fill_launch(e->table, lo, mine, e->D, seed, amp, e->stream, e->err);
   if (s) return s;
   PHX_CUDA_TRY(cudaStreamSynchronize(e->stream), e->err);
+  return PHX_OK;
+}
+
+phx_status phx_table_ipc_handle(phx_engine* e, uint8_t out[PHX_IPC_HANDLE_BYTES]) {
+  if (!e || !out) return PHX_E_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == PHX_IPC_HANDLE_BYTES, "IPC handle size");
+  cudaSetDevice(e->device);
+  cudaIpcMemHandle_t h;
+  PHX_CUDA_TRY(cudaIpcGetMemHandle(&h, e->table), e->err);
+  memcpy(out, &h, sizeof(h));
+  return PHX_OK;
+}
+
+phx_status phx_table_attach_peer(phx_engine* e, int32_t rank, const uint8_t handle[PHX_IPC_HANDLE_BYTES]) {
+  if (!e || !handle || rank < 0 || rank >= e->table_world || rank == e->table_rank) { if (e) e->err = "phx_table_attach_peer: bad rank"; return PHX_E_ARG; }
+  cudaSetDevice(e->device);
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  PHX_CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), e->err);
+  e->ipc_opened[rank] = p;
+  e->shard_ptr[rank] = static_cast<const bf16*>(p);
+  return PHX_OK;
+}
+
+phx_status phx_table_local_ptr(phx_engine* e, void** out) {
+  if (!e || !out) return PHX_E_ARG;
+  *out = e->table;
+  return PHX_OK;
+}
+
+phx_status phx_table_attach_peer_ptr(phx_engine* e, int32_t rank, const void* shard_dev) {
+  if (!e || !shard_dev || rank < 0 || rank >= e->table_world || rank == e->table_rank) { if (e) e->err = "phx_table_attach_peer_ptr: bad rank"; return PHX_E_ARG; }
+  e->shard_ptr[rank] = static_cast<const bf16*>(shard_dev);
   return PHX_OK;
 }
 
@@ -511,7 +577,7 @@ phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* bd, cons
   if (!e || !bd || !od) return PHX_E_ARG;
   if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
   if (bd->batch < 0 || bd->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
-  if (!params_complete(e, true)) return PHX_E_STATE;
+  if (!params_complete(e, true) || !shards_complete(e)) return PHX_E_STATE;
   cudaSetDevice(e->device);
   const int B = bd->batch;
   e->last_batch = B; e->last_launches = 0; e->prof_used = 0;
@@ -658,7 +724,8 @@ phx_status phx_gather_sum_device(phx_engine* e, int32_t family, const int64_t* i
   region_offsets(e->cfg, &off[0], &off[1], &off[2], &off[3], &off[4]);
   const phx_hash_family* fams[4] = {&e->cfg.user, &e->cfg.item, &e->cfg.author, &e->cfg.ip};
   PHX_CUDA_TRY(cudaEventRecord(e->ev0, e->stream), e->err);
-  phx_status s = gather_sum_launch(to_dev(*fams[family], (int)off[family]), e->table, e->table_rows, e->D,
+  if (!shards_complete(e)) return PHX_E_STATE;
+  phx_status s = gather_sum_launch(to_dev(*fams[family], (int)off[family]), table_view(e), e->D,
                                    (const long long*)ids_dev, n, (bf16*)out_dev, e->stream, e->err);
   if (s) return s;
   PHX_CUDA_TRY(cudaEventRecord(e->ev1, e->stream), e->err);
@@ -668,7 +735,7 @@ phx_status phx_gather_sum_device(phx_engine* e, int32_t family, const int64_t* i
 phx_status phx_user_tower_device(phx_engine* e, const phx_rank_batch* bd, float* users_dev) {
   if (!e || !bd || !users_dev) return PHX_E_ARG;
   if (bd->batch < 0 || bd->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
-  if (!params_complete(e, false)) return PHX_E_STATE;
+  if (!params_complete(e, false) || !shards_complete(e)) return PHX_E_STATE;
   cudaSetDevice(e->device);
   const int B = bd->batch;
   e->last_batch = B; e->last_launches = 0; e->prof_used = 0;

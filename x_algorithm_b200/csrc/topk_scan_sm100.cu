@@ -42,6 +42,20 @@ __device__ __forceinline__ void append_survivor(const TcScanArgs& a, int u, unsi
   if (slot < a.cap) a.surv[(size_t)u * a.cap + slot] = key;
 }
 
+// One survivor: stage it in the warp's shared-memory queue (the global append is an atomic whose result the store
+// depends on, a memory round trip per hit); when the queue is full (dense regime) append directly.
+__device__ __noinline__ void stage_hit(int* counts, unsigned long long* surv, int cap, uint4* queue, int* qcnt, int u,
+                                       float v, uint32_t global_row) {
+  const unsigned long long key = ((unsigned long long)ord32(round_bf(v)) << 32) | (unsigned long long)(0xFFFFFFFFu - global_row);
+  const int qs = atomicAdd(qcnt, 1);
+  if (qs < QCAP) {
+    queue[qs] = make_uint4((uint32_t)key, (uint32_t)(key >> 32), (uint32_t)u, 0u);
+  } else {
+    const int slot = atomicAdd(&counts[u], 1);
+    if (slot < cap) surv[(size_t)u * cap + slot] = key;
+  }
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 scan_tc_kernel(const __grid_constant__ CUtensorMap map_corpus, const __grid_constant__ CUtensorMap map_users,
@@ -157,24 +171,26 @@ scan_tc_kernel(const __grid_constant__ CUtensorMap map_corpus, const __grid_cons
         tmem_ld32(taddr + c * 32, r);
         const int u0 = half * 128 + c * 32;
         if (MODE == 1) {
+          // branch-free hit mask over the 32 columns, then the rare hits one by one: a taken branch per
+          // element (hit code laid out inline 32 times) made this loop instruction-fetch bound
+          uint32_t hits = 0;
 #pragma unroll
           for (int k4 = 0; k4 < 8; ++k4) {
             const float4 t4 = *reinterpret_cast<const float4*>(&s_thr[u0 + k4 * 4]);
-            const float tt[4] = {t4.x, t4.y, t4.z, t4.w};
+            hits |= (__uint_as_float(r[k4 * 4 + 0]) >= t4.x ? 1u : 0u) << (k4 * 4 + 0);
+            hits |= (__uint_as_float(r[k4 * 4 + 1]) >= t4.y ? 1u : 0u) << (k4 * 4 + 1);
+            hits |= (__uint_as_float(r[k4 * 4 + 2]) >= t4.z ? 1u : 0u) << (k4 * 4 + 2);
+            hits |= (__uint_as_float(r[k4 * 4 + 3]) >= t4.w ? 1u : 0u) << (k4 * 4 + 3);
+          }
+          if (!row_ok) hits = 0;
+          while (hits) {
+            const int k = __ffs(hits) - 1;
+            hits &= hits - 1;
+            uint32_t bits = 0;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float v = __uint_as_float(r[k4 * 4 + e]);
-              if (v >= tt[e] && row_ok) {
-                // stage the hit in the warp's shared-memory queue: the global append (an atomic whose result the
-                // store depends on) would stall the whole warp for a memory round trip per hit
-                const unsigned long long key = ((unsigned long long)ord32(round_bf(v)) << 32) |
-                                               (unsigned long long)(0xFFFFFFFFu - (uint32_t)(a.row_offset + row));
-                const int u = u0 + k4 * 4 + e;
-                const int qs = atomicAdd(&s_qcnt[ew], 1);
-                if (qs < QCAP) s_queue[ew * QCAP + qs] = make_uint4((uint32_t)key, (uint32_t)(key >> 32), (uint32_t)u, 0u);
-                else append_survivor(a, u, key);   // queue full (dense regime): append directly
-              }
-            }
+            for (int i = 0; i < 32; ++i) bits = (i == k) ? r[i] : bits;   // register select, no local memory
+            stage_hit(a.counts, a.surv, a.cap, s_queue + ew * QCAP, &s_qcnt[ew], u0 + k, __uint_as_float(bits),
+                      (uint32_t)(a.row_offset + row));
           }
         } else {
           const long long grp = w * 4 + quad;

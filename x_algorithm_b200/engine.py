@@ -86,6 +86,24 @@ class PhoenixEngine:
     def table_fill_synthetic(self, seed: int, amp: float):
         self._check(lib.phx_table_fill_synthetic(self._h, seed, amp))
 
+    # -- row-sharded table: export this engine's shard / map the others ---------------------------
+    def table_ipc_handle(self) -> bytes:
+        buf = (C.c_uint8 * 64)()
+        self._check(lib.phx_table_ipc_handle(self._h, buf))
+        return bytes(buf)
+
+    def table_attach_peer(self, rank: int, handle: bytes):
+        buf = (C.c_uint8 * 64).from_buffer_copy(handle)
+        self._check(lib.phx_table_attach_peer(self._h, rank, buf))
+
+    def table_local_ptr(self) -> int:
+        p = C.c_void_p()
+        self._check(lib.phx_table_local_ptr(self._h, C.byref(p)))
+        return int(p.value)
+
+    def table_attach_peer_ptr(self, rank: int, ptr: int):
+        self._check(lib.phx_table_attach_peer_ptr(self._h, rank, ptr))
+
     def set_blend(self, spec: _lib.BlendSpec):
         self._check(lib.phx_set_blend(self._h, C.byref(spec)))
         self._has_blend = True
