@@ -2,6 +2,7 @@
 
     python -m x_algorithm_b200.microbench gather  [--ids 4194304] [--log2-rows 25] [--width 256] [--hashes 4]
     python -m x_algorithm_b200.microbench topk    [--rows 12500000] [--dim 128] [--queries 256] [--k 1000]
+    torchrun --nproc-per-node N -m x_algorithm_b200.microbench retrieve [--rows 100000000] [--check]
     python -m x_algorithm_b200.microbench attention [--batch 64] [--heads 16] [--dh 128] [--hist 1024] [--cands 1024]
 
 gather: the multi-hash gather-sum workload (8 tables x 2^24 rows x 256 bf16 = 64 GiB, realised as the four hash
@@ -95,6 +96,63 @@ def bench_topk(a):
     sh.close()
 
 
+def bench_retrieve(a):
+    """Two-tower retrieval over a row-sharded corpus, one rank per GPU (launch with torchrun): per-shard fused
+    top-k -> NCCL all-gather of [B,k] (score, id) -> merge by (score desc, id asc).  --check also scans the whole
+    corpus on every rank and demands the identical answer."""
+    import torch
+    import torch.distributed as dist
+    from x_algorithm_b200.retrieval import CorpusShard, Retriever
+    from x_algorithm_b200.parallel import shard_range
+    hbm, tf, src = _peaks()
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lo, hi = shard_range(a.rows, world, rank)
+    sh = CorpusShard(hi - lo, a.dim, row_offset=lo, max_queries=a.queries, max_k=a.k, device=local)
+    sh.fill_synthetic(4)
+    rng = np.random.default_rng(5)
+    u = rng.standard_normal((a.queries, a.dim)).astype(np.float32)
+    u /= np.linalg.norm(u, axis=1, keepdims=True)
+    users = torch.from_numpy(u).cuda()
+    ret = Retriever([sh])
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for it in range(a.warmup + a.iters):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ev0.record()
+        sc, ids = ret.retrieve(users, a.k)
+        ev1.record()
+        torch.cuda.synchronize()
+        if it >= a.warmup:
+            times.append(ev0.elapsed_time(ev1))
+    t = torch.tensor([float(np.median(times))], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ok = None
+    if a.check:
+        full = CorpusShard(a.rows, a.dim, row_offset=0, max_queries=a.queries, max_k=a.k, device=local)
+        full.fill_synthetic(4)
+        s2 = torch.empty_like(sc); i2 = torch.empty_like(ids)
+        full.topk_device(users, a.queries, a.k, s2, i2)
+        full.sync()
+        ok = bool(torch.equal(ids, i2) and torch.equal(sc, s2))
+        full.close()
+    if rank == 0:
+        ms = float(t[0])
+        print(json.dumps(dict(op="retrieve_sharded", n_gpus=world, rows=a.rows, dim=a.dim, queries=a.queries, k=a.k, ms=ms,
+                              queries_per_s=a.queries / (ms * 1e-3), corpus_gbs_aggregate=a.rows * a.dim * 2 / (ms * 1e-3) / 1e9,
+                              peak_gbs_per_gpu=hbm, frac_of_aggregate_hbm=a.rows * a.dim * 2 / (ms * 1e-3) / 1e9 / (hbm * world),
+                              matches_unsharded=ok, peak_source=src)))
+    sh.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def bench_attention(a):
     import torch
     from x_algorithm_b200.engine import ranker_attention
@@ -119,7 +177,8 @@ def bench_attention(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gather", "topk", "attention"])
+    ap.add_argument("op", choices=["gather", "topk", "attention", "retrieve"])
+    ap.add_argument("--check", action="store_true")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--ids", type=int, default=1 << 22)
@@ -136,7 +195,7 @@ def main():
     ap.add_argument("--hist", type=int, default=1024)
     ap.add_argument("--cands", type=int, default=1024)
     a = ap.parse_args()
-    {"gather": bench_gather, "topk": bench_topk, "attention": bench_attention}[a.op](a)
+    {"gather": bench_gather, "topk": bench_topk, "attention": bench_attention, "retrieve": bench_retrieve}[a.op](a)
 
 
 if __name__ == "__main__":
