@@ -128,8 +128,8 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--table-log2", type=int, default=22, help="log2 buckets per hash region (smaller for profiling captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--tables", default="sharded", choices=["sharded", "replicated"],
-                    help="N > 1: row-shard the embedding table over the ranks (peer loads over NVLink) or replicate it")
+    ap.add_argument("--tables", default="replicated", choices=["sharded", "replicated"],
+                    help="N > 1: one full table per GPU (it fits: 17 GB) or row-sharded over the ranks with peer loads over NVLink")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -178,7 +178,11 @@ def main():
     torch.cuda.synchronize()
 
     def step(i):
+        # forward of batch i, then (sharded tables) the token gather of batch i+1 on the engine's side stream,
+        # which overlaps the forward just enqueued
         eng.rank_device(B, *dbatches[i % n_rot], lp, cont, sc)
+        if sharded:
+            eng.rank_prefetch_device(B, *dbatches[(i + 1) % n_rot])
 
     for i in range(args.warmup):
         step(i)

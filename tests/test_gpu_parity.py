@@ -222,6 +222,31 @@ def test_row_sharded_table_is_bit_identical(torch, monkeypatch):
         e.close()
 
 
+def test_token_prefetch_is_transparent(torch):
+    """forward(i); prefetch(i+1) pipelining gives bit-identical outputs to plain forwards, also when the prefetched
+    batch is not the one that follows (it is discarded)."""
+    ocfg, w, rows_fn, eng = make_pair(max_batch=4)
+    batches = [po.make_batch(ocfg, 4, seed=30 + i, ragged=True) for i in range(4)]
+    want = [eng.rank(to_inputs(b)).log_probs.copy() for b in batches]
+    dev = [[torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in
+            (b.hist_post_ids, b.hist_author_ids, b.hist_actions, b.hist_surfaces, b.cand_post_ids, b.cand_author_ids)]
+           for b in batches]
+    lp = torch.empty((4, ocfg.num_candidates, ocfg.num_actions), dtype=torch.float32, device="cuda")
+    cont = torch.empty((4, ocfg.num_candidates, 1), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    got = []
+    eng.rank_prefetch_device(4, *dev[0])
+    for i in range(4):
+        eng.rank_device(4, *dev[i], lp, cont)
+        nxt = (i + 1) % 4 if i != 1 else 3          # after batch 1 prefetch the wrong batch on purpose
+        eng.rank_prefetch_device(4, *dev[nxt])
+        eng.sync()
+        got.append(lp.cpu().numpy().copy())
+    for i in range(4):
+        np.testing.assert_array_equal(got[i], want[i])
+    eng.close()
+
+
 def test_engine_errors_are_statuses(torch):
     import x_algorithm_b200 as px
     with pytest.raises(px.PhoenixError) as ei:

@@ -63,6 +63,7 @@ SIGNATURES = {
     "phx_table_attach_peer_ptr": (C.c_int32, [_P, C.c_int32, _P]),
     "phx_rank_forward": (C.c_int32, [_P, C.POINTER(RankBatch), C.POINTER(RankOut)]),
     "phx_rank_forward_device": (C.c_int32, [_P, C.POINTER(RankBatch), C.POINTER(RankOut)]),
+    "phx_rank_prefetch_device": (C.c_int32, [_P, C.POINTER(RankBatch)]),
     "phx_sync": (C.c_int32, [_P]),
     "phx_last_device_ms": (C.c_int32, [_P, C.POINTER(C.c_float)]),
     "phx_last_launch_count": (C.c_int32, [_P, C.POINTER(C.c_int32)]),

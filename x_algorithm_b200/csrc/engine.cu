@@ -7,6 +7,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <map>
 #include <mutex>
 #include <vector>
@@ -95,6 +96,16 @@ struct phx_engine {
   size_t in_stage_bytes = 0;
   float* lp_dev = nullptr; float* cont_dev = nullptr; double* score_dev = nullptr;
   float* lp_host = nullptr; float* cont_host = nullptr; double* score_host = nullptr;
+
+  // token prefetch (phx_rank_prefetch_device): tokens of the next batch are built on a side stream into the
+  // alternate residual buffer while the current forward runs
+  cudaStream_t side_stream = nullptr;
+  cudaEvent_t ev_prefetch = nullptr;
+  cudaEvent_t ev_done[2] = {nullptr, nullptr};   // ends of the last two forwards; done_idx = the most recent
+  int done_idx = 0;
+  bf16* x_alt = nullptr; int* seg_alt = nullptr;
+  bool prefetch_valid = false;
+  phx_rank_batch prefetch_key;
 
   int last_batch = 0;
   int last_launches = 0;
@@ -301,7 +312,8 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len) {
   return PHX_OK;
 }
 
-phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc) {
+phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc, bf16* x_dst = nullptr, int* seg_dst = nullptr,
+                        cudaStream_t stream = nullptr) {
   long long ou, oi, oa, oip, tot;
   region_offsets(e->cfg, &ou, &oi, &oa, &oip, &tot);
   TokenBuildArgs ta;
@@ -314,8 +326,9 @@ phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc) 
   ta.item = to_dev(e->cfg.item, (int)oi); ta.author = to_dev(e->cfg.author, (int)oa);
   ta.B = B; ta.S = e->S; ta.C = Cc; ta.D = e->D;
   ta.input_scale = sqrtf((float)e->D);  // scaling.py:40-41
-  ta.x = e->x; ta.tokens = e->debug_taps ? e->tokens : nullptr; ta.hashes = e->debug_taps ? e->hashes : nullptr;
-  ta.seg = e->seg;
+  ta.x = x_dst ? x_dst : e->x; ta.tokens = e->debug_taps ? e->tokens : nullptr; ta.hashes = e->debug_taps ? e->hashes : nullptr;
+  ta.seg = seg_dst ? seg_dst : e->seg;
+  if (stream) return build_tokens_launch(ta, stream, e->err);   // prefetch on the side stream: not profiled
   e->last_launches++;
   ProfScope ps(e, KC_TOKENS);
   return build_tokens_launch(ta, e->stream, e->err);
@@ -450,7 +463,7 @@ void phx_engine_destroy(phx_engine* e) {
     fr(L.w_qkv_t); fr(L.w_out_t); fr(L.w_up_t); fr(L.w_down_t);
   }
   fr(e->cos_tab); fr(e->sin_tab); fr(e->x); fr(e->hbuf); fr(e->qkv); fr(e->attn); fr(e->ffn); fr(e->tmp); fr(e->tokens);
-  fr(e->seg); fr(e->hashes); fr(e->err_flag); fr(e->in_stage_dev); fr(e->lp_dev); fr(e->cont_dev); fr(e->score_dev);
+  fr(e->x_alt); fr(e->seg_alt); fr(e->seg); fr(e->hashes); fr(e->err_flag); fr(e->in_stage_dev); fr(e->lp_dev); fr(e->cont_dev); fr(e->score_dev);
   if (e->in_stage_host) cudaFreeHost(e->in_stage_host);
   if (e->lp_host) cudaFreeHost(e->lp_host);
   if (e->cont_host) cudaFreeHost(e->cont_host);
@@ -459,6 +472,9 @@ void phx_engine_destroy(phx_engine* e) {
   if (e->ev1) cudaEventDestroy(e->ev1);
   for (auto& pe : e->prof_events) { cudaEventDestroy(pe.second.first); cudaEventDestroy(pe.second.second); }
   for (auto m : e->marks) if (m) cudaEventDestroy(m);
+  if (e->ev_prefetch) cudaEventDestroy(e->ev_prefetch);
+  for (auto d : e->ev_done) if (d) cudaEventDestroy(d);
+  if (e->side_stream) cudaStreamDestroy(e->side_stream);
   if (e->stream) cudaStreamDestroy(e->stream);
   delete e;
 }
@@ -584,7 +600,16 @@ phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* bd, cons
   if (B == 0) return PHX_OK;
   PHX_CUDA_TRY(cudaEventRecord(e->ev0, e->stream), e->err);
   phx_status s;
-  if ((s = build_tokens(e, bd, B, e->C))) return s;
+  if (e->prefetch_valid && memcmp(&e->prefetch_key, bd, sizeof(*bd)) == 0) {
+    // tokens of this batch were built ahead of time: adopt the alternate buffers
+    PHX_CUDA_TRY(cudaStreamWaitEvent(e->stream, e->ev_prefetch, 0), e->err);
+    std::swap(e->x, e->x_alt);
+    std::swap(e->seg, e->seg_alt);
+    e->prefetch_valid = false;
+  } else {
+    e->prefetch_valid = false;
+    if ((s = build_tokens(e, bd, B, e->C))) return s;
+  }
   if ((s = run_trunk(e, B, e->T, e->S, e->S))) return s;
   HeadsArgs ha;
   ha.x = e->x; ha.final_gain = e->final_norm; ha.unembed_t = e->unembed_t;
@@ -597,6 +622,33 @@ phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* bd, cons
   { ProfScope ps(e, KC_HEADS); if ((s = heads_launch(ha, e->stream, e->err))) return s; }
   e->last_launches++;
   PHX_CUDA_TRY(cudaEventRecord(e->ev1, e->stream), e->err);
+  if (e->ev_done[0]) { e->done_idx ^= 1; PHX_CUDA_TRY(cudaEventRecord(e->ev_done[e->done_idx], e->stream), e->err); }
+  return PHX_OK;
+}
+
+phx_status phx_rank_prefetch_device(phx_engine* e, const phx_rank_batch* bd) {
+  if (!e || !bd) return PHX_E_ARG;
+  if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
+  if (bd->batch <= 0 || bd->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
+  if (!params_complete(e, true) || !shards_complete(e)) return PHX_E_STATE;
+  cudaSetDevice(e->device);
+  if (!e->side_stream) {
+    PHX_CUDA_TRY(cudaStreamCreateWithFlags(&e->side_stream, cudaStreamNonBlocking), e->err);
+    PHX_CUDA_TRY(cudaEventCreateWithFlags(&e->ev_prefetch, cudaEventDisableTiming), e->err);
+    for (int i = 0; i < 2; ++i) PHX_CUDA_TRY(cudaEventCreateWithFlags(&e->ev_done[i], cudaEventDisableTiming), e->err);
+    PHX_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&e->x_alt), (size_t)e->max_tokens * e->D * sizeof(bf16)), e->err);
+    PHX_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&e->seg_alt), (size_t)e->max_tokens * sizeof(int)), e->err);
+    for (int i = 0; i < 2; ++i) PHX_CUDA_TRY(cudaEventRecord(e->ev_done[i], e->stream), e->err);
+  }
+  // Call order per step: forward(batch i), then prefetch(batch i+1).  The alternate buffers were the working
+  // buffers of forward(i-1); the side stream waits for THAT forward's end (the event before the most recent one),
+  // not for forward(i), so the gather overlaps forward(i).
+  PHX_CUDA_TRY(cudaStreamWaitEvent(e->side_stream, e->ev_done[e->done_idx ^ 1], 0), e->err);
+  phx_status s = build_tokens(e, bd, bd->batch, e->C, e->x_alt, e->seg_alt, e->side_stream);
+  if (s) return s;
+  PHX_CUDA_TRY(cudaEventRecord(e->ev_prefetch, e->side_stream), e->err);
+  e->prefetch_key = *bd;
+  e->prefetch_valid = true;
   return PHX_OK;
 }
 

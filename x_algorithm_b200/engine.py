@@ -137,6 +137,12 @@ class PhoenixEngine:
         o = _lib.RankOut(_ptr(lp), _ptr(cont), _ptr(sc))
         self._check(lib.phx_rank_forward_device(self._h, C.byref(b), C.byref(o)))
 
+    def rank_prefetch_device(self, B, hp, ha, act, srf, cp, ca):
+        """Build the tokens of the batch the next rank_device call will carry, on a side stream (overlaps the
+        forward enqueued right after this call; matters when the table is row-sharded over GPUs)."""
+        b = self._batch_struct(B, hp, ha, act, srf, cp, ca)
+        self._check(lib.phx_rank_prefetch_device(self._h, C.byref(b)))
+
     def user_tower_device(self, B, hp, ha, act, srf, users):
         b = self._batch_struct(B, hp, ha, act, srf, None, None)
         self._check(lib.phx_user_tower_device(self._h, C.byref(b), _ptr(users)))
