@@ -247,6 +247,24 @@ def test_token_prefetch_is_transparent(torch):
     eng.close()
 
 
+def test_fused_rmsnorm_matches_separate_kernels(torch, monkeypatch):
+    """RMSNorm folded into the GEMMs (gain in the weights, 1/rms applied in the epilogue from row statistics the
+    previous GEMM left behind) against the stand-alone norm kernels: same forward up to bf16 rounding noise, and
+    both within tolerance of the oracle."""
+    ocfg, w, rows_fn, eng = make_pair(max_batch=4, emb_size=256, num_q_heads=4, num_kv_heads=4, key_size=64,
+                                      history_len=40, num_candidates=24, num_layers=3)
+    b = po.make_batch(ocfg, 4, seed=12, ragged=True)
+    fused = eng.rank(to_inputs(b)); eng.close()
+    monkeypatch.setenv("PHX_NORM", "separate")
+    ocfg, w, rows_fn, eng2 = make_pair(max_batch=4, emb_size=256, num_q_heads=4, num_kv_heads=4, key_size=64,
+                                       history_len=40, num_candidates=24, num_layers=3)
+    sep = eng2.rank(to_inputs(b)); eng2.close()
+    lp, cont, _ = po.rank_forward(ocfg, w, rows_fn, b)
+    valid = b.cand_post_ids != 0
+    assert rel_l2(fused.log_probs[valid], sep.log_probs[valid]) < 5e-3
+    assert rel_l2(fused.log_probs[valid], lp[valid]) < TOL and rel_l2(sep.log_probs[valid], lp[valid]) < TOL
+
+
 def test_engine_errors_are_statuses(torch):
     import x_algorithm_b200 as px
     with pytest.raises(px.PhoenixError) as ei:

@@ -66,6 +66,18 @@ struct GemmRope {
   int group, g;
 };
 
+// RMSNorm folded around a GEMM.  Consumer side (ss_in): the A rows are the raw residual stream, the norm's gain is
+// folded into the weights, and the epilogue scales row r by rsqrt(sum_t ss_in[r][t] / D + eps) before rounding
+// (x rstd g) W = rstd (x (g W)).  Producer side (ss_out, residual epilogue): the sum of squares of each new bf16
+// residual row is left in ss_out[r][column slab] for the next consumer - one slot per 64-column slab, no atomics,
+// so the statistics are deterministic.
+struct GemmNorm {
+  const float* ss_in;
+  float* ss_out;
+  int slots_in;
+  float inv_d, eps;
+};
+
 // One GEMM problem bound to fixed buffers: C[M,N] = epi(A[M,K] @ Wt[N,K]^T).  The tensor maps
 // are encoded once for (pointer, rows_max) and reused for every M <= rows_max.
 struct GemmPlan {
@@ -88,8 +100,9 @@ phx_status gemm_plan_create(GemmPlan* plan, const bf16* A, const bf16* Wt, int64
                             bool narrow_tiles, std::string& err);
 // Launch on `stream`.  `R` is the residual (EPI_RESIDUAL) or null.  `err_flag` is a device int the
 // kernel sets to 1 when a bounded wait ran out.
-phx_status gemm_launch(GemmPlan& plan, bf16* C, const bf16* R, int64_t M, int epilogue, const GemmRope* rope,
-                       int* err_flag, int num_sms, cudaStream_t stream, std::string& err);
+phx_status gemm_launch(GemmPlan& plan, const bf16* A, bf16* C, const bf16* R, int64_t M, int epilogue,
+                       const GemmRope* rope, const GemmNorm* norm, int* err_flag, int num_sms, cudaStream_t stream,
+                       std::string& err);
 // Plain SIMT GEMM with the same epilogues (debug / cross-check path, selected by PHX_GEMM=simt).
 phx_status gemm_simt_launch(const bf16* A, const bf16* Wt, bf16* C, const bf16* R, int64_t M, int N, int K,
                             int epilogue, cudaStream_t stream, std::string& err);
@@ -140,6 +153,8 @@ struct TokenBuildArgs {
   int B, S, C, D;
   float input_scale;
   bf16* x;         // [B,T,D] scaled tokens
+  float* row_ss;   // optional [B*T, ss_slots]: sum of squares of each x row in slot 0, zeros in the others
+  int ss_slots;
   bf16* tokens;    // optional [B,T,D] unscaled gather-sum output
   int* hashes;     // optional [B,T,2H]
   int* seg;        // [B,T] 1 / -1 / 0
@@ -158,6 +173,8 @@ phx_status corpus_fill_launch(bf16* rows_ptr, long long global_row0, long long r
 // y = bf16(norm(x) * gain); with `res` non-null y = bf16(res + bf16(norm(x) * gain)).  y may alias x or res.
 phx_status rmsnorm_launch(const bf16* x, const float* gain, bf16* y, const bf16* res, long long rows, int D, float eps,
                           cudaStream_t stream, std::string& err);
+phx_status fold_gain_launch(const bf16* w_t, const float* gain, bf16* out, int N, int K, cudaStream_t stream,
+                            std::string& err);
 struct QkNormRopeArgs {
   bf16* qkv;             // [M, qkv_width], merged layout per kv group [q_0..q_{g-1}, k, v]
   long long M;

@@ -96,7 +96,22 @@ __global__ void __launch_bounds__(256) qknorm_rope_kernel(QkNormRopeArgs a) {
   }
 }
 
+// out[n][k] = bf16(w_t[n][k] * gain[k]): a norm's gain folded into the K-major weight of the GEMM that follows it
+__global__ void fold_gain_kernel(const bf16* __restrict__ w_t, const float* __restrict__ gain, bf16* __restrict__ out,
+                                 long long total, int K) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+    out[i] = f2bf(bf2f(w_t[i]) * gain[i % K]);
+}
+
 }  // namespace
+
+phx_status fold_gain_launch(const bf16* w_t, const float* gain, bf16* out, int N, int K, cudaStream_t stream,
+                            std::string& err) {
+  const long long total = (long long)N * K;
+  fold_gain_kernel<<<(unsigned)((total + 255) / 256 > 4096 ? 4096 : (total + 255) / 256), 256, 0, stream>>>(w_t, gain, out, total, K);
+  PHX_CUDA_TRY(cudaGetLastError(), err);
+  return PHX_OK;
+}
 
 phx_status rmsnorm_launch(const bf16* x, const float* gain, bf16* y, const bf16* res, long long rows, int D, float eps,
                           cudaStream_t stream, std::string& err) {

@@ -64,12 +64,18 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
     act = act < 0 ? 0 : (act > a.num_action_types ? a.num_action_types : act);
     srf = srf < 0 ? 0 : (srf > a.num_surfaces ? a.num_surfaces : srf);
   }
+  // every lane takes part in these shuffles (lanes whose column chunk lies past D skip the loop below, so a
+  // shuffle inside the loop would leave the warp split across two different shuffle instructions)
+  const bf16* rowp[2 * PHX_MAX_HASHES];
+#pragma unroll
+  for (int j = 0; j < 2 * PHX_MAX_HASHES; ++j)
+    rowp[j] = a.table.row_ptr(__shfl_sync(0xffffffffu, my_idx, j < 2 * H ? j : 0), a.D);
+  float row_ss = 0.f;
   for (int col = lane * 8; col < a.D; col += 256) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int j = 0; j < 2 * H; ++j) {
-      const long long idx = __shfl_sync(0xffffffffu, my_idx, j);
-      acc_row(acc, a.table.row_ptr(idx, a.D), col);
-    }
+#pragma unroll
+    for (int j = 0; j < 2 * PHX_MAX_HASHES; ++j)
+      if (j < 2 * H) acc_row(acc, rowp[j], col);
     if (is_hist) {
       acc_row(acc, a.action_table + (long long)act * a.D, col);
       acc_row(acc, a.surface_table + (long long)srf * a.D, col);
@@ -81,9 +87,14 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
     }
     float s[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) s[i] = round_bf(acc[i]) * a.input_scale;
+    for (int i = 0; i < 8; ++i) { s[i] = round_bf(round_bf(acc[i]) * a.input_scale); row_ss += s[i] * s[i]; }
     o.x = pack_bf2(s[0], s[1]); o.y = pack_bf2(s[2], s[3]); o.z = pack_bf2(s[4], s[5]); o.w = pack_bf2(s[6], s[7]);
     *reinterpret_cast<uint4*>(a.x + tok * a.D + col) = o;
+  }
+  if (a.row_ss) {   // statistics of the bf16 row for the first fused RMSNorm
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) row_ss += __shfl_xor_sync(0xffffffffu, row_ss, o);
+    if (lane < a.ss_slots) a.row_ss[tok * a.ss_slots + lane] = (lane == 0) ? row_ss : 0.f;
   }
 }
 

@@ -44,11 +44,14 @@ struct Layer {
   float* post_ffn_norm = nullptr;
   float* q_norm = nullptr;
   float* k_norm = nullptr;
+  bf16* w_qkv_f = nullptr;   // [QW, D] with the pre-attention norm gain folded in
+  bf16* w_up_f = nullptr;    // [F, D] with the pre-FFN norm gain folded in
   bf16* w_qkv_t = nullptr;   // [QW, D]
   bf16* w_out_t = nullptr;   // [D, HD]
   bf16* w_up_t = nullptr;    // [F, D]
   bf16* w_down_t = nullptr;  // [D, F]
   GemmPlan p_qkv, p_out, p_up, p_down;
+  GemmPlan p_qkv_f, p_up_f;  // fused-norm variants: A = residual stream, folded weights
 };
 
 }  // namespace phx
@@ -88,6 +91,10 @@ struct phx_engine {
   // work space
   bf16 *x = nullptr, *hbuf = nullptr, *qkv = nullptr, *attn = nullptr, *ffn = nullptr, *tmp = nullptr, *tokens = nullptr;
   int* seg = nullptr;
+  float* rowss_a = nullptr;  // [tokens, D/64] sum-of-squares partials of the rows entering the attention block
+  float* rowss_f = nullptr;  // ... entering the FFN block
+  bool fused_norm = false;   // RMSNorm folded into the GEMMs (no primer norm, no qk-norm-before-fusion issue, tcgen05 path)
+  bool folded_dirty = true;
   int* hashes = nullptr;
   int* err_flag = nullptr;
   // staging for the host-buffer entry point
@@ -103,13 +110,14 @@ struct phx_engine {
   cudaEvent_t ev_prefetch = nullptr;
   cudaEvent_t ev_done[2] = {nullptr, nullptr};   // ends of the last two forwards; done_idx = the most recent
   int done_idx = 0;
-  bf16* x_alt = nullptr; int* seg_alt = nullptr;
+  bf16* x_alt = nullptr; int* seg_alt = nullptr; float* rowss_a_alt = nullptr;
   bool prefetch_valid = false;
   phx_rank_batch prefetch_key;
 
   int last_batch = 0;
   int last_launches = 0;
   bool debug_taps = false;
+  bool sync_debug = false;
 
   // optional per-kernel-class timing (phx_profile_enable): events around every launch
   bool profile = false;
@@ -122,7 +130,7 @@ namespace {
 enum KernelClass { KC_TOKENS = 0, KC_NORM = 1, KC_GEMM = 2, KC_ROPE = 3, KC_ATTN = 4, KC_HEADS = 5, KC_COUNT = 6 };
 struct ProfScope {
   phx_engine* e; cudaEvent_t stop = nullptr;
-  ProfScope(phx_engine* e_, int cls) : e(e_) {
+  ProfScope(phx_engine* e_, int cls) : e(e_), cls_(cls) {
     if (!e->profile) return;
     if (e->prof_used == e->prof_events.size()) {
       cudaEvent_t a, b; cudaEventCreate(&a); cudaEventCreate(&b);
@@ -133,7 +141,15 @@ struct ProfScope {
     cudaEventRecord(pe.second.first, e->stream);
     stop = pe.second.second;
   }
-  ~ProfScope() { if (stop) cudaEventRecord(stop, e->stream); }
+  ~ProfScope() {
+    if (stop) cudaEventRecord(stop, e->stream);
+    if (e->sync_debug) {   // PHX_SYNC_DEBUG=1: find the launch an asynchronous error belongs to
+      cudaError_t ce = cudaStreamSynchronize(e->stream);
+      if (ce != cudaSuccess)
+        fprintf(stderr, "[phx sync-debug] launch #%d (kernel class %d): %s\n", e->last_launches, cls_, cudaGetErrorString(ce));
+    }
+  }
+  int cls_ = -1;
 };
 }  // namespace
 
@@ -223,12 +239,24 @@ phx_status upload_bf16(phx_engine* e, bf16** dst, const float* host, int64_t row
   return PHX_OK;
 }
 
-phx_status do_gemm(phx_engine* e, GemmPlan& p, bf16* Cc, const bf16* R, int64_t M, int epi,
-                   const GemmRope* rope = nullptr) {
+phx_status do_gemm(phx_engine* e, GemmPlan& p, const bf16* A, bf16* Cc, const bf16* R, int64_t M, int epi,
+                   const GemmRope* rope = nullptr, const GemmNorm* norm = nullptr) {
   ProfScope ps(e, KC_GEMM);
   e->last_launches++;
-  if (e->use_simt_gemm) return gemm_simt_launch(p.A, p.Wt, Cc, R, M, p.N, p.K, epi, e->stream, e->err);
-  return gemm_launch(p, Cc, R, M, epi, rope, e->err_flag, e->num_sms, e->stream, e->err);
+  if (e->use_simt_gemm) return gemm_simt_launch(A, p.Wt, Cc, R, M, p.N, p.K, epi, e->stream, e->err);
+  return gemm_launch(p, A, Cc, R, M, epi, rope, norm, e->err_flag, e->num_sms, e->stream, e->err);
+}
+
+// fold the norm gains into the weights of the GEMMs that consume the normed rows (after any parameter reload)
+phx_status refresh_folded(phx_engine* e) {
+  if (!e->fused_norm || !e->folded_dirty) return PHX_OK;
+  for (auto& L : e->layers) {
+    phx_status s;
+    if ((s = fold_gain_launch(L.w_qkv_t, L.pre_attn_norm, L.w_qkv_f, e->QW, e->D, e->stream, e->err))) return s;
+    if ((s = fold_gain_launch(L.w_up_t, L.pre_ffn_norm, L.w_up_f, e->F, e->D, e->stream, e->err))) return s;
+  }
+  e->folded_dirty = false;
+  return PHX_OK;
 }
 
 bool params_complete(phx_engine* e, bool need_heads) {
@@ -256,18 +284,29 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len) {
   phx_status s;
   for (int l = 0; l < c.num_layers; ++l) {
     Layer& L = e->layers[l];
-    { ProfScope ps(e, KC_NORM);
-    if ((s = rmsnorm_launch(e->x, L.pre_attn_norm, e->hbuf, nullptr, M, e->D, c.rms_eps, e->stream, e->err))) return s; }
-    e->last_launches++;
+    const bool fused = e->fused_norm;
+    const int slots = e->D / 64;
+    GemmNorm n_attn_in = {e->rowss_a, nullptr, slots, 1.0f / (float)e->D, c.rms_eps};   // consume stats of x -> QKV
+    GemmNorm n_attn_out = {nullptr, e->rowss_f, 0, 0.f, 0.f};                           // out-proj leaves stats for the FFN
+    GemmNorm n_ffn_in = {e->rowss_f, nullptr, slots, 1.0f / (float)e->D, c.rms_eps};
+    GemmNorm n_ffn_out = {nullptr, e->rowss_a, 0, 0.f, 0.f};                            // down-proj leaves stats for the next layer
+    if (!fused) {
+      { ProfScope ps(e, KC_NORM);
+      if ((s = rmsnorm_launch(e->x, L.pre_attn_norm, e->hbuf, nullptr, M, e->D, c.rms_eps, e->stream, e->err))) return s; }
+      e->last_launches++;
+    }
+    GemmPlan& pq = fused ? L.p_qkv_f : L.p_qkv;
+    GemmPlan& pu = fused ? L.p_up_f : L.p_up;
+    const bf16* a_in = fused ? e->x : e->hbuf;
     // RoPE rides in the QKV epilogue unless qk-norm has to run first or the head dim is 128
     const bool fuse_rope = c.rotary && !c.qk_norm && !e->use_simt_gemm && (e->dh == 32 || e->dh == 64);
     if (fuse_rope) {
       GemmRope gr;
       gr.cos_tab = e->cos_tab; gr.sin_tab = e->sin_tab; gr.T = Tt; gr.pos_cap = pos_cap; gr.dh = e->dh;
       gr.g = e->Hq / e->Hkv; gr.group = gr.g + 2;
-      if ((s = do_gemm(e, L.p_qkv, e->qkv, nullptr, M, EPI_ROPE, &gr))) return s;
+      if ((s = do_gemm(e, pq, a_in, e->qkv, nullptr, M, EPI_ROPE, &gr, fused ? &n_attn_in : nullptr))) return s;
     } else {
-      if ((s = do_gemm(e, L.p_qkv, e->qkv, nullptr, M, EPI_STORE))) return s;
+      if ((s = do_gemm(e, pq, a_in, e->qkv, nullptr, M, EPI_STORE, nullptr, fused ? &n_attn_in : nullptr))) return s;
     }
     if (!fuse_rope && (c.rotary || c.qk_norm)) {
       QkNormRopeArgs qa;
@@ -292,28 +331,30 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len) {
     e->last_launches++;
     if (c.primer_norm) {
       // x = x + post_attn_norm(out(attn)) (transformer.py:531-541)
-      if ((s = do_gemm(e, L.p_out, e->tmp, nullptr, M, EPI_STORE))) return s;
+      if ((s = do_gemm(e, L.p_out, e->attn, e->tmp, nullptr, M, EPI_STORE))) return s;
       { ProfScope ps(e, KC_NORM); if ((s = rmsnorm_launch(e->tmp, L.post_attn_norm, e->x, e->x, M, e->D, c.rms_eps, e->stream, e->err))) return s; }
       e->last_launches++;
     } else {
-      if ((s = do_gemm(e, L.p_out, e->x, e->x, M, EPI_RESIDUAL))) return s;
+      if ((s = do_gemm(e, L.p_out, e->attn, e->x, e->x, M, EPI_RESIDUAL, nullptr, fused ? &n_attn_out : nullptr))) return s;
     }
-    { ProfScope ps(e, KC_NORM); if ((s = rmsnorm_launch(e->x, L.pre_ffn_norm, e->hbuf, nullptr, M, e->D, c.rms_eps, e->stream, e->err))) return s; }
-    e->last_launches++;
-    if ((s = do_gemm(e, L.p_up, e->ffn, nullptr, M, EPI_GELU))) return s;
+    if (!fused) {
+      { ProfScope ps(e, KC_NORM); if ((s = rmsnorm_launch(e->x, L.pre_ffn_norm, e->hbuf, nullptr, M, e->D, c.rms_eps, e->stream, e->err))) return s; }
+      e->last_launches++;
+    }
+    if ((s = do_gemm(e, pu, a_in, e->ffn, nullptr, M, EPI_GELU, nullptr, fused ? &n_ffn_in : nullptr))) return s;
     if (c.primer_norm) {
-      if ((s = do_gemm(e, L.p_down, e->tmp, nullptr, M, EPI_STORE))) return s;
+      if ((s = do_gemm(e, L.p_down, e->ffn, e->tmp, nullptr, M, EPI_STORE))) return s;
       { ProfScope ps(e, KC_NORM); if ((s = rmsnorm_launch(e->tmp, L.post_ffn_norm, e->x, e->x, M, e->D, c.rms_eps, e->stream, e->err))) return s; }
       e->last_launches++;
     } else {
-      if ((s = do_gemm(e, L.p_down, e->x, e->x, M, EPI_RESIDUAL))) return s;
+      if ((s = do_gemm(e, L.p_down, e->ffn, e->x, e->x, M, EPI_RESIDUAL, nullptr, fused ? &n_ffn_out : nullptr))) return s;
     }
   }
   return PHX_OK;
 }
 
 phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc, bf16* x_dst = nullptr, int* seg_dst = nullptr,
-                        cudaStream_t stream = nullptr) {
+                        cudaStream_t stream = nullptr, float* ss_dst = nullptr) {
   long long ou, oi, oa, oip, tot;
   region_offsets(e->cfg, &ou, &oi, &oa, &oip, &tot);
   TokenBuildArgs ta;
@@ -328,6 +369,8 @@ phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc, 
   ta.input_scale = sqrtf((float)e->D);  // scaling.py:40-41
   ta.x = x_dst ? x_dst : e->x; ta.tokens = e->debug_taps ? e->tokens : nullptr; ta.hashes = e->debug_taps ? e->hashes : nullptr;
   ta.seg = seg_dst ? seg_dst : e->seg;
+  ta.row_ss = e->fused_norm ? (ss_dst ? ss_dst : e->rowss_a) : nullptr;
+  ta.ss_slots = e->D / 64;
   if (stream) return build_tokens_launch(ta, stream, e->err);   // prefetch on the side stream: not profiled
   e->last_launches++;
   ProfScope ps(e, KC_TOKENS);
@@ -369,6 +412,7 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
   e->use_simt_gemm = gi && strcmp(gi, "simt") == 0;
   const char* dt = getenv("PHX_DEBUG_TAPS");
   e->debug_taps = dt && dt[0] == '1';
+  { const char* sd = getenv("PHX_SYNC_DEBUG"); e->sync_debug = sd && sd[0] == '1'; }
   e->D = cfg->emb_size; e->S = cfg->history_len; e->C = cfg->num_candidates; e->T = e->S + e->C;
   e->Hq = cfg->num_q_heads; e->Hkv = cfg->num_kv_heads; e->dh = cfg->key_size; e->F = cfg->ffn_size;
   e->QW = (e->Hq + 2 * e->Hkv) * e->dh; e->HD = e->Hq * e->dh; e->V = cfg->num_actions; e->NC = cfg->num_continuous;
@@ -395,6 +439,14 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
   TRY(dev_alloc(e, &e->attn, (size_t)M * e->HD));
   TRY(dev_alloc(e, &e->ffn, (size_t)M * e->F));
   TRY(dev_alloc(e, &e->seg, (size_t)M));
+  {
+    const char* nf = getenv("PHX_NORM");
+    e->fused_norm = !cfg->primer_norm && !e->use_simt_gemm && !(nf && strcmp(nf, "separate") == 0);
+    if (e->fused_norm) {
+      TRY(dev_alloc(e, &e->rowss_a, (size_t)M * (e->D / 64)));
+      TRY(dev_alloc(e, &e->rowss_f, (size_t)M * (e->D / 64)));
+    }
+  }
   if (cfg->primer_norm) TRY(dev_alloc(e, &e->tmp, (size_t)M * e->D));
   if (e->debug_taps) {
     TRY(dev_alloc(e, &e->tokens, (size_t)M * e->D));
@@ -426,6 +478,12 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
     TRY(dev_alloc(e, &L.w_up_t, (size_t)e->F * e->D));
     TRY(dev_alloc(e, &L.w_down_t, (size_t)e->D * e->F));
     TRY(gemm_plan_create(&L.p_qkv, e->hbuf, L.w_qkv_t, M, e->QW, e->D, false, e->err));
+    if (e->fused_norm) {
+      TRY(dev_alloc(e, &L.w_qkv_f, (size_t)e->QW * e->D));
+      TRY(dev_alloc(e, &L.w_up_f, (size_t)e->F * e->D));
+      TRY(gemm_plan_create(&L.p_qkv_f, e->x, L.w_qkv_f, M, e->QW, e->D, false, e->err));
+      TRY(gemm_plan_create(&L.p_up_f, e->x, L.w_up_f, M, e->F, e->D, false, e->err));
+    }
     TRY(gemm_plan_create(&L.p_out, e->attn, L.w_out_t, M, e->D, e->HD, e->HD <= 1024 && !cfg->primer_norm, e->err));
     TRY(gemm_plan_create(&L.p_up, e->hbuf, L.w_up_t, M, e->F, e->D, false, e->err));
     TRY(gemm_plan_create(&L.p_down, e->ffn, L.w_down_t, M, e->D, e->F, false, e->err));
@@ -460,10 +518,10 @@ void phx_engine_destroy(phx_engine* e) {
   fr(e->table); fr(e->action_table); fr(e->surface_table); fr(e->final_norm); fr(e->unembed_t);
   for (auto& L : e->layers) {
     fr(L.pre_attn_norm); fr(L.pre_ffn_norm); fr(L.post_attn_norm); fr(L.post_ffn_norm); fr(L.q_norm); fr(L.k_norm);
-    fr(L.w_qkv_t); fr(L.w_out_t); fr(L.w_up_t); fr(L.w_down_t);
+    fr(L.w_qkv_t); fr(L.w_out_t); fr(L.w_up_t); fr(L.w_down_t); fr(L.w_qkv_f); fr(L.w_up_f);
   }
   fr(e->cos_tab); fr(e->sin_tab); fr(e->x); fr(e->hbuf); fr(e->qkv); fr(e->attn); fr(e->ffn); fr(e->tmp); fr(e->tokens);
-  fr(e->x_alt); fr(e->seg_alt); fr(e->seg); fr(e->hashes); fr(e->err_flag); fr(e->in_stage_dev); fr(e->lp_dev); fr(e->cont_dev); fr(e->score_dev);
+  fr(e->x_alt); fr(e->seg_alt); fr(e->rowss_a_alt); fr(e->rowss_a); fr(e->rowss_f); fr(e->seg); fr(e->hashes); fr(e->err_flag); fr(e->in_stage_dev); fr(e->lp_dev); fr(e->cont_dev); fr(e->score_dev);
   if (e->in_stage_host) cudaFreeHost(e->in_stage_host);
   if (e->lp_host) cudaFreeHost(e->lp_host);
   if (e->cont_host) cudaFreeHost(e->cont_host);
@@ -521,7 +579,7 @@ phx_status phx_load_param(phx_engine* e, const char* name, const float* host, in
     else if (f == "w_down") { if (!shape(e->F, e->D)) return PHX_E_ARG; s = upload_bf16(e, &L.w_down_t, host, rows, cols, true); }
     else { e->err = "unknown parameter " + n; return PHX_E_ARG; }
   } else { e->err = "unknown parameter " + n; return PHX_E_ARG; }
-  if (s == PHX_OK) e->loaded[n] = true;
+  if (s == PHX_OK) { e->loaded[n] = true; e->folded_dirty = true; }
   return s;
 }
 
@@ -600,11 +658,13 @@ phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* bd, cons
   if (B == 0) return PHX_OK;
   PHX_CUDA_TRY(cudaEventRecord(e->ev0, e->stream), e->err);
   phx_status s;
+  if ((s = refresh_folded(e))) return s;
   if (e->prefetch_valid && memcmp(&e->prefetch_key, bd, sizeof(*bd)) == 0) {
     // tokens of this batch were built ahead of time: adopt the alternate buffers
     PHX_CUDA_TRY(cudaStreamWaitEvent(e->stream, e->ev_prefetch, 0), e->err);
     std::swap(e->x, e->x_alt);
     std::swap(e->seg, e->seg_alt);
+    std::swap(e->rowss_a, e->rowss_a_alt);
     e->prefetch_valid = false;
   } else {
     e->prefetch_valid = false;
@@ -638,13 +698,14 @@ phx_status phx_rank_prefetch_device(phx_engine* e, const phx_rank_batch* bd) {
     for (int i = 0; i < 2; ++i) PHX_CUDA_TRY(cudaEventCreateWithFlags(&e->ev_done[i], cudaEventDisableTiming), e->err);
     PHX_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&e->x_alt), (size_t)e->max_tokens * e->D * sizeof(bf16)), e->err);
     PHX_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&e->seg_alt), (size_t)e->max_tokens * sizeof(int)), e->err);
+    PHX_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&e->rowss_a_alt), (size_t)e->max_tokens * (e->D / 64) * sizeof(float)), e->err);
     for (int i = 0; i < 2; ++i) PHX_CUDA_TRY(cudaEventRecord(e->ev_done[i], e->stream), e->err);
   }
   // Call order per step: forward(batch i), then prefetch(batch i+1).  The alternate buffers were the working
   // buffers of forward(i-1); the side stream waits for THAT forward's end (the event before the most recent one),
   // not for forward(i), so the gather overlaps forward(i).
   PHX_CUDA_TRY(cudaStreamWaitEvent(e->side_stream, e->ev_done[e->done_idx ^ 1], 0), e->err);
-  phx_status s = build_tokens(e, bd, bd->batch, e->C, e->x_alt, e->seg_alt, e->side_stream);
+  phx_status s = build_tokens(e, bd, bd->batch, e->C, e->x_alt, e->seg_alt, e->side_stream, e->rowss_a_alt);
   if (s) return s;
   PHX_CUDA_TRY(cudaEventRecord(e->ev_prefetch, e->side_stream), e->err);
   e->prefetch_key = *bd;
@@ -794,6 +855,7 @@ phx_status phx_user_tower_device(phx_engine* e, const phx_rank_batch* bd, float*
   if (B == 0) return PHX_OK;
   PHX_CUDA_TRY(cudaEventRecord(e->ev0, e->stream), e->err);
   phx_status s;
+  if ((s = refresh_folded(e))) return s;
   // history only: tokens laid out [B, S]; every valid token is "history" so attention is full among them
   if ((s = build_tokens(e, bd, B, 0))) return s;
   if ((s = run_trunk(e, B, e->S, e->S, e->S))) return s;
@@ -849,7 +911,7 @@ phx_status phx_gemm_device(int32_t device, const uint16_t* A, const uint16_t* Wt
     s = gemm_plan_create(&plan, (const bf16*)A, (const bf16*)Wt, M, N, K, epilogue == 1 && K <= 1024, err);
     cudaEventRecord(e0, 0);
     if (s == PHX_OK && (epilogue < 0 || epilogue > 2)) { err = "phx_gemm_device: epilogue must be 0, 1 or 2"; s = PHX_E_ARG; }
-    if (s == PHX_OK) s = gemm_launch(plan, (bf16*)C, (const bf16*)R, M, epilogue, nullptr, flag, prop.multiProcessorCount, 0, err);
+    if (s == PHX_OK) s = gemm_launch(plan, (const bf16*)A, (bf16*)C, (const bf16*)R, M, epilogue, nullptr, nullptr, flag, prop.multiProcessorCount, 0, err);
     cudaEventRecord(e1, 0);
   }
   cudaError_t ce = cudaEventSynchronize(e1);

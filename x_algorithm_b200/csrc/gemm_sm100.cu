@@ -117,7 +117,7 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_r,
-                    GemmRope rope, long long M, int N, int K, int* err_flag) {
+                    GemmRope rope, GemmNorm norm, long long M, int N, int K, int* err_flag) {
   // C and R may be the same buffer (in-place residual update): a slab is fetched before it is written back,
   // and no other CTA touches the tile.
   using cfg = Cfg<BN>;
@@ -235,6 +235,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (RES && issuer) {
       for (int i = 0; i < DIST && i < my_items; ++i) issue_res(i);
     }
+    float rstd = 1.0f;   // 1/rms of this thread's row, refreshed at each tile
     for (long long i = 0; i < my_items; ++i) {
       const long long q = 2 * i + gidx;
       const int s = (int)(q % SLABS);
@@ -243,6 +244,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const uint32_t slab = gslab + bi * SLAB_BYTES;
       long long m0; int c0; coords(i, m0, c0);
       const bool first_of_tile = (s < 2);               // this group's first slab of the tile
+      // RMSNorm folded into this GEMM: the row's 1/rms comes from the sum of squares its producer left behind
+      // (partials in fixed slots, summed in slot order: deterministic), the gain is folded into the weights.
+      // Read once per tile, before the wait on the accumulator, so the loads hide behind it.
+      float4 ssa = make_float4(0.f, 0.f, 0.f, 0.f), ssb = ssa;   // up to 8 partials, summed after the wait below
+      float ss_rest = 0.f;
+      const bool need_rstd = !RES && norm.ss_in != nullptr && first_of_tile;
+      if (need_rstd) {
+        const long long row = m0 + row_in_tile;
+        if (row < M) {
+          const float* sp = norm.ss_in + row * norm.slots_in;
+          if (norm.slots_in == 8) {
+            ssa = __ldg(reinterpret_cast<const float4*>(sp));
+            ssb = __ldg(reinterpret_cast<const float4*>(sp + 4));
+          } else if (norm.slots_in == 4) {
+            ssa = __ldg(reinterpret_cast<const float4*>(sp));
+          } else {
+            for (int t = 0; t < norm.slots_in; ++t) ss_rest += __ldg(sp + t);
+          }
+        }
+      }
       const bool last_of_tile = (s + 2 >= SLABS);       // ... and its last
       if (RES && issuer && i + DIST < my_items) {
         // the buffer of item i + DIST was last used by item i - 1: its store must have drained
@@ -253,6 +274,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (first_of_tile) ok = mbar_wait(tfull_bar(acc), acc_phase, verr);
       if (RES && ok) ok = mbar_wait(res_bar(gidx * NB + bi), (uint32_t)((i / NB) & 1), verr);
       ok = __all_sync(0xffffffffu, ok);
+      if (need_rstd) {   // slot order: deterministic
+        float ss = ss_rest;
+        ss += ssa.x; ss += ssa.y; ss += ssa.z; ss += ssa.w; ss += ssb.x; ss += ssb.y; ss += ssb.z; ss += ssb.w;
+        rstd = rsqrtf(ss * norm.inv_d + norm.eps);
+      }
       const uint32_t row_addr = slab + row_in_tile * 128;
       const int sw = row_in_tile & 7;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16) + s * SLAB_COLS;
@@ -270,7 +296,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (last_of_tile) { tc_fence_before(); mbar_arrive(tempty_bar(acc)); }
           float v[64];
 #pragma unroll
-          for (int k = 0; k < 64; ++k) v[k] = round_bf(__uint_as_float(r[k]));   // Linear output is bf16
+          for (int k = 0; k < 64; ++k) v[k] = round_bf(__uint_as_float(r[k]) * rstd);   // Linear output is bf16
           rope_slab(v, rope, c0, m0 + row_in_tile);
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
@@ -280,6 +306,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             st_shared_v4(row_addr + ((uint32_t)(c ^ sw) << 4), o);
           }
         } else {
+          float ss_out = 0.f;
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {              // two 32-column halves keep the register footprint low
             uint32_t r[32];
@@ -288,7 +315,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             float v[32];
 #pragma unroll
             for (int k = 0; k < 32; ++k) {
-              v[k] = round_bf(__uint_as_float(r[k]));                          // Linear output is bf16
+              v[k] = round_bf(__uint_as_float(r[k]) * rstd);                   // Linear output is bf16
               if (EPI == EPI_GELU) v[k] = gelu_tanh_f(v[k]);
             }
 #pragma unroll
@@ -299,6 +326,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const float2 a = unpack_bf2(rr.x), b = unpack_bf2(rr.y), cc = unpack_bf2(rr.z), d = unpack_bf2(rr.w);
                 v[c * 8 + 0] += a.x; v[c * 8 + 1] += a.y; v[c * 8 + 2] += b.x; v[c * 8 + 3] += b.y;
                 v[c * 8 + 4] += cc.x; v[c * 8 + 5] += cc.y; v[c * 8 + 6] += d.x; v[c * 8 + 7] += d.y;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) ss_out += v[c * 8 + k] * v[c * 8 + k];   // statistics of the fp32 sums (pre-rounding)
               }
               uint4 o;
               o.x = pack_bf2(v[c * 8 + 0], v[c * 8 + 1]); o.y = pack_bf2(v[c * 8 + 2], v[c * 8 + 3]);
@@ -306,6 +335,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               st_shared_v4(addr, o);
             }
           }
+          if (RES && norm.ss_out != nullptr && m0 + row_in_tile < M && c0 < N)
+            norm.ss_out[(m0 + row_in_tile) * (long long)(N / SLAB_COLS) + c0 / SLAB_COLS] = ss_out;
         }
         fence_async_smem();
       }
@@ -329,7 +360,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 template <int BN, int EPI>
-phx_status launch_t(const GemmPlan& p, const GemmRope& rope, int64_t M, int* err_flag, int num_sms,
+phx_status launch_t(const GemmPlan& p, const GemmRope& rope, const GemmNorm& norm, int64_t M, int* err_flag, int num_sms,
                     cudaStream_t stream, std::string& err) {
   using cfg = Cfg<BN>;
   static bool attr_set = false;
@@ -342,7 +373,7 @@ phx_status launch_t(const GemmPlan& p, const GemmRope& rope, int64_t M, int* err
   int grid = (int)(tiles < num_sms ? tiles : num_sms);
   if (grid <= 0) return PHX_OK;
   gemm_tcgen05_kernel<BN, EPI><<<grid, GEMM_THREADS, cfg::SMEM_BYTES, stream>>>(
-      p.map_a, p.map_b, p.map_c, (EPI == EPI_RESIDUAL) ? p.map_r : p.map_c, rope, M, p.N, p.K, err_flag);
+      p.map_a, p.map_b, p.map_c, (EPI == EPI_RESIDUAL) ? p.map_r : p.map_c, rope, norm, M, p.N, p.K, err_flag);
   PHX_CUDA_TRY(cudaGetLastError(), err);
   return PHX_OK;
 }
@@ -393,12 +424,21 @@ phx_status gemm_plan_create(GemmPlan* plan, const bf16* A, const bf16* Wt, int64
   return PHX_OK;
 }
 
-phx_status gemm_launch(GemmPlan& p, bf16* C, const bf16* R, int64_t M, int epilogue, const GemmRope* rope,
-                       int* err_flag, int num_sms, cudaStream_t stream, std::string& err) {
+phx_status gemm_launch(GemmPlan& p, const bf16* A, bf16* C, const bf16* R, int64_t M, int epilogue, const GemmRope* rope,
+                       const GemmNorm* norm, int* err_flag, int num_sms, cudaStream_t stream, std::string& err) {
   if (!p.ready || M > p.rows_max) { err = "gemm: plan not ready or M exceeds plan rows"; return PHX_E_ARG; }
   if (epilogue == EPI_RESIDUAL && R == nullptr) { err = "gemm: residual epilogue needs R"; return PHX_E_ARG; }
   GemmRope rp;
   memset(&rp, 0, sizeof(rp));
+  GemmNorm nm;
+  memset(&nm, 0, sizeof(nm));
+  if (norm) nm = *norm;
+  if (nm.ss_out && (epilogue != EPI_RESIDUAL || p.N % SLAB_COLS != 0)) { err = "gemm: row statistics are produced by the residual epilogue only"; return PHX_E_ARG; }
+  if (A != p.A) {   // the activation buffer moved (double-buffered residual stream): re-encode its map
+    phx_status s = make_map(&p.map_a, A, p.rows_max, p.K, BM, err);
+    if (s != PHX_OK) return s;
+    p.A = A;
+  }
   if (epilogue == EPI_ROPE) {
     if (!rope || (rope->dh != 32 && rope->dh != 64) || rope->T <= 0 || p.N % rope->dh != 0) {
       err = "gemm: the RoPE epilogue needs head dim 32 or 64";
@@ -419,17 +459,17 @@ phx_status gemm_launch(GemmPlan& p, bf16* C, const bf16* R, int64_t M, int epilo
   }
   if (p.BN == 256) {
     switch (epilogue) {
-      case EPI_STORE: return launch_t<256, EPI_STORE>(p, rp, M, err_flag, num_sms, stream, err);
-      case EPI_RESIDUAL: return launch_t<256, EPI_RESIDUAL>(p, rp, M, err_flag, num_sms, stream, err);
-      case EPI_GELU: return launch_t<256, EPI_GELU>(p, rp, M, err_flag, num_sms, stream, err);
-      case EPI_ROPE: return launch_t<256, EPI_ROPE>(p, rp, M, err_flag, num_sms, stream, err);
+      case EPI_STORE: return launch_t<256, EPI_STORE>(p, rp, nm, M, err_flag, num_sms, stream, err);
+      case EPI_RESIDUAL: return launch_t<256, EPI_RESIDUAL>(p, rp, nm, M, err_flag, num_sms, stream, err);
+      case EPI_GELU: return launch_t<256, EPI_GELU>(p, rp, nm, M, err_flag, num_sms, stream, err);
+      case EPI_ROPE: return launch_t<256, EPI_ROPE>(p, rp, nm, M, err_flag, num_sms, stream, err);
     }
   } else {
     switch (epilogue) {
-      case EPI_STORE: return launch_t<128, EPI_STORE>(p, rp, M, err_flag, num_sms, stream, err);
-      case EPI_RESIDUAL: return launch_t<128, EPI_RESIDUAL>(p, rp, M, err_flag, num_sms, stream, err);
-      case EPI_GELU: return launch_t<128, EPI_GELU>(p, rp, M, err_flag, num_sms, stream, err);
-      case EPI_ROPE: return launch_t<128, EPI_ROPE>(p, rp, M, err_flag, num_sms, stream, err);
+      case EPI_STORE: return launch_t<128, EPI_STORE>(p, rp, nm, M, err_flag, num_sms, stream, err);
+      case EPI_RESIDUAL: return launch_t<128, EPI_RESIDUAL>(p, rp, nm, M, err_flag, num_sms, stream, err);
+      case EPI_GELU: return launch_t<128, EPI_GELU>(p, rp, nm, M, err_flag, num_sms, stream, err);
+      case EPI_ROPE: return launch_t<128, EPI_ROPE>(p, rp, nm, M, err_flag, num_sms, stream, err);
     }
   }
   err = "gemm: unknown epilogue";
