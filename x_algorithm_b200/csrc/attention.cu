@@ -12,6 +12,9 @@
 // bf16 with fp32 accumulation, fragments come from padded shared memory through ldmatrix, P is rounded
 // to bf16 before P V as the reference does, and the output tile is staged in shared memory so global
 // stores are full 16-byte chunks of contiguous rows.
+#include <stdlib.h>
+#include <string.h>
+
 #include "common.cuh"
 
 namespace phx {
@@ -320,6 +323,11 @@ phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::
   if (a.Hq % a.Hkv != 0) { err = "attention: Hq must be a multiple of Hkv"; return PHX_E_ARG; }
   if (a.B == 0 || a.T == 0) return PHX_OK;
   if (a.B > 65535 || a.Hq > 65535) { err = "attention: batch or head count too large for one launch"; return PHX_E_CAPACITY; }
+  {
+    const char* force = getenv("PHX_ATTN");
+    const bool legacy = force && strcmp(force, "mma") == 0;
+    if (!legacy && a.err_flag && ranker_attention_tc_supported(a)) return ranker_attention_tc_launch(a, a.err_flag, stream, err);
+  }
   const bool cap = a.cap_method != 0 && a.cap > 0.f;
   switch (a.dh) {
     case 32: return cap ? launch_dh<32, true>(a, stream, err) : launch_dh<32, false>(a, stream, err);

@@ -1,0 +1,364 @@
+// Candidate-isolated ("ranker") attention on Blackwell tensor cores (tcgen05 + TMEM + TMA); same semantics as
+// attention.cu (mask: phoenix/xrex/pallas/ranker_attention_utils.py:16-56; softmax and P rounding:
+// phoenix/xrex/pallas/ranker_attention_v2.py:113-148, 183).
+//
+// One CTA = 128 query rows of one (batch, head), 192 threads:
+//   warp 0      TMA producer: the Q tile once, then per key block the K tile and the V tile (3-D tensor maps over
+//               [batch][token][column]: rows past the request's last token are zero-filled, never the next request's)
+//   warp 1      MMA issuer: S = Q K^T into TMEM (M=128, N=keys of the block), later O += P V with P read from shared
+//               memory (K-major) and V as an MN-major operand straight from its row-major tile
+//   warps 2-5   softmax: thread = query row; S row from TMEM, mask / max / exp2 / row sum in registers, P rounded to
+//               bf16 into swizzled shared memory, O rescaled in TMEM when the running max moved; at the end the
+//               candidate's self key is folded in with a per-row dot product, O is normalised, staged in shared
+//               memory and written with TMA stores
+// Only history keys are ever multiplied: the candidate x candidate block does not exist in this kernel.
+// Waits are bounded; when one runs out the flag is raised and every later wait returns at once, so all roles
+// drain through the same control flow (no thread is left at a barrier) and the host reports PHX_E_TIMEOUT.
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace phx {
+namespace {
+
+using namespace sm100;
+
+constexpr int QT = 128;            // query rows per CTA
+constexpr int A_THREADS = 192;
+constexpr int SLAB = QT * 128;     // bytes of one [128 rows x 64 bf16] swizzled tile
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float capped_log2(float s, float sm_scale, float cap, int method) {
+  float v = s * sm_scale;
+  if (method == 1) v = v / (1.0f + fabsf(v) / cap);
+  else if (method == 2) v = cap * tanhf(v / cap);
+  return v * 1.4426950408889634f;
+}
+__device__ __forceinline__ void bar_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_16(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+struct AttnTcArgs {
+  const bf16* q; const bf16* k; const bf16* v;          // for the per-row self term (plain loads)
+  long long q_tok_stride, k_tok_stride, v_tok_stride;
+  int q_head_stride, k_head_stride, v_head_stride;
+  const int* seg;
+  int B, T, Hq, Hkv, hist_len;
+  float sm_scale, cap;
+  int cap_method;
+  int* err_flag;
+};
+
+template <int DH, bool CAP>
+__global__ void __launch_bounds__(A_THREADS, 2)
+ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                           const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                           AttnTcArgs a) {
+  constexpr int KBLK = (DH == 64) ? 128 : 64;   // keys per block (keeps shared memory at 80 KB: two CTAs per SM)
+  constexpr int DCH = DH / 64;                  // 64-column chunks of the head dim
+  constexpr int PCH = KBLK / 64;                // 64-key slabs of P
+  constexpr uint32_t TM_S = 0, TM_O = 128;      // TMEM columns of S and O
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = base;                               // DCH x [128 x 128 B]; reused to stage the output
+  const uint32_t sK = sQ + DCH * SLAB;                    // DCH x [KBLK x 128 B]
+  const uint32_t sV = sK + DCH * KBLK * 128;              // DCH x [KBLK x 128 B]
+  const uint32_t sP = sV + DCH * KBLK * 128;              // PCH x [128 x 128 B]
+  const uint32_t sMask = sP + PCH * SLAB;                 // [2][4] key-validity words
+  const uint32_t bars = sMask + 64;
+  const uint32_t q_full = bars, k_full = bars + 8, k_empty = bars + 16, v_full = bars + 24, v_empty = bars + 32,
+                 s_full = bars + 40, p_ready = bars + 48, o_done = bars + 56, tmem_slot = bars + 64;
+  uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+  uint32_t* mask_words = reinterpret_cast<uint32_t*>(smem_raw + (sMask - smem_u32(smem_raw)));
+
+  const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * QT;
+  const int hk = h / (a.Hq / a.Hkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int T = a.T;
+  const int n_hist = a.hist_len < T ? a.hist_len : T;
+  const int n_blocks = (n_hist + KBLK - 1) / KBLK;
+  volatile int* verr = a.err_flag;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1); mbar_init(k_full, 1); mbar_init(k_empty, 1); mbar_init(v_full, 1); mbar_init(v_empty, 1);
+    mbar_init(s_full, 1); mbar_init(p_ready, 128); mbar_init(o_done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 256);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      mbar_expect_tx(q_full, DCH * SLAB);
+      for (int c = 0; c < DCH; ++c) tma_load_3d(sQ + c * SLAB, &map_q, q_full, h * a.q_head_stride + c * 64, q0, b);
+      for (int j = 0; j < n_blocks; ++j) {
+        const uint32_t ph = (uint32_t)(j & 1);
+        mbar_wait(k_empty, ph ^ 1, verr);
+        mbar_expect_tx(k_full, DCH * KBLK * 128);
+        for (int c = 0; c < DCH; ++c) tma_load_3d(sK + c * KBLK * 128, &map_k, k_full, hk * a.k_head_stride + c * 64, j * KBLK, b);
+        mbar_wait(v_empty, ph ^ 1, verr);
+        mbar_expect_tx(v_full, DCH * KBLK * 128);
+        for (int c = 0; c < DCH; ++c) tma_load_3d(sV + c * KBLK * 128, &map_v, v_full, hk * a.v_head_stride + c * 64, j * KBLK, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(QT, KBLK);
+      constexpr uint32_t idesc_o = make_idesc_b_mn(QT, DH);
+      mbar_wait(q_full, 0, verr);
+      for (int j = 0; j < n_blocks; ++j) {
+        const uint32_t ph = (uint32_t)(j & 1);
+        mbar_wait(k_full, ph, verr);
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < DCH; ++c) {
+          const uint64_t qd = make_smem_desc(sQ + c * SLAB), kd = make_smem_desc(sK + c * KBLK * 128);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_bf16(tmem + TM_S, qd + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), idesc_s, (c | k) != 0);
+        }
+        umma_commit(k_empty);
+        umma_commit(s_full);
+        mbar_wait(p_ready, ph, verr);
+        mbar_wait(v_full, ph, verr);
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < KBLK / 16; ++kk) {
+          const uint64_t pd = make_smem_desc(sP + (kk >> 2) * SLAB) + (uint64_t)((kk & 3) * 2);
+          const uint64_t vd = make_smem_desc_mn(sV + kk * 16 * 128, KBLK * 128, 1024);
+          umma_bf16(tmem + TM_O, pd, vd, idesc_o, (j | kk) != 0);
+        }
+        umma_commit(v_empty);
+        umma_commit(o_done);
+      }
+    }
+  } else {
+    // ---------------- softmax / epilogue (warps 2..5, thread = query row) ----------------
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int sw = r & 7;
+    const int row = q0 + r;
+    const long long tok0 = (long long)b * T;
+    const int segq = (row < T) ? a.seg[tok0 + row] : 0;
+    const uint32_t lane_base = ((uint32_t)(quad * 32) << 16);
+    const float csc = CAP ? 1.0f : a.sm_scale * 1.4426950408889634f;
+    float m = -INFINITY, l = 0.f;
+
+    for (int j = 0; j < n_blocks; ++j) {
+      const uint32_t ph = (uint32_t)(j & 1);
+      // validity of the block's keys: thread r looks at key r of the block
+      {
+        const int key = j * KBLK + r;
+        const bool ok = (r < KBLK) && (key < n_hist) && (a.seg[tok0 + key] == 1);
+        const uint32_t word = __ballot_sync(0xffffffffu, ok);
+        if (lane == 0) mask_words[(j & 1) * 4 + quad] = word;
+      }
+      bar_sync_128();
+      uint32_t kmask[4];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) kmask[w] = mask_words[(j & 1) * 4 + w];
+      bool all_ok = true;
+#pragma unroll
+      for (int w = 0; w < KBLK / 32; ++w) all_ok = all_ok && (kmask[w] == 0xffffffffu);
+
+      mbar_wait(s_full, ph, verr);
+      tc_fence_after();
+      float s[KBLK];
+#pragma unroll
+      for (int c = 0; c < KBLK / 32; ++c) tmem_ld32(tmem + TM_S + lane_base + c * 32, reinterpret_cast<uint32_t*>(s) + c * 32);
+      if (CAP) {
+#pragma unroll
+        for (int k = 0; k < KBLK; ++k) s[k] = capped_log2(s[k], a.sm_scale, a.cap, a.cap_method);
+      }
+      if (!all_ok) {
+#pragma unroll
+        for (int k = 0; k < KBLK; ++k)
+          if (!((kmask[k >> 5] >> (k & 31)) & 1u)) s[k] = -INFINITY;
+      }
+      float bm = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < KBLK; ++k) bm = fmaxf(bm, s[k]);
+      const float m_new = fmaxf(m, bm * csc);
+      const float mns = (m_new == -INFINITY) ? 0.f : m_new;   // finite stand-in while nothing is allowed yet
+      const float alpha = ex2f(m - mns);                      // -inf - finite -> 0
+      m = m_new;
+      float ls = 0.f;
+#pragma unroll
+      for (int k = 0; k < KBLK; ++k) { s[k] = ex2f(fmaf(s[k], csc, -mns)); ls += s[k]; }   // masked: 2^-inf = 0
+      l = l * alpha + ls;
+
+      if (j > 0) {
+        // O of the previous blocks must be complete (and P's previous contents consumed) before it is rescaled
+        mbar_wait(o_done, ph ^ 1, verr);
+        tc_fence_after();
+        const bool need = __any_sync(0xffffffffu, alpha != 1.0f);
+        if (need) {
+#pragma unroll
+          for (int c = 0; c < DH / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tmem + TM_O + lane_base + c * 32, o);
+#pragma unroll
+            for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
+            tmem_st32(tmem + TM_O + lane_base + c * 32, o);
+          }
+        }
+      }
+      // P (bf16) into the swizzled K-major slabs the second MMA reads
+#pragma unroll
+      for (int c = 0; c < KBLK / 8; ++c) {
+        uint4 o;
+        o.x = pack_bf2(s[c * 8 + 0], s[c * 8 + 1]); o.y = pack_bf2(s[c * 8 + 2], s[c * 8 + 3]);
+        o.z = pack_bf2(s[c * 8 + 4], s[c * 8 + 5]); o.w = pack_bf2(s[c * 8 + 6], s[c * 8 + 7]);
+        st_shared_16(sP + (c >> 3) * SLAB + r * 128 + ((uint32_t)((c & 7) ^ sw) << 4), o);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      mbar_arrive(p_ready);
+    }
+
+    // ---- epilogue: O row, self key of a candidate, normalise, stage, TMA store --------------------------------
+    float o[DH];
+    if (n_blocks > 0) {
+      mbar_wait(o_done, (uint32_t)((n_blocks - 1) & 1), verr);
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < DH / 32; ++c) tmem_ld32(tmem + TM_O + lane_base + c * 32, reinterpret_cast<uint32_t*>(o) + c * 32);
+    } else {
+#pragma unroll
+      for (int k = 0; k < DH; ++k) o[k] = 0.f;
+    }
+    if (segq == -1) {
+      const long long tok = tok0 + row;
+      const uint4* qp = reinterpret_cast<const uint4*>(a.q + tok * a.q_tok_stride + (long long)h * a.q_head_stride);
+      const uint4* kp = reinterpret_cast<const uint4*>(a.k + tok * a.k_tok_stride + (long long)hk * a.k_head_stride);
+      const uint4* vp = reinterpret_cast<const uint4*>(a.v + tok * a.v_tok_stride + (long long)hk * a.v_head_stride);
+      float dot = 0.f;
+#pragma unroll
+      for (int c = 0; c < DH / 8; ++c) {
+        const uint4 qa = __ldg(qp + c), ka = __ldg(kp + c);
+        const float2 q0f = unpack_bf2(qa.x), q1f = unpack_bf2(qa.y), q2f = unpack_bf2(qa.z), q3f = unpack_bf2(qa.w);
+        const float2 k0f = unpack_bf2(ka.x), k1f = unpack_bf2(ka.y), k2f = unpack_bf2(ka.z), k3f = unpack_bf2(ka.w);
+        dot += q0f.x * k0f.x + q0f.y * k0f.y + q1f.x * k1f.x + q1f.y * k1f.y + q2f.x * k2f.x + q2f.y * k2f.y + q3f.x * k3f.x + q3f.y * k3f.y;
+      }
+      const float sv = CAP ? capped_log2(dot, a.sm_scale, a.cap, a.cap_method) : dot * csc;
+      const float mn = fmaxf(m, sv);
+      const float alpha = ex2f(m - mn);           // no history: 2^-inf = 0
+      const float p = ex2f(sv - mn);
+      const float pr = round_bf(p);
+      l = l * alpha + p;
+#pragma unroll
+      for (int c = 0; c < DH / 8; ++c) {
+        const uint4 va = __ldg(vp + c);
+        const float2 v0 = unpack_bf2(va.x), v1 = unpack_bf2(va.y), v2 = unpack_bf2(va.z), v3 = unpack_bf2(va.w);
+        o[c * 8 + 0] = o[c * 8 + 0] * alpha + pr * v0.x; o[c * 8 + 1] = o[c * 8 + 1] * alpha + pr * v0.y;
+        o[c * 8 + 2] = o[c * 8 + 2] * alpha + pr * v1.x; o[c * 8 + 3] = o[c * 8 + 3] * alpha + pr * v1.y;
+        o[c * 8 + 4] = o[c * 8 + 4] * alpha + pr * v2.x; o[c * 8 + 5] = o[c * 8 + 5] * alpha + pr * v2.y;
+        o[c * 8 + 6] = o[c * 8 + 6] * alpha + pr * v3.x; o[c * 8 + 7] = o[c * 8 + 7] * alpha + pr * v3.y;
+      }
+    }
+    const float inv = (l == 0.f || segq == 0) ? 0.f : 1.0f / l;   // padded rows, rows with no allowed key -> zeros
+#pragma unroll
+    for (int c = 0; c < DH / 8; ++c) {
+      uint4 w;
+      w.x = pack_bf2(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv); w.y = pack_bf2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
+      w.z = pack_bf2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv); w.w = pack_bf2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
+      st_shared_16(sQ + (c >> 3) * SLAB + r * 128 + ((uint32_t)((c & 7) ^ sw) << 4), w);   // Q is no longer needed
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    bar_sync_128();
+    if (warp == 2 && lane == 0) {
+      for (int c = 0; c < DCH; ++c) tma_store_3d(&map_o, sQ + c * SLAB, h * DH + c * 64, q0, b);
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+  }
+
+  if (*verr != 0) __nanosleep(1000000);  // error path: let in-flight bulk copies land before the CTA retires
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
+// tensor maps are cached: the engine calls with the same buffers every layer and every step
+typedef std::tuple<const void*, long long, int, int, long long, int> MapKey;
+std::map<MapKey, CUtensorMap> g_map_cache;
+std::mutex g_map_mu;
+
+phx_status cached_map3d(const CUtensorMap** out, const bf16* ptr, long long cols, int T, int B, long long tok_stride,
+                        int box_rows, std::string& err) {
+  std::lock_guard<std::mutex> lk(g_map_mu);
+  MapKey key(ptr, cols, T, B, tok_stride, box_rows);
+  auto it = g_map_cache.find(key);
+  if (it == g_map_cache.end()) {
+    if (g_map_cache.size() > 4096) g_map_cache.clear();
+    CUtensorMap m;
+    phx_status s = make_map3d(&m, ptr, cols, T, B, tok_stride * 2, (long long)T * tok_stride * 2, box_rows, err);
+    if (s) return s;
+    it = g_map_cache.emplace(key, m).first;
+  }
+  *out = &it->second;
+  return PHX_OK;
+}
+
+template <int DH, bool CAP>
+phx_status launch_tc(const AttnArgs& a, int* err_flag, cudaStream_t stream, std::string& err) {
+  constexpr int KBLK = (DH == 64) ? 128 : 64;
+  constexpr int DCH = DH / 64, PCH = KBLK / 64;
+  const size_t smem = (size_t)DCH * SLAB + 2 * (size_t)DCH * KBLK * 128 + (size_t)PCH * SLAB + 64 + 128 + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    PHX_CUDA_TRY(cudaFuncSetAttribute(ranker_attention_tc_kernel<DH, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), err);
+    attr_set = true;
+  }
+  const CUtensorMap *mq, *mk, *mv, *mo;
+  phx_status s;
+  if ((s = cached_map3d(&mq, a.q, (long long)(a.Hq - 1) * a.q_head_stride + DH, a.T, a.B, a.q_tok_stride, QT, err))) return s;
+  if ((s = cached_map3d(&mk, a.k, (long long)(a.Hkv - 1) * a.k_head_stride + DH, a.T, a.B, a.k_tok_stride, KBLK, err))) return s;
+  if ((s = cached_map3d(&mv, a.v, (long long)(a.Hkv - 1) * a.v_head_stride + DH, a.T, a.B, a.v_tok_stride, KBLK, err))) return s;
+  if ((s = cached_map3d(&mo, a.out, (long long)a.Hq * DH, a.T, a.B, (long long)a.Hq * DH, QT, err))) return s;
+  AttnTcArgs t;
+  t.q = a.q; t.k = a.k; t.v = a.v;
+  t.q_tok_stride = a.q_tok_stride; t.k_tok_stride = a.k_tok_stride; t.v_tok_stride = a.v_tok_stride;
+  t.q_head_stride = a.q_head_stride; t.k_head_stride = a.k_head_stride; t.v_head_stride = a.v_head_stride;
+  t.seg = a.seg; t.B = a.B; t.T = a.T; t.Hq = a.Hq; t.Hkv = a.Hkv; t.hist_len = a.hist_len;
+  t.sm_scale = a.sm_scale; t.cap = a.cap; t.cap_method = a.cap_method; t.err_flag = err_flag;
+  dim3 grid((a.T + QT - 1) / QT, a.Hq, a.B);
+  ranker_attention_tc_kernel<DH, CAP><<<grid, A_THREADS, smem, stream>>>(*mq, *mk, *mv, *mo, t);
+  PHX_CUDA_TRY(cudaGetLastError(), err);
+  return PHX_OK;
+}
+
+}  // namespace
+
+bool ranker_attention_tc_supported(const AttnArgs& a) {
+  if (a.dh != 64 && a.dh != 128) return false;
+  // TMA: 16-byte aligned bases and strides, head offsets that are multiples of 8 elements
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return al(a.q) && al(a.k) && al(a.v) && al(a.out) && a.q_tok_stride % 8 == 0 && a.k_tok_stride % 8 == 0 &&
+         a.v_tok_stride % 8 == 0 && a.q_head_stride % 8 == 0 && a.k_head_stride % 8 == 0 && a.v_head_stride % 8 == 0;
+}
+
+phx_status ranker_attention_tc_launch(const AttnArgs& a, int* err_flag, cudaStream_t stream, std::string& err) {
+  const bool cap = a.cap_method != 0 && a.cap > 0.f;
+  if (a.dh == 64) return cap ? launch_tc<64, true>(a, err_flag, stream, err) : launch_tc<64, false>(a, err_flag, stream, err);
+  if (a.dh == 128) return cap ? launch_tc<128, true>(a, err_flag, stream, err) : launch_tc<128, false>(a, err_flag, stream, err);
+  err = "attention (tcgen05): head dim must be 64 or 128";
+  return PHX_E_ARG;
+}
+
+}  // namespace phx

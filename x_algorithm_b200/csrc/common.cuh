@@ -198,7 +198,11 @@ struct AttnArgs {
   int B, T, Hq, Hkv, dh, hist_len;
   float sm_scale, cap;
   int cap_method;
+  int* err_flag;         // device int raised by a bounded wait that ran out (tcgen05 path); null = mma.sync path only
 };
+// tcgen05 / TMEM kernel for head dims 64 and 128 (attention_sm100.cu); the mma.sync kernel covers the rest
+bool ranker_attention_tc_supported(const AttnArgs& a);
+phx_status ranker_attention_tc_launch(const AttnArgs& a, int* err_flag, cudaStream_t stream, std::string& err);
 phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::string& err);
 
 // ---- heads + blend ------------------------------------------------------------------------------

@@ -327,6 +327,7 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len) {
     aa.out = e->attn; aa.seg = e->seg; aa.B = B; aa.T = Tt; aa.Hq = e->Hq; aa.Hkv = e->Hkv; aa.dh = e->dh;
     aa.hist_len = hist_len; aa.sm_scale = sm_scale; aa.cap = c.attn_logit_cap;
     aa.cap_method = (c.attn_logit_cap > 0.f) ? c.cap_method : 0;
+    aa.err_flag = e->err_flag;
     { ProfScope ps(e, KC_ATTN); if ((s = ranker_attention_launch(aa, e->stream, e->err))) return s; }
     e->last_launches++;
     if (c.primer_norm) {
@@ -382,7 +383,7 @@ phx_status check_err_flag(phx_engine* e) {
   PHX_CUDA_TRY(cudaMemcpy(&flag, e->err_flag, sizeof(int), cudaMemcpyDeviceToHost), e->err);
   if (flag != 0) {
     cudaMemset(e->err_flag, 0, sizeof(int));
-    e->err = "a bounded device-side wait ran out (GEMM pipeline)";
+    e->err = "a bounded device-side wait ran out (GEMM / attention pipeline)";
     return PHX_E_TIMEOUT;
   }
   return PHX_OK;
@@ -877,6 +878,10 @@ phx_status phx_ranker_attention_device(int32_t device, const uint16_t* q, const 
   aa.q_head_stride = aa.k_head_stride = aa.v_head_stride = dh;
   aa.out = (bf16*)out; aa.seg = seg; aa.B = B; aa.T = T; aa.Hq = Hq; aa.Hkv = Hkv; aa.dh = dh; aa.hist_len = hist_len;
   aa.sm_scale = sm_scale; aa.cap = cap; aa.cap_method = cap > 0.f ? cap_method : 0;
+  int* flag = nullptr;
+  if (cudaMalloc(&flag, sizeof(int)) != cudaSuccess) { set_global_error("cudaMalloc failed"); return PHX_E_CUDA; }
+  cudaMemset(flag, 0, sizeof(int));
+  aa.err_flag = flag;
   cudaEvent_t e0, e1;
   cudaEventCreate(&e0); cudaEventCreate(&e1);
   cudaEventRecord(e0, 0);
@@ -885,6 +890,12 @@ phx_status phx_ranker_attention_device(int32_t device, const uint16_t* q, const 
   cudaError_t ce = cudaEventSynchronize(e1);
   if (s == PHX_OK && ce != cudaSuccess) { err = cudaGetErrorString(ce); s = PHX_E_CUDA; }
   if (s == PHX_OK && device_ms) cudaEventElapsedTime(device_ms, e0, e1);
+  if (s == PHX_OK) {
+    int hflag = 0;
+    cudaMemcpy(&hflag, flag, sizeof(int), cudaMemcpyDeviceToHost);
+    if (hflag) { err = "a bounded device-side wait ran out (attention pipeline)"; s = PHX_E_TIMEOUT; }
+  }
+  cudaFree(flag);
   cudaEventDestroy(e0); cudaEventDestroy(e1);
   if (s) set_global_error(err);
   return s;

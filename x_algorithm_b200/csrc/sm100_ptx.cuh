@@ -56,6 +56,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -91,6 +102,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// 32 registers per thread -> 32 lanes x 32 consecutive fp32 columns
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, 8-row
 // groups 1024 bytes apart (stride byte offset), descriptor version 1 (Blackwell).
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
@@ -102,6 +127,18 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;                               // layout: SWIZZLE_128B
   return d;
 }
+// MN-major operand (the MN index is contiguous in shared memory), 128-byte swizzle: a 128-byte row holds 64
+// consecutive MN elements of one K index, 8 consecutive K rows form a 1024-byte atom; `sbo` = bytes between
+// 8-row K groups, `lbo` = bytes between 64-element MN chunks.
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
 // Instruction descriptor for kind::f16: D fp32, A/B bf16, both K-major, M x N tile.
 __host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
   return (1u << 4)                       // D format: f32
@@ -110,6 +147,8 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
          | ((uint32_t)(N >> 3) << 17)    // N / 8
          | ((uint32_t)(M >> 4) << 24);   // M / 16
 }
+// same with the B operand MN-major (bit 16)
+__host__ __device__ constexpr uint32_t make_idesc_b_mn(int M, int N) { return make_idesc(M, N) | (1u << 16); }
 
 // ---- tensor map creation through the runtime's driver entry point (no libcuda link needed) ---------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -152,6 +191,30 @@ inline phx_status make_map(CUtensorMap* map, const bf16* ptr, int64_t rows, int6
   return PHX_OK;
 }
 
+
+// 3-D bf16 tensor [d2][d1][cols] with byte strides s1 (between d1 rows) and s2 (between d2 slices); box =
+// [1][box_rows][64 cols], 128-byte swizzle.  Coordinates past d1 / d2 are zero-filled on load and clipped on store.
+inline phx_status make_map3d(CUtensorMap* map, const bf16* ptr, int64_t cols, int64_t d1, int64_t d2, int64_t s1_bytes,
+                             int64_t s2_bytes, int box_rows, std::string& err) {
+  EncodeTiledFn fn = get_encode_fn(err);
+  if (!fn) return PHX_E_CUDA;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (s1_bytes % 16) != 0 || (s2_bytes % 16) != 0 || cols % 8 != 0) {
+    err = "tensor map: pointer and strides must be 16-byte aligned";
+    return PHX_E_ARG;
+  }
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)d1, (cuuint64_t)d2};
+  cuuint64_t strides[2] = {(cuuint64_t)s1_bytes, (cuuint64_t)s2_bytes};
+  cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<bf16*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    err = "cuTensorMapEncodeTiled (3-D) failed with code " + std::to_string((int)r);
+    return PHX_E_CUDA;
+  }
+  return PHX_OK;
+}
 
 }  // namespace sm100
 }  // namespace phx
