@@ -326,7 +326,14 @@ phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::
   {
     const char* force = getenv("PHX_ATTN");
     const bool legacy = force && strcmp(force, "mma") == 0;
-    if (!legacy && a.err_flag && ranker_attention_tc_supported(a)) return ranker_attention_tc_launch(a, a.err_flag, stream, err);
+    const bool forced_tc = force && (strcmp(force, "tcgen05") == 0 || strcmp(force, "resident") == 0);
+    // Measured on B200: with a history of one key block (<= 128 keys at head dim 64) a tile's tensor work is ~0.1 us
+    // and the tcgen05 pipeline's hand-offs between its warps dominate, so the mma.sync kernel (16 independent warps
+    // per SM) is faster there (2.4 vs 2.6-2.9 ms per step at B=256, S=128, C=512); longer histories and head dim 128
+    // go to the tcgen05 kernel (2.0 vs 4.6 ms at 1024 + 1024 tokens, 16 heads x 128).
+    const int n_hist = a.hist_len < a.T ? a.hist_len : a.T;
+    const bool prefer_tc = forced_tc || a.dh == 128 || n_hist > 128;
+    if (!legacy && prefer_tc && a.err_flag && ranker_attention_tc_supported(a)) return ranker_attention_tc_launch(a, a.err_flag, stream, err);
   }
   const bool cap = a.cap_method != 0 && a.cap > 0.f;
   switch (a.dh) {

@@ -14,6 +14,9 @@
 // Only history keys are ever multiplied: the candidate x candidate block does not exist in this kernel.
 // Waits are bounded; when one runs out the flag is raised and every later wait returns at once, so all roles
 // drain through the same control flow (no thread is left at a barrier) and the host reports PHX_E_TIMEOUT.
+#include <stdlib.h>
+#include <string.h>
+
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -294,6 +297,215 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   }
 }
 
+// ---- resident-history variant -----------------------------------------------------------------------------------
+// History of at most 128 keys, head dim 64 (the ranking trunk's shape): K and V of the (batch, head) are loaded once
+// and stay in shared memory while the CTA walks over all of the request's query tiles.  Q tiles are double-buffered
+// (the producer runs one tile ahead), O is double-buffered in TMEM, so S = Q K^T of tile t+1 is issued while the
+// softmax warps still normalise and store tile t; a finished tile is staged in its own Q buffer and handed back to
+// the producer once the TMA store has read it.
+__global__ void __launch_bounds__(A_THREADS, 2)
+ranker_attention_resident_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                                 AttnTcArgs a, int cap_on) {
+  constexpr int DH = 64, KBLK = 128;
+  constexpr uint32_t TM_S = 0, TM_O = 128;      // O buffers at columns 128 and 192
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = base;                     // 2 x [128 x 128 B]
+  const uint32_t sK = sQ + 2 * SLAB;            // [128 x 128 B]
+  const uint32_t sV = sK + SLAB;                // [128 x 128 B]
+  const uint32_t sP = sV + SLAB;                // 2 x [128 x 128 B]
+  const uint32_t sMask = sP + 2 * SLAB;
+  const uint32_t bars = sMask + 64;
+  auto q_full = [&](int i) { return bars + 8u * i; };
+  auto q_free = [&](int i) { return bars + 16u + 8u * i; };
+  const uint32_t kv_full = bars + 32, s_full = bars + 40, p_ready = bars + 48, o_done = bars + 56, tmem_slot = bars + 64;
+  uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+  uint32_t* mask_words = reinterpret_cast<uint32_t*>(smem_raw + (sMask - smem_u32(smem_raw)));
+
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int hk = h / (a.Hq / a.Hkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int T = a.T;
+  const int n_hist = a.hist_len < T ? a.hist_len : T;
+  const int n_tiles = (T + QT - 1) / QT;
+  volatile int* verr = a.err_flag;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) { mbar_init(q_full(i), 1); mbar_init(q_free(i), 1); }
+    mbar_init(kv_full, 1); mbar_init(s_full, 1); mbar_init(p_ready, 128); mbar_init(o_done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 256);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * SLAB);
+      tma_load_3d(sK, &map_k, kv_full, hk * a.k_head_stride, 0, b);
+      tma_load_3d(sV, &map_v, kv_full, hk * a.v_head_stride, 0, b);
+      for (int t = 0; t < n_tiles; ++t) {
+        const int bq = t & 1;
+        mbar_wait(q_free(bq), (uint32_t)(((t >> 1) & 1) ^ 1), verr);
+        mbar_expect_tx(q_full(bq), SLAB);
+        tma_load_3d(sQ + bq * SLAB, &map_q, q_full(bq), h * a.q_head_stride, t * QT, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(QT, KBLK);
+      constexpr uint32_t idesc_o = make_idesc_b_mn(QT, DH);
+      mbar_wait(kv_full, 0, verr);
+      for (int t = 0; t < n_tiles; ++t) {
+        const int bq = t & 1;
+        const uint32_t ph = (uint32_t)(t & 1);
+        mbar_wait(q_full(bq), (uint32_t)((t >> 1) & 1), verr);
+        tc_fence_after();
+        const uint64_t qd = make_smem_desc(sQ + bq * SLAB), kd = make_smem_desc(sK);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_bf16(tmem + TM_S, qd + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), idesc_s, k != 0);
+        umma_commit(s_full);
+        mbar_wait(p_ready, ph, verr);
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < KBLK / 16; ++kk) {
+          const uint64_t pd = make_smem_desc(sP + (kk >> 2) * SLAB) + (uint64_t)((kk & 3) * 2);
+          const uint64_t vd = make_smem_desc_mn(sV + kk * 16 * 128, KBLK * 128, 1024);
+          umma_bf16(tmem + TM_O + bq * DH, pd, vd, idesc_o, kk != 0);
+        }
+        umma_commit(o_done);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int sw = r & 7;
+    const long long tok0 = (long long)b * T;
+    const uint32_t lane_base = ((uint32_t)(quad * 32) << 16);
+    const float csc = cap_on ? 1.0f : a.sm_scale * 1.4426950408889634f;
+    // key validity, the same for every tile of the request
+    {
+      const bool ok = (r < n_hist) && (a.seg[tok0 + r] == 1);
+      const uint32_t word = __ballot_sync(0xffffffffu, ok);
+      if (lane == 0) mask_words[quad] = word;
+    }
+    bar_sync_128();
+    uint32_t kmask[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) kmask[w] = mask_words[w];
+    const bool all_ok = (kmask[0] & kmask[1] & kmask[2] & kmask[3]) == 0xffffffffu;
+
+    for (int t = 0; t < n_tiles; ++t) {
+      const int bq = t & 1;
+      const uint32_t ph = (uint32_t)(t & 1);
+      const int row = t * QT + r;
+      const int segq = (row < T) ? a.seg[tok0 + row] : 0;
+      // self logit of a candidate row: loads issued before the wait on S
+      float self_logit = 0.f;
+      const long long tok = tok0 + (row < T ? row : 0);
+      if (segq == -1) {
+        const uint4* qp = reinterpret_cast<const uint4*>(a.q + tok * a.q_tok_stride + (long long)h * a.q_head_stride);
+        const uint4* kp = reinterpret_cast<const uint4*>(a.k + tok * a.k_tok_stride + (long long)hk * a.k_head_stride);
+        float dot = 0.f;
+#pragma unroll
+        for (int c = 0; c < DH / 8; ++c) {
+          const uint4 qa = __ldg(qp + c), ka = __ldg(kp + c);
+          const float2 q0f = unpack_bf2(qa.x), q1f = unpack_bf2(qa.y), q2f = unpack_bf2(qa.z), q3f = unpack_bf2(qa.w);
+          const float2 k0f = unpack_bf2(ka.x), k1f = unpack_bf2(ka.y), k2f = unpack_bf2(ka.z), k3f = unpack_bf2(ka.w);
+          dot += q0f.x * k0f.x + q0f.y * k0f.y + q1f.x * k1f.x + q1f.y * k1f.y + q2f.x * k2f.x + q2f.y * k2f.y + q3f.x * k3f.x + q3f.y * k3f.y;
+        }
+        self_logit = cap_on ? capped_log2(dot, a.sm_scale, a.cap, a.cap_method) : dot * csc;
+      }
+
+      mbar_wait(s_full, ph, verr);
+      tc_fence_after();
+      float s[KBLK];
+#pragma unroll
+      for (int c = 0; c < KBLK / 32; ++c) tmem_ld32(tmem + TM_S + lane_base + c * 32, reinterpret_cast<uint32_t*>(s) + c * 32);
+      if (cap_on) {
+#pragma unroll
+        for (int k = 0; k < KBLK; ++k) s[k] = capped_log2(s[k], a.sm_scale, a.cap, a.cap_method);
+      }
+      if (!all_ok) {
+#pragma unroll
+        for (int k = 0; k < KBLK; ++k)
+          if (!((kmask[k >> 5] >> (k & 31)) & 1u)) s[k] = -INFINITY;
+      }
+      float bm = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < KBLK; ++k) bm = fmaxf(bm, s[k]);
+      float m = bm * csc;
+      if (segq == -1) m = fmaxf(m, self_logit);          // the self key takes part in the row maximum right away
+      const float mns = (m == -INFINITY) ? 0.f : m;
+      float l = 0.f;
+#pragma unroll
+      for (int k = 0; k < KBLK; ++k) { s[k] = ex2f(fmaf(s[k], csc, -mns)); l += s[k]; }
+      // P's previous contents (tile t-1) must have been consumed by its P V product
+      if (t > 0) mbar_wait(o_done, ph ^ 1, verr);
+#pragma unroll
+      for (int c = 0; c < KBLK / 8; ++c) {
+        uint4 o;
+        o.x = pack_bf2(s[c * 8 + 0], s[c * 8 + 1]); o.y = pack_bf2(s[c * 8 + 2], s[c * 8 + 3]);
+        o.z = pack_bf2(s[c * 8 + 4], s[c * 8 + 5]); o.w = pack_bf2(s[c * 8 + 6], s[c * 8 + 7]);
+        st_shared_16(sP + (c >> 3) * SLAB + r * 128 + ((uint32_t)((c & 7) ^ sw) << 4), o);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      mbar_arrive(p_ready);
+
+      // ---- epilogue of this tile (the MMA warp is already on S of tile t+1) ----
+      float p_self = 0.f;
+      uint4 vrow[DH / 8];
+      if (segq == -1) {
+        p_self = ex2f(self_logit - mns);
+        l += p_self;
+        const uint4* vp = reinterpret_cast<const uint4*>(a.v + tok * a.v_tok_stride + (long long)hk * a.v_head_stride);
+#pragma unroll
+        for (int c = 0; c < DH / 8; ++c) vrow[c] = __ldg(vp + c);
+      }
+      const float pr = round_bf(p_self);
+      mbar_wait(o_done, ph, verr);
+      tc_fence_after();
+      float o[DH];
+#pragma unroll
+      for (int c = 0; c < DH / 32; ++c) tmem_ld32(tmem + TM_O + bq * DH + lane_base + c * 32, reinterpret_cast<uint32_t*>(o) + c * 32);
+      const float inv = (l == 0.f || segq == 0) ? 0.f : 1.0f / l;
+#pragma unroll
+      for (int c = 0; c < DH / 8; ++c) {
+        if (segq == -1) {
+          const float2 v0 = unpack_bf2(vrow[c].x), v1 = unpack_bf2(vrow[c].y), v2 = unpack_bf2(vrow[c].z), v3 = unpack_bf2(vrow[c].w);
+          o[c * 8 + 0] += pr * v0.x; o[c * 8 + 1] += pr * v0.y; o[c * 8 + 2] += pr * v1.x; o[c * 8 + 3] += pr * v1.y;
+          o[c * 8 + 4] += pr * v2.x; o[c * 8 + 5] += pr * v2.y; o[c * 8 + 6] += pr * v3.x; o[c * 8 + 7] += pr * v3.y;
+        }
+        uint4 w;
+        w.x = pack_bf2(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv); w.y = pack_bf2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
+        w.z = pack_bf2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv); w.w = pack_bf2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
+        st_shared_16(sQ + bq * SLAB + r * 128 + ((uint32_t)((c & 7) ^ sw) << 4), w);   // this tile's Q buffer is free
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      bar_sync_128();
+      if (warp == 2 && lane == 0) {
+        tma_store_3d(&map_o, sQ + bq * SLAB, h * DH, t * QT, b);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        mbar_arrive(q_free(bq));                      // the producer may refill this Q buffer
+      }
+    }
+    if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+
+  if (*verr != 0) __nanosleep(1000000);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
 // tensor maps are cached: the engine calls with the same buffers every layer and every step
 typedef std::tuple<const void*, long long, int, int, long long, int> MapKey;
 std::map<MapKey, CUtensorMap> g_map_cache;
@@ -343,6 +555,32 @@ phx_status launch_tc(const AttnArgs& a, int* err_flag, cudaStream_t stream, std:
   return PHX_OK;
 }
 
+phx_status launch_resident(const AttnArgs& a, int* err_flag, cudaStream_t stream, std::string& err) {
+  const size_t smem = 6 * (size_t)SLAB + 64 + 128 + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    PHX_CUDA_TRY(cudaFuncSetAttribute(ranker_attention_resident_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), err);
+    attr_set = true;
+  }
+  const CUtensorMap *mq, *mk, *mv, *mo;
+  phx_status s;
+  if ((s = cached_map3d(&mq, a.q, (long long)(a.Hq - 1) * a.q_head_stride + 64, a.T, a.B, a.q_tok_stride, QT, err))) return s;
+  if ((s = cached_map3d(&mk, a.k, (long long)(a.Hkv - 1) * a.k_head_stride + 64, a.T, a.B, a.k_tok_stride, 128, err))) return s;
+  if ((s = cached_map3d(&mv, a.v, (long long)(a.Hkv - 1) * a.v_head_stride + 64, a.T, a.B, a.v_tok_stride, 128, err))) return s;
+  if ((s = cached_map3d(&mo, a.out, (long long)a.Hq * 64, a.T, a.B, (long long)a.Hq * 64, QT, err))) return s;
+  AttnTcArgs t;
+  t.q = a.q; t.k = a.k; t.v = a.v;
+  t.q_tok_stride = a.q_tok_stride; t.k_tok_stride = a.k_tok_stride; t.v_tok_stride = a.v_tok_stride;
+  t.q_head_stride = a.q_head_stride; t.k_head_stride = a.k_head_stride; t.v_head_stride = a.v_head_stride;
+  t.seg = a.seg; t.B = a.B; t.T = a.T; t.Hq = a.Hq; t.Hkv = a.Hkv; t.hist_len = a.hist_len;
+  t.sm_scale = a.sm_scale; t.cap = a.cap; t.cap_method = a.cap_method; t.err_flag = err_flag;
+  const int cap_on = (a.cap_method != 0 && a.cap > 0.f) ? 1 : 0;
+  dim3 grid(1, a.Hq, a.B);
+  ranker_attention_resident_kernel<<<grid, A_THREADS, smem, stream>>>(*mq, *mk, *mv, *mo, t, cap_on);
+  PHX_CUDA_TRY(cudaGetLastError(), err);
+  return PHX_OK;
+}
+
 }  // namespace
 
 bool ranker_attention_tc_supported(const AttnArgs& a) {
@@ -355,6 +593,12 @@ bool ranker_attention_tc_supported(const AttnArgs& a) {
 
 phx_status ranker_attention_tc_launch(const AttnArgs& a, int* err_flag, cudaStream_t stream, std::string& err) {
   const bool cap = a.cap_method != 0 && a.cap > 0.f;
+  {
+    const char* force = getenv("PHX_ATTN");
+    const bool resident = force && strcmp(force, "resident") == 0;
+    const int n_hist = a.hist_len < a.T ? a.hist_len : a.T;
+    if (resident && a.dh == 64 && n_hist <= 128 && n_hist > 0) return launch_resident(a, err_flag, stream, err);
+  }
   if (a.dh == 64) return cap ? launch_tc<64, true>(a, err_flag, stream, err) : launch_tc<64, false>(a, err_flag, stream, err);
   if (a.dh == 128) return cap ? launch_tc<128, true>(a, err_flag, stream, err) : launch_tc<128, false>(a, err_flag, stream, err);
   err = "attention (tcgen05): head dim must be 64 or 128";
