@@ -92,6 +92,8 @@ struct GemmPlan {
   int64_t rows_max = 0;
   int N = 0, K = 0, BN = 0;
   bool ready = false;
+  unsigned long long* counters = nullptr;  // optional device counters [3]: MMA issuer cycles total / waiting for
+                                           // operands / waiting for a free accumulator (diagnostics)
 };
 
 // narrow_tiles: use 128 x 128 tiles even when N is a multiple of 256 (more output slab buffers; meant for

@@ -913,6 +913,7 @@ phx_status phx_gemm_device(int32_t device, const uint16_t* A, const uint16_t* Wt
   cudaEvent_t e0, e1;
   cudaEventCreate(&e0); cudaEventCreate(&e1);
   phx_status s = PHX_OK;
+  unsigned long long* ctr = nullptr;   // PHX_GEMM_COUNTERS=1: print where the MMA issuer waited (diagnostics)
   if (impl == 1) {
     cudaEventRecord(e0, 0);
     s = gemm_simt_launch((const bf16*)A, (const bf16*)Wt, (bf16*)C, (const bf16*)R, M, N, K, epilogue, 0, err);
@@ -920,6 +921,7 @@ phx_status phx_gemm_device(int32_t device, const uint16_t* A, const uint16_t* Wt
   } else {
     GemmPlan plan;
     s = gemm_plan_create(&plan, (const bf16*)A, (const bf16*)Wt, M, N, K, epilogue == 1 && K <= 1024, err);
+    if (getenv("PHX_GEMM_COUNTERS")) { cudaMalloc(&ctr, 24); cudaMemset(ctr, 0, 24); plan.counters = ctr; }
     cudaEventRecord(e0, 0);
     if (s == PHX_OK && (epilogue < 0 || epilogue > 2)) { err = "phx_gemm_device: epilogue must be 0, 1 or 2"; s = PHX_E_ARG; }
     if (s == PHX_OK) s = gemm_launch(plan, (const bf16*)A, (bf16*)C, (const bf16*)R, M, epilogue, nullptr, nullptr, flag, prop.multiProcessorCount, 0, err);
@@ -932,6 +934,14 @@ phx_status phx_gemm_device(int32_t device, const uint16_t* A, const uint16_t* Wt
   if (s == PHX_OK) {
     cudaMemcpy(&hflag, flag, sizeof(int), cudaMemcpyDeviceToHost);
     if (hflag) { err = "a bounded device-side wait ran out (GEMM pipeline)"; s = PHX_E_TIMEOUT; }
+  }
+  if (ctr) {
+    unsigned long long h[3] = {0, 0, 0};
+    cudaMemcpy(h, ctr, 24, cudaMemcpyDeviceToHost);
+    fprintf(stderr, "[phx gemm counters] MMA issuer cycles (sum over CTAs): total %llu, waiting for operands %llu (%.1f%%), "
+            "waiting for a free accumulator %llu (%.1f%%)\n", h[0], h[1], 100.0 * h[1] / (double)(h[0] ? h[0] : 1), h[2],
+            100.0 * h[2] / (double)(h[0] ? h[0] : 1));
+    cudaFree(ctr);
   }
   cudaFree(flag);
   cudaEventDestroy(e0); cudaEventDestroy(e1);

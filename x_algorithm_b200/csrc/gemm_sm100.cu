@@ -117,7 +117,8 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_r,
-                    GemmRope rope, GemmNorm norm, long long M, int N, int K, int* err_flag) {
+                    GemmRope rope, GemmNorm norm, long long M, int N, int K, int* err_flag,
+                    unsigned long long* counters) {
   // C and R may be the same buffer (in-place residual update): a slab is fetched before it is written back,
   // and no other CTA touches the tile.
   using cfg = Cfg<BN>;
@@ -179,13 +180,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int stage = 0; uint32_t phase = 0;
       uint32_t it = 0;
       bool ok = true;
+      long long cnt_tempty = 0, cnt_full = 0;
+      const long long t_start = counters ? clock64() : 0;
       for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
         const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+        long long c0 = counters ? clock64() : 0;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, verr)) { ok = false; break; }
+        if (counters) cnt_tempty += clock64() - c0;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
+          c0 = counters ? clock64() : 0;
           if (!mbar_wait(full_bar(stage), phase, verr)) { ok = false; break; }
+          if (counters) cnt_full += clock64() - c0;
           tc_fence_after();
           const uint32_t a_src = smem_base + stage * cfg::STAGE_BYTES;
           const uint64_t adesc = make_smem_desc(a_src);
@@ -199,6 +206,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (++stage == cfg::STAGES) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(tfull_bar(acc));  // accumulator complete
+      }
+      if (counters) {   // diagnostic: where the MMA issuer spent its time (cycles summed over CTAs)
+        atomicAdd(&counters[0], (unsigned long long)(clock64() - t_start));
+        atomicAdd(&counters[1], (unsigned long long)cnt_full);
+        atomicAdd(&counters[2], (unsigned long long)cnt_tempty);
       }
     }
   } else {
@@ -373,7 +385,7 @@ phx_status launch_t(const GemmPlan& p, const GemmRope& rope, const GemmNorm& nor
   int grid = (int)(tiles < num_sms ? tiles : num_sms);
   if (grid <= 0) return PHX_OK;
   gemm_tcgen05_kernel<BN, EPI><<<grid, GEMM_THREADS, cfg::SMEM_BYTES, stream>>>(
-      p.map_a, p.map_b, p.map_c, (EPI == EPI_RESIDUAL) ? p.map_r : p.map_c, rope, norm, M, p.N, p.K, err_flag);
+      p.map_a, p.map_b, p.map_c, (EPI == EPI_RESIDUAL) ? p.map_r : p.map_c, rope, norm, M, p.N, p.K, err_flag, p.counters);
   PHX_CUDA_TRY(cudaGetLastError(), err);
   return PHX_OK;
 }
