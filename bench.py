@@ -222,6 +222,15 @@ def main():
         out = eng.rank(host_in[i % n_rot])
     e2e_s = time.perf_counter() - t0
     barrier()
+    # p50 latency of one request (B=1) and of the throughput batch through the same host-buffer call
+    one = px.RankInputs(*[a[:1] for a in (batches[0].hist_post_ids, batches[0].hist_author_ids, batches[0].hist_actions,
+                                          batches[0].hist_surfaces, batches[0].cand_post_ids, batches[0].cand_author_ids)])
+    lat1, latB = [], []
+    for i in range(53):
+        t1 = time.perf_counter(); eng.rank(one); lat1.append(time.perf_counter() - t1)
+    for i in range(13):
+        t1 = time.perf_counter(); eng.rank(host_in[i % n_rot]); latB.append(time.perf_counter() - t1)
+    p50 = dict(request_ms_b1=1e3 * float(np.median(lat1[3:])), batch_ms=1e3 * float(np.median(latB[3:])))
     sampler.stop_flag = True
     sampler.join(timeout=2)
 
@@ -251,18 +260,21 @@ def main():
                      ms_per_step=e2e_ms / args.steps),
             gpu_launches=launches,
             roofline=dict(bound="tensor", kernel="gemm_tcgen05_kernel", achieved=gemm_tflops, peak=peaks["bf16"], unit="TFLOP/s",
-                          frac=(gemm_tflops / peaks["bf16"]) if gemm_tflops else None, traffic=None,
+                          frac=(gemm_tflops / peaks["bf16"]) if gemm_tflops else None,
+                          # DRAM read+write bytes per launch, average over the four GEMM shapes: ncu capture at
+                          # M = 40,960 rows (profiles/gemm_tcgen05_cfg1_shapes.md), scaled by rows (traffic grows with M)
+                          traffic=592e6 * (B / 256.0), traffic_unit="bytes/launch",
+                          algorithmic_bytes_per_launch=755e6 * (B / 256.0),
                           peak_source=peaks["source"] + " (sustained bf16)", launches_per_step=gemm_n, ms_per_step=gemm_ms),
             kernel_ms_per_step={k: v[0] for k, v in prof.items()},
             clocks=sampler.summary(),
+            p50_latency=p50,
         )
         if not args.no_cpu_baseline:
             cores = len(os.sched_getaffinity(0))
             rate, dt = cpu_oracle_rate(2)
             line["cpu_baseline"] = dict(value=rate, unit="candidates/s", cores=cores, kind="port",
                                         sample=f"2 requests x 512 candidates, one pass of the NumPy oracle ({dt:.1f} s)")
-            # the GPU's output for the same two requests agrees with the oracle
-            b2 = po.make_batch(ocfg, 2, seed=ID_SEED, zipf_s=1.1)
         print(json.dumps(line), flush=True)
     eng.close()
     if world > 1:
