@@ -218,7 +218,8 @@ phx_status phx_ranker_attention_device(int32_t device, const uint16_t* q, const 
                                        int32_t Hkv, int32_t dh, int32_t hist_len, float sm_scale, float cap,
                                        int32_t cap_method, float* device_ms);
 /* C[M,N] = epilogue(A[M,K] @ W) on the engine's GEMM kernel; Wt is [N,K] bf16 (K-major).
- * epilogue: 0 store, 1 add residual R[M,N] (bf16), 2 GELU-tanh.  impl: 0 tcgen05, 1 SIMT reference.
+ * epilogue: 0 store, 1 add residual R[M,N] (bf16), 2 GELU-tanh.  impl: 0 tcgen05 (CTA pairs sharing 256-row
+ * tiles unless PHX_GEMM=cta1), 1 SIMT reference, 2 tcgen05 with one CTA per 128-row tile.
  * Replaces the Linear layers (linear_layer.py:52-91). */
 phx_status phx_gemm_device(int32_t device, const uint16_t* A, const uint16_t* Wt, const uint16_t* R, uint16_t* C,
                            int64_t M, int32_t N, int32_t K, int32_t epilogue, int32_t impl, float* device_ms);

@@ -72,7 +72,7 @@ def test_gemm_tcgen05_vs_fp32(torch, M, N, K, epi):
     elif epi == 2:
         ref = torch.nn.functional.gelu(ref, approximate="tanh")
     ref = ref.to(torch.bfloat16).float()
-    for impl in (0, 1):
+    for impl in (0, 1, 2):   # tcgen05 with CTA pairs (the default), SIMT cross-check, tcgen05 one CTA per tile
         c, ms = gemm(a, wt, r, epilogue=epi, impl=impl)
         err = rel_l2(c.float().cpu().numpy(), ref.cpu().numpy())
         assert err < 4e-3, (impl, err)

@@ -91,6 +91,7 @@ struct GemmPlan {
   const bf16* Wt = nullptr;
   int64_t rows_max = 0;
   int N = 0, K = 0, BN = 0;
+  bool pair = false;   // two CTAs of a cluster share each 256-row tile (tcgen05 cta_group::2)
   bool ready = false;
   unsigned long long* counters = nullptr;  // optional device counters [3]: MMA issuer cycles total / waiting for
                                            // operands / waiting for a free accumulator (diagnostics)
@@ -99,7 +100,9 @@ struct GemmPlan {
 // narrow_tiles: use 128 x 128 tiles even when N is a multiple of 256 (more output slab buffers; meant for
 // residual GEMMs with a short K, which are bound by HBM rather than by the tensor pipe)
 phx_status gemm_plan_create(GemmPlan* plan, const bf16* A, const bf16* Wt, int64_t rows_max, int N, int K,
-                            bool narrow_tiles, std::string& err);
+                            bool narrow_tiles, std::string& err, int pair = -1);
+// pair: 1 = CTA pairs share 256-row tiles (cta_group::2), 0 = one CTA per 128-row tile, -1 = pairs unless the
+// environment says PHX_GEMM=cta1
 // Launch on `stream`.  `R` is the residual (EPI_RESIDUAL) or null.  `err_flag` is a device int the
 // kernel sets to 1 when a bounded wait ran out.
 phx_status gemm_launch(GemmPlan& plan, const bf16* A, bf16* C, const bf16* R, int64_t M, int epilogue,

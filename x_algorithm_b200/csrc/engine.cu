@@ -920,7 +920,7 @@ phx_status phx_gemm_device(int32_t device, const uint16_t* A, const uint16_t* Wt
     cudaEventRecord(e1, 0);
   } else {
     GemmPlan plan;
-    s = gemm_plan_create(&plan, (const bf16*)A, (const bf16*)Wt, M, N, K, epilogue == 1 && K <= 1024, err);
+    s = gemm_plan_create(&plan, (const bf16*)A, (const bf16*)Wt, M, N, K, epilogue == 1 && K <= 1024, err, impl == 2 ? 0 : -1);
     if (getenv("PHX_GEMM_COUNTERS")) { cudaMalloc(&ctr, 24); cudaMemset(ctr, 0, 24); plan.counters = ctr; }
     cudaEventRecord(e0, 0);
     if (s == PHX_OK && (epilogue < 0 || epilogue > 2)) { err = "phx_gemm_device: epilogue must be 0, 1 or 2"; s = PHX_E_ARG; }

@@ -1,17 +1,22 @@
 // bf16 GEMM for the Linear layers of the Phoenix trunk (phoenix/xrex/models/linear_layer.py:52-91)
 // on Blackwell tensor cores: C[M,N] = epilogue(A[M,K] @ Wt[N,K]^T), fp32 accumulation in TMEM.
 //
-// Persistent kernel, one CTA per SM, 192 threads:
-//   warp 0      TMA producer: A tile 128x64 and W tile BNx64 (bf16, 128-byte swizzle) per k-step
-//               into a ring of shared-memory stages (cp.async.bulk.tensor + mbarrier tx count)
-//   warp 1      MMA issuer: one lane issues tcgen05.mma (M=128, N=BN, K=16) x4 per stage into one
-//               of two TMEM accumulators, tcgen05.commit releases the stage / publishes the tile
-//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (each warp its 32-lane quadrant) in
-//               64-column slabs, fused op (store | +residual | GELU-tanh | RoPE), bf16 slab staged in
-//               swizzled shared memory and written by one TMA bulk store; the residual slab is
-//               fetched by TMA one slab ahead; overlaps the next tile's main loop through the second
-//               accumulator
+// Persistent kernel, one CTA per SM, 320 threads:
+//   warp 0      TMA producer: A tile 128x64 and W tile per k-step (bf16, 128-byte swizzle) into a ring of
+//               shared-memory stages (cp.async.bulk.tensor + mbarrier tx count)
+//   warp 1      MMA issuer: one lane issues tcgen05.mma (N=BN, K=16) x4 per stage into one of two TMEM
+//               accumulators, tcgen05.commit releases the stage / publishes the tile
+//   warps 2-9   epilogue, two groups of four warps: tcgen05.ld the finished accumulator (each warp its
+//               32-lane quadrant) in 64-column slabs, fused op (store | +residual | GELU-tanh | RoPE | RMSNorm
+//               scale), bf16 slab staged in swizzled shared memory and written by one TMA bulk store; the
+//               residual slab is fetched by TMA ahead of its use; overlaps the next tile's main loop through
+//               the second accumulator
+// PAIR variant (cta_group::2): the two CTAs of a cluster work on one 256 x BN tile.  Each loads its own 128 rows of
+// A and its own half of the W tile, the even CTA issues one MMA (M=256) that reads both shared memories and
+// writes each CTA's 128 rows into that CTA's TMEM, and each CTA runs the epilogue on its own rows.  Operand bytes
+// per CTA per k-step fall from 128+BN to 128+BN/2 rows: the GEMM is bound by that shared-memory fill.
 // Every mbarrier wait is bounded by wall time; on expiry the kernel raises *err_flag and unwinds.
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -25,12 +30,13 @@ using namespace sm100;
 constexpr int BM = 128;
 constexpr int GEMM_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
 
-template <int BN>
+template <int BN, bool PAIR>
 struct Cfg {
-  static constexpr int STAGES = 4;
-  static constexpr int NSLAB = (BN == 256) ? 2 : 6;   // output slab buffers (half per epilogue group)
+  static constexpr int STAGES = PAIR ? 5 : 4;
+  static constexpr int NSLAB = PAIR ? ((BN == 256) ? 4 : 6) : ((BN == 256) ? 2 : 6);   // output slab buffers (half per epilogue group)
+  static constexpr int B_ROWS = PAIR ? BN / 2 : BN;   // rows of the W tile this CTA loads
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int B_BYTES = B_ROWS * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_BYTES = 256;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NSLAB * (128 * 64 * 2) + BAR_BYTES + 1024;  // + slabs, +1024 alignment slack
@@ -113,7 +119,7 @@ __device__ __forceinline__ void rope_slab(float (&v)[64], const GemmRope& rp, in
   }
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_r,
@@ -121,7 +127,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     unsigned long long* counters) {
   // C and R may be the same buffer (in-place residual update): a slab is fetched before it is written back,
   // and no other CTA touches the tile.
-  using cfg = Cfg<BN>;
+  using cfg = Cfg<BN, PAIR>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
   const uint32_t slab_base = smem_base + cfg::STAGES * cfg::STAGE_BYTES;   // output slab buffers
@@ -136,21 +142,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int TILE_M = PAIR ? 2 * BM : BM;          // rows of one work tile (of the CTA pair)
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u; // 0 = the CTA that issues the pair's MMAs
+  const long long first_tile = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+  const long long tile_step = PAIR ? (gridDim.x >> 1) : gridDim.x;
   const int n_tiles = (N + BN - 1) / BN;
-  const long long m_tiles = (M + BM - 1) / BM;
+  const long long m_tiles = (M + TILE_M - 1) / TILE_M;
   const long long total_tiles = m_tiles * n_tiles;
   const int k_blocks = (K + BK - 1) / BK;
   volatile int* verr = err_flag;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < cfg::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), EPI_THREADS); }
+    // a pair's accumulators are drained by the epilogue threads of both CTAs, counted on the issuing CTA
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), PAIR ? 2 * EPI_THREADS : EPI_THREADS); }
     for (int a = 0; a < cfg::NSLAB; ++a) mbar_init(res_bar(a), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(tmem_slot, cfg::TMEM_COLS);
+  if (warp == 1) {
+    if (PAIR) tmem_alloc_pair(tmem_slot, cfg::TMEM_COLS);
+    else tmem_alloc(tmem_slot, cfg::TMEM_COLS);
+  }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
@@ -159,30 +174,46 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (long long tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
         const int n_blk = (int)(tile % n_tiles);
         const long long m_blk = tile / n_tiles;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, verr)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * cfg::STAGE_BYTES;
           const uint32_t b_dst = a_dst + cfg::A_BYTES;
-          mbar_expect_tx(full_bar(stage), cfg::STAGE_BYTES);
-          tma_load_2d(a_dst, &map_a, full_bar(stage), kb * BK, (int)(m_blk * BM));
-          tma_load_2d(b_dst, &map_b, full_bar(stage), kb * BK, n_blk * BN);
+          if (PAIR) {
+            // both CTAs' bytes are counted on the issuing CTA's barrier
+            const uint32_t bar0 = mapa_shared(full_bar(stage), 0);
+            if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * cfg::STAGE_BYTES);
+            tma_load_2d_pair(a_dst, &map_a, bar0, kb * BK, (int)(m_blk * TILE_M + rank * BM));
+            tma_load_2d_pair(b_dst, &map_b, bar0, kb * BK, n_blk * BN + (int)rank * cfg::B_ROWS);
+          } else {
+            mbar_expect_tx(full_bar(stage), cfg::STAGE_BYTES);
+            tma_load_2d(a_dst, &map_a, full_bar(stage), kb * BK, (int)(m_blk * BM));
+            tma_load_2d(b_dst, &map_b, full_bar(stage), kb * BK, n_blk * BN);
+          }
+          if (++stage == cfg::STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (PAIR && ok) {
+        // the issuing CTA releases stages in this CTA by remote arrivals: all of them must have landed before
+        // this CTA may retire
+        for (int s = 0; s < cfg::STAGES; ++s) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, verr)) break;
           if (++stage == cfg::STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BM, BN);
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc(TILE_M, BN);
       int stage = 0; uint32_t phase = 0;
       uint32_t it = 0;
       bool ok = true;
       long long cnt_tempty = 0, cnt_full = 0;
       const long long t_start = counters ? clock64() : 0;
-      for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      for (long long tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++it) {
         const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
         long long c0 = counters ? clock64() : 0;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, verr)) { ok = false; break; }
@@ -200,12 +231,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advancing 16 elements along K inside the 128-byte swizzle row = +32 bytes = +2 in the address field
-            umma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+            if (PAIR) umma_bf16_pair(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+            else umma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb | k) != 0);
           }
-          umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+          // stage reusable (in both CTAs of a pair) once these MMAs have read it
+          if (PAIR) umma_commit_pair(empty_bar(stage), 3); else umma_commit(empty_bar(stage));
           if (++stage == cfg::STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(tfull_bar(acc));  // accumulator complete
+        if (ok) {  // accumulator complete
+          if (PAIR) umma_commit_pair(tfull_bar(acc), 3); else umma_commit(tfull_bar(acc));
+        }
       }
       if (counters) {   // diagnostic: where the MMA issuer spent its time (cycles summed over CTAs)
         atomicAdd(&counters[0], (unsigned long long)(clock64() - t_start));
@@ -228,14 +263,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int quad = warp & 3;                          // TMEM lane quadrant this warp may read
     const int row_in_tile = quad * 32 + lane;
     const bool issuer = ((ew & 3) == 0 && lane == 0);
-    const long long my_tiles = (total_tiles > blockIdx.x) ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const long long my_tiles = (total_tiles > first_tile) ? (total_tiles - first_tile + tile_step - 1) / tile_step : 0;
+    // the accumulator-drained signal goes to the CTA that issues the MMAs
+    const uint32_t tempty0 = PAIR ? mapa_shared(tempty_bar(0), 0) : tempty_bar(0);
+    const uint32_t tempty1 = PAIR ? mapa_shared(tempty_bar(1), 0) : tempty_bar(1);
+    auto release_acc = [&](uint32_t a) {
+      tc_fence_before();
+      if (PAIR) mbar_arrive_cluster(a ? tempty1 : tempty0);
+      else mbar_arrive(a ? tempty1 : tempty0);
+    };
     const long long total_items = my_tiles * SLABS;
     const long long my_items = (total_items > gidx) ? (total_items - gidx + 1) / 2 : 0;
     const uint32_t gslab = slab_base + gidx * NB * SLAB_BYTES;
     auto coords = [&](long long i, long long& m0, int& c0) {   // i = item index inside this group
       const long long q = 2 * i + gidx;
-      const long long tile = blockIdx.x + (q / SLABS) * gridDim.x;
-      m0 = (tile / n_tiles) * BM;
+      const long long tile = first_tile + (q / SLABS) * tile_step;
+      m0 = (tile / n_tiles) * TILE_M + rank * BM;
       c0 = (int)(tile % n_tiles) * BN + (int)(q % SLABS) * SLAB_COLS;
     };
     auto issue_res = [&](long long i) {
@@ -305,7 +348,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           uint32_t r[64];
           tmem_ld32(taddr, r);
           tmem_ld32(taddr + 32, r + 32);
-          if (last_of_tile) { tc_fence_before(); mbar_arrive(tempty_bar(acc)); }
+          if (last_of_tile) release_acc(acc);
           float v[64];
 #pragma unroll
           for (int k = 0; k < 64; ++k) v[k] = round_bf(__uint_as_float(r[k]) * rstd);   // Linear output is bf16
@@ -323,7 +366,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           for (int hh = 0; hh < 2; ++hh) {              // two 32-column halves keep the register footprint low
             uint32_t r[32];
             tmem_ld32(taddr + hh * 32, r);
-            if (hh == 1 && last_of_tile) { tc_fence_before(); mbar_arrive(tempty_bar(acc)); }
+            if (hh == 1 && last_of_tile) release_acc(acc);
             float v[32];
 #pragma unroll
             for (int k = 0; k < 32; ++k) {
@@ -353,7 +396,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         fence_async_smem();
       }
       if (!epi_barrier_and(ok, 1 + gidx)) break;        // uniform over the group's 128 threads
-      if (issuer && c0 < N) {
+      if (issuer && c0 < N && m0 < M) {
         tma_store_2d(&map_c, slab, c0, (int)m0);
         bulk_commit();
       }
@@ -365,29 +408,68 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (*verr != 0) __nanosleep(1000000);  // error path: let in-flight bulk copies land before the CTA retires
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // neither CTA retires (or frees tensor memory) while the other may still signal or read it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, cfg::TMEM_COLS);
+    if (PAIR) tmem_dealloc_pair(tmem_base, cfg::TMEM_COLS);
+    else tmem_dealloc(tmem_base, cfg::TMEM_COLS);
   }
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool PAIR>
 phx_status launch_t(const GemmPlan& p, const GemmRope& rope, const GemmNorm& norm, int64_t M, int* err_flag, int num_sms,
                     cudaStream_t stream, std::string& err) {
-  using cfg = Cfg<BN>;
+  using cfg = Cfg<BN, PAIR>;
+  auto kern = gemm_tcgen05_kernel<BN, EPI, PAIR>;
   static bool attr_set = false;
+  static int max_pairs = 0;
+  cudaLaunchConfig_t lc;
+  memset(&lc, 0, sizeof(lc));
+  cudaLaunchAttribute attr[1];
+  lc.blockDim = dim3(GEMM_THREADS);
+  lc.dynamicSmemBytes = cfg::SMEM_BYTES;
+  lc.stream = stream;
+  if (PAIR) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    lc.attrs = attr; lc.numAttrs = 1;
+  }
   if (!attr_set) {
-    PHX_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      cfg::SMEM_BYTES), err);
+    PHX_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES), err);
+    if (PAIR) {   // how many CTA pairs the device can hold at once (pairs need two SMs of one cluster-capable group)
+      lc.gridDim = dim3(2 * (num_sms / 2));
+      int n = 0;
+      PHX_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kern, &lc), err);
+      max_pairs = n < num_sms / 2 ? n : num_sms / 2;
+      if (max_pairs <= 0) { err = "gemm: the device cannot hold a CTA pair of this kernel"; return PHX_E_CUDA; }
+    }
     attr_set = true;
   }
-  const long long tiles = ((M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  int grid = (int)(tiles < num_sms ? tiles : num_sms);
-  if (grid <= 0) return PHX_OK;
-  gemm_tcgen05_kernel<BN, EPI><<<grid, GEMM_THREADS, cfg::SMEM_BYTES, stream>>>(
-      p.map_a, p.map_b, p.map_c, (EPI == EPI_RESIDUAL) ? p.map_r : p.map_c, rope, norm, M, p.N, p.K, err_flag, p.counters);
-  PHX_CUDA_TRY(cudaGetLastError(), err);
+  constexpr int TILE_M = PAIR ? 2 * BM : BM;
+  const long long tiles = ((M + TILE_M - 1) / TILE_M) * ((p.N + BN - 1) / BN);
+  const int slots = PAIR ? max_pairs : num_sms;
+  const int units = (int)(tiles < slots ? tiles : slots);
+  if (units <= 0) return PHX_OK;
+  lc.gridDim = dim3(PAIR ? 2 * units : units);
+  const CUtensorMap& mr = (EPI == EPI_RESIDUAL) ? p.map_r : p.map_c;
+  long long Mll = M;
+  int N = p.N, K = p.K;
+  unsigned long long* counters = p.counters;
+  PHX_CUDA_TRY(cudaLaunchKernelEx(&lc, kern, p.map_a, p.map_b, p.map_c, mr, rope, norm, Mll, N, K, err_flag, counters), err);
   return PHX_OK;
+}
+
+template <int BN, bool PAIR>
+phx_status launch_e(const GemmPlan& p, int epilogue, const GemmRope& rp, const GemmNorm& nm, int64_t M, int* err_flag,
+                    int num_sms, cudaStream_t stream, std::string& err) {
+  switch (epilogue) {
+    case EPI_STORE: return launch_t<BN, EPI_STORE, PAIR>(p, rp, nm, M, err_flag, num_sms, stream, err);
+    case EPI_RESIDUAL: return launch_t<BN, EPI_RESIDUAL, PAIR>(p, rp, nm, M, err_flag, num_sms, stream, err);
+    case EPI_GELU: return launch_t<BN, EPI_GELU, PAIR>(p, rp, nm, M, err_flag, num_sms, stream, err);
+    case EPI_ROPE: return launch_t<BN, EPI_ROPE, PAIR>(p, rp, nm, M, err_flag, num_sms, stream, err);
+  }
+  err = "gemm: unknown epilogue";
+  return PHX_E_ARG;
 }
 
 // ---- SIMT cross-check GEMM --------------------------------------------------------------------------
@@ -420,7 +502,7 @@ __global__ void gemm_simt_kernel(const bf16* __restrict__ A, const bf16* __restr
 }  // namespace
 
 phx_status gemm_plan_create(GemmPlan* plan, const bf16* A, const bf16* Wt, int64_t rows_max, int N, int K,
-                            bool narrow_tiles, std::string& err) {
+                            bool narrow_tiles, std::string& err, int pair) {
   if (N % 8 != 0 || K % 8 != 0 || N <= 0 || K <= 0 || rows_max <= 0) {
     err = "gemm: N and K must be positive multiples of 8";
     return PHX_E_ARG;
@@ -428,9 +510,12 @@ phx_status gemm_plan_create(GemmPlan* plan, const bf16* A, const bf16* Wt, int64
   plan->A = A; plan->Wt = Wt; plan->rows_max = rows_max; plan->N = N; plan->K = K;
   // 128-wide tiles leave room for six output slabs: deep residual prefetch for the HBM-bound short-K GEMMs
   plan->BN = (N % 256 == 0 && !narrow_tiles) ? 256 : 128;
+  // CTA pairs by default; PHX_GEMM=cta1 keeps every CTA on its own tile (for comparison)
+  const char* mode = getenv("PHX_GEMM");
+  plan->pair = pair >= 0 ? (pair != 0) : !(mode && strcmp(mode, "cta1") == 0);
   phx_status s = make_map(&plan->map_a, A, rows_max, K, BM, err);
   if (s != PHX_OK) return s;
-  s = make_map(&plan->map_b, Wt, N, K, plan->BN, err);
+  s = make_map(&plan->map_b, Wt, N, K, plan->pair ? plan->BN / 2 : plan->BN, err);
   if (s != PHX_OK) return s;
   plan->ready = true;
   return PHX_OK;
@@ -470,22 +555,11 @@ phx_status gemm_launch(GemmPlan& p, const bf16* A, bf16* C, const bf16* R, int64
     p.r_ptr = R; p.r_rows = M;
   }
   if (p.BN == 256) {
-    switch (epilogue) {
-      case EPI_STORE: return launch_t<256, EPI_STORE>(p, rp, nm, M, err_flag, num_sms, stream, err);
-      case EPI_RESIDUAL: return launch_t<256, EPI_RESIDUAL>(p, rp, nm, M, err_flag, num_sms, stream, err);
-      case EPI_GELU: return launch_t<256, EPI_GELU>(p, rp, nm, M, err_flag, num_sms, stream, err);
-      case EPI_ROPE: return launch_t<256, EPI_ROPE>(p, rp, nm, M, err_flag, num_sms, stream, err);
-    }
-  } else {
-    switch (epilogue) {
-      case EPI_STORE: return launch_t<128, EPI_STORE>(p, rp, nm, M, err_flag, num_sms, stream, err);
-      case EPI_RESIDUAL: return launch_t<128, EPI_RESIDUAL>(p, rp, nm, M, err_flag, num_sms, stream, err);
-      case EPI_GELU: return launch_t<128, EPI_GELU>(p, rp, nm, M, err_flag, num_sms, stream, err);
-      case EPI_ROPE: return launch_t<128, EPI_ROPE>(p, rp, nm, M, err_flag, num_sms, stream, err);
-    }
+    return p.pair ? launch_e<256, true>(p, epilogue, rp, nm, M, err_flag, num_sms, stream, err)
+                  : launch_e<256, false>(p, epilogue, rp, nm, M, err_flag, num_sms, stream, err);
   }
-  err = "gemm: unknown epilogue";
-  return PHX_E_ARG;
+  return p.pair ? launch_e<128, true>(p, epilogue, rp, nm, M, err_flag, num_sms, stream, err)
+                : launch_e<128, false>(p, epilogue, rp, nm, M, err_flag, num_sms, stream, err);
 }
 
 phx_status gemm_simt_launch(const bf16* A, const bf16* Wt, bf16* C, const bf16* R, int64_t M, int N, int K,
