@@ -114,6 +114,7 @@ struct phx_engine {
   bool prefetch_valid = false;
   phx_rank_batch prefetch_key;
 
+  unsigned long long* gemm_counters = nullptr;   // PHX_GEMM_COUNTERS: [role][total, operand wait, accumulator wait]
   int last_batch = 0;
   int last_launches = 0;
   bool debug_taps = false;
@@ -137,7 +138,7 @@ struct ProfScope {
       e->prof_events.push_back({cls, {a, b}});
     }
     auto& pe = e->prof_events[e->prof_used++];
-    pe.first = cls;
+    pe.first = cls;   // low byte: kernel class; next byte: optional sub-class
     cudaEventRecord(pe.second.first, e->stream);
     stop = pe.second.second;
   }
@@ -146,7 +147,7 @@ struct ProfScope {
     if (e->sync_debug) {   // PHX_SYNC_DEBUG=1: find the launch an asynchronous error belongs to
       cudaError_t ce = cudaStreamSynchronize(e->stream);
       if (ce != cudaSuccess)
-        fprintf(stderr, "[phx sync-debug] launch #%d (kernel class %d): %s\n", e->last_launches, cls_, cudaGetErrorString(ce));
+        fprintf(stderr, "[phx sync-debug] launch #%d (kernel class %d): %s\n", e->last_launches, cls_ & 0xff, cudaGetErrorString(ce));
     }
   }
   int cls_ = -1;
@@ -241,7 +242,7 @@ phx_status upload_bf16(phx_engine* e, bf16** dst, const float* host, int64_t row
 
 phx_status do_gemm(phx_engine* e, GemmPlan& p, const bf16* A, bf16* Cc, const bf16* R, int64_t M, int epi,
                    const GemmRope* rope = nullptr, const GemmNorm* norm = nullptr) {
-  ProfScope ps(e, KC_GEMM);
+  ProfScope ps(e, KC_GEMM | ((epi + 1) << 8));   // sub-class = epilogue, for the optional per-GEMM breakdown
   e->last_launches++;
   if (e->use_simt_gemm) return gemm_simt_launch(A, p.Wt, Cc, R, M, p.N, p.K, epi, e->stream, e->err);
   return gemm_launch(p, A, Cc, R, M, epi, rope, norm, e->err_flag, e->num_sms, e->stream, e->err);
@@ -488,6 +489,16 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
     TRY(gemm_plan_create(&L.p_out, e->attn, L.w_out_t, M, e->D, e->HD, e->HD <= 1024 && !cfg->primer_norm, e->err));
     TRY(gemm_plan_create(&L.p_up, e->hbuf, L.w_up_t, M, e->F, e->D, false, e->err));
     TRY(gemm_plan_create(&L.p_down, e->ffn, L.w_down_t, M, e->D, e->F, false, e->err));
+    if (getenv("PHX_GEMM_COUNTERS")) {   // diagnostics: MMA-issuer wait counters by role, summed over layers and forwards
+      if (!e->gemm_counters) {
+        CU(cudaMalloc(reinterpret_cast<void**>(&e->gemm_counters), 4 * 3 * sizeof(unsigned long long)));
+        CU(cudaMemset(e->gemm_counters, 0, 4 * 3 * sizeof(unsigned long long)));
+      }
+      L.p_qkv.counters = L.p_qkv_f.counters = e->gemm_counters;
+      L.p_out.counters = e->gemm_counters + 3;
+      L.p_up.counters = L.p_up_f.counters = e->gemm_counters + 6;
+      L.p_down.counters = e->gemm_counters + 9;
+    }
   }
   if (e->V + e->NC > 0) TRY(dev_alloc(e, &e->unembed_t, (size_t)(e->V + e->NC) * e->D));
   // staging for the host entry point
@@ -516,6 +527,7 @@ void phx_engine_destroy(phx_engine* e) {
   if (e->stream) cudaStreamSynchronize(e->stream);
   for (auto p : e->ipc_opened) if (p) cudaIpcCloseMemHandle(p);
   auto fr = [](void* p) { if (p) cudaFree(p); };
+  fr(e->gemm_counters);
   fr(e->table); fr(e->action_table); fr(e->surface_table); fr(e->final_norm); fr(e->unembed_t);
   for (auto& L : e->layers) {
     fr(L.pre_attn_norm); fr(L.pre_ffn_norm); fr(L.post_attn_norm); fr(L.post_ffn_norm); fr(L.q_norm); fr(L.k_norm);
@@ -773,11 +785,34 @@ phx_status phx_profile_read(phx_engine* e, float* ms_by_class, int32_t* launches
   cudaSetDevice(e->device);
   PHX_CUDA_TRY(cudaStreamSynchronize(e->stream), e->err);
   for (int i = 0; i < KC_COUNT; ++i) { ms_by_class[i] = 0.f; launches_by_class[i] = 0; }
+  float sub_ms[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  int sub_n[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  int res_seen = 0;
   for (size_t i = 0; i < e->prof_used; ++i) {
     float ms = 0.f;
     PHX_CUDA_TRY(cudaEventElapsedTime(&ms, e->prof_events[i].second.first, e->prof_events[i].second.second), e->err);
-    ms_by_class[e->prof_events[i].first] += ms;
-    launches_by_class[e->prof_events[i].first] += 1;
+    const int cls = e->prof_events[i].first & 0xff;
+    int sub = (e->prof_events[i].first >> 8) & 0xff;
+    ms_by_class[cls] += ms;
+    launches_by_class[cls] += 1;
+    if (cls == KC_GEMM && sub > 0) {
+      // the two residual GEMMs of a layer alternate: out-projection first, then the FFN down-projection
+      if (sub - 1 == EPI_RESIDUAL) sub = (res_seen++ & 1) ? 6 : 5;
+      sub_ms[sub & 7] += ms; sub_n[sub & 7] += 1;
+    }
+  }
+  if (e->gemm_counters) {
+    unsigned long long h[12];
+    PHX_CUDA_TRY(cudaMemcpy(h, e->gemm_counters, sizeof(h), cudaMemcpyDeviceToHost), e->err);
+    const char* role[4] = {"qkv", "out", "up", "down"};
+    for (int r = 0; r < 4; ++r)
+      fprintf(stderr, "[phx gemm counters] %s: MMA issuer waiting for operands %.1f%%, for a free accumulator %.1f%%\n", role[r],
+              100.0 * h[3 * r + 1] / (double)(h[3 * r] ? h[3 * r] : 1), 100.0 * h[3 * r + 2] / (double)(h[3 * r] ? h[3 * r] : 1));
+  }
+  if (getenv("PHX_PROF_GEMM")) {   // diagnostics: GEMM time of the last forward by role
+    fprintf(stderr, "[phx gemm breakdown] qkv(store) %.3f ms/%d  qkv(rope) %.3f ms/%d  up(gelu) %.3f ms/%d  out(res) %.3f ms/%d  down(res) %.3f ms/%d\n",
+            sub_ms[1 + EPI_STORE], sub_n[1 + EPI_STORE], sub_ms[1 + EPI_ROPE], sub_n[1 + EPI_ROPE], sub_ms[1 + EPI_GELU],
+            sub_n[1 + EPI_GELU], sub_ms[5], sub_n[5], sub_ms[6], sub_n[6]);
   }
   return PHX_OK;
 }

@@ -509,10 +509,16 @@ phx_status gemm_plan_create(GemmPlan* plan, const bf16* A, const bf16* Wt, int64
   }
   plan->A = A; plan->Wt = Wt; plan->rows_max = rows_max; plan->N = N; plan->K = K;
   // 128-wide tiles leave room for six output slabs: deep residual prefetch for the HBM-bound short-K GEMMs
-  plan->BN = (N % 256 == 0 && !narrow_tiles) ? 256 : 128;
+  { const char* t = getenv("PHX_GEMM_TILES");   // diagnostics: wide | narrow overrides the caller's choice
+    if (t && strcmp(t, "wide") == 0) narrow_tiles = false;
+    if (t && strcmp(t, "narrow") == 0) narrow_tiles = true; }
   // CTA pairs by default; PHX_GEMM=cta1 keeps every CTA on its own tile (for comparison)
   const char* mode = getenv("PHX_GEMM");
   plan->pair = pair >= 0 ? (pair != 0) : !(mode && strcmp(mode, "cta1") == 0);
+  // a pair fills 128 + BN/2 operand rows per CTA and k-step: the wide tile is the cheaper one per FLOP there
+  // (out-projection, N = K = 512: 0.100 ms wide against 0.146 ms narrow)
+  if (plan->pair && !(getenv("PHX_GEMM_TILES") && strcmp(getenv("PHX_GEMM_TILES"), "narrow") == 0)) narrow_tiles = false;
+  plan->BN = (N % 256 == 0 && !narrow_tiles) ? 256 : 128;
   phx_status s = make_map(&plan->map_a, A, rows_max, K, BM, err);
   if (s != PHX_OK) return s;
   s = make_map(&plan->map_b, Wt, N, K, plan->pair ? plan->BN / 2 : plan->BN, err);
