@@ -28,12 +28,15 @@ namespace {
 
 using namespace sm100;
 constexpr int BM = 128;
-constexpr int GEMM_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
+// threads: TMA warp, MMA warp, NG epilogue groups of four warps
+constexpr int gemm_threads(int ng) { return 64 + ng * 128; }
 
-template <int BN, bool PAIR>
+template <int BN, bool PAIR, int NG>
 struct Cfg {
+  static_assert(NG == 2 || (NG == 4 && PAIR), "four epilogue groups need the smaller stages of a CTA pair");
   static constexpr int STAGES = PAIR ? 5 : 4;
-  static constexpr int NSLAB = PAIR ? ((BN == 256) ? 4 : 6) : ((BN == 256) ? 2 : 6);   // output slab buffers (half per epilogue group)
+  // output slab buffers, NSLAB / NG per epilogue group
+  static constexpr int NSLAB = NG == 4 ? 4 : (PAIR ? ((BN == 256) ? 4 : 6) : ((BN == 256) ? 2 : 6));
   static constexpr int B_ROWS = PAIR ? BN / 2 : BN;   // rows of the W tile this CTA loads
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = B_ROWS * BK * 2;
@@ -46,7 +49,6 @@ struct Cfg {
 // ---- epilogue helpers -----------------------------------------------------------------------------
 constexpr int SLAB_COLS = 64;                 // one output slab = 128 rows x 64 bf16 columns = 128-byte rows
 constexpr int SLAB_BYTES = BM * SLAB_COLS * 2;
-constexpr int EPI_THREADS = 256;
 
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -75,59 +77,18 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// RoPE on the q / k head parts held in one 64-column slab (layers.py:52-67, 784-788): pairs (j, j + dh/2)
-__device__ __forceinline__ void rope_slab(float (&v)[64], const GemmRope& rp, int col0, long long row) {
-  const int t = (int)(row % rp.T);
-  const int pos = t < rp.pos_cap ? t : rp.pos_cap;
-  if (rp.dh == 64) {
-    const int kind = (col0 >> 6) % rp.group;
-    if (kind > rp.g) return;  // v part
-    const float4* c4 = reinterpret_cast<const float4*>(rp.cos_tab + (long long)pos * 32);
-    const float4* s4 = reinterpret_cast<const float4*>(rp.sin_tab + (long long)pos * 32);
-#pragma unroll
-    for (int jj = 0; jj < 8; ++jj) {
-      const float4 c = __ldg(c4 + jj), s = __ldg(s4 + jj);
-      const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {s.x, s.y, s.z, s.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int j = jj * 4 + e;
-        const float x1 = v[j], x2 = v[j + 32];
-        v[j] = x1 * cc[e] - x2 * ss[e];
-        v[j + 32] = x2 * cc[e] + x1 * ss[e];
-      }
-    }
-  } else {  // dh == 32: two head parts per slab
-    const float4* c4 = reinterpret_cast<const float4*>(rp.cos_tab + (long long)pos * 16);
-    const float4* s4 = reinterpret_cast<const float4*>(rp.sin_tab + (long long)pos * 16);
-#pragma unroll
-    for (int part = 0; part < 2; ++part) {
-      const int kind = ((col0 >> 5) + part) % rp.group;
-      if (kind > rp.g) continue;
-#pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
-        const float4 c = __ldg(c4 + jj), s = __ldg(s4 + jj);
-        const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {s.x, s.y, s.z, s.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = part * 32 + jj * 4 + e;
-          const float x1 = v[j], x2 = v[j + 16];
-          v[j] = x1 * cc[e] - x2 * ss[e];
-          v[j + 16] = x2 * cc[e] + x1 * ss[e];
-        }
-      }
-    }
-  }
-}
-
-template <int BN, int EPI, bool PAIR>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+template <int BN, int EPI, bool PAIR, int NG>
+__global__ void __launch_bounds__(gemm_threads(NG), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_r,
                     GemmRope rope, GemmNorm norm, long long M, int N, int K, int* err_flag,
                     unsigned long long* counters) {
   // C and R may be the same buffer (in-place residual update): a slab is fetched before it is written back,
   // and no other CTA touches the tile.
-  using cfg = Cfg<BN, PAIR>;
+  using cfg = Cfg<BN, PAIR, NG>;
+  constexpr int SLABS = BN / SLAB_COLS;
+  // epilogue threads that drain one accumulator (a tile with fewer slabs than groups is shared by SLABS groups)
+  constexpr int DRAIN_THREADS = (SLABS < NG ? SLABS : NG) * 128 * (PAIR ? 2 : 1);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
   const uint32_t slab_base = smem_base + cfg::STAGES * cfg::STAGE_BYTES;   // output slab buffers
@@ -155,7 +116,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (threadIdx.x == 0) {
     for (int s = 0; s < cfg::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     // a pair's accumulators are drained by the epilogue threads of both CTAs, counted on the issuing CTA
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), PAIR ? 2 * EPI_THREADS : EPI_THREADS); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), DRAIN_THREADS); }
     for (int a = 0; a < cfg::NSLAB; ++a) mbar_init(res_bar(a), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -249,13 +210,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else {
-    // ---------------- epilogue (warps 2..9: two groups of four warps) ----------------
-    // Work item = one 64-column slab of a tile; group gidx takes the items with q % 2 == gidx and owns NB
+    // ---------------- epilogue (warps 2..: NG groups of four warps) ----------------
+    // Work item = one 64-column slab of a tile; group gidx takes the items with q % NG == gidx and owns NB
     // slab buffers, an issuing thread and named barrier 1 + gidx.  Per item: TMEM -> registers -> fused op
     // -> swizzled shared-memory slab -> one TMA bulk store.  The residual slab arrives by TMA into the same
     // buffer (up to NB - 1 items ahead, at least one) and is updated in place.
-    constexpr int SLABS = BN / SLAB_COLS;
-    constexpr int NB = cfg::NSLAB / 2;
+    constexpr int NB = cfg::NSLAB / NG;
     constexpr bool RES = (EPI == EPI_RESIDUAL);
     constexpr int DIST = NB - 1;                        // residual prefetch distance (items of this group)
     const int ew = warp - 2;
@@ -273,10 +233,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       else mbar_arrive(a ? tempty1 : tempty0);
     };
     const long long total_items = my_tiles * SLABS;
-    const long long my_items = (total_items > gidx) ? (total_items - gidx + 1) / 2 : 0;
+    const long long my_items = (total_items > gidx) ? (total_items - gidx + NG - 1) / NG : 0;
     const uint32_t gslab = slab_base + gidx * NB * SLAB_BYTES;
     auto coords = [&](long long i, long long& m0, int& c0) {   // i = item index inside this group
-      const long long q = 2 * i + gidx;
+      const long long q = (long long)NG * i + gidx;
       const long long tile = first_tile + (q / SLABS) * tile_step;
       m0 = (tile / n_tiles) * TILE_M + rank * BM;
       c0 = (int)(tile % n_tiles) * BN + (int)(q % SLABS) * SLAB_COLS;
@@ -292,13 +252,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     float rstd = 1.0f;   // 1/rms of this thread's row, refreshed at each tile
     for (long long i = 0; i < my_items; ++i) {
-      const long long q = 2 * i + gidx;
+      const long long q = (long long)NG * i + gidx;
       const int s = (int)(q % SLABS);
       const uint32_t it = (uint32_t)(q / SLABS), acc = it & 1, acc_phase = (it >> 1) & 1;
       const int bi = (int)(i % NB);
       const uint32_t slab = gslab + bi * SLAB_BYTES;
       long long m0; int c0; coords(i, m0, c0);
-      const bool first_of_tile = (s < 2);               // this group's first slab of the tile
+      const bool first_of_tile = (s < NG);              // this group's first slab of the tile
       // RMSNorm folded into this GEMM: the row's 1/rms comes from the sum of squares its producer left behind
       // (partials in fixed slots, summed in slot order: deterministic), the gain is folded into the weights.
       // Read once per tile, before the wait on the accumulator, so the loads hide behind it.
@@ -319,7 +279,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
-      const bool last_of_tile = (s + 2 >= SLABS);       // ... and its last
+      const bool last_of_tile = (s + NG >= SLABS);      // ... and its last
       if (RES && issuer && i + DIST < my_items) {
         // the buffer of item i + DIST was last used by item i - 1: its store must have drained
         bulk_wait_read<0>();
@@ -345,20 +305,56 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (ok) {
         tc_fence_after();
         if (EPI == EPI_ROPE) {
-          uint32_t r[64];
-          tmem_ld32(taddr, r);
-          tmem_ld32(taddr + 32, r + 32);
-          if (last_of_tile) release_acc(acc);
-          float v[64];
+          // RoPE on the q / k head parts of this slab (layers.py:52-67, 784-788), pairs (j, j + dh/2), in two
+          // passes of 16 pairs so that only 32 values are live: head dim 64 = one part per slab, pass p rotates
+          // columns [16p, 16p+16) against [32+16p, 48+16p); head dim 32 = pass p is the slab's p-th part.
+          const long long row = m0 + row_in_tile;
+          const int t = (int)(row % rope.T);
+          const int pos = t < rope.pos_cap ? t : rope.pos_cap;
+          const bool d64 = (rope.dh == 64);
+          const int half = rope.dh >> 1;
 #pragma unroll
-          for (int k = 0; k < 64; ++k) v[k] = round_bf(__uint_as_float(r[k]) * rstd);   // Linear output is bf16
-          rope_slab(v, rope, c0, m0 + row_in_tile);
+          for (int p = 0; p < 2; ++p) {
+            const int lo_col = d64 ? 16 * p : 32 * p;
+            const int hi_col = d64 ? 32 + 16 * p : 32 * p + 16;
+            uint32_t rl[16], rh[16];
+            tmem_ld16_nowait(taddr + lo_col, rl);
+            tmem_ld16_nowait(taddr + hi_col, rh);
+            tmem_ld_wait();
+            if (p == 1 && last_of_tile) release_acc(acc);
+            const int kind = d64 ? (c0 >> 6) % rope.group : ((c0 >> 5) + p) % rope.group;
+            float lo[16], hi[16];
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            uint4 o;
-            o.x = pack_bf2(v[c * 8 + 0], v[c * 8 + 1]); o.y = pack_bf2(v[c * 8 + 2], v[c * 8 + 3]);
-            o.z = pack_bf2(v[c * 8 + 4], v[c * 8 + 5]); o.w = pack_bf2(v[c * 8 + 6], v[c * 8 + 7]);
-            st_shared_v4(row_addr + ((uint32_t)(c ^ sw) << 4), o);
+            for (int k = 0; k < 16; ++k) {   // Linear output is bf16
+              lo[k] = round_bf(__uint_as_float(rl[k]) * rstd);
+              hi[k] = round_bf(__uint_as_float(rh[k]) * rstd);
+            }
+            if (kind <= rope.g) {   // q or k part (v parts pass through)
+              const float4* c4 = reinterpret_cast<const float4*>(rope.cos_tab + (long long)pos * half + (d64 ? 16 * p : 0));
+              const float4* s4 = reinterpret_cast<const float4*>(rope.sin_tab + (long long)pos * half + (d64 ? 16 * p : 0));
+#pragma unroll
+              for (int jj = 0; jj < 4; ++jj) {
+                const float4 c = __ldg(c4 + jj), sn = __ldg(s4 + jj);
+                const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int j = jj * 4 + e;
+                  const float x1 = lo[j], x2 = hi[j];
+                  lo[j] = x1 * cc[e] - x2 * ss[e];
+                  hi[j] = x2 * cc[e] + x1 * ss[e];
+                }
+              }
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint4 o;
+              o.x = pack_bf2(lo[h * 8 + 0], lo[h * 8 + 1]); o.y = pack_bf2(lo[h * 8 + 2], lo[h * 8 + 3]);
+              o.z = pack_bf2(lo[h * 8 + 4], lo[h * 8 + 5]); o.w = pack_bf2(lo[h * 8 + 6], lo[h * 8 + 7]);
+              st_shared_v4(row_addr + ((uint32_t)(((lo_col >> 3) + h) ^ sw) << 4), o);
+              o.x = pack_bf2(hi[h * 8 + 0], hi[h * 8 + 1]); o.y = pack_bf2(hi[h * 8 + 2], hi[h * 8 + 3]);
+              o.z = pack_bf2(hi[h * 8 + 4], hi[h * 8 + 5]); o.w = pack_bf2(hi[h * 8 + 6], hi[h * 8 + 7]);
+              st_shared_v4(row_addr + ((uint32_t)(((hi_col >> 3) + h) ^ sw) << 4), o);
+            }
           }
         } else {
           float ss_out = 0.f;
@@ -419,14 +415,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 template <int BN, int EPI, bool PAIR>
 phx_status launch_t(const GemmPlan& p, const GemmRope& rope, const GemmNorm& norm, int64_t M, int* err_flag, int num_sms,
                     cudaStream_t stream, std::string& err) {
-  using cfg = Cfg<BN, PAIR>;
-  auto kern = gemm_tcgen05_kernel<BN, EPI, PAIR>;
+  // the residual epilogues are fed by TMA prefetch and keep up with two groups; the others (RoPE, GELU, norm
+  // scaling) are bound by the latency of each thread's instruction stream and get four groups where a pair's
+  // smaller stages leave room for the slab buffers
+  constexpr int NG = (PAIR && EPI != EPI_RESIDUAL) ? 4 : 2;
+  using cfg = Cfg<BN, PAIR, NG>;
+  auto kern = gemm_tcgen05_kernel<BN, EPI, PAIR, NG>;
   static bool attr_set = false;
   static int max_pairs = 0;
   cudaLaunchConfig_t lc;
   memset(&lc, 0, sizeof(lc));
   cudaLaunchAttribute attr[1];
-  lc.blockDim = dim3(GEMM_THREADS);
+  lc.blockDim = dim3(gemm_threads(NG));
   lc.dynamicSmemBytes = cfg::SMEM_BYTES;
   lc.stream = stream;
   if (PAIR) {
