@@ -93,7 +93,7 @@ struct GemmPlan {
   int N = 0, K = 0, BN = 0;
   bool pair = false;   // two CTAs of a cluster share each 256-row tile (tcgen05 cta_group::2)
   bool ready = false;
-  unsigned long long* counters = nullptr;  // optional device counters [3]: MMA issuer cycles total / waiting for
+  unsigned long long* counters = nullptr;  // optional device counters [8]: MMA issuer cycles total / waiting for
                                            // operands / waiting for a free accumulator (diagnostics)
 };
 

@@ -491,13 +491,13 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
     TRY(gemm_plan_create(&L.p_down, e->ffn, L.w_down_t, M, e->D, e->F, false, e->err));
     if (getenv("PHX_GEMM_COUNTERS")) {   // diagnostics: MMA-issuer wait counters by role, summed over layers and forwards
       if (!e->gemm_counters) {
-        CU(cudaMalloc(reinterpret_cast<void**>(&e->gemm_counters), 4 * 3 * sizeof(unsigned long long)));
-        CU(cudaMemset(e->gemm_counters, 0, 4 * 3 * sizeof(unsigned long long)));
+        CU(cudaMalloc(reinterpret_cast<void**>(&e->gemm_counters), 4 * 8 * sizeof(unsigned long long)));
+        CU(cudaMemset(e->gemm_counters, 0, 4 * 8 * sizeof(unsigned long long)));
       }
       L.p_qkv.counters = L.p_qkv_f.counters = e->gemm_counters;
-      L.p_out.counters = e->gemm_counters + 3;
-      L.p_up.counters = L.p_up_f.counters = e->gemm_counters + 6;
-      L.p_down.counters = e->gemm_counters + 9;
+      L.p_out.counters = e->gemm_counters + 8;
+      L.p_up.counters = L.p_up_f.counters = e->gemm_counters + 16;
+      L.p_down.counters = e->gemm_counters + 24;
     }
   }
   if (e->V + e->NC > 0) TRY(dev_alloc(e, &e->unembed_t, (size_t)(e->V + e->NC) * e->D));
@@ -802,12 +802,12 @@ phx_status phx_profile_read(phx_engine* e, float* ms_by_class, int32_t* launches
     }
   }
   if (e->gemm_counters) {
-    unsigned long long h[12];
+    unsigned long long h[32];
     PHX_CUDA_TRY(cudaMemcpy(h, e->gemm_counters, sizeof(h), cudaMemcpyDeviceToHost), e->err);
     const char* role[4] = {"qkv", "out", "up", "down"};
     for (int r = 0; r < 4; ++r)
       fprintf(stderr, "[phx gemm counters] %s: MMA issuer waiting for operands %.1f%%, for a free accumulator %.1f%%\n", role[r],
-              100.0 * h[3 * r + 1] / (double)(h[3 * r] ? h[3 * r] : 1), 100.0 * h[3 * r + 2] / (double)(h[3 * r] ? h[3 * r] : 1));
+              100.0 * h[8 * r + 1] / (double)(h[8 * r] ? h[8 * r] : 1), 100.0 * h[8 * r + 2] / (double)(h[8 * r] ? h[8 * r] : 1));
   }
   if (getenv("PHX_PROF_GEMM")) {   // diagnostics: GEMM time of the last forward by role
     fprintf(stderr, "[phx gemm breakdown] qkv(store) %.3f ms/%d  qkv(rope) %.3f ms/%d  up(gelu) %.3f ms/%d  out(res) %.3f ms/%d  down(res) %.3f ms/%d\n",
@@ -956,7 +956,7 @@ phx_status phx_gemm_device(int32_t device, const uint16_t* A, const uint16_t* Wt
   } else {
     GemmPlan plan;
     s = gemm_plan_create(&plan, (const bf16*)A, (const bf16*)Wt, M, N, K, epilogue == 1 && K <= 1024, err, impl == 2 ? 0 : -1);
-    if (getenv("PHX_GEMM_COUNTERS")) { cudaMalloc(&ctr, 24); cudaMemset(ctr, 0, 24); plan.counters = ctr; }
+    if (getenv("PHX_GEMM_COUNTERS")) { cudaMalloc(&ctr, 64); cudaMemset(ctr, 0, 64); plan.counters = ctr; }
     cudaEventRecord(e0, 0);
     if (s == PHX_OK && (epilogue < 0 || epilogue > 2)) { err = "phx_gemm_device: epilogue must be 0, 1 or 2"; s = PHX_E_ARG; }
     if (s == PHX_OK) s = gemm_launch(plan, (const bf16*)A, (bf16*)C, (const bf16*)R, M, epilogue, nullptr, nullptr, flag, prop.multiProcessorCount, 0, err);
@@ -971,8 +971,10 @@ phx_status phx_gemm_device(int32_t device, const uint16_t* A, const uint16_t* Wt
     if (hflag) { err = "a bounded device-side wait ran out (GEMM pipeline)"; s = PHX_E_TIMEOUT; }
   }
   if (ctr) {
-    unsigned long long h[3] = {0, 0, 0};
-    cudaMemcpy(h, ctr, 24, cudaMemcpyDeviceToHost);
+    unsigned long long h[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    cudaMemcpy(h, ctr, 64, cudaMemcpyDeviceToHost);
+    fprintf(stderr, "[phx gemm timeline, CTA 0] entry -> first MMA wait %.1f us, MMA window %.1f us, last MMA issued -> CTA done %.1f us\n",
+            (h[4] - h[3]) * 1e-3, (h[5] - h[4]) * 1e-3, (h[6] - h[5]) * 1e-3);
     fprintf(stderr, "[phx gemm counters] MMA issuer cycles (sum over CTAs): total %llu, waiting for operands %llu (%.1f%%), "
             "waiting for a free accumulator %llu (%.1f%%)\n", h[0], h[1], 100.0 * h[1] / (double)(h[0] ? h[0] : 1), h[2],
             100.0 * h[2] / (double)(h[0] ? h[0] : 1));

@@ -103,6 +103,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (counters && blockIdx.x == 0 && threadIdx.x == 0) counters[3] = globaltimer_ns();   // diagnostics: kernel entry
   constexpr int TILE_M = PAIR ? 2 * BM : BM;          // rows of one work tile (of the CTA pair)
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u; // 0 = the CTA that issues the pair's MMAs
   const long long first_tile = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
@@ -174,6 +175,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       bool ok = true;
       long long cnt_tempty = 0, cnt_full = 0;
       const long long t_start = counters ? clock64() : 0;
+      if (counters && blockIdx.x == 0) counters[4] = globaltimer_ns();   // first MMA wait
       for (long long tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++it) {
         const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
         long long c0 = counters ? clock64() : 0;
@@ -207,6 +209,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         atomicAdd(&counters[0], (unsigned long long)(clock64() - t_start));
         atomicAdd(&counters[1], (unsigned long long)cnt_full);
         atomicAdd(&counters[2], (unsigned long long)cnt_tempty);
+        if (blockIdx.x == 0) counters[5] = globaltimer_ns();   // last MMA issued
       }
     }
   } else {
@@ -410,6 +413,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (PAIR) tmem_dealloc_pair(tmem_base, cfg::TMEM_COLS);
     else tmem_dealloc(tmem_base, cfg::TMEM_COLS);
   }
+  if (counters && blockIdx.x == 0 && threadIdx.x == 0) counters[6] = globaltimer_ns();   // CTA 0 done
 }
 
 template <int BN, int EPI, bool PAIR>
