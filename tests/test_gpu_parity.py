@@ -83,9 +83,10 @@ def test_gemm_tcgen05_vs_fp32(torch, M, N, K, epi):
 
 @pytest.mark.parametrize("dh,S,Cn,H", [(32, 32, 8, 4), (64, 128, 64, 2), (128, 96, 40, 2), (64, 200, 56, 3), (128, 300, 200, 1)])
 @pytest.mark.parametrize("cap", [(-1.0, 0), (30.0, 1), (30.0, 2)])
-@pytest.mark.parametrize("impl", ["tcgen05", "mma", "resident"])
+@pytest.mark.parametrize("impl", ["tcgen05", "mma", "resident", "strip"])
 def test_ranker_attention_vs_oracle(torch, monkeypatch, dh, S, Cn, H, cap, impl):
-    """Both kernels: tcgen05/TMEM (head dim 64 / 128; dim 32 falls to mma.sync) and the mma.sync one."""
+    """tcgen05/TMEM kernels (head dim 64 / 128; dim 32 falls to mma.sync), the streaming mma.sync kernel and the
+    resident-history mma.sync kernel ("strip": head dim 64, <= 128 history keys; other shapes fall through)."""
     from x_algorithm_b200.engine import ranker_attention
     monkeypatch.setenv("PHX_ATTN", impl)   # "resident" applies to head dim 64 with <= 128 history keys, else tcgen05
     B, T = 3, S + Cn

@@ -317,6 +317,279 @@ phx_status launch_dh(const AttnArgs& a, cudaStream_t stream, std::string& err) {
   return PHX_OK;
 }
 
+
+// ---- resident-history variant for head dim 64 and a history of at most 128 keys --------------------------------
+// One CTA = one (batch, head): the history K/V (<= 128 x 64) is loaded once and stays in shared memory while the
+// CTA walks over all query tiles of the request.  Each warp owns a 16-row strip per tile and runs its own cp.async
+// pipeline: the strip's Q rows for tile i+1 are requested right after tile i's Q fragments are in registers, its
+// own K/V rows (for the candidates' self key) right after tile i's self term, so every load has a whole tile of
+// tensor work to hide behind and, after the prologue, no CTA-wide barrier is needed.  Rows are 128 bytes with the
+// 16-byte chunk index XOR-ed with (row & 7): conflict-free ldmatrix without padding, 96 KB per CTA, two CTAs per SM.
+constexpr int STRIP_HIST = 128;
+constexpr int STRIP_SMEM = 2 * STRIP_HIST * 64 * 2 + ATT_WARPS * 4 * 16 * 64 * 2 + (STRIP_HIST + 4) * (int)sizeof(int);
+
+__device__ __forceinline__ int swz(int row, int chunk) { return row * 64 + ((chunk ^ (row & 7)) << 3); }   // element offset
+
+template <bool CAP>
+__global__ void __launch_bounds__(ATT_THREADS, 2) ranker_attention_strip_kernel(AttnArgs a) {
+  constexpr int DH = 64, KSTEPS = 4, DT = 8, CH = 8;
+  extern __shared__ __align__(128) uint8_t asm_raw[];
+  bf16* hk_s = reinterpret_cast<bf16*>(asm_raw);                 // [128][64] history K
+  bf16* hv_s = hk_s + STRIP_HIST * 64;                            // [128][64] history V
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  bf16* wbase = hv_s + STRIP_HIST * 64 + warp * (4 * 16 * 64);    // this warp's strip buffers
+  auto wq = [&](int i) { return wbase + (i & 1) * (16 * 64); };   // Q strip (double-buffered), later the output strip
+  bf16* wks = wbase + 2 * 16 * 64;                                // K rows of the strip's own tokens
+  bf16* wvs = wbase + 3 * 16 * 64;                                // V rows of the strip's own tokens
+  int* skey_ok = reinterpret_cast<int*>(hv_s + STRIP_HIST * 64 + ATT_WARPS * 4 * 16 * 64);   // [128]
+  int* sall_ok = skey_ok + STRIP_HIST;                                                       // [4] per 32 keys
+  const float csc = CAP ? 1.0f : a.sm_scale * 1.4426950408889634f;
+
+  const int b = blockIdx.y, h = blockIdx.x;
+  const int hk = h / (a.Hq / a.Hkv);
+  const int g = lane >> 2, t4 = lane & 3;
+  const int T = a.T;
+  const long long tok0 = (long long)b * T;
+  const int n_hist = a.hist_len < T ? a.hist_len : T;
+  const int n_blocks = (n_hist + KB - 1) / KB;
+  const int n_tiles = (T + QROWS - 1) / QROWS;
+  const bf16* qbase = a.q + (long long)h * a.q_head_stride;
+  const bf16* kbase = a.k + (long long)hk * a.k_head_stride;
+  const bf16* vbase = a.v + (long long)hk * a.v_head_stride;
+
+  auto load_q = [&](int tile, bf16* dst) {     // this warp's 16 Q rows of `tile`
+    const int r0 = tile * QROWS + warp * 16;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = lane + 32 * k, r = c >> 3, ch = c & 7;
+      const bool ok = (r0 + r) < T;
+      const long long tok = tok0 + (ok ? r0 + r : 0);
+      cp16((uint32_t)__cvta_generic_to_shared(dst + swz(r, ch)), qbase + tok * a.q_tok_stride + ch * 8, ok);
+    }
+  };
+  auto strip_has_cand = [&](int tile) {
+    const int r0 = tile * QROWS + warp * 16;
+    return r0 < T && r0 + 16 > n_hist;
+  };
+  auto load_own_kv = [&](int tile) {
+    const int r0 = tile * QROWS + warp * 16;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = lane + 32 * k, r = c >> 3, ch = c & 7;
+      const bool ok = (r0 + r) < T;
+      const long long tok = tok0 + (ok ? r0 + r : 0);
+      cp16((uint32_t)__cvta_generic_to_shared(wks + swz(r, ch)), kbase + tok * a.k_tok_stride + ch * 8, ok);
+      cp16((uint32_t)__cvta_generic_to_shared(wvs + swz(r, ch)), vbase + tok * a.v_tok_stride + ch * 8, ok);
+    }
+  };
+
+  // ---- prologue: history K/V for the CTA, strip 0 for each warp ----------------------------------------
+  for (int c = threadIdx.x; c < STRIP_HIST * CH; c += ATT_THREADS) {
+    const int kr = c >> 3, ch = c & 7;
+    const bool ok = kr < n_hist;
+    const long long tok = tok0 + (ok ? kr : 0);
+    cp16((uint32_t)__cvta_generic_to_shared(hk_s + swz(kr, ch)), kbase + tok * a.k_tok_stride + ch * 8, ok);
+    cp16((uint32_t)__cvta_generic_to_shared(hv_s + swz(kr, ch)), vbase + tok * a.v_tok_stride + ch * 8, ok);
+  }
+  if (threadIdx.x < STRIP_HIST) {   // warps 0..3
+    const int key = threadIdx.x;
+    const int ok = (key < n_hist) && (a.seg[tok0 + key] == 1);
+    skey_ok[key] = ok;
+    const int all32 = __all_sync(0xffffffffu, ok);
+    if (lane == 0) sall_ok[key >> 5] = all32;
+  }
+  load_q(0, wq(0));
+  if (strip_has_cand(0)) load_own_kv(0);
+  cp_commit();
+  cp_wait<0>();
+  __syncthreads();
+
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int q0 = tile * QROWS;
+    bf16* sq = wq(tile);
+    const int rq[2] = {q0 + warp * 16 + g, q0 + warp * 16 + g + 8};
+    int segq[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) segq[i] = (rq[i] < T) ? a.seg[tok0 + rq[i]] : 0;
+    const bool has_cand = strip_has_cand(tile);
+
+    if (tile > 0) { cp_wait<1>(); __syncwarp(); }   // this tile's Q strip has landed (its own K/V may still be in flight)
+    uint32_t qf[KSTEPS][4];
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks)
+      ldsm_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3],
+              (uint32_t)__cvta_generic_to_shared(sq + swz(lane & 15, ks * 2 + (lane >> 4))));
+    __syncwarp();
+    if (tile + 1 < n_tiles) load_q(tile + 1, wq(tile + 1));   // that buffer's last reader was tile-1's output copy
+    cp_commit();
+
+    float o[DT][4];
+#pragma unroll
+    for (int j = 0; j < DT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, mprev[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    if (q0 + warp * 16 < T) {
+      for (int blk = 0; blk < n_blocks; ++blk) {
+        const bf16* sk = hk_s + blk * KB * 64;     // KB is a multiple of 8: the swizzle phase is unchanged
+        const bf16* sv = hv_s + blk * KB * 64;
+        const int* kok = skey_ok + blk * KB;
+        float s[KB / 8][4];
+#pragma unroll
+        for (int j = 0; j < KB / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+          for (int j = 0; j < KB / 8; j += 2) {
+            uint32_t b0, b1, b2, b3;
+            const int kr = j * 8 + (lane & 7) + ((lane >> 4) << 3);
+            const int kc = ks * 2 + ((lane >> 3) & 1);
+            ldsm_x4(b0, b1, b2, b3, (uint32_t)__cvta_generic_to_shared(sk + swz(kr, kc)));
+            mma_bf16_16816(s[j], qf[ks], b0, b1);
+            mma_bf16_16816(s[j + 1], qf[ks], b2, b3);
+          }
+        }
+        if (CAP) {
+#pragma unroll
+          for (int j = 0; j < KB / 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[j][e] = scaled_logit(s[j][e], a.sm_scale, a.cap, a.cap_method);
+        }
+        if (!(sall_ok[blk * 2] & sall_ok[blk * 2 + 1])) {
+#pragma unroll
+          for (int j = 0; j < KB / 8; ++j) {
+            const int2 okp = *reinterpret_cast<const int2*>(&kok[j * 8 + 2 * t4]);
+            if (!okp.x) { s[j][0] = -INFINITY; s[j][2] = -INFINITY; }
+            if (!okp.y) { s[j][1] = -INFINITY; s[j][3] = -INFINITY; }
+          }
+        }
+        float bm[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < KB / 8; ++j) {
+          bm[0] = fmaxf(bm[0], fmaxf(s[j][0], s[j][1]));
+          bm[1] = fmaxf(bm[1], fmaxf(s[j][2], s[j][3]));
+        }
+        float alpha[2], mn[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          bm[i] = fmaxf(bm[i], __shfl_xor_sync(0xffffffffu, bm[i], 1));
+          bm[i] = fmaxf(bm[i], __shfl_xor_sync(0xffffffffu, bm[i], 2));
+          m[i] = fmaxf(m[i], bm[i] * csc);
+          mn[i] = (m[i] == -INFINITY) ? 0.f : m[i];
+          alpha[i] = ex2(mprev[i] - mn[i]);
+          mprev[i] = m[i];
+        }
+        uint32_t pf[KB / 16][4];
+        float ls[2] = {0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < KB / 8; ++j) {
+          float p[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int ri = e >> 1;
+            p[e] = ex2(fmaf(s[j][e], csc, -mn[ri]));
+            ls[ri] += p[e];
+          }
+          pf[j >> 1][(j & 1) * 2 + 0] = pack_bf2(p[0], p[1]);
+          pf[j >> 1][(j & 1) * 2 + 1] = pack_bf2(p[2], p[3]);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          ls[i] += __shfl_xor_sync(0xffffffffu, ls[i], 1);
+          ls[i] += __shfl_xor_sync(0xffffffffu, ls[i], 2);
+          l[i] = l[i] * alpha[i] + ls[i];
+        }
+#pragma unroll
+        for (int j = 0; j < DT; ++j) { o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1]; }
+#pragma unroll
+        for (int kk = 0; kk < KB / 16; ++kk) {
+#pragma unroll
+          for (int jd = 0; jd < DT; jd += 2) {
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_trans(b0, b1, b2, b3,
+                          (uint32_t)__cvta_generic_to_shared(sv + swz(kk * 16 + (lane & 15), jd + (lane >> 4))));
+            mma_bf16_16816(o[jd], pf[kk], b0, b1);
+            mma_bf16_16816(o[jd + 1], pf[kk], b2, b3);
+          }
+        }
+      }
+    }
+
+    // ---- self key of candidate rows ------------------------------------------------------------------
+    cp_wait<1>();      // the strip's own K/V rows (requested one tile ago) have landed; the next Q may still be in flight
+    __syncwarp();
+    if (has_cand) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const bool is_cand = segq[i] == -1;
+        const int lr = g + 8 * i;  // row inside the strip
+        float dot = 0.f;
+        if (is_cand) {
+#pragma unroll
+          for (int ks = 0; ks < KSTEPS; ++ks) {
+            const float2 qa = unpack_bf2(qf[ks][i]), qb = unpack_bf2(qf[ks][i + 2]);
+            const float2 ka = unpack_bf2(*reinterpret_cast<const uint32_t*>(wks + swz(lr, ks * 2) + 2 * t4));
+            const float2 kb = unpack_bf2(*reinterpret_cast<const uint32_t*>(wks + swz(lr, ks * 2 + 1) + 2 * t4));
+            dot += qa.x * ka.x + qa.y * ka.y + qb.x * kb.x + qb.y * kb.y;
+          }
+        }
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        if (is_cand) {
+          const float sv_ = CAP ? scaled_logit(dot, a.sm_scale, a.cap, a.cap_method) : dot * csc;
+          const float mn = fmaxf(m[i], sv_);
+          const float alpha = ex2(m[i] - mn);
+          const float p = ex2(sv_ - mn);
+          const float pr = round_bf(p);
+          l[i] = l[i] * alpha + p;
+          m[i] = mn;
+#pragma unroll
+          for (int j = 0; j < DT; ++j) {
+            const float2 vv = unpack_bf2(*reinterpret_cast<const uint32_t*>(wvs + swz(lr, j) + 2 * t4));
+            o[j][2 * i + 0] = o[j][2 * i + 0] * alpha + pr * vv.x;
+            o[j][2 * i + 1] = o[j][2 * i + 1] * alpha + pr * vv.y;
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (tile + 1 < n_tiles && strip_has_cand(tile + 1)) load_own_kv(tile + 1);
+    cp_commit();
+
+    // ---- normalise, stage the strip in its (free) Q buffer, store 16-byte chunks ---------------------------
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float inv = (l[i] == 0.f || segq[i] == 0) ? 0.f : 1.0f / l[i];
+      const int lr = g + 8 * i;
+#pragma unroll
+      for (int j = 0; j < DT; ++j)
+        *reinterpret_cast<uint32_t*>(sq + swz(lr, j) + 2 * t4) = pack_bf2(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = lane + 32 * k, r = c >> 3, ch = c & 7;
+      const int row = q0 + warp * 16 + r;
+      if (row < T)
+        *reinterpret_cast<uint4*>(a.out + ((tok0 + row) * a.Hq + h) * DH + ch * 8) =
+            *reinterpret_cast<const uint4*>(sq + swz(r, ch));
+    }
+  }
+  cp_wait<0>();
+}
+
+template <bool CAP>
+phx_status launch_strip(const AttnArgs& a, cudaStream_t stream, std::string& err) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    PHX_CUDA_TRY(cudaFuncSetAttribute(ranker_attention_strip_kernel<CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, STRIP_SMEM), err);
+    attr_set = true;
+  }
+  dim3 grid(a.Hq, a.B);
+  ranker_attention_strip_kernel<CAP><<<grid, ATT_THREADS, STRIP_SMEM, stream>>>(a);
+  PHX_CUDA_TRY(cudaGetLastError(), err);
+  return PHX_OK;
+}
+
 }  // namespace
 
 phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::string& err) {
@@ -336,6 +609,13 @@ phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::
     if (!legacy && prefer_tc && a.err_flag && ranker_attention_tc_supported(a)) return ranker_attention_tc_launch(a, a.err_flag, stream, err);
   }
   const bool cap = a.cap_method != 0 && a.cap > 0.f;
+  {
+    // head dim 64 with the whole history in one shared-memory panel: the resident-history kernel
+    const char* force = getenv("PHX_ATTN");
+    const bool strip_off = force && strcmp(force, "strip") != 0;
+    const int n_hist = a.hist_len < a.T ? a.hist_len : a.T;
+    if (!strip_off && a.dh == 64 && n_hist <= STRIP_HIST) return cap ? launch_strip<true>(a, stream, err) : launch_strip<false>(a, stream, err);
+  }
   switch (a.dh) {
     case 32: return cap ? launch_dh<32, true>(a, stream, err) : launch_dh<32, false>(a, stream, err);
     case 64: return cap ? launch_dh<64, true>(a, stream, err) : launch_dh<64, false>(a, stream, err);
