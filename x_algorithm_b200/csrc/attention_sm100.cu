@@ -51,6 +51,7 @@ __device__ __forceinline__ void st_shared_16(uint32_t addr, uint4 v) {
 
 struct AttnTcArgs {
   const bf16* q; const bf16* k; const bf16* v;          // for the per-row self term (plain loads)
+  bf16* out;                                            // [B*T][Hq][dh], for kernels that store rows directly
   long long q_tok_stride, k_tok_stride, v_tok_stride;
   int q_head_stride, k_head_stride, v_head_stride;
   const int* seg;
@@ -300,9 +301,9 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
 // ---- resident-history variant -----------------------------------------------------------------------------------
 // History of at most 128 keys, head dim 64 (the ranking trunk's shape): K and V of the (batch, head) are loaded once
 // and stay in shared memory while the CTA walks over all of the request's query tiles.  Q tiles are double-buffered
-// (the producer runs one tile ahead), O is double-buffered in TMEM, so S = Q K^T of tile t+1 is issued while the
-// softmax warps still normalise and store tile t; a finished tile is staged in its own Q buffer and handed back to
-// the producer once the TMA store has read it.
+// (the producer runs ahead), O is double-buffered in TMEM, so S = Q K^T of tile t+1 is issued while the softmax
+// warps still normalise tile t; output rows go straight from registers to global memory (128 contiguous bytes per
+// thread), and the rows a candidate needs for its self key are requested one tile ahead.
 __global__ void __launch_bounds__(A_THREADS, 2)
 ranker_attention_resident_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
@@ -332,7 +333,8 @@ ranker_attention_resident_kernel(const __grid_constant__ CUtensorMap map_q, cons
   volatile int* verr = a.err_flag;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) { mbar_init(q_full(i), 1); mbar_init(q_free(i), 1); }
+    // a Q buffer is free once S has been computed from it (commit) and the 128 softmax threads have read their rows
+    for (int i = 0; i < 2; ++i) { mbar_init(q_full(i), 1); mbar_init(q_free(i), 129); }
     mbar_init(kv_full, 1); mbar_init(s_full, 1); mbar_init(p_ready, 128); mbar_init(o_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -368,6 +370,7 @@ ranker_attention_resident_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
         for (int k = 0; k < 4; ++k) umma_bf16(tmem + TM_S, qd + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), idesc_s, k != 0);
         umma_commit(s_full);
+        umma_commit(q_free(bq));          // the Q buffer is free as soon as S has been computed
         mbar_wait(p_ready, ph, verr);
         tc_fence_after();
 #pragma unroll
@@ -398,74 +401,123 @@ ranker_attention_resident_kernel(const __grid_constant__ CUtensorMap map_q, cons
     for (int w = 0; w < 4; ++w) kmask[w] = mask_words[w];
     const bool all_ok = (kmask[0] & kmask[1] & kmask[2] & kmask[3]) == 0xffffffffu;
 
+    // Per-row work for a candidate's self key needs the row's own q, k and v.  Its k and v rows come from HBM, so
+    // they are requested one tile ahead: k(t+1) at the start of tile t (used after tile t's softmax, when the dot
+    // product for tile t+1 is formed against the Q row already sitting in the Q buffer), v(t+1) at the end of tile t.
+    const bf16* kbase = a.k + (long long)hk * a.k_head_stride;
+    const bf16* vbase = a.v + (long long)hk * a.v_head_stride;
+    auto seg_of = [&](int t) { const int row = t * QT + r; return (row < T) ? a.seg[tok0 + row] : 0; };
+    auto tok_of = [&](int t) { const int row = t * QT + r; return tok0 + (row < T ? row : 0); };
+    auto load_row = [&](const bf16* base, long long stride, int t, bool on, uint4 (&dst)[DH / 8]) {
+      if (on) {
+        const uint4* p = reinterpret_cast<const uint4*>(base + tok_of(t) * stride);
+#pragma unroll
+        for (int c = 0; c < DH / 8; ++c) dst[c] = __ldg(p + c);
+      }
+    };
+    // q(t) . k(t) for this row, q from the (swizzled) Q buffer; every thread then lets go of the buffer
+    auto self_dot = [&](int t, bool on, const uint4 (&krow)[DH / 8]) {
+      const int bq = t & 1;
+      mbar_wait(q_full(bq), (uint32_t)((t >> 1) & 1), verr);
+      float dot = 0.f;
+      if (on) {
+        float d4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < DH / 8; ++c) {
+          uint4 qa;
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(qa.x), "=r"(qa.y), "=r"(qa.z), "=r"(qa.w)
+                       : "r"(sQ + bq * SLAB + r * 128 + ((uint32_t)(c ^ sw) << 4)));
+          const uint4 ka = krow[c];
+          const float2 q0f = unpack_bf2(qa.x), q1f = unpack_bf2(qa.y), q2f = unpack_bf2(qa.z), q3f = unpack_bf2(qa.w);
+          const float2 k0f = unpack_bf2(ka.x), k1f = unpack_bf2(ka.y), k2f = unpack_bf2(ka.z), k3f = unpack_bf2(ka.w);
+          d4[0] += q0f.x * k0f.x + q0f.y * k0f.y; d4[1] += q1f.x * k1f.x + q1f.y * k1f.y;
+          d4[2] += q2f.x * k2f.x + q2f.y * k2f.y; d4[3] += q3f.x * k3f.x + q3f.y * k3f.y;
+        }
+        dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+      }
+      mbar_arrive(q_free(bq));
+      return cap_on ? capped_log2(dot, a.sm_scale, a.cap, a.cap_method) : dot * csc;
+    };
+    // one 64-key half of the S row, capped and masked, into registers
+    auto load_s_half = [&](int c, float (&sv)[64]) {
+      tmem_ld32_nowait(tmem + TM_S + lane_base + c * 64, reinterpret_cast<uint32_t*>(sv));
+      tmem_ld32_nowait(tmem + TM_S + lane_base + c * 64 + 32, reinterpret_cast<uint32_t*>(sv) + 32);
+      tmem_ld_wait();
+      if (cap_on) {
+#pragma unroll
+        for (int k = 0; k < 64; ++k) sv[k] = capped_log2(sv[k], a.sm_scale, a.cap, a.cap_method);
+      }
+      if (!all_ok) {
+#pragma unroll
+        for (int k = 0; k < 64; ++k)
+          if (!((kmask[c * 2 + (k >> 5)] >> (k & 31)) & 1u)) sv[k] = -INFINITY;
+      }
+    };
+
+    uint4 krow[DH / 8], vrow[DH / 8];
+    int segq = seg_of(0);
+    int seg_next = (1 < n_tiles) ? seg_of(1) : 0;
+    load_row(kbase, a.k_tok_stride, 0, segq == -1, krow);
+    load_row(vbase, a.v_tok_stride, 0, segq == -1, vrow);
+    float self_logit = self_dot(0, segq == -1, krow);
+
     for (int t = 0; t < n_tiles; ++t) {
       const int bq = t & 1;
       const uint32_t ph = (uint32_t)(t & 1);
       const int row = t * QT + r;
-      const int segq = (row < T) ? a.seg[tok0 + row] : 0;
-      // self logit of a candidate row: loads issued before the wait on S
-      float self_logit = 0.f;
-      const long long tok = tok0 + (row < T ? row : 0);
-      if (segq == -1) {
-        const uint4* qp = reinterpret_cast<const uint4*>(a.q + tok * a.q_tok_stride + (long long)h * a.q_head_stride);
-        const uint4* kp = reinterpret_cast<const uint4*>(a.k + tok * a.k_tok_stride + (long long)hk * a.k_head_stride);
-        float dot = 0.f;
-#pragma unroll
-        for (int c = 0; c < DH / 8; ++c) {
-          const uint4 qa = __ldg(qp + c), ka = __ldg(kp + c);
-          const float2 q0f = unpack_bf2(qa.x), q1f = unpack_bf2(qa.y), q2f = unpack_bf2(qa.z), q3f = unpack_bf2(qa.w);
-          const float2 k0f = unpack_bf2(ka.x), k1f = unpack_bf2(ka.y), k2f = unpack_bf2(ka.z), k3f = unpack_bf2(ka.w);
-          dot += q0f.x * k0f.x + q0f.y * k0f.y + q1f.x * k1f.x + q1f.y * k1f.y + q2f.x * k2f.x + q2f.y * k2f.y + q3f.x * k3f.x + q3f.y * k3f.y;
-        }
-        self_logit = cap_on ? capped_log2(dot, a.sm_scale, a.cap, a.cap_method) : dot * csc;
-      }
+      const bool more = (t + 1 < n_tiles);
+      const int seg_next2 = (t + 2 < n_tiles) ? seg_of(t + 2) : 0;   // two tiles ahead: it gates the loads issued next tile
+      if (more) load_row(kbase, a.k_tok_stride, t + 1, seg_next == -1, krow);
 
       mbar_wait(s_full, ph, verr);
       tc_fence_after();
-      float s[KBLK];
-#pragma unroll
-      for (int c = 0; c < KBLK / 32; ++c) tmem_ld32(tmem + TM_S + lane_base + c * 32, reinterpret_cast<uint32_t*>(s) + c * 32);
-      if (cap_on) {
-#pragma unroll
-        for (int k = 0; k < KBLK; ++k) s[k] = capped_log2(s[k], a.sm_scale, a.cap, a.cap_method);
-      }
-      if (!all_ok) {
-#pragma unroll
-        for (int k = 0; k < KBLK; ++k)
-          if (!((kmask[k >> 5] >> (k & 31)) & 1u)) s[k] = -INFINITY;
-      }
+      // pass 1: row maximum (S is read twice, 64 keys at a time, to keep the row out of the register file)
       float bm = -INFINITY;
 #pragma unroll
-      for (int k = 0; k < KBLK; ++k) bm = fmaxf(bm, s[k]);
+      for (int c = 0; c < 2; ++c) {
+        float sv[64];
+        load_s_half(c, sv);
+        float b4[4] = {sv[0], sv[1], sv[2], sv[3]};   // four independent chains: the warp has little else to overlap with
+#pragma unroll
+        for (int k = 4; k < 64; ++k) b4[k & 3] = fmaxf(b4[k & 3], sv[k]);
+        bm = fmaxf(bm, fmaxf(fmaxf(b4[0], b4[1]), fmaxf(b4[2], b4[3])));
+      }
       float m = bm * csc;
       if (segq == -1) m = fmaxf(m, self_logit);          // the self key takes part in the row maximum right away
       const float mns = (m == -INFINITY) ? 0.f : m;
-      float l = 0.f;
-#pragma unroll
-      for (int k = 0; k < KBLK; ++k) { s[k] = ex2f(fmaf(s[k], csc, -mns)); l += s[k]; }
       // P's previous contents (tile t-1) must have been consumed by its P V product
       if (t > 0) mbar_wait(o_done, ph ^ 1, verr);
+      // pass 2: probabilities, row sum, P in bf16 into the swizzled operand buffer
+      float l = 0.f;
 #pragma unroll
-      for (int c = 0; c < KBLK / 8; ++c) {
-        uint4 o;
-        o.x = pack_bf2(s[c * 8 + 0], s[c * 8 + 1]); o.y = pack_bf2(s[c * 8 + 2], s[c * 8 + 3]);
-        o.z = pack_bf2(s[c * 8 + 4], s[c * 8 + 5]); o.w = pack_bf2(s[c * 8 + 6], s[c * 8 + 7]);
-        st_shared_16(sP + (c >> 3) * SLAB + r * 128 + ((uint32_t)((c & 7) ^ sw) << 4), o);
+      for (int c = 0; c < 2; ++c) {
+        float sv[64];
+        load_s_half(c, sv);
+#pragma unroll
+        for (int k = 0; k < 64; ++k) sv[k] = ex2f(fmaf(sv[k], csc, -mns));
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int k = 0; k < 64; ++k) l4[k & 3] += sv[k];
+        l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+          uint4 o;
+          o.x = pack_bf2(sv[cc * 8 + 0], sv[cc * 8 + 1]); o.y = pack_bf2(sv[cc * 8 + 2], sv[cc * 8 + 3]);
+          o.z = pack_bf2(sv[cc * 8 + 4], sv[cc * 8 + 5]); o.w = pack_bf2(sv[cc * 8 + 6], sv[cc * 8 + 7]);
+          st_shared_16(sP + c * SLAB + r * 128 + ((uint32_t)(cc ^ sw) << 4), o);
+        }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       mbar_arrive(p_ready);
 
-      // ---- epilogue of this tile (the MMA warp is already on S of tile t+1) ----
+      // while the P V product runs: the self logit of the next tile (its k row was requested at the top)
+      float self_next = 0.f;
+      if (more) self_next = self_dot(t + 1, seg_next == -1, krow);
+
+      // ---- epilogue of this tile ----
       float p_self = 0.f;
-      uint4 vrow[DH / 8];
-      if (segq == -1) {
-        p_self = ex2f(self_logit - mns);
-        l += p_self;
-        const uint4* vp = reinterpret_cast<const uint4*>(a.v + tok * a.v_tok_stride + (long long)hk * a.v_head_stride);
-#pragma unroll
-        for (int c = 0; c < DH / 8; ++c) vrow[c] = __ldg(vp + c);
-      }
+      if (segq == -1) { p_self = ex2f(self_logit - mns); l += p_self; }
       const float pr = round_bf(p_self);
       mbar_wait(o_done, ph, verr);
       tc_fence_after();
@@ -473,28 +525,32 @@ ranker_attention_resident_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
       for (int c = 0; c < DH / 32; ++c) tmem_ld32(tmem + TM_O + bq * DH + lane_base + c * 32, reinterpret_cast<uint32_t*>(o) + c * 32);
       const float inv = (l == 0.f || segq == 0) ? 0.f : 1.0f / l;
+      // the thread's output row is 128 contiguous bytes: four 32-byte stores, no staging
+      bf16* orow = a.out + ((tok0 + row) * a.Hq + h) * DH;
 #pragma unroll
-      for (int c = 0; c < DH / 8; ++c) {
-        if (segq == -1) {
-          const float2 v0 = unpack_bf2(vrow[c].x), v1 = unpack_bf2(vrow[c].y), v2 = unpack_bf2(vrow[c].z), v3 = unpack_bf2(vrow[c].w);
-          o[c * 8 + 0] += pr * v0.x; o[c * 8 + 1] += pr * v0.y; o[c * 8 + 2] += pr * v1.x; o[c * 8 + 3] += pr * v1.y;
-          o[c * 8 + 4] += pr * v2.x; o[c * 8 + 5] += pr * v2.y; o[c * 8 + 6] += pr * v3.x; o[c * 8 + 7] += pr * v3.y;
+      for (int c2 = 0; c2 < DH / 16; ++c2) {
+        uint32_t w[8];
+#pragma unroll
+        for (int hc = 0; hc < 2; ++hc) {
+          const int c = c2 * 2 + hc;
+          if (segq == -1) {
+            const float2 v0 = unpack_bf2(vrow[c].x), v1 = unpack_bf2(vrow[c].y), v2 = unpack_bf2(vrow[c].z), v3 = unpack_bf2(vrow[c].w);
+            o[c * 8 + 0] += pr * v0.x; o[c * 8 + 1] += pr * v0.y; o[c * 8 + 2] += pr * v1.x; o[c * 8 + 3] += pr * v1.y;
+            o[c * 8 + 4] += pr * v2.x; o[c * 8 + 5] += pr * v2.y; o[c * 8 + 6] += pr * v3.x; o[c * 8 + 7] += pr * v3.y;
+          }
+          w[hc * 4 + 0] = pack_bf2(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv); w[hc * 4 + 1] = pack_bf2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
+          w[hc * 4 + 2] = pack_bf2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv); w[hc * 4 + 3] = pack_bf2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
         }
-        uint4 w;
-        w.x = pack_bf2(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv); w.y = pack_bf2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
-        w.z = pack_bf2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv); w.w = pack_bf2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
-        st_shared_16(sQ + bq * SLAB + r * 128 + ((uint32_t)((c & 7) ^ sw) << 4), w);   // this tile's Q buffer is free
+        if (row < T)
+          asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                       ::"l"(orow + c2 * 16), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      bar_sync_128();
-      if (warp == 2 && lane == 0) {
-        tma_store_3d(&map_o, sQ + bq * SLAB, h * DH, t * QT, b);
-        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        mbar_arrive(q_free(bq));                      // the producer may refill this Q buffer
-      }
+      // next tile's v row: a whole tile to arrive
+      if (more) load_row(vbase, a.v_tok_stride, t + 1, seg_next == -1, vrow);
+      segq = seg_next;
+      seg_next = seg_next2;
+      self_logit = self_next;
     }
-    if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   if (*verr != 0) __nanosleep(1000000);
@@ -544,7 +600,7 @@ phx_status launch_tc(const AttnArgs& a, int* err_flag, cudaStream_t stream, std:
   if ((s = cached_map3d(&mv, a.v, (long long)(a.Hkv - 1) * a.v_head_stride + DH, a.T, a.B, a.v_tok_stride, KBLK, err))) return s;
   if ((s = cached_map3d(&mo, a.out, (long long)a.Hq * DH, a.T, a.B, (long long)a.Hq * DH, QT, err))) return s;
   AttnTcArgs t;
-  t.q = a.q; t.k = a.k; t.v = a.v;
+  t.q = a.q; t.k = a.k; t.v = a.v; t.out = a.out;
   t.q_tok_stride = a.q_tok_stride; t.k_tok_stride = a.k_tok_stride; t.v_tok_stride = a.v_tok_stride;
   t.q_head_stride = a.q_head_stride; t.k_head_stride = a.k_head_stride; t.v_head_stride = a.v_head_stride;
   t.seg = a.seg; t.B = a.B; t.T = a.T; t.Hq = a.Hq; t.Hkv = a.Hkv; t.hist_len = a.hist_len;
@@ -569,7 +625,7 @@ phx_status launch_resident(const AttnArgs& a, int* err_flag, cudaStream_t stream
   if ((s = cached_map3d(&mv, a.v, (long long)(a.Hkv - 1) * a.v_head_stride + 64, a.T, a.B, a.v_tok_stride, 128, err))) return s;
   if ((s = cached_map3d(&mo, a.out, (long long)a.Hq * 64, a.T, a.B, (long long)a.Hq * 64, QT, err))) return s;
   AttnTcArgs t;
-  t.q = a.q; t.k = a.k; t.v = a.v;
+  t.q = a.q; t.k = a.k; t.v = a.v; t.out = a.out;
   t.q_tok_stride = a.q_tok_stride; t.k_tok_stride = a.k_tok_stride; t.v_tok_stride = a.v_tok_stride;
   t.q_head_stride = a.q_head_stride; t.k_head_stride = a.k_head_stride; t.v_head_stride = a.v_head_stride;
   t.seg = a.seg; t.B = a.B; t.T = a.T; t.Hq = a.Hq; t.Hkv = a.Hkv; t.hist_len = a.hist_len;
