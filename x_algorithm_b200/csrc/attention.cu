@@ -478,28 +478,36 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) ranker_attention_strip_kernel(
           alpha[i] = ex2(mprev[i] - mn[i]);
           mprev[i] = m[i];
         }
+        // P = 2^(S - m) with packed fp32 arithmetic (two columns of a row per instruction)
         uint32_t pf[KB / 16][4];
-        float ls[2] = {0.f, 0.f};
+        float2 ls2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+        const float2 csc2 = make_float2(csc, csc);
+        const float2 nm2[2] = {make_float2(-mn[0], -mn[0]), make_float2(-mn[1], -mn[1])};
 #pragma unroll
         for (int j = 0; j < KB / 8; ++j) {
-          float p[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int ri = e >> 1;
-            p[e] = ex2(fmaf(s[j][e], csc, -mn[ri]));
-            ls[ri] += p[e];
+          for (int ri = 0; ri < 2; ++ri) {
+            const float2 e = __ffma2_rn(make_float2(s[j][2 * ri], s[j][2 * ri + 1]), csc2, nm2[ri]);
+            const float2 pp = make_float2(ex2(e.x), ex2(e.y));      // masked logit: -inf -> 0
+            ls2[ri] = __fadd2_rn(ls2[ri], pp);
+            pf[j >> 1][(j & 1) * 2 + ri] = pack_bf2(pp.x, pp.y);
           }
-          pf[j >> 1][(j & 1) * 2 + 0] = pack_bf2(p[0], p[1]);
-          pf[j >> 1][(j & 1) * 2 + 1] = pack_bf2(p[2], p[3]);
         }
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          ls[i] += __shfl_xor_sync(0xffffffffu, ls[i], 1);
-          ls[i] += __shfl_xor_sync(0xffffffffu, ls[i], 2);
-          l[i] = l[i] * alpha[i] + ls[i];
+        for (int i = 0; i < 2; ++i) {  // a row's 64 probabilities are spread over the 4 lanes of its quad
+          float lsum = ls2[i].x + ls2[i].y;
+          lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
+          lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
+          l[i] = l[i] * alpha[i] + lsum;
         }
+        if (blk > 0) {   // nothing to rescale before the first block
+          const float2 a0 = make_float2(alpha[0], alpha[0]), a1 = make_float2(alpha[1], alpha[1]);
 #pragma unroll
-        for (int j = 0; j < DT; ++j) { o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1]; }
+          for (int j = 0; j < DT; ++j) {
+            const float2 x = __fmul2_rn(make_float2(o[j][0], o[j][1]), a0), y = __fmul2_rn(make_float2(o[j][2], o[j][3]), a1);
+            o[j][0] = x.x; o[j][1] = x.y; o[j][2] = y.x; o[j][3] = y.y;
+          }
+        }
 #pragma unroll
         for (int kk = 0; kk < KB / 16; ++kk) {
 #pragma unroll
@@ -514,41 +522,59 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) ranker_attention_strip_kernel(
       }
     }
 
-    // ---- self key of candidate rows ------------------------------------------------------------------
+    // ---- self key of candidate rows: one more online-softmax step, on the tensor cores -----------------------
+    // The strip's 16 x 16 block Q K_own^T holds the self logits on its diagonal; the probabilities go back in as a
+    // diagonal P block against the strip's own V rows.
     cp_wait<1>();      // the strip's own K/V rows (requested one tile ago) have landed; the next Q may still be in flight
     __syncwarp();
     if (has_cand) {
+      float sd[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) { sd[j][0] = sd[j][1] = sd[j][2] = sd[j][3] = 0.f; }
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        uint32_t b0, b1, b2, b3;
+        const int kr = (lane & 7) + ((lane >> 4) << 3);
+        const int kc = ks * 2 + ((lane >> 3) & 1);
+        ldsm_x4(b0, b1, b2, b3, (uint32_t)__cvta_generic_to_shared(wks + swz(kr, kc)));
+        mma_bf16_16816(sd[0], qf[ks], b0, b1);
+        mma_bf16_16816(sd[1], qf[ks], b2, b3);
+      }
+      // row g's self key is column g of the first 8-key tile, row g+8's is column g of the second: both sit in the
+      // quad's lane t4 == g / 2
+      float dsel[2] = {(g & 1) ? sd[0][1] : sd[0][0], (g & 1) ? sd[1][3] : sd[1][2]};
+      const int src = (lane & ~3) | (g >> 1);
+      const bool mine = (t4 == (g >> 1));
+      uint32_t pa[4] = {0u, 0u, 0u, 0u};
+      float alpha[2];
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
+        const float dot = __shfl_sync(0xffffffffu, dsel[i], src);
         const bool is_cand = segq[i] == -1;
-        const int lr = g + 8 * i;  // row inside the strip
-        float dot = 0.f;
-        if (is_cand) {
+        const float sv_ = is_cand ? (CAP ? scaled_logit(dot, a.sm_scale, a.cap, a.cap_method) : dot * csc) : -INFINITY;
+        const float mnew = fmaxf(m[i], sv_);
+        const float mns = (mnew == -INFINITY) ? 0.f : mnew;
+        alpha[i] = ex2(m[i] - mns);                      // no history yet: 2^-inf = 0; unchanged maximum: 1
+        const float p = ex2(sv_ - mns);                  // 0 for rows that are not candidates
+        l[i] = l[i] * alpha[i] + p;
+        m[i] = mnew;
+        const uint32_t pk = (g & 1) ? pack_bf2(0.f, p) : pack_bf2(p, 0.f);   // P rounded to bf16 like every other key
+        if (mine) pa[i == 0 ? 0 : 3] = pk;               // A fragment: [g][2t4..], [g+8][2t4..], [g][2t4+8..], [g+8][2t4+8..]
+      }
+      {
+        const float2 a0 = make_float2(alpha[0], alpha[0]), a1 = make_float2(alpha[1], alpha[1]);
 #pragma unroll
-          for (int ks = 0; ks < KSTEPS; ++ks) {
-            const float2 qa = unpack_bf2(qf[ks][i]), qb = unpack_bf2(qf[ks][i + 2]);
-            const float2 ka = unpack_bf2(*reinterpret_cast<const uint32_t*>(wks + swz(lr, ks * 2) + 2 * t4));
-            const float2 kb = unpack_bf2(*reinterpret_cast<const uint32_t*>(wks + swz(lr, ks * 2 + 1) + 2 * t4));
-            dot += qa.x * ka.x + qa.y * ka.y + qb.x * kb.x + qb.y * kb.y;
-          }
+        for (int j = 0; j < DT; ++j) {
+          const float2 x = __fmul2_rn(make_float2(o[j][0], o[j][1]), a0), y = __fmul2_rn(make_float2(o[j][2], o[j][3]), a1);
+          o[j][0] = x.x; o[j][1] = x.y; o[j][2] = y.x; o[j][3] = y.y;
         }
-        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-        if (is_cand) {
-          const float sv_ = CAP ? scaled_logit(dot, a.sm_scale, a.cap, a.cap_method) : dot * csc;
-          const float mn = fmaxf(m[i], sv_);
-          const float alpha = ex2(m[i] - mn);
-          const float p = ex2(sv_ - mn);
-          const float pr = round_bf(p);
-          l[i] = l[i] * alpha + p;
-          m[i] = mn;
+      }
 #pragma unroll
-          for (int j = 0; j < DT; ++j) {
-            const float2 vv = unpack_bf2(*reinterpret_cast<const uint32_t*>(wvs + swz(lr, j) + 2 * t4));
-            o[j][2 * i + 0] = o[j][2 * i + 0] * alpha + pr * vv.x;
-            o[j][2 * i + 1] = o[j][2 * i + 1] * alpha + pr * vv.y;
-          }
-        }
+      for (int jd = 0; jd < DT; jd += 2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_trans(b0, b1, b2, b3, (uint32_t)__cvta_generic_to_shared(wvs + swz(lane & 15, jd + (lane >> 4))));
+        mma_bf16_16816(o[jd], pa, b0, b1);
+        mma_bf16_16816(o[jd + 1], pa, b2, b3);
       }
     }
     __syncwarp();
