@@ -108,6 +108,7 @@ struct phx_engine {
   // alternate residual buffer while the current forward runs
   cudaStream_t side_stream = nullptr;
   cudaEvent_t ev_prefetch = nullptr;
+  cudaEvent_t ev_chunk[4] = {nullptr, nullptr, nullptr, nullptr};   // result chunks of the host-buffer call
   cudaEvent_t ev_done[2] = {nullptr, nullptr};   // ends of the last two forwards; done_idx = the most recent
   int done_idx = 0;
   bf16* x_alt = nullptr; int* seg_alt = nullptr; float* rowss_a_alt = nullptr;
@@ -749,13 +750,29 @@ phx_status phx_rank_forward(phx_engine* e, const phx_rank_batch* bh, const phx_r
   phx_status s = phx_rank_forward_device(e, &bd, &od);
   if (s) return s;
   const size_t rows = B * C;
-  if (oh->log_probs) PHX_CUDA_TRY(cudaMemcpyAsync(e->lp_host, e->lp_dev, rows * e->V * 4, cudaMemcpyDeviceToHost, e->stream), e->err);
-  if (oh->continuous) PHX_CUDA_TRY(cudaMemcpyAsync(e->cont_host, e->cont_dev, rows * e->NC * 4, cudaMemcpyDeviceToHost, e->stream), e->err);
-  if (oh->scores && e->has_blend) PHX_CUDA_TRY(cudaMemcpyAsync(e->score_host, e->score_dev, rows * 8, cudaMemcpyDeviceToHost, e->stream), e->err);
+  // results come back in four row chunks: while the host copies chunk i out of the pinned staging block, chunk i+1
+  // is still on the bus
+  constexpr int NCH = 4;
+  const size_t step = (rows + NCH - 1) / NCH;
+  for (int i = 0; i < NCH; ++i) {
+    const size_t r0 = i * step, r1 = (r0 + step < rows) ? r0 + step : rows;
+    if (r0 < r1) {
+      if (oh->log_probs) PHX_CUDA_TRY(cudaMemcpyAsync(e->lp_host + r0 * e->V, e->lp_dev + r0 * e->V, (r1 - r0) * e->V * 4, cudaMemcpyDeviceToHost, e->stream), e->err);
+      if (oh->continuous) PHX_CUDA_TRY(cudaMemcpyAsync(e->cont_host + r0 * e->NC, e->cont_dev + r0 * e->NC, (r1 - r0) * e->NC * 4, cudaMemcpyDeviceToHost, e->stream), e->err);
+      if (oh->scores && e->has_blend) PHX_CUDA_TRY(cudaMemcpyAsync(e->score_host + r0, e->score_dev + r0, (r1 - r0) * 8, cudaMemcpyDeviceToHost, e->stream), e->err);
+    }
+    if (!e->ev_chunk[i]) PHX_CUDA_TRY(cudaEventCreateWithFlags(&e->ev_chunk[i], cudaEventDisableTiming), e->err);
+    PHX_CUDA_TRY(cudaEventRecord(e->ev_chunk[i], e->stream), e->err);
+  }
+  for (int i = 0; i < NCH; ++i) {
+    PHX_CUDA_TRY(cudaEventSynchronize(e->ev_chunk[i]), e->err);
+    const size_t r0 = i * step, r1 = (r0 + step < rows) ? r0 + step : rows;
+    if (r0 >= r1) continue;
+    if (oh->log_probs) memcpy(oh->log_probs + r0 * e->V, e->lp_host + r0 * e->V, (r1 - r0) * e->V * 4);
+    if (oh->continuous) memcpy(oh->continuous + r0 * e->NC, e->cont_host + r0 * e->NC, (r1 - r0) * e->NC * 4);
+    if (oh->scores && e->has_blend) memcpy(oh->scores + r0, e->score_host + r0, (r1 - r0) * 8);
+  }
   PHX_CUDA_TRY(cudaStreamSynchronize(e->stream), e->err);
-  if (oh->log_probs) memcpy(oh->log_probs, e->lp_host, rows * e->V * 4);
-  if (oh->continuous) memcpy(oh->continuous, e->cont_host, rows * e->NC * 4);
-  if (oh->scores && e->has_blend) memcpy(oh->scores, e->score_host, rows * 8);
   return check_err_flag(e);
 }
 

@@ -116,16 +116,23 @@ class PhoenixEngine:
         b.cand_post_ids, b.cand_author_ids = _ptr(cp), _ptr(ca)
         return b
 
-    def rank(self, inp: RankInputs) -> RankOutputs:
-        """Host buffers in, host buffers out (copies inside the call)."""
+    def rank(self, inp: RankInputs, out: "RankOutputs | None" = None) -> RankOutputs:
+        """Host buffers in, host buffers out (copies inside the call).  `out`: a RankOutputs of an earlier call with
+        the same batch size to write into (a server reuses its result buffers; fresh 10 MB arrays cost a page fault
+        per 4 KB on every call)."""
         cfg, B = self.cfg, inp.batch
         arrs = [np.ascontiguousarray(inp.hist_post_ids, np.int64), np.ascontiguousarray(inp.hist_author_ids, np.int64),
                 np.ascontiguousarray(inp.hist_actions, np.int32), np.ascontiguousarray(inp.hist_surfaces, np.int32),
                 np.ascontiguousarray(inp.cand_post_ids, np.int64), np.ascontiguousarray(inp.cand_author_ids, np.int64)]
         assert arrs[0].shape == (B, cfg.history_len) and arrs[4].shape == (B, cfg.num_candidates)
-        lp = np.empty((B, cfg.num_candidates, cfg.num_actions), np.float32)
-        cont = np.empty((B, cfg.num_candidates, cfg.num_continuous), np.float32)
-        sc = np.empty((B, cfg.num_candidates), np.float64) if self._has_blend else None
+        if out is not None and out.log_probs.shape == (B, cfg.num_candidates, cfg.num_actions):
+            lp, cont, sc = out.log_probs, out.continuous, out.scores
+            if self._has_blend and sc is None:
+                sc = np.empty((B, cfg.num_candidates), np.float64)
+        else:
+            lp = np.empty((B, cfg.num_candidates, cfg.num_actions), np.float32)
+            cont = np.empty((B, cfg.num_candidates, cfg.num_continuous), np.float32)
+            sc = np.empty((B, cfg.num_candidates), np.float64) if self._has_blend else None
         b = self._batch_struct(B, *arrs)
         o = _lib.RankOut(_ptr(lp), _ptr(cont), _ptr(sc))
         self._check(lib.phx_rank_forward(self._h, C.byref(b), C.byref(o)))
