@@ -37,6 +37,12 @@ __device__ __forceinline__ float unord32(uint32_t o) {
   return __uint_as_float(u);
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ void append_survivor(const TcScanArgs& a, int u, unsigned long long key) {
   const int slot = atomicAdd(&a.counts[u], 1);
   if (slot < a.cap) a.surv[(size_t)u * a.cap + slot] = key;
@@ -68,7 +74,7 @@ scan_tc_kernel(const __grid_constant__ CUtensorMap map_corpus, const __grid_cons
   const uint32_t stage_bytes = (uint32_t)kblk * TC_ROWS * 128;
   const uint32_t stage_base = users_smem + users_bytes;
   const uint32_t thr_smem = stage_base + TC_STAGES * stage_bytes;  // [256] float thresholds
-  const uint32_t queue_smem = thr_smem + TC_Q * 4;                 // [8 warps][QCAP] uint4 records + [8] counters
+  const uint32_t queue_smem = thr_smem + TC_Q * 4 + 32;            // (+ [8] minima of the thresholds per 32 columns) [8 warps][QCAP] uint4 records + [8] counters
   const uint32_t bars = queue_smem + 8 * QCAP * 16 + 64;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (TC_STAGES + s); };
@@ -78,6 +84,7 @@ scan_tc_kernel(const __grid_constant__ CUtensorMap map_corpus, const __grid_cons
   const uint32_t tmem_slot = bars + 8u * (2 * TC_STAGES + 5);
   uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
   float* s_thr = reinterpret_cast<float*>(smem_raw + (thr_smem - smem_u32(smem_raw)));
+  float* s_thr_min = s_thr + TC_Q;
   uint4* s_queue = reinterpret_cast<uint4*>(smem_raw + (queue_smem - smem_u32(smem_raw)));
   int* s_qcnt = reinterpret_cast<int*>(s_queue + 8 * QCAP);
   if (threadIdx.x < 8) s_qcnt[threadIdx.x] = 0;
@@ -111,6 +118,15 @@ scan_tc_kernel(const __grid_constant__ CUtensorMap map_corpus, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  if (MODE == 1 && warp >= 2) {   // every consumer warp fills the same eight minima (same values, benign) for its own use
+    for (int g8 = 0; g8 < 8; ++g8) {
+      float t = s_thr[g8 * 32 + lane];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) t = fminf(t, __shfl_xor_sync(0xffffffffu, t, o));
+      if (lane == 0) s_thr_min[g8] = t;
+    }
+    __syncwarp();
+  }
 
   if (warp == 0) {
     if (lane == 0) {
@@ -165,12 +181,27 @@ scan_tc_kernel(const __grid_constant__ CUtensorMap map_corpus, const __grid_cons
       const long long row = tile * TC_ROWS + quad * 32 + lane;
       const bool row_ok = row < a.rows;
       const uint32_t taddr = tmem_base + acc * TC_Q + ((uint32_t)(quad * 32) << 16) + half * 128;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        const int u0 = half * 128 + c * 32;
-        if (MODE == 1) {
+      if (MODE == 1) {
+        // the warp's whole slice of the tile (32 rows x 128 queries) in one round trip to TMEM, then the accumulator
+        // goes straight back to the MMA warp: the filtering below works from registers
+        uint32_t rr[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32_nowait(taddr + c * 32, rr[c]);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(tempty_bar(acc));
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t (&r)[32] = rr[c];
+          const int u0 = half * 128 + c * 32;
+          // First a filter: the largest of the row's 32 scores against the smallest of the 32 thresholds (16
+          // three-input max instructions).  Survivors are a few in 10^5 elements, so for almost every group the
+          // warp stops here; the exact per-column test below runs only when some lane's group passes.
+          float mx = max3(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
+#pragma unroll
+          for (int k = 3; k + 1 < 32; k += 2) mx = max3(mx, __uint_as_float(r[k]), __uint_as_float(r[k + 1]));
+          mx = fmaxf(mx, __uint_as_float(r[31]));
+          if (!__any_sync(0xffffffffu, row_ok && mx >= s_thr_min[(u0 >> 5)])) continue;
           // branch-free hit mask over the 32 columns, then the rare hits one by one: a taken branch per
           // element (hit code laid out inline 32 times) made this loop instruction-fetch bound
           uint32_t hits = 0;
@@ -192,7 +223,13 @@ scan_tc_kernel(const __grid_constant__ CUtensorMap map_corpus, const __grid_cons
             stage_hit(a.counts, a.surv, a.cap, s_queue + ew * QCAP, &s_qcnt[ew], u0 + k, __uint_as_float(bits),
                       (uint32_t)(a.row_offset + row));
           }
-        } else {
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          const int u0 = half * 128 + c * 32;
           const long long grp = w * 4 + quad;
 #pragma unroll
           for (int k = 0; k < 32; ++k) {
@@ -203,9 +240,9 @@ scan_tc_kernel(const __grid_constant__ CUtensorMap map_corpus, const __grid_cons
             if (lane == 0 && u < a.B) a.gmax[(size_t)u * a.n_groups + grp] = unord32(mx);
           }
         }
+        tc_fence_before();
+        mbar_arrive(tempty_bar(acc));
       }
-      tc_fence_before();
-      mbar_arrive(tempty_bar(acc));
       if (MODE == 1) {
         __syncwarp();
         const int nq = s_qcnt[ew] < QCAP ? s_qcnt[ew] : QCAP;
@@ -253,7 +290,7 @@ phx_status tc_scan_make_maps(CUtensorMap* map_corpus, CUtensorMap* map_users, co
 phx_status tc_scan_launch(const CUtensorMap& map_corpus, const CUtensorMap& map_users, const TcScanArgs& a, int mode,
                           int num_sms, int* err_flag, cudaStream_t stream, std::string& err) {
   const int kblk = a.dim / BK;
-  const size_t smem = (size_t)kblk * TC_Q * 128 + (size_t)TC_STAGES * kblk * TC_ROWS * 128 + TC_Q * 4 + 8 * QCAP * 16 + 64 + 256 + 1024;
+  const size_t smem = (size_t)kblk * TC_Q * 128 + (size_t)TC_STAGES * kblk * TC_ROWS * 128 + TC_Q * 4 + 32 + 8 * QCAP * 16 + 64 + 256 + 1024;
   const long long n_tiles = (a.rows + TC_ROWS - 1) / TC_ROWS;
   const long long n_work = (mode == 0) ? (n_tiles + a.stride - 1) / a.stride : n_tiles;
   const int grid = (int)(n_work < num_sms ? n_work : num_sms);
