@@ -69,17 +69,24 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   constexpr int KBLK = (DH == 64) ? 128 : 64;   // keys per block (keeps shared memory at 80 KB: two CTAs per SM)
   constexpr int DCH = DH / 64;                  // 64-column chunks of the head dim
   constexpr int PCH = KBLK / 64;                // 64-key slabs of P
-  constexpr uint32_t TM_S = 0, TM_O = 128;      // TMEM columns of S and O
+  // S is double-buffered in TMEM (and K in shared memory): S of block j+1 is computed while the softmax warps are
+  // still on block j, so the tensor pipe and the softmax overlap inside one CTA.  KBLK <= 64 or two S buffers of
+  // 128 columns would not fit next to O in the CTA's 256 columns; at head dim 64 (KBLK 128) S stays single.
+  constexpr int NSB = (KBLK <= 64) ? 2 : 1;     // S buffers (TMEM) = K buffers (shared memory)
+  constexpr uint32_t TM_S = 0, TM_O = 128;      // TMEM columns of S (NSB x KBLK) and O
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sQ = base;                               // DCH x [128 x 128 B]; reused to stage the output
-  const uint32_t sK = sQ + DCH * SLAB;                    // DCH x [KBLK x 128 B]
-  const uint32_t sV = sK + DCH * KBLK * 128;              // DCH x [KBLK x 128 B]
+  const uint32_t sK = sQ + DCH * SLAB;                    // NSB x DCH x [KBLK x 128 B]
+  const uint32_t sV = sK + NSB * DCH * KBLK * 128;        // DCH x [KBLK x 128 B]
   const uint32_t sP = sV + DCH * KBLK * 128;              // PCH x [128 x 128 B]
   const uint32_t sMask = sP + PCH * SLAB;                 // [2][4] key-validity words
   const uint32_t bars = sMask + 64;
-  const uint32_t q_full = bars, k_full = bars + 8, k_empty = bars + 16, v_full = bars + 24, v_empty = bars + 32,
-                 s_full = bars + 40, p_ready = bars + 48, o_done = bars + 56, tmem_slot = bars + 64;
+  const uint32_t q_full = bars, v_full = bars + 8, v_empty = bars + 16, p_ready = bars + 24, o_done = bars + 32,
+                 tmem_slot = bars + 88;
+  auto k_full = [&](int i) { return bars + 40u + 8u * i; };
+  auto k_empty = [&](int i) { return bars + 56u + 8u * i; };
+  auto s_full = [&](int i) { return bars + 72u + 8u * i; };
   uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
   uint32_t* mask_words = reinterpret_cast<uint32_t*>(smem_raw + (sMask - smem_u32(smem_raw)));
 
@@ -92,8 +99,8 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   volatile int* verr = a.err_flag;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1); mbar_init(k_full, 1); mbar_init(k_empty, 1); mbar_init(v_full, 1); mbar_init(v_empty, 1);
-    mbar_init(s_full, 1); mbar_init(p_ready, 128); mbar_init(o_done, 1);
+    mbar_init(q_full, 1); mbar_init(v_full, 1); mbar_init(v_empty, 1); mbar_init(p_ready, 128); mbar_init(o_done, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(k_full(i), 1); mbar_init(k_empty(i), 1); mbar_init(s_full(i), 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(tmem_slot, 256);
@@ -107,11 +114,17 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     if (lane == 0) {
       mbar_expect_tx(q_full, DCH * SLAB);
       for (int c = 0; c < DCH; ++c) tma_load_3d(sQ + c * SLAB, &map_q, q_full, h * a.q_head_stride + c * 64, q0, b);
+      auto load_k = [&](int j) {   // K block j into buffer j % NSB, once S of block j - NSB has been computed
+        const int kb = j % NSB; const uint32_t use = (uint32_t)(j / NSB);
+        mbar_wait(k_empty(kb), (use & 1) ^ 1, verr);
+        mbar_expect_tx(k_full(kb), DCH * KBLK * 128);
+        for (int c = 0; c < DCH; ++c)
+          tma_load_3d(sK + (kb * DCH + c) * KBLK * 128, &map_k, k_full(kb), hk * a.k_head_stride + c * 64, j * KBLK, b);
+      };
+      for (int j = 0; j < NSB - 1 && j < n_blocks; ++j) load_k(j);
       for (int j = 0; j < n_blocks; ++j) {
         const uint32_t ph = (uint32_t)(j & 1);
-        mbar_wait(k_empty, ph ^ 1, verr);
-        mbar_expect_tx(k_full, DCH * KBLK * 128);
-        for (int c = 0; c < DCH; ++c) tma_load_3d(sK + c * KBLK * 128, &map_k, k_full, hk * a.k_head_stride + c * 64, j * KBLK, b);
+        if (j + NSB - 1 < n_blocks) load_k(j + NSB - 1);
         mbar_wait(v_empty, ph ^ 1, verr);
         mbar_expect_tx(v_full, DCH * KBLK * 128);
         for (int c = 0; c < DCH; ++c) tma_load_3d(sV + c * KBLK * 128, &map_v, v_full, hk * a.v_head_stride + c * 64, j * KBLK, b);
@@ -123,18 +136,24 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       constexpr uint32_t idesc_s = make_idesc(QT, KBLK);
       constexpr uint32_t idesc_o = make_idesc_b_mn(QT, DH);
       mbar_wait(q_full, 0, verr);
-      for (int j = 0; j < n_blocks; ++j) {
-        const uint32_t ph = (uint32_t)(j & 1);
-        mbar_wait(k_full, ph, verr);
+      auto issue_s = [&](int j) {   // S(j) = Q K(j)^T into S buffer j % NSB
+        const int kb = j % NSB; const uint32_t use = (uint32_t)(j / NSB);
+        mbar_wait(k_full(kb), use & 1, verr);
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < DCH; ++c) {
-          const uint64_t qd = make_smem_desc(sQ + c * SLAB), kd = make_smem_desc(sK + c * KBLK * 128);
+          const uint64_t qd = make_smem_desc(sQ + c * SLAB), kd = make_smem_desc(sK + (kb * DCH + c) * KBLK * 128);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_bf16(tmem + TM_S, qd + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), idesc_s, (c | k) != 0);
+          for (int k = 0; k < 4; ++k) umma_bf16(tmem + TM_S + kb * KBLK, qd + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), idesc_s, (c | k) != 0);
         }
-        umma_commit(k_empty);
-        umma_commit(s_full);
+        umma_commit(k_empty(kb));
+        umma_commit(s_full(kb));
+      };
+      for (int j = 0; j < NSB - 1 && j < n_blocks; ++j) issue_s(j);
+      for (int j = 0; j < n_blocks; ++j) {
+        const uint32_t ph = (uint32_t)(j & 1);
+        // the S buffer of block j + NSB - 1 was last read by the softmax of block j - 1, whose P has been awaited below
+        if (j + NSB - 1 < n_blocks) issue_s(j + NSB - 1);
         mbar_wait(p_ready, ph, verr);
         mbar_wait(v_full, ph, verr);
         tc_fence_after();
@@ -177,11 +196,12 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
 #pragma unroll
       for (int w = 0; w < KBLK / 32; ++w) all_ok = all_ok && (kmask[w] == 0xffffffffu);
 
-      mbar_wait(s_full, ph, verr);
+      mbar_wait(s_full(j % NSB), (uint32_t)((j / NSB) & 1), verr);
       tc_fence_after();
       float s[KBLK];
 #pragma unroll
-      for (int c = 0; c < KBLK / 32; ++c) tmem_ld32(tmem + TM_S + lane_base + c * 32, reinterpret_cast<uint32_t*>(s) + c * 32);
+      for (int c = 0; c < KBLK / 32; ++c) tmem_ld32_nowait(tmem + TM_S + (j % NSB) * KBLK + lane_base + c * 32, reinterpret_cast<uint32_t*>(s) + c * 32);
+      tmem_ld_wait();
       if (CAP) {
 #pragma unroll
         for (int k = 0; k < KBLK; ++k) s[k] = capped_log2(s[k], a.sm_scale, a.cap, a.cap_method);
@@ -194,9 +214,14 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       float bm = -INFINITY;
 #pragma unroll
       for (int k = 0; k < KBLK; ++k) bm = fmaxf(bm, s[k]);
-      const float m_new = fmaxf(m, bm * csc);
+      // The reference point of the exponentials only has to bound them, not equal the running maximum: it moves
+      // when the maximum has grown by more than 2^8 since it was set (P stays below 256, exact in bf16 up to the same
+      // power of two), which spares the rescaling of O in tensor memory for almost every block.
+      const float m_true = fmaxf(m, bm * csc);
+      const bool move = __any_sync(0xffffffffu, m_true > m + 8.0f || (m == -INFINITY && m_true != -INFINITY));
+      const float m_new = move ? m_true : m;
       const float mns = (m_new == -INFINITY) ? 0.f : m_new;   // finite stand-in while nothing is allowed yet
-      const float alpha = ex2f(m - mns);                      // -inf - finite -> 0
+      const float alpha = ex2f(m - mns);                      // -inf - finite -> 0; unmoved: 1
       m = m_new;
       float ls = 0.f;
 #pragma unroll
@@ -587,7 +612,8 @@ template <int DH, bool CAP>
 phx_status launch_tc(const AttnArgs& a, int* err_flag, cudaStream_t stream, std::string& err) {
   constexpr int KBLK = (DH == 64) ? 128 : 64;
   constexpr int DCH = DH / 64, PCH = KBLK / 64;
-  const size_t smem = (size_t)DCH * SLAB + 2 * (size_t)DCH * KBLK * 128 + (size_t)PCH * SLAB + 64 + 128 + 1024;
+  constexpr int NSB = (KBLK <= 64) ? 2 : 1;   // K buffers, as in the kernel
+  const size_t smem = (size_t)DCH * SLAB + (NSB + 1) * (size_t)DCH * KBLK * 128 + (size_t)PCH * SLAB + 64 + 128 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
     PHX_CUDA_TRY(cudaFuncSetAttribute(ranker_attention_tc_kernel<DH, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), err);
