@@ -44,6 +44,11 @@ __device__ __forceinline__ float capped_log2(float s, float sm_scale, float cap,
   else if (method == 2) v = cap * tanhf(v / cap);
   return v * 1.4426950408889634f;
 }
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ void bar_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ void st_shared_16(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
@@ -211,9 +216,18 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         for (int k = 0; k < KBLK; ++k)
           if (!((kmask[k >> 5] >> (k & 31)) & 1u)) s[k] = -INFINITY;
       }
-      float bm = -INFINITY;
+      float bm;
+      {
+        float b4[4] = {s[0], s[1], s[2], s[3]};   // four chains of three-input max
 #pragma unroll
-      for (int k = 0; k < KBLK; ++k) bm = fmaxf(bm, s[k]);
+        for (int k = 4; k + 7 < KBLK + 4 && k + 7 < KBLK; k += 8) {
+          b4[0] = max3f(b4[0], s[k], s[k + 1]); b4[1] = max3f(b4[1], s[k + 2], s[k + 3]);
+          b4[2] = max3f(b4[2], s[k + 4], s[k + 5]); b4[3] = max3f(b4[3], s[k + 6], s[k + 7]);
+        }
+        bm = fmaxf(max3f(b4[0], b4[1], b4[2]), b4[3]);
+#pragma unroll
+        for (int k = KBLK - 4; k < KBLK; ++k) bm = fmaxf(bm, s[k]);   // the tail the 8-wide loop leaves (4 elements)
+      }
       // The reference point of the exponentials only has to bound them, not equal the running maximum: it moves
       // when the maximum has grown by more than 2^8 since it was set (P stays below 256, exact in bf16 up to the same
       // power of two), which spares the rescaling of O in tensor memory for almost every block.
@@ -223,9 +237,18 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       const float mns = (m_new == -INFINITY) ? 0.f : m_new;   // finite stand-in while nothing is allowed yet
       const float alpha = ex2f(m - mns);                      // -inf - finite -> 0; unmoved: 1
       m = m_new;
-      float ls = 0.f;
+      float ls;
+      {
+        const float2 c2 = make_float2(csc, csc), n2 = make_float2(-mns, -mns);
+        float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-      for (int k = 0; k < KBLK; ++k) { s[k] = ex2f(fmaf(s[k], csc, -mns)); ls += s[k]; }   // masked: 2^-inf = 0
+        for (int k = 0; k < KBLK; k += 2) {   // packed fp32: two columns per instruction; masked: 2^-inf = 0
+          const float2 e = __ffma2_rn(make_float2(s[k], s[k + 1]), c2, n2);
+          s[k] = ex2f(e.x); s[k + 1] = ex2f(e.y);
+          acc2[(k >> 1) & 1] = __fadd2_rn(acc2[(k >> 1) & 1], make_float2(s[k], s[k + 1]));
+        }
+        ls = (acc2[0].x + acc2[0].y) + (acc2[1].x + acc2[1].y);
+      }
       l = l * alpha + ls;
 
       if (j > 0) {
