@@ -32,6 +32,7 @@ using namespace sm100;
 constexpr int QT = 128;            // query rows per CTA
 constexpr int A_THREADS = 192;
 constexpr int SLAB = QT * 128;     // bytes of one [128 rows x 64 bf16] swizzled tile
+constexpr int TC_MAX_BLOCKS = 256; // key blocks whose validity words fit the CTA's table
 
 __device__ __forceinline__ float ex2f(float x) {
   float y;
@@ -85,8 +86,8 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   const uint32_t sK = sQ + DCH * SLAB;                    // NSB x DCH x [KBLK x 128 B]
   const uint32_t sV = sK + NSB * DCH * KBLK * 128;        // DCH x [KBLK x 128 B]
   const uint32_t sP = sV + DCH * KBLK * 128;              // PCH x [128 x 128 B]
-  const uint32_t sMask = sP + PCH * SLAB;                 // [2][4] key-validity words
-  const uint32_t bars = sMask + 64;
+  const uint32_t sMask = sP + PCH * SLAB;                 // [TC_MAX_BLOCKS][4] key-validity words
+  const uint32_t bars = sMask + TC_MAX_BLOCKS * 16;
   const uint32_t q_full = bars, v_full = bars + 8, v_empty = bars + 16, p_ready = bars + 24, o_done = bars + 32,
                  tmem_slot = bars + 88;
   auto k_full = [&](int i) { return bars + 40u + 8u * i; };
@@ -184,19 +185,21 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     const float csc = CAP ? 1.0f : a.sm_scale * 1.4426950408889634f;
     float m = -INFINITY, l = 0.f;
 
+    // validity of every history key, once per CTA (thread r looks at key r of each block; the loads of all blocks are
+    // in flight together instead of one exposed round trip per block)
+    for (int j = 0; j < n_blocks; ++j) {
+      const int key = j * KBLK + r;
+      const bool ok = (r < KBLK) && (key < n_hist) && (a.seg[tok0 + key] == 1);
+      const uint32_t word = __ballot_sync(0xffffffffu, ok);
+      if (lane == 0) mask_words[j * 4 + quad] = word;
+    }
+    bar_sync_128();
+
     for (int j = 0; j < n_blocks; ++j) {
       const uint32_t ph = (uint32_t)(j & 1);
-      // validity of the block's keys: thread r looks at key r of the block
-      {
-        const int key = j * KBLK + r;
-        const bool ok = (r < KBLK) && (key < n_hist) && (a.seg[tok0 + key] == 1);
-        const uint32_t word = __ballot_sync(0xffffffffu, ok);
-        if (lane == 0) mask_words[(j & 1) * 4 + quad] = word;
-      }
-      bar_sync_128();
       uint32_t kmask[4];
 #pragma unroll
-      for (int w = 0; w < 4; ++w) kmask[w] = mask_words[(j & 1) * 4 + w];
+      for (int w = 0; w < 4; ++w) kmask[w] = mask_words[j * 4 + w];
       bool all_ok = true;
 #pragma unroll
       for (int w = 0; w < KBLK / 32; ++w) all_ok = all_ok && (kmask[w] == 0xffffffffu);
@@ -636,7 +639,7 @@ phx_status launch_tc(const AttnArgs& a, int* err_flag, cudaStream_t stream, std:
   constexpr int KBLK = (DH == 64) ? 128 : 64;
   constexpr int DCH = DH / 64, PCH = KBLK / 64;
   constexpr int NSB = (KBLK <= 64) ? 2 : 1;   // K buffers, as in the kernel
-  const size_t smem = (size_t)DCH * SLAB + (NSB + 1) * (size_t)DCH * KBLK * 128 + (size_t)PCH * SLAB + 64 + 128 + 1024;
+  const size_t smem = (size_t)DCH * SLAB + (NSB + 1) * (size_t)DCH * KBLK * 128 + (size_t)PCH * SLAB + TC_MAX_BLOCKS * 16 + 128 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
     PHX_CUDA_TRY(cudaFuncSetAttribute(ranker_attention_tc_kernel<DH, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), err);
@@ -690,6 +693,10 @@ phx_status launch_resident(const AttnArgs& a, int* err_flag, cudaStream_t stream
 
 bool ranker_attention_tc_supported(const AttnArgs& a) {
   if (a.dh != 64 && a.dh != 128) return false;
+  {
+    const int n_hist = a.hist_len < a.T ? a.hist_len : a.T;
+    if ((n_hist + 63) / 64 > TC_MAX_BLOCKS) return false;   // validity table of the CTA
+  }
   // TMA: 16-byte aligned bases and strides, head offsets that are multiples of 8 elements
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   return al(a.q) && al(a.k) && al(a.v) && al(a.out) && a.q_tok_stride % 8 == 0 && a.k_tok_stride % 8 == 0 &&
