@@ -202,6 +202,26 @@ phx_status phx_last_launch_count(phx_engine* e, int32_t* n);
  * (the gather-sum output before scaling), "hidden" bf16 bits [B,T,D] (trunk output). */
 phx_status phx_debug_read(phx_engine* e, const char* what, void* host, size_t nbytes);
 
+/* ---- row-sharded table, exchange by all-to-all ------------------------------------------------------------------
+ * The device-side steps of the reference's id / row exchange (phoenix/xrex/cuda/row_emb/src/row_emb_comm.cc:655-743:
+ * all-to-all of ids, owner-side gather, all-to-all of rows; combine by sum as recsys_embedding.py:282-331).  The two
+ * collectives themselves are issued by the host side (NCCL, `parallel.ShardedGatherSum`).  All pointers are device
+ * pointers, `stream` is a cudaStream_t (null = default stream); nothing is allocated; errors: phx_global_error().
+ *
+ * phx_shard_bucket: rows_dev int32 [n_req] unified-table rows (phx_hash_ids_device) -> counts_dev int32 [world]
+ * requests per owning rank (owner = row / rows_per_shard), send_rows_dev int32 [n_req] the owner-local row numbers
+ * grouped by owner, pos_dev int32 [n_req] the slot of request i in that grouped order; cursor_dev int32 [world] is
+ * scratch (on return: the end of each bucket). */
+phx_status phx_shard_bucket(const int32_t* rows_dev, int64_t n_req, int64_t rows_per_shard, int32_t world, int32_t* counts_dev,
+                            int32_t* cursor_dev, int32_t* send_rows_dev, int32_t* pos_dev, void* stream);
+/* Owner side: out_dev bf16 [m, width] = shard rows local_rows_dev[0..m) (out of range -> row 0, emb_table.rs:124-140). */
+phx_status phx_shard_gather_rows(const uint16_t* shard_dev, int64_t shard_rows, const int32_t* local_rows_dev, int64_t m,
+                                 int32_t width, uint16_t* out_dev, void* stream);
+/* Requester side: out_dev bf16 [n, width], row i = bf16(sum over h of rows_dev[pos_dev[i*num_hashes + h]]) in fp32, in
+ * hash-slot order: bit-identical to phx_gather_sum_device on the unsharded table. */
+phx_status phx_shard_sum_rows(const uint16_t* rows_dev, const int32_t* pos_dev, int64_t n, int32_t num_hashes, int32_t width,
+                              uint16_t* out_dev, void* stream);
+
 /* ---- stand-alone operators (micro-benchmarks and parity tests of single kernels) ------------- */
 
 /* Multi-hash id -> unified-table rows; `family`: 0 user, 1 item, 2 author, 3 ip.

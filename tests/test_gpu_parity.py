@@ -339,3 +339,70 @@ def test_topk_large_shard_uses_pivot_path(torch, monkeypatch, impl, dim):
     np.testing.assert_array_equal(ids.cpu().numpy(), want_i)
     np.testing.assert_array_equal(sc.cpu().numpy(), want_s)
     sh.close()
+
+
+def test_sharded_gather_exchange_kernels_bit_identical(torch):
+    """The device-side steps of the all-to-all exchange (bucket by owner, owner-side gather, fixed-order sum), with
+    the two collectives emulated by slicing: two "ranks" on one device, each holding half of the table.  The result
+    is bit-identical to the gather-sum over the unsharded table."""
+    import x_algorithm_b200 as px
+    from x_algorithm_b200 import _lib
+    from x_algorithm_b200.engine import _ptr
+    from x_algorithm_b200.parallel import rows_per_shard
+    lib = _lib.lib
+    W, n, width, H = 2, 5000, 256, 4
+    mk = lambda **kw: px.PhoenixConfig(emb_size=width, num_layers=1, num_q_heads=4, num_kv_heads=4, key_size=64, history_len=1,
+                                       num_candidates=1, max_batch=1, num_hashes=H, table_size=1 << 12, **kw)
+    full = px.PhoenixEngine(mk(), 0)
+    full.table_fill_synthetic(7, 0.0625)
+    shards = [px.PhoenixEngine(mk(table_world=W, table_rank=r), 0) for r in range(W)]
+    for e in shards:
+        e.table_fill_synthetic(7, 0.0625)
+    rps = rows_per_shard(full.cfg.table_rows, W)
+    rng = np.random.default_rng(3)
+    ids = [torch.from_numpy(rng.integers(-2**40, 2**40, n).astype(np.int64)).cuda() for _ in range(W)]
+    ids[0][:3] = 0                                              # id 0 -> row 0 for every hash
+    i32 = dict(dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    rows, send, pos, counts = [], [], [], []
+    for r in range(W):
+        rw = torch.empty(n * H, **i32)
+        shards[r].hash_ids_device(1, ids[r], n, rw); shards[r].sync()
+        sr, ps, ct, cur = torch.empty(n * H, **i32), torch.empty(n * H, **i32), torch.empty(W, **i32), torch.empty(W, **i32)
+        assert lib.phx_shard_bucket(_ptr(rw), n * H, rps, W, _ptr(ct), _ptr(cur), _ptr(sr), _ptr(ps), st) == 0
+        torch.cuda.synchronize()
+        rows.append(rw); send.append(sr); pos.append(ps); counts.append(ct.tolist())
+        assert sum(counts[r]) == n * H
+        owner = (rw.cpu().numpy() // rps)
+        assert counts[r] == [int((owner == o).sum()) for o in range(W)]
+        # every request landed in its owner's bucket with the right local row
+        base = np.concatenate([[0], np.cumsum(counts[r])])
+        p_np, s_np, r_np = ps.cpu().numpy(), sr.cpu().numpy(), rw.cpu().numpy()
+        assert sorted(p_np.tolist()) == list(range(n * H))
+        assert ((p_np >= base[owner]) & (p_np < base[owner + 1])).all()
+        np.testing.assert_array_equal(s_np[p_np], r_np - owner * rps)
+    # "all-to-all" of the row numbers, owner-side gather, "all-to-all" of the rows
+    back = [torch.empty((n * H, width), dtype=torch.int16, device="cuda") for _ in range(W)]
+    for o in range(W):
+        parts = []
+        for r in range(W):
+            b0 = sum(counts[r][:o])
+            parts.append(send[r][b0:b0 + counts[r][o]])
+        req = torch.cat(parts)
+        got = torch.empty((req.numel(), width), dtype=torch.int16, device="cuda")
+        assert lib.phx_shard_gather_rows(shards[o].table_local_ptr(), rps, _ptr(req), req.numel(), width, _ptr(got), st) == 0
+        off = 0
+        for r in range(W):
+            b0 = sum(counts[r][:o])
+            back[r][b0:b0 + counts[r][o]] = got[off:off + counts[r][o]]
+            off += counts[r][o]
+    for r in range(W):
+        out = torch.empty((n, width), dtype=torch.int16, device="cuda")
+        assert lib.phx_shard_sum_rows(_ptr(back[r]), _ptr(pos[r]), n, H, width, _ptr(out), st) == 0
+        want = torch.empty_like(out)
+        full.gather_sum_device(1, ids[r], n, want); full.sync()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want)
+    assert lib.phx_shard_bucket(0, 1, rps, W, 0, 0, 0, 0, st) == 1        # PHX_E_ARG on null pointers
+    for e in shards + [full]:
+        e.close()

@@ -73,6 +73,9 @@ SIGNATURES = {
     "phx_profile_read": (C.c_int32, [_P, C.POINTER(C.c_float), C.POINTER(C.c_int32)]),
     "phx_debug_read": (C.c_int32, [_P, C.c_char_p, _P, C.c_size_t]),
     "phx_hash_ids_device": (C.c_int32, [_P, C.c_int32, _P, C.c_int64, _P]),
+    "phx_shard_bucket": (C.c_int32, [_P, C.c_int64, C.c_int64, C.c_int32, _P, _P, _P, _P, _P]),
+    "phx_shard_gather_rows": (C.c_int32, [_P, C.c_int64, _P, C.c_int64, C.c_int32, _P, _P]),
+    "phx_shard_sum_rows": (C.c_int32, [_P, _P, C.c_int64, C.c_int32, C.c_int32, _P, _P]),
     "phx_gather_sum_device": (C.c_int32, [_P, C.c_int32, _P, C.c_int64, _P]),
     "phx_ranker_attention_device": (C.c_int32, [C.c_int32, _P, _P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32,
                                                 C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_float, C.c_int32,

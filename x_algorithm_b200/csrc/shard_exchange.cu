@@ -1,0 +1,177 @@
+// Row-sharded embedding table, exchange by all-to-all: the device-side steps around the two collectives of the
+// reference's id / row exchange (phoenix/xrex/cuda/row_emb/src/row_emb_comm.cc:655-743: ids to their owners, the
+// owner-side gather, rows back to the requesters; combine by sum as recsys_embedding.py:282-331).
+//
+//   requester:  hash ids -> unified-table rows (phx_hash_ids_device)
+//               phx_shard_bucket:       group the row requests by owning rank (counting sort over `world` buckets),
+//                                       remember where each request went
+//   collective: counts, then the local row numbers, to their owners        (NCCL all-to-all, issued by the host side)
+//   owner:      phx_shard_gather_rows:  copy the requested rows of the local shard into one send block
+//   collective: the rows back to the requesters                            (NCCL all-to-all)
+//   requester:  phx_shard_sum_rows:     per id, the fp32 sum of its rows in hash-slot order, one rounding to bf16
+//
+// The sum order is by hash slot and does not depend on how requests were grouped or on the number of ranks, so the
+// result is bit-identical to the single-table gather-sum kernel.  Every function launches on the stream it is
+// given (the host side passes the stream its collectives run on) and allocates nothing.
+#include <string>
+
+#include "common.cuh"
+
+namespace phx {
+namespace {
+
+constexpr int SX_THREADS = 256;
+constexpr int SX_PER_THREAD = 8;
+constexpr int SX_MAX_WORLD = 64;
+
+__global__ void __launch_bounds__(SX_THREADS) sx_count_kernel(const int* __restrict__ rows, long long n, long long rows_per_shard,
+                                                              int world, int* __restrict__ counts) {
+  __shared__ int hist[SX_MAX_WORLD];
+  if (threadIdx.x < world) hist[threadIdx.x] = 0;
+  __syncthreads();
+  const long long base = (long long)blockIdx.x * SX_THREADS * SX_PER_THREAD;
+#pragma unroll
+  for (int k = 0; k < SX_PER_THREAD; ++k) {
+    const long long i = base + k * SX_THREADS + threadIdx.x;
+    if (i < n) atomicAdd(&hist[(int)(rows[i] / rows_per_shard)], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x < world && hist[threadIdx.x]) atomicAdd(&counts[threadIdx.x], hist[threadIdx.x]);
+}
+
+// cursor[o] = first slot of owner o's bucket (exclusive scan of the counts)
+__global__ void sx_scan_kernel(const int* __restrict__ counts, int world, int* __restrict__ cursor) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int run = 0;
+    for (int o = 0; o < world; ++o) { cursor[o] = run; run += counts[o]; }
+  }
+}
+
+// Each block reserves a range in every bucket for its own requests with one global atomic per owner, then places
+// them with shared-memory atomics.  The order inside a bucket is arbitrary; `pos` records it.
+__global__ void __launch_bounds__(SX_THREADS) sx_scatter_kernel(const int* __restrict__ rows, long long n, long long rows_per_shard,
+                                                                int world, int* __restrict__ cursor, int* __restrict__ send_rows,
+                                                                int* __restrict__ pos) {
+  __shared__ int hist[SX_MAX_WORLD];
+  __shared__ int gbase[SX_MAX_WORLD];
+  if (threadIdx.x < world) hist[threadIdx.x] = 0;
+  __syncthreads();
+  const long long base = (long long)blockIdx.x * SX_THREADS * SX_PER_THREAD;
+  int owner[SX_PER_THREAD], local[SX_PER_THREAD], slot[SX_PER_THREAD];
+#pragma unroll
+  for (int k = 0; k < SX_PER_THREAD; ++k) {
+    const long long i = base + k * SX_THREADS + threadIdx.x;
+    owner[k] = -1;
+    if (i < n) {
+      const int r = rows[i];
+      owner[k] = (int)(r / rows_per_shard);
+      local[k] = (int)(r - owner[k] * rows_per_shard);
+      slot[k] = atomicAdd(&hist[owner[k]], 1);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < world) gbase[threadIdx.x] = hist[threadIdx.x] ? atomicAdd(&cursor[threadIdx.x], hist[threadIdx.x]) : 0;
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < SX_PER_THREAD; ++k) {
+    if (owner[k] >= 0) {
+      const long long i = base + k * SX_THREADS + threadIdx.x;
+      const int p = gbase[owner[k]] + slot[k];
+      send_rows[p] = local[k];
+      pos[i] = p;
+    }
+  }
+}
+
+// one warp per requested row: 16 bytes per lane and step
+__global__ void __launch_bounds__(256) sx_gather_rows_kernel(const bf16* __restrict__ shard, long long shard_rows,
+                                                             const int* __restrict__ idx, long long m, int width,
+                                                             bf16* __restrict__ out) {
+  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= m) return;
+  long long r = idx[w];
+  if (r < 0 || r >= shard_rows) r = 0;   // out of range -> row 0, like the reference gather (emb_table.rs:124-140)
+  const uint4* src = reinterpret_cast<const uint4*>(shard + r * width);
+  uint4* dst = reinterpret_cast<uint4*>(out + w * width);
+  for (int c = lane; c < width / 8; c += 32) __stcs(dst + c, __ldg(src + c));
+}
+
+// one warp per id: rows at pos[i*H + h], h = 0..H-1, summed in that order in fp32, rounded once
+__global__ void __launch_bounds__(256) sx_sum_rows_kernel(const bf16* __restrict__ rows, const int* __restrict__ pos, long long n,
+                                                          int H, int width, bf16* __restrict__ out) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (i >= n) return;
+  int p[PHX_MAX_HASHES];
+#pragma unroll
+  for (int h = 0; h < PHX_MAX_HASHES; ++h) p[h] = (h < H) ? pos[i * H + h] : 0;
+  for (int c = lane; c < width / 8; c += 32) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int h = 0; h < PHX_MAX_HASHES; ++h) {
+      if (h < H) {
+        const uint4 u = __ldcs(reinterpret_cast<const uint4*>(rows + (long long)p[h] * width) + c);
+        const float2 a = unpack_bf2(u.x), b = unpack_bf2(u.y), cc = unpack_bf2(u.z), d = unpack_bf2(u.w);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+        acc[4] += cc.x; acc[5] += cc.y; acc[6] += d.x; acc[7] += d.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf2(acc[0], acc[1]); o.y = pack_bf2(acc[2], acc[3]); o.z = pack_bf2(acc[4], acc[5]); o.w = pack_bf2(acc[6], acc[7]);
+    __stcs(reinterpret_cast<uint4*>(out + i * width) + c, o);
+  }
+}
+
+phx_status fail_arg(const char* msg) { set_global_error(msg); return PHX_E_ARG; }
+phx_status check_launch(const char* what) {
+  cudaError_t ce = cudaGetLastError();
+  if (ce != cudaSuccess) { set_global_error(std::string(what) + ": " + cudaGetErrorString(ce)); return PHX_E_CUDA; }
+  return PHX_OK;
+}
+
+}  // namespace
+}  // namespace phx
+
+using namespace phx;
+
+extern "C" {
+
+phx_status phx_shard_bucket(const int32_t* rows_dev, int64_t n_req, int64_t rows_per_shard, int32_t world, int32_t* counts_dev,
+                            int32_t* cursor_dev, int32_t* send_rows_dev, int32_t* pos_dev, void* stream) {
+  if (!rows_dev || !counts_dev || !cursor_dev || !send_rows_dev || !pos_dev || n_req < 0 || rows_per_shard <= 0 || world < 1 ||
+      world > SX_MAX_WORLD)
+    return fail_arg("phx_shard_bucket: bad argument (world must be 1..64)");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cudaMemsetAsync(counts_dev, 0, sizeof(int32_t) * world, st) != cudaSuccess) return check_launch("phx_shard_bucket");
+  if (n_req > 0) {
+    const unsigned blocks = (unsigned)((n_req + SX_THREADS * SX_PER_THREAD - 1) / (SX_THREADS * SX_PER_THREAD));
+    sx_count_kernel<<<blocks, SX_THREADS, 0, st>>>(rows_dev, n_req, rows_per_shard, world, counts_dev);
+    sx_scan_kernel<<<1, 32, 0, st>>>(counts_dev, world, cursor_dev);
+    sx_scatter_kernel<<<blocks, SX_THREADS, 0, st>>>(rows_dev, n_req, rows_per_shard, world, cursor_dev, send_rows_dev, pos_dev);
+  }
+  return check_launch("phx_shard_bucket");
+}
+
+phx_status phx_shard_gather_rows(const uint16_t* shard_dev, int64_t shard_rows, const int32_t* local_rows_dev, int64_t m,
+                                 int32_t width, uint16_t* out_dev, void* stream) {
+  if (!shard_dev || shard_rows <= 0 || m < 0 || width <= 0 || width % 8 != 0 || (m > 0 && (!local_rows_dev || !out_dev)))
+    return fail_arg("phx_shard_gather_rows: bad argument (width must be a multiple of 8)");
+  if (m == 0) return PHX_OK;
+  sx_gather_rows_kernel<<<(unsigned)((m * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const bf16*)shard_dev, shard_rows, local_rows_dev, m, width, (bf16*)out_dev);
+  return check_launch("phx_shard_gather_rows");
+}
+
+phx_status phx_shard_sum_rows(const uint16_t* rows_dev, const int32_t* pos_dev, int64_t n, int32_t num_hashes, int32_t width,
+                              uint16_t* out_dev, void* stream) {
+  if (n < 0 || num_hashes < 1 || num_hashes > PHX_MAX_HASHES || width <= 0 || width % 8 != 0 ||
+      (n > 0 && (!rows_dev || !pos_dev || !out_dev)))
+    return fail_arg("phx_shard_sum_rows: bad argument");
+  if (n == 0) return PHX_OK;
+  sx_sum_rows_kernel<<<(unsigned)((n * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const bf16*)rows_dev, pos_dev, n, num_hashes, width, (bf16*)out_dev);
+  return check_launch("phx_shard_sum_rows");
+}
+
+}  // extern "C"

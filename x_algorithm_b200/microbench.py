@@ -1,6 +1,7 @@
 """Micro-benchmarks of the stand-alone operators against their rooflines (one JSON line each).
 
     python -m x_algorithm_b200.microbench gather  [--ids 4194304] [--log2-rows 25] [--width 256] [--hashes 4]
+    torchrun --nproc-per-node N -m x_algorithm_b200.microbench gather [--exchange a2a|peer] [--check]
     python -m x_algorithm_b200.microbench topk    [--rows 12500000] [--dim 128] [--queries 256] [--k 1000]
     torchrun --nproc-per-node N -m x_algorithm_b200.microbench retrieve [--rows 100000000] [--check]
     python -m x_algorithm_b200.microbench attention [--batch 64] [--heads 16] [--dh 128] [--hist 1024] [--cands 1024]
@@ -45,28 +46,78 @@ def bench_gather(a):
     import torch
     import x_algorithm_b200 as px
     hbm, _, src = _peaks()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    dev = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", dev))
     cfg = px.PhoenixConfig(emb_size=a.width, num_layers=1, num_q_heads=a.width // 64, num_kv_heads=a.width // 64,
                            key_size=64, history_len=1, num_candidates=1, max_batch=1, num_hashes=a.hashes,
-                           table_size=1 << a.log2_rows)
-    eng = px.PhoenixEngine(cfg, 0)
+                           table_size=1 << a.log2_rows, table_world=world, table_rank=rank)
+    eng = px.PhoenixEngine(cfg, dev)
     eng.table_fill_synthetic(7, 1.0 / math.sqrt(a.width))
-    n = a.ids
-    sets = [torch.from_numpy(_zipf_ids(n, 100 + i)).cuda() for i in range(3)]
+    n = a.ids // world                      # the step's ids are split over the ranks (data parallel), the table is sharded
+    sets = [torch.from_numpy(_zipf_ids(a.ids, 100 + i)[rank * n:(rank + 1) * n].copy()).cuda() for i in range(3)]
     out = torch.empty((n, a.width), dtype=torch.int16, device="cuda")
+    op = None
+    if world > 1:
+        from x_algorithm_b200 import parallel
+        if a.exchange == "a2a":
+            op = parallel.ShardedGatherSum(eng, n)
+        else:
+            parallel.attach_table_shards(eng)
     torch.cuda.synchronize()
     times = []
     for it in range(a.warmup + a.iters):
         fam = it % 4
-        eng.gather_sum_device(fam, sets[it % 3], n, out)
-        eng.sync()
+        if world > 1:
+            dist.barrier()
+        if op is not None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            op(fam, sets[it % 3], n, out)
+            e1.record()
+            torch.cuda.synchronize()
+            ms_it = e0.elapsed_time(e1)
+        else:
+            eng.gather_sum_device(fam, sets[it % 3], n, out)
+            eng.sync()
+            ms_it = eng.last_device_ms()
+        if world > 1:
+            t = torch.tensor([ms_it], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_it = float(t[0])
         if it >= a.warmup:
-            times.append(eng.last_device_ms())
+            times.append(ms_it)
     ms = float(np.median(times))
+    ok = None
+    if a.check:   # against an unsharded table on this GPU: bit exact
+        full = px.PhoenixEngine(px.PhoenixConfig(emb_size=a.width, num_layers=1, num_q_heads=a.width // 64,
+                                                 num_kv_heads=a.width // 64, key_size=64, history_len=1, num_candidates=1,
+                                                 max_batch=1, num_hashes=a.hashes, table_size=1 << a.log2_rows), dev)
+        full.table_fill_synthetic(7, 1.0 / math.sqrt(a.width))
+        want = torch.empty_like(out)
+        fam = (a.warmup + a.iters - 1) % 4
+        full.gather_sum_device(fam, sets[(a.warmup + a.iters - 1) % 3], n, want)
+        full.sync()
+        ok = bool(torch.equal(out, want))
+        full.close()
+        if world > 1:
+            t = torch.tensor([1.0 if ok else 0.0], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            ok = bool(t[0] > 0)
     per_id = a.hashes * a.width * 2 + a.width * 2 + 8
-    gbs = per_id * n / (ms * 1e-3) / 1e9
-    print(json.dumps(dict(op="gather_sum", ids=n, hashes=a.hashes, width=a.width, table_gib=cfg.table_rows * a.width * 2 / 2**30,
-                          ms=ms, bytes_per_id=per_id, achieved_gbs=gbs, peak_gbs=hbm, frac=gbs / hbm, peak_source=src)))
+    gbs = per_id * n * world / (ms * 1e-3) / 1e9
+    if rank == 0:
+        print(json.dumps(dict(op="gather_sum", n_gpus=world, exchange=(a.exchange if world > 1 else "local"), ids=n * world,
+                              hashes=a.hashes, width=a.width, table_gib=cfg.table_rows * a.width * 2 / 2**30, ms=ms,
+                              bytes_per_id=per_id, achieved_gbs=gbs, peak_gbs=hbm * world, frac=gbs / (hbm * world),
+                              peak_source=src, matches_unsharded=ok)))
     eng.close()
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def bench_topk(a):
@@ -179,6 +230,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["gather", "topk", "attention", "retrieve"])
     ap.add_argument("--check", action="store_true")
+    ap.add_argument("--exchange", choices=["a2a", "peer"], default="a2a",
+                    help="gather on >1 GPU: NCCL all-to-all of row numbers and rows, or peer loads inside the kernel")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--ids", type=int, default=1 << 22)

@@ -6,7 +6,11 @@
   phoenix/xrex/models/recsys_two_tower_model.py:216: global row = shard * rows_local + local);
 * `attach_table_shards` wires the engines of a torch.distributed job together: every rank exports its table shard
   as a CUDA IPC handle, all-gathers the handles and maps the other ranks' shards, after which the gather kernel
-  reads remote rows over NVLink directly (no id / row exchange collectives on the data path).
+  reads remote rows over NVLink directly (no id / row exchange collectives on the data path);
+* `ShardedGatherSum` is the reference's exchange itself (phoenix/xrex/cuda/row_emb/src/row_emb_comm.cc:655-743):
+  row requests grouped by owner, NCCL all-to-all of the row numbers, owner-side gather, NCCL all-to-all of the rows,
+  fixed-order sum at the requester.  Bulk transfers reach several times the NVLink throughput of the per-row peer
+  loads, so this is the path for large id batches; both give bit-identical results.
 """
 from __future__ import annotations
 
@@ -52,3 +56,70 @@ def attach_table_shards(engine, group=None) -> None:
         if r != rank:
             engine.table_attach_peer(r, h)
     dist.barrier(group)
+
+
+class ShardedGatherSum:
+    """Multi-hash gather-sum over a table row-sharded across the ranks of a torch.distributed (NCCL) group.
+
+    `engine` holds this rank's shard (`PhoenixConfig(table_world=W, table_rank=r)`); each call takes this rank's ids
+    and returns their summed rows, like `engine.gather_sum_device` on an unsharded table, bit for bit.  All kernels
+    and collectives run on the current torch CUDA stream; the only host synchronisation is the read of the two count
+    vectors that size the variable all-to-all."""
+
+    def __init__(self, engine, max_ids: int, group=None):
+        import torch
+        import torch.distributed as dist
+        self.eng, self.group = engine, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        cfg = engine.cfg
+        assert cfg.table_world == self.world and cfg.table_rank == self.rank
+        self.H, self.width = cfg.num_hashes, cfg.emb_size
+        self.shard_rows = rows_per_shard(cfg.table_rows, self.world)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        nreq = max_ids * self.H
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.rows = torch.empty(nreq, **i32)
+        self.send_rows = torch.empty(nreq, **i32)
+        self.pos = torch.empty(nreq, **i32)
+        self.counts = torch.empty(self.world, **i32)
+        self.cursor = torch.empty(self.world, **i32)
+        self.recv_counts = torch.empty(self.world, **i32)
+        self.back = torch.empty((nreq, self.width), dtype=torch.int16, device=dev)
+        self._recv_rows = torch.empty(0, **i32)
+        self._gathered = torch.empty((0, self.width), dtype=torch.int16, device=dev)
+        self.max_ids = max_ids
+
+    def __call__(self, family: int, ids, n: int, out):
+        import torch
+        import torch.distributed as dist
+        from . import _lib
+        from .engine import _ptr
+        lib = _lib.lib
+        assert n <= self.max_ids
+        st = torch.cuda.current_stream().cuda_stream
+        nreq = n * self.H
+
+        def chk(status):
+            if status != 0:
+                raise _lib.PhoenixError(status, lib.phx_global_error().decode())
+
+        # ids -> unified-table rows (engine stream), then everything else on torch's stream
+        self.eng.hash_ids_device(family, ids, n, self.rows)
+        self.eng.sync()
+        chk(lib.phx_shard_bucket(_ptr(self.rows), nreq, self.shard_rows, self.world, _ptr(self.counts), _ptr(self.cursor),
+                                 _ptr(self.send_rows), _ptr(self.pos), st))
+        dist.all_to_all_single(self.recv_counts, self.counts, group=self.group)
+        send_splits = self.counts.tolist()            # host sync: the variable all-to-all needs its sizes
+        recv_splits = self.recv_counts.tolist()
+        m = sum(recv_splits)
+        if self._recv_rows.numel() < m:               # grows to the largest request volume seen, then stays
+            self._recv_rows = torch.empty(int(m * 1.25) + 1, dtype=torch.int32, device=self.rows.device)
+            self._gathered = torch.empty((int(m * 1.25) + 1, self.width), dtype=torch.int16, device=self.rows.device)
+        recv_rows, gathered = self._recv_rows[:m], self._gathered[:m]
+        dist.all_to_all_single(recv_rows, self.send_rows[:nreq], recv_splits, send_splits, group=self.group)
+        chk(lib.phx_shard_gather_rows(self.eng.table_local_ptr(), self.shard_rows, _ptr(recv_rows), m, self.width,
+                                      _ptr(gathered), st))
+        back = self.back[:nreq]
+        dist.all_to_all_single(back, gathered, send_splits, recv_splits, group=self.group)
+        chk(lib.phx_shard_sum_rows(_ptr(back), _ptr(self.pos), n, self.H, self.width, _ptr(out), st))
+        return out
