@@ -222,6 +222,24 @@ phx_status phx_shard_gather_rows(const uint16_t* shard_dev, int64_t shard_rows, 
 phx_status phx_shard_sum_rows(const uint16_t* rows_dev, const int32_t* pos_dev, int64_t n, int32_t num_hashes, int32_t width,
                               uint16_t* out_dev, void* stream);
 
+/* Owner-side gather with the row transfer folded in (one kernel instead of gather + all-to-all of rows): request j
+ * (of m = seg_dev[world]) belongs to requester r with seg_dev[r] <= j < seg_dev[r+1] (int64 [world+1]); its row is
+ * stored at row j - seg_dev[r] of dest_dev[r] (uint64 [world]: device addresses, local memory or a peer mapping opened
+ * with phx_ipc_open), i.e. straight into the bucket that requester reserved for this owner in its landing buffer.  The
+ * host side orders the ranks around it (a collective before the landing buffers are rewritten and after the stores).
+ * No counterpart as a single call in the reference: row_emb_comm.cc:655-743 gathers, then runs the collective. */
+phx_status phx_shard_gather_push(const uint16_t* shard_dev, int64_t shard_rows, const int32_t* local_rows_dev, int64_t m,
+                                 const int64_t* seg_dev, const uint64_t* dest_dev, int32_t world, int32_t width, void* stream);
+/* One asynchronous device-to-device copy on `stream`; dst / src may be local memory or a peer mapping (the copy engines
+ * move a requester's bucket of gathered rows in one piece). */
+phx_status phx_copy_async(void* dst, const void* src, uint64_t bytes, void* stream);
+/* Device memory that other processes of the node can map: allocate + export / map / unmap / free.  Stand in for the
+ * reference's communicator-owned exchange buffers (row_emb_comm.cc:301-336). */
+phx_status phx_ipc_alloc(int32_t device, uint64_t bytes, void** ptr_out, uint8_t handle_out[PHX_IPC_HANDLE_BYTES]);
+phx_status phx_ipc_open(int32_t device, const uint8_t handle[PHX_IPC_HANDLE_BYTES], void** ptr_out);
+phx_status phx_ipc_close(void* ptr);
+phx_status phx_ipc_free(void* ptr);
+
 /* ---- stand-alone operators (micro-benchmarks and parity tests of single kernels) ------------- */
 
 /* Multi-hash id -> unified-table rows; `family`: 0 user, 1 item, 2 author, 3 ip.

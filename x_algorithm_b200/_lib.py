@@ -76,6 +76,12 @@ SIGNATURES = {
     "phx_shard_bucket": (C.c_int32, [_P, C.c_int64, C.c_int64, C.c_int32, _P, _P, _P, _P, _P]),
     "phx_shard_gather_rows": (C.c_int32, [_P, C.c_int64, _P, C.c_int64, C.c_int32, _P, _P]),
     "phx_shard_sum_rows": (C.c_int32, [_P, _P, C.c_int64, C.c_int32, C.c_int32, _P, _P]),
+    "phx_shard_gather_push": (C.c_int32, [_P, C.c_int64, _P, C.c_int64, _P, _P, C.c_int32, C.c_int32, _P]),
+    "phx_copy_async": (C.c_int32, [_P, _P, C.c_uint64, _P]),
+    "phx_ipc_alloc": (C.c_int32, [C.c_int32, C.c_uint64, C.POINTER(_P), _P]),
+    "phx_ipc_open": (C.c_int32, [C.c_int32, _P, C.POINTER(_P)]),
+    "phx_ipc_close": (C.c_int32, [_P]),
+    "phx_ipc_free": (C.c_int32, [_P]),
     "phx_gather_sum_device": (C.c_int32, [_P, C.c_int32, _P, C.c_int64, _P]),
     "phx_ranker_attention_device": (C.c_int32, [C.c_int32, _P, _P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32,
                                                 C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_float, C.c_int32,

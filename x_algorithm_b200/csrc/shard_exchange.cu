@@ -13,6 +13,8 @@
 // The sum order is by hash slot and does not depend on how requests were grouped or on the number of ranks, so the
 // result is bit-identical to the single-table gather-sum kernel.  Every function launches on the stream it is
 // given (the host side passes the stream its collectives run on) and allocates nothing.
+#include <string.h>
+
 #include <string>
 
 #include "common.cuh"
@@ -123,6 +125,30 @@ __global__ void __launch_bounds__(256) sx_sum_rows_kernel(const bf16* __restrict
   }
 }
 
+// Owner side with the row transfer folded in: request j belongs to the requester r with seg[r] <= j < seg[r+1]; its row
+// goes straight into that requester's landing buffer (a peer mapping, or local memory for r = this rank) at row
+// j - seg[r] of the bucket the requester reserved for this owner.  One warp per row: a 512-byte row is one coalesced
+// store of 32 x 16 bytes, which is what NVLink moves best; stores are posted, so the kernel does not wait on the link.
+__global__ void __launch_bounds__(256) sx_gather_push_kernel(const bf16* __restrict__ shard, long long shard_rows,
+                                                             const int* __restrict__ idx, const long long* __restrict__ seg,
+                                                             const unsigned long long* __restrict__ dest, int world, int width) {
+  __shared__ long long s_seg[SX_MAX_WORLD + 1];
+  __shared__ unsigned long long s_dest[SX_MAX_WORLD];
+  if (threadIdx.x <= world) s_seg[threadIdx.x] = seg[threadIdx.x];
+  if (threadIdx.x < world) s_dest[threadIdx.x] = dest[threadIdx.x];
+  __syncthreads();
+  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= s_seg[world]) return;
+  int r = 0;
+  while (r + 1 < world && w >= s_seg[r + 1]) ++r;
+  long long row = idx[w];
+  if (row < 0 || row >= shard_rows) row = 0;
+  const uint4* src = reinterpret_cast<const uint4*>(shard + row * width);
+  uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(s_dest[r]) + (w - s_seg[r]) * width);
+  for (int c = lane; c < width / 8; c += 32) dst[c] = __ldg(src + c);
+}
+
 phx_status fail_arg(const char* msg) { set_global_error(msg); return PHX_E_ARG; }
 phx_status check_launch(const char* what) {
   cudaError_t ce = cudaGetLastError();
@@ -172,6 +198,66 @@ phx_status phx_shard_sum_rows(const uint16_t* rows_dev, const int32_t* pos_dev, 
   sx_sum_rows_kernel<<<(unsigned)((n * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
       (const bf16*)rows_dev, pos_dev, n, num_hashes, width, (bf16*)out_dev);
   return check_launch("phx_shard_sum_rows");
+}
+
+phx_status phx_shard_gather_push(const uint16_t* shard_dev, int64_t shard_rows, const int32_t* local_rows_dev, int64_t m,
+                                 const int64_t* seg_dev, const uint64_t* dest_dev, int32_t world, int32_t width, void* stream) {
+  if (!shard_dev || shard_rows <= 0 || m < 0 || !seg_dev || !dest_dev || world < 1 || world > SX_MAX_WORLD || width <= 0 ||
+      width % 8 != 0 || (m > 0 && !local_rows_dev))
+    return fail_arg("phx_shard_gather_push: bad argument (world must be 1..64, width a multiple of 8)");
+  if (m == 0) return PHX_OK;
+  sx_gather_push_kernel<<<(unsigned)((m * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const bf16*)shard_dev, shard_rows, local_rows_dev, (const long long*)seg_dev, (const unsigned long long*)dest_dev, world, width);
+  return check_launch("phx_shard_gather_push");
+}
+
+phx_status phx_copy_async(void* dst, const void* src, uint64_t bytes, void* stream) {
+  if (bytes == 0) return PHX_OK;
+  if (!dst || !src) return fail_arg("phx_copy_async: null pointer");
+  cudaError_t ce = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, (cudaStream_t)stream);   // unified addressing: local or peer
+  if (ce != cudaSuccess) { set_global_error(std::string("phx_copy_async: ") + cudaGetErrorString(ce)); return PHX_E_CUDA; }
+  return PHX_OK;
+}
+
+phx_status phx_ipc_alloc(int32_t device, uint64_t bytes, void** ptr_out, uint8_t handle_out[PHX_IPC_HANDLE_BYTES]) {
+  if (!ptr_out || !handle_out || bytes == 0) return fail_arg("phx_ipc_alloc: bad argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == PHX_IPC_HANDLE_BYTES, "IPC handle size");
+  if (cudaSetDevice(device) != cudaSuccess) return check_launch("phx_ipc_alloc");
+  void* p = nullptr;
+  cudaError_t ce = cudaMalloc(&p, bytes);
+  if (ce != cudaSuccess) { set_global_error(std::string("phx_ipc_alloc: ") + cudaGetErrorString(ce)); return PHX_E_CUDA; }
+  cudaIpcMemHandle_t h;
+  ce = cudaIpcGetMemHandle(&h, p);
+  if (ce != cudaSuccess) { cudaFree(p); set_global_error(std::string("phx_ipc_alloc: ") + cudaGetErrorString(ce)); return PHX_E_CUDA; }
+  memcpy(handle_out, &h, sizeof(h));
+  *ptr_out = p;
+  return PHX_OK;
+}
+
+phx_status phx_ipc_open(int32_t device, const uint8_t handle[PHX_IPC_HANDLE_BYTES], void** ptr_out) {
+  if (!handle || !ptr_out) return fail_arg("phx_ipc_open: bad argument");
+  if (cudaSetDevice(device) != cudaSuccess) return check_launch("phx_ipc_open");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  cudaError_t ce = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (ce != cudaSuccess) { set_global_error(std::string("phx_ipc_open: ") + cudaGetErrorString(ce)); return PHX_E_CUDA; }
+  *ptr_out = p;
+  return PHX_OK;
+}
+
+phx_status phx_ipc_close(void* ptr) {
+  if (!ptr) return PHX_OK;
+  cudaError_t ce = cudaIpcCloseMemHandle(ptr);
+  if (ce != cudaSuccess) { set_global_error(std::string("phx_ipc_close: ") + cudaGetErrorString(ce)); return PHX_E_CUDA; }
+  return PHX_OK;
+}
+
+phx_status phx_ipc_free(void* ptr) {
+  if (!ptr) return PHX_OK;
+  cudaError_t ce = cudaFree(ptr);
+  if (ce != cudaSuccess) { set_global_error(std::string("phx_ipc_free: ") + cudaGetErrorString(ce)); return PHX_E_CUDA; }
+  return PHX_OK;
 }
 
 }  // extern "C"

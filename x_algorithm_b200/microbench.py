@@ -1,7 +1,7 @@
 """Micro-benchmarks of the stand-alone operators against their rooflines (one JSON line each).
 
     python -m x_algorithm_b200.microbench gather  [--ids 4194304] [--log2-rows 25] [--width 256] [--hashes 4]
-    torchrun --nproc-per-node N -m x_algorithm_b200.microbench gather [--exchange a2a|peer] [--check]
+    torchrun --nproc-per-node N -m x_algorithm_b200.microbench gather [--exchange copy|push|a2a|peer] [--check]
     python -m x_algorithm_b200.microbench topk    [--rows 12500000] [--dim 128] [--queries 256] [--k 1000]
     torchrun --nproc-per-node N -m x_algorithm_b200.microbench retrieve [--rows 100000000] [--check]
     python -m x_algorithm_b200.microbench attention [--batch 64] [--heads 16] [--dh 128] [--hist 1024] [--cands 1024]
@@ -64,8 +64,8 @@ def bench_gather(a):
     op = None
     if world > 1:
         from x_algorithm_b200 import parallel
-        if a.exchange == "a2a":
-            op = parallel.ShardedGatherSum(eng, n)
+        if a.exchange in ("a2a", "push", "copy"):
+            op = parallel.ShardedGatherSum(eng, n, exchange=a.exchange)
         else:
             parallel.attach_table_shards(eng)
     torch.cuda.synchronize()
@@ -92,6 +92,12 @@ def bench_gather(a):
         if it >= a.warmup:
             times.append(ms_it)
     ms = float(np.median(times))
+    phases = None
+    if op is not None:   # one more call with per-phase device times
+        op.phase_ms = {}
+        op(0, sets[0], n, out)
+        phases = {k: round(v, 3) for k, v in op.phase_ms.items()}
+        op.phase_ms = None
     ok = None
     if a.check:   # against an unsharded table on this GPU: bit exact
         full = px.PhoenixEngine(px.PhoenixConfig(emb_size=a.width, num_layers=1, num_q_heads=a.width // 64,
@@ -114,7 +120,9 @@ def bench_gather(a):
         print(json.dumps(dict(op="gather_sum", n_gpus=world, exchange=(a.exchange if world > 1 else "local"), ids=n * world,
                               hashes=a.hashes, width=a.width, table_gib=cfg.table_rows * a.width * 2 / 2**30, ms=ms,
                               bytes_per_id=per_id, achieved_gbs=gbs, peak_gbs=hbm * world, frac=gbs / (hbm * world),
-                              peak_source=src, matches_unsharded=ok)))
+                              peak_source=src, matches_unsharded=ok, phase_ms_rank0=phases)))
+    if op is not None:
+        op.close()
     eng.close()
     if world > 1:
         dist.destroy_process_group()
@@ -230,8 +238,10 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["gather", "topk", "attention", "retrieve"])
     ap.add_argument("--check", action="store_true")
-    ap.add_argument("--exchange", choices=["a2a", "peer"], default="a2a",
-                    help="gather on >1 GPU: NCCL all-to-all of row numbers and rows, or peer loads inside the kernel")
+    ap.add_argument("--exchange", choices=["copy", "push", "a2a", "peer"], default="copy",
+                    help="gather on >1 GPU: owner-side gather + copy-engine transfer into the requester's buffer (copy), "
+                         "gather kernel storing into the requester's buffer (push), NCCL all-to-all of the rows (a2a), "
+                         "or peer loads inside the requester's kernel (peer)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--ids", type=int, default=1 << 22)

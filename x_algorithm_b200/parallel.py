@@ -63,31 +63,85 @@ class ShardedGatherSum:
 
     `engine` holds this rank's shard (`PhoenixConfig(table_world=W, table_rank=r)`); each call takes this rank's ids
     and returns their summed rows, like `engine.gather_sum_device` on an unsharded table, bit for bit.  All kernels
-    and collectives run on the current torch CUDA stream; the only host synchronisation is the read of the two count
-    vectors that size the variable all-to-all."""
+    and collectives run on the current torch CUDA stream; the only host synchronisation is the read of the count
+    vectors that size the exchange.
 
-    def __init__(self, engine, max_ids: int, group=None):
+    exchange="copy" (default): the owner gathers each requester's bucket into a send block in chunks and the copy
+    engines move every finished chunk into that requester's landing buffer (peer memory mapped over CUDA IPC) while
+    the next chunk is being gathered; the owner's own bucket is gathered in place.  exchange="push": the gather kernel
+    stores every row straight into the requester's landing buffer (one kernel, but SM-issued stores reach about a
+    third of the copy engines' NVLink rate).  exchange="a2a": gather into a send block, then an NCCL all-to-all of
+    the rows.  In every mode a small collective on either side orders the ranks."""
+
+    COPY_CHUNKS = 4
+
+    def __init__(self, engine, max_ids: int, group=None, exchange: str = "copy"):
+        import ctypes as C
         import torch
         import torch.distributed as dist
-        self.eng, self.group = engine, group
+        from . import _lib
+        assert exchange in ("copy", "push", "a2a")
+        self.eng, self.group, self.exchange = engine, group, exchange
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         cfg = engine.cfg
         assert cfg.table_world == self.world and cfg.table_rank == self.rank
         self.H, self.width = cfg.num_hashes, cfg.emb_size
         self.shard_rows = rows_per_shard(cfg.table_rows, self.world)
-        dev = torch.device("cuda", torch.cuda.current_device())
+        self.device = torch.cuda.current_device()
+        dev = torch.device("cuda", self.device)
         nreq = max_ids * self.H
         i32 = dict(dtype=torch.int32, device=dev)
         self.rows = torch.empty(nreq, **i32)
         self.send_rows = torch.empty(nreq, **i32)
         self.pos = torch.empty(nreq, **i32)
-        self.counts = torch.empty(self.world, **i32)
+        self.meta = torch.empty((self.world, 2), **i32)        # per owner: request count, first slot of its bucket
+        self.recv_meta = torch.empty((self.world, 2), **i32)
         self.cursor = torch.empty(self.world, **i32)
-        self.recv_counts = torch.empty(self.world, **i32)
-        self.back = torch.empty((nreq, self.width), dtype=torch.int16, device=dev)
+        self.flag = torch.zeros(1, **i32)
         self._recv_rows = torch.empty(0, **i32)
-        self._gathered = torch.empty((0, self.width), dtype=torch.int16, device=dev)
         self.max_ids = max_ids
+        self.phase_ms = None        # set to {} to collect per-phase device times of the next call (diagnostics)
+        self._peer_ptrs, self._back_ptr = None, None
+        self._gathered = torch.empty((0, self.width), dtype=torch.bfloat16, device=dev)
+        if exchange == "copy":
+            self._side = torch.cuda.Stream(device=dev)
+        if exchange in ("push", "copy"):
+            lib = _lib.lib
+            ptr, handle = C.c_void_p(), (C.c_uint8 * 64)()
+            st = lib.phx_ipc_alloc(self.device, nreq * self.width * 2, C.byref(ptr), handle)
+            if st != 0:
+                raise _lib.PhoenixError(st, lib.phx_global_error().decode())
+            self._back_ptr = int(ptr.value)
+            handles = [b""] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            self._peer_ptrs = [0] * self.world
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    self._peer_ptrs[r] = self._back_ptr
+                else:
+                    p = C.c_void_p()
+                    st = lib.phx_ipc_open(self.device, (C.c_uint8 * 64).from_buffer_copy(h), C.byref(p))
+                    if st != 0:
+                        raise _lib.PhoenixError(st, lib.phx_global_error().decode())
+                    self._peer_ptrs[r] = int(p.value)
+            dist.barrier(group)
+        else:
+            self.back = torch.empty((nreq, self.width), dtype=torch.bfloat16, device=dev)   # (NCCL has no int16)
+
+    def close(self):
+        """Unmap the peers' landing buffers and free this rank's (collective: every rank calls it)."""
+        if self._peer_ptrs is not None:
+            import torch
+            import torch.distributed as dist
+            from . import _lib
+            torch.cuda.synchronize()
+            dist.barrier(self.group)
+            for r, p in enumerate(self._peer_ptrs):
+                if r != self.rank and p:
+                    _lib.lib.phx_ipc_close(p)
+            dist.barrier(self.group)
+            _lib.lib.phx_ipc_free(self._back_ptr)
+            self._peer_ptrs, self._back_ptr = None, None
 
     def __call__(self, family: int, ids, n: int, out):
         import torch
@@ -98,28 +152,102 @@ class ShardedGatherSum:
         assert n <= self.max_ids
         st = torch.cuda.current_stream().cuda_stream
         nreq = n * self.H
+        W = self.world
 
         def chk(status):
             if status != 0:
                 raise _lib.PhoenixError(status, lib.phx_global_error().decode())
 
+        marks = []
+
+        def mark(name):
+            if self.phase_ms is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
         # ids -> unified-table rows (engine stream), then everything else on torch's stream
         self.eng.hash_ids_device(family, ids, n, self.rows)
         self.eng.sync()
-        chk(lib.phx_shard_bucket(_ptr(self.rows), nreq, self.shard_rows, self.world, _ptr(self.counts), _ptr(self.cursor),
+        mark("hash")
+        counts = self.meta[:, 0].contiguous()
+        chk(lib.phx_shard_bucket(_ptr(self.rows), nreq, self.shard_rows, W, _ptr(counts), _ptr(self.cursor),
                                  _ptr(self.send_rows), _ptr(self.pos), st))
-        dist.all_to_all_single(self.recv_counts, self.counts, group=self.group)
-        send_splits = self.counts.tolist()            # host sync: the variable all-to-all needs its sizes
-        recv_splits = self.recv_counts.tolist()
+        self.meta[:, 0] = counts
+        self.meta[:, 1] = torch.cumsum(counts, 0, dtype=torch.int32) - counts          # first slot of each bucket
+        mark("bucket")
+        dist.all_to_all_single(self.recv_meta, self.meta, group=self.group)
+        send_meta, recv_meta = self.meta.tolist(), self.recv_meta.tolist()   # host sync: the exchange needs its sizes
+        send_splits = [c for c, _ in send_meta]
+        recv_splits = [c for c, _ in recv_meta]
         m = sum(recv_splits)
         if self._recv_rows.numel() < m:               # grows to the largest request volume seen, then stays
             self._recv_rows = torch.empty(int(m * 1.25) + 1, dtype=torch.int32, device=self.rows.device)
-            self._gathered = torch.empty((int(m * 1.25) + 1, self.width), dtype=torch.int16, device=self.rows.device)
-        recv_rows, gathered = self._recv_rows[:m], self._gathered[:m]
+            if self.exchange in ("a2a", "copy"):
+                self._gathered = torch.empty((int(m * 1.25) + 1, self.width), dtype=torch.bfloat16, device=self.rows.device)
+        recv_rows = self._recv_rows[:m]
+        mark("counts")
         dist.all_to_all_single(recv_rows, self.send_rows[:nreq], recv_splits, send_splits, group=self.group)
-        chk(lib.phx_shard_gather_rows(self.eng.table_local_ptr(), self.shard_rows, _ptr(recv_rows), m, self.width,
-                                      _ptr(gathered), st))
-        back = self.back[:nreq]
-        dist.all_to_all_single(back, gathered, send_splits, recv_splits, group=self.group)
-        chk(lib.phx_shard_sum_rows(_ptr(back), _ptr(self.pos), n, self.H, self.width, _ptr(out), st))
+        mark("a2a_row_numbers")
+        if self.exchange == "copy":
+            row_bytes = self.width * 2
+            shard, gathered = self.eng.table_local_ptr(), self._gathered
+            seg = [0]
+            for c in recv_splits:
+                seg.append(seg[-1] + c)
+            cur = torch.cuda.current_stream()
+            # remote buckets first, in chunks: gather a chunk, hand it to the copy engines, gather the next
+            for r in [x for x in range(W) if x != self.rank]:
+                cnt = recv_splits[r]
+                step = max((cnt + self.COPY_CHUNKS - 1) // self.COPY_CHUNKS, 1)
+                for c0 in range(0, cnt, step):
+                    c1 = min(c0 + step, cnt)
+                    src = gathered[seg[r] + c0: seg[r] + c1]
+                    chk(lib.phx_shard_gather_rows(shard, self.shard_rows, _ptr(recv_rows) + (seg[r] + c0) * 4, c1 - c0,
+                                                  self.width, _ptr(src), st))
+                    ev = torch.cuda.Event()
+                    ev.record(cur)
+                    self._side.wait_event(ev)
+                    chk(lib.phx_copy_async(self._peer_ptrs[r] + (recv_meta[r][1] + c0) * row_bytes, _ptr(src),
+                                           (c1 - c0) * row_bytes, self._side.cuda_stream))
+            # this rank's own bucket: straight into its landing buffer
+            r = self.rank
+            chk(lib.phx_shard_gather_rows(shard, self.shard_rows, _ptr(recv_rows) + seg[r] * 4, recv_splits[r], self.width,
+                                          self._back_ptr + recv_meta[r][1] * row_bytes, st))
+            cur.wait_stream(self._side)
+            mark("owner_gather_copy")
+            dist.all_reduce(self.flag, group=self.group)      # every rank's copies are complete before any rank sums
+            mark("fence")
+            back_ptr = self._back_ptr
+        elif self.exchange == "push":
+            seg = [0]
+            for c in recv_splits:
+                seg.append(seg[-1] + c)
+            row_bytes = self.width * 2
+            dest = [self._peer_ptrs[r] + recv_meta[r][1] * row_bytes for r in range(W)]
+            seg_t = torch.tensor(seg, dtype=torch.int64, device=self.rows.device)
+            dest_t = torch.tensor(dest, dtype=torch.int64, device=self.rows.device)     # addresses < 2^63
+            # the row-number all-to-all above already ordered this rank behind every peer's previous sum
+            chk(lib.phx_shard_gather_push(self.eng.table_local_ptr(), self.shard_rows, _ptr(recv_rows), m, _ptr(seg_t),
+                                          _ptr(dest_t), W, self.width, st))
+            mark("owner_gather_push")
+            dist.all_reduce(self.flag, group=self.group)      # every rank's stores are complete before any rank sums
+            mark("fence")
+            back_ptr = self._back_ptr
+        else:
+            gathered = self._gathered[:m]
+            chk(lib.phx_shard_gather_rows(self.eng.table_local_ptr(), self.shard_rows, _ptr(recv_rows), m, self.width,
+                                          _ptr(gathered), st))
+            mark("owner_gather")
+            back = self.back[:nreq]
+            dist.all_to_all_single(back, gathered, send_splits, recv_splits, group=self.group)
+            mark("a2a_rows")
+            back_ptr = _ptr(back)
+        chk(lib.phx_shard_sum_rows(back_ptr, _ptr(self.pos), n, self.H, self.width, _ptr(out), st))
+        mark("sum")
+        if self.phase_ms is not None:
+            torch.cuda.synchronize()
+            for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
+                self.phase_ms[name] = self.phase_ms.get(name, 0.0) + a.elapsed_time(b)
         return out
