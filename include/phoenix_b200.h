@@ -214,6 +214,15 @@ phx_status phx_debug_read(phx_engine* e, const char* what, void* host, size_t nb
  * scratch (on return: the end of each bucket). */
 phx_status phx_shard_bucket(const int32_t* rows_dev, int64_t n_req, int64_t rows_per_shard, int32_t world, int32_t* counts_dev,
                             int32_t* cursor_dev, int32_t* send_rows_dev, int32_t* pos_dev, void* stream);
+/* Distinct rows of a request list (ids repeat under a skewed distribution; only distinct rows need to cross the link):
+ * table_dev uint64 [table_slots] is scratch (a power of two >= 2 * n_req), slot_dev int32 [n_req] and urows_dev int32
+ * [up to n_req] outputs, *nu_dev the number of distinct rows.  urows_dev then goes through phx_shard_bucket (giving
+ * upos), and phx_shard_dedup_expand turns that into pos_dev int32 [n_req] for phx_shard_sum_rows.  The reference
+ * deduplicates before its exchange as well (the slot_unique / owner_unique workspaces, row_emb_comm.cc:122-136). */
+phx_status phx_shard_dedup(const int32_t* rows_dev, int64_t n_req, uint64_t* table_dev, int64_t table_slots, int32_t* slot_dev,
+                           int32_t* urows_dev, int32_t* nu_dev, void* stream);
+phx_status phx_shard_dedup_expand(const int32_t* slot_dev, const uint64_t* table_dev, const int32_t* upos_dev, int64_t n_req,
+                                  int32_t* pos_dev, void* stream);
 /* Owner side: out_dev bf16 [m, width] = shard rows local_rows_dev[0..m) (out of range -> row 0, emb_table.rs:124-140). */
 phx_status phx_shard_gather_rows(const uint16_t* shard_dev, int64_t shard_rows, const int32_t* local_rows_dev, int64_t m,
                                  int32_t width, uint16_t* out_dev, void* stream);

@@ -403,6 +403,36 @@ def test_sharded_gather_exchange_kernels_bit_identical(torch):
         full.gather_sum_device(1, ids[r], n, want); full.sync()
         torch.cuda.synchronize()
         assert torch.equal(out, want)
+    # duplicate requests folded first: distinct rows -> bucket -> positions expanded back to every request
+    r = 0
+    dup_ids = ids[r].clone(); dup_ids[n // 2:] = dup_ids[:n - n // 2]          # every id (at least) twice
+    rw = torch.empty(n * H, **i32)
+    shards[r].hash_ids_device(1, dup_ids, n, rw); shards[r].sync()
+    slots = 1 << 16
+    table = torch.empty(slots, dtype=torch.int64, device="cuda")
+    slot, urows, upos, ps2 = (torch.empty(n * H, **i32) for _ in range(4))
+    nu = torch.empty(1, **i32)
+    assert lib.phx_shard_dedup(_ptr(rw), n * H, _ptr(table), slots, _ptr(slot), _ptr(urows), _ptr(nu), st) == 0
+    nuq = int(nu.item())
+    assert nuq == len(np.unique(rw.cpu().numpy())) and nuq <= n * H // 2 + H * 3
+    np.testing.assert_array_equal(np.sort(urows[:nuq].cpu().numpy()), np.unique(rw.cpu().numpy()))
+    sr, ct, cur = torch.empty(n * H, **i32), torch.empty(W, **i32), torch.empty(W, **i32)
+    assert lib.phx_shard_bucket(_ptr(urows), nuq, rps, W, _ptr(ct), _ptr(cur), _ptr(sr), _ptr(upos), st) == 0
+    assert lib.phx_shard_dedup_expand(_ptr(slot), _ptr(table), _ptr(upos), n * H, _ptr(ps2), st) == 0
+    torch.cuda.synchronize()
+    cts = ct.tolist()
+    landing = torch.empty((nuq, width), dtype=torch.int16, device="cuda")
+    for o in range(W):
+        b0 = sum(cts[:o])
+        assert lib.phx_shard_gather_rows(shards[o].table_local_ptr(), rps, _ptr(sr) + 4 * b0, cts[o], width,
+                                         _ptr(landing) + 2 * width * b0, st) == 0
+    out = torch.empty((n, width), dtype=torch.int16, device="cuda")
+    assert lib.phx_shard_sum_rows(_ptr(landing), _ptr(ps2), n, H, width, _ptr(out), st) == 0
+    want = torch.empty_like(out)
+    full.gather_sum_device(1, dup_ids, n, want); full.sync()
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)
+    assert lib.phx_shard_dedup(_ptr(rw), n * H, _ptr(table), 1000, _ptr(slot), _ptr(urows), _ptr(nu), st) == 1   # not a power of two
     assert lib.phx_shard_bucket(0, 1, rps, W, 0, 0, 0, 0, st) == 1        # PHX_E_ARG on null pointers
     for e in shards + [full]:
         e.close()

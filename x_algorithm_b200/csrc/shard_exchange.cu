@@ -149,6 +149,57 @@ __global__ void __launch_bounds__(256) sx_gather_push_kernel(const bf16* __restr
   for (int c = lane; c < width / 8; c += 32) dst[c] = __ldg(src + c);
 }
 
+// ---- duplicate requests ------------------------------------------------------------------------------------------------
+// Zipf-distributed ids ask for the same rows again and again (three of four row reads of the single-GPU gather hit
+// L2); only distinct rows need to cross NVLink.  An open-addressing table (64-bit entries: row + 1 in the low word, the
+// row's index in the list of distinct rows in the high word; 0 = empty) finds them without sorting.
+__device__ __forceinline__ uint32_t sx_mix(uint32_t x) {
+  x ^= x >> 16; x *= 0x7FEB352Du; x ^= x >> 15; x *= 0x846CA68Bu; x ^= x >> 16;
+  return x;
+}
+
+__global__ void __launch_bounds__(256) sx_dedup_insert_kernel(const int* __restrict__ rows, long long n, unsigned long long* table,
+                                                              unsigned int mask, int* __restrict__ slot_of) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const unsigned long long key = (unsigned long long)((unsigned int)rows[i]) + 1ull;
+  unsigned int s = sx_mix((unsigned int)key) & mask;
+  for (;;) {
+    const unsigned long long old = atomicCAS(&table[s], 0ull, key);
+    if (old == 0ull || (old & 0xFFFFFFFFull) == key) break;   // claimed the slot, or the row is already there
+    s = (s + 1) & mask;                                       // the table is at most half full: the probe ends
+  }
+  slot_of[i] = (int)s;
+}
+
+// every occupied slot gets the next index in the list of distinct rows (one global atomic per block)
+__global__ void __launch_bounds__(256) sx_dedup_compact_kernel(unsigned long long* table, long long cap, int* __restrict__ urows,
+                                                               int* __restrict__ nu) {
+  __shared__ int s_cnt, s_base;
+  if (threadIdx.x == 0) s_cnt = 0;
+  __syncthreads();
+  const long long s = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  unsigned long long e = (s < cap) ? table[s] : 0ull;
+  int my = -1;
+  if (e != 0ull) my = atomicAdd(&s_cnt, 1);
+  __syncthreads();
+  if (threadIdx.x == 0) s_base = s_cnt ? atomicAdd(nu, s_cnt) : 0;
+  __syncthreads();
+  if (my >= 0) {
+    const int u = s_base + my;
+    urows[u] = (int)((e & 0xFFFFFFFFull) - 1ull);
+    table[s] = (e & 0xFFFFFFFFull) | ((unsigned long long)(unsigned int)u << 32);
+  }
+}
+
+// request i -> slot of its distinct row in the grouped order
+__global__ void __launch_bounds__(256) sx_dedup_expand_kernel(const int* __restrict__ slot_of, const unsigned long long* __restrict__ table,
+                                                              const int* __restrict__ upos, long long n, int* __restrict__ pos) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  pos[i] = upos[(int)(table[slot_of[i]] >> 32)];
+}
+
 phx_status fail_arg(const char* msg) { set_global_error(msg); return PHX_E_ARG; }
 phx_status check_launch(const char* what) {
   cudaError_t ce = cudaGetLastError();
@@ -209,6 +260,32 @@ phx_status phx_shard_gather_push(const uint16_t* shard_dev, int64_t shard_rows, 
   sx_gather_push_kernel<<<(unsigned)((m * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
       (const bf16*)shard_dev, shard_rows, local_rows_dev, (const long long*)seg_dev, (const unsigned long long*)dest_dev, world, width);
   return check_launch("phx_shard_gather_push");
+}
+
+phx_status phx_shard_dedup(const int32_t* rows_dev, int64_t n_req, uint64_t* table_dev, int64_t table_slots, int32_t* slot_dev,
+                           int32_t* urows_dev, int32_t* nu_dev, void* stream) {
+  if (n_req < 0 || !table_dev || !nu_dev || table_slots < 2 || (table_slots & (table_slots - 1)) != 0 || table_slots < 2 * n_req ||
+      table_slots > (1ll << 31) || (n_req > 0 && (!rows_dev || !slot_dev || !urows_dev)))
+    return fail_arg("phx_shard_dedup: bad argument (table_slots must be a power of two >= 2 * n_req)");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cudaMemsetAsync(table_dev, 0, sizeof(uint64_t) * (size_t)table_slots, st) != cudaSuccess) return check_launch("phx_shard_dedup");
+  if (cudaMemsetAsync(nu_dev, 0, sizeof(int32_t), st) != cudaSuccess) return check_launch("phx_shard_dedup");
+  if (n_req > 0) {
+    sx_dedup_insert_kernel<<<(unsigned)((n_req + 255) / 256), 256, 0, st>>>(rows_dev, n_req, (unsigned long long*)table_dev,
+                                                                          (unsigned int)(table_slots - 1), slot_dev);
+    sx_dedup_compact_kernel<<<(unsigned)((table_slots + 255) / 256), 256, 0, st>>>((unsigned long long*)table_dev, table_slots,
+                                                                                  urows_dev, nu_dev);
+  }
+  return check_launch("phx_shard_dedup");
+}
+
+phx_status phx_shard_dedup_expand(const int32_t* slot_dev, const uint64_t* table_dev, const int32_t* upos_dev, int64_t n_req,
+                                  int32_t* pos_dev, void* stream) {
+  if (n_req < 0 || (n_req > 0 && (!slot_dev || !table_dev || !upos_dev || !pos_dev))) return fail_arg("phx_shard_dedup_expand: bad argument");
+  if (n_req == 0) return PHX_OK;
+  sx_dedup_expand_kernel<<<(unsigned)((n_req + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      slot_dev, (const unsigned long long*)table_dev, upos_dev, n_req, pos_dev);
+  return check_launch("phx_shard_dedup_expand");
 }
 
 phx_status phx_copy_async(void* dst, const void* src, uint64_t bytes, void* stream) {

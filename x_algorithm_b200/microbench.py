@@ -65,7 +65,7 @@ def bench_gather(a):
     if world > 1:
         from x_algorithm_b200 import parallel
         if a.exchange in ("a2a", "push", "copy"):
-            op = parallel.ShardedGatherSum(eng, n, exchange=a.exchange)
+            op = parallel.ShardedGatherSum(eng, n, exchange=a.exchange, dedup=not a.no_dedup)
         else:
             parallel.attach_table_shards(eng)
     torch.cuda.synchronize()
@@ -238,6 +238,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["gather", "topk", "attention", "retrieve"])
     ap.add_argument("--check", action="store_true")
+    ap.add_argument("--no-dedup", action="store_true", help="sharded gather: send every request, not only distinct rows")
     ap.add_argument("--exchange", choices=["copy", "push", "a2a", "peer"], default="copy",
                     help="gather on >1 GPU: owner-side gather + copy-engine transfer into the requester's buffer (copy), "
                          "gather kernel storing into the requester's buffer (push), NCCL all-to-all of the rows (a2a), "

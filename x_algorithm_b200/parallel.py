@@ -75,7 +75,7 @@ class ShardedGatherSum:
 
     COPY_CHUNKS = 4
 
-    def __init__(self, engine, max_ids: int, group=None, exchange: str = "copy"):
+    def __init__(self, engine, max_ids: int, group=None, exchange: str = "copy", dedup: bool = True):
         import ctypes as C
         import torch
         import torch.distributed as dist
@@ -98,6 +98,17 @@ class ShardedGatherSum:
         self.recv_meta = torch.empty((self.world, 2), **i32)
         self.cursor = torch.empty(self.world, **i32)
         self.flag = torch.zeros(1, **i32)
+        # duplicate requests are folded before the exchange (skewed ids ask for the same rows over and over)
+        self.dedup = dedup
+        if dedup:
+            slots = 2
+            while slots < 2 * nreq:
+                slots *= 2
+            self.table = torch.empty(slots, dtype=torch.int64, device=dev)
+            self.slot = torch.empty(nreq, **i32)
+            self.urows = torch.empty(nreq, **i32)
+            self.upos = torch.empty(nreq, **i32)
+            self.nu = torch.empty(1, **i32)
         self._recv_rows = torch.empty(0, **i32)
         self.max_ids = max_ids
         self.phase_ms = None        # set to {} to collect per-phase device times of the next call (diagnostics)
@@ -172,8 +183,17 @@ class ShardedGatherSum:
         self.eng.sync()
         mark("hash")
         counts = self.meta[:, 0].contiguous()
-        chk(lib.phx_shard_bucket(_ptr(self.rows), nreq, self.shard_rows, W, _ptr(counts), _ptr(self.cursor),
-                                 _ptr(self.send_rows), _ptr(self.pos), st))
+        if self.dedup:
+            chk(lib.phx_shard_dedup(_ptr(self.rows), nreq, _ptr(self.table), self.table.numel(), _ptr(self.slot),
+                                    _ptr(self.urows), _ptr(self.nu), st))
+            nsend = int(self.nu.item())                # host sync: the number of distinct rows sizes what follows
+            chk(lib.phx_shard_bucket(_ptr(self.urows), nsend, self.shard_rows, W, _ptr(counts), _ptr(self.cursor),
+                                     _ptr(self.send_rows), _ptr(self.upos), st))
+            chk(lib.phx_shard_dedup_expand(_ptr(self.slot), _ptr(self.table), _ptr(self.upos), nreq, _ptr(self.pos), st))
+        else:
+            nsend = nreq
+            chk(lib.phx_shard_bucket(_ptr(self.rows), nreq, self.shard_rows, W, _ptr(counts), _ptr(self.cursor),
+                                     _ptr(self.send_rows), _ptr(self.pos), st))
         self.meta[:, 0] = counts
         self.meta[:, 1] = torch.cumsum(counts, 0, dtype=torch.int32) - counts          # first slot of each bucket
         mark("bucket")
@@ -188,7 +208,7 @@ class ShardedGatherSum:
                 self._gathered = torch.empty((int(m * 1.25) + 1, self.width), dtype=torch.bfloat16, device=self.rows.device)
         recv_rows = self._recv_rows[:m]
         mark("counts")
-        dist.all_to_all_single(recv_rows, self.send_rows[:nreq], recv_splits, send_splits, group=self.group)
+        dist.all_to_all_single(recv_rows, self.send_rows[:nsend], recv_splits, send_splits, group=self.group)
         mark("a2a_row_numbers")
         if self.exchange == "copy":
             row_bytes = self.width * 2
@@ -240,7 +260,7 @@ class ShardedGatherSum:
             chk(lib.phx_shard_gather_rows(self.eng.table_local_ptr(), self.shard_rows, _ptr(recv_rows), m, self.width,
                                           _ptr(gathered), st))
             mark("owner_gather")
-            back = self.back[:nreq]
+            back = self.back[:nsend]
             dist.all_to_all_single(back, gathered, send_splits, recv_splits, group=self.group)
             mark("a2a_rows")
             back_ptr = _ptr(back)
