@@ -436,3 +436,26 @@ def test_sharded_gather_exchange_kernels_bit_identical(torch):
     assert lib.phx_shard_bucket(0, 1, rps, W, 0, 0, 0, 0, st) == 1        # PHX_E_ARG on null pointers
     for e in shards + [full]:
         e.close()
+
+
+def test_graph_replay_matches_eager(torch, monkeypatch):
+    """A host-buffer call that repeats the previous call's batch size is captured into a CUDA graph and replayed:
+    outputs identical to the eager launches, also after the inputs' contents change and after the blend is reset."""
+    ocfg, w, rows_fn, eng = make_pair(max_batch=8)
+    b1 = po.make_batch(ocfg, 8, seed=31, ragged=True)
+    b2 = po.make_batch(ocfg, 8, seed=32, ragged=False)
+    monkeypatch.setenv("PHX_GRAPH", "0")
+    ocfg, w, rows_fn, eager = make_pair(max_batch=8)
+    want1, want2 = eager.rank(to_inputs(b1)), eager.rank(to_inputs(b2))
+    eager.close()
+    monkeypatch.delenv("PHX_GRAPH")
+    got = [eng.rank(to_inputs(b)) for b in (b1, b1, b1, b2, b2, b1)]      # eager, capture, replay, replay with new data ...
+    for g, wnt in zip(got, (want1, want1, want1, want2, want2, want1)):
+        np.testing.assert_array_equal(g.log_probs, wnt.log_probs)
+        np.testing.assert_array_equal(g.continuous, wnt.continuous)
+        np.testing.assert_array_equal(g.scores, wnt.scores)
+    small = po.make_batch(ocfg, 3, seed=33, ragged=True)                  # another batch size: new key, eager again
+    ocfg2, w2, rows_fn2, ref = make_pair(max_batch=8)
+    np.testing.assert_array_equal(eng.rank(to_inputs(small)).log_probs, ref.rank(to_inputs(small)).log_probs)
+    ref.close()
+    eng.close()

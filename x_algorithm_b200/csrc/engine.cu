@@ -115,6 +115,14 @@ struct phx_engine {
   bool prefetch_valid = false;
   phx_rank_batch prefetch_key;
 
+  // CUDA graph of the forward: a call that repeats the previous call's batch size and buffers is captured once and
+  // replayed afterwards (the forward is ~42 launches; at small batches their launch gaps are most of its time)
+  bool graphs_enabled = true;
+  cudaGraphExec_t graph_exec = nullptr;
+  bool graph_key_valid = false;
+  phx_rank_batch graph_key_b;
+  phx_rank_out graph_key_o;
+  int graph_launches = 0;
   unsigned long long* gemm_counters = nullptr;   // PHX_GEMM_COUNTERS: [role][total, operand wait, accumulator wait]
   int last_batch = 0;
   int last_launches = 0;
@@ -416,6 +424,7 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
   const char* dt = getenv("PHX_DEBUG_TAPS");
   e->debug_taps = dt && dt[0] == '1';
   { const char* sd = getenv("PHX_SYNC_DEBUG"); e->sync_debug = sd && sd[0] == '1'; }
+  { const char* g = getenv("PHX_GRAPH"); e->graphs_enabled = !(g && g[0] == '0'); }
   e->D = cfg->emb_size; e->S = cfg->history_len; e->C = cfg->num_candidates; e->T = e->S + e->C;
   e->Hq = cfg->num_q_heads; e->Hkv = cfg->num_kv_heads; e->dh = cfg->key_size; e->F = cfg->ffn_size;
   e->QW = (e->Hq + 2 * e->Hkv) * e->dh; e->HD = e->Hq * e->dh; e->V = cfg->num_actions; e->NC = cfg->num_continuous;
@@ -529,6 +538,7 @@ void phx_engine_destroy(phx_engine* e) {
   for (auto p : e->ipc_opened) if (p) cudaIpcCloseMemHandle(p);
   auto fr = [](void* p) { if (p) cudaFree(p); };
   fr(e->gemm_counters);
+  if (e->graph_exec) cudaGraphExecDestroy(e->graph_exec);
   fr(e->table); fr(e->action_table); fr(e->surface_table); fr(e->final_norm); fr(e->unembed_t);
   for (auto& L : e->layers) {
     fr(L.pre_attn_norm); fr(L.pre_ffn_norm); fr(L.post_attn_norm); fr(L.post_ffn_norm); fr(L.q_norm); fr(L.k_norm);
@@ -552,6 +562,7 @@ void phx_engine_destroy(phx_engine* e) {
 }
 
 phx_status phx_load_param(phx_engine* e, const char* name, const float* host, int64_t rows, int64_t cols) {
+  if (e) { e->graph_key_valid = false; if (e->graph_exec) { cudaGraphExecDestroy(e->graph_exec); e->graph_exec = nullptr; } }   // a captured forward holds the old state
   if (!e || !name || !host) return PHX_E_ARG;
   cudaSetDevice(e->device);
   const std::string n(name);
@@ -654,12 +665,33 @@ phx_status phx_table_attach_peer_ptr(phx_engine* e, int32_t rank, const void* sh
 }
 
 phx_status phx_set_blend(phx_engine* e, const phx_blend_spec* spec) {
+  if (e) { e->graph_key_valid = false; if (e->graph_exec) { cudaGraphExecDestroy(e->graph_exec); e->graph_exec = nullptr; } }   // a captured forward holds the old state
   if (!e || !spec || spec->num_terms < 0 || spec->num_terms > PHX_MAX_BLEND_TERMS) { if (e) e->err = "phx_set_blend: bad spec"; return PHX_E_ARG; }
   for (int i = 0; i < spec->num_terms; ++i)
     if (spec->src[i] < 0 || spec->src[i] >= e->V + e->NC) { e->err = "phx_set_blend: term source out of range"; return PHX_E_ARG; }
   e->blend = *spec; e->has_blend = true;
   return PHX_OK;
 }
+
+namespace {
+// the launches of one forward, in order, on the engine's stream
+phx_status enqueue_forward(phx_engine* e, const phx_rank_batch* bd, const phx_rank_out* od, int B, bool tokens_ready) {
+  phx_status s;
+  if (!tokens_ready && (s = build_tokens(e, bd, B, e->C))) return s;
+  if ((s = run_trunk(e, B, e->T, e->S, e->S))) return s;
+  HeadsArgs ha;
+  ha.x = e->x; ha.final_gain = e->final_norm; ha.unembed_t = e->unembed_t;
+  ha.B = B; ha.T = e->T; ha.S = e->S; ha.C = e->C; ha.D = e->D; ha.V = e->V; ha.NC = e->NC;
+  ha.eps = e->cfg.rms_eps; ha.output_scale = 2.0f * sqrtf(512.0f / (float)e->D);  // scaling.py:43-44
+  ha.final_logit_cap = e->cfg.final_logit_cap; ha.dwell_norm_scale = e->cfg.dwell_norm_scale;
+  ha.has_blend = e->has_blend ? 1 : 0;
+  if (e->has_blend) ha.blend = e->blend; else memset(&ha.blend, 0, sizeof(ha.blend));
+  ha.log_probs = od->log_probs; ha.continuous = od->continuous; ha.scores = od->scores;
+  { ProfScope ps(e, KC_HEADS); if ((s = heads_launch(ha, e->stream, e->err))) return s; }
+  e->last_launches++;
+  return PHX_OK;
+}
+}  // namespace
 
 phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* bd, const phx_rank_out* od) {
   if (!e || !bd || !od) return PHX_E_ARG;
@@ -673,28 +705,47 @@ phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* bd, cons
   PHX_CUDA_TRY(cudaEventRecord(e->ev0, e->stream), e->err);
   phx_status s;
   if ((s = refresh_folded(e))) return s;
+  bool tokens_ready = false;
   if (e->prefetch_valid && memcmp(&e->prefetch_key, bd, sizeof(*bd)) == 0) {
     // tokens of this batch were built ahead of time: adopt the alternate buffers
     PHX_CUDA_TRY(cudaStreamWaitEvent(e->stream, e->ev_prefetch, 0), e->err);
     std::swap(e->x, e->x_alt);
     std::swap(e->seg, e->seg_alt);
     std::swap(e->rowss_a, e->rowss_a_alt);
-    e->prefetch_valid = false;
-  } else {
-    e->prefetch_valid = false;
-    if ((s = build_tokens(e, bd, B, e->C))) return s;
+    tokens_ready = true;
   }
-  if ((s = run_trunk(e, B, e->T, e->S, e->S))) return s;
-  HeadsArgs ha;
-  ha.x = e->x; ha.final_gain = e->final_norm; ha.unembed_t = e->unembed_t;
-  ha.B = B; ha.T = e->T; ha.S = e->S; ha.C = e->C; ha.D = e->D; ha.V = e->V; ha.NC = e->NC;
-  ha.eps = e->cfg.rms_eps; ha.output_scale = 2.0f * sqrtf(512.0f / (float)e->D);  // scaling.py:43-44
-  ha.final_logit_cap = e->cfg.final_logit_cap; ha.dwell_norm_scale = e->cfg.dwell_norm_scale;
-  ha.has_blend = e->has_blend ? 1 : 0;
-  if (e->has_blend) ha.blend = e->blend; else memset(&ha.blend, 0, sizeof(ha.blend));
-  ha.log_probs = od->log_probs; ha.continuous = od->continuous; ha.scores = od->scores;
-  { ProfScope ps(e, KC_HEADS); if ((s = heads_launch(ha, e->stream, e->err))) return s; }
-  e->last_launches++;
+  e->prefetch_valid = false;
+  // Graph replay: same batch size and the same buffers as the previous call (a serving loop over its own staging
+  // buffers).  The first such repeat is captured; diagnostics, prefetching and buffer swaps keep the eager path.
+  const bool same_key = e->graph_key_valid && memcmp(&e->graph_key_b, bd, sizeof(*bd)) == 0 && memcmp(&e->graph_key_o, od, sizeof(*od)) == 0;
+  const bool eligible = e->graphs_enabled && !e->profile && !e->sync_debug && !e->debug_taps && !e->side_stream && !tokens_ready;
+  if (!same_key && e->graph_exec) { cudaGraphExecDestroy(e->graph_exec); e->graph_exec = nullptr; }
+  if (eligible && same_key && e->graph_exec) {
+    PHX_CUDA_TRY(cudaGraphLaunch(e->graph_exec, e->stream), e->err);
+    e->last_launches = e->graph_launches;
+  } else if (eligible && same_key) {
+    bool captured = false;
+    if (cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+      s = enqueue_forward(e, bd, od, B, false);
+      cudaGraph_t g = nullptr;
+      const cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
+      if (s == PHX_OK && ce == cudaSuccess && g && cudaGraphInstantiate(&e->graph_exec, g, 0) == cudaSuccess) captured = true;
+      if (g) cudaGraphDestroy(g);
+    }
+    if (captured) {
+      e->graph_launches = e->last_launches;
+      PHX_CUDA_TRY(cudaGraphLaunch(e->graph_exec, e->stream), e->err);
+    } else {   // capture is an optimisation: fall back to plain launches for the rest of the engine's life
+      cudaGetLastError();
+      e->graph_exec = nullptr;
+      e->graphs_enabled = false;
+      e->last_launches = 0;
+      if ((s = enqueue_forward(e, bd, od, B, false))) return s;
+    }
+  } else {
+    if ((s = enqueue_forward(e, bd, od, B, tokens_ready))) return s;
+  }
+  e->graph_key_b = *bd; e->graph_key_o = *od; e->graph_key_valid = true;
   PHX_CUDA_TRY(cudaEventRecord(e->ev1, e->stream), e->err);
   if (e->ev_done[0]) { e->done_idx ^= 1; PHX_CUDA_TRY(cudaEventRecord(e->ev_done[e->done_idx], e->stream), e->err); }
   return PHX_OK;
