@@ -126,4 +126,6 @@ def main(ref: str, outdir: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", os.path.dirname(os.path.abspath(__file__)))
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/gen_golden.py <path to a checkout of xai-org/x-algorithm>")
+    main(sys.argv[1], os.path.dirname(os.path.abspath(__file__)))
