@@ -249,6 +249,15 @@ phx_status phx_ipc_open(int32_t device, const uint8_t handle[PHX_IPC_HANDLE_BYTE
 phx_status phx_ipc_close(void* ptr);
 phx_status phx_ipc_free(void* ptr);
 
+/* Diagnostic: the two resources the GEMM main loop lives on, measured apart and together.  148 CTAs (pair != 0: 74
+ * CTA pairs, tcgen05 cta_group::2) issue the GEMM's MMAs over fixed shared-memory tiles for `ksteps` k-steps (a
+ * multiple of 8); fill_tiles_per_kstep (0..3) 16 KB TMA tiles per k-step and CTA are streamed beside them without
+ * synchronisation; sync_mode 0 = one commit per 8 k-steps, 1 = one per k-step, 2 = one per k-step plus a wait on the
+ * commit of four k-steps earlier.  Out: kernel time, the MMA issuer's cycles per k-step (512 = the pipe's full rate),
+ * the fill thread's cycles per k-step.  No counterpart in the reference. */
+phx_status phx_diag_mma_rate(int32_t device, int32_t pair, int32_t ksteps, int32_t fill_tiles_per_kstep, int32_t sync_mode,
+                             float* ms_out, double* mma_cycles_per_kstep, double* fill_cycles_per_kstep);
+
 /* ---- stand-alone operators (micro-benchmarks and parity tests of single kernels) ------------- */
 
 /* Multi-hash id -> unified-table rows; `family`: 0 user, 1 item, 2 author, 3 ip.

@@ -79,6 +79,8 @@ SIGNATURES = {
     "phx_shard_gather_push": (C.c_int32, [_P, C.c_int64, _P, C.c_int64, _P, _P, C.c_int32, C.c_int32, _P]),
     "phx_shard_dedup": (C.c_int32, [_P, C.c_int64, _P, C.c_int64, _P, _P, _P, _P]),
     "phx_shard_dedup_expand": (C.c_int32, [_P, _P, _P, C.c_int64, _P, _P]),
+    "phx_diag_mma_rate": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_float),
+                                      C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "phx_copy_async": (C.c_int32, [_P, _P, C.c_uint64, _P]),
     "phx_ipc_alloc": (C.c_int32, [C.c_int32, C.c_uint64, C.POINTER(_P), _P]),
     "phx_ipc_open": (C.c_int32, [C.c_int32, _P, C.POINTER(_P)]),

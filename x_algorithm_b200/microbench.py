@@ -4,6 +4,7 @@
     torchrun --nproc-per-node N -m x_algorithm_b200.microbench gather [--exchange copy|push|a2a|peer] [--check]
     python -m x_algorithm_b200.microbench topk    [--rows 12500000] [--dim 128] [--queries 256] [--k 1000]
     torchrun --nproc-per-node N -m x_algorithm_b200.microbench retrieve [--rows 100000000] [--check]
+    python -m x_algorithm_b200.microbench mma [--ksteps 200000]
     python -m x_algorithm_b200.microbench attention [--batch 64] [--heads 16] [--dh 128] [--hist 1024] [--cands 1024]
 
 gather: the multi-hash gather-sum workload (8 tables x 2^24 rows x 256 bf16 = 64 GiB, realised as the four hash
@@ -234,9 +235,30 @@ def bench_attention(a):
                           peak_source=src)))
 
 
+def bench_mma(a):
+    """The tcgen05 pipe and the L2 -> shared-memory fill, apart and together (the GEMM's two resources)."""
+    import ctypes as C
+    from x_algorithm_b200 import _lib
+    lib = _lib.lib
+    cases = [("pipe alone", 1, 0, 2), ("pipe + 32 KB/k-step fill (a CTA pair's 256x256 tile)", 1, 2, 2),
+             ("pipe + 16 KB/k-step fill", 1, 1, 2), ("one CTA per tile: pipe + 48 KB/k-step fill", 0, 3, 2)]
+    for name, pair, tiles, mode in cases:
+        ms, mc, fc = C.c_float(), C.c_double(), C.c_double()
+        st = lib.phx_diag_mma_rate(0, pair, a.ksteps, tiles, mode, C.byref(ms), C.byref(mc), C.byref(fc))
+        if st != 0:
+            raise _lib.PhoenixError(st, lib.phx_global_error().decode())
+        flop = 2.0 * 128 * 256 * 64 * a.ksteps * 148
+        cyc = max(mc.value, fc.value)
+        print(json.dumps(dict(op="mma_rate", case=name, ksteps=a.ksteps, ms=ms.value, mma_cycles_per_kstep=round(mc.value, 1),
+                              fill_cycles_per_kstep=round(fc.value, 1), tflops=flop / ms.value / 1e9,
+                              sm_ghz=round(cyc * a.ksteps / (ms.value * 1e-3) / 1e9, 3),
+                              fill_tbs=tiles * 16384.0 * a.ksteps * 148 / (ms.value * 1e-3) / 1e12)))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gather", "topk", "attention", "retrieve"])
+    ap.add_argument("op", choices=["gather", "topk", "attention", "retrieve", "mma"])
+    ap.add_argument("--ksteps", type=int, default=200000, help="mma: k-steps per CTA (2000000 runs about a second)")
     ap.add_argument("--check", action="store_true")
     ap.add_argument("--no-dedup", action="store_true", help="sharded gather: send every request, not only distinct rows")
     ap.add_argument("--exchange", choices=["copy", "push", "a2a", "peer"], default="copy",
@@ -259,7 +281,7 @@ def main():
     ap.add_argument("--hist", type=int, default=1024)
     ap.add_argument("--cands", type=int, default=1024)
     a = ap.parse_args()
-    {"gather": bench_gather, "topk": bench_topk, "attention": bench_attention, "retrieve": bench_retrieve}[a.op](a)
+    {"gather": bench_gather, "topk": bench_topk, "attention": bench_attention, "retrieve": bench_retrieve, "mma": bench_mma}[a.op](a)
 
 
 if __name__ == "__main__":
