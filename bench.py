@@ -6,8 +6,8 @@ A step = one ranking forward (hash -> gather-sum -> 8-layer transformer with can
 attention -> heads -> weighted blend) over one synthetic batch of 256 requests x 512 candidates
 (D=512, 8 heads x 64, FFN 2048, history 128; unified embedding table of 4 x 2^22 rows x 512 bf16).
 Prints one JSON line:  value = ranked candidates/s with inputs resident in HBM (CUDA events on the
-engine's stream), e2e = the same through the host-buffer C-ABI call (H2D + D2H inside the timed
-region), roofline = the GEMM kernel against the measured bf16 peak, cpu_baseline = the NumPy oracle
+engine's stream), e2e = the same through the host-buffer C-ABI calls, two requests in flight (each
+step's H2D + D2H inside the timed region; `e2e.sync_call` = one blocking call per step), roofline = the GEMM kernel against the measured bf16 peak, cpu_baseline = the NumPy oracle
 on the host cores over a bounded sample.  `--impl reference` times the CPU oracle alone.
 """
 from __future__ import annotations
@@ -214,14 +214,27 @@ def main():
     # end to end through the host-buffer call: pinned staging + H2D + forward + D2H inside the timed region
     host_in = [px.RankInputs(b.hist_post_ids, b.hist_author_ids, b.hist_actions, b.hist_surfaces, b.cand_post_ids,
                              b.cand_author_ids) for b in batches]
-    out = None
+    # two requests in flight (phx_rank_submit / phx_rank_collect): the copies of one overlap the forward of the other;
+    # every step still pays its own H2D and D2H inside the timed region.  Result arrays are reused, as a server would.
+    outs = [None, None]
     for i in range(2):
-        out = eng.rank(host_in[i % n_rot], out)       # result arrays are reused, as a server would
+        outs[i] = eng.rank(host_in[i % n_rot], None)
+    eng.rank_submit(host_in[0], 0); outs[0] = eng.rank_collect(0, outs[0])      # warm the pipelined path
     barrier()
+    t0 = time.perf_counter()
+    eng.rank_submit(host_in[0], 0)
+    for i in range(1, args.steps):
+        eng.rank_submit(host_in[i % n_rot], i & 1)
+        outs[(i - 1) & 1] = eng.rank_collect((i - 1) & 1, outs[(i - 1) & 1])
+    outs[(args.steps - 1) & 1] = eng.rank_collect((args.steps - 1) & 1, outs[(args.steps - 1) & 1])
+    out = outs[0]
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    # the same with one blocking call per step (no overlap between steps)
     t0 = time.perf_counter()
     for i in range(args.steps):
         out = eng.rank(host_in[i % n_rot], out)
-    e2e_s = time.perf_counter() - t0
+    e2e_sync_s = time.perf_counter() - t0
     barrier()
     # p50 latency of one request (B=1) and of the throughput batch through the same host-buffer call
     one = px.RankInputs(*[a[:1] for a in (batches[0].hist_post_ids, batches[0].hist_author_ids, batches[0].hist_actions,
@@ -258,7 +271,9 @@ def main():
                         tables=("row-sharded over ranks, remote rows by NVLink peer loads" if sharded else "one full table per GPU"),
                         l2="working set per step (activations 1.7 GB, table 17 GB) exceeds the 126 MB L2; 4 input batches rotated"),
             e2e=dict(value=total / (e2e_ms * 1e-3), unit="candidates/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
-                     ms_per_step=e2e_ms / args.steps),
+                     ms_per_step=e2e_ms / args.steps, api="phx_rank_submit / phx_rank_collect, two requests in flight",
+                     sync_call=dict(value=B * C * args.steps / e2e_sync_s, ms_per_step=1e3 * e2e_sync_s / args.steps,
+                                    api="phx_rank_forward, rank 0")),
             gpu_launches=launches,
             roofline=dict(bound="tensor", kernel="gemm_tcgen05_kernel", achieved=gemm_tflops, peak=peaks["bf16"], unit="TFLOP/s",
                           frac=(gemm_tflops / peaks["bf16"]) if gemm_tflops else None,

@@ -170,6 +170,14 @@ phx_status phx_table_attach_peer_ptr(phx_engine* e, int32_t rank, const void* sh
  * heads -> blend, copies results out, returns when they are readable.  Replaces
  * RankingModelRunner.gather_embeddings_and_forward + reply (model_runner.py:4141-4222). */
 phx_status phx_rank_forward(phx_engine* e, const phx_rank_batch* batch_host, const phx_rank_out* out_host);
+/* Two-deep pipeline of host-buffer requests: phx_rank_submit copies the inputs into the slot's pinned block and
+ * enqueues H2D copy, forward and D2H copies (the copies on their own stream: they overlap the forward of the other
+ * slot); phx_rank_collect waits for the slot's results and copies them out.  Same semantics as phx_rank_forward per
+ * request; a slot must be collected before it is submitted again (PHX_E_STATE otherwise).  A serving loop that keeps
+ * both slots in flight hides the host-side copies behind the forward — the reference runner's async dispatch /
+ * reply split (model_runner.py:4141-4222). */
+phx_status phx_rank_submit(phx_engine* e, const phx_rank_batch* batch_host, int32_t slot);
+phx_status phx_rank_collect(phx_engine* e, int32_t slot, const phx_rank_out* out_host);
 /* Same with DEVICE buffers, asynchronous on the engine's stream (call phx_sync to wait). */
 phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* batch_dev, const phx_rank_out* out_dev);
 /* Build the tokens (hash -> gather-sum) of the batch that the NEXT phx_rank_forward_device call will carry, on a

@@ -459,3 +459,29 @@ def test_graph_replay_matches_eager(torch, monkeypatch):
     np.testing.assert_array_equal(eng.rank(to_inputs(small)).log_probs, ref.rank(to_inputs(small)).log_probs)
     ref.close()
     eng.close()
+
+
+def test_pipelined_submit_collect_matches_blocking_call(torch):
+    """Two requests in flight through phx_rank_submit / phx_rank_collect give the results of the blocking call,
+    whatever the order of collection; a slot cannot be resubmitted before it is collected."""
+    import x_algorithm_b200 as px
+    ocfg, w, rows_fn, eng = make_pair(max_batch=8)
+    bs = [po.make_batch(ocfg, n, seed=40 + i, ragged=bool(i & 1)) for i, n in enumerate((8, 5, 8, 1))]
+    want = [eng.rank(to_inputs(b)) for b in bs]
+    eng.rank_submit(to_inputs(bs[0]), 0)
+    eng.rank_submit(to_inputs(bs[1]), 1)
+    with pytest.raises(px.PhoenixError) as ei:
+        eng.rank_submit(to_inputs(bs[2]), 1)
+    assert ei.value.status == 6
+    got0 = eng.rank_collect(0)
+    eng.rank_submit(to_inputs(bs[2]), 0)
+    got1 = eng.rank_collect(1)
+    eng.rank_submit(to_inputs(bs[3]), 1)
+    got3 = eng.rank_collect(1)
+    got2 = eng.rank_collect(0)
+    for g, wnt in zip((got0, got1, got2, got3), want):
+        np.testing.assert_array_equal(g.log_probs, wnt.log_probs)
+        np.testing.assert_array_equal(g.continuous, wnt.continuous)
+    with pytest.raises(px.PhoenixError):
+        eng.rank_collect(0)
+    eng.close()

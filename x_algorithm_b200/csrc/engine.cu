@@ -109,6 +109,19 @@ struct phx_engine {
   cudaStream_t side_stream = nullptr;
   cudaEvent_t ev_prefetch = nullptr;
   cudaEvent_t ev_chunk[4] = {nullptr, nullptr, nullptr, nullptr};   // result chunks of the host-buffer call
+  // two-deep pipeline of host-buffer requests (phx_rank_submit / phx_rank_collect): per slot its own staging blocks
+  // and events; the copies run on their own stream so that they overlap the forward of the other slot
+  struct StageSlot {
+    void* in_dev = nullptr; void* in_host = nullptr;
+    float* lp_dev = nullptr; float* cont_dev = nullptr; double* score_dev = nullptr;
+    float* lp_host = nullptr; float* cont_host = nullptr; double* score_host = nullptr;
+    cudaEvent_t in_ready = nullptr, fwd_done = nullptr, out_done = nullptr;
+    cudaEvent_t chunk[4] = {nullptr, nullptr, nullptr, nullptr};
+    bool busy = false;
+    int batch = 0;
+  };
+  StageSlot slots[2];
+  cudaStream_t copy_stream = nullptr;
   cudaEvent_t ev_done[2] = {nullptr, nullptr};   // ends of the last two forwards; done_idx = the most recent
   int done_idx = 0;
   bf16* x_alt = nullptr; int* seg_alt = nullptr; float* rowss_a_alt = nullptr;
@@ -539,6 +552,18 @@ void phx_engine_destroy(phx_engine* e) {
   auto fr = [](void* p) { if (p) cudaFree(p); };
   fr(e->gemm_counters);
   if (e->graph_exec) cudaGraphExecDestroy(e->graph_exec);
+  for (auto& sl : e->slots) {
+    fr(sl.in_dev); fr(sl.lp_dev); fr(sl.cont_dev); fr(sl.score_dev);
+    if (sl.in_host) cudaFreeHost(sl.in_host);
+    if (sl.lp_host) cudaFreeHost(sl.lp_host);
+    if (sl.cont_host) cudaFreeHost(sl.cont_host);
+    if (sl.score_host) cudaFreeHost(sl.score_host);
+    if (sl.in_ready) cudaEventDestroy(sl.in_ready);
+    if (sl.fwd_done) cudaEventDestroy(sl.fwd_done);
+    if (sl.out_done) cudaEventDestroy(sl.out_done);
+    for (auto& ev : sl.chunk) if (ev) cudaEventDestroy(ev);
+  }
+  if (e->copy_stream) cudaStreamDestroy(e->copy_stream);
   fr(e->table); fr(e->action_table); fr(e->surface_table); fr(e->final_norm); fr(e->unembed_t);
   for (auto& L : e->layers) {
     fr(L.pre_attn_norm); fr(L.pre_ffn_norm); fr(L.post_attn_norm); fr(L.post_ffn_norm); fr(L.q_norm); fr(L.k_norm);
@@ -824,6 +849,97 @@ phx_status phx_rank_forward(phx_engine* e, const phx_rank_batch* bh, const phx_r
     if (oh->scores && e->has_blend) memcpy(oh->scores + r0, e->score_host + r0, (r1 - r0) * 8);
   }
   PHX_CUDA_TRY(cudaStreamSynchronize(e->stream), e->err);
+  return check_err_flag(e);
+}
+
+// ---- pipelined host-buffer requests ------------------------------------------------------------------------------
+namespace {
+phx_status slots_init(phx_engine* e) {
+  if (e->copy_stream) return PHX_OK;
+  PHX_CUDA_TRY(cudaStreamCreateWithFlags(&e->copy_stream, cudaStreamNonBlocking), e->err);
+  const size_t rows = (size_t)e->cfg.max_batch * e->C;
+  for (auto& sl : e->slots) {
+    PHX_CUDA_TRY(cudaMalloc(&sl.in_dev, e->in_stage_bytes), e->err);
+    PHX_CUDA_TRY(cudaMallocHost(&sl.in_host, e->in_stage_bytes), e->err);
+    PHX_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&sl.lp_dev), rows * (e->V > 0 ? e->V : 1) * 4), e->err);
+    PHX_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&sl.cont_dev), rows * (e->NC > 0 ? e->NC : 1) * 4), e->err);
+    PHX_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&sl.score_dev), rows * 8), e->err);
+    PHX_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&sl.lp_host), rows * (e->V > 0 ? e->V : 1) * 4), e->err);
+    PHX_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&sl.cont_host), rows * (e->NC > 0 ? e->NC : 1) * 4), e->err);
+    PHX_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&sl.score_host), rows * 8), e->err);
+    PHX_CUDA_TRY(cudaEventCreateWithFlags(&sl.in_ready, cudaEventDisableTiming), e->err);
+    PHX_CUDA_TRY(cudaEventCreateWithFlags(&sl.fwd_done, cudaEventDisableTiming), e->err);
+    PHX_CUDA_TRY(cudaEventCreateWithFlags(&sl.out_done, cudaEventDisableTiming), e->err);
+    for (auto& ev : sl.chunk) PHX_CUDA_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), e->err);
+  }
+  return PHX_OK;
+}
+constexpr int SLOT_CHUNKS = 4;
+}  // namespace
+
+phx_status phx_rank_submit(phx_engine* e, const phx_rank_batch* bh, int32_t slot) {
+  if (!e || !bh || slot < 0 || slot > 1) return PHX_E_ARG;
+  if (bh->batch <= 0 || bh->batch > e->cfg.max_batch) { e->err = "batch must be 1..max_batch"; return PHX_E_CAPACITY; }
+  cudaSetDevice(e->device);
+  phx_status s = slots_init(e);
+  if (s) return s;
+  auto& sl = e->slots[slot];
+  if (sl.busy) { e->err = "phx_rank_submit: the slot holds a request that has not been collected"; return PHX_E_STATE; }
+  const size_t B = bh->batch, S = e->S, C = e->C;
+  uint8_t* hp = (uint8_t*)sl.in_host;
+  uint8_t* dp = (uint8_t*)sl.in_dev;
+  size_t off = 0;
+  phx_rank_batch bd; bd.batch = bh->batch; bd._pad = 0;
+  auto put = [&](const void* src, size_t bytes) { memcpy(hp + off, src, bytes); const void* d = dp + off; off += bytes; return d; };
+  bd.hist_post_ids = (const int64_t*)put(bh->hist_post_ids, B * S * 8);
+  bd.hist_author_ids = (const int64_t*)put(bh->hist_author_ids, B * S * 8);
+  bd.cand_post_ids = (const int64_t*)put(bh->cand_post_ids, B * C * 8);
+  bd.cand_author_ids = (const int64_t*)put(bh->cand_author_ids, B * C * 8);
+  bd.hist_actions = (const int32_t*)put(bh->hist_actions, B * S * 4);
+  bd.hist_surfaces = (const int32_t*)put(bh->hist_surfaces, B * S * 4);
+  // inputs: on the copy stream, once the forward that last read this slot's device block is done
+  PHX_CUDA_TRY(cudaStreamWaitEvent(e->copy_stream, sl.fwd_done, 0), e->err);
+  PHX_CUDA_TRY(cudaMemcpyAsync(dp, hp, off, cudaMemcpyHostToDevice, e->copy_stream), e->err);
+  PHX_CUDA_TRY(cudaEventRecord(sl.in_ready, e->copy_stream), e->err);
+  // forward: after the inputs have landed and the slot's previous results have left its device block
+  PHX_CUDA_TRY(cudaStreamWaitEvent(e->stream, sl.in_ready, 0), e->err);
+  PHX_CUDA_TRY(cudaStreamWaitEvent(e->stream, sl.out_done, 0), e->err);
+  phx_rank_out od; od.log_probs = sl.lp_dev; od.continuous = sl.cont_dev; od.scores = sl.score_dev;
+  if ((s = phx_rank_forward_device(e, &bd, &od))) return s;
+  PHX_CUDA_TRY(cudaEventRecord(sl.fwd_done, e->stream), e->err);
+  // results: back on the copy stream, in row chunks
+  PHX_CUDA_TRY(cudaStreamWaitEvent(e->copy_stream, sl.fwd_done, 0), e->err);
+  const size_t rows = B * C, step = (rows + SLOT_CHUNKS - 1) / SLOT_CHUNKS;
+  for (int i = 0; i < SLOT_CHUNKS; ++i) {
+    const size_t r0 = i * step, r1 = (r0 + step < rows) ? r0 + step : rows;
+    if (r0 < r1) {
+      PHX_CUDA_TRY(cudaMemcpyAsync(sl.lp_host + r0 * e->V, sl.lp_dev + r0 * e->V, (r1 - r0) * e->V * 4, cudaMemcpyDeviceToHost, e->copy_stream), e->err);
+      PHX_CUDA_TRY(cudaMemcpyAsync(sl.cont_host + r0 * e->NC, sl.cont_dev + r0 * e->NC, (r1 - r0) * e->NC * 4, cudaMemcpyDeviceToHost, e->copy_stream), e->err);
+      if (e->has_blend) PHX_CUDA_TRY(cudaMemcpyAsync(sl.score_host + r0, sl.score_dev + r0, (r1 - r0) * 8, cudaMemcpyDeviceToHost, e->copy_stream), e->err);
+    }
+    PHX_CUDA_TRY(cudaEventRecord(sl.chunk[i], e->copy_stream), e->err);
+  }
+  PHX_CUDA_TRY(cudaEventRecord(sl.out_done, e->copy_stream), e->err);
+  sl.busy = true;
+  sl.batch = bh->batch;
+  return PHX_OK;
+}
+
+phx_status phx_rank_collect(phx_engine* e, int32_t slot, const phx_rank_out* oh) {
+  if (!e || !oh || slot < 0 || slot > 1) return PHX_E_ARG;
+  auto& sl = e->slots[slot];
+  if (!sl.busy) { e->err = "phx_rank_collect: nothing was submitted to this slot"; return PHX_E_STATE; }
+  cudaSetDevice(e->device);
+  const size_t rows = (size_t)sl.batch * e->C, step = (rows + SLOT_CHUNKS - 1) / SLOT_CHUNKS;
+  for (int i = 0; i < SLOT_CHUNKS; ++i) {
+    PHX_CUDA_TRY(cudaEventSynchronize(sl.chunk[i]), e->err);
+    const size_t r0 = i * step, r1 = (r0 + step < rows) ? r0 + step : rows;
+    if (r0 >= r1) continue;
+    if (oh->log_probs) memcpy(oh->log_probs + r0 * e->V, sl.lp_host + r0 * e->V, (r1 - r0) * e->V * 4);
+    if (oh->continuous) memcpy(oh->continuous + r0 * e->NC, sl.cont_host + r0 * e->NC, (r1 - r0) * e->NC * 4);
+    if (oh->scores && e->has_blend) memcpy(oh->scores + r0, sl.score_host + r0, (r1 - r0) * 8);
+  }
+  sl.busy = false;
   return check_err_flag(e);
 }
 

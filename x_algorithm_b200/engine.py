@@ -138,6 +138,39 @@ class PhoenixEngine:
         self._check(lib.phx_rank_forward(self._h, C.byref(b), C.byref(o)))
         return RankOutputs(lp, cont, sc)
 
+    def rank_submit(self, inp: RankInputs, slot: int) -> None:
+        """Start a host-buffer request in pipeline slot 0 or 1 and return at once (the inputs are copied before the
+        call returns).  `rank_collect(slot)` delivers its results; with both slots in flight the host-side copies of
+        one request overlap the forward of the other."""
+        cfg, B = self.cfg, inp.batch
+        arrs = [np.ascontiguousarray(inp.hist_post_ids, np.int64), np.ascontiguousarray(inp.hist_author_ids, np.int64),
+                np.ascontiguousarray(inp.hist_actions, np.int32), np.ascontiguousarray(inp.hist_surfaces, np.int32),
+                np.ascontiguousarray(inp.cand_post_ids, np.int64), np.ascontiguousarray(inp.cand_author_ids, np.int64)]
+        assert arrs[0].shape == (B, cfg.history_len) and arrs[4].shape == (B, cfg.num_candidates)
+        b = self._batch_struct(B, *arrs)
+        self._check(lib.phx_rank_submit(self._h, C.byref(b), slot))
+        self._slot_batch = getattr(self, "_slot_batch", {})
+        self._slot_batch[slot] = B
+
+    def rank_collect(self, slot: int, out: "RankOutputs | None" = None) -> RankOutputs:
+        """Wait for the request submitted to `slot` and return its results (into `out` when given)."""
+        cfg = self.cfg
+        B = getattr(self, "_slot_batch", {}).get(slot)
+        if B is None:
+            raise PhoenixError(6, "rank_collect: nothing was submitted to this slot")
+        if out is not None and out.log_probs.shape == (B, cfg.num_candidates, cfg.num_actions):
+            lp, cont, sc = out.log_probs, out.continuous, out.scores
+            if self._has_blend and sc is None:
+                sc = np.empty((B, cfg.num_candidates), np.float64)
+        else:
+            lp = np.empty((B, cfg.num_candidates, cfg.num_actions), np.float32)
+            cont = np.empty((B, cfg.num_candidates, cfg.num_continuous), np.float32)
+            sc = np.empty((B, cfg.num_candidates), np.float64) if self._has_blend else None
+        o = _lib.RankOut(_ptr(lp), _ptr(cont), _ptr(sc))
+        self._check(lib.phx_rank_collect(self._h, slot, C.byref(o)))
+        del self._slot_batch[slot]
+        return RankOutputs(lp, cont, sc)
+
     def rank_device(self, B, hp, ha, act, srf, cp, ca, lp, cont, sc=None):
         """Device tensors (torch) in and out; asynchronous on the engine's stream."""
         b = self._batch_struct(B, hp, ha, act, srf, cp, ca)
