@@ -1,12 +1,12 @@
 // bf16 GEMM for the Linear layers of the Phoenix trunk (phoenix/xrex/models/linear_layer.py:52-91)
 // on Blackwell tensor cores: C[M,N] = epilogue(A[M,K] @ Wt[N,K]^T), fp32 accumulation in TMEM.
 //
-// Persistent kernel, one CTA per SM, 320 threads:
+// Persistent kernel, one CTA per SM, 64 + 128 x NG threads (NG = epilogue groups: 2 or 4):
 //   warp 0      TMA producer: A tile 128x64 and W tile per k-step (bf16, 128-byte swizzle) into a ring of
 //               shared-memory stages (cp.async.bulk.tensor + mbarrier tx count)
 //   warp 1      MMA issuer: one lane issues tcgen05.mma (N=BN, K=16) x4 per stage into one of two TMEM
 //               accumulators, tcgen05.commit releases the stage / publishes the tile
-//   warps 2-9   epilogue, two groups of four warps: tcgen05.ld the finished accumulator (each warp its
+//   warps 2..   epilogue, NG groups of four warps: tcgen05.ld the finished accumulator (each warp its
 //               32-lane quadrant) in 64-column slabs, fused op (store | +residual | GELU-tanh | RoPE | RMSNorm
 //               scale), bf16 slab staged in swizzled shared memory and written by one TMA bulk store; the
 //               residual slab is fetched by TMA ahead of its use; overlaps the next tile's main loop through
