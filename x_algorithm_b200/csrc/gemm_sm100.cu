@@ -168,44 +168,60 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
+    // One thread, and the pipe only stays fed if this loop is short: the thread shares its scheduler with four
+    // epilogue warps, so every instruction here costs several cycles of wall time.  Stage addresses and descriptors
+    // are carried as running values (no per-step address arithmetic), the wait counters exist only when asked for.
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = make_idesc(TILE_M, BN);
+      constexpr uint64_t DESC_STEP = (uint64_t)(cfg::STAGE_BYTES >> 4);    // descriptor address field: bytes / 16
+      const uint64_t adesc0 = make_smem_desc(smem_base);
+      const uint64_t bdesc0 = make_smem_desc(smem_base + cfg::A_BYTES);
+      uint64_t adesc = adesc0, bdesc = bdesc0;
+      uint32_t full_addr = full_bar(0), empty_addr = empty_bar(0);
       int stage = 0; uint32_t phase = 0;
       uint32_t it = 0;
       bool ok = true;
       long long cnt_tempty = 0, cnt_full = 0;
-      const long long t_start = counters ? clock64() : 0;
-      if (counters && blockIdx.x == 0) counters[4] = globaltimer_ns();   // first MMA wait
+      const bool timed = counters != nullptr;
+      const long long t_start = timed ? clock64() : 0;
+      if (timed && blockIdx.x == 0) counters[4] = globaltimer_ns();   // first MMA wait
       for (long long tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++it) {
         const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
-        long long c0 = counters ? clock64() : 0;
+        long long c0 = timed ? clock64() : 0;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, verr)) { ok = false; break; }
-        if (counters) cnt_tempty += clock64() - c0;
+        if (timed) cnt_tempty += clock64() - c0;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          c0 = counters ? clock64() : 0;
-          if (!mbar_wait(full_bar(stage), phase, verr)) { ok = false; break; }
-          if (counters) cnt_full += clock64() - c0;
+          if (timed) c0 = clock64();
+          if (!mbar_wait(full_addr, phase, verr)) { ok = false; break; }
+          if (timed) cnt_full += clock64() - c0;
           tc_fence_after();
-          const uint32_t a_src = smem_base + stage * cfg::STAGE_BYTES;
-          const uint64_t adesc = make_smem_desc(a_src);
-          const uint64_t bdesc = make_smem_desc(a_src + cfg::A_BYTES);
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            // advancing 16 elements along K inside the 128-byte swizzle row = +32 bytes = +2 in the address field
-            if (PAIR) umma_bf16_pair(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb | k) != 0);
-            else umma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+          // advancing 16 elements along K inside the 128-byte swizzle row = +32 bytes = +2 in the address field
+          if (PAIR) {
+            umma_bf16_pair(tmem_d, adesc, bdesc, idesc, kb != 0);
+            umma_bf16_pair(tmem_d, adesc + 2, bdesc + 2, idesc, 1);
+            umma_bf16_pair(tmem_d, adesc + 4, bdesc + 4, idesc, 1);
+            umma_bf16_pair(tmem_d, adesc + 6, bdesc + 6, idesc, 1);
+            umma_commit_pair(empty_addr, 3);   // stage reusable (in both CTAs) once these MMAs have read it
+          } else {
+            umma_bf16(tmem_d, adesc, bdesc, idesc, kb != 0);
+            umma_bf16(tmem_d, adesc + 2, bdesc + 2, idesc, 1);
+            umma_bf16(tmem_d, adesc + 4, bdesc + 4, idesc, 1);
+            umma_bf16(tmem_d, adesc + 6, bdesc + 6, idesc, 1);
+            umma_commit(empty_addr);
           }
-          // stage reusable (in both CTAs of a pair) once these MMAs have read it
-          if (PAIR) umma_commit_pair(empty_bar(stage), 3); else umma_commit(empty_bar(stage));
-          if (++stage == cfg::STAGES) { stage = 0; phase ^= 1; }
+          adesc += DESC_STEP; bdesc += DESC_STEP; full_addr += 8; empty_addr += 8;
+          if (++stage == cfg::STAGES) {
+            stage = 0; phase ^= 1;
+            adesc = adesc0; bdesc = bdesc0; full_addr = full_bar(0); empty_addr = empty_bar(0);
+          }
         }
         if (ok) {  // accumulator complete
           if (PAIR) umma_commit_pair(tfull_bar(acc), 3); else umma_commit(tfull_bar(acc));
         }
       }
-      if (counters) {   // diagnostic: where the MMA issuer spent its time (cycles summed over CTAs)
+      if (timed) {   // diagnostic: where the MMA issuer spent its time (cycles summed over CTAs)
         atomicAdd(&counters[0], (unsigned long long)(clock64() - t_start));
         atomicAdd(&counters[1], (unsigned long long)cnt_full);
         atomicAdd(&counters[2], (unsigned long long)cnt_tempty);
