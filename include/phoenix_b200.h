@@ -170,6 +170,15 @@ phx_status phx_table_attach_peer_ptr(phx_engine* e, int32_t rank, const void* sh
  * heads -> blend, copies results out, returns when they are readable.  Replaces
  * RankingModelRunner.gather_embeddings_and_forward + reply (model_runner.py:4141-4222). */
 phx_status phx_rank_forward(phx_engine* e, const phx_rank_batch* batch_host, const phx_rank_out* out_host);
+/* Row-sharded table with the rows exchanged in bulk between the two halves of a forward (parallel.ShardedRanker):
+ * phx_rank_rows_device writes the unified-table row of every token slot (int32 [B, S+C, 2*num_hashes]: post hashes,
+ * then author hashes) and stops; after the exchange (phx_shard_*), phx_rank_forward_rows_device runs the forward
+ * taking slot j of token t from landing_dev[pos_dev[t * 2*num_hashes + j]] (bf16 rows of emb_size) instead of the
+ * table.  Same results as phx_rank_forward_device on an unsharded table, bit for bit.  The reference does the same
+ * split around its row_emb exchange (row_emb_comm.cc:655-743). */
+phx_status phx_rank_rows_device(phx_engine* e, const phx_rank_batch* batch_dev, int32_t* rows_dev);
+phx_status phx_rank_forward_rows_device(phx_engine* e, const phx_rank_batch* batch_dev, const uint16_t* landing_dev,
+                                        const int32_t* pos_dev, const phx_rank_out* out_dev);
 /* Two-deep pipeline of host-buffer requests: phx_rank_submit copies the inputs into the slot's pinned block and
  * enqueues H2D copy, forward and D2H copies (the copies on their own stream: they overlap the forward of the other
  * slot); phx_rank_collect waits for the slot's results and copies them out.  Same semantics as phx_rank_forward per

@@ -485,3 +485,78 @@ def test_pipelined_submit_collect_matches_blocking_call(torch):
     with pytest.raises(px.PhoenixError):
         eng.rank_collect(0)
     eng.close()
+
+
+def _device_batch(torch, b):
+    t = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a, dt)).cuda()
+    return (t(b.hist_post_ids, np.int64), t(b.hist_author_ids, np.int64), t(b.hist_actions, np.int32),
+            t(b.hist_surfaces, np.int32), t(b.cand_post_ids, np.int64), t(b.cand_author_ids, np.int64))
+
+
+def _device_out(torch, cfg, B):
+    return (torch.empty((B, cfg.num_candidates, cfg.num_actions), dtype=torch.float32, device="cuda"),
+            torch.empty((B, cfg.num_candidates, cfg.num_continuous), dtype=torch.float32, device="cuda"))
+
+
+def test_forward_from_exchanged_rows_bit_identical(torch):
+    """phx_rank_rows_device + phx_rank_forward_rows_device (the two halves of a forward around a row exchange):
+    the rows it names are those of the oracle's hashes, and the forward over a shuffled, de-duplicated landing
+    buffer equals the forward over the table bit for bit (ragged batch: padded slots name row 0)."""
+    from x_algorithm_b200 import _lib
+    from x_algorithm_b200.engine import _ptr
+    ocfg, w, rows_fn, eng = make_pair(max_batch=8)
+    cfg, B = eng.cfg, 7
+    b = po.make_batch(ocfg, B, seed=51, ragged=True)
+    dev = _device_batch(torch, b)
+    want = _device_out(torch, cfg, B)
+    eng.rank_device(B, *dev, *want); eng.sync()
+    T, H2 = cfg.history_len + cfg.num_candidates, 2 * cfg.num_hashes
+    rows = torch.empty(B * T * H2, dtype=torch.int32, device="cuda")
+    eng.rank_rows_device(B, *dev, rows); eng.sync()
+    r = rows.cpu().numpy().reshape(B, T, H2)
+    post = np.concatenate([b.hist_post_ids, b.cand_post_ids], 1)
+    auth = np.concatenate([b.hist_author_ids, b.cand_author_ids], 1)
+    lay = ocfg.hash_layout()
+    np.testing.assert_array_equal(r[..., :cfg.num_hashes], lay.item_hash(post))
+    np.testing.assert_array_equal(r[..., cfg.num_hashes:], lay.author_hash(auth))
+    urows, inv = torch.unique(rows, return_inverse=True)
+    perm = torch.randperm(urows.numel(), device="cuda", generator=torch.Generator("cuda").manual_seed(5))
+    where = torch.empty_like(perm); where[perm] = torch.arange(perm.numel(), device="cuda")
+    landing = torch.empty((urows.numel(), cfg.emb_size), dtype=torch.bfloat16, device="cuda")
+    shuffled = urows[perm].to(torch.int32).contiguous()
+    st = torch.cuda.current_stream().cuda_stream
+    assert _lib.lib.phx_shard_gather_rows(eng.table_local_ptr(), cfg.table_rows, _ptr(shuffled), shuffled.numel(),
+                                          cfg.emb_size, _ptr(landing), st) == 0
+    pos = where[inv].to(torch.int32).contiguous()
+    torch.cuda.synchronize()
+    got = _device_out(torch, cfg, B)
+    eng.rank_forward_rows_device(B, *dev, _ptr(landing), pos, *got); eng.sync()
+    assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+    eng.close()
+
+
+def test_sharded_ranker_world1_matches_plain_forward(torch):
+    """parallel.ShardedRanker end to end in a one-rank NCCL group (collectives, IPC landing buffer, dedup and the
+    copy path all run; the row traffic stays on the device): same outputs as the plain forward, for every exchange."""
+    import socket
+    import torch.distributed as dist
+    from x_algorithm_b200.parallel import ShardedRanker
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1,
+                            device_id=torch.device("cuda", 0))
+    try:
+        ocfg, w, rows_fn, eng = make_pair(max_batch=8)
+        cfg = eng.cfg
+        for i, (exchange, dedup) in enumerate((("copy", True), ("push", False), ("a2a", True))):
+            sr = ShardedRanker(eng, exchange=exchange, dedup=dedup)
+            for B in (8, 3):
+                b = po.make_batch(ocfg, B, seed=60 + i, ragged=B == 3)
+                dev = _device_batch(torch, b)
+                want, got = _device_out(torch, cfg, B), _device_out(torch, cfg, B)
+                eng.rank_device(B, *dev, *want); eng.sync()
+                sr.rank_device(B, *dev, *got); eng.sync()
+                assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1]), (exchange, B)
+            sr.close()
+        eng.close()
+    finally:
+        dist.destroy_process_group()

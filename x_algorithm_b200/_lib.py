@@ -62,6 +62,8 @@ SIGNATURES = {
     "phx_table_local_ptr": (C.c_int32, [_P, C.POINTER(_P)]),
     "phx_table_attach_peer_ptr": (C.c_int32, [_P, C.c_int32, _P]),
     "phx_rank_forward": (C.c_int32, [_P, C.POINTER(RankBatch), C.POINTER(RankOut)]),
+    "phx_rank_rows_device": (C.c_int32, [_P, C.POINTER(RankBatch), _P]),
+    "phx_rank_forward_rows_device": (C.c_int32, [_P, C.POINTER(RankBatch), _P, _P, C.POINTER(RankOut)]),
     "phx_rank_submit": (C.c_int32, [_P, C.POINTER(RankBatch), C.c_int32]),
     "phx_rank_collect": (C.c_int32, [_P, C.c_int32, C.POINTER(RankOut)]),
     "phx_rank_forward_device": (C.c_int32, [_P, C.POINTER(RankBatch), C.POINTER(RankOut)]),

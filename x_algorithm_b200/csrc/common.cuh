@@ -163,6 +163,11 @@ struct TokenBuildArgs {
   bf16* tokens;    // optional [B,T,D] unscaled gather-sum output
   int* hashes;     // optional [B,T,2H]
   int* seg;        // [B,T] 1 / -1 / 0
+  // row-sharded table, exchange done outside the kernel: rows_only = just write the [B,T,2H] unified-table rows to
+  // `hashes` and stop; landing / pos = take slot j of a token from landing[pos[tok*2H + j]] instead of the table
+  int rows_only = 0;
+  const bf16* landing = nullptr;
+  const int* pos = nullptr;
 };
 phx_status build_tokens_launch(const TokenBuildArgs& a, cudaStream_t stream, std::string& err);
 phx_status hash_ids_launch(const HashFamilyDev& fam, const long long* ids, long long n, int* out, cudaStream_t stream,

@@ -55,6 +55,7 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
     my_idx = hash_one(auth_id, a.author.scales[j], a.author.biases[j], a.author);
   }
   if (a.hashes && lane < 2 * H) a.hashes[tok * (2 * H) + lane] = my_idx;
+  if (a.rows_only) return;   // uniform over the grid: the caller only wants the rows (exchange outside the kernel)
   const int first_post_hash = __shfl_sync(0xffffffffu, my_idx, 0);
   if (lane == 0) a.seg[tok] = (first_post_hash != 0) ? (is_hist ? 1 : -1) : 0;
   int act = 0, srf = 0;
@@ -67,9 +68,15 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
   // every lane takes part in these shuffles (lanes whose column chunk lies past D skip the loop below, so a
   // shuffle inside the loop would leave the warp split across two different shuffle instructions)
   const bf16* rowp[2 * PHX_MAX_HASHES];
+  int my_pos = 0;   // exchanged rows: where slot `lane` of this token sits in the landing buffer
+  if (a.landing && lane < 2 * H) my_pos = a.pos[tok * (2 * H) + lane];
 #pragma unroll
-  for (int j = 0; j < 2 * PHX_MAX_HASHES; ++j)
-    rowp[j] = a.table.row_ptr(__shfl_sync(0xffffffffu, my_idx, j < 2 * H ? j : 0), a.D);
+  for (int j = 0; j < 2 * PHX_MAX_HASHES; ++j) {
+    const int jj = j < 2 * H ? j : 0;
+    const int idx = __shfl_sync(0xffffffffu, my_idx, jj);
+    const int ps = __shfl_sync(0xffffffffu, my_pos, jj);
+    rowp[j] = a.landing ? a.landing + (long long)ps * a.D : a.table.row_ptr(idx, a.D);
+  }
   float row_ss = 0.f;
   for (int col = lane * 8; col < a.D; col += 256) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};

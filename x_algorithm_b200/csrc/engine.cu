@@ -378,7 +378,8 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len) {
 }
 
 phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc, bf16* x_dst = nullptr, int* seg_dst = nullptr,
-                        cudaStream_t stream = nullptr, float* ss_dst = nullptr) {
+                        cudaStream_t stream = nullptr, float* ss_dst = nullptr, int* rows_out = nullptr,
+                        const bf16* landing = nullptr, const int* pos = nullptr) {
   long long ou, oi, oa, oip, tot;
   region_offsets(e->cfg, &ou, &oi, &oa, &oip, &tot);
   TokenBuildArgs ta;
@@ -395,6 +396,8 @@ phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc, 
   ta.seg = seg_dst ? seg_dst : e->seg;
   ta.row_ss = e->fused_norm ? (ss_dst ? ss_dst : e->rowss_a) : nullptr;
   ta.ss_slots = e->D / 64;
+  if (rows_out) { ta.rows_only = 1; ta.hashes = rows_out; }
+  ta.landing = landing; ta.pos = pos;
   if (stream) return build_tokens_launch(ta, stream, e->err);   // prefetch on the side stream: not profiled
   e->last_launches++;
   ProfScope ps(e, KC_TOKENS);
@@ -700,9 +703,10 @@ phx_status phx_set_blend(phx_engine* e, const phx_blend_spec* spec) {
 
 namespace {
 // the launches of one forward, in order, on the engine's stream
-phx_status enqueue_forward(phx_engine* e, const phx_rank_batch* bd, const phx_rank_out* od, int B, bool tokens_ready) {
+phx_status enqueue_forward(phx_engine* e, const phx_rank_batch* bd, const phx_rank_out* od, int B, bool tokens_ready,
+                           const bf16* landing = nullptr, const int* pos = nullptr) {
   phx_status s;
-  if (!tokens_ready && (s = build_tokens(e, bd, B, e->C))) return s;
+  if (!tokens_ready && (s = build_tokens(e, bd, B, e->C, nullptr, nullptr, nullptr, nullptr, nullptr, landing, pos))) return s;
   if ((s = run_trunk(e, B, e->T, e->S, e->S))) return s;
   HeadsArgs ha;
   ha.x = e->x; ha.final_gain = e->final_norm; ha.unembed_t = e->unembed_t;
@@ -771,6 +775,36 @@ phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* bd, cons
     if ((s = enqueue_forward(e, bd, od, B, tokens_ready))) return s;
   }
   e->graph_key_b = *bd; e->graph_key_o = *od; e->graph_key_valid = true;
+  PHX_CUDA_TRY(cudaEventRecord(e->ev1, e->stream), e->err);
+  if (e->ev_done[0]) { e->done_idx ^= 1; PHX_CUDA_TRY(cudaEventRecord(e->ev_done[e->done_idx], e->stream), e->err); }
+  return PHX_OK;
+}
+
+// Row-sharded table with the exchange done by the host side (parallel.ShardedRanker): first the unified-table rows
+// of every token slot, then, once their rows sit in a landing buffer, the forward from there.
+phx_status phx_rank_rows_device(phx_engine* e, const phx_rank_batch* bd, int32_t* rows_dev) {
+  if (!e || !bd || !rows_dev) return PHX_E_ARG;
+  if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
+  if (bd->batch <= 0 || bd->batch > e->cfg.max_batch) { e->err = "batch must be 1..max_batch"; return PHX_E_CAPACITY; }
+  cudaSetDevice(e->device);
+  return build_tokens(e, bd, bd->batch, e->C, nullptr, nullptr, e->stream, nullptr, rows_dev);
+}
+
+phx_status phx_rank_forward_rows_device(phx_engine* e, const phx_rank_batch* bd, const uint16_t* landing_dev, const int32_t* pos_dev,
+                                        const phx_rank_out* od) {
+  if (!e || !bd || !od || !landing_dev || !pos_dev) return PHX_E_ARG;
+  if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
+  if (bd->batch <= 0 || bd->batch > e->cfg.max_batch) { e->err = "batch must be 1..max_batch"; return PHX_E_CAPACITY; }
+  if (!params_complete(e, true)) return PHX_E_STATE;
+  cudaSetDevice(e->device);
+  const int B = bd->batch;
+  e->last_batch = B; e->last_launches = 0; e->prof_used = 0;
+  e->prefetch_valid = false;
+  e->graph_key_valid = false;
+  PHX_CUDA_TRY(cudaEventRecord(e->ev0, e->stream), e->err);
+  phx_status s;
+  if ((s = refresh_folded(e))) return s;
+  if ((s = enqueue_forward(e, bd, od, B, false, (const bf16*)landing_dev, pos_dev))) return s;
   PHX_CUDA_TRY(cudaEventRecord(e->ev1, e->stream), e->err);
   if (e->ev_done[0]) { e->done_idx ^= 1; PHX_CUDA_TRY(cudaEventRecord(e->ev_done[e->done_idx], e->stream), e->err); }
   return PHX_OK;

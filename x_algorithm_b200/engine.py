@@ -177,6 +177,19 @@ class PhoenixEngine:
         o = _lib.RankOut(_ptr(lp), _ptr(cont), _ptr(sc))
         self._check(lib.phx_rank_forward_device(self._h, C.byref(b), C.byref(o)))
 
+    def rank_rows_device(self, B, hp, ha, act, srf, cp, ca, rows):
+        """Unified-table rows of every token slot of the batch (int32 [B, S+C, 2*num_hashes]) -> `rows`; the first
+        half of a forward whose rows are exchanged between ranks (parallel.ShardedRanker)."""
+        b = self._batch_struct(B, hp, ha, act, srf, cp, ca)
+        self._check(lib.phx_rank_rows_device(self._h, C.byref(b), _ptr(rows)))
+
+    def rank_forward_rows_device(self, B, hp, ha, act, srf, cp, ca, landing_ptr, pos, lp, cont, sc=None):
+        """The forward with slot j of token t taken from row pos[t * 2*num_hashes + j] of the landing buffer at device
+        address `landing_ptr` instead of the table."""
+        b = self._batch_struct(B, hp, ha, act, srf, cp, ca)
+        o = _lib.RankOut(_ptr(lp), _ptr(cont), _ptr(sc))
+        self._check(lib.phx_rank_forward_rows_device(self._h, C.byref(b), landing_ptr, _ptr(pos), C.byref(o)))
+
     def rank_prefetch_device(self, B, hp, ha, act, srf, cp, ca):
         """Build the tokens of the batch the next rank_device call will carry, on a side stream (overlaps the
         forward enqueued right after this call; matters when the table is row-sharded over GPUs)."""

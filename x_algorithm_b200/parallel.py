@@ -156,13 +156,29 @@ class ShardedGatherSum:
 
     def __call__(self, family: int, ids, n: int, out):
         import torch
+        from . import _lib
+        from .engine import _ptr
+        assert n <= self.max_ids
+        # ids -> unified-table rows (engine stream), then everything else on torch's stream
+        self.eng.hash_ids_device(family, ids, n, self.rows)
+        self.eng.sync()
+        back_ptr = self.exchange_rows(n * self.H)
+        status = _lib.lib.phx_shard_sum_rows(back_ptr, _ptr(self.pos), n, self.H, self.width, _ptr(out),
+                                             torch.cuda.current_stream().cuda_stream)
+        if status != 0:
+            raise _lib.PhoenixError(status, _lib.lib.phx_global_error().decode())
+        return out
+
+    def exchange_rows(self, nreq: int) -> int:
+        """Fetch the rows `self.rows[:nreq]` names from their owners.  Returns the device address of the landing
+        buffer; request i's row sits at row `self.pos[i]` of it once the work queued on the current torch stream is
+        done.  The buffer is overwritten by the next call."""
+        import torch
         import torch.distributed as dist
         from . import _lib
         from .engine import _ptr
         lib = _lib.lib
-        assert n <= self.max_ids
         st = torch.cuda.current_stream().cuda_stream
-        nreq = n * self.H
         W = self.world
 
         def chk(status):
@@ -178,10 +194,6 @@ class ShardedGatherSum:
                 marks.append((name, ev))
 
         mark("start")
-        # ids -> unified-table rows (engine stream), then everything else on torch's stream
-        self.eng.hash_ids_device(family, ids, n, self.rows)
-        self.eng.sync()
-        mark("hash")
         counts = self.meta[:, 0].contiguous()
         if self.dedup:
             chk(lib.phx_shard_dedup(_ptr(self.rows), nreq, _ptr(self.table), self.table.numel(), _ptr(self.slot),
@@ -264,10 +276,40 @@ class ShardedGatherSum:
             dist.all_to_all_single(back, gathered, send_splits, recv_splits, group=self.group)
             mark("a2a_rows")
             back_ptr = _ptr(back)
-        chk(lib.phx_shard_sum_rows(back_ptr, _ptr(self.pos), n, self.H, self.width, _ptr(out), st))
-        mark("sum")
         if self.phase_ms is not None:
             torch.cuda.synchronize()
             for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
                 self.phase_ms[name] = self.phase_ms.get(name, 0.0) + a.elapsed_time(b)
-        return out
+        return back_ptr
+
+
+class ShardedRanker:
+    """Ranking forward over a unified table row-sharded across the ranks of a torch.distributed (NCCL) group, with
+    the rows fetched by the bulk exchange of `ShardedGatherSum` instead of per-row peer loads: the engine writes the
+    table row of every token slot, the ranks exchange rows, and the forward assembles its tokens from the landing
+    buffer.  Each rank ranks its own requests (data parallel); every rank must call `rank_device` the same number of
+    times (the exchange is collective).  Results equal `engine.rank_device` on an unsharded table bit for bit.
+    The reference splits its forward the same way around the row_emb exchange
+    (phoenix/xrex/cuda/row_emb/src/row_emb_comm.cc:655-743, phoenix/xrex/models/model_runner.py:4141-4222)."""
+
+    def __init__(self, engine, group=None, exchange: str = "copy", dedup: bool = True):
+        cfg = engine.cfg
+        self.eng = engine
+        self.slots = 2 * cfg.num_hashes                                  # post hashes then author hashes per token
+        self.tokens = cfg.max_batch * (cfg.history_len + cfg.num_candidates)
+        # one "id" of the exchange = num_hashes requests: two per token
+        self.xchg = ShardedGatherSum(engine, 2 * self.tokens, group=group, exchange=exchange, dedup=dedup)
+
+    def close(self):
+        self.xchg.close()
+
+    def rank_device(self, B, hp, ha, act, srf, cp, ca, lp, cont, sc=None):
+        """Arguments as for `PhoenixEngine.rank_device`; asynchronous like it (call `engine.sync()`)."""
+        import torch
+        cfg = self.eng.cfg
+        nreq = B * (cfg.history_len + cfg.num_candidates) * self.slots
+        self.eng.rank_rows_device(B, hp, ha, act, srf, cp, ca, self.xchg.rows)   # engine stream, behind the last forward
+        self.eng.sync()
+        landing = self.xchg.exchange_rows(nreq)
+        torch.cuda.current_stream().synchronize()                  # rows landed before the engine stream reads them
+        self.eng.rank_forward_rows_device(B, hp, ha, act, srf, cp, ca, landing, self.xchg.pos, lp, cont, sc)
