@@ -128,8 +128,10 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--table-log2", type=int, default=22, help="log2 buckets per hash region (smaller for profiling captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--tables", default="replicated", choices=["sharded", "replicated"],
-                    help="N > 1: one full table per GPU (it fits: 17 GB) or row-sharded over the ranks with peer loads over NVLink")
+    ap.add_argument("--tables", default="replicated", choices=["sharded", "exchange", "replicated"],
+                    help="N > 1: one full table per GPU (it fits: 17 GB); row-sharded over the ranks with per-row peer loads "
+                         "over NVLink (sharded); or row-sharded with the bulk row exchange before each forward (exchange: the "
+                         "device-timed steps; the host-buffer calls of the e2e leg still use peer loads)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -152,7 +154,8 @@ def main():
     wl = dict(WORKLOAD)
     wl["table_size"] = 1 << args.table_log2
     B = args.batch
-    sharded = world > 1 and args.tables == "sharded"
+    sharded = world > 1 and args.tables in ("sharded", "exchange")
+    exchange = sharded and args.tables == "exchange"
     cfg = px.PhoenixConfig(max_batch=B, table_world=world if sharded else 1, table_rank=rank if sharded else 0, **wl)
     eng = px.PhoenixEngine(cfg, local_rank)
     ocfg = po.ModelConfig(**wl)
@@ -177,9 +180,20 @@ def main():
     sc = torch.empty((B, C), dtype=torch.float64, device=dev)
     torch.cuda.synchronize()
 
+    ranker = None
+    if exchange:
+        from x_algorithm_b200.parallel import ShardedRanker
+        ranker = ShardedRanker(eng)
+
     def step(i):
         # forward of batch i, then (sharded tables) the token gather of batch i+1 on the engine's side stream,
         # which overlaps the forward just enqueued
+        if ranker is not None:
+            # forward of batch i from the rows exchanged during the previous step, then the exchange of batch i+1
+            # beside it
+            ranker.rank_device(B, *dbatches[i % n_rot], lp, cont, sc)
+            ranker.prefetch(B, *dbatches[(i + 1) % n_rot])
+            return
         eng.rank_device(B, *dbatches[i % n_rot], lp, cont, sc)
         if sharded:
             eng.rank_prefetch_device(B, *dbatches[(i + 1) % n_rot])
@@ -210,6 +224,16 @@ def main():
     step(0)
     prof = eng.profile_read()
     eng.profile_enable(False)
+    xphase = None
+    if ranker is not None:                      # device time of each phase of one exchange (rank 0's view)
+        for x in ranker.xchg:
+            x.phase_ms = {}
+        step(1)
+        eng.sync()
+        xphase = {}
+        for x in ranker.xchg:
+            xphase.update(x.phase_ms)
+            x.phase_ms = None
 
     # end to end through the host-buffer call: pinned staging + H2D + forward + D2H inside the timed region
     host_in = [px.RankInputs(b.hist_post_ids, b.hist_author_ids, b.hist_actions, b.hist_surfaces, b.cand_post_ids,
@@ -268,7 +292,8 @@ def main():
             vs_baseline=None, dtype="bf16", data="synthetic",
             config=dict(workload="phoenix_rank_bf16_D512_L8_H8x64_B256_S128_C512", batch_per_gpu=B, history=cfg.history_len,
                         candidates=C, table_rows=cfg.table_rows, parallelism=f"dp{world}",
-                        tables=("row-sharded over ranks, remote rows by NVLink peer loads" if sharded else "one full table per GPU"),
+                        tables=("row-sharded over ranks, rows fetched by the bulk exchange before each forward" if exchange else
+                                "row-sharded over ranks, remote rows by NVLink peer loads" if sharded else "one full table per GPU"),
                         l2="working set per step (activations 1.7 GB, table 17 GB) exceeds the 126 MB L2; 4 input batches rotated"),
             e2e=dict(value=total / (e2e_ms * 1e-3), unit="candidates/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
                      ms_per_step=e2e_ms / args.steps, api="phx_rank_submit / phx_rank_collect, two requests in flight",
@@ -286,12 +311,16 @@ def main():
             clocks=sampler.summary(),
             p50_latency=p50,
         )
+        if xphase is not None:
+            line["exchange_phase_ms"] = xphase
         if not args.no_cpu_baseline:
             cores = len(os.sched_getaffinity(0))
             rate, dt = cpu_oracle_rate(2)
             line["cpu_baseline"] = dict(value=rate, unit="candidates/s", cores=cores, kind="port",
                                         sample=f"2 requests x 512 candidates, one pass of the NumPy oracle ({dt:.1f} s)")
         print(json.dumps(line), flush=True)
+    if ranker is not None:
+        ranker.close()
     eng.close()
     if world > 1:
         dist.destroy_process_group()

@@ -172,11 +172,11 @@ phx_status phx_table_attach_peer_ptr(phx_engine* e, int32_t rank, const void* sh
 phx_status phx_rank_forward(phx_engine* e, const phx_rank_batch* batch_host, const phx_rank_out* out_host);
 /* Row-sharded table with the rows exchanged in bulk between the two halves of a forward (parallel.ShardedRanker):
  * phx_rank_rows_device writes the unified-table row of every token slot (int32 [B, S+C, 2*num_hashes]: post hashes,
- * then author hashes) and stops; after the exchange (phx_shard_*), phx_rank_forward_rows_device runs the forward
+ * then author hashes) on `stream` (a cudaStream_t; NULL = the engine's stream) and stops; after the exchange (phx_shard_*), phx_rank_forward_rows_device runs the forward
  * taking slot j of token t from landing_dev[pos_dev[t * 2*num_hashes + j]] (bf16 rows of emb_size) instead of the
  * table.  Same results as phx_rank_forward_device on an unsharded table, bit for bit.  The reference does the same
  * split around its row_emb exchange (row_emb_comm.cc:655-743). */
-phx_status phx_rank_rows_device(phx_engine* e, const phx_rank_batch* batch_dev, int32_t* rows_dev);
+phx_status phx_rank_rows_device(phx_engine* e, const phx_rank_batch* batch_dev, int32_t* rows_dev, void* stream);
 phx_status phx_rank_forward_rows_device(phx_engine* e, const phx_rank_batch* batch_dev, const uint16_t* landing_dev,
                                         const int32_t* pos_dev, const phx_rank_out* out_dev);
 /* Two-deep pipeline of host-buffer requests: phx_rank_submit copies the inputs into the slot's pinned block and
@@ -200,10 +200,12 @@ phx_status phx_sync(phx_engine* e);
 /* Time of the last phx_rank_forward_device / phx_user_tower_device call on the engine's stream,
  * measured with CUDA events (milliseconds). */
 phx_status phx_last_device_ms(phx_engine* e, float* ms);
-/* Device-side timing on the engine's stream: phx_mark records event `slot` (0..3) behind the work
- * queued so far, phx_elapsed_ms waits for `to_slot` and returns the time between two marks.  Replaces
+/* Device-side timing on the engine's stream: phx_mark records event `slot` (0..7) behind the work
+ * queued so far, phx_elapsed_ms waits for `to_slot` and returns the time between two marks, phx_mark_wait
+ * blocks the host until the work in front of a mark is done (a mark never recorded is done).  Replaces
  * the reference's per-step latency metrics (model_runner.py:3089-3092, 4176-4179). */
 phx_status phx_mark(phx_engine* e, int32_t slot);
+phx_status phx_mark_wait(phx_engine* e, int32_t slot);
 phx_status phx_elapsed_ms(phx_engine* e, int32_t from_slot, int32_t to_slot, float* ms);
 /* Per-kernel-class timing of the last forward (CUDA events around every launch while enabled).
  * Classes: 0 token build (hash + gather-sum), 1 RMSNorm, 2 GEMM, 3 qk-norm/RoPE, 4 attention,

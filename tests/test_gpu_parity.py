@@ -549,12 +549,17 @@ def test_sharded_ranker_world1_matches_plain_forward(torch):
         cfg = eng.cfg
         for i, (exchange, dedup) in enumerate((("copy", True), ("push", False), ("a2a", True))):
             sr = ShardedRanker(eng, exchange=exchange, dedup=dedup)
-            for B in (8, 3):
-                b = po.make_batch(ocfg, B, seed=60 + i, ragged=B == 3)
-                dev = _device_batch(torch, b)
+            nxt = None
+            for j, B in enumerate((8, 3, 8, 5)):           # prefetched and inline exchanges, both buffer sets
+                dev = nxt or _device_batch(torch, po.make_batch(ocfg, B, seed=60 + 10 * i + j, ragged=B == 3))
                 want, got = _device_out(torch, cfg, B), _device_out(torch, cfg, B)
                 eng.rank_device(B, *dev, *want); eng.sync()
-                sr.rank_device(B, *dev, *got); eng.sync()
+                sr.rank_device(B, *dev, *got)
+                nxt = None
+                if j == 1:                                   # exchange the next batch beside this forward
+                    nxt = _device_batch(torch, po.make_batch(ocfg, 8, seed=99 + i, ragged=True))
+                    sr.prefetch(8, *nxt)
+                eng.sync()
                 assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1]), (exchange, B)
             sr.close()
         eng.close()

@@ -62,7 +62,7 @@ SIGNATURES = {
     "phx_table_local_ptr": (C.c_int32, [_P, C.POINTER(_P)]),
     "phx_table_attach_peer_ptr": (C.c_int32, [_P, C.c_int32, _P]),
     "phx_rank_forward": (C.c_int32, [_P, C.POINTER(RankBatch), C.POINTER(RankOut)]),
-    "phx_rank_rows_device": (C.c_int32, [_P, C.POINTER(RankBatch), _P]),
+    "phx_rank_rows_device": (C.c_int32, [_P, C.POINTER(RankBatch), _P, _P]),
     "phx_rank_forward_rows_device": (C.c_int32, [_P, C.POINTER(RankBatch), _P, _P, C.POINTER(RankOut)]),
     "phx_rank_submit": (C.c_int32, [_P, C.POINTER(RankBatch), C.c_int32]),
     "phx_rank_collect": (C.c_int32, [_P, C.c_int32, C.POINTER(RankOut)]),
@@ -72,6 +72,7 @@ SIGNATURES = {
     "phx_last_device_ms": (C.c_int32, [_P, C.POINTER(C.c_float)]),
     "phx_last_launch_count": (C.c_int32, [_P, C.POINTER(C.c_int32)]),
     "phx_mark": (C.c_int32, [_P, C.c_int32]),
+    "phx_mark_wait": (C.c_int32, [_P, C.c_int32]),
     "phx_elapsed_ms": (C.c_int32, [_P, C.c_int32, C.c_int32, C.POINTER(C.c_float)]),
     "phx_profile_enable": (C.c_int32, [_P, C.c_int32]),
     "phx_profile_read": (C.c_int32, [_P, C.POINTER(C.c_float), C.POINTER(C.c_int32)]),

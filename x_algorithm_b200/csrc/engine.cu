@@ -146,7 +146,7 @@ struct phx_engine {
   bool profile = false;
   std::vector<std::pair<int, std::pair<cudaEvent_t, cudaEvent_t>>> prof_events;  // (class, (start, stop))
   size_t prof_used = 0;
-  cudaEvent_t marks[4] = {nullptr, nullptr, nullptr, nullptr};
+  cudaEvent_t marks[8] = {};
 };
 
 namespace {
@@ -782,12 +782,12 @@ phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* bd, cons
 
 // Row-sharded table with the exchange done by the host side (parallel.ShardedRanker): first the unified-table rows
 // of every token slot, then, once their rows sit in a landing buffer, the forward from there.
-phx_status phx_rank_rows_device(phx_engine* e, const phx_rank_batch* bd, int32_t* rows_dev) {
+phx_status phx_rank_rows_device(phx_engine* e, const phx_rank_batch* bd, int32_t* rows_dev, void* stream) {
   if (!e || !bd || !rows_dev) return PHX_E_ARG;
   if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
   if (bd->batch <= 0 || bd->batch > e->cfg.max_batch) { e->err = "batch must be 1..max_batch"; return PHX_E_CAPACITY; }
   cudaSetDevice(e->device);
-  return build_tokens(e, bd, bd->batch, e->C, nullptr, nullptr, e->stream, nullptr, rows_dev);
+  return build_tokens(e, bd, bd->batch, e->C, nullptr, nullptr, stream ? (cudaStream_t)stream : e->stream, nullptr, rows_dev);
 }
 
 phx_status phx_rank_forward_rows_device(phx_engine* e, const phx_rank_batch* bd, const uint16_t* landing_dev, const int32_t* pos_dev,
@@ -1036,15 +1036,22 @@ phx_status phx_profile_read(phx_engine* e, float* ms_by_class, int32_t* launches
 }
 
 phx_status phx_mark(phx_engine* e, int32_t slot) {
-  if (!e || slot < 0 || slot > 3) return PHX_E_ARG;
+  if (!e || slot < 0 || slot > 7) return PHX_E_ARG;
   cudaSetDevice(e->device);
   if (!e->marks[slot]) PHX_CUDA_TRY(cudaEventCreate(&e->marks[slot]), e->err);
   PHX_CUDA_TRY(cudaEventRecord(e->marks[slot], e->stream), e->err);
   return PHX_OK;
 }
 
+phx_status phx_mark_wait(phx_engine* e, int32_t slot) {
+  if (!e || slot < 0 || slot > 7) return PHX_E_ARG;
+  if (!e->marks[slot]) return PHX_OK;   // never recorded: nothing to wait for
+  PHX_CUDA_TRY(cudaEventSynchronize(e->marks[slot]), e->err);
+  return PHX_OK;
+}
+
 phx_status phx_elapsed_ms(phx_engine* e, int32_t from_slot, int32_t to_slot, float* ms) {
-  if (!e || !ms || from_slot < 0 || from_slot > 3 || to_slot < 0 || to_slot > 3 || !e->marks[from_slot] || !e->marks[to_slot]) return PHX_E_ARG;
+  if (!e || !ms || from_slot < 0 || from_slot > 7 || to_slot < 0 || to_slot > 7 || !e->marks[from_slot] || !e->marks[to_slot]) return PHX_E_ARG;
   PHX_CUDA_TRY(cudaEventSynchronize(e->marks[to_slot]), e->err);
   PHX_CUDA_TRY(cudaEventElapsedTime(ms, e->marks[from_slot], e->marks[to_slot]), e->err);
   return PHX_OK;

@@ -177,11 +177,11 @@ class PhoenixEngine:
         o = _lib.RankOut(_ptr(lp), _ptr(cont), _ptr(sc))
         self._check(lib.phx_rank_forward_device(self._h, C.byref(b), C.byref(o)))
 
-    def rank_rows_device(self, B, hp, ha, act, srf, cp, ca, rows):
+    def rank_rows_device(self, B, hp, ha, act, srf, cp, ca, rows, stream=None):
         """Unified-table rows of every token slot of the batch (int32 [B, S+C, 2*num_hashes]) -> `rows`; the first
         half of a forward whose rows are exchanged between ranks (parallel.ShardedRanker)."""
         b = self._batch_struct(B, hp, ha, act, srf, cp, ca)
-        self._check(lib.phx_rank_rows_device(self._h, C.byref(b), _ptr(rows)))
+        self._check(lib.phx_rank_rows_device(self._h, C.byref(b), _ptr(rows), stream))
 
     def rank_forward_rows_device(self, B, hp, ha, act, srf, cp, ca, landing_ptr, pos, lp, cont, sc=None):
         """The forward with slot j of token t taken from row pos[t * 2*num_hashes + j] of the landing buffer at device
@@ -215,6 +215,9 @@ class PhoenixEngine:
 
     def mark(self, slot: int):
         self._check(lib.phx_mark(self._h, slot))
+
+    def mark_wait(self, slot: int):
+        self._check(lib.phx_mark_wait(self._h, slot))
 
     def elapsed_ms(self, a: int, b: int) -> float:
         ms = C.c_float()

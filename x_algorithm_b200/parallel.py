@@ -297,19 +297,49 @@ class ShardedRanker:
         self.eng = engine
         self.slots = 2 * cfg.num_hashes                                  # post hashes then author hashes per token
         self.tokens = cfg.max_batch * (cfg.history_len + cfg.num_candidates)
-        # one "id" of the exchange = num_hashes requests: two per token
-        self.xchg = ShardedGatherSum(engine, 2 * self.tokens, group=group, exchange=exchange, dedup=dedup)
+        # one "id" of the exchange = num_hashes requests: two per token.  Two sets of buffers: the exchange of the
+        # next batch fills one while the forward reads the other.
+        self.xchg = [ShardedGatherSum(engine, 2 * self.tokens, group=group, exchange=exchange, dedup=dedup)
+                     for _ in range(2)]
+        self._last = 1            # buffer set the latest forward reads
+        self._ready = None        # (key of the prefetched batch, buffer set, landing address)
+
+    MARK0 = 6                     # engine marks 6 / 7: behind the forward that last read buffer set 0 / 1
 
     def close(self):
-        self.xchg.close()
+        for x in self.xchg:
+            x.close()
+
+    @staticmethod
+    def _key(B, batch):
+        return (B,) + tuple(t.data_ptr() for t in batch)
+
+    def _fetch(self, buf, B, batch):
+        import torch
+        cfg, x = self.eng.cfg, self.xchg[buf]
+        self.eng.mark_wait(self.MARK0 + buf)       # the forward that read this set (two forwards ago) is done
+        cur = torch.cuda.current_stream()
+        self.eng.rank_rows_device(B, *batch, x.rows, stream=cur.cuda_stream)
+        landing = x.exchange_rows(B * (cfg.history_len + cfg.num_candidates) * self.slots)
+        cur.synchronize()                          # rows landed before the engine's stream reads them
+        return landing
+
+    def prefetch(self, B, hp, ha, act, srf, cp, ca):
+        """Exchange the rows of the batch the next `rank_device` call will carry (the same tensors, unchanged until
+        then).  Runs on the current torch stream beside the forward queued on the engine's stream; collective."""
+        batch = (hp, ha, act, srf, cp, ca)
+        buf = self._last ^ 1
+        self._ready = (self._key(B, batch), buf, self._fetch(buf, B, batch))
 
     def rank_device(self, B, hp, ha, act, srf, cp, ca, lp, cont, sc=None):
         """Arguments as for `PhoenixEngine.rank_device`; asynchronous like it (call `engine.sync()`)."""
-        import torch
-        cfg = self.eng.cfg
-        nreq = B * (cfg.history_len + cfg.num_candidates) * self.slots
-        self.eng.rank_rows_device(B, hp, ha, act, srf, cp, ca, self.xchg.rows)   # engine stream, behind the last forward
-        self.eng.sync()
-        landing = self.xchg.exchange_rows(nreq)
-        torch.cuda.current_stream().synchronize()                  # rows landed before the engine stream reads them
-        self.eng.rank_forward_rows_device(B, hp, ha, act, srf, cp, ca, landing, self.xchg.pos, lp, cont, sc)
+        batch = (hp, ha, act, srf, cp, ca)
+        if self._ready is not None and self._ready[0] == self._key(B, batch):
+            _, buf, landing = self._ready
+        else:
+            buf = self._last ^ 1
+            landing = self._fetch(buf, B, batch)
+        self._ready = None
+        self.eng.rank_forward_rows_device(B, *batch, landing, self.xchg[buf].pos, lp, cont, sc)
+        self.eng.mark(self.MARK0 + buf)
+        self._last = buf
