@@ -38,9 +38,12 @@ def flops_per_request(c) -> dict:
     D, F, T = c["emb_size"], int(c["widening_factor"] * c["emb_size"]), c["history_len"] + c["num_candidates"]
     HD = c["num_q_heads"] * c["key_size"]
     QW = (c["num_q_heads"] + 2 * c["num_kv_heads"]) * c["key_size"]
-    gemm = c["num_layers"] * (2 * T * D * QW + 2 * T * HD * D + 4 * T * D * F)
     S, C = c["history_len"], c["num_candidates"]
-    attn = c["num_layers"] * 4 * c["key_size"] * c["num_q_heads"] * (S * S + C * (S + 1))
+    L, n_tail = c["num_layers"], c.get("num_candidate_only_layers", 0)
+    # a candidate-only tail layer projects QKV for every row but runs the out-projection and the FFN over the
+    # candidate rows only, and its attention has no history queries
+    gemm = L * 2 * T * D * QW + ((L - n_tail) * T + n_tail * C) * (2 * HD * D + 4 * D * F)
+    attn = 4 * c["key_size"] * c["num_q_heads"] * ((L - n_tail) * S * S + L * C * (S + 1))
     return dict(gemm=gemm, attn=attn)
 
 
@@ -132,6 +135,9 @@ def main():
                     help="N > 1: one full table per GPU (it fits: 17 GB); row-sharded over the ranks with per-row peer loads "
                          "over NVLink (sharded); or row-sharded with the bulk row exchange before each forward (exchange: the "
                          "device-timed steps; the host-buffer calls of the e2e leg still use peer loads)")
+    ap.add_argument("--candidate-only-layers", type=int, default=0,
+                    help="tail layers that update the candidate rows only (the reference's production ranker uses 2; "
+                         "BASELINE config 1 has none, so a line measured with this flag is not the headline workload)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -153,6 +159,8 @@ def main():
 
     wl = dict(WORKLOAD)
     wl["table_size"] = 1 << args.table_log2
+    if args.candidate_only_layers:
+        wl["num_candidate_only_layers"] = args.candidate_only_layers
     B = args.batch
     sharded = world > 1 and args.tables in ("sharded", "exchange")
     exchange = sharded and args.tables == "exchange"
@@ -292,6 +300,7 @@ def main():
             vs_baseline=None, dtype="bf16", data="synthetic",
             config=dict(workload="phoenix_rank_bf16_D512_L8_H8x64_B256_S128_C512", batch_per_gpu=B, history=cfg.history_len,
                         candidates=C, table_rows=cfg.table_rows, parallelism=f"dp{world}",
+                        **({"candidate_only_layers": args.candidate_only_layers} if args.candidate_only_layers else {}),
                         tables=("row-sharded over ranks, rows fetched by the bulk exchange before each forward" if exchange else
                                 "row-sharded over ranks, remote rows by NVLink peer loads" if sharded else "one full table per GPU"),
                         l2="working set per step (activations 1.7 GB, table 17 GB) exceeds the 126 MB L2; 4 input batches rotated"),

@@ -230,6 +230,7 @@ class ModelConfig:
     rope_base: int = 10000
     dwell_norm_scale: float = 30.0
     compute: str = "bf16"          # "bf16" | "fp32"
+    num_candidate_only_layers: int = 0   # tail layers that leave the history rows frozen (transformer.py:789-871)
 
     @property
     def ffn_size(self) -> int:
@@ -417,13 +418,24 @@ def gelu_tanh(x: np.ndarray) -> np.ndarray:
 
 
 def transformer_trunk(cfg: ModelConfig, w: Dict[str, np.ndarray], x: np.ndarray, segment_ids: np.ndarray,
-                      positions: np.ndarray, mask: np.ndarray, taps: Optional[dict] = None) -> np.ndarray:
+                      positions: np.ndarray, mask: np.ndarray, taps: Optional[dict] = None,
+                      frozen_front: int = 0) -> np.ndarray:
     """L x DecoderLayer (transformer.py:461-618): x + out(attn(rope(qknorm(qkv(norm(x)))))),
     then x + down(gelu(up(norm(x)))).  x [B,T,D] float32 (bf16-representable in bf16 mode)."""
     rnd = _Rounder(cfg.compute)
     sm_scale = math.sqrt(128.0) / cfg.key_size  # scaling.py:46-47
     x = rnd(x)  # transformer.py:726
+    # Candidate-only tail (transformer.py:789-871, 908-941): the last n layers run as usual, then every row in front
+    # of the candidates is put back to its value at the tail's entrance (`split_history_and_candidates`, 829-836, splits
+    # by position; the layer's keys / values of the history are projected from those frozen rows, layers.py:608-619).
+    # Padded candidate slots are not specified by the reference (its two tail paths treat them differently).
+    # `frozen_front` = number of rows in front of the candidates (0: no tail, e.g. the user tower).
+    n_front = frozen_front if cfg.num_candidate_only_layers else 0
+    tail_start = cfg.num_layers - cfg.num_candidate_only_layers
+    frozen = None
     for l in range(cfg.num_layers):
+        if n_front and l == tail_start:
+            frozen = x[:, :n_front].copy()
         p = f"layer{l}."
         h = rnd(rms_normalize(x, w[p + "pre_attn_norm"], cfg.rms_eps))
         qkv = rnd(h @ w[p + "w_qkv"])
@@ -450,6 +462,8 @@ def transformer_trunk(cfg: ModelConfig, w: Dict[str, np.ndarray], x: np.ndarray,
         if cfg.primer_norm:
             h_ffn = rnd(rms_normalize(h_ffn, w[p + "post_ffn_norm"], cfg.rms_eps))
         x = rnd(x + h_ffn)
+        if frozen is not None:
+            x = np.concatenate([frozen, x[:, n_front:]], axis=1)
     return x
 
 
@@ -542,7 +556,7 @@ def rank_forward(cfg: ModelConfig, w: Dict[str, np.ndarray], table_rows_fn, batc
     idx = np.arange(T)[None, :]
     positions = np.where(idx >= S, S, idx).astype(np.float32).repeat(x.shape[0], 0)  # 6159-6167
     mask = ranker_mask(seg)
-    hfin = transformer_trunk(cfg, w, x, seg, positions, mask, taps)
+    hfin = transformer_trunk(cfg, w, x, seg, positions, mask, taps, frozen_front=cfg.history_len)
     hfin = rnd(rms_normalize(hfin, w["final_norm"], cfg.rms_eps))  # 4792-4796
     cand = hfin[:, S:, :]
     logits = rnd(cand @ w["unembed"])                       # decode, 3557-3560

@@ -22,7 +22,8 @@ def make_pair(max_batch=4, table_seed=7, **kw):
         num_surfaces=ocfg.num_surfaces, num_hashes=ocfg.num_hashes, table_size=ocfg.table_size,
         rotary=ocfg.rotary, qk_norm=ocfg.qk_norm, primer_norm=ocfg.primer_norm, attn_logit_cap=ocfg.attn_logit_cap,
         attn_logit_cap_method=ocfg.attn_logit_cap_method, final_logit_cap=ocfg.final_logit_cap,
-        rms_eps=ocfg.rms_eps, rope_base=float(ocfg.rope_base), dwell_norm_scale=ocfg.dwell_norm_scale)
+        rms_eps=ocfg.rms_eps, rope_base=float(ocfg.rope_base), dwell_norm_scale=ocfg.dwell_norm_scale,
+        num_candidate_only_layers=ocfg.num_candidate_only_layers)
     eng = px.PhoenixEngine(pcfg, 0)
     eng.load_weights(w)
     eng.table_fill_synthetic(table_seed, amp)

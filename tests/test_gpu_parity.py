@@ -171,6 +171,48 @@ def test_rank_forward_options_vs_oracle(torch, opts):
     eng.close()
 
 
+@pytest.mark.parametrize("opts,attn", [
+    (dict(num_candidate_only_layers=1), None),
+    (dict(num_candidate_only_layers=2), None),
+    (dict(num_candidate_only_layers=1, qk_norm=True), None),
+    (dict(num_candidate_only_layers=1, primer_norm=True), None),
+    (dict(num_candidate_only_layers=2, emb_size=256, num_q_heads=4, num_kv_heads=4, key_size=64, history_len=48,
+          num_candidates=24, num_layers=3), "strip"),
+    (dict(num_candidate_only_layers=2, emb_size=256, num_q_heads=4, num_kv_heads=4, key_size=64, history_len=160,
+          num_candidates=200, num_layers=3), None),
+    (dict(num_candidate_only_layers=3, emb_size=128, num_q_heads=1, num_kv_heads=1, key_size=128, history_len=40,
+          num_candidates=24, num_layers=3), None)])
+def test_candidate_only_tail_layers_vs_oracle(torch, monkeypatch, opts, attn):
+    """The last n layers update the candidate rows only (transformer.py:789-871): history rows stay as the main layers
+    left them and every tail layer takes its history keys / values from those rows."""
+    if attn:
+        monkeypatch.setenv("PHX_ATTN", attn)
+    ocfg, w, rows_fn, eng = make_pair(max_batch=5, **opts)
+    for batch, ragged in ((5, True), (2, False)):
+        b, taps, lp, cont, logits, spec, res = _forward_case(ocfg, w, rows_fn, eng, batch, ragged)
+        valid = b.cand_post_ids != 0
+        assert rel_l2(res.log_probs[valid], lp[valid]) < TOL, opts
+        assert rel_l2(res.continuous[valid], cont[valid]) < TOL, opts
+        # history rows stay as the main layers left them: the first B * S rows of the residual stream (split layout:
+        # history block first) equal the output of the model cut after its main layers, not the full model's
+        import dataclasses
+        S, L, n = ocfg.history_len, ocfg.num_layers, ocfg.num_candidate_only_layers
+        hid = eng.debug_read("hidden", (batch * S, ocfg.emb_size), np.uint16).reshape(batch, S, -1)
+        hid = po.rms_normalize(po.bf16_from_bits(hid), w["final_norm"], ocfg.rms_eps)
+        hv = b.hist_post_ids != 0
+        if L > n:
+            t_main = {}
+            po.rank_forward(dataclasses.replace(ocfg, num_layers=L - n, num_candidate_only_layers=0), w, rows_fn, b, t_main)
+            want_hist = t_main["hfin"][:, :S]
+        else:   # every layer is a tail layer: the history rows are still the input tokens
+            want_hist = po.rms_normalize(taps["x0"][:, :S], w["final_norm"], ocfg.rms_eps)
+        t_full = {}
+        po.rank_forward(dataclasses.replace(ocfg, num_candidate_only_layers=0), w, rows_fn, b, t_full)
+        err_main, err_full = rel_l2(hid[hv], want_hist[hv]), rel_l2(hid[hv], t_full["hfin"][:, :S][hv])
+        assert err_main < TOL and err_main < 0.3 * err_full, (opts, err_main, err_full)
+    eng.close()
+
+
 def test_simt_gemm_path_matches_tcgen05(torch, monkeypatch):
     """The cross-check GEMM and the tcgen05 GEMM give the same forward (accumulation order aside)."""
     ocfg, w, rows_fn, eng = make_pair(max_batch=4)

@@ -199,3 +199,39 @@ def test_rank_forward_properties():
     _, _, l16 = po.rank_forward(cfg16, w, rows, b)
     rel = np.linalg.norm(l16 - logits) / np.linalg.norm(logits)
     assert rel < 2e-2, rel
+
+
+def test_candidate_only_tail_layers_restated_layer_by_layer():
+    """Candidate-only tail (transformer.py:789-871): the oracle's trunk with `num_candidate_only_layers` equals the
+    layers run one at a time, every tail layer fed [history rows as they left the main layers, current candidate
+    rows] with only its candidate rows carried on."""
+    import dataclasses
+    cfg = po.ModelConfig(compute="fp32", num_layers=3, num_candidate_only_layers=2)
+    w = po.make_weights(cfg, 0)
+    rows = lambda idx: po.synthetic_table_rows(idx, cfg.emb_size, 7, 1.0 / math.sqrt(cfg.emb_size))
+    b = po.make_batch(cfg, 2, seed=4, ragged=True)
+    taps = {}
+    lp, cont, _ = po.rank_forward(cfg, w, rows, b, taps)
+    S = cfg.history_len
+    x, pad, _ = po.build_tokens(cfg, w, rows, b)
+    seg = po.attention_segment_ids(pad, S)
+    T = x.shape[1]
+    idx = np.arange(T)[None, :]
+    positions = np.where(idx >= S, S, idx).astype(np.float32).repeat(x.shape[0], 0)
+    mask = po.ranker_mask(seg)
+    one = dataclasses.replace(cfg, num_layers=1, num_candidate_only_layers=0)
+
+    def layer(l, xin):
+        wl = {k.replace(f"layer{l}.", "layer0."): v for k, v in w.items() if k.startswith(f"layer{l}.")}
+        return po.transformer_trunk(one, wl, xin, seg, positions, mask)
+
+    h = layer(0, x)
+    hist, cand = h[:, :S], h[:, S:]
+    for l in (1, 2):
+        cand = layer(l, np.concatenate([hist, cand], axis=1))[:, S:]
+    np.testing.assert_array_equal(taps["hfin"][:, S:],
+                                  po.rms_normalize(np.concatenate([hist, cand], axis=1), w["final_norm"], cfg.rms_eps)[:, S:])
+    # and the tail changes the result: with every layer updating every row the candidates come out differently
+    lp_full, _, _ = po.rank_forward(dataclasses.replace(cfg, num_candidate_only_layers=0), w, rows, b)
+    valid = b.cand_post_ids != 0
+    assert not np.allclose(lp[valid], lp_full[valid], rtol=1e-4, atol=1e-6)

@@ -28,7 +28,8 @@ class ModelConfig(C.Structure):
         "rotary", "qk_norm", "primer_norm", "cap_method")] + [(n, C.c_float) for n in (
         "attn_logit_cap", "final_logit_cap", "rms_eps", "rope_base", "dwell_norm_scale")] + [
         ("user", HashFamily), ("item", HashFamily), ("author", HashFamily), ("ip", HashFamily),
-        ("table_world", C.c_int32), ("table_rank", C.c_int32)]
+        ("table_world", C.c_int32), ("table_rank", C.c_int32), ("num_candidate_only_layers", C.c_int32),
+        ("_pad0", C.c_int32)]
 
 
 class BlendSpec(C.Structure):

@@ -76,6 +76,7 @@ class PhoenixConfig:
     dwell_norm_scale: float = 30.0
     table_world: int = 1        # row-shard the unified table over this many engines (one per GPU)
     table_rank: int = 0
+    num_candidate_only_layers: int = 0   # tail layers that update candidate rows only (transformer.py:789-871)
 
     @property
     def ffn_size(self) -> int:  # phoenix/xrex/utils/utils.py:37-52
@@ -110,4 +111,5 @@ class PhoenixConfig:
         u, i, a, p = self.families()
         c.user, c.item, c.author, c.ip = u.to_c(), i.to_c(), a.to_c(), p.to_c()
         c.table_world, c.table_rank = int(self.table_world), int(self.table_rank)
+        c.num_candidate_only_layers = int(self.num_candidate_only_layers)
         return c

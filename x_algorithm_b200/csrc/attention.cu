@@ -77,11 +77,13 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
   const float csc = CAP ? 1.0f : a.sm_scale * 1.4426950408889634f;
 
   const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * QROWS;
+  if (q0 + QROWS <= a.q_start) return;   // candidate-only layer: these query rows are not wanted
   const int hk = h / (a.Hq / a.Hkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int T = a.T;
-  const long long tok0 = (long long)b * T;
+  // token row of position t of this request (plain or split layout)
+  auto trow = [&](int t) -> long long { return token_row(a.split, a.B, a.hist_len, T, b, t); };
   const int n_hist = a.hist_len < T ? a.hist_len : T;
   const int n_blocks = (n_hist + KB - 1) / KB;
   const bool has_cand = (q0 + QROWS > n_hist);     // rows at or past hist_len may be candidates
@@ -96,13 +98,13 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
       const int kr = c / CH, dc = (c % CH) * 8;
       const int key = blk * KB + kr;
       const bool ok = key < n_hist;
-      const long long tok = tok0 + (ok ? key : 0);
+      const long long tok = trow(ok ? key : 0);
       cp16((uint32_t)__cvta_generic_to_shared(dk + kr * LD + dc), kbase + tok * a.k_tok_stride + dc, ok);
       cp16((uint32_t)__cvta_generic_to_shared(dv + kr * LD + dc), vbase + tok * a.v_tok_stride + dc, ok);
     }
     if (threadIdx.x < KB) {  // warps 0 and 1
       const int key = blk * KB + threadIdx.x;
-      const int ok = (key < n_hist) && (a.seg[tok0 + key] == 1);
+      const int ok = (key < n_hist) && (a.seg[trow(key)] == 1);
       skey_ok[buf * KB + threadIdx.x] = ok;
       const int all32 = __all_sync(0xffffffffu, ok);
       if ((threadIdx.x & 31) == 0) sall_ok[buf * 2 + (threadIdx.x >> 5)] = all32;
@@ -113,7 +115,7 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
   for (int c = threadIdx.x; c < QROWS * CH; c += ATT_THREADS) {
     const int r = c / CH, dc = (c % CH) * 8;
     const bool ok = (q0 + r) < T;
-    const long long tok = tok0 + (ok ? q0 + r : 0);
+    const long long tok = trow(ok ? q0 + r : 0);
     cp16((uint32_t)__cvta_generic_to_shared(sq + r * LD + dc), a.q + tok * a.q_tok_stride + (long long)h * a.q_head_stride + dc, ok);
     if (has_cand) {
       cp16((uint32_t)__cvta_generic_to_shared(sks + r * LD + dc), kbase + tok * a.k_tok_stride + dc, ok);
@@ -128,7 +130,7 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
   const int rq[2] = {q0 + warp * 16 + g, q0 + warp * 16 + g + 8};
   int segq[2];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) segq[i] = (rq[i] < T) ? a.seg[tok0 + rq[i]] : 0;
+  for (int i = 0; i < 2; ++i) segq[i] = (rq[i] < T) ? a.seg[trow(rq[i])] : 0;
 
   cp_wait<1>();
   __syncthreads();
@@ -297,7 +299,7 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
     const int r = c / CH, dc = (c % CH) * 8;
     const int row = q0 + warp * 16 + r;
     if (row < T)
-      *reinterpret_cast<uint4*>(a.out + ((tok0 + row) * a.Hq + h) * DH + dc) =
+      *reinterpret_cast<uint4*>(a.out + (trow(row) * a.Hq + h) * DH + dc) =
           *reinterpret_cast<const uint4*>(sq + (warp * 16 + r) * LD + dc);
   }
 }
@@ -349,7 +351,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) ranker_attention_strip_kernel(
   const int hk = h / (a.Hq / a.Hkv);
   const int g = lane >> 2, t4 = lane & 3;
   const int T = a.T;
-  const long long tok0 = (long long)b * T;
+  // token row of position t of this request (plain or split layout)
+  auto trow = [&](int t) -> long long { return token_row(a.split, a.B, a.hist_len, T, b, t); };
   const int n_hist = a.hist_len < T ? a.hist_len : T;
   const int n_blocks = (n_hist + KB - 1) / KB;
   const int n_tiles = (T + QROWS - 1) / QROWS;
@@ -363,7 +366,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) ranker_attention_strip_kernel(
     for (int k = 0; k < 4; ++k) {
       const int c = lane + 32 * k, r = c >> 3, ch = c & 7;
       const bool ok = (r0 + r) < T;
-      const long long tok = tok0 + (ok ? r0 + r : 0);
+      const long long tok = trow(ok ? r0 + r : 0);
       cp16((uint32_t)__cvta_generic_to_shared(dst + swz(r, ch)), qbase + tok * a.q_tok_stride + ch * 8, ok);
     }
   };
@@ -377,7 +380,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) ranker_attention_strip_kernel(
     for (int k = 0; k < 4; ++k) {
       const int c = lane + 32 * k, r = c >> 3, ch = c & 7;
       const bool ok = (r0 + r) < T;
-      const long long tok = tok0 + (ok ? r0 + r : 0);
+      const long long tok = trow(ok ? r0 + r : 0);
       cp16((uint32_t)__cvta_generic_to_shared(wks + swz(r, ch)), kbase + tok * a.k_tok_stride + ch * 8, ok);
       cp16((uint32_t)__cvta_generic_to_shared(wvs + swz(r, ch)), vbase + tok * a.v_tok_stride + ch * 8, ok);
     }
@@ -387,33 +390,34 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) ranker_attention_strip_kernel(
   for (int c = threadIdx.x; c < STRIP_HIST * CH; c += ATT_THREADS) {
     const int kr = c >> 3, ch = c & 7;
     const bool ok = kr < n_hist;
-    const long long tok = tok0 + (ok ? kr : 0);
+    const long long tok = trow(ok ? kr : 0);
     cp16((uint32_t)__cvta_generic_to_shared(hk_s + swz(kr, ch)), kbase + tok * a.k_tok_stride + ch * 8, ok);
     cp16((uint32_t)__cvta_generic_to_shared(hv_s + swz(kr, ch)), vbase + tok * a.v_tok_stride + ch * 8, ok);
   }
   if (threadIdx.x < STRIP_HIST) {   // warps 0..3
     const int key = threadIdx.x;
-    const int ok = (key < n_hist) && (a.seg[tok0 + key] == 1);
+    const int ok = (key < n_hist) && (a.seg[trow(key)] == 1);
     skey_ok[key] = ok;
     const int all32 = __all_sync(0xffffffffu, ok);
     if (lane == 0) sall_ok[key >> 5] = all32;
   }
-  load_q(0, wq(0));
-  if (strip_has_cand(0)) load_own_kv(0);
+  const int tile0 = a.q_start / QROWS;   // candidate-only layer: query tiles in front of q_start are not wanted
+  load_q(tile0, wq(tile0));
+  if (strip_has_cand(tile0)) load_own_kv(tile0);
   cp_commit();
   cp_wait<0>();
   __syncthreads();
 
-  for (int tile = 0; tile < n_tiles; ++tile) {
+  for (int tile = tile0; tile < n_tiles; ++tile) {
     const int q0 = tile * QROWS;
     bf16* sq = wq(tile);
     const int rq[2] = {q0 + warp * 16 + g, q0 + warp * 16 + g + 8};
     int segq[2];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) segq[i] = (rq[i] < T) ? a.seg[tok0 + rq[i]] : 0;
+    for (int i = 0; i < 2; ++i) segq[i] = (rq[i] < T) ? a.seg[trow(rq[i])] : 0;
     const bool has_cand = strip_has_cand(tile);
 
-    if (tile > 0) { cp_wait<1>(); __syncwarp(); }   // this tile's Q strip has landed (its own K/V may still be in flight)
+    if (tile > tile0) { cp_wait<1>(); __syncwarp(); }   // this tile's Q strip has landed (its own K/V may still be in flight)
     uint32_t qf[KSTEPS][4];
 #pragma unroll
     for (int ks = 0; ks < KSTEPS; ++ks)
@@ -596,7 +600,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) ranker_attention_strip_kernel(
       const int c = lane + 32 * k, r = c >> 3, ch = c & 7;
       const int row = q0 + warp * 16 + r;
       if (row < T)
-        *reinterpret_cast<uint4*>(a.out + ((tok0 + row) * a.Hq + h) * DH + ch * 8) =
+        *reinterpret_cast<uint4*>(a.out + (trow(row) * a.Hq + h) * DH + ch * 8) =
             *reinterpret_cast<const uint4*>(sq + swz(r, ch));
     }
   }
@@ -632,7 +636,8 @@ phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::
     // go to the tcgen05 kernel (2.0 vs 4.6 ms at 1024 + 1024 tokens, 16 heads x 128).
     const int n_hist = a.hist_len < a.T ? a.hist_len : a.T;
     const bool prefer_tc = forced_tc || a.dh == 128 || n_hist > 128;
-    if (!legacy && prefer_tc && a.err_flag && ranker_attention_tc_supported(a)) return ranker_attention_tc_launch(a, a.err_flag, stream, err);
+    const bool plain = !a.split && a.q_start == 0;   // the tcgen05 kernel's tensor maps assume [B, T] token rows
+    if (plain && !legacy && prefer_tc && a.err_flag && ranker_attention_tc_supported(a)) return ranker_attention_tc_launch(a, a.err_flag, stream, err);
   }
   const bool cap = a.cap_method != 0 && a.cap > 0.f;
   {

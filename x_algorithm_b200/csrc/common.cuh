@@ -64,7 +64,19 @@ struct GemmRope {
   int pos_cap;
   int dh;                // 32 or 64
   int group, g;
+  // split token layout (all history rows, then all candidate rows): GEMM row r is token row r + row_offset; rows
+  // below split_rows are history rows of `T` per request, the rows from split_rows on sit at position pos_cap.
+  // split_rows = 0: plain layout.
+  long long row_offset = 0, split_rows = 0;
 };
+
+// Token rows of a [B, S + C] batch.  Plain layout: row = b * T + t.  Split layout (engines with candidate-only tail
+// layers): the B * S history rows first, then the B * C candidate rows, so that the GEMMs of a tail layer run over
+// one contiguous block of candidate rows and leave the history block untouched.
+__host__ __device__ inline long long token_row(int split, int B, int S, int T, int b, int t) {
+  if (!split) return (long long)b * T + t;
+  return t < S ? (long long)b * S + t : (long long)B * S + (long long)b * (T - S) + (t - S);
+}
 
 // RMSNorm folded around a GEMM.  Consumer side (ss_in): the A rows are the raw residual stream, the norm's gain is
 // folded into the weights, and the epilogue scales row r by rsqrt(sum_t ss_in[r][t] / D + eps) before rounding
@@ -90,6 +102,7 @@ struct GemmPlan {
   const bf16* A = nullptr;
   const bf16* Wt = nullptr;
   int64_t rows_max = 0;
+  int64_t a_rows = 0;   // rows the A map was encoded over (rows_max, or the M of the call that moved A)
   int N = 0, K = 0, BN = 0;
   bool pair = false;   // two CTAs of a cluster share each 256-row tile (tcgen05 cta_group::2)
   bool ready = false;
@@ -166,6 +179,7 @@ struct TokenBuildArgs {
   // row-sharded table, exchange done outside the kernel: rows_only = just write the [B,T,2H] unified-table rows to
   // `hashes` and stop; landing / pos = take slot j of a token from landing[pos[tok*2H + j]] instead of the table
   int rows_only = 0;
+  int split = 0;   // x / seg / row_ss rows in split layout (token_row)
   const bf16* landing = nullptr;
   const int* pos = nullptr;
 };
@@ -195,6 +209,7 @@ struct QkNormRopeArgs {
   const float* k_gain;   // [Hkv*dh] or null
   const float* cos_tab;  // [pos_cap+1, dh/2]
   const float* sin_tab;
+  long long row_offset = 0, split_rows = 0;   // split token layout, as in GemmRope
 };
 phx_status qknorm_rope_launch(const QkNormRopeArgs& a, cudaStream_t stream, std::string& err);
 
@@ -209,6 +224,9 @@ struct AttnArgs {
   float sm_scale, cap;
   int cap_method;
   int* err_flag;         // device int raised by a bounded wait that ran out (tcgen05 path); null = mma.sync path only
+  // Split token layout (token_row): q / k / v / out / seg rows are the B * hist_len history rows followed by the
+  // candidate rows; mma.sync kernels only.  q_start > 0: query rows below it are not computed (candidate-only layers).
+  int split = 0, q_start = 0;
 };
 // tcgen05 / TMEM kernel for head dims 64 and 128 (attention_sm100.cu); the mma.sync kernel covers the rest
 bool ranker_attention_tc_supported(const AttnArgs& a);

@@ -56,8 +56,11 @@ __global__ void __launch_bounds__(256) qknorm_rope_kernel(QkNormRopeArgs a) {
   const int g = a.Hq / a.Hkv, dh = a.dh, half = dh >> 1;
   const int width = (a.Hq + 2 * a.Hkv) * dh;
   bf16* r = a.qkv + row * width;
-  const int t = (int)(row % a.T);
-  const int pos = t < a.pos_cap ? t : a.pos_cap;
+  int pos = a.pos_cap;   // split layout (GemmRope): the candidate block sits at the cap
+  if (a.split_rows == 0 || row + a.row_offset < a.split_rows) {
+    const int t = (int)((row + a.row_offset) % a.T);
+    pos = t < a.pos_cap ? t : a.pos_cap;
+  }
   const float* ct = a.cos_tab + (long long)pos * half;
   const float* st = a.sin_tab + (long long)pos * half;
 #pragma unroll 1

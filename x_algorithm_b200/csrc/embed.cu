@@ -56,8 +56,9 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
   }
   if (a.hashes && lane < 2 * H) a.hashes[tok * (2 * H) + lane] = my_idx;
   if (a.rows_only) return;   // uniform over the grid: the caller only wants the rows (exchange outside the kernel)
+  const long long orow = token_row(a.split, a.B, a.S, T, b, t);   // where this token's row goes
   const int first_post_hash = __shfl_sync(0xffffffffu, my_idx, 0);
-  if (lane == 0) a.seg[tok] = (first_post_hash != 0) ? (is_hist ? 1 : -1) : 0;
+  if (lane == 0) a.seg[orow] = (first_post_hash != 0) ? (is_hist ? 1 : -1) : 0;
   int act = 0, srf = 0;
   if (is_hist) {
     act = a.hist_actions[(long long)b * a.S + t];
@@ -96,12 +97,12 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) { s[i] = round_bf(round_bf(acc[i]) * a.input_scale); row_ss += s[i] * s[i]; }
     o.x = pack_bf2(s[0], s[1]); o.y = pack_bf2(s[2], s[3]); o.z = pack_bf2(s[4], s[5]); o.w = pack_bf2(s[6], s[7]);
-    *reinterpret_cast<uint4*>(a.x + tok * a.D + col) = o;
+    *reinterpret_cast<uint4*>(a.x + orow * a.D + col) = o;
   }
   if (a.row_ss) {   // statistics of the bf16 row for the first fused RMSNorm
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) row_ss += __shfl_xor_sync(0xffffffffu, row_ss, o);
-    if (lane < a.ss_slots) a.row_ss[tok * a.ss_slots + lane] = (lane == 0) ? row_ss : 0.f;
+    if (lane < a.ss_slots) a.row_ss[orow * a.ss_slots + lane] = (lane == 0) ? row_ss : 0.f;
   }
 }
 

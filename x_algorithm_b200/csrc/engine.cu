@@ -75,6 +75,10 @@ struct phx_engine {
   const bf16* shard_ptr[PHX_MAX_SHARDS] = {nullptr};   // this device's view of every shard
   void* ipc_opened[PHX_MAX_SHARDS] = {nullptr};
   long long max_tokens = 0;
+  // candidate-only tail layers (ranking forward): token rows in split layout, the last n_tail layers update the
+  // candidate block only
+  bool split = false;
+  int n_tail = 0;
 
   // parameters
   bf16* table = nullptr;
@@ -238,6 +242,7 @@ phx_status check_cfg(const phx_model_config& c, std::string& err) {
   if (c.cap_method < 0 || c.cap_method > 2) return bad("cap_method");
   if (c.table_world < 0 || c.table_world > PHX_MAX_SHARDS || (c.table_world > 1 && (c.table_rank < 0 || c.table_rank >= c.table_world)))
     return bad("table_world / table_rank");
+  if (c.num_candidate_only_layers < 0 || c.num_candidate_only_layers > c.num_layers) return bad("num_candidate_only_layers");
   return PHX_OK;
 }
 
@@ -299,8 +304,12 @@ bool params_complete(phx_engine* e, bool need_heads) {
   return true;
 }
 
-// trunk over `Tt` tokens per request (history + candidates, or history only for the tower)
-phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len) {
+// trunk over `Tt` tokens per request (history + candidates, or history only for the tower).
+// split: the rows are in split layout (token_row); the last `n_tail` layers then update the candidate rows only
+// (transformer.py:789-871): their QKV projection still covers every row - the history keys / values of a tail layer
+// come from the frozen history rows through that layer's own norm and weights (layers.py:608-619) - while attention
+// (queries), out-projection and FFN run over the contiguous candidate block.
+phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len, bool split = false, int n_tail = 0) {
   const long long M = (long long)B * Tt;
   const phx_model_config& c = e->cfg;
   const float sm_scale = sqrtf(128.0f) / (float)c.key_size;  // phoenix/xrex/models/scaling.py:46-47
@@ -309,10 +318,13 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len) {
     Layer& L = e->layers[l];
     const bool fused = e->fused_norm;
     const int slots = e->D / 64;
+    const bool tail = split && l >= c.num_layers - n_tail;
+    const long long off = tail ? (long long)B * hist_len : 0;   // first row the out-projection and FFN update
+    const long long Mu = M - off;                                // rows they update
     GemmNorm n_attn_in = {e->rowss_a, nullptr, slots, 1.0f / (float)e->D, c.rms_eps};   // consume stats of x -> QKV
-    GemmNorm n_attn_out = {nullptr, e->rowss_f, 0, 0.f, 0.f};                           // out-proj leaves stats for the FFN
-    GemmNorm n_ffn_in = {e->rowss_f, nullptr, slots, 1.0f / (float)e->D, c.rms_eps};
-    GemmNorm n_ffn_out = {nullptr, e->rowss_a, 0, 0.f, 0.f};                            // down-proj leaves stats for the next layer
+    GemmNorm n_attn_out = {nullptr, e->rowss_f ? e->rowss_f + off * slots : nullptr, 0, 0.f, 0.f};   // out-proj leaves stats for the FFN
+    GemmNorm n_ffn_in = {e->rowss_f ? e->rowss_f + off * slots : nullptr, nullptr, slots, 1.0f / (float)e->D, c.rms_eps};
+    GemmNorm n_ffn_out = {nullptr, e->rowss_a ? e->rowss_a + off * slots : nullptr, 0, 0.f, 0.f};    // down-proj leaves stats for the next layer
     if (!fused) {
       { ProfScope ps(e, KC_NORM);
       if ((s = rmsnorm_launch(e->x, L.pre_attn_norm, e->hbuf, nullptr, M, e->D, c.rms_eps, e->stream, e->err))) return s; }
@@ -327,6 +339,7 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len) {
       GemmRope gr;
       gr.cos_tab = e->cos_tab; gr.sin_tab = e->sin_tab; gr.T = Tt; gr.pos_cap = pos_cap; gr.dh = e->dh;
       gr.g = e->Hq / e->Hkv; gr.group = gr.g + 2;
+      if (split) { gr.T = hist_len; gr.split_rows = (long long)B * hist_len; }
       if ((s = do_gemm(e, pq, a_in, e->qkv, nullptr, M, EPI_ROPE, &gr, fused ? &n_attn_in : nullptr))) return s;
     } else {
       if ((s = do_gemm(e, pq, a_in, e->qkv, nullptr, M, EPI_STORE, nullptr, fused ? &n_attn_in : nullptr))) return s;
@@ -336,6 +349,7 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len) {
       qa.qkv = e->qkv; qa.M = M; qa.T = Tt; qa.Hq = e->Hq; qa.Hkv = e->Hkv; qa.dh = e->dh; qa.pos_cap = pos_cap;
       qa.rotary = c.rotary; qa.qk_norm = c.qk_norm; qa.q_gain = L.q_norm; qa.k_gain = L.k_norm;
       qa.cos_tab = e->cos_tab; qa.sin_tab = e->sin_tab;
+      if (split) { qa.T = hist_len; qa.split_rows = (long long)B * hist_len; }
       { ProfScope ps(e, KC_ROPE); if ((s = qknorm_rope_launch(qa, e->stream, e->err))) return s; }
       e->last_launches++;
     }
@@ -351,27 +365,31 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len) {
     aa.hist_len = hist_len; aa.sm_scale = sm_scale; aa.cap = c.attn_logit_cap;
     aa.cap_method = (c.attn_logit_cap > 0.f) ? c.cap_method : 0;
     aa.err_flag = e->err_flag;
+    aa.split = split ? 1 : 0; aa.q_start = tail ? hist_len : 0;
     { ProfScope ps(e, KC_ATTN); if ((s = ranker_attention_launch(aa, e->stream, e->err))) return s; }
     e->last_launches++;
+    bf16* xu = e->x + off * e->D;                       // the rows this layer updates
+    const bf16* attn_u = e->attn + off * e->HD;
+    bf16* ffn_u = e->ffn + off * e->F;
     if (c.primer_norm) {
       // x = x + post_attn_norm(out(attn)) (transformer.py:531-541)
-      if ((s = do_gemm(e, L.p_out, e->attn, e->tmp, nullptr, M, EPI_STORE))) return s;
-      { ProfScope ps(e, KC_NORM); if ((s = rmsnorm_launch(e->tmp, L.post_attn_norm, e->x, e->x, M, e->D, c.rms_eps, e->stream, e->err))) return s; }
+      if ((s = do_gemm(e, L.p_out, attn_u, e->tmp, nullptr, Mu, EPI_STORE))) return s;
+      { ProfScope ps(e, KC_NORM); if ((s = rmsnorm_launch(e->tmp, L.post_attn_norm, xu, xu, Mu, e->D, c.rms_eps, e->stream, e->err))) return s; }
       e->last_launches++;
     } else {
-      if ((s = do_gemm(e, L.p_out, e->attn, e->x, e->x, M, EPI_RESIDUAL, nullptr, fused ? &n_attn_out : nullptr))) return s;
+      if ((s = do_gemm(e, L.p_out, attn_u, xu, xu, Mu, EPI_RESIDUAL, nullptr, fused ? &n_attn_out : nullptr))) return s;
     }
     if (!fused) {
-      { ProfScope ps(e, KC_NORM); if ((s = rmsnorm_launch(e->x, L.pre_ffn_norm, e->hbuf, nullptr, M, e->D, c.rms_eps, e->stream, e->err))) return s; }
+      { ProfScope ps(e, KC_NORM); if ((s = rmsnorm_launch(xu, L.pre_ffn_norm, e->hbuf, nullptr, Mu, e->D, c.rms_eps, e->stream, e->err))) return s; }
       e->last_launches++;
     }
-    if ((s = do_gemm(e, pu, a_in, e->ffn, nullptr, M, EPI_GELU, nullptr, fused ? &n_ffn_in : nullptr))) return s;
+    if ((s = do_gemm(e, pu, fused ? xu : e->hbuf, ffn_u, nullptr, Mu, EPI_GELU, nullptr, fused ? &n_ffn_in : nullptr))) return s;
     if (c.primer_norm) {
-      if ((s = do_gemm(e, L.p_down, e->ffn, e->tmp, nullptr, M, EPI_STORE))) return s;
-      { ProfScope ps(e, KC_NORM); if ((s = rmsnorm_launch(e->tmp, L.post_ffn_norm, e->x, e->x, M, e->D, c.rms_eps, e->stream, e->err))) return s; }
+      if ((s = do_gemm(e, L.p_down, ffn_u, e->tmp, nullptr, Mu, EPI_STORE))) return s;
+      { ProfScope ps(e, KC_NORM); if ((s = rmsnorm_launch(e->tmp, L.post_ffn_norm, xu, xu, Mu, e->D, c.rms_eps, e->stream, e->err))) return s; }
       e->last_launches++;
     } else {
-      if ((s = do_gemm(e, L.p_down, e->ffn, e->x, e->x, M, EPI_RESIDUAL, nullptr, fused ? &n_ffn_out : nullptr))) return s;
+      if ((s = do_gemm(e, L.p_down, ffn_u, xu, xu, Mu, EPI_RESIDUAL, nullptr, fused ? &n_ffn_out : nullptr))) return s;
     }
   }
   return PHX_OK;
@@ -396,6 +414,7 @@ phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc, 
   ta.seg = seg_dst ? seg_dst : e->seg;
   ta.row_ss = e->fused_norm ? (ss_dst ? ss_dst : e->rowss_a) : nullptr;
   ta.ss_slots = e->D / 64;
+  ta.split = (e->split && Cc > 0) ? 1 : 0;
   if (rows_out) { ta.rows_only = 1; ta.hashes = rows_out; }
   ta.landing = landing; ta.pos = pos;
   if (stream) return build_tokens_launch(ta, stream, e->err);   // prefetch on the side stream: not profiled
@@ -453,6 +472,8 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
   e->table_rank = cfg->table_world > 1 ? cfg->table_rank : 0;
   e->shard_rows = (tot + e->table_world - 1) / e->table_world;
   e->max_tokens = (long long)cfg->max_batch * e->T;
+  e->n_tail = e->C > 0 ? cfg->num_candidate_only_layers : 0;
+  e->split = e->n_tail > 0;
   const long long M = e->max_tokens;
 #define TRY(x) do { phx_status _s = (x); if (_s) return fail(_s); } while (0)
 #define CU(x) do { cudaError_t _c = (x); if (_c != cudaSuccess) { e->err = std::string(#x) + ": " + cudaGetErrorString(_c); return fail(PHX_E_CUDA); } } while (0)
@@ -707,10 +728,11 @@ phx_status enqueue_forward(phx_engine* e, const phx_rank_batch* bd, const phx_ra
                            const bf16* landing = nullptr, const int* pos = nullptr) {
   phx_status s;
   if (!tokens_ready && (s = build_tokens(e, bd, B, e->C, nullptr, nullptr, nullptr, nullptr, nullptr, landing, pos))) return s;
-  if ((s = run_trunk(e, B, e->T, e->S, e->S))) return s;
+  if ((s = run_trunk(e, B, e->T, e->S, e->S, e->split, e->n_tail))) return s;
   HeadsArgs ha;
   ha.x = e->x; ha.final_gain = e->final_norm; ha.unembed_t = e->unembed_t;
   ha.B = B; ha.T = e->T; ha.S = e->S; ha.C = e->C; ha.D = e->D; ha.V = e->V; ha.NC = e->NC;
+  if (e->split) { ha.x = e->x + (long long)B * e->S * e->D; ha.T = e->C; ha.S = 0; }   // the candidate block of the split layout
   ha.eps = e->cfg.rms_eps; ha.output_scale = 2.0f * sqrtf(512.0f / (float)e->D);  // scaling.py:43-44
   ha.final_logit_cap = e->cfg.final_logit_cap; ha.dwell_norm_scale = e->cfg.dwell_norm_scale;
   ha.has_blend = e->has_blend ? 1 : 0;

@@ -327,9 +327,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           // RoPE on the q / k head parts of this slab (layers.py:52-67, 784-788), pairs (j, j + dh/2), in two
           // passes of 16 pairs so that only 32 values are live: head dim 64 = one part per slab, pass p rotates
           // columns [16p, 16p+16) against [32+16p, 48+16p); head dim 32 = pass p is the slab's p-th part.
-          const long long row = m0 + row_in_tile;
-          const int t = (int)(row % rope.T);
-          const int pos = t < rope.pos_cap ? t : rope.pos_cap;
+          const long long row = m0 + row_in_tile + rope.row_offset;
+          int pos = rope.pos_cap;                       // split layout: the candidate block sits at the cap
+          if (rope.split_rows == 0 || row < rope.split_rows) {
+            const int t = (int)(row % rope.T);
+            pos = t < rope.pos_cap ? t : rope.pos_cap;
+          }
           const bool d64 = (rope.dh == 64);
           const int half = rope.dh >> 1;
 #pragma unroll
@@ -527,7 +530,7 @@ phx_status gemm_plan_create(GemmPlan* plan, const bf16* A, const bf16* Wt, int64
     err = "gemm: N and K must be positive multiples of 8";
     return PHX_E_ARG;
   }
-  plan->A = A; plan->Wt = Wt; plan->rows_max = rows_max; plan->N = N; plan->K = K;
+  plan->A = A; plan->Wt = Wt; plan->rows_max = rows_max; plan->a_rows = rows_max; plan->N = N; plan->K = K;
   // 128-wide tiles leave room for six output slabs: deep residual prefetch for the HBM-bound short-K GEMMs
   { const char* t = getenv("PHX_GEMM_TILES");   // diagnostics: wide | narrow overrides the caller's choice
     if (t && strcmp(t, "wide") == 0) narrow_tiles = false;
@@ -557,10 +560,12 @@ phx_status gemm_launch(GemmPlan& p, const bf16* A, bf16* C, const bf16* R, int64
   memset(&nm, 0, sizeof(nm));
   if (norm) nm = *norm;
   if (nm.ss_out && (epilogue != EPI_RESIDUAL || p.N % SLAB_COLS != 0)) { err = "gemm: row statistics are produced by the residual epilogue only"; return PHX_E_ARG; }
-  if (A != p.A) {   // the activation buffer moved (double-buffered residual stream): re-encode its map
-    phx_status s = make_map(&p.map_a, A, p.rows_max, p.K, BM, err);
+  if (A != p.A || (p.a_rows != M && p.a_rows != p.rows_max)) {
+    // the activation buffer moved (double-buffered residual stream, or a block of rows inside it): re-encode its
+    // map over exactly the M rows of this call, so that no tile reads past them
+    phx_status s = make_map(&p.map_a, A, M, p.K, BM, err);
     if (s != PHX_OK) return s;
-    p.A = A;
+    p.A = A; p.a_rows = M;
   }
   if (epilogue == EPI_ROPE) {
     if (!rope || (rope->dh != 32 && rope->dh != 64) || rope->T <= 0 || p.N % rope->dh != 0) {
