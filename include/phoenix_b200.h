@@ -88,7 +88,10 @@ typedef struct phx_model_config {
    * 789-871, 908-941; layers.py:589-725; production value 2, configs/xrecsys.py:554-555).  0 = every layer
    * updates every row.  Applies to the ranking forward; the user tower has no candidates. */
   int32_t num_candidate_only_layers;
-  int32_t _pad0;
+  /* 1 = full-precision path: every activation in fp32 (weights the same bf16-representable values), plain SIMT
+   * kernels; the precision of the reference's CPU-runnable fp32 model, for parity runs (within 1e-5 of the fp32
+   * model), not for throughput.  0 = bf16 activations with fp32 accumulation on the tcgen05 kernels. */
+  int32_t compute_fp32;
 } phx_model_config;
 
 /* Weighted blend in term-list form: xai-value-model/scoring.rs:67-73, 112-120, 282-291.

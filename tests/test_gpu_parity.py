@@ -213,6 +213,47 @@ def test_candidate_only_tail_layers_vs_oracle(torch, monkeypatch, opts, attn):
     eng.close()
 
 
+TOL_FP32 = 1e-5   # full-precision path against the fp32 model: the bar north_star states
+
+
+@pytest.mark.parametrize("opts", [dict(), dict(qk_norm=True), dict(primer_norm=True),
+                                  dict(attn_logit_cap=20.0, attn_logit_cap_method="tanh", final_logit_cap=10.0),
+                                  dict(attn_logit_cap=20.0), dict(rotary=False), dict(num_candidate_only_layers=2, num_layers=3),
+                                  dict(emb_size=256, num_q_heads=4, num_kv_heads=4, key_size=64, history_len=48,
+                                       num_candidates=24, num_layers=3)])
+def test_rank_forward_fp32_path_vs_fp32_oracle(torch, opts):
+    """BASELINE config 0 is an fp32 model: the engine's full-precision path (fp32 activations, SIMT kernels) against the
+    oracle's fp32 mode, relative L2 below 1e-5 on the residual stream, log-probabilities and continuous head."""
+    ocfg, w, rows_fn, eng = make_pair(max_batch=16, compute="fp32", **opts)
+    for batch, ragged in ((16, False), (7, True)):
+        b, taps, lp, cont, logits, spec, res = _forward_case(ocfg, w, rows_fn, eng, batch, ragged)
+        valid = b.cand_post_ids != 0
+        T, S = ocfg.seq_len, ocfg.history_len
+        hid = eng.debug_read("hidden", (batch, T, ocfg.emb_size), np.float32)
+        hid = po.rms_normalize(hid, w["final_norm"], ocfg.rms_eps)
+        tv = np.concatenate([b.hist_post_ids != 0, valid], axis=1)
+        assert rel_l2(hid[tv], taps["hfin"][tv]) < TOL_FP32, opts
+        assert rel_l2(res.log_probs[valid], lp[valid]) < TOL_FP32, opts
+        assert rel_l2(res.continuous[valid], cont[valid]) < TOL_FP32, opts
+        want_s = po.blend_scores(spec, res.log_probs, res.continuous)
+        np.testing.assert_allclose(res.scores[valid], want_s[valid], rtol=1e-12, atol=1e-15)
+        assert rel_l2(res.scores[valid], po.blend_scores(spec, lp, cont)[valid]) < 1e-4
+    eng.close()
+
+
+def test_user_tower_fp32_path_vs_fp32_oracle(torch):
+    ocfg, w, rows_fn, eng = make_pair(max_batch=8, compute="fp32", emb_size=128, num_candidates=0, history_len=32)
+    b = po.make_batch(po.ModelConfig(history_len=32, num_candidates=1), 8, seed=4, ragged=True)
+    want = po.user_tower(ocfg, w, rows_fn, b)
+    dev = [torch.from_numpy(x).cuda() for x in (b.hist_post_ids, b.hist_author_ids, b.hist_actions, b.hist_surfaces)]
+    users = torch.empty((8, 128), dtype=torch.float32, device="cuda")
+    eng.user_tower_device(8, *dev, users)
+    eng.sync()
+    ok = b.hist_post_ids[:, 0] != 0
+    assert rel_l2(users.cpu().numpy()[ok], want[ok]) < TOL_FP32
+    eng.close()
+
+
 def test_simt_gemm_path_matches_tcgen05(torch, monkeypatch):
     """The cross-check GEMM and the tcgen05 GEMM give the same forward (accumulation order aside)."""
     ocfg, w, rows_fn, eng = make_pair(max_batch=4)

@@ -77,6 +77,7 @@ class PhoenixConfig:
     table_world: int = 1        # row-shard the unified table over this many engines (one per GPU)
     table_rank: int = 0
     num_candidate_only_layers: int = 0   # tail layers that update candidate rows only (transformer.py:789-871)
+    compute: str = "bf16"       # "bf16" (tcgen05 kernels) | "fp32" (full-precision SIMT path for parity runs)
 
     @property
     def ffn_size(self) -> int:  # phoenix/xrex/utils/utils.py:37-52
@@ -112,4 +113,7 @@ class PhoenixConfig:
         c.user, c.item, c.author, c.ip = u.to_c(), i.to_c(), a.to_c(), p.to_c()
         c.table_world, c.table_rank = int(self.table_world), int(self.table_rank)
         c.num_candidate_only_layers = int(self.num_candidate_only_layers)
+        if self.compute not in ("bf16", "fp32"):
+            raise ValueError("compute must be 'bf16' or 'fp32'")
+        c.compute_fp32 = 1 if self.compute == "fp32" else 0
         return c

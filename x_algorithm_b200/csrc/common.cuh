@@ -180,6 +180,7 @@ struct TokenBuildArgs {
   // `hashes` and stop; landing / pos = take slot j of a token from landing[pos[tok*2H + j]] instead of the table
   int rows_only = 0;
   int split = 0;   // x / seg / row_ss rows in split layout (token_row)
+  float* x32 = nullptr;   // full-precision path: bf16(sum) * input_scale kept in fp32 here (x is then not written)
   const bf16* landing = nullptr;
   const int* pos = nullptr;
 };
@@ -245,8 +246,21 @@ struct HeadsArgs {
   float* log_probs; float* continuous; double* scores;
 };
 phx_status heads_launch(const HeadsArgs& a, cudaStream_t stream, std::string& err);
-// masked mean pool + L2 normalise of final-normed history rows -> f32 [B,D]
-phx_status tower_pool_launch(const bf16* x, const float* final_gain, const int* seg, int B, int T, int D, float eps,
-                             float* users, cudaStream_t stream, std::string& err);
+// masked mean pool + L2 normalise of final-normed history rows -> f32 [B,D]; x bf16, or fp32 (nothing rounded) when
+// x_is_f32
+phx_status tower_pool_launch(const void* x, const float* final_gain, const int* seg, int B, int T, int D, float eps,
+                             float* users, cudaStream_t stream, std::string& err, bool x_is_f32 = false);
+
+// ---- full-precision path (fp32_path.cu): fp32 activations, SIMT kernels, plain [B, T] token rows -------------------
+phx_status f32_rmsnorm_launch(const float* x, const float* gain, float* y, const float* res, long long rows, int D, float eps,
+                              cudaStream_t stream, std::string& err);
+phx_status f32_gemm_launch(const float* A, const bf16* Wt, float* C, const float* R, int64_t M, int N, int K, int epilogue,
+                           cudaStream_t stream, std::string& err);
+phx_status f32_qknorm_rope_launch(float* qkv, long long M, int T, int Hq, int Hkv, int dh, int pos_cap, int rotary, int qk_norm,
+                                  const float* q_gain, const float* k_gain, const float* cos_tab, const float* sin_tab,
+                                  cudaStream_t stream, std::string& err);
+phx_status f32_attention_launch(const float* qkv, const int* seg, float* out, int B, int T, int Hq, int Hkv, int dh,
+                                int hist_len, float sm_scale, float cap, int cap_method, cudaStream_t stream, std::string& err);
+phx_status f32_heads_launch(const float* x, const HeadsArgs& a, cudaStream_t stream, std::string& err);
 
 }  // namespace phx

@@ -93,6 +93,12 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
       o.x = pack_bf2(acc[0], acc[1]); o.y = pack_bf2(acc[2], acc[3]); o.z = pack_bf2(acc[4], acc[5]); o.w = pack_bf2(acc[6], acc[7]);
       *reinterpret_cast<uint4*>(a.tokens + tok * a.D + col) = o;
     }
+    if (a.x32) {   // full-precision path: the token is the bf16 sum, its scaled value stays fp32
+      float* dst = a.x32 + orow * a.D + col;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dst[i] = round_bf(acc[i]) * a.input_scale;
+      continue;
+    }
     float s[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) { s[i] = round_bf(round_bf(acc[i]) * a.input_scale); row_ss += s[i] * s[i]; }

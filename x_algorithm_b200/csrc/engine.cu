@@ -79,6 +79,9 @@ struct phx_engine {
   // candidate block only
   bool split = false;
   int n_tail = 0;
+  // full-precision path (cfg.compute_fp32): fp32 activations, plain row order
+  bool fp32 = false;
+  float *x32 = nullptr, *h32 = nullptr, *qkv32 = nullptr, *attn32 = nullptr, *ffn32 = nullptr, *tmp32 = nullptr, *hist32 = nullptr;
 
   // parameters
   bf16* table = nullptr;
@@ -242,6 +245,7 @@ phx_status check_cfg(const phx_model_config& c, std::string& err) {
   if (c.cap_method < 0 || c.cap_method > 2) return bad("cap_method");
   if (c.table_world < 0 || c.table_world > PHX_MAX_SHARDS || (c.table_world > 1 && (c.table_rank < 0 || c.table_rank >= c.table_world)))
     return bad("table_world / table_rank");
+  if (c.compute_fp32 != 0 && c.compute_fp32 != 1) return bad("compute_fp32 must be 0 or 1");
   if (c.num_candidate_only_layers < 0 || c.num_candidate_only_layers > c.num_layers) return bad("num_candidate_only_layers");
   return PHX_OK;
 }
@@ -304,12 +308,69 @@ bool params_complete(phx_engine* e, bool need_heads) {
   return true;
 }
 
+// The same layers in fp32 (fp32_path.cu), rows in plain [B, Tt] order.  A candidate-only tail is done the way the
+// reference's non-kernel path does it (transformer.py:848-858): the layer runs over every row, then the history rows
+// are put back to their values at the tail's entrance.
+phx_status run_trunk_f32(phx_engine* e, int B, int Tt, int pos_cap, int hist_len, int n_tail) {
+  const long long M = (long long)B * Tt;
+  const phx_model_config& c = e->cfg;
+  const float sm_scale = sqrtf(128.0f) / (float)c.key_size;
+  const size_t hist_bytes = (size_t)hist_len * e->D * sizeof(float), row_bytes = (size_t)Tt * e->D * sizeof(float);
+  phx_status s;
+  auto gemm = [&](const float* A, const bf16* Wt, float* Cc, const float* R, int N, int K, int epi) {
+    ProfScope ps(e, KC_GEMM | ((epi + 1) << 8));
+    e->last_launches++;
+    return f32_gemm_launch(A, Wt, Cc, R, M, N, K, epi, e->stream, e->err);
+  };
+  auto norm = [&](const float* x, const float* gain, float* y, const float* res) {
+    ProfScope ps(e, KC_NORM);
+    e->last_launches++;
+    return f32_rmsnorm_launch(x, gain, y, res, M, e->D, c.rms_eps, e->stream, e->err);
+  };
+  for (int l = 0; l < c.num_layers; ++l) {
+    Layer& L = e->layers[l];
+    const bool tail = n_tail > 0 && l >= c.num_layers - n_tail;
+    if (tail && l == c.num_layers - n_tail)
+      PHX_CUDA_TRY(cudaMemcpy2DAsync(e->hist32, hist_bytes, e->x32, row_bytes, hist_bytes, B, cudaMemcpyDeviceToDevice, e->stream), e->err);
+    if ((s = norm(e->x32, L.pre_attn_norm, e->h32, nullptr))) return s;
+    if ((s = gemm(e->h32, L.w_qkv_t, e->qkv32, nullptr, e->QW, e->D, EPI_STORE))) return s;
+    if (c.rotary || c.qk_norm) {
+      ProfScope ps(e, KC_ROPE);
+      e->last_launches++;
+      if ((s = f32_qknorm_rope_launch(e->qkv32, M, Tt, e->Hq, e->Hkv, e->dh, pos_cap, c.rotary, c.qk_norm, L.q_norm, L.k_norm,
+                                      e->cos_tab, e->sin_tab, e->stream, e->err))) return s;
+    }
+    { ProfScope ps(e, KC_ATTN);
+      e->last_launches++;
+      if ((s = f32_attention_launch(e->qkv32, e->seg, e->attn32, B, Tt, e->Hq, e->Hkv, e->dh, hist_len, sm_scale, c.attn_logit_cap,
+                                    (c.attn_logit_cap > 0.f) ? c.cap_method : 0, e->stream, e->err))) return s; }
+    if (c.primer_norm) {
+      if ((s = gemm(e->attn32, L.w_out_t, e->tmp32, nullptr, e->D, e->HD, EPI_STORE))) return s;
+      if ((s = norm(e->tmp32, L.post_attn_norm, e->x32, e->x32))) return s;
+    } else {
+      if ((s = gemm(e->attn32, L.w_out_t, e->x32, e->x32, e->D, e->HD, EPI_RESIDUAL))) return s;
+    }
+    if ((s = norm(e->x32, L.pre_ffn_norm, e->h32, nullptr))) return s;
+    if ((s = gemm(e->h32, L.w_up_t, e->ffn32, nullptr, e->F, e->D, EPI_GELU))) return s;
+    if (c.primer_norm) {
+      if ((s = gemm(e->ffn32, L.w_down_t, e->tmp32, nullptr, e->D, e->F, EPI_STORE))) return s;
+      if ((s = norm(e->tmp32, L.post_ffn_norm, e->x32, e->x32))) return s;
+    } else {
+      if ((s = gemm(e->ffn32, L.w_down_t, e->x32, e->x32, e->D, e->F, EPI_RESIDUAL))) return s;
+    }
+    if (tail)
+      PHX_CUDA_TRY(cudaMemcpy2DAsync(e->x32, row_bytes, e->hist32, hist_bytes, hist_bytes, B, cudaMemcpyDeviceToDevice, e->stream), e->err);
+  }
+  return PHX_OK;
+}
+
 // trunk over `Tt` tokens per request (history + candidates, or history only for the tower).
 // split: the rows are in split layout (token_row); the last `n_tail` layers then update the candidate rows only
 // (transformer.py:789-871): their QKV projection still covers every row - the history keys / values of a tail layer
 // come from the frozen history rows through that layer's own norm and weights (layers.py:608-619) - while attention
 // (queries), out-projection and FFN run over the contiguous candidate block.
 phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len, bool split = false, int n_tail = 0) {
+  if (e->fp32) return run_trunk_f32(e, B, Tt, pos_cap, hist_len, n_tail);
   const long long M = (long long)B * Tt;
   const phx_model_config& c = e->cfg;
   const float sm_scale = sqrtf(128.0f) / (float)c.key_size;  // phoenix/xrex/models/scaling.py:46-47
@@ -415,6 +476,7 @@ phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc, 
   ta.row_ss = e->fused_norm ? (ss_dst ? ss_dst : e->rowss_a) : nullptr;
   ta.ss_slots = e->D / 64;
   ta.split = (e->split && Cc > 0) ? 1 : 0;
+  if (e->fp32) ta.x32 = e->x32;
   if (rows_out) { ta.rows_only = 1; ta.hashes = rows_out; }
   ta.landing = landing; ta.pos = pos;
   if (stream) return build_tokens_launch(ta, stream, e->err);   // prefetch on the side stream: not profiled
@@ -473,7 +535,8 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
   e->shard_rows = (tot + e->table_world - 1) / e->table_world;
   e->max_tokens = (long long)cfg->max_batch * e->T;
   e->n_tail = e->C > 0 ? cfg->num_candidate_only_layers : 0;
-  e->split = e->n_tail > 0;
+  e->fp32 = cfg->compute_fp32 != 0;
+  e->split = e->n_tail > 0 && !e->fp32;
   const long long M = e->max_tokens;
 #define TRY(x) do { phx_status _s = (x); if (_s) return fail(_s); } while (0)
 #define CU(x) do { cudaError_t _c = (x); if (_c != cudaSuccess) { e->err = std::string(#x) + ": " + cudaGetErrorString(_c); return fail(PHX_E_CUDA); } } while (0)
@@ -490,13 +553,22 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
   TRY(dev_alloc(e, &e->seg, (size_t)M));
   {
     const char* nf = getenv("PHX_NORM");
-    e->fused_norm = !cfg->primer_norm && !e->use_simt_gemm && !(nf && strcmp(nf, "separate") == 0);
+    e->fused_norm = !cfg->primer_norm && !e->use_simt_gemm && !e->fp32 && !(nf && strcmp(nf, "separate") == 0);
     if (e->fused_norm) {
       TRY(dev_alloc(e, &e->rowss_a, (size_t)M * (e->D / 64)));
       TRY(dev_alloc(e, &e->rowss_f, (size_t)M * (e->D / 64)));
     }
   }
   if (cfg->primer_norm) TRY(dev_alloc(e, &e->tmp, (size_t)M * e->D));
+  if (e->fp32) {
+    TRY(dev_alloc(e, &e->x32, (size_t)M * e->D));
+    TRY(dev_alloc(e, &e->h32, (size_t)M * e->D));
+    TRY(dev_alloc(e, &e->qkv32, (size_t)M * e->QW));
+    TRY(dev_alloc(e, &e->attn32, (size_t)M * e->HD));
+    TRY(dev_alloc(e, &e->ffn32, (size_t)M * e->F));
+    if (cfg->primer_norm) TRY(dev_alloc(e, &e->tmp32, (size_t)M * e->D));
+    if (e->n_tail > 0) TRY(dev_alloc(e, &e->hist32, (size_t)cfg->max_batch * e->S * e->D));
+  }
   if (e->debug_taps) {
     TRY(dev_alloc(e, &e->tokens, (size_t)M * e->D));
     TRY(dev_alloc(e, &e->hashes, (size_t)M * 2 * cfg->item.num_hashes));
@@ -594,6 +666,7 @@ void phx_engine_destroy(phx_engine* e) {
     fr(L.w_qkv_t); fr(L.w_out_t); fr(L.w_up_t); fr(L.w_down_t); fr(L.w_qkv_f); fr(L.w_up_f);
   }
   fr(e->cos_tab); fr(e->sin_tab); fr(e->x); fr(e->hbuf); fr(e->qkv); fr(e->attn); fr(e->ffn); fr(e->tmp); fr(e->tokens);
+  fr(e->x32); fr(e->h32); fr(e->qkv32); fr(e->attn32); fr(e->ffn32); fr(e->tmp32); fr(e->hist32);
   fr(e->x_alt); fr(e->seg_alt); fr(e->rowss_a_alt); fr(e->rowss_a); fr(e->rowss_f); fr(e->seg); fr(e->hashes); fr(e->err_flag); fr(e->in_stage_dev); fr(e->lp_dev); fr(e->cont_dev); fr(e->score_dev);
   if (e->in_stage_host) cudaFreeHost(e->in_stage_host);
   if (e->lp_host) cudaFreeHost(e->lp_host);
@@ -729,6 +802,7 @@ phx_status enqueue_forward(phx_engine* e, const phx_rank_batch* bd, const phx_ra
   phx_status s;
   if (!tokens_ready && (s = build_tokens(e, bd, B, e->C, nullptr, nullptr, nullptr, nullptr, nullptr, landing, pos))) return s;
   if ((s = run_trunk(e, B, e->T, e->S, e->S, e->split, e->n_tail))) return s;
+  const bool f32 = e->fp32;
   HeadsArgs ha;
   ha.x = e->x; ha.final_gain = e->final_norm; ha.unembed_t = e->unembed_t;
   ha.B = B; ha.T = e->T; ha.S = e->S; ha.C = e->C; ha.D = e->D; ha.V = e->V; ha.NC = e->NC;
@@ -738,7 +812,7 @@ phx_status enqueue_forward(phx_engine* e, const phx_rank_batch* bd, const phx_ra
   ha.has_blend = e->has_blend ? 1 : 0;
   if (e->has_blend) ha.blend = e->blend; else memset(&ha.blend, 0, sizeof(ha.blend));
   ha.log_probs = od->log_probs; ha.continuous = od->continuous; ha.scores = od->scores;
-  { ProfScope ps(e, KC_HEADS); if ((s = heads_launch(ha, e->stream, e->err))) return s; }
+  { ProfScope ps(e, KC_HEADS); if ((s = f32 ? f32_heads_launch(e->x32, ha, e->stream, e->err) : heads_launch(ha, e->stream, e->err))) return s; }
   e->last_launches++;
   return PHX_OK;
 }
@@ -836,6 +910,7 @@ phx_status phx_rank_prefetch_device(phx_engine* e, const phx_rank_batch* bd) {
   if (!e || !bd) return PHX_E_ARG;
   if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
   if (bd->batch <= 0 || bd->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
+  if (e->fp32) { e->err = "token prefetch is not available on the full-precision path"; return PHX_E_ARG; }
   if (!params_complete(e, true) || !shards_complete(e)) return PHX_E_STATE;
   cudaSetDevice(e->device);
   if (!e->side_stream) {
@@ -1091,7 +1166,8 @@ phx_status phx_debug_read(phx_engine* e, const char* what, void* host, size_t nb
   const std::string w(what);
   const size_t M = (size_t)e->last_batch * e->T;
   const void* src = nullptr; size_t avail = 0;
-  if (w == "hidden") { src = e->x; avail = M * e->D * 2; }
+  if (w == "hidden" && e->fp32) { src = e->x32; avail = M * e->D * 4; }   // full-precision path: fp32 rows
+  else if (w == "hidden") { src = e->x; avail = M * e->D * 2; }
   else if (w == "seg") { src = e->seg; avail = M * 4; }
   else if (w == "attn") { src = e->attn; avail = M * e->HD * 2; }
   else if (w == "qkv") { src = e->qkv; avail = M * e->QW * 2; }
@@ -1142,7 +1218,7 @@ phx_status phx_user_tower_device(phx_engine* e, const phx_rank_batch* bd, float*
   // history only: tokens laid out [B, S]; every valid token is "history" so attention is full among them
   if ((s = build_tokens(e, bd, B, 0))) return s;
   if ((s = run_trunk(e, B, e->S, e->S, e->S))) return s;
-  { ProfScope ps(e, KC_HEADS); if ((s = tower_pool_launch(e->x, e->final_norm, e->seg, B, e->S, e->D, e->cfg.rms_eps, users_dev, e->stream, e->err))) return s; }
+  { ProfScope ps(e, KC_HEADS); if ((s = tower_pool_launch(e->fp32 ? (const void*)e->x32 : (const void*)e->x, e->final_norm, e->seg, B, e->S, e->D, e->cfg.rms_eps, users_dev, e->stream, e->err, e->fp32))) return s; }
   e->last_launches++;
   PHX_CUDA_TRY(cudaEventRecord(e->ev1, e->stream), e->err);
   return PHX_OK;

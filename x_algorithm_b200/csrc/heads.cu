@@ -256,19 +256,21 @@ phx_status launch_heads_mma(const HeadsArgs& a, long long rows, cudaStream_t str
 }
 
 // users[b] = l2norm(mean over valid t of final_norm(x[b,t])), fp32; one CTA per user, one thread per column
-__global__ void tower_pool_kernel(const bf16* __restrict__ x, const float* __restrict__ gain, const int* __restrict__ seg,
+template <bool F32>   // F32: fp32 rows, nothing rounded (the full-precision path)
+__global__ void tower_pool_kernel(const void* __restrict__ xv, const float* __restrict__ gain, const int* __restrict__ seg,
                                   int T, int D, float eps, float* __restrict__ users) {
+  auto ld = [&](long long i) { return F32 ? reinterpret_cast<const float*>(xv)[i] : bf2f(reinterpret_cast<const bf16*>(xv)[i]); };
   extern __shared__ float psm[];  // [T] rstd (0 for invalid) + reduction scratch
   float* rstd = psm;
   float* red = psm + T;
   const int b = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   for (int t = warp; t < T; t += nw) {
-    const bf16* xr = x + ((long long)b * T + t) * D;
+    const long long r0 = ((long long)b * T + t) * D;
     float ss = 0.f;
-    for (int k = lane; k < D; k += 32) { float v = bf2f(xr[k]); ss += v * v; }
+    for (int k = lane; k < D; k += 32) { float v = ld(r0 + k); ss += v * v; }
     ss = warp_sum(ss);
-    if (lane == 0) rstd[t] = (seg[(long long)b * T + t] != 0) ? rsqrtf(ss / (float)D + eps) : 0.f;
+    if (lane == 0) rstd[t] = (seg[(long long)b * T + t] != 0) ? (F32 ? 1.0f / sqrtf(ss / (float)D + eps) : rsqrtf(ss / (float)D + eps)) : 0.f;
   }
   __syncthreads();
   float cnt = 0.f;
@@ -280,7 +282,10 @@ __global__ void tower_pool_kernel(const bf16* __restrict__ x, const float* __res
     float acc = 0.f;
     const float gk = gain[k];
     for (int t = 0; t < T; ++t) {  // fixed order over positions
-      if (rstd[t] != 0.f) acc = acc + round_bf(bf2f(x[((long long)b * T + t) * D + k]) * rstd[t] * gk);
+      if (rstd[t] != 0.f) {
+        const float v = ld(((long long)b * T + t) * D + k) * rstd[t] * gk;
+        acc = acc + (F32 ? v : round_bf(v));
+      }
     }
     const float rep = acc / fmaxf(cnt, 1.0f);
     vals[nv] = rep;
@@ -327,13 +332,14 @@ phx_status heads_launch(const HeadsArgs& a, cudaStream_t stream, std::string& er
   return PHX_OK;
 }
 
-phx_status tower_pool_launch(const bf16* x, const float* final_gain, const int* seg, int B, int T, int D, float eps,
-                             float* users, cudaStream_t stream, std::string& err) {
+phx_status tower_pool_launch(const void* x, const float* final_gain, const int* seg, int B, int T, int D, float eps,
+                             float* users, cudaStream_t stream, std::string& err, bool x_is_f32) {
   if (B == 0) return PHX_OK;
   int threads = 256;
   if (D > 8 * threads) { err = "tower_pool: D too large"; return PHX_E_CAPACITY; }
   const size_t smem = (size_t)(T + 32) * sizeof(float);
-  tower_pool_kernel<<<B, threads, smem, stream>>>(x, final_gain, seg, T, D, eps, users);
+  if (x_is_f32) tower_pool_kernel<true><<<B, threads, smem, stream>>>(x, final_gain, seg, T, D, eps, users);
+  else tower_pool_kernel<false><<<B, threads, smem, stream>>>(x, final_gain, seg, T, D, eps, users);
   PHX_CUDA_TRY(cudaGetLastError(), err);
   return PHX_OK;
 }
