@@ -9,8 +9,10 @@ be imported.  Instead the source text of individual pure functions is cut out of
 files with `ast` and executed unchanged:
   * `_hash_ids_batch` runs under numba exactly as in the reference (it only needs numpy+numba);
   * the jnp-only helpers (rope_angles, apply_rope, rotate_half, rms_normalize, _split_merged_qkv,
-    attention_segment_ids, history_candidate_mask) run with a small NumPy stand-in for the
-    `jnp` / `jax.lax` names they use.  The arithmetic library is therefore NumPy, not XLA; the
+    attention_segment_ids, history_candidate_mask) and the reference's own plain candidate-isolation
+    attention (`attention_reference` with `_apply_cap`, `tanh`, `_abs` of
+    pallas/ranker_attention_fa3.py) run with a small NumPy stand-in for the `jnp` / `jax.lax` names
+    they use.  The arithmetic library is therefore NumPy, not XLA; the
     control flow, constants and operation order are the reference's own.
 Nothing from the reference is copied into this repository; only inputs and outputs are stored.
 """
@@ -43,6 +45,11 @@ class _Lax:
         return (np.float32(1.0) / np.sqrt(x)).astype(np.float32)
 
     @staticmethod
+    def logistic(x):
+        x = np.asarray(x)
+        return (1.0 / (1.0 + np.exp(-x))).astype(x.dtype)
+
+    @staticmethod
     def broadcasted_iota(dtype, shape, dim):
         return np.broadcast_to(np.arange(shape[dim], dtype=dtype).reshape([-1 if i == dim else 1 for i in range(len(shape))]), shape)
 
@@ -50,7 +57,8 @@ class _Lax:
 def _jnp():
     m = types.SimpleNamespace()
     for k in ("arange", "asarray", "einsum", "tile", "split", "concatenate", "mean", "square", "where",
-              "broadcast_to", "logical_or", "logical_not", "float32", "int32", "bfloat16", "ndarray"):
+              "broadcast_to", "logical_or", "logical_not", "float32", "int32", "bfloat16", "ndarray", "any", "exp",
+              "inf", "log2", "abs", "tanh"):
         if hasattr(np, k):
             setattr(m, k, getattr(np, k))
     return m
@@ -122,6 +130,32 @@ def main(ref: str, outdir: str):
         rms_x=xin, rms_gain=gain, rms_out=normed,
         qkv=qkv, q=q, k=k, v=v, pad=pad, seg=seg, hmask=hmask,
     )
+
+    # ---- the reference's plain candidate-isolation attention (pallas/ranker_attention_fa3.py:1185-1236) ----------
+    import math
+    ns_a = dict(base)
+    ns_a.update(math=math, Tuple=__import__("typing").Tuple,
+                ranker_attention_utils=types.SimpleNamespace(history_candidate_mask=ns["history_candidate_mask"]))
+    for name, src in cut(os.path.join(ref, "phoenix/xrex/pallas/ranker_attention_fa3.py"),
+                         ["tanh", "_abs", "_apply_cap", "attention_reference"]).items():
+        exec("from __future__ import annotations\n" + src, ns_a)
+    att = {}
+    cases = [  # (name, B, T, Hq, Hkv, dh, bound, cap, cap_method)
+        ("full", 2, 40, 4, 4, 32, (0, 32, 32, 40), -1.0, "tanh"),
+        ("ragged", 2, 48, 4, 2, 32, (0, 19, 32, 43), -1.0, "tanh"),       # padded history tail and padded candidates, GQA
+        ("offset", 1, 40, 2, 2, 64, (3, 30, 33, 40), 20.0, "soft_sign"),  # history not starting at 0, soft-sign cap
+        ("tanhcap", 2, 24, 2, 1, 32, (0, 16, 16, 24), 15.0, "tanh"),
+    ]
+    for name, B_, T_, Hq_, Hkv_, dh_, bound, cap, method in cases:
+        q_ = (rng.standard_normal((B_, T_, Hq_, dh_), dtype=np.float32) * 1.5).astype(np.float32)
+        k_ = (rng.standard_normal((B_, T_, Hkv_, dh_), dtype=np.float32) * 1.5).astype(np.float32)
+        v_ = rng.standard_normal((B_, T_, Hkv_, dh_), dtype=np.float32)
+        sm = math.sqrt(128.0) / dh_
+        o_ = ns_a["attention_reference"](q_, k_, v_, bound=bound, sm_scale=sm, cap=cap, cap_method=method)
+        att.update({f"{name}_q": q_, f"{name}_k": k_, f"{name}_v": v_, f"{name}_out": np.asarray(o_, dtype=np.float32),
+                    f"{name}_bound": np.array(bound, dtype=np.int32),
+                    f"{name}_params": np.array([sm, cap, 1.0 if method == "tanh" else 0.0], dtype=np.float64)})
+    np.savez_compressed(os.path.join(outdir, "attention_golden.npz"), **att)
     print("wrote", outdir)
 
 

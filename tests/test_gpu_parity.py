@@ -117,6 +117,26 @@ def test_ranker_attention_vs_oracle(torch, monkeypatch, dh, S, Cn, H, cap, impl)
     assert not np.array_equal(got[0, S + 1], got2[0, S + 1])
 
 
+@pytest.mark.parametrize("name", ["full", "ragged", "offset", "tanhcap"])
+@pytest.mark.parametrize("impl", ["tcgen05", "mma"])
+def test_ranker_attention_vs_reference_function_golden(torch, monkeypatch, name, impl):
+    """The CUDA kernels against stored outputs of the reference's own plain candidate-isolation attention
+    (`attention_reference`, pallas/ranker_attention_fa3.py:1185-1236; tests/golden/attention_golden.npz): bf16 inputs
+    (the stored fp32 inputs rounded), so the bar is the bf16 one, 2e-2 relative."""
+    import os
+    from tests.test_oracle_golden import att_case
+    from x_algorithm_b200.engine import ranker_attention
+    monkeypatch.setenv("PHX_ATTN", impl)
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "attention_golden.npz"))
+    q, k, v, seg, cand_start, sm, cap, method, want = att_case(g, name)
+    tq, tk, tv = (torch.from_numpy(po.bf16_round(x)).to(torch.bfloat16).cuda() for x in (q, k, v))
+    out, _ = ranker_attention(tq, tk, tv, torch.from_numpy(seg).cuda(), cand_start, sm, cap,
+                              0 if cap <= 0 else (2 if method == "tanh" else 1))
+    got = out.float().cpu().numpy()
+    assert rel_l2(got, want) < TOL
+    assert (got[seg == 0] == 0).all()
+
+
 def _forward_case(ocfg, w, rows_fn, eng, batch, ragged):
     b = po.make_batch(ocfg, batch, seed=2, ragged=ragged)
     taps = {}

@@ -83,6 +83,32 @@ def test_elementwise_match_reference_functions():
     np.testing.assert_array_equal(po.ranker_mask(seg)[0], g["hmask"])
 
 
+ATT_CASES = ("full", "ragged", "offset", "tanhcap")
+
+
+def att_case(g, name):
+    """Inputs, segment ids and the output of the reference's own `attention_reference`
+    (pallas/ranker_attention_fa3.py:1185-1236) for one stored case."""
+    hl, hu, cl, cu = (int(x) for x in g[name + "_bound"])
+    q = g[name + "_q"]
+    seg = np.zeros(q.shape[:2], np.int32)
+    seg[:, hl:hu] = 1
+    seg[:, cl:cu] = -1
+    sm, cap, is_tanh = g[name + "_params"]
+    return q, g[name + "_k"], g[name + "_v"], seg, cl, float(sm), float(cap), ("tanh" if is_tanh else "soft_sign"), g[name + "_out"]
+
+
+@pytest.mark.parametrize("name", ATT_CASES)
+def test_attention_matches_reference_attention_function(name):
+    """The oracle's masked attention against the output of the reference's plain candidate-isolation attention run
+    on the same inputs (padded history tail, padded candidates, history not starting at 0, GQA, both caps)."""
+    g = np.load(os.path.join(G, "attention_golden.npz"))
+    q, k, v, seg, _, sm, cap, method, want = att_case(g, name)
+    got = po.masked_attention(q, k, v, po.ranker_mask(seg), sm, cap, method)
+    np.testing.assert_allclose(got, want, rtol=2e-5, atol=2e-6)
+    assert (got[seg == 0] == 0).all() and (want[seg == 0] == 0).all()
+
+
 def test_gather_oob_and_lcg_indices():
     # emb_table.rs:124-140 (OOB -> row 0) with the index generator of emb_table.rs:1689-1701
     num_rows, w = 257, 64
