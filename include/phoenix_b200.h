@@ -119,6 +119,21 @@ typedef struct phx_rank_batch {
   const int64_t* cand_author_ids; /* [B,C] */
 } phx_rank_batch;
 
+/* The same batch as the reference's batch-prep fills it (xai-recsys-engine/src/python.rs:1394-1440:
+ * history_post_hashes / history_auth_hashes i32[B,S,H], candidate_post_hashes / candidate_auth_hashes i32[B,C,H]):
+ * rows of the unified table, already hashed and offset on the host (recsys_embedding.py:282-331), 0 = padding,
+ * rows outside the table read row 0 (emb_table.rs:134-137).  Actions / surfaces as in phx_rank_batch. */
+typedef struct phx_rank_batch_hashed {
+  int32_t batch;
+  int32_t _pad;
+  const int32_t* hist_post_hashes;   /* [B,S,H] */
+  const int32_t* hist_author_hashes; /* [B,S,H] */
+  const int32_t* hist_actions;       /* [B,S] */
+  const int32_t* hist_surfaces;      /* [B,S] */
+  const int32_t* cand_post_hashes;   /* [B,C,H] */
+  const int32_t* cand_author_hashes; /* [B,C,H] */
+} phx_rank_batch_hashed;
+
 /* Outputs of a ranking call, the arguments of the reference's reply
  * (xai-recsys-engine/src/python.rs:390-396) plus the blended score.  Any pointer may be NULL. */
 typedef struct phx_rank_out {
@@ -199,6 +214,12 @@ phx_status phx_rank_submit(phx_engine* e, const phx_rank_batch* batch_host, int3
 phx_status phx_rank_collect(phx_engine* e, int32_t slot, const phx_rank_out* out_host);
 /* Same with DEVICE buffers, asynchronous on the engine's stream (call phx_sync to wait). */
 phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* batch_dev, const phx_rank_out* out_dev);
+/* The ranking forward from pre-hashed rows (phx_rank_batch_hashed): the drop-in for a host that keeps the reference's
+ * own batch-prep (compute_batch_inputs_rust_quick, model_runner.py:3072-3077) and hands over its buffers unchanged.
+ * Device buffers, asynchronous on the engine's stream; results identical to phx_rank_forward_device on the ids the
+ * rows were hashed from.  phx_rank_forward_hashed is the same with HOST buffers, blocking like phx_rank_forward. */
+phx_status phx_rank_forward_hashed_device(phx_engine* e, const phx_rank_batch_hashed* batch_dev, const phx_rank_out* out_dev);
+phx_status phx_rank_forward_hashed(phx_engine* e, const phx_rank_batch_hashed* batch_host, const phx_rank_out* out_host);
 /* Build the tokens (hash -> gather-sum) of the batch that the NEXT phx_rank_forward_device call will carry, on a
  * side stream, so that the gather - which waits on other GPUs' memory when the table is row-sharded - overlaps the
  * forward that is already enqueued.  Call order per step: forward(batch i), then prefetch(batch i+1).  The next

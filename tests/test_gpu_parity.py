@@ -274,6 +274,35 @@ def test_user_tower_fp32_path_vs_fp32_oracle(torch):
     eng.close()
 
 
+@pytest.mark.parametrize("opts", [dict(), dict(num_hashes=4, emb_size=256, num_q_heads=4, num_kv_heads=4, key_size=64),
+                                  dict(num_candidate_only_layers=1)])
+def test_rank_forward_from_prehashed_rows_bit_identical(torch, opts):
+    """The batch-prep buffers of the reference (rows hashed on the host by its own hash functions,
+    recsys_embedding.py:282-331 = the oracle's hash layout) give the same bits as the forward that hashes on the
+    device; out-of-table rows read row 0 (emb_table.rs:134-137)."""
+    ocfg, w, rows_fn, eng = make_pair(max_batch=6, **opts)
+    b = po.make_batch(ocfg, 6, seed=21, ragged=True)
+    want = eng.rank(to_inputs(b))
+    lay = ocfg.hash_layout()
+    hp, ha = lay.item_hash(b.hist_post_ids), lay.author_hash(b.hist_author_ids)
+    cp, ca = lay.item_hash(b.cand_post_ids), lay.author_hash(b.cand_author_ids)
+    got = eng.rank_hashed(hp, ha, b.hist_actions, b.hist_surfaces, cp, ca)
+    np.testing.assert_array_equal(got.log_probs, want.log_probs)
+    np.testing.assert_array_equal(got.continuous, want.continuous)
+    # device buffers, and a row past the table's end: read as row 0 (the padding row), never out of bounds
+    dev = [torch.from_numpy(np.ascontiguousarray(x, np.int32)).cuda() for x in (hp, ha, b.hist_actions, b.hist_surfaces, cp, ca)]
+    lp = torch.empty((6, ocfg.num_candidates, ocfg.num_actions), dtype=torch.float32, device="cuda")
+    cont = torch.empty((6, ocfg.num_candidates, ocfg.num_continuous), dtype=torch.float32, device="cuda")
+    eng.rank_hashed_device(6, *dev, lp, cont)
+    eng.sync()
+    np.testing.assert_array_equal(lp.cpu().numpy(), want.log_probs)
+    ca2 = ca.copy(); ca2[0, 0, 1] = np.iinfo(np.int32).max; ca0 = ca.copy(); ca0[0, 0, 1] = 0
+    r_oob = eng.rank_hashed(hp, ha, b.hist_actions, b.hist_surfaces, cp, ca2)
+    r_zero = eng.rank_hashed(hp, ha, b.hist_actions, b.hist_surfaces, cp, ca0)
+    np.testing.assert_array_equal(r_oob.log_probs, r_zero.log_probs)
+    eng.close()
+
+
 def test_simt_gemm_path_matches_tcgen05(torch, monkeypatch):
     """The cross-check GEMM and the tcgen05 GEMM give the same forward (accumulation order aside)."""
     ocfg, w, rows_fn, eng = make_pair(max_batch=4)

@@ -43,6 +43,10 @@ class RankBatch(C.Structure):
                 ("cand_post_ids", C.c_void_p), ("cand_author_ids", C.c_void_p)]
 
 
+# phx_rank_batch_hashed: the same layout with int32 [.., H] row arrays in place of the int64 id arrays
+RankBatchHashed = RankBatch
+
+
 class RankOut(C.Structure):
     _fields_ = [("log_probs", C.c_void_p), ("continuous", C.c_void_p), ("scores", C.c_void_p)]
 
@@ -68,6 +72,8 @@ SIGNATURES = {
     "phx_rank_submit": (C.c_int32, [_P, C.POINTER(RankBatch), C.c_int32]),
     "phx_rank_collect": (C.c_int32, [_P, C.c_int32, C.POINTER(RankOut)]),
     "phx_rank_forward_device": (C.c_int32, [_P, C.POINTER(RankBatch), C.POINTER(RankOut)]),
+    "phx_rank_forward_hashed_device": (C.c_int32, [_P, C.POINTER(RankBatchHashed), C.POINTER(RankOut)]),
+    "phx_rank_forward_hashed": (C.c_int32, [_P, C.POINTER(RankBatchHashed), C.POINTER(RankOut)]),
     "phx_rank_prefetch_device": (C.c_int32, [_P, C.POINTER(RankBatch)]),
     "phx_sync": (C.c_int32, [_P]),
     "phx_last_device_ms": (C.c_int32, [_P, C.POINTER(C.c_float)]),

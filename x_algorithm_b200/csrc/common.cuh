@@ -180,6 +180,10 @@ struct TokenBuildArgs {
   // `hashes` and stop; landing / pos = take slot j of a token from landing[pos[tok*2H + j]] instead of the table
   int rows_only = 0;
   int split = 0;   // x / seg / row_ss rows in split layout (token_row)
+  // pre-hashed input (the batch-prep buffers of the reference as they are): unified-table rows [B,S,H] / [B,C,H] per
+  // feature, 0 = padding; when pre_hist_post is set the ids are not read and nothing is hashed
+  const int* pre_hist_post = nullptr; const int* pre_hist_author = nullptr;
+  const int* pre_cand_post = nullptr; const int* pre_cand_author = nullptr;
   float* x32 = nullptr;   // full-precision path: bf16(sum) * input_scale kept in fp32 here (x is then not written)
   const bf16* landing = nullptr;
   const int* pos = nullptr;

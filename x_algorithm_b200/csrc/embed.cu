@@ -44,15 +44,21 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
   if (tok >= (long long)a.B * T) return;
   const int b = (int)(tok / T), t = (int)(tok % T);
   const bool is_hist = t < a.S;
-  const long long post_id = is_hist ? a.hist_post[(long long)b * a.S + t] : a.cand_post[(long long)b * a.C + (t - a.S)];
-  const long long auth_id = is_hist ? a.hist_author[(long long)b * a.S + t] : a.cand_author[(long long)b * a.C + (t - a.S)];
   const int H = a.item.num_hashes;
-  // lanes 0..H-1 hash the post id, lanes H..2H-1 the author id
+  const long long slot = is_hist ? (long long)b * a.S + t : (long long)b * a.C + (t - a.S);
+  // lanes 0..H-1 hold the post rows, lanes H..2H-1 the author rows: hashed here, or taken as given
   int my_idx = 0;
-  if (lane < H) my_idx = hash_one(post_id, a.item.scales[lane], a.item.biases[lane], a.item);
-  else if (lane < 2 * H) {
-    const int j = lane - H;
-    my_idx = hash_one(auth_id, a.author.scales[j], a.author.biases[j], a.author);
+  if (a.pre_hist_post) {
+    if (lane < H) my_idx = (is_hist ? a.pre_hist_post : a.pre_cand_post)[slot * H + lane];
+    else if (lane < 2 * H) my_idx = (is_hist ? a.pre_hist_author : a.pre_cand_author)[slot * H + (lane - H)];
+  } else {
+    const long long post_id = is_hist ? a.hist_post[slot] : a.cand_post[slot];
+    const long long auth_id = is_hist ? a.hist_author[slot] : a.cand_author[slot];
+    if (lane < H) my_idx = hash_one(post_id, a.item.scales[lane], a.item.biases[lane], a.item);
+    else if (lane < 2 * H) {
+      const int j = lane - H;
+      my_idx = hash_one(auth_id, a.author.scales[j], a.author.biases[j], a.author);
+    }
   }
   if (a.hashes && lane < 2 * H) a.hashes[tok * (2 * H) + lane] = my_idx;
   if (a.rows_only) return;   // uniform over the grid: the caller only wants the rows (exchange outside the kernel)

@@ -458,13 +458,20 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len, bo
 
 phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc, bf16* x_dst = nullptr, int* seg_dst = nullptr,
                         cudaStream_t stream = nullptr, float* ss_dst = nullptr, int* rows_out = nullptr,
-                        const bf16* landing = nullptr, const int* pos = nullptr) {
+                        const bf16* landing = nullptr, const int* pos = nullptr, const phx_rank_batch_hashed* hb = nullptr) {
   long long ou, oi, oa, oip, tot;
   region_offsets(e->cfg, &ou, &oi, &oa, &oip, &tot);
   TokenBuildArgs ta;
-  ta.hist_post = (const long long*)bd->hist_post_ids; ta.hist_author = (const long long*)bd->hist_author_ids;
-  ta.hist_actions = bd->hist_actions; ta.hist_surfaces = bd->hist_surfaces;
-  ta.cand_post = (const long long*)bd->cand_post_ids; ta.cand_author = (const long long*)bd->cand_author_ids;
+  if (hb) {   // rows already hashed by the host's batch-prep (bd is not read)
+    ta.hist_post = ta.hist_author = ta.cand_post = ta.cand_author = nullptr;
+    ta.pre_hist_post = hb->hist_post_hashes; ta.pre_hist_author = hb->hist_author_hashes;
+    ta.pre_cand_post = hb->cand_post_hashes; ta.pre_cand_author = hb->cand_author_hashes;
+    ta.hist_actions = hb->hist_actions; ta.hist_surfaces = hb->hist_surfaces;
+  } else {
+    ta.hist_post = (const long long*)bd->hist_post_ids; ta.hist_author = (const long long*)bd->hist_author_ids;
+    ta.hist_actions = bd->hist_actions; ta.hist_surfaces = bd->hist_surfaces;
+    ta.cand_post = (const long long*)bd->cand_post_ids; ta.cand_author = (const long long*)bd->cand_author_ids;
+  }
   ta.table = table_view(e);
   ta.action_table = e->action_table; ta.surface_table = e->surface_table;
   ta.num_action_types = e->cfg.num_action_types; ta.num_surfaces = e->cfg.num_surfaces;
@@ -623,7 +630,9 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
   // staging for the host entry point
   {
     const size_t B = cfg->max_batch;
-    e->in_stage_bytes = B * ((size_t)e->S * (8 + 8 + 4 + 4) + (size_t)e->C * 16);
+    const size_t H = (size_t)cfg->item.num_hashes;   // raw ids (8 bytes each) or pre-hashed rows (4 bytes x H each)
+    const size_t per_id = 8 > 4 * H ? 8 : 4 * H;
+    e->in_stage_bytes = B * ((size_t)e->S * (2 * per_id + 4 + 4) + (size_t)e->C * 2 * per_id);
     CU(cudaMalloc(&e->in_stage_dev, e->in_stage_bytes));
     CU(cudaMallocHost(&e->in_stage_host, e->in_stage_bytes));
     const size_t rows = B * (size_t)(e->C > 0 ? e->C : 1);
@@ -798,9 +807,9 @@ phx_status phx_set_blend(phx_engine* e, const phx_blend_spec* spec) {
 namespace {
 // the launches of one forward, in order, on the engine's stream
 phx_status enqueue_forward(phx_engine* e, const phx_rank_batch* bd, const phx_rank_out* od, int B, bool tokens_ready,
-                           const bf16* landing = nullptr, const int* pos = nullptr) {
+                           const bf16* landing = nullptr, const int* pos = nullptr, const phx_rank_batch_hashed* hb = nullptr) {
   phx_status s;
-  if (!tokens_ready && (s = build_tokens(e, bd, B, e->C, nullptr, nullptr, nullptr, nullptr, nullptr, landing, pos))) return s;
+  if (!tokens_ready && (s = build_tokens(e, bd, B, e->C, nullptr, nullptr, nullptr, nullptr, nullptr, landing, pos, hb))) return s;
   if ((s = run_trunk(e, B, e->T, e->S, e->S, e->split, e->n_tail))) return s;
   const bool f32 = e->fp32;
   HeadsArgs ha;
@@ -904,6 +913,62 @@ phx_status phx_rank_forward_rows_device(phx_engine* e, const phx_rank_batch* bd,
   PHX_CUDA_TRY(cudaEventRecord(e->ev1, e->stream), e->err);
   if (e->ev_done[0]) { e->done_idx ^= 1; PHX_CUDA_TRY(cudaEventRecord(e->ev_done[e->done_idx], e->stream), e->err); }
   return PHX_OK;
+}
+
+phx_status phx_rank_forward_hashed_device(phx_engine* e, const phx_rank_batch_hashed* hb, const phx_rank_out* od) {
+  if (!e || !hb || !od) return PHX_E_ARG;
+  if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
+  if (hb->batch < 0 || hb->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
+  if (!hb->hist_post_hashes || !hb->hist_author_hashes || !hb->cand_post_hashes || !hb->cand_author_hashes ||
+      !hb->hist_actions || !hb->hist_surfaces) { e->err = "phx_rank_forward_hashed: null input array"; return PHX_E_ARG; }
+  if (!params_complete(e, true) || !shards_complete(e)) return PHX_E_STATE;
+  cudaSetDevice(e->device);
+  const int B = hb->batch;
+  e->last_batch = B; e->last_launches = 0; e->prof_used = 0;
+  e->prefetch_valid = false;
+  e->graph_key_valid = false;   // plain launches: the graph cache is keyed on id batches
+  if (B == 0) return PHX_OK;
+  PHX_CUDA_TRY(cudaEventRecord(e->ev0, e->stream), e->err);
+  phx_status s;
+  if ((s = refresh_folded(e))) return s;
+  if ((s = enqueue_forward(e, nullptr, od, B, false, nullptr, nullptr, hb))) return s;
+  PHX_CUDA_TRY(cudaEventRecord(e->ev1, e->stream), e->err);
+  if (e->ev_done[0]) { e->done_idx ^= 1; PHX_CUDA_TRY(cudaEventRecord(e->ev_done[e->done_idx], e->stream), e->err); }
+  return PHX_OK;
+}
+
+phx_status phx_rank_forward_hashed(phx_engine* e, const phx_rank_batch_hashed* bh, const phx_rank_out* oh) {
+  if (!e || !bh || !oh) return PHX_E_ARG;
+  if (bh->batch < 0 || bh->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
+  if (!bh->hist_post_hashes || !bh->hist_author_hashes || !bh->cand_post_hashes || !bh->cand_author_hashes ||
+      !bh->hist_actions || !bh->hist_surfaces) { e->err = "phx_rank_forward_hashed: null input array"; return PHX_E_ARG; }
+  cudaSetDevice(e->device);
+  const size_t B = bh->batch, S = e->S, C = e->C, H = e->cfg.item.num_hashes;
+  if (B == 0) return PHX_OK;
+  uint8_t* hp = (uint8_t*)e->in_stage_host;
+  uint8_t* dp = (uint8_t*)e->in_stage_dev;
+  size_t off = 0;
+  phx_rank_batch_hashed bd; bd.batch = bh->batch; bd._pad = 0;
+  auto put = [&](const void* src, size_t bytes) { memcpy(hp + off, src, bytes); const void* d = dp + off; off += bytes; return (const int32_t*)d; };
+  bd.hist_post_hashes = put(bh->hist_post_hashes, B * S * H * 4);
+  bd.hist_author_hashes = put(bh->hist_author_hashes, B * S * H * 4);
+  bd.cand_post_hashes = put(bh->cand_post_hashes, B * C * H * 4);
+  bd.cand_author_hashes = put(bh->cand_author_hashes, B * C * H * 4);
+  bd.hist_actions = put(bh->hist_actions, B * S * 4);
+  bd.hist_surfaces = put(bh->hist_surfaces, B * S * 4);
+  PHX_CUDA_TRY(cudaMemcpyAsync(dp, hp, off, cudaMemcpyHostToDevice, e->stream), e->err);
+  phx_rank_out od; od.log_probs = e->lp_dev; od.continuous = e->cont_dev; od.scores = e->score_dev;
+  phx_status s = phx_rank_forward_hashed_device(e, &bd, &od);
+  if (s) return s;
+  const size_t rows = B * C;
+  if (oh->log_probs) PHX_CUDA_TRY(cudaMemcpyAsync(e->lp_host, e->lp_dev, rows * e->V * 4, cudaMemcpyDeviceToHost, e->stream), e->err);
+  if (oh->continuous) PHX_CUDA_TRY(cudaMemcpyAsync(e->cont_host, e->cont_dev, rows * e->NC * 4, cudaMemcpyDeviceToHost, e->stream), e->err);
+  if (oh->scores && e->has_blend) PHX_CUDA_TRY(cudaMemcpyAsync(e->score_host, e->score_dev, rows * 8, cudaMemcpyDeviceToHost, e->stream), e->err);
+  PHX_CUDA_TRY(cudaStreamSynchronize(e->stream), e->err);
+  if (oh->log_probs) memcpy(oh->log_probs, e->lp_host, rows * e->V * 4);
+  if (oh->continuous) memcpy(oh->continuous, e->cont_host, rows * e->NC * 4);
+  if (oh->scores && e->has_blend) memcpy(oh->scores, e->score_host, rows * 8);
+  return check_err_flag(e);
 }
 
 phx_status phx_rank_prefetch_device(phx_engine* e, const phx_rank_batch* bd) {

@@ -138,6 +138,29 @@ class PhoenixEngine:
         self._check(lib.phx_rank_forward(self._h, C.byref(b), C.byref(o)))
         return RankOutputs(lp, cont, sc)
 
+    def rank_hashed(self, hist_post_hashes, hist_author_hashes, hist_actions, hist_surfaces, cand_post_hashes,
+                    cand_author_hashes) -> RankOutputs:
+        """The forward from the reference batch-prep's own buffers (xai-recsys-engine/src/python.rs:1394-1440):
+        int32 unified-table rows [B,S,H] / [B,C,H], already hashed on the host; host arrays in and out."""
+        cfg = self.cfg
+        arrs = [np.ascontiguousarray(a, np.int32) for a in (hist_post_hashes, hist_author_hashes, hist_actions,
+                                                             hist_surfaces, cand_post_hashes, cand_author_hashes)]
+        B = arrs[0].shape[0]
+        assert arrs[0].shape == (B, cfg.history_len, cfg.num_hashes) and arrs[4].shape == (B, cfg.num_candidates, cfg.num_hashes)
+        lp = np.empty((B, cfg.num_candidates, cfg.num_actions), np.float32)
+        cont = np.empty((B, cfg.num_candidates, cfg.num_continuous), np.float32)
+        sc = np.empty((B, cfg.num_candidates), np.float64) if self._has_blend else None
+        b = self._batch_struct(B, *arrs)
+        o = _lib.RankOut(_ptr(lp), _ptr(cont), _ptr(sc))
+        self._check(lib.phx_rank_forward_hashed(self._h, C.byref(b), C.byref(o)))
+        return RankOutputs(lp, cont, sc)
+
+    def rank_hashed_device(self, B, hp, ha, act, srf, cp, ca, lp, cont, sc=None):
+        """Same with device tensors (int32 rows), asynchronous on the engine's stream."""
+        b = self._batch_struct(B, hp, ha, act, srf, cp, ca)
+        o = _lib.RankOut(_ptr(lp), _ptr(cont), _ptr(sc))
+        self._check(lib.phx_rank_forward_hashed_device(self._h, C.byref(b), C.byref(o)))
+
     def rank_submit(self, inp: RankInputs, slot: int) -> None:
         """Start a host-buffer request in pipeline slot 0 or 1 and return at once (the inputs are copied before the
         call returns).  `rank_collect(slot)` delivers its results; with both slots in flight the host-side copies of
