@@ -595,6 +595,15 @@ class ValueModelWeights:
     post_unexplored_include_out_of_network: bool = False
     bidirectional_follow_reply_weight_boost: float = 0.0
     bidirectional_follow_dwell_weight_boost: float = 0.0
+    enable_author_diversity: bool = False
+    author_diversity_decay: float = 0.0
+    author_diversity_floor: float = 0.0
+    oon_rescore_in_network_replies_retweets: bool = False
+    multiplier_pre_offset: bool = False
+    multiplicative: bool = False
+    not_dwelled_power_exponent: float = 0.0
+    not_dwelled_power_offset: float = 0.0
+    engage_bias: float = 0.0
 
     def get(self, k: str) -> float:
         return float(self.w.get(k, 0.0))
@@ -613,6 +622,18 @@ class ValueModelWeights:
 
     def total_sum(self) -> float:  # weights.rs:87-89
         return self.positive_sum() + self.negative_sum()
+
+    def multiplicative_negative_sum(self) -> float:  # weights.rs:91-93
+        return -(self.get("not_interested") + self.get("block_author") + self.get("mute_author") + self.get("report"))
+
+    def multiplicative_total_sum(self) -> float:  # weights.rs:95-97
+        return self.positive_sum() + self.engage_bias + self.multiplicative_negative_sum()
+
+    def offset_negative_sum(self) -> float:  # weights.rs:99-105
+        return self.multiplicative_negative_sum() if self.multiplicative else self.negative_sum()
+
+    def offset_total_sum(self) -> float:  # weights.rs:107-113
+        return self.multiplicative_total_sum() if self.multiplicative else self.total_sum()
 
 
 # order of the 30 terms of `weighted_terms` (xai-value-model/scoring.rs:145-260)
@@ -685,9 +706,187 @@ def offset_score(combined: float, total_sum: float, negative_sum: float) -> floa
     return combined + NEGATIVE_SCORES_OFFSET
 
 
+MIN_NOT_DWELLED_POWER_OFFSET = 1e-2  # weights.rs:5
+MIN_SKIP_BASE = 1e-6                 # scoring.rs:4
+
+
+def multiplicative_score(wt: ValueModelWeights, scores: Dict[str, float], **kw) -> float:
+    """scoring.rs:75-110: skip(not_dwelled) * (engage + bias) * (1 + max(dwell-time term, 0)), then the offset."""
+    engage = 0.0
+    for name, t in weighted_terms(wt, scores, **kw):      # engage_sum, 91-97
+        if name != "dwell_time" and name != "not_dwelled":
+            engage = engage + t
+    engage = engage + wt.engage_bias
+    ts, ns = wt.offset_total_sum(), wt.offset_negative_sum()
+    if engage < 0.0:
+        return offset_score(engage, ts, ns)
+    p = scores.get("not_dwelled")
+    if p is None or not math.isfinite(p) or wt.not_dwelled_power_exponent == 0.0:     # skip_score, 75-89
+        skip = 1.0
+    else:
+        skip = max(p + max(wt.not_dwelled_power_offset, MIN_NOT_DWELLED_POWER_OFFSET), MIN_SKIP_BASE) ** wt.not_dwelled_power_exponent
+    dt = scores.get("dwell_time")
+    time_factor = 1.0 + max((0.0 if dt is None else float(dt)) * wt.get("cont_dwell_time"), 0.0)   # 99-101
+    return offset_score(skip * engage * time_factor, ts, ns)
+
+
 def fuse_heads(wt: ValueModelWeights, scores: Dict[str, float], **kw) -> float:
-    """scoring.rs:67-73, weighted mode."""
-    return offset_score(compute_weighted_score(wt, scores, **kw), wt.total_sum(), wt.negative_sum())
+    """scoring.rs:67-73."""
+    if wt.multiplicative:
+        return multiplicative_score(wt, scores, **kw)
+    return offset_score(compute_weighted_score(wt, scores, **kw), wt.offset_total_sum(), wt.offset_negative_sum())
+
+
+@dataclass
+class ScoringCandidate:
+    """CandidateScoringInputs (xai-value-model/inputs.rs:3-17)."""
+
+    scores: Dict[str, float] = field(default_factory=dict)      # PhoenixScores: a missing key is None
+    author_id: int = 0
+    in_network: Optional[bool] = None
+    is_reply: bool = False
+    is_retweet: bool = False
+    is_mutual_follow_author: bool = False
+    vqv_eligible: bool = False
+    quoted_vqv_eligible: bool = False
+    cold_start_lift_to_rank: Optional[int] = None
+    weighted_score: Optional[float] = None
+    author_exploration_bonus: float = 0.0
+    user_video_continuation_secs: Optional[float] = None
+
+    def gates(self) -> dict:
+        return dict(vqv_eligible=self.vqv_eligible, quoted_vqv_eligible=self.quoted_vqv_eligible,
+                    in_network=self.in_network,
+                    boost_eligible=(not self.is_reply and not self.is_retweet and self.is_mutual_follow_author),  # inputs.rs:19-23
+                    user_video_continuation_secs=self.user_video_continuation_secs)
+
+
+@dataclass
+class ScoringContext:
+    """QueryScoringContext (inputs.rs:43-56); a factor pair is (engagement, dwell_time) or None."""
+
+    effective_oon_weight: float = 1.0
+    oon_factors: Optional[Tuple[float, float]] = None
+    in_network_factors: Optional[Tuple[float, float]] = None
+
+
+def class_factors(engagement: float, dwell_time: float) -> Optional[Tuple[float, float]]:
+    """ClassFactors::new (inputs.rs:32-40): finite and non-negative, else None."""
+    ok = lambda f: math.isfinite(f) and f >= 0.0
+    return (engagement, dwell_time) if ok(engagement) and ok(dwell_time) else None
+
+
+def set_user_video_continuation(cands: List[ScoringCandidate]) -> None:
+    """scoring.rs:263-280: open-weighted mean continuation over the request, left-to-right f64 folds."""
+    secs, opens = 0.0, 0.0
+    for c in cands:
+        o, cont = c.scores.get("video_open"), c.scores.get("home_video_continuation_secs")
+        if o is None or cont is None:
+            continue
+        secs, opens = secs + o * cont, opens + o
+    user = secs / opens if opens > 0.0 else None
+    for c in cands:
+        c.user_video_continuation_secs = user
+
+
+def unoffset_score(weighted: float, total_sum: float, negative_sum: float) -> float:
+    """scoring.rs:293-302."""
+    if total_sum == 0.0:
+        return weighted
+    if weighted < NEGATIVE_SCORES_OFFSET:
+        return weighted / NEGATIVE_SCORES_OFFSET * total_sum - negative_sum
+    return weighted - NEGATIVE_SCORES_OFFSET
+
+
+def diversity_multiplier(decay: float, floor: float, exponent: float) -> float:
+    """scoring.rs:304-306."""
+    return (1.0 - floor) * decay ** exponent + floor
+
+
+def author_pool_counts(author_ids: Sequence[int], ordering_scores: Sequence[float]) -> List[int]:
+    """scoring.rs:308-327: walk the candidates by score, highest first (stable: equal scores keep their order);
+    each gets the number of candidates of the same author seen before it."""
+    order = sorted(range(len(ordering_scores)), key=lambda i: -ordering_scores[i])   # Python's sort is stable
+    counts, seen = [0] * len(author_ids), {}
+    for i in order:
+        k = seen.get(author_ids[i], 0)
+        counts[i] = k
+        seen[author_ids[i]] = k + 1
+    return counts
+
+
+def oon_applies(wt: ValueModelWeights, c: ScoringCandidate) -> bool:
+    """scoring.rs:329-338."""
+    if c.in_network is False:
+        return True
+    if c.in_network is True:
+        return wt.oon_rescore_in_network_replies_retweets and (c.is_reply or c.is_retweet)
+    return False
+
+
+def class_factor_score(wt: ValueModelWeights, ctx: ScoringContext, c: ScoringCandidate, score: float) -> Optional[float]:
+    """scoring.rs:340-366."""
+    if wt.multiplicative or c.in_network is None:
+        return None
+    if c.in_network:
+        level = ctx.effective_oon_weight if oon_applies(wt, c) else 1.0
+        factors = ctx.in_network_factors
+    else:
+        level, factors = 1.0, ctx.oon_factors
+    if factors is None:
+        return None
+    dt = c.scores.get("dwell_time")
+    dwell = (0.0 if dt is None else float(dt)) * wt.get("cont_dwell_time")
+    if score >= NEGATIVE_SCORES_OFFSET and math.isfinite(dwell):
+        dwell = min(max(dwell, 0.0), score)      # f64::clamp(0.0, score)
+    else:
+        dwell = 0.0
+    return level * (factors[0] * (score - dwell) + factors[1] * dwell)
+
+
+def post_fusion_multipliers(wt: ValueModelWeights, ctx: ScoringContext, cands: List[ScoringCandidate],
+                            ordering_scores: Sequence[float]) -> List[Tuple[float, float]]:
+    """scoring.rs:368-402 -> (author_diversity, oon) per candidate."""
+    if wt.enable_author_diversity:
+        div = [diversity_multiplier(wt.author_diversity_decay, wt.author_diversity_floor, float(k))
+               for k in author_pool_counts([c.author_id for c in cands], ordering_scores)]
+    else:
+        div = [1.0] * len(cands)
+    return [(d, ctx.effective_oon_weight if oon_applies(wt, c) else 1.0) for c, d in zip(cands, div)]
+
+
+def apply_cold_start_decisions(scores: Sequence[float], cands: List[ScoringCandidate]) -> List[float]:
+    """scoring.rs:414-431: the first candidate that carries a lift rank is raised to the score at that rank."""
+    eff = list(scores)
+    lift = next(((i, c.cold_start_lift_to_rank) for i, c in enumerate(cands) if c.cold_start_lift_to_rank is not None), None)
+    if lift is not None and lift[1] < len(scores):
+        ranked = sorted(scores, reverse=True)
+        eff[lift[0]] = max(eff[lift[0]], ranked[lift[1]])
+    return eff
+
+
+def compute_value_scores(wt: ValueModelWeights, ctx: ScoringContext, cands: List[ScoringCandidate]):
+    """scoring.rs:404-412, 433-489 -> (weighted, scores)."""
+    ts, ns = wt.offset_total_sum(), wt.offset_negative_sum()
+    weighted = [c.weighted_score if (c.weighted_score is not None and not wt.multiplicative)
+                else fuse_heads(wt, c.scores, **c.gates()) for c in cands]
+    if wt.multiplier_pre_offset:
+        mult = post_fusion_multipliers(wt, ctx, cands, weighted)
+        pre = []
+        for wv, c, (d, o) in zip(weighted, cands, mult):
+            net = unoffset_score(wv, ts, ns) + c.author_exploration_bonus
+            pre.append(offset_score((d * o) * net if net >= 0.0 else net, ts, ns))
+        return weighted, apply_cold_start_decisions(pre, cands)
+    base = [wv if c.author_exploration_bonus == 0.0 else
+            offset_score(unoffset_score(wv, ts, ns) + c.author_exploration_bonus, ts, ns)      # add_exploration_bonus, 491-496
+            for wv, c in zip(weighted, cands)]
+    adjusted = apply_cold_start_decisions(base, cands)
+    mult = post_fusion_multipliers(wt, ctx, cands, adjusted)
+    scores = []
+    for sv, (d, o), c in zip(adjusted, mult, cands):
+        cs = class_factor_score(wt, ctx, c, sv)
+        scores.append(cs * d if cs is not None else sv * d * o)
+    return weighted, scores
 
 
 # The 19 discrete heads of the BASELINE workload, named after the PhoenixScores fields they

@@ -261,3 +261,110 @@ def test_candidate_only_tail_layers_restated_layer_by_layer():
     lp_full, _, _ = po.rank_forward(dataclasses.replace(cfg, num_candidate_only_layers=0), w, rows, b)
     valid = b.cand_post_ids != 0
     assert not np.allclose(lp[valid], lp_full[valid], rtol=1e-4, atol=1e-6)
+
+
+# ---- full value model: known answers of xai-value-model/scoring.rs' own tests ---------------------------------------
+
+def value_model_kats():
+    """(name, weights, context, candidates, expected weighted or None, expected scores) for every known-answer test
+    of xai-value-model/scoring.rs that goes through compute_value_scores; inputs and expected expressions as written
+    there (lines cited per case)."""
+    SC, CTX = po.ScoringCandidate, po.ScoringContext
+    out = []
+    # hand_computed_parity, scoring.rs:498-636
+    wt = po.ValueModelWeights(
+        w=dict(favorite=2.0, reply=4.0, retweet=1.0, dwell=0.5, vqv=3.0, cont_dwell_time=0.1, cont_click_dwell_time=0.2,
+               post_unexplored=1.5, post_video=2.5, report=-100.0, not_interested=-10.0),
+        bidirectional_follow_reply_weight_boost=1.0, bidirectional_follow_dwell_weight_boost=0.5,
+        enable_author_diversity=True, author_diversity_decay=0.5, author_diversity_floor=0.25,
+        oon_rescore_in_network_replies_retweets=True)
+    cands = [
+        SC(dict(favorite=0.5, reply=0.1, dwell=0.4, dwell_time=10.0, post_unexplored=0.2, post_video=0.04), author_id=1,
+           in_network=True, is_mutual_follow_author=True),
+        SC(dict(favorite=0.2, vqv=0.9, click_dwell_time=5.0, post_unexplored=0.2), author_id=2, in_network=False),
+        SC(dict(favorite=0.05, vqv=0.5, click_dwell_time=5.0), author_id=1, in_network=True, vqv_eligible=True),
+        SC(dict(favorite=0.01, report=0.05), author_id=3, in_network=True, is_reply=True, is_mutual_follow_author=True)]
+    off = 0.001
+    pos, negm = 2.0 + 4.0 + 1.0 + 0.5 + 3.0 + 1.5 + 2.5, 10.0 + 100.0
+    w0 = 2.0 * 0.5 + (4.0 + 1.0) * 0.1 + (0.5 + 0.5) * 0.4 + 0.1 * 10.0 + 1.5 * 0.2 + 2.5 * 0.04 + off
+    w1 = 2.0 * 0.2 + 0.2 * 5.0 + off
+    w2 = 2.0 * 0.05 + 3.0 * 0.5 + 0.2 * 5.0 + off
+    w3 = ((2.0 * 0.01 - 100.0 * 0.05) + negm) / (pos + negm) * off
+    div2 = (1.0 - 0.25) * 0.5 + 0.25
+    out.append(("hand_computed_parity", wt, CTX(effective_oon_weight=0.75), cands, [w0, w1, w2, w3],
+                [w0, w1 * 0.75, w2 * div2, w3 * 0.75]))
+    # class_factors_scale_dwell_time_and_engagement_separately, scoring.rs:638-724
+    cfw = lambda **kw: po.ValueModelWeights(w=dict(favorite=2.0, cont_dwell_time=0.1, report=-100.0),
+                                            oon_rescore_in_network_replies_retweets=True, **kw)
+    cfc = lambda inn, fav, dw, **kw: SC(dict(favorite=fav, **({} if dw is None else dict(dwell_time=dw))), in_network=inn, **kw)
+    rep = lambda inn, r: SC(dict(report=r, dwell_time=4.0), in_network=inn)
+    ctx = CTX(0.75, po.class_factors(0.6, 0.9), po.class_factors(1.2, 0.7))
+    cands = [cfc(False, 0.2, 4.0), cfc(True, 0.2, 4.0), cfc(True, 0.2, 4.0, is_reply=True), cfc(False, 0.2, None),
+             cfc(None, 0.2, 4.0), rep(False, 0.003), rep(True, 0.003), rep(False, 0.05)]
+    eng, dwell = 2.0 * 0.2 + off, 0.1 * 4.0
+    capped = 0.4 - 100.0 * 0.003 + off
+    negative = (0.4 - 100.0 * 0.05 + 100.0) / 102.0 * off
+    out.append(("class_factors_separately", cfw(), ctx, cands, None,
+                [0.6 * eng + 0.9 * dwell, 1.2 * eng + 0.7 * dwell, 0.75 * (1.2 * eng + 0.7 * dwell), 0.6 * eng,
+                 eng + dwell, 0.9 * capped, 0.7 * capped, 0.6 * negative]))
+    # class_factors_use_a_cached_weighted_score, scoring.rs:770-790
+    out.append(("cached_weighted", cfw(), CTX(0.75, po.class_factors(0.6, 0.9), None),
+                [cfc(False, 0.2, 4.0, weighted_score=1.0), cfc(True, 0.2, 4.0, weighted_score=1.0)], [1.0, 1.0],
+                [0.6 * (1.0 - 0.4) + 0.9 * 0.4, 1.0]))
+    return out
+
+
+@pytest.mark.parametrize("case", value_model_kats(), ids=lambda c: c[0])
+def test_value_model_known_answers(case):
+    _, wt, ctx, cands, want_w, want_s = case
+    weighted, scores = po.compute_value_scores(wt, ctx, cands)
+    np.testing.assert_allclose(scores, want_s, rtol=0, atol=1e-12)
+    if want_w is not None:
+        np.testing.assert_allclose(weighted, want_w, rtol=0, atol=1e-12)
+
+
+def neutral_factor_case():
+    """neutral_class_factors_match_the_single_oon_factor, scoring.rs:726-769."""
+    SC, CTX = po.ScoringCandidate, po.ScoringContext
+    wt = po.ValueModelWeights(w=dict(favorite=2.0, cont_dwell_time=0.1, report=-100.0),
+                              oon_rescore_in_network_replies_retweets=True, enable_author_diversity=True,
+                              author_diversity_decay=0.5, author_diversity_floor=0.25)
+    cfc = lambda inn, fav, dw, **kw: SC(dict(favorite=fav, **({} if dw is None else dict(dwell_time=dw))), in_network=inn, **kw)
+    cands = [cfc(False, 0.2, 4.0), cfc(False, 0.1, 9.0), cfc(True, 0.2, 4.0), cfc(True, 0.3, 8.0, is_retweet=True),
+             cfc(False, 0.2, None), cfc(None, 0.2, 4.0), SC(dict(report=0.05, dwell_time=4.0), in_network=False)]
+    single = CTX(effective_oon_weight=0.75)
+    neutral = CTX(0.75, po.class_factors(0.75, 0.75), po.class_factors(1.0, 1.0))
+    return wt, single, neutral, cands
+
+
+def test_value_model_neutral_factors_and_modes():
+    wt, single, neutral, cands = neutral_factor_case()
+    want_w, want = po.compute_value_scores(wt, single, cands)
+    _, got = po.compute_value_scores(wt, neutral, cands)
+    np.testing.assert_allclose(got, want, rtol=0, atol=1e-12)
+    assert want[1] < 0.75 * want_w[1]          # all seven share author 0: diversity decays the second one
+    # class factors are ignored in multiplicative and pre-offset modes, scoring.rs:792-821
+    import dataclasses
+    ctx = po.ScoringContext(0.75, po.class_factors(0.6, 0.9), po.class_factors(1.2, 0.7))
+    base = po.ValueModelWeights(w=dict(favorite=2.0, cont_dwell_time=0.1, report=-100.0), oon_rescore_in_network_replies_retweets=True)
+    two = cands[:1] + cands[2:3]
+    for w2 in (dataclasses.replace(base, multiplicative=True), dataclasses.replace(base, multiplier_pre_offset=True)):
+        assert po.compute_value_scores(w2, ctx, two) == po.compute_value_scores(w2, single, two)
+    assert po.class_factors(0.0, 0.0) is not None and po.class_factors(-1.0, 0.9) is None        # 823-837
+    assert po.class_factors(float("nan"), 0.9) is None and po.class_factors(0.6, float("inf")) is None
+
+
+def test_value_model_multiplicative_known_answer():
+    # multiplicative_score_is_skip_times_engage_times_time, scoring.rs:839-896
+    import dataclasses
+    wt = po.ValueModelWeights(w=dict(favorite=0.5, video_continuation=0.003, report=-100.0, cont_dwell_time=0.1),
+                              multiplicative=True, not_dwelled_power_exponent=-0.5, not_dwelled_power_offset=0.11, engage_bias=0.1)
+    pos = dict(favorite=0.4, video_open=0.5, home_video_continuation_secs=10.0, dwell_time=20.0, not_dwelled=0.25)
+    want = 0.36 ** -0.5 * 0.315 * 3.0 + 0.001
+    got = po.fuse_heads(wt, pos)
+    assert abs(got - want) < 1e-12
+    toxic = po.fuse_heads(wt, dict(report=0.05, dwell_time=20.0, not_dwelled=0.25))
+    assert toxic < 0.002 and toxic < got
+    stale = po.ScoringCandidate(dict(pos), weighted_score=99.0)
+    assert abs(po.compute_value_scores(wt, po.ScoringContext(), [stale])[0][0] - want) < 1e-12
+    assert abs(po.compute_value_scores(dataclasses.replace(wt, multiplicative=False), po.ScoringContext(), [stale])[0][0] - 99.0) < 1e-12
