@@ -377,6 +377,72 @@ phx_status phx_corpus_sync(phx_corpus* c);
 phx_status phx_corpus_last_device_ms(phx_corpus* c, float* ms);
 const char* phx_corpus_last_error(const phx_corpus* c);
 
+/* ---- value model after the heads (xai-value-model/scoring.rs) ---------------------------------- */
+
+/* PhoenixScores fields in declaration order (xai-value-model/phoenix_scores.rs:2-32): favorite, reply, retweet,
+ * photo_expand, video_open, click, open_link, profile_click, vqv, share, share_via_dm, share_via_copy_link, dwell,
+ * quote, quoted_click, quoted_vqv, follow_author, not_interested, block_author, mute_author, report, not_dwelled,
+ * post_unexplored, post_video, grok_analyze, dwell_time, click_dwell_time, home_video_continuation_secs,
+ * home_profile_visit_secs. */
+#define PHX_VM_FIELDS 29
+#define PHX_VM_TERMS 30
+#define PHX_VM_MAX_CANDIDATES 4096
+
+/* ValueModelWeights (xai-value-model/weights.rs:8-53) in the form the scoring functions read it. */
+typedef struct phx_value_model {
+  /* where each PhoenixScores field comes from: column j < num_actions is exp(log_probs[j]) (the wire conversion,
+   * home-mixer/candidate_pipeline/performance_tests.rs:516-521), num_actions + j is continuous[j], -1 = None */
+  int32_t src[32];
+  /* the weight of each of the 30 terms of weighted_terms, in its order (scoring.rs:145-260), before the per-candidate
+   * gates: favorite, reply, retweet, photo_expand, video_open, click, open_link, profile_click, vqv, share,
+   * share_via_dm, share_via_copy_link, dwell, quote, quoted_click, quoted_vqv, cont_dwell_time,
+   * cont_click_dwell_time, video_continuation, user_video_continuation, profile_visit_secs, follow_author,
+   * not_interested, block_author, mute_author, report, not_dwelled, post_unexplored, post_video, grok_analyze */
+  double w[PHX_VM_TERMS];
+  double reply_boost, dwell_boost;                 /* bidirectional_follow_*_weight_boost */
+  double author_diversity_decay, author_diversity_floor;
+  double not_dwelled_power_exponent, not_dwelled_power_offset, engage_bias;
+  double offset_total_sum, offset_negative_sum;    /* weights.rs:99-113 */
+  int32_t post_unexplored_include_oon, enable_author_diversity, oon_rescore_in_network_replies_retweets;
+  int32_t multiplier_pre_offset, multiplicative, _pad;
+} phx_value_model;
+
+/* bits of phx_value_inputs.flags (CandidateScoringInputs, xai-value-model/inputs.rs:3-17) */
+#define PHX_VM_IN_NETWORK_KNOWN 1
+#define PHX_VM_IN_NETWORK 2
+#define PHX_VM_IS_REPLY 4
+#define PHX_VM_IS_RETWEET 8
+#define PHX_VM_MUTUAL_FOLLOW 16
+#define PHX_VM_VQV_ELIGIBLE 32
+#define PHX_VM_QUOTED_VQV_ELIGIBLE 64
+
+/* One batch of requests for the value model: DEVICE pointers, per candidate [B,C] unless noted.  Optional arrays may
+ * be NULL. */
+typedef struct phx_value_inputs {
+  int32_t batch, num_candidates, num_actions, num_continuous;
+  const float* log_probs;            /* [B,C,V] as phx_rank_out.log_probs */
+  const float* continuous;           /* [B,C,NC] */
+  const double* weighted;            /* cached weighted_score (phx_rank_out.scores) or NULL: fuse_heads is run */
+  const int64_t* author_ids;
+  const uint8_t* flags;              /* PHX_VM_* bits; NULL = all zero */
+  const double* exploration_bonus;   /* NULL = 0 */
+  const int32_t* cold_start_rank;    /* cold_start_lift_to_rank, -1 = None; NULL = none */
+  const int32_t* num_valid;          /* [B] candidates of each request (the rest are ignored); NULL = C */
+  const double* context;             /* [B,5] effective_oon_weight, oon engagement / dwell_time factors, in-network
+                                        engagement / dwell_time factors (a NaN engagement factor = None); NULL =
+                                        QueryScoringContext::default() */
+} phx_value_inputs;
+
+/* compute_value_scores (xai-value-model/scoring.rs:404-489) for B requests, one thread block per request:
+ * fuse_heads with the per-candidate gates, the multiplicative mode and the request's user_video_continuation
+ * (scoring.rs:67-280) unless a cached weighted score is given; exploration bonus; cold-start lift; author diversity
+ * (rank among the same author's candidates by score, ties in input order); out-of-network weight; class factors.
+ * Writes weighted_out / scores_out f64 [B,C] (weighted_out may be NULL) on `stream` (a cudaStream_t, NULL = default
+ * stream).  Replaces home-mixer's value-model scorer calling into xai-value-model on the CPU
+ * (home-mixer/scorers/value_model.rs). */
+phx_status phx_value_scores_device(int32_t device, const phx_value_model* model, const phx_value_inputs* in,
+                                   double* weighted_out, double* scores_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -697,3 +697,130 @@ def test_sharded_ranker_world1_matches_plain_forward(torch):
         eng.close()
     finally:
         dist.destroy_process_group()
+
+
+# ---- full value model (xai-value-model/scoring.rs:404-489) ----------------------------------------------------------
+
+VM_HEADS = ["favorite", "reply", "retweet", "photo_expand", "video_open", "click", "open_link", "profile_click", "vqv", "share",
+            "share_via_dm", "share_via_copy_link", "dwell", "quote", "quoted_click", "quoted_vqv", "follow_author",
+            "not_interested", "block_author", "mute_author", "report", "not_dwelled", "post_unexplored", "post_video",
+            "grok_analyze"]
+VM_CONTS = ["dwell_time", "click_dwell_time", "home_video_continuation_secs", "home_profile_visit_secs"]
+
+
+def _vm_run(torch, wt, requests, contexts):
+    """Run the kernel and the oracle on the same requests (lists of po.ScoringCandidate, one context each).  The kernel
+    reads f32 log-probabilities, so the oracle is given exp(f64(f32(ln p))) - the wire conversion - as its
+    probabilities; a field a candidate lacks is probability / value 0."""
+    import dataclasses
+    import x_algorithm_b200.value_model as vm
+    B, C = len(requests), max(len(r) for r in requests)
+    V, NC = len(VM_HEADS), len(VM_CONTS)
+    lp = np.full((B, C, V), -np.inf, np.float32)
+    cont = np.zeros((B, C, NC), np.float32)
+    auth = np.zeros((B, C), np.int64); flags = np.zeros((B, C), np.uint8)
+    bonus = np.zeros((B, C), np.float64); lift = np.full((B, C), -1, np.int32)
+    cached = np.full((B, C), np.nan, np.float64)
+    nvalid = np.array([len(r) for r in requests], np.int32)
+    ctxa = np.zeros((B, 5), np.float64)
+    oracle_reqs = []
+    for b, (req, ctx) in enumerate(zip(requests, contexts)):
+        ctxa[b] = [ctx.effective_oon_weight, *(ctx.oon_factors or (np.nan, np.nan)), *(ctx.in_network_factors or (np.nan, np.nan))]
+        oreq = []
+        for i, c in enumerate(req):
+            sc = {}
+            for j, h in enumerate(VM_HEADS):
+                if h in c.scores:
+                    with np.errstate(divide="ignore"):
+                        lp[b, i, j] = np.float32(np.log(c.scores[h]))
+                sc[h] = float(np.exp(np.float64(lp[b, i, j])))
+            for j, h in enumerate(VM_CONTS):
+                cont[b, i, j] = np.float32(c.scores.get(h, 0.0)); sc[h] = float(cont[b, i, j])
+            auth[b, i] = c.author_id
+            flags[b, i] = ((vm.IN_NETWORK_KNOWN if c.in_network is not None else 0) | (vm.IN_NETWORK if c.in_network else 0)
+                           | (vm.IS_REPLY if c.is_reply else 0) | (vm.IS_RETWEET if c.is_retweet else 0)
+                           | (vm.MUTUAL_FOLLOW if c.is_mutual_follow_author else 0) | (vm.VQV_ELIGIBLE if c.vqv_eligible else 0)
+                           | (vm.QUOTED_VQV_ELIGIBLE if c.quoted_vqv_eligible else 0))
+            bonus[b, i] = c.author_exploration_bonus
+            lift[b, i] = -1 if c.cold_start_lift_to_rank is None else c.cold_start_lift_to_rank
+            if c.weighted_score is not None:
+                cached[b, i] = c.weighted_score
+            oreq.append(dataclasses.replace(c, scores=sc))
+        po.set_user_video_continuation(oreq)
+        oracle_reqs.append(oreq)
+    use_cached = not np.isnan(cached[nvalid[:, None] > np.arange(C)[None]]).any()
+    pw = vm.ValueModelWeights(**{f.name: getattr(wt, f.name) for f in dataclasses.fields(wt)})
+    model = vm.value_model_struct(pw, VM_HEADS, VM_CONTS)
+    cu = lambda a: torch.from_numpy(a).cuda()
+    w_got, s_got = vm.value_scores(model, cu(lp), cu(cont), cu(auth), weighted=cu(cached) if use_cached else None,
+                                   flags=cu(flags), exploration_bonus=cu(bonus), cold_start_rank=cu(lift),
+                                   num_valid=cu(nvalid), context=cu(ctxa))
+    torch.cuda.synchronize()
+    w_got, s_got = w_got.cpu().numpy(), s_got.cpu().numpy()
+    out = []
+    for b, (oreq, ctx) in enumerate(zip(oracle_reqs, contexts)):
+        if not use_cached:
+            oreq = [dataclasses.replace(c, weighted_score=None) for c in oreq]
+        w_want, s_want = po.compute_value_scores(wt, ctx, oreq)
+        n = len(oreq)
+        np.testing.assert_allclose(w_got[b, :n], w_want, rtol=1e-12, atol=1e-15)
+        np.testing.assert_allclose(s_got[b, :n], s_want, rtol=1e-12, atol=1e-15)
+        assert (s_got[b, n:] == 0).all()
+        out.append((w_got[b, :n], s_got[b, :n]))
+    return out
+
+
+def test_value_model_kernel_known_answers(torch):
+    """The known answers of xai-value-model/scoring.rs' own tests through the kernel: equal to the oracle to 1e-12 on
+    the kernel's inputs, and to the reference's expected numbers to the f32 precision of the log-probabilities."""
+    from tests.test_oracle_golden import value_model_kats, neutral_factor_case
+    for name, wt, ctx, cands, want_w, want_s in value_model_kats():
+        (w_got, s_got), = _vm_run(torch, wt, [cands], [ctx])
+        np.testing.assert_allclose(s_got, want_s, rtol=2e-6, atol=1e-9, err_msg=name)
+        if want_w is not None:
+            np.testing.assert_allclose(w_got, want_w, rtol=2e-6, atol=1e-9, err_msg=name)
+    wt, single, neutral, cands = neutral_factor_case()
+    (_, a), (_, b) = _vm_run(torch, wt, [cands, cands], [single, neutral])
+    np.testing.assert_allclose(a, b, rtol=1e-12)
+
+
+@pytest.mark.parametrize("mode", ["weighted", "pre_offset", "multiplicative", "cached"])
+def test_value_model_kernel_vs_oracle_random(torch, mode):
+    """Random requests: ragged candidate counts (up to 700 per request), few authors (so author diversity bites), tied
+    scores (duplicated candidates: ties rank in input order), every gate, bonus, cold-start lift and context form."""
+    rng = np.random.default_rng({"weighted": 1, "pre_offset": 2, "multiplicative": 3, "cached": 4}[mode])
+    w = {h: float(rng.uniform(0.0, 5.0)) for h in VM_HEADS}
+    for h in ("not_interested", "block_author", "mute_author", "report", "not_dwelled"):
+        w[h] = -float(rng.uniform(1.0, 100.0))
+    w.update(cont_dwell_time=0.01, cont_click_dwell_time=0.02, video_continuation=0.003, user_video_continuation=0.002,
+             profile_visit_secs=0.004)
+    wt = po.ValueModelWeights(w=w, post_unexplored_include_out_of_network=False, bidirectional_follow_reply_weight_boost=1.5,
+                              bidirectional_follow_dwell_weight_boost=0.25, enable_author_diversity=True,
+                              author_diversity_decay=0.6, author_diversity_floor=0.2, oon_rescore_in_network_replies_retweets=True,
+                              multiplier_pre_offset=(mode == "pre_offset"), multiplicative=(mode == "multiplicative"),
+                              not_dwelled_power_exponent=-0.5, not_dwelled_power_offset=0.11, engage_bias=0.1)
+    requests, contexts = [], []
+    for n in (1, 2, 37, 256, 700):
+        req = []
+        for i in range(n):
+            sc = {h: float(rng.uniform(0.0, 0.3) if h not in ("report", "block_author", "mute_author", "not_interested")
+                           else rng.uniform(0.0, 0.02)) for h in VM_HEADS}
+            sc.update(dwell_time=float(rng.uniform(0, 30)), click_dwell_time=float(rng.uniform(0, 10)),
+                      home_video_continuation_secs=float(rng.uniform(0, 20)), home_profile_visit_secs=float(rng.uniform(0, 5)))
+            req.append(po.ScoringCandidate(
+                scores=sc, author_id=int(rng.integers(1, max(2, n // 4 + 1))),
+                in_network=[None, True, False][int(rng.integers(0, 3))], is_reply=bool(rng.random() < 0.2),
+                is_retweet=bool(rng.random() < 0.2), is_mutual_follow_author=bool(rng.random() < 0.5),
+                vqv_eligible=bool(rng.random() < 0.5), quoted_vqv_eligible=bool(rng.random() < 0.5),
+                author_exploration_bonus=float(rng.uniform(-0.5, 0.5)) if rng.random() < 0.3 else 0.0,
+                weighted_score=float(rng.uniform(-0.0005, 3.0)) if mode == "cached" else None))
+        if n >= 4:
+            import dataclasses
+            req[3] = dataclasses.replace(req[1])               # an exact tie: same scores, same author
+            req[n // 2].cold_start_lift_to_rank = n // 3
+            req[n - 1].cold_start_lift_to_rank = 0             # ignored: only the first candidate with a lift counts
+        requests.append(req)
+        contexts.append([po.ScoringContext(), po.ScoringContext(0.75), po.ScoringContext(0.6, po.class_factors(0.6, 0.9), None),
+                         po.ScoringContext(0.8, po.class_factors(0.5, 1.1), po.class_factors(1.2, 0.7)),
+                         po.ScoringContext(0.9, None, po.class_factors(1.1, 0.9))][len(contexts)])
+    _vm_run(torch, wt, requests, contexts)

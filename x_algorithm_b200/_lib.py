@@ -51,6 +51,23 @@ class RankOut(C.Structure):
     _fields_ = [("log_probs", C.c_void_p), ("continuous", C.c_void_p), ("scores", C.c_void_p)]
 
 
+class ValueModel(C.Structure):   # phx_value_model
+    _fields_ = [("src", C.c_int32 * 32), ("w", C.c_double * 30), ("reply_boost", C.c_double), ("dwell_boost", C.c_double),
+                ("author_diversity_decay", C.c_double), ("author_diversity_floor", C.c_double),
+                ("not_dwelled_power_exponent", C.c_double), ("not_dwelled_power_offset", C.c_double),
+                ("engage_bias", C.c_double), ("offset_total_sum", C.c_double), ("offset_negative_sum", C.c_double),
+                ("post_unexplored_include_oon", C.c_int32), ("enable_author_diversity", C.c_int32),
+                ("oon_rescore_in_network_replies_retweets", C.c_int32), ("multiplier_pre_offset", C.c_int32),
+                ("multiplicative", C.c_int32), ("_pad", C.c_int32)]
+
+
+class ValueInputs(C.Structure):  # phx_value_inputs
+    _fields_ = [("batch", C.c_int32), ("num_candidates", C.c_int32), ("num_actions", C.c_int32),
+                ("num_continuous", C.c_int32)] + [(n, C.c_void_p) for n in (
+        "log_probs", "continuous", "weighted", "author_ids", "flags", "exploration_bonus", "cold_start_rank",
+        "num_valid", "context")]
+
+
 # every symbol include/phoenix_b200.h declares: name -> (restype, argtypes)
 _P = C.c_void_p
 SIGNATURES = {
@@ -72,6 +89,7 @@ SIGNATURES = {
     "phx_rank_submit": (C.c_int32, [_P, C.POINTER(RankBatch), C.c_int32]),
     "phx_rank_collect": (C.c_int32, [_P, C.c_int32, C.POINTER(RankOut)]),
     "phx_rank_forward_device": (C.c_int32, [_P, C.POINTER(RankBatch), C.POINTER(RankOut)]),
+    "phx_value_scores_device": (C.c_int32, [C.c_int32, C.POINTER(ValueModel), C.POINTER(ValueInputs), _P, _P, _P]),
     "phx_rank_forward_hashed_device": (C.c_int32, [_P, C.POINTER(RankBatchHashed), C.POINTER(RankOut)]),
     "phx_rank_forward_hashed": (C.c_int32, [_P, C.POINTER(RankBatchHashed), C.POINTER(RankOut)]),
     "phx_rank_prefetch_device": (C.c_int32, [_P, C.POINTER(RankBatch)]),
