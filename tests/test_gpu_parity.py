@@ -824,3 +824,25 @@ def test_value_model_kernel_vs_oracle_random(torch, mode):
                          po.ScoringContext(0.8, po.class_factors(0.5, 1.1), po.class_factors(1.2, 0.7)),
                          po.ScoringContext(0.9, None, po.class_factors(1.1, 0.9))][len(contexts)])
     _vm_run(torch, wt, requests, contexts)
+
+
+def test_value_model_scorer_plugin(torch):
+    """The plugin over the kernel: the reference's hand-computed case (scoring.rs:498-636) through Candidate objects;
+    a candidate without scores becomes an error string and the rest are still scored."""
+    import x_algorithm_b200 as px
+    from tests.test_oracle_golden import value_model_kats
+    name, wt, ctx, cands, want_w, want_s = value_model_kats()[0]
+    import dataclasses
+    pw = px.ValueModelWeights(**{f.name: getattr(wt, f.name) for f in dataclasses.fields(wt)})
+    scorer = px.ValueModelScorer(pw, VM_HEADS, VM_CONTS, context=(ctx.effective_oon_weight, ctx.oon_factors, ctx.in_network_factors))
+    pcs = [px.Candidate(post_id=10 + i, author_id=c.author_id, phoenix_scores=dict(c.scores), in_network=c.in_network,
+                        is_reply=c.is_reply, is_retweet=c.is_retweet, is_mutual_follow_author=c.is_mutual_follow_author,
+                        vqv_eligible=c.vqv_eligible, quoted_vqv_eligible=c.quoted_vqv_eligible) for i, c in enumerate(cands)]
+    pcs.insert(2, px.Candidate(post_id=99, author_id=7))            # no scores
+    res = scorer.run(px.Query(), pcs)
+    assert len(res) == 5 and isinstance(res[2], str)
+    got = [r for r in res if not isinstance(r, str)]
+    np.testing.assert_allclose([r.score for r in got], want_s, rtol=2e-6, atol=1e-9)
+    np.testing.assert_allclose([r.weighted_score for r in got], want_w, rtol=2e-6, atol=1e-9)
+    scorer.update_all(pcs, res)
+    assert pcs[2].score is None and pcs[0].score == got[0].score

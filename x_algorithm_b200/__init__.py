@@ -6,5 +6,5 @@ from ._lib import PhoenixError, LIB_PATH  # noqa: F401  (raises ImportError when
 from .config import PhoenixConfig, HashFamilySpec  # noqa: F401
 from .engine import PhoenixEngine, RankInputs, RankOutputs  # noqa: F401
 from .value_model import ValueModelWeights, blend_spec_from_weights, HEAD_NAMES_19  # noqa: F401
-from .plugin import PhoenixScorer, PhoenixSource, Candidate, Query  # noqa: F401
+from .plugin import PhoenixScorer, PhoenixSource, ValueModelScorer, Candidate, Query  # noqa: F401
 from .retrieval import CorpusShard  # noqa: F401

@@ -160,17 +160,24 @@ __global__ void __launch_bounds__(256) value_scores_kernel(phx_value_model m, ph
     inn_some = !isnan(cx[3]); inn_f[0] = cx[3]; inn_f[1] = cx[4];
   }
   const bool cached = in.weighted != nullptr && !m.multiplicative;                                    // scoring.rs:445-450
+  // set_user_video_continuation (263-280): two left-to-right folds over the request's candidates.  The products are
+  // formed by all threads, the two sums run in candidate order on one thread (a candidate that lacks either value
+  // adds nothing, here as 0.0).
+  const bool want_user_cont = !cached && m.src[F_VIDEO_OPEN] >= 0 && m.src[F_HOME_VIDEO_CONT] >= 0 && m.w[T_USER_VIDEO_CONT] != 0.0;
+  if (want_user_cont) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const Opt o = field(m, in, base + i, F_VIDEO_OPEN), c = field(m, in, base + i, F_HOME_VIDEO_CONT);
+      s_ord[i] = o.v * c.v;
+      s_w[i] = o.v;
+    }
+  }
+  __syncthreads();
   if (threadIdx.x == 0) {
     sh_lift_idx = 0x7fffffff;
     sh_lift_val = 0.0;
-    // set_user_video_continuation (263-280): two left-to-right folds over the request's candidates
     double secs = 0.0, opens = 0.0;
-    if (!cached && m.src[F_VIDEO_OPEN] >= 0 && m.src[F_HOME_VIDEO_CONT] >= 0 && m.w[T_USER_VIDEO_CONT] != 0.0) {
-      for (int i = 0; i < n; ++i) {
-        const Opt o = field(m, in, base + i, F_VIDEO_OPEN), c = field(m, in, base + i, F_HOME_VIDEO_CONT);
-        if (o.some && c.some) { secs = secs + o.v * c.v; opens = opens + o.v; }
-      }
-    }
+    if (want_user_cont)
+      for (int i = 0; i < n; ++i) { secs = secs + s_ord[i]; opens = opens + s_w[i]; }
     sh_user_some = opens > 0.0;
     sh_user_cont = opens > 0.0 ? secs / opens : 0.0;
   }

@@ -255,9 +255,40 @@ def bench_mma(a):
                               fill_tbs=tiles * 16384.0 * a.ksteps * 148 / (ms.value * 1e-3) / 1e12)))
 
 
+def bench_value(a):
+    """The value model behind the heads (phx_value_scores_device): --batch requests x --cands candidates, every gate,
+    author diversity and class factors on, fuse_heads recomputed (no cached weighted score)."""
+    import torch
+    from . import value_model as vm
+    heads = vm.SCORE_FIELDS[:25]; conts = vm.SCORE_FIELDS[25:]
+    rng = np.random.default_rng(3)
+    w = {h: float(rng.uniform(0, 5)) for h in heads}
+    w.update(report=-80.0, not_interested=-20.0, cont_dwell_time=0.01, video_continuation=0.003, user_video_continuation=0.002)
+    wt = vm.ValueModelWeights(w=w, bidirectional_follow_reply_weight_boost=1.0, enable_author_diversity=True,
+                              author_diversity_decay=0.6, author_diversity_floor=0.2, oon_rescore_in_network_replies_retweets=True)
+    model = vm.value_model_struct(wt, heads, conts)
+    B, C = a.batch, a.cands
+    g = torch.Generator(device="cuda").manual_seed(1)
+    lp = torch.log(torch.rand((B, C, 25), device="cuda", generator=g) * 0.3 + 1e-4)
+    cont = torch.rand((B, C, 4), device="cuda", generator=g) * 20
+    auth = torch.randint(1, max(2, C // 4), (B, C), device="cuda", generator=g)
+    flags = torch.randint(0, 128, (B, C), device="cuda", generator=g).to(torch.uint8)
+    lift = torch.full((B, C), -1, dtype=torch.int32, device="cuda"); lift[:, C // 2] = C // 3
+    ctx = torch.tensor([[0.75, 0.6, 0.9, 1.2, 0.7]], dtype=torch.float64, device="cuda").repeat(B, 1)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(a.warmup + a.iters):
+        if i == a.warmup:
+            ev0.record()
+        vm.value_scores(model, lp, cont, auth, flags=flags, cold_start_rank=lift, context=ctx)
+    ev1.record(); torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / a.iters
+    print(json.dumps(dict(op="value_scores", batch=B, candidates=C, ms=ms, candidates_per_s=B * C / (ms * 1e-3),
+                          note="includes the two torch.zeros output allocations of the Python wrapper")))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gather", "topk", "attention", "retrieve", "mma"])
+    ap.add_argument("op", choices=["gather", "topk", "attention", "retrieve", "mma", "value"])
     ap.add_argument("--ksteps", type=int, default=200000, help="mma: k-steps per CTA (2000000 runs about a second)")
     ap.add_argument("--check", action="store_true")
     ap.add_argument("--no-dedup", action="store_true", help="sharded gather: send every request, not only distinct rows")
@@ -281,7 +312,8 @@ def main():
     ap.add_argument("--hist", type=int, default=1024)
     ap.add_argument("--cands", type=int, default=1024)
     a = ap.parse_args()
-    {"gather": bench_gather, "topk": bench_topk, "attention": bench_attention, "retrieve": bench_retrieve, "mma": bench_mma}[a.op](a)
+    {"gather": bench_gather, "topk": bench_topk, "attention": bench_attention, "retrieve": bench_retrieve, "mma": bench_mma,
+     "value": bench_value}[a.op](a)
 
 
 if __name__ == "__main__":

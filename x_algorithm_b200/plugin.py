@@ -43,6 +43,16 @@ class Candidate:
     phoenix_scores: Optional[Dict[str, float]] = None   # head name -> probability (dwell_time: seconds)
     weighted_score: Optional[float] = None
     score: Optional[float] = None
+    # what the value model reads besides the scores (xai-value-model/inputs.rs:3-17, filled as in
+    # home-mixer/scorers/value_model.rs:67-94)
+    in_network: Optional[bool] = None
+    is_reply: bool = False
+    is_retweet: bool = False
+    is_mutual_follow_author: bool = False
+    vqv_eligible: bool = False
+    quoted_vqv_eligible: bool = False
+    cold_start_lift_to_rank: Optional[int] = None
+    author_exploration_bonus: float = 0.0
 
 
 Result = Union[Candidate, str]   # Ok(candidate) | Err(message)
@@ -136,6 +146,74 @@ class PhoenixScorer(Scorer):
         if scored.weighted_score is not None:
             candidate.weighted_score = scored.weighted_score
             candidate.score = scored.score
+
+
+class ValueModelScorer(Scorer):
+    """The value model over candidates that already carry `phoenix_scores` (home-mixer/scorers/value_model.rs:62-103
+    building the inputs, xai-value-model/scoring.rs:404-489 scoring them): one kernel launch per request,
+    `weighted_score` = fuse_heads with the candidate's gates, `score` = the final value score (exploration bonus,
+    cold-start lift, author diversity, out-of-network weight, class factors).  A candidate without scores gets an
+    error string, the others are still scored."""
+
+    def __init__(self, weights, head_names: Sequence[str], cont_names: Sequence[str] = ("dwell_time",), device: int = 0,
+                 context: Optional[Tuple[float, Optional[Tuple[float, float]], Optional[Tuple[float, float]]]] = None):
+        from .value_model import value_model_struct
+        self.head_names, self.cont_names = list(head_names), list(cont_names)
+        self.model = value_model_struct(weights, self.head_names, self.cont_names)
+        self.device = device
+        self.context = context      # (effective_oon_weight, oon factors, in-network factors) or None = defaults
+
+    def score(self, query: Query, candidates: Sequence[Candidate]) -> List[Result]:
+        import torch
+
+        from . import value_model as vm
+        n = len(candidates)
+        if n == 0:
+            return []
+        ok = [c.phoenix_scores is not None for c in candidates]
+        idx = [i for i in range(n) if ok[i]]
+        if not idx:
+            return ["value model: candidate without phoenix scores"] * n
+        m = len(idx)
+        V, NC = len(self.head_names), len(self.cont_names)
+        lp = np.full((1, m, V), -np.inf, np.float32); cont = np.zeros((1, m, max(NC, 1)), np.float32)
+        auth = np.zeros((1, m), np.int64); flags = np.zeros((1, m), np.uint8)
+        bonus = np.zeros((1, m), np.float64); lift = np.full((1, m), -1, np.int32)
+        for j, i in enumerate(idx):
+            c = candidates[i]
+            for k, name in enumerate(self.head_names):
+                p = c.phoenix_scores.get(name)
+                if p is not None and p > 0.0:
+                    lp[0, j, k] = math.log(p)
+            for k, name in enumerate(self.cont_names):
+                cont[0, j, k] = c.phoenix_scores.get(name) or 0.0
+            auth[0, j] = c.author_id
+            flags[0, j] = ((vm.IN_NETWORK_KNOWN if c.in_network is not None else 0) | (vm.IN_NETWORK if c.in_network else 0)
+                           | (vm.IS_REPLY if c.is_reply else 0) | (vm.IS_RETWEET if c.is_retweet else 0)
+                           | (vm.MUTUAL_FOLLOW if c.is_mutual_follow_author else 0) | (vm.VQV_ELIGIBLE if c.vqv_eligible else 0)
+                           | (vm.QUOTED_VQV_ELIGIBLE if c.quoted_vqv_eligible else 0))
+            bonus[0, j] = c.author_exploration_bonus
+            lift[0, j] = -1 if c.cold_start_lift_to_rank is None else c.cold_start_lift_to_rank
+        ctx = None
+        if self.context is not None:
+            eow, oon, inn = self.context
+            ctx = np.array([[eow, *(oon or (np.nan, np.nan)), *(inn or (np.nan, np.nan))]], np.float64)
+        try:
+            dev = torch.device("cuda", self.device)
+            cu = lambda a: None if a is None else torch.from_numpy(a).to(dev)
+            w, s = vm.value_scores(self.model, cu(lp), cu(cont[:, :, :NC]) if NC else None, cu(auth), flags=cu(flags),
+                                   exploration_bonus=cu(bonus), cold_start_rank=cu(lift), context=cu(ctx), device=self.device)
+            w, s = w.cpu().numpy()[0], s.cpu().numpy()[0]
+        except (PhoenixError, RuntimeError) as err:
+            return [f"value model failed: {err}"] * n
+        out: List[Result] = ["value model: candidate without phoenix scores"] * n
+        for j, i in enumerate(idx):
+            c = candidates[i]
+            out[i] = Candidate(post_id=c.post_id, author_id=c.author_id, weighted_score=float(w[j]), score=float(s[j]))
+        return out
+
+    def update(self, candidate: Candidate, scored: Candidate) -> None:
+        candidate.weighted_score, candidate.score = scored.weighted_score, scored.score
 
 
 class Source:
