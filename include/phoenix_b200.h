@@ -92,6 +92,13 @@ typedef struct phx_model_config {
    * kernels; the precision of the reference's CPU-runnable fp32 model, for parity runs (within 1e-5 of the fp32
    * model), not for throughput.  0 = bf16 activations with fp32 accumulation on the tcgen05 kernels. */
   int32_t compute_fp32;
+  /* How the gathered rows of a token are combined.  0: summed in fp32 in slot order, one rounding (the benchmark's
+   * restatement).  1: laid side by side and multiplied by a projection matrix, the reference's own form
+   * (block_history_reduce / block_candidate_reduce, recsys_model.py:2163-2365: concat(post rows, author rows
+   * [, action row, surface row]) @ proj_mat): parameters "proj_hist" [(2H+2)*emb_size, emb_size] and "proj_cand"
+   * [2H*emb_size, emb_size]. */
+  int32_t token_project;
+  int32_t _pad1;
 } phx_model_config;
 
 /* Weighted blend in term-list form: xai-value-model/scoring.rs:67-73, 112-120, 282-291.

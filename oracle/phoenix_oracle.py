@@ -231,6 +231,7 @@ class ModelConfig:
     dwell_norm_scale: float = 30.0
     compute: str = "bf16"          # "bf16" | "fp32"
     num_candidate_only_layers: int = 0   # tail layers that leave the history rows frozen (transformer.py:789-871)
+    token_combine: str = "sum"     # "sum" | "project": concat(rows) @ proj_mat (recsys_model.py:2163-2365)
 
     @property
     def ffn_size(self) -> int:
@@ -296,6 +297,10 @@ def make_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02) -> Dict[str
     w["final_norm"] = gain(D)
     w["unembed"] = mat(D, cfg.num_actions)
     w["cont_unembed"] = mat(D, cfg.num_continuous)
+    if cfg.token_combine == "project":   # drawn last: the other parameters do not depend on the combine mode
+        H2 = 2 * cfg.num_hashes
+        w["proj_hist"] = bf16_round(rng.standard_normal(((H2 + 2) * D, D), dtype=np.float32) / np.float32(math.sqrt(D)))
+        w["proj_cand"] = bf16_round(rng.standard_normal((H2 * D, D), dtype=np.float32) / np.float32(math.sqrt(D)))
     return w
 
 
@@ -531,7 +536,15 @@ def build_tokens(cfg: ModelConfig, w: Dict[str, np.ndarray], table_rows_fn, batc
     srf = bf16_bits(w["surface_table"])[np.clip(batch.hist_surfaces, 0, cfg.num_surfaces)]
     hist_rows = np.concatenate([table_rows_fn(hp), table_rows_fn(ha), act[:, :, None, :], srf[:, :, None, :]], axis=2)
     cand_rows = np.concatenate([table_rows_fn(cp), table_rows_fn(ca)], axis=2)
-    hist_tok, cand_tok = gather_sum(hist_rows), gather_sum(cand_rows)
+    if cfg.token_combine == "project":
+        # block_history_reduce / block_candidate_reduce (recsys_model.py:2190-2221, 2307-2329): the rows side by side,
+        # fp32 dot with the projection matrix, cast back to the embedding dtype
+        def proj(rows_bits, mat):
+            cat = bf16_from_bits(rows_bits).reshape(rows_bits.shape[0], rows_bits.shape[1], -1)
+            return bf16_bits(bf16_round((cat @ mat).astype(np.float32)))
+        hist_tok, cand_tok = proj(hist_rows, w["proj_hist"]), proj(cand_rows, w["proj_cand"])
+    else:
+        hist_tok, cand_tok = gather_sum(hist_rows), gather_sum(cand_rows)
     hist_mask, cand_mask = hp[:, :, 0] != 0, cp[:, :, 0] != 0
     tok = bf16_from_bits(np.concatenate([hist_tok, cand_tok], axis=1))
     pad = np.concatenate([hist_mask, cand_mask], axis=1)

@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol():
 def test_struct_layouts_match_header():
     from x_algorithm_b200 import _lib
     assert C.sizeof(_lib.HashFamily) == 8 * 4 + 8 * 4 + 8 + 8 + 4 + 4
-    assert C.sizeof(_lib.ModelConfig) == 17 * 4 + 5 * 4 + 4 * C.sizeof(_lib.HashFamily) + 4 * 4
+    assert C.sizeof(_lib.ModelConfig) == 17 * 4 + 5 * 4 + 4 * C.sizeof(_lib.HashFamily) + 6 * 4
     assert C.sizeof(_lib.BlendSpec) == 8 + 32 * 4 + 32 * 8 + 16 - 4 + 4   # int + pad, src, weight, two doubles
     assert C.sizeof(_lib.RankBatch) == 8 + 6 * 8 and C.sizeof(_lib.RankOut) == 24
 

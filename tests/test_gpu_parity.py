@@ -303,6 +303,34 @@ def test_rank_forward_from_prehashed_rows_bit_identical(torch, opts):
     eng.close()
 
 
+@pytest.mark.parametrize("opts", [dict(), dict(num_candidate_only_layers=1),
+                                  dict(num_hashes=4, emb_size=256, num_q_heads=4, num_kv_heads=4, key_size=64, history_len=48,
+                                       num_candidates=24, num_layers=3)])
+def test_projected_tokens_vs_oracle(torch, monkeypatch, opts):
+    """The reference's own combine (block_history_reduce / block_candidate_reduce, recsys_model.py:2163-2365): gathered
+    rows side by side times a projection matrix.  The gathered operand is a byte copy, so the projected tokens are
+    compared before anything else; then the forward."""
+    monkeypatch.setenv("PHX_DEBUG_TAPS", "1")
+    ocfg, w, rows_fn, eng = make_pair(max_batch=6, token_combine="project", **opts)
+    b, taps, lp, cont, logits, spec, res = _forward_case(ocfg, w, rows_fn, eng, 6, True)
+    T = ocfg.seq_len
+    tokens = po.bf16_from_bits(eng.debug_read("tokens", (6, T, ocfg.emb_size), np.uint16))
+    want_tok = po.bf16_from_bits(np.concatenate([taps["hist_tok"], taps["cand_tok"]], axis=1))
+    assert rel_l2(tokens, want_tok) < 4e-3          # one bf16 rounding of an fp32 dot product in another summation order
+    valid = b.cand_post_ids != 0
+    assert rel_l2(res.log_probs[valid], lp[valid]) < TOL, opts
+    assert rel_l2(res.continuous[valid], cont[valid]) < TOL, opts
+    # the user tower goes through the same history projection
+    want_users = po.user_tower(ocfg, w, rows_fn, b)
+    dev = [torch.from_numpy(x).cuda() for x in (b.hist_post_ids, b.hist_author_ids, b.hist_actions, b.hist_surfaces)]
+    users = torch.empty((6, ocfg.emb_size), dtype=torch.float32, device="cuda")
+    eng.user_tower_device(6, *dev, users)
+    eng.sync()
+    ok = b.hist_post_ids[:, 0] != 0
+    assert rel_l2(users.cpu().numpy()[ok], want_users[ok]) < TOL
+    eng.close()
+
+
 def test_simt_gemm_path_matches_tcgen05(torch, monkeypatch):
     """The cross-check GEMM and the tcgen05 GEMM give the same forward (accumulation order aside)."""
     ocfg, w, rows_fn, eng = make_pair(max_batch=4)

@@ -78,6 +78,8 @@ class PhoenixConfig:
     table_rank: int = 0
     num_candidate_only_layers: int = 0   # tail layers that update candidate rows only (transformer.py:789-871)
     compute: str = "bf16"       # "bf16" (tcgen05 kernels) | "fp32" (full-precision SIMT path for parity runs)
+    token_combine: str = "sum"  # "sum" (fp32 sum of the gathered rows) | "project" (concat(rows) @ proj_hist / proj_cand,
+                                # recsys_model.py:2163-2365)
 
     @property
     def ffn_size(self) -> int:  # phoenix/xrex/utils/utils.py:37-52
@@ -116,4 +118,7 @@ class PhoenixConfig:
         if self.compute not in ("bf16", "fp32"):
             raise ValueError("compute must be 'bf16' or 'fp32'")
         c.compute_fp32 = 1 if self.compute == "fp32" else 0
+        if self.token_combine not in ("sum", "project"):
+            raise ValueError("token_combine must be 'sum' or 'project'")
+        c.token_project = 1 if self.token_combine == "project" else 0
         return c

@@ -184,10 +184,15 @@ struct TokenBuildArgs {
   // feature, 0 = padding; when pre_hist_post is set the ids are not read and nothing is hashed
   const int* pre_hist_post = nullptr; const int* pre_hist_author = nullptr;
   const int* pre_cand_post = nullptr; const int* pre_cand_author = nullptr;
+  // projected tokens: when concat_hist is set the kernel only lays the gathered rows side by side -
+  // concat_hist [B*S, (2H+2)*D], concat_cand [B*C, 2H*D] - and writes the segment ids
+  bf16* concat_hist = nullptr; bf16* concat_cand = nullptr;
   float* x32 = nullptr;   // full-precision path: bf16(sum) * input_scale kept in fp32 here (x is then not written)
   const bf16* landing = nullptr;
   const int* pos = nullptr;
 };
+phx_status finish_tokens_launch(const bf16* tok_hist, const bf16* tok_cand, const TokenBuildArgs& a, cudaStream_t stream,
+                                std::string& err);
 phx_status build_tokens_launch(const TokenBuildArgs& a, cudaStream_t stream, std::string& err);
 phx_status hash_ids_launch(const HashFamilyDev& fam, const long long* ids, long long n, int* out, cudaStream_t stream,
                            std::string& err);

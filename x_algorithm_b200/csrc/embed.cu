@@ -84,6 +84,25 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
     const int ps = __shfl_sync(0xffffffffu, my_pos, jj);
     rowp[j] = a.landing ? a.landing + (long long)ps * a.D : a.table.row_ptr(idx, a.D);
   }
+  if (a.concat_hist) {
+    // projected tokens: the gathered rows side by side - post rows, author rows, then (history) action and surface
+    // rows - as one GEMM operand row (recsys_model.py:2190-2207, 2307-2316); the projection, the scaling and the row
+    // statistics follow in their own launches
+    const int nslot = 2 * H + (is_hist ? 2 : 0);
+    bf16* dst = is_hist ? a.concat_hist + slot * (long long)nslot * a.D : a.concat_cand + slot * (long long)nslot * a.D;
+    for (int col = lane * 8; col < a.D; col += 256) {
+#pragma unroll
+      for (int j = 0; j < 2 * PHX_MAX_HASHES; ++j)
+        if (j < 2 * H) *reinterpret_cast<uint4*>(dst + (long long)j * a.D + col) = __ldg(reinterpret_cast<const uint4*>(rowp[j] + col));
+      if (is_hist) {
+        *reinterpret_cast<uint4*>(dst + (long long)(2 * H) * a.D + col) =
+            __ldg(reinterpret_cast<const uint4*>(a.action_table + (long long)act * a.D + col));
+        *reinterpret_cast<uint4*>(dst + (long long)(2 * H + 1) * a.D + col) =
+            __ldg(reinterpret_cast<const uint4*>(a.surface_table + (long long)srf * a.D + col));
+      }
+    }
+    return;
+  }
   float row_ss = 0.f;
   for (int col = lane * 8; col < a.D; col += 256) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -112,6 +131,37 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
     *reinterpret_cast<uint4*>(a.x + orow * a.D + col) = o;
   }
   if (a.row_ss) {   // statistics of the bf16 row for the first fused RMSNorm
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) row_ss += __shfl_xor_sync(0xffffffffu, row_ss, o);
+    if (lane < a.ss_slots) a.row_ss[orow * a.ss_slots + lane] = (lane == 0) ? row_ss : 0.f;
+  }
+}
+
+// Projected tokens, last step: x = bf16(token * input_scale) at the token's row of the residual stream (plain or
+// split layout) with the row statistics of the first fused RMSNorm; tok_hist [B*S, D] and tok_cand [B*C, D] are the
+// outputs of the two projection GEMMs.  One warp per token.
+__global__ void __launch_bounds__(256) finish_tokens_kernel(const bf16* __restrict__ tok_hist, const bf16* __restrict__ tok_cand,
+                                                            TokenBuildArgs a) {
+  const int T = a.S + a.C;
+  const long long tok = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (tok >= (long long)a.B * T) return;
+  const int b = (int)(tok / T), t = (int)(tok % T);
+  const bf16* src = t < a.S ? tok_hist + ((long long)b * a.S + t) * a.D : tok_cand + ((long long)b * a.C + (t - a.S)) * a.D;
+  const long long orow = token_row(a.split, a.B, a.S, T, b, t);
+  float row_ss = 0.f;
+  for (int col = lane * 8; col < a.D; col += 256) {
+    const uint4 u = *reinterpret_cast<const uint4*>(src + col);
+    if (a.tokens) *reinterpret_cast<uint4*>(a.tokens + tok * a.D + col) = u;
+    const float2 p0 = unpack_bf2(u.x), p1 = unpack_bf2(u.y), p2 = unpack_bf2(u.z), p3 = unpack_bf2(u.w);
+    float s[8] = {p0.x, p0.y, p1.x, p1.y, p2.x, p2.y, p3.x, p3.y};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { s[i] = round_bf(s[i] * a.input_scale); row_ss += s[i] * s[i]; }
+    uint4 o;
+    o.x = pack_bf2(s[0], s[1]); o.y = pack_bf2(s[2], s[3]); o.z = pack_bf2(s[4], s[5]); o.w = pack_bf2(s[6], s[7]);
+    *reinterpret_cast<uint4*>(a.x + orow * a.D + col) = o;
+  }
+  if (a.row_ss) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) row_ss += __shfl_xor_sync(0xffffffffu, row_ss, o);
     if (lane < a.ss_slots) a.row_ss[orow * a.ss_slots + lane] = (lane == 0) ? row_ss : 0.f;
@@ -220,6 +270,15 @@ phx_status build_tokens_launch(const TokenBuildArgs& a, cudaStream_t stream, std
   if (toks == 0) return PHX_OK;
   const int warps = 8;
   build_tokens_kernel<<<(unsigned)((toks + warps - 1) / warps), warps * 32, 0, stream>>>(a);
+  PHX_CUDA_TRY(cudaGetLastError(), err);
+  return PHX_OK;
+}
+
+phx_status finish_tokens_launch(const bf16* tok_hist, const bf16* tok_cand, const TokenBuildArgs& a, cudaStream_t stream,
+                                std::string& err) {
+  const long long toks = (long long)a.B * (a.S + a.C);
+  if (toks == 0) return PHX_OK;
+  finish_tokens_kernel<<<(unsigned)((toks + 7) / 8), 256, 0, stream>>>(tok_hist, tok_cand, a);
   PHX_CUDA_TRY(cudaGetLastError(), err);
   return PHX_OK;
 }

@@ -79,6 +79,12 @@ struct phx_engine {
   // candidate block only
   bool split = false;
   int n_tail = 0;
+  // projected tokens (cfg.token_project): gathered rows side by side, two projection GEMMs, then scaling
+  bool project = false;
+  int Kh = 0, Kc = 0;                              // (2H + 2) * D and 2H * D
+  bf16 *proj_hist_t = nullptr, *proj_cand_t = nullptr;   // [D, Kh], [D, Kc]
+  bf16 *cat_hist = nullptr, *cat_cand = nullptr, *tok_proj = nullptr;   // [max_batch*S, Kh], [max_batch*C, Kc], [max_tokens, D]
+  GemmPlan p_proj_hist, p_proj_cand;
   // full-precision path (cfg.compute_fp32): fp32 activations, plain row order
   bool fp32 = false;
   float *x32 = nullptr, *h32 = nullptr, *qkv32 = nullptr, *attn32 = nullptr, *ffn32 = nullptr, *tmp32 = nullptr, *hist32 = nullptr;
@@ -246,6 +252,8 @@ phx_status check_cfg(const phx_model_config& c, std::string& err) {
   if (c.table_world < 0 || c.table_world > PHX_MAX_SHARDS || (c.table_world > 1 && (c.table_rank < 0 || c.table_rank >= c.table_world)))
     return bad("table_world / table_rank");
   if (c.compute_fp32 != 0 && c.compute_fp32 != 1) return bad("compute_fp32 must be 0 or 1");
+  if (c.token_project != 0 && c.token_project != 1) return bad("token_project must be 0 or 1");
+  if (c.token_project && c.compute_fp32) return bad("projected tokens are not available on the full-precision path");
   if (c.num_candidate_only_layers < 0 || c.num_candidate_only_layers > c.num_layers) return bad("num_candidate_only_layers");
   return PHX_OK;
 }
@@ -293,6 +301,7 @@ phx_status refresh_folded(phx_engine* e) {
 
 bool params_complete(phx_engine* e, bool need_heads) {
   std::vector<std::string> need = {"action_table", "surface_table", "final_norm"};
+  if (e->project) { need.push_back("proj_hist"); if (need_heads) need.push_back("proj_cand"); }
   if (need_heads) {
     if (e->V > 0) need.push_back("unembed");
     if (e->NC > 0) need.push_back("cont_unembed");
@@ -486,6 +495,20 @@ phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc, 
   if (e->fp32) ta.x32 = e->x32;
   if (rows_out) { ta.rows_only = 1; ta.hashes = rows_out; }
   ta.landing = landing; ta.pos = pos;
+  if (e->project && !rows_out) {
+    // gathered rows side by side -> two projection GEMMs -> scale, place and take the row statistics
+    if (stream) { e->err = "token prefetch is not available with projected tokens"; return PHX_E_ARG; }
+    ta.concat_hist = e->cat_hist; ta.concat_cand = e->cat_cand;
+    cudaStream_t st = e->stream;
+    phx_status s;
+    { e->last_launches++; ProfScope ps(e, KC_TOKENS); if ((s = build_tokens_launch(ta, st, e->err))) return s; }
+    bf16* tok_h = e->tok_proj; bf16* tok_c = e->tok_proj + (long long)B * e->S * e->D;
+    if ((s = do_gemm(e, e->p_proj_hist, e->cat_hist, tok_h, nullptr, (long long)B * e->S, EPI_STORE))) return s;
+    if (Cc > 0 && (s = do_gemm(e, e->p_proj_cand, e->cat_cand, tok_c, nullptr, (long long)B * Cc, EPI_STORE))) return s;
+    e->last_launches++;
+    ProfScope ps(e, KC_TOKENS);
+    return finish_tokens_launch(tok_h, tok_c, ta, st, e->err);
+  }
   if (stream) return build_tokens_launch(ta, stream, e->err);   // prefetch on the side stream: not profiled
   e->last_launches++;
   ProfScope ps(e, KC_TOKENS);
@@ -567,6 +590,19 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
     }
   }
   if (cfg->primer_norm) TRY(dev_alloc(e, &e->tmp, (size_t)M * e->D));
+  e->project = cfg->token_project != 0;
+  if (e->project) {
+    const int H2 = 2 * cfg->item.num_hashes;
+    e->Kh = (H2 + 2) * e->D; e->Kc = H2 * e->D;
+    const long long mh = (long long)cfg->max_batch * e->S, mc = (long long)cfg->max_batch * (e->C > 0 ? e->C : 1);
+    TRY(dev_alloc(e, &e->proj_hist_t, (size_t)e->D * e->Kh));
+    TRY(dev_alloc(e, &e->proj_cand_t, (size_t)e->D * e->Kc));
+    TRY(dev_alloc(e, &e->cat_hist, (size_t)mh * e->Kh));
+    TRY(dev_alloc(e, &e->cat_cand, (size_t)mc * e->Kc));
+    TRY(dev_alloc(e, &e->tok_proj, (size_t)M * e->D));
+    TRY(gemm_plan_create(&e->p_proj_hist, e->cat_hist, e->proj_hist_t, mh, e->D, e->Kh, false, e->err));
+    TRY(gemm_plan_create(&e->p_proj_cand, e->cat_cand, e->proj_cand_t, mc, e->D, e->Kc, false, e->err));
+  }
   if (e->fp32) {
     TRY(dev_alloc(e, &e->x32, (size_t)M * e->D));
     TRY(dev_alloc(e, &e->h32, (size_t)M * e->D));
@@ -675,6 +711,7 @@ void phx_engine_destroy(phx_engine* e) {
     fr(L.w_qkv_t); fr(L.w_out_t); fr(L.w_up_t); fr(L.w_down_t); fr(L.w_qkv_f); fr(L.w_up_f);
   }
   fr(e->cos_tab); fr(e->sin_tab); fr(e->x); fr(e->hbuf); fr(e->qkv); fr(e->attn); fr(e->ffn); fr(e->tmp); fr(e->tokens);
+  fr(e->proj_hist_t); fr(e->proj_cand_t); fr(e->cat_hist); fr(e->cat_cand); fr(e->tok_proj);
   fr(e->x32); fr(e->h32); fr(e->qkv32); fr(e->attn32); fr(e->ffn32); fr(e->tmp32); fr(e->hist32);
   fr(e->x_alt); fr(e->seg_alt); fr(e->rowss_a_alt); fr(e->rowss_a); fr(e->rowss_f); fr(e->seg); fr(e->hashes); fr(e->err_flag); fr(e->in_stage_dev); fr(e->lp_dev); fr(e->cont_dev); fr(e->score_dev);
   if (e->in_stage_host) cudaFreeHost(e->in_stage_host);
@@ -707,6 +744,12 @@ phx_status phx_load_param(phx_engine* e, const char* name, const float* host, in
   if (n == "action_table") { if (!shape(e->cfg.num_action_types + 1, e->D)) return PHX_E_ARG; s = upload_bf16(e, &e->action_table, host, rows, cols, false); }
   else if (n == "surface_table") { if (!shape(e->cfg.num_surfaces + 1, e->D)) return PHX_E_ARG; s = upload_bf16(e, &e->surface_table, host, rows, cols, false); }
   else if (n == "final_norm") { if (!shape(1, e->D)) return PHX_E_ARG; s = upload_f32(e, &e->final_norm, host, e->D, true); }
+  else if (n == "proj_hist" || n == "proj_cand") {
+    if (!e->project) { e->err = "phx_load_param(" + n + "): the engine was created without token_project"; return PHX_E_ARG; }
+    const bool h = n == "proj_hist";
+    if (!shape(h ? e->Kh : e->Kc, e->D)) return PHX_E_ARG;
+    s = upload_bf16(e, h ? &e->proj_hist_t : &e->proj_cand_t, host, rows, cols, true);
+  }
   else if (n == "unembed" || n == "cont_unembed") {
     const bool cont = n == "cont_unembed";
     const int nout = cont ? e->NC : e->V;
