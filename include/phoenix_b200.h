@@ -358,6 +358,12 @@ phx_status phx_corpus_fill_synthetic(phx_corpus* c, uint32_t seed);
  * cuda/top_k_by_key/__init__.py:56-94).  Asynchronous on the corpus' stream. */
 phx_status phx_corpus_topk_device(phx_corpus* c, const float* users_dev, int32_t B, int32_t k, float* scores_dev,
                                   int64_t* ids_dev);
+/* The same top-k over rows [row_begin, row_end) of the shard only (shard-local row numbers): the reference's dataset
+ * windows, where every retrieval dataset is a contiguous row range of the post table and each gets its own top-k
+ * (slice_and_top_k, recsys_two_tower_model.py:2660-2686; ids come back offset by the window's start, as there).
+ * k must not exceed the window's rows. */
+phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, int32_t B, int32_t k, int64_t row_begin,
+                                         int64_t row_end, float* scores_dev, int64_t* ids_dev);
 /* Merge P per-shard lists laid out [P,B,k] into [B,k] by (score desc, id asc)
  * (strided_dataset_top_k, recsys_two_tower_model.py:215-220). */
 phx_status phx_topk_merge_device(phx_corpus* c, const float* scores_dev, const int64_t* ids_dev, int32_t P,

@@ -501,6 +501,41 @@ def test_topk_large_shard_uses_pivot_path(torch, monkeypatch, impl, dim):
     sh.close()
 
 
+@pytest.mark.parametrize("impl,dim,N,windows", [
+    ("tc", 128, 60_000, [(0, 60_000), (128, 5_000), (777, 59_999), (30_001, 31_500)]),
+    ("tc", 64, 700_000, [(100_003, 650_001), (0, 1_000)]),          # windows larger than the survivor buffer: pivot path
+    ("simt", 96, 40_000, [(5, 39_000), (20_000, 21_500)])])
+def test_topk_dataset_windows_exact(torch, monkeypatch, impl, dim, N, windows):
+    """Top-k restricted to a row window of the shard (the reference's dataset ranges): exact id sets and order against
+    the oracle's top-k of the sliced scores, ids offset by the shard's first row and the window's start."""
+    from x_algorithm_b200.retrieval import CorpusShard
+    if impl == "simt":
+        monkeypatch.setenv("PHX_TOPK", "simt")
+    B, k, off = 5, 200, 1_000_000
+    shard = CorpusShard(N, dim, row_offset=off, max_queries=8, max_k=k)
+    shard.fill_synthetic(13)
+    corpus = po.synthetic_corpus_rows(np.arange(off, off + N), dim, 13)
+    rng = np.random.default_rng(dim)
+    users = rng.standard_normal((B, dim)).astype(np.float32)
+    users /= np.linalg.norm(users, axis=1, keepdims=True)
+    tu = torch.from_numpy(users).cuda()
+    sc_all = po.corpus_scores(users, corpus)
+    for r0, r1 in windows:
+        scores = torch.empty((B, k), dtype=torch.float32, device="cuda"); ids = torch.empty((B, k), dtype=torch.int64, device="cuda")
+        shard.topk_window_device(tu, B, k, r0, r1, scores, ids)
+        shard.sync()
+        want_s, want_i = po.top_k(sc_all[:, r0:r1], k, row_offset=off + r0)
+        np.testing.assert_array_equal(ids.cpu().numpy(), want_i)
+        # scores are bf16 roundings of fp32 dot products summed in another order: at most one bf16 step apart
+        np.testing.assert_allclose(scores.cpu().numpy(), want_s, rtol=2.0 ** -7, atol=0)
+    # a window past the shard, an empty one, or one with fewer than k rows is refused
+    import x_algorithm_b200 as px
+    for bad in ((0, N + 1), (10, 10), (0, k - 1)):
+        with pytest.raises(px.PhoenixError):
+            shard.topk_window_device(tu, B, k, bad[0], bad[1], scores, ids)
+    shard.close()
+
+
 def test_sharded_gather_exchange_kernels_bit_identical(torch):
     """The device-side steps of the all-to-all exchange (bucket by owner, owner-side gather, fixed-order sum), with
     the two collectives emulated by slicing: two "ranks" on one device, each holding half of the table.  The result

@@ -337,6 +337,8 @@ struct phx_corpus {
   int* err_flag = nullptr;       // raised by a bounded device-side wait that ran out
   bool use_tc = false;           // tcgen05 scan (dim 64 / 128), else the mma.sync scan
   CUtensorMap map_corpus, map_users;
+  CUtensorMap map_window;                    // corpus map of the last scanned window (phx_corpus_topk_window_device)
+  long long win_begin = -1, win_end = -1;
   cudaStream_t stream = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   std::string err;
@@ -445,12 +447,26 @@ phx_status phx_corpus_fill_synthetic(phx_corpus* c, uint32_t seed) {
   return PHX_OK;
 }
 
-phx_status phx_corpus_topk_device(phx_corpus* c, const float* users_dev, int32_t B, int32_t k, float* scores_dev,
-                                  int64_t* ids_dev) {
+phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, int32_t B, int32_t k, int64_t row_begin,
+                                         int64_t row_end, float* scores_dev, int64_t* ids_dev) {
   if (!c || !users_dev || !scores_dev || !ids_dev) return PHX_E_ARG;
   if (B <= 0 || B > c->max_queries || k <= 0 || k > c->max_k) { c->err = "topk: B or k exceeds what the corpus was created for"; return PHX_E_CAPACITY; }
-  if (k > c->rows) { c->err = "topk: k exceeds the shard's rows"; return PHX_E_ARG; }
+  if (row_begin < 0 || row_end > c->rows || row_begin >= row_end) { c->err = "topk: window outside the shard's rows"; return PHX_E_ARG; }
+  // the window [row_begin, row_end) of the shard scanned as a corpus of its own: rows, first row and global id of row 0
+  const long long rows = row_end - row_begin, roff = c->row_offset + row_begin;
+  const bf16* data = c->data + row_begin * (long long)c->dim;
+  if (k > rows) { c->err = "topk: k exceeds the rows of the window"; return PHX_E_ARG; }
   cudaSetDevice(c->device);
+  const CUtensorMap* map_corpus = &c->map_corpus;
+  if (c->use_tc && (row_begin != 0 || row_end != c->rows)) {
+    if (c->win_begin != row_begin || c->win_end != row_end) {
+      CUtensorMap users_unused;
+      phx_status ms = tc_scan_make_maps(&c->map_window, &users_unused, data, rows, c->dim, c->users_bf, c->err);
+      if (ms) return ms;
+      c->win_begin = row_begin; c->win_end = row_end;
+    }
+    map_corpus = &c->map_window;
+  }
   const int Bpad = c->use_tc ? 256 : (B <= 16 ? 16 : (B <= 64 ? 64 : 256));
   PHX_CUDA_TRY(cudaEventRecord(c->ev0, c->stream), c->err);
   users_to_bf16_kernel<<<(Bpad * c->dim + 255) / 256, 256, 0, c->stream>>>(users_dev, c->users_bf, B, Bpad, c->dim);
@@ -461,14 +477,14 @@ phx_status phx_corpus_topk_device(phx_corpus* c, const float* users_dev, int32_t
   const int tile_rows = c->use_tc ? 128 : TILE_ROWS;
   const double group_rows = c->use_tc ? 32.0 : 16.0;
   ScanArgs a;
-  a.corpus = c->data; a.users = c->users_bf; a.rows = c->rows; a.row_offset = c->row_offset; a.dim = c->dim; a.B = B; a.Bpad = Bpad;
+  a.corpus = data; a.users = c->users_bf; a.rows = rows; a.row_offset = roff; a.dim = c->dim; a.B = B; a.Bpad = Bpad;
   a.stride = 1; a.gmax = c->gmax; a.n_groups = 0; a.pivot = c->pivot; a.surv = c->surv; a.counts = c->counts; a.cap = c->cap;
   TcScanArgs ta;
-  ta.rows = c->rows; ta.row_offset = c->row_offset; ta.dim = c->dim; ta.B = B; ta.stride = 1; ta.gmax = c->gmax; ta.n_groups = 0;
+  ta.rows = rows; ta.row_offset = roff; ta.dim = c->dim; ta.B = B; ta.stride = 1; ta.gmax = c->gmax; ta.n_groups = 0;
   ta.pivot = c->pivot; ta.surv = c->surv; ta.counts = c->counts; ta.cap = c->cap;
-  const long long n_tiles = (c->rows + tile_rows - 1) / tile_rows;
+  const long long n_tiles = (rows + tile_rows - 1) / tile_rows;
   int j = 0;
-  if (c->rows > c->cap) {
+  if (rows > c->cap) {
     // sample every stride-th tile so that about 48 of the wanted ~3k rows fall into the sample
     const double want = 3.0 * k;
     long long stride = (long long)(want / 48.0);
@@ -478,12 +494,12 @@ phx_status phx_corpus_topk_device(phx_corpus* c, const float* users_dev, int32_t
     a.stride = ta.stride = (int)stride;
     a.n_groups = ta.n_groups = sampled_tiles * 4;
     // per-row tail fraction f = want / rows; a group of g rows exceeds the level with 1 - (1-f)^g
-    const double f = want / (double)c->rows;
+    const double f = want / (double)rows;
     const double qg = 1.0 - pow(1.0 - (f < 0.5 ? f : 0.5), group_rows);
     j = (int)ceil(qg * (double)a.n_groups);
     if (j < 1) j = 1;
     phx_status s;
-    if (c->use_tc) s = tc_scan_launch(c->map_corpus, c->map_users, ta, 0, c->num_sms, c->err_flag, c->stream, c->err);
+    if (c->use_tc) s = tc_scan_launch(*map_corpus, c->map_users, ta, 0, c->num_sms, c->err_flag, c->stream, c->err);
     else s = run_scan(c, a, 0, (int)(sampled_tiles < c->num_sms * 2 ? sampled_tiles : c->num_sms * 2));
     if (s) return s;
   }
@@ -491,7 +507,7 @@ phx_status phx_corpus_topk_device(phx_corpus* c, const float* users_dev, int32_t
   PHX_CUDA_TRY(cudaGetLastError(), c->err);
   {
     phx_status s;
-    if (c->use_tc) s = tc_scan_launch(c->map_corpus, c->map_users, ta, 1, c->num_sms, c->err_flag, c->stream, c->err);
+    if (c->use_tc) s = tc_scan_launch(*map_corpus, c->map_users, ta, 1, c->num_sms, c->err_flag, c->stream, c->err);
     else s = run_scan(c, a, 1, (int)(n_tiles < c->num_sms * 2 ? n_tiles : c->num_sms * 2));
     if (s) return s;
   }
@@ -501,6 +517,13 @@ phx_status phx_corpus_topk_device(phx_corpus* c, const float* users_dev, int32_t
   PHX_CUDA_TRY(cudaGetLastError(), c->err);
   PHX_CUDA_TRY(cudaEventRecord(c->ev1, c->stream), c->err);
   return PHX_OK;
+}
+
+phx_status phx_corpus_topk_device(phx_corpus* c, const float* users_dev, int32_t B, int32_t k, float* scores_dev,
+                                  int64_t* ids_dev) {
+  if (!c) return PHX_E_ARG;
+  if (k > c->rows) { c->err = "topk: k exceeds the shard's rows"; return PHX_E_ARG; }
+  return phx_corpus_topk_window_device(c, users_dev, B, k, 0, c->rows, scores_dev, ids_dev);
 }
 
 phx_status phx_topk_merge_device(phx_corpus* c, const float* scores_dev, const int64_t* ids_dev, int32_t P, int32_t B,

@@ -50,6 +50,12 @@ class CorpusShard:
         self._check(lib.phx_corpus_topk_device(self._h, int(users.data_ptr()), B, k, int(scores.data_ptr()),
                                                int(ids.data_ptr())))
 
+    def topk_window_device(self, users, B: int, k: int, row_begin: int, row_end: int, scores, ids):
+        """Top-k over shard-local rows [row_begin, row_end) only: one retrieval dataset of the reference's post table
+        (recsys_two_tower_model.py:2660-2686); ids are global rows as in `topk_device`."""
+        self._check(lib.phx_corpus_topk_window_device(self._h, int(users.data_ptr()), B, k, row_begin, row_end,
+                                                      int(scores.data_ptr()), int(ids.data_ptr())))
+
     def merge_device(self, scores, ids, P: int, B: int, k: int, out_scores, out_ids):
         self._check(lib.phx_topk_merge_device(self._h, int(scores.data_ptr()), int(ids.data_ptr()), P, B, k,
                                               int(out_scores.data_ptr()), int(out_ids.data_ptr())))
