@@ -98,7 +98,13 @@ typedef struct phx_model_config {
    * [, action row, surface row]) @ proj_mat): parameters "proj_hist" [(2H+2)*emb_size, emb_size] and "proj_cand"
    * [2H*emb_size, emb_size]. */
   int32_t token_project;
-  int32_t _pad1;
+  /* 1 = ragged batches are packed: phx_rank_forward (host buffers) counts each request's leading non-padding history
+   * slots and candidates and the forward runs over those rows only, back to back (the reference serves ragged users
+   * through sequence packing, phoenix/xrex/data/sequence_packing.py:317; here the packing is by rows, requests stay
+   * independent).  Requests must be front-filled (padding only behind the valid slots); a batch that is not is run
+   * over all its slots.  Outputs of padded candidate slots are zero.  The device-pointer entry points and the
+   * submit / collect pipeline run over all slots. */
+  int32_t pack_ragged;
 } phx_model_config;
 
 /* Weighted blend in term-list form: xai-value-model/scoring.rs:67-73, 112-120, 282-291.

@@ -331,6 +331,46 @@ def test_projected_tokens_vs_oracle(torch, monkeypatch, opts):
     eng.close()
 
 
+@pytest.mark.parametrize("opts,attn", [
+    (dict(), None), (dict(num_candidate_only_layers=1), None), (dict(qk_norm=True), None), (dict(token_combine="project"), None),
+    (dict(emb_size=256, num_q_heads=4, num_kv_heads=4, key_size=64, history_len=48, num_candidates=24, num_layers=3,
+          num_candidate_only_layers=2), "strip"),
+    (dict(emb_size=256, num_q_heads=4, num_kv_heads=4, key_size=64, history_len=160, num_candidates=200, num_layers=2), "mma")])
+def test_packed_ragged_batches_match_unpacked(torch, monkeypatch, opts, attn):
+    """pack_ragged: the host-buffer call runs a ragged batch over its valid rows only.  Valid candidates get the same
+    bits as on the engine that runs every slot (a row's arithmetic does not depend on where the row sits), padded
+    candidate slots read zero, and both agree with the oracle.  Also: a request without history, one without
+    candidates, a full batch, and a batch that is not front-filled (run over all slots)."""
+    if attn:
+        monkeypatch.setenv("PHX_ATTN", attn)
+    ocfg, w, rows_fn, plain = make_pair(max_batch=6, **opts)
+    _, _, _, packed = make_pair(max_batch=6, engine_kw=dict(pack_ragged=True), **opts)
+    b = po.make_batch(ocfg, 6, seed=31, ragged=True)
+    b.hist_post_ids[1, :] = 0; b.hist_author_ids[1, :] = 0          # no history
+    b.cand_post_ids[2, :] = 0; b.cand_author_ids[2, :] = 0          # no candidates
+    full = po.make_batch(ocfg, 6, seed=32, ragged=False)
+    holes = po.make_batch(ocfg, 6, seed=33, ragged=True)
+    holes.cand_post_ids[0, 0] = 0                                   # padding in front of valid slots
+    for name, batch in (("ragged", b), ("full", full), ("holes", holes), ("ragged again", b)):
+        want = plain.rank(to_inputs(batch))
+        got = packed.rank(to_inputs(batch))
+        valid = batch.cand_post_ids != 0
+        np.testing.assert_array_equal(got.log_probs[valid], want.log_probs[valid], err_msg=name)
+        np.testing.assert_array_equal(got.continuous[valid], want.continuous[valid], err_msg=name)
+        if name.startswith("ragged"):
+            assert (got.log_probs[~valid] == 0).all() and (got.continuous[~valid] == 0).all()
+    lp, cont, _ = po.rank_forward(ocfg, w, rows_fn, b)
+    valid = b.cand_post_ids != 0
+    assert rel_l2(got.log_probs[valid], lp[valid]) < TOL
+    # the device-pointer entry point of the packing engine runs every slot
+    dev = _device_batch(torch, b)
+    out = _device_out(torch, packed.cfg, 6)
+    packed.rank_device(6, *dev, *out[:2])
+    packed.sync()
+    np.testing.assert_array_equal(out[0].cpu().numpy()[valid], want.log_probs[valid])
+    plain.close(); packed.close()
+
+
 def test_simt_gemm_path_matches_tcgen05(torch, monkeypatch):
     """The cross-check GEMM and the tcgen05 GEMM give the same forward (accumulation order aside)."""
     ocfg, w, rows_fn, eng = make_pair(max_batch=4)

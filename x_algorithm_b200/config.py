@@ -81,6 +81,8 @@ class PhoenixConfig:
     token_combine: str = "sum"  # "sum" (fp32 sum of the gathered rows) | "project" (concat(rows) @ proj_hist / proj_cand,
                                 # recsys_model.py:2163-2365)
 
+    pack_ragged: bool = False   # run ragged host-buffer batches over their valid rows only (sequence_packing.py:317)
+
     @property
     def ffn_size(self) -> int:  # phoenix/xrex/utils/utils.py:37-52
         f = int(self.widening_factor * self.emb_size)
@@ -121,4 +123,5 @@ class PhoenixConfig:
         if self.token_combine not in ("sum", "project"):
             raise ValueError("token_combine must be 'sum' or 'project'")
         c.token_project = 1 if self.token_combine == "project" else 0
+        c.pack_ragged = int(bool(self.pack_ragged))
         return c

@@ -77,14 +77,20 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
   const float csc = CAP ? 1.0f : a.sm_scale * 1.4426950408889634f;
 
   const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * QROWS;
-  if (q0 + QROWS <= a.q_start) return;   // candidate-only layer: these query rows are not wanted
+  // rows of this request: the batch's common shape, or its own counts when the rows are packed
+  int T = a.T, hist_len = a.hist_len, q_start = a.q_start;
+  if (a.pack.on()) {
+    hist_len = a.pack.hist_cnt(b);
+    T = hist_len + a.pack.cand_cnt(b);
+    if (q_start > 0) q_start = hist_len;
+  }
+  if (q0 >= T || q0 + QROWS <= q_start) return;   // past the request's rows, or history queries of a candidate-only layer
   const int hk = h / (a.Hq / a.Hkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
-  const int T = a.T;
-  // token row of position t of this request (plain or split layout)
-  auto trow = [&](int t) -> long long { return token_row(a.split, a.B, a.hist_len, T, b, t); };
-  const int n_hist = a.hist_len < T ? a.hist_len : T;
+  // token row of position t of this request (plain, split or packed layout)
+  auto trow = [&](int t) -> long long { return a.pack.on() ? a.pack.row(b, t) : token_row(a.split, a.B, hist_len, T, b, t); };
+  const int n_hist = hist_len < T ? hist_len : T;
   const int n_blocks = (n_hist + KB - 1) / KB;
   const bool has_cand = (q0 + QROWS > n_hist);     // rows at or past hist_len may be candidates
 
@@ -350,10 +356,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) ranker_attention_strip_kernel(
   const int b = blockIdx.y, h = blockIdx.x;
   const int hk = h / (a.Hq / a.Hkv);
   const int g = lane >> 2, t4 = lane & 3;
-  const int T = a.T;
-  // token row of position t of this request (plain or split layout)
-  auto trow = [&](int t) -> long long { return token_row(a.split, a.B, a.hist_len, T, b, t); };
-  const int n_hist = a.hist_len < T ? a.hist_len : T;
+  int T = a.T, hist_len = a.hist_len, q_start = a.q_start;   // the batch's common shape, or this request's own counts
+  if (a.pack.on()) {
+    hist_len = a.pack.hist_cnt(b);
+    T = hist_len + a.pack.cand_cnt(b);
+    if (q_start > 0) q_start = hist_len;
+  }
+  // token row of position t of this request (plain, split or packed layout)
+  auto trow = [&](int t) -> long long { return a.pack.on() ? a.pack.row(b, t) : token_row(a.split, a.B, hist_len, T, b, t); };
+  const int n_hist = hist_len < T ? hist_len : T;
   const int n_blocks = (n_hist + KB - 1) / KB;
   const int n_tiles = (T + QROWS - 1) / QROWS;
   const bf16* qbase = a.q + (long long)h * a.q_head_stride;
@@ -401,7 +412,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) ranker_attention_strip_kernel(
     const int all32 = __all_sync(0xffffffffu, ok);
     if (lane == 0) sall_ok[key >> 5] = all32;
   }
-  const int tile0 = a.q_start / QROWS;   // candidate-only layer: query tiles in front of q_start are not wanted
+  const int tile0 = q_start / QROWS;   // candidate-only layer: query tiles in front of q_start are not wanted
   load_q(tile0, wq(tile0));
   if (strip_has_cand(tile0)) load_own_kv(tile0);
   cp_commit();
@@ -636,7 +647,7 @@ phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::
     // go to the tcgen05 kernel (2.0 vs 4.6 ms at 1024 + 1024 tokens, 16 heads x 128).
     const int n_hist = a.hist_len < a.T ? a.hist_len : a.T;
     const bool prefer_tc = forced_tc || a.dh == 128 || n_hist > 128;
-    const bool plain = !a.split && a.q_start == 0;   // the tcgen05 kernel's tensor maps assume [B, T] token rows
+    const bool plain = !a.split && a.q_start == 0 && !a.pack.hist_off;   // the tcgen05 kernel's tensor maps assume [B, T] token rows
     if (plain && !legacy && prefer_tc && a.err_flag && ranker_attention_tc_supported(a)) return ranker_attention_tc_launch(a, a.err_flag, stream, err);
   }
   const bool cap = a.cap_method != 0 && a.cap > 0.f;

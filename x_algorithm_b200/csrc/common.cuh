@@ -68,6 +68,7 @@ struct GemmRope {
   // below split_rows are history rows of `T` per request, the rows from split_rows on sit at position pos_cap.
   // split_rows = 0: plain layout.
   long long row_offset = 0, split_rows = 0;
+  const int* pos_rows = nullptr;   // packed rows: position of every token row (overrides the rule above)
 };
 
 // Token rows of a [B, S + C] batch.  Plain layout: row = b * T + t.  Split layout (engines with candidate-only tail
@@ -77,6 +78,24 @@ __host__ __device__ inline long long token_row(int split, int B, int S, int T, i
   if (!split) return (long long)b * T + t;
   return t < S ? (long long)b * S + t : (long long)B * S + (long long)b * (T - S) + (t - S);
 }
+
+// Packed token rows (ragged batches): request b keeps only its first hist_cnt history slots and its first cand_cnt
+// candidate slots (front-filled requests), the history rows of all requests back to back, then all candidate rows:
+// row of history slot t = hist_off[b] + t, of candidate slot c = cand_base + cand_off[b] + c.  hist_off / cand_off are
+// exclusive prefix sums with B + 1 entries.  off = null: not packed.
+struct PackMap {
+  const int* hist_off = nullptr;
+  const int* cand_off = nullptr;
+  long long cand_base = 0;
+  __device__ __forceinline__ bool on() const { return hist_off != nullptr; }
+  __device__ __forceinline__ int hist_cnt(int b) const { return hist_off[b + 1] - hist_off[b]; }
+  __device__ __forceinline__ int cand_cnt(int b) const { return cand_off[b + 1] - cand_off[b]; }
+  // row of position t of request b in its own packed coordinates (history 0..hist_cnt-1, then candidates)
+  __device__ __forceinline__ long long row(int b, int t) const {
+    const int hc = hist_cnt(b);
+    return t < hc ? (long long)hist_off[b] + t : cand_base + cand_off[b] + (t - hc);
+  }
+};
 
 // RMSNorm folded around a GEMM.  Consumer side (ss_in): the A rows are the raw residual stream, the norm's gain is
 // folded into the weights, and the epilogue scales row r by rsqrt(sum_t ss_in[r][t] / D + eps) before rounding
@@ -187,10 +206,13 @@ struct TokenBuildArgs {
   // projected tokens: when concat_hist is set the kernel only lays the gathered rows side by side -
   // concat_hist [B*S, (2H+2)*D], concat_cand [B*C, 2H*D] - and writes the segment ids
   bf16* concat_hist = nullptr; bf16* concat_cand = nullptr;
+  PackMap pack;           // packed rows: slots past a request's counts are skipped altogether
   float* x32 = nullptr;   // full-precision path: bf16(sum) * input_scale kept in fp32 here (x is then not written)
   const bf16* landing = nullptr;
   const int* pos = nullptr;
 };
+phx_status pack_plan_launch(const PackMap& pk, int B, int S, int C, int* pos_rows, int* out_index, cudaStream_t stream,
+                            std::string& err);
 phx_status finish_tokens_launch(const bf16* tok_hist, const bf16* tok_cand, const TokenBuildArgs& a, cudaStream_t stream,
                                 std::string& err);
 phx_status build_tokens_launch(const TokenBuildArgs& a, cudaStream_t stream, std::string& err);
@@ -220,6 +242,7 @@ struct QkNormRopeArgs {
   const float* cos_tab;  // [pos_cap+1, dh/2]
   const float* sin_tab;
   long long row_offset = 0, split_rows = 0;   // split token layout, as in GemmRope
+  const int* pos_rows = nullptr;              // packed rows, as in GemmRope
 };
 phx_status qknorm_rope_launch(const QkNormRopeArgs& a, cudaStream_t stream, std::string& err);
 
@@ -237,6 +260,9 @@ struct AttnArgs {
   // Split token layout (token_row): q / k / v / out / seg rows are the B * hist_len history rows followed by the
   // candidate rows; mma.sync kernels only.  q_start > 0: query rows below it are not computed (candidate-only layers).
   int split = 0, q_start = 0;
+  // Packed rows (PackMap): per-request history / candidate counts; T and hist_len are then the largest a request can
+  // have (grid sizing), q_start > 0 means "history queries are not wanted".  mma.sync kernels only.
+  PackMap pack;
 };
 // tcgen05 / TMEM kernel for head dims 64 and 128 (attention_sm100.cu); the mma.sync kernel covers the rest
 bool ranker_attention_tc_supported(const AttnArgs& a);
@@ -253,6 +279,10 @@ struct HeadsArgs {
   phx_blend_spec blend;
   int has_blend;
   float* log_probs; float* continuous; double* scores;
+  // packed rows: x holds `rows` candidate rows back to back and row r's outputs go to candidate slot out_index[r] of
+  // the [B, C] output arrays (the other slots are left as they are)
+  const int* out_index = nullptr;
+  long long rows = 0;
 };
 phx_status heads_launch(const HeadsArgs& a, cudaStream_t stream, std::string& err);
 // masked mean pool + L2 normalise of final-normed history rows -> f32 [B,D]; x bf16, or fp32 (nothing rounded) when

@@ -57,7 +57,9 @@ __global__ void __launch_bounds__(256) qknorm_rope_kernel(QkNormRopeArgs a) {
   const int width = (a.Hq + 2 * a.Hkv) * dh;
   bf16* r = a.qkv + row * width;
   int pos = a.pos_cap;   // split layout (GemmRope): the candidate block sits at the cap
-  if (a.split_rows == 0 || row + a.row_offset < a.split_rows) {
+  if (a.pos_rows) {
+    pos = a.pos_rows[row + a.row_offset];
+  } else if (a.split_rows == 0 || row + a.row_offset < a.split_rows) {
     const int t = (int)((row + a.row_offset) % a.T);
     pos = t < a.pos_cap ? t : a.pos_cap;
   }

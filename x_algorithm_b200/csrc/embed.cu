@@ -46,6 +46,14 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
   const bool is_hist = t < a.S;
   const int H = a.item.num_hashes;
   const long long slot = is_hist ? (long long)b * a.S + t : (long long)b * a.C + (t - a.S);
+  long long orow;   // where this token's row goes
+  if (a.pack.on() && !a.rows_only) {
+    // packed rows: slots past the request's counts are not built at all (one token per warp: the whole warp leaves)
+    if (is_hist ? t >= a.pack.hist_cnt(b) : (t - a.S) >= a.pack.cand_cnt(b)) return;
+    orow = is_hist ? (long long)a.pack.hist_off[b] + t : a.pack.cand_base + a.pack.cand_off[b] + (t - a.S);
+  } else {
+    orow = token_row(a.split, a.B, a.S, T, b, t);
+  }
   // lanes 0..H-1 hold the post rows, lanes H..2H-1 the author rows: hashed here, or taken as given
   int my_idx = 0;
   if (a.pre_hist_post) {
@@ -62,7 +70,6 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
   }
   if (a.hashes && lane < 2 * H) a.hashes[tok * (2 * H) + lane] = my_idx;
   if (a.rows_only) return;   // uniform over the grid: the caller only wants the rows (exchange outside the kernel)
-  const long long orow = token_row(a.split, a.B, a.S, T, b, t);   // where this token's row goes
   const int first_post_hash = __shfl_sync(0xffffffffu, my_idx, 0);
   if (lane == 0) a.seg[orow] = (first_post_hash != 0) ? (is_hist ? 1 : -1) : 0;
   int act = 0, srf = 0;
@@ -148,7 +155,13 @@ __global__ void __launch_bounds__(256) finish_tokens_kernel(const bf16* __restri
   if (tok >= (long long)a.B * T) return;
   const int b = (int)(tok / T), t = (int)(tok % T);
   const bf16* src = t < a.S ? tok_hist + ((long long)b * a.S + t) * a.D : tok_cand + ((long long)b * a.C + (t - a.S)) * a.D;
-  const long long orow = token_row(a.split, a.B, a.S, T, b, t);
+  long long orow;
+  if (a.pack.on()) {
+    if (t < a.S ? t >= a.pack.hist_cnt(b) : (t - a.S) >= a.pack.cand_cnt(b)) return;
+    orow = t < a.S ? (long long)a.pack.hist_off[b] + t : a.pack.cand_base + a.pack.cand_off[b] + (t - a.S);
+  } else {
+    orow = token_row(a.split, a.B, a.S, T, b, t);
+  }
   float row_ss = 0.f;
   for (int col = lane * 8; col < a.D; col += 256) {
     const uint4 u = *reinterpret_cast<const uint4*>(src + col);
@@ -165,6 +178,22 @@ __global__ void __launch_bounds__(256) finish_tokens_kernel(const bf16* __restri
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) row_ss += __shfl_xor_sync(0xffffffffu, row_ss, o);
     if (lane < a.ss_slots) a.row_ss[orow * a.ss_slots + lane] = (lane == 0) ? row_ss : 0.f;
+  }
+}
+
+// Packed rows: the position of every packed row (RoPE) and, for the candidate rows, the slot of the [B, C] output
+// arrays each one answers.  One thread per (request, slot).
+__global__ void pack_plan_kernel(PackMap pk, int B, int S, int C, int* __restrict__ pos_rows, int* __restrict__ out_index) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int T = S + C;
+  if (i >= (long long)B * T) return;
+  const int b = (int)(i / T), t = (int)(i % T);
+  if (t < S) {
+    if (t < pk.hist_cnt(b)) pos_rows[pk.hist_off[b] + t] = t;
+  } else if (t - S < pk.cand_cnt(b)) {
+    const int r = pk.cand_off[b] + (t - S);
+    pos_rows[pk.cand_base + r] = S;               // every candidate sits at the first position after the history
+    out_index[r] = b * C + (t - S);
   }
 }
 
@@ -270,6 +299,15 @@ phx_status build_tokens_launch(const TokenBuildArgs& a, cudaStream_t stream, std
   if (toks == 0) return PHX_OK;
   const int warps = 8;
   build_tokens_kernel<<<(unsigned)((toks + warps - 1) / warps), warps * 32, 0, stream>>>(a);
+  PHX_CUDA_TRY(cudaGetLastError(), err);
+  return PHX_OK;
+}
+
+phx_status pack_plan_launch(const PackMap& pk, int B, int S, int C, int* pos_rows, int* out_index, cudaStream_t stream,
+                            std::string& err) {
+  const long long n = (long long)B * (S + C);
+  if (n == 0) return PHX_OK;
+  pack_plan_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(pk, B, S, C, pos_rows, out_index);
   PHX_CUDA_TRY(cudaGetLastError(), err);
   return PHX_OK;
 }

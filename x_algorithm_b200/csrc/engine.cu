@@ -79,6 +79,20 @@ struct phx_engine {
   // candidate block only
   bool split = false;
   int n_tail = 0;
+  // packed rows (cfg.pack_ragged): every forward addresses its token rows through a PackMap; `full` covers all slots
+  // of every request (device-pointer entry points, batches that are not front-filled), `ragged` the counts the
+  // host-buffer call found in its batch
+  struct PackState {
+    int *hist_off = nullptr, *cand_off = nullptr, *pos_rows = nullptr, *out_index = nullptr;   // device
+    long long M = 0, Mh = 0;      // packed rows in all, history rows
+    int planned_batch = -1;       // batch size pos_rows / out_index were last planned for (full plan)
+    bool ragged = false;
+  };
+  bool pack = false;
+  PackState pack_full, pack_ragged;
+  PackState* pack_next = nullptr;   // set by the host-buffer call for the forward it is about to enqueue
+  PackState* cur_pack = nullptr;    // the forward being enqueued
+  std::vector<int> pack_host;       // host copy of the offsets of the ragged plan
   // projected tokens (cfg.token_project): gathered rows side by side, two projection GEMMs, then scaling
   bool project = false;
   int Kh = 0, Kc = 0;                              // (2H + 2) * D and 2H * D
@@ -209,6 +223,12 @@ HashFamilyDev to_dev(const phx_hash_family& f, int offset) {
   return d;
 }
 
+PackMap pack_map(const phx_engine::PackState* ps) {
+  PackMap m;
+  if (ps) { m.hist_off = ps->hist_off; m.cand_off = ps->cand_off; m.cand_base = ps->Mh; }
+  return m;
+}
+
 TableView table_view(const phx_engine* e) {
   TableView v;
   for (int i = 0; i < PHX_MAX_SHARDS; ++i) v.base[i] = e->shard_ptr[i];
@@ -254,6 +274,8 @@ phx_status check_cfg(const phx_model_config& c, std::string& err) {
   if (c.compute_fp32 != 0 && c.compute_fp32 != 1) return bad("compute_fp32 must be 0 or 1");
   if (c.token_project != 0 && c.token_project != 1) return bad("token_project must be 0 or 1");
   if (c.token_project && c.compute_fp32) return bad("projected tokens are not available on the full-precision path");
+  if (c.pack_ragged != 0 && c.pack_ragged != 1) return bad("pack_ragged must be 0 or 1");
+  if (c.pack_ragged && c.compute_fp32) return bad("packed rows are not available on the full-precision path");
   if (c.num_candidate_only_layers < 0 || c.num_candidate_only_layers > c.num_layers) return bad("num_candidate_only_layers");
   return PHX_OK;
 }
@@ -380,7 +402,8 @@ phx_status run_trunk_f32(phx_engine* e, int B, int Tt, int pos_cap, int hist_len
 // (queries), out-projection and FFN run over the contiguous candidate block.
 phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len, bool split = false, int n_tail = 0) {
   if (e->fp32) return run_trunk_f32(e, B, Tt, pos_cap, hist_len, n_tail);
-  const long long M = (long long)B * Tt;
+  const phx_engine::PackState* pk = split ? nullptr : e->cur_pack;   // packed rows (ranking forward of a packing engine)
+  const long long M = pk ? pk->M : (long long)B * Tt;
   const phx_model_config& c = e->cfg;
   const float sm_scale = sqrtf(128.0f) / (float)c.key_size;  // phoenix/xrex/models/scaling.py:46-47
   phx_status s;
@@ -388,8 +411,8 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len, bo
     Layer& L = e->layers[l];
     const bool fused = e->fused_norm;
     const int slots = e->D / 64;
-    const bool tail = split && l >= c.num_layers - n_tail;
-    const long long off = tail ? (long long)B * hist_len : 0;   // first row the out-projection and FFN update
+    const bool tail = (split || pk) && l >= c.num_layers - n_tail;
+    const long long off = tail ? (pk ? pk->Mh : (long long)B * hist_len) : 0;   // first row the out-projection and FFN update
     const long long Mu = M - off;                                // rows they update
     GemmNorm n_attn_in = {e->rowss_a, nullptr, slots, 1.0f / (float)e->D, c.rms_eps};   // consume stats of x -> QKV
     GemmNorm n_attn_out = {nullptr, e->rowss_f ? e->rowss_f + off * slots : nullptr, 0, 0.f, 0.f};   // out-proj leaves stats for the FFN
@@ -410,6 +433,7 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len, bo
       gr.cos_tab = e->cos_tab; gr.sin_tab = e->sin_tab; gr.T = Tt; gr.pos_cap = pos_cap; gr.dh = e->dh;
       gr.g = e->Hq / e->Hkv; gr.group = gr.g + 2;
       if (split) { gr.T = hist_len; gr.split_rows = (long long)B * hist_len; }
+      if (pk) gr.pos_rows = pk->pos_rows;
       if ((s = do_gemm(e, pq, a_in, e->qkv, nullptr, M, EPI_ROPE, &gr, fused ? &n_attn_in : nullptr))) return s;
     } else {
       if ((s = do_gemm(e, pq, a_in, e->qkv, nullptr, M, EPI_STORE, nullptr, fused ? &n_attn_in : nullptr))) return s;
@@ -420,6 +444,7 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len, bo
       qa.rotary = c.rotary; qa.qk_norm = c.qk_norm; qa.q_gain = L.q_norm; qa.k_gain = L.k_norm;
       qa.cos_tab = e->cos_tab; qa.sin_tab = e->sin_tab;
       if (split) { qa.T = hist_len; qa.split_rows = (long long)B * hist_len; }
+      if (pk) qa.pos_rows = pk->pos_rows;
       { ProfScope ps(e, KC_ROPE); if ((s = qknorm_rope_launch(qa, e->stream, e->err))) return s; }
       e->last_launches++;
     }
@@ -436,8 +461,10 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len, bo
     aa.cap_method = (c.attn_logit_cap > 0.f) ? c.cap_method : 0;
     aa.err_flag = e->err_flag;
     aa.split = split ? 1 : 0; aa.q_start = tail ? hist_len : 0;
+    aa.pack = pack_map(pk);
     { ProfScope ps(e, KC_ATTN); if ((s = ranker_attention_launch(aa, e->stream, e->err))) return s; }
     e->last_launches++;
+    if (Mu == 0) continue;                              // a candidate-only layer of a batch without candidates
     bf16* xu = e->x + off * e->D;                       // the rows this layer updates
     const bf16* attn_u = e->attn + off * e->HD;
     bf16* ffn_u = e->ffn + off * e->F;
@@ -492,6 +519,7 @@ phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc, 
   ta.row_ss = e->fused_norm ? (ss_dst ? ss_dst : e->rowss_a) : nullptr;
   ta.ss_slots = e->D / 64;
   ta.split = (e->split && Cc > 0) ? 1 : 0;
+  if (e->cur_pack && Cc > 0 && !rows_out) ta.pack = pack_map(e->cur_pack);
   if (e->fp32) ta.x32 = e->x32;
   if (rows_out) { ta.rows_only = 1; ta.hashes = rows_out; }
   ta.landing = landing; ta.pos = pos;
@@ -566,7 +594,8 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
   e->max_tokens = (long long)cfg->max_batch * e->T;
   e->n_tail = e->C > 0 ? cfg->num_candidate_only_layers : 0;
   e->fp32 = cfg->compute_fp32 != 0;
-  e->split = e->n_tail > 0 && !e->fp32;
+  e->pack = cfg->pack_ragged != 0 && e->C > 0;
+  e->split = e->n_tail > 0 && !e->fp32 && !e->pack;   // packed rows carry their own history-first order
   const long long M = e->max_tokens;
 #define TRY(x) do { phx_status _s = (x); if (_s) return fail(_s); } while (0)
 #define CU(x) do { cudaError_t _c = (x); if (_c != cudaSuccess) { e->err = std::string(#x) + ": " + cudaGetErrorString(_c); return fail(PHX_E_CUDA); } } while (0)
@@ -590,6 +619,21 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
     }
   }
   if (cfg->primer_norm) TRY(dev_alloc(e, &e->tmp, (size_t)M * e->D));
+  if (e->pack) {
+    const int Bm = cfg->max_batch;
+    for (phx_engine::PackState* ps : {&e->pack_full, &e->pack_ragged}) {
+      TRY(dev_alloc(e, &ps->hist_off, (size_t)Bm + 1));
+      TRY(dev_alloc(e, &ps->cand_off, (size_t)Bm + 1));
+      TRY(dev_alloc(e, &ps->pos_rows, (size_t)M));
+      TRY(dev_alloc(e, &ps->out_index, (size_t)Bm * e->C));
+    }
+    std::vector<int> ho(Bm + 1), co(Bm + 1);
+    for (int b = 0; b <= Bm; ++b) { ho[b] = b * e->S; co[b] = b * e->C; }
+    CU(cudaMemcpy(e->pack_full.hist_off, ho.data(), ho.size() * 4, cudaMemcpyHostToDevice));
+    CU(cudaMemcpy(e->pack_full.cand_off, co.data(), co.size() * 4, cudaMemcpyHostToDevice));
+    e->pack_ragged.ragged = true;
+    e->pack_host.resize(2 * ((size_t)Bm + 1));
+  }
   e->project = cfg->token_project != 0;
   if (e->project) {
     const int H2 = 2 * cfg->item.num_hashes;
@@ -668,7 +712,7 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
     const size_t B = cfg->max_batch;
     const size_t H = (size_t)cfg->item.num_hashes;   // raw ids (8 bytes each) or pre-hashed rows (4 bytes x H each)
     const size_t per_id = 8 > 4 * H ? 8 : 4 * H;
-    e->in_stage_bytes = B * ((size_t)e->S * (2 * per_id + 4 + 4) + (size_t)e->C * 2 * per_id);
+    e->in_stage_bytes = B * ((size_t)e->S * (2 * per_id + 4 + 4) + (size_t)e->C * 2 * per_id) + 2 * (B + 1) * 4 + 64;
     CU(cudaMalloc(&e->in_stage_dev, e->in_stage_bytes));
     CU(cudaMallocHost(&e->in_stage_host, e->in_stage_bytes));
     const size_t rows = B * (size_t)(e->C > 0 ? e->C : 1);
@@ -711,6 +755,7 @@ void phx_engine_destroy(phx_engine* e) {
     fr(L.w_qkv_t); fr(L.w_out_t); fr(L.w_up_t); fr(L.w_down_t); fr(L.w_qkv_f); fr(L.w_up_f);
   }
   fr(e->cos_tab); fr(e->sin_tab); fr(e->x); fr(e->hbuf); fr(e->qkv); fr(e->attn); fr(e->ffn); fr(e->tmp); fr(e->tokens);
+  for (phx_engine::PackState* ps : {&e->pack_full, &e->pack_ragged}) { fr(ps->hist_off); fr(ps->cand_off); fr(ps->pos_rows); fr(ps->out_index); }
   fr(e->proj_hist_t); fr(e->proj_cand_t); fr(e->cat_hist); fr(e->cat_cand); fr(e->tok_proj);
   fr(e->x32); fr(e->h32); fr(e->qkv32); fr(e->attn32); fr(e->ffn32); fr(e->tmp32); fr(e->hist32);
   fr(e->x_alt); fr(e->seg_alt); fr(e->rowss_a_alt); fr(e->rowss_a); fr(e->rowss_f); fr(e->seg); fr(e->hashes); fr(e->err_flag); fr(e->in_stage_dev); fr(e->lp_dev); fr(e->cont_dev); fr(e->score_dev);
@@ -852,6 +897,14 @@ namespace {
 phx_status enqueue_forward(phx_engine* e, const phx_rank_batch* bd, const phx_rank_out* od, int B, bool tokens_ready,
                            const bf16* landing = nullptr, const int* pos = nullptr, const phx_rank_batch_hashed* hb = nullptr) {
   phx_status s;
+  phx_engine::PackState* pk = e->cur_pack;
+  if (pk && (pk->ragged || pk->planned_batch != B)) {
+    // positions of the packed rows and the output slot of every candidate row (the full plan only when B changed)
+    if (!pk->ragged) { pk->Mh = (long long)B * e->S; pk->M = (long long)B * e->T; }
+    e->last_launches++;
+    if ((s = pack_plan_launch(pack_map(pk), B, e->S, e->C, pk->pos_rows, pk->out_index, e->stream, e->err))) return s;
+    pk->planned_batch = pk->ragged ? -1 : B;
+  }
   if (!tokens_ready && (s = build_tokens(e, bd, B, e->C, nullptr, nullptr, nullptr, nullptr, nullptr, landing, pos, hb))) return s;
   if ((s = run_trunk(e, B, e->T, e->S, e->S, e->split, e->n_tail))) return s;
   const bool f32 = e->fp32;
@@ -859,6 +912,15 @@ phx_status enqueue_forward(phx_engine* e, const phx_rank_batch* bd, const phx_ra
   ha.x = e->x; ha.final_gain = e->final_norm; ha.unembed_t = e->unembed_t;
   ha.B = B; ha.T = e->T; ha.S = e->S; ha.C = e->C; ha.D = e->D; ha.V = e->V; ha.NC = e->NC;
   if (e->split) { ha.x = e->x + (long long)B * e->S * e->D; ha.T = e->C; ha.S = 0; }   // the candidate block of the split layout
+  if (pk) {   // packed rows: candidate rows back to back, scattered to their output slots; padded slots read zero
+    ha.x = e->x + pk->Mh * e->D; ha.out_index = pk->out_index; ha.rows = pk->M - pk->Mh;
+    if (pk->ragged) {
+      const size_t rows = (size_t)B * e->C;
+      if (od->log_probs) PHX_CUDA_TRY(cudaMemsetAsync(od->log_probs, 0, rows * e->V * 4, e->stream), e->err);
+      if (od->continuous) PHX_CUDA_TRY(cudaMemsetAsync(od->continuous, 0, rows * e->NC * 4, e->stream), e->err);
+      if (od->scores) PHX_CUDA_TRY(cudaMemsetAsync(od->scores, 0, rows * 8, e->stream), e->err);
+    }
+  }
   ha.eps = e->cfg.rms_eps; ha.output_scale = 2.0f * sqrtf(512.0f / (float)e->D);  // scaling.py:43-44
   ha.final_logit_cap = e->cfg.final_logit_cap; ha.dwell_norm_scale = e->cfg.dwell_norm_scale;
   ha.has_blend = e->has_blend ? 1 : 0;
@@ -878,6 +940,8 @@ phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* bd, cons
   cudaSetDevice(e->device);
   const int B = bd->batch;
   e->last_batch = B; e->last_launches = 0; e->prof_used = 0;
+  e->cur_pack = e->pack ? (e->pack_next ? e->pack_next : &e->pack_full) : nullptr;
+  e->pack_next = nullptr;
   if (B == 0) return PHX_OK;
   PHX_CUDA_TRY(cudaEventRecord(e->ev0, e->stream), e->err);
   phx_status s;
@@ -895,7 +959,8 @@ phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* bd, cons
   // Graph replay: same batch size and the same buffers as the previous call (a serving loop over its own staging
   // buffers).  The first such repeat is captured; diagnostics, prefetching and buffer swaps keep the eager path.
   const bool same_key = e->graph_key_valid && memcmp(&e->graph_key_b, bd, sizeof(*bd)) == 0 && memcmp(&e->graph_key_o, od, sizeof(*od)) == 0;
-  const bool eligible = e->graphs_enabled && !e->profile && !e->sync_debug && !e->debug_taps && !e->side_stream && !tokens_ready;
+  const bool eligible = e->graphs_enabled && !e->profile && !e->sync_debug && !e->debug_taps && !e->side_stream && !tokens_ready &&
+                        !(e->cur_pack && e->cur_pack->ragged);   // a ragged plan changes the launches from call to call
   if (!same_key && e->graph_exec) { cudaGraphExecDestroy(e->graph_exec); e->graph_exec = nullptr; }
   if (eligible && same_key && e->graph_exec) {
     PHX_CUDA_TRY(cudaGraphLaunch(e->graph_exec, e->stream), e->err);
@@ -949,6 +1014,7 @@ phx_status phx_rank_forward_rows_device(phx_engine* e, const phx_rank_batch* bd,
   e->last_batch = B; e->last_launches = 0; e->prof_used = 0;
   e->prefetch_valid = false;
   e->graph_key_valid = false;
+  e->cur_pack = e->pack ? &e->pack_full : nullptr;
   PHX_CUDA_TRY(cudaEventRecord(e->ev0, e->stream), e->err);
   phx_status s;
   if ((s = refresh_folded(e))) return s;
@@ -970,6 +1036,7 @@ phx_status phx_rank_forward_hashed_device(phx_engine* e, const phx_rank_batch_ha
   e->last_batch = B; e->last_launches = 0; e->prof_used = 0;
   e->prefetch_valid = false;
   e->graph_key_valid = false;   // plain launches: the graph cache is keyed on id batches
+  e->cur_pack = e->pack ? &e->pack_full : nullptr;
   if (B == 0) return PHX_OK;
   PHX_CUDA_TRY(cudaEventRecord(e->ev0, e->stream), e->err);
   phx_status s;
@@ -1019,6 +1086,7 @@ phx_status phx_rank_prefetch_device(phx_engine* e, const phx_rank_batch* bd) {
   if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
   if (bd->batch <= 0 || bd->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
   if (e->fp32) { e->err = "token prefetch is not available on the full-precision path"; return PHX_E_ARG; }
+  if (e->pack) { e->err = "token prefetch is not available on an engine that packs ragged batches"; return PHX_E_ARG; }
   if (!params_complete(e, true) || !shards_complete(e)) return PHX_E_STATE;
   cudaSetDevice(e->device);
   if (!e->side_stream) {
@@ -1060,7 +1128,40 @@ phx_status phx_rank_forward(phx_engine* e, const phx_rank_batch* bh, const phx_r
   bd.cand_author_ids = (const int64_t*)put(bh->cand_author_ids, B * C * 8);
   bd.hist_actions = (const int32_t*)put(bh->hist_actions, B * S * 4);
   bd.hist_surfaces = (const int32_t*)put(bh->hist_surfaces, B * S * 4);
-  PHX_CUDA_TRY(cudaMemcpyAsync(dp, hp, off, cudaMemcpyHostToDevice, e->stream), e->err);
+  if (e->pack) {
+    // Packed rows: the leading non-padding slots of every request (id 0 = padding).  A batch with padding in front
+    // of a valid slot is run over all its slots.  A request keeps at least one history row (a padded one when it has
+    // none), so every request has a key block.
+    int* ho = e->pack_host.data();
+    int* co = ho + (B + 1);
+    bool front_filled = true;
+    ho[0] = co[0] = 0;
+    for (size_t b = 0; b < B && front_filled; ++b) {
+      const int64_t* hpid = bh->hist_post_ids + b * S;
+      const int64_t* cpid = bh->cand_post_ids + b * C;
+      size_t hc = 0, cc = 0;
+      while (hc < S && hpid[hc] != 0) ++hc;
+      while (cc < C && cpid[cc] != 0) ++cc;
+      for (size_t t = hc; t < S; ++t) if (hpid[t] != 0) front_filled = false;
+      for (size_t c = cc; c < C; ++c) if (cpid[c] != 0) front_filled = false;
+      ho[b + 1] = ho[b] + (int)(hc > 0 ? hc : 1);
+      co[b + 1] = co[b] + (int)cc;
+    }
+    if (!front_filled)
+      for (size_t b = 0; b < B; ++b) { ho[b + 1] = (int)((b + 1) * S); co[b + 1] = (int)((b + 1) * C); }
+    off = (off + 15) & ~(size_t)15;
+    const int* ho_dev = (const int*)put(ho, (B + 1) * 4);
+    const int* co_dev = (const int*)put(co, (B + 1) * 4);
+    phx_engine::PackState& pk = e->pack_ragged;
+    pk.Mh = ho[B]; pk.M = (long long)ho[B] + co[B];
+    // the plan's offset arrays live in the engine's own buffers: copied there behind the input block
+    PHX_CUDA_TRY(cudaMemcpyAsync(dp, hp, off, cudaMemcpyHostToDevice, e->stream), e->err);
+    PHX_CUDA_TRY(cudaMemcpyAsync(pk.hist_off, ho_dev, (B + 1) * 4, cudaMemcpyDeviceToDevice, e->stream), e->err);
+    PHX_CUDA_TRY(cudaMemcpyAsync(pk.cand_off, co_dev, (B + 1) * 4, cudaMemcpyDeviceToDevice, e->stream), e->err);
+    e->pack_next = &pk;
+  } else {
+    PHX_CUDA_TRY(cudaMemcpyAsync(dp, hp, off, cudaMemcpyHostToDevice, e->stream), e->err);
+  }
   phx_rank_out od; od.log_probs = e->lp_dev; od.continuous = e->cont_dev; od.scores = e->score_dev;
   phx_status s = phx_rank_forward_device(e, &bd, &od);
   if (s) return s;
@@ -1324,6 +1425,7 @@ phx_status phx_user_tower_device(phx_engine* e, const phx_rank_batch* bd, float*
   phx_status s;
   if ((s = refresh_folded(e))) return s;
   // history only: tokens laid out [B, S]; every valid token is "history" so attention is full among them
+  e->cur_pack = nullptr;
   if ((s = build_tokens(e, bd, B, 0))) return s;
   if ((s = run_trunk(e, B, e->S, e->S, e->S))) return s;
   { ProfScope ps(e, KC_HEADS); if ((s = tower_pool_launch(e->fp32 ? (const void*)e->x32 : (const void*)e->x, e->final_norm, e->seg, B, e->S, e->D, e->cfg.rms_eps, users_dev, e->stream, e->err, e->fp32))) return s; }

@@ -329,7 +329,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           // columns [16p, 16p+16) against [32+16p, 48+16p); head dim 32 = pass p is the slab's p-th part.
           const long long row = m0 + row_in_tile + rope.row_offset;
           int pos = rope.pos_cap;                       // split layout: the candidate block sits at the cap
-          if (rope.split_rows == 0 || row < rope.split_rows) {
+          if (rope.pos_rows) {                          // packed rows: the position comes with the row
+            pos = row < M + rope.row_offset ? rope.pos_rows[row] : 0;
+          } else if (rope.split_rows == 0 || row < rope.split_rows) {
             const int t = (int)(row % rope.T);
             pos = t < rope.pos_cap ? t : rope.pos_cap;
           }

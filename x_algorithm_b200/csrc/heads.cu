@@ -27,11 +27,13 @@ __global__ void __launch_bounds__(256) heads_kernel(HeadsArgs a) {
     *reinterpret_cast<uint4*>(sw + i) = *reinterpret_cast<const uint4*>(a.unembed_t + i);
   __syncthreads();
   const int lane = threadIdx.x & 31;
-  const long long nrows = (long long)a.B * a.C;
+  const long long nrows = a.out_index ? a.rows : (long long)a.B * a.C;
   for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < nrows;
        r += (long long)gridDim.x * (blockDim.x >> 5)) {
     const int b = (int)(r / a.C), c = (int)(r % a.C);
-    const bf16* xr = a.x + ((long long)b * a.T + a.S + c) * a.D;
+    // packed rows: candidate rows back to back, each answering the output slot out_index[r]
+    const bf16* xr = a.out_index ? a.x + r * a.D : a.x + ((long long)b * a.T + a.S + c) * a.D;
+    const long long orow = a.out_index ? a.out_index[r] : r;
     float ss = 0.f;
     for (int k = lane * 8; k < a.D; k += 256) {
       uint4 u = *reinterpret_cast<const uint4*>(xr + k);
@@ -77,12 +79,12 @@ __global__ void __launch_bounds__(256) heads_kernel(HeadsArgs a) {
       float lg = round_bf(round_bf(mine) * a.output_scale);
       if (a.final_logit_cap > 0.f) lg = round_bf(a.final_logit_cap * tanhf(lg / a.final_logit_cap));
       logp = fminf(lg, 0.f) - log1pf(expf(-fabsf(lg)));  // log_sigmoid in fp32
-      if (a.log_probs) a.log_probs[r * a.V + lane] = logp;
+      if (a.log_probs) a.log_probs[orow * a.V + lane] = logp;
     } else if (lane < NO) {
       float cl = round_bf(mine);
       float sg = round_bf(1.0f / (1.0f + expf(-cl)));
       value = round_bf(sg * a.dwell_norm_scale);
-      if (a.continuous) a.continuous[r * a.NC + (lane - a.V)] = value;
+      if (a.continuous) a.continuous[orow * a.NC + (lane - a.V)] = value;
     }
     if (a.has_blend && a.scores) {
       // exp(ln p as f32 -> f64) like the client side; terms summed left to right in f64 by lane 0
@@ -98,7 +100,7 @@ __global__ void __launch_bounds__(256) heads_kernel(HeadsArgs a) {
         if (a.blend.total_sum == 0.0) out = s > 0.0 ? s : 0.0;
         else if (s < 0.0) out = (s + a.blend.negative_sum) / a.blend.total_sum * 0.001;
         else out = s + 0.001;
-        a.scores[r] = out;
+        a.scores[orow] = out;
       }
     }
   }
@@ -141,7 +143,7 @@ __global__ void __launch_bounds__(HM_WARPS * 32) heads_mma_kernel(HeadsArgs a) {
   __syncthreads();
   float* sC = sC_all + warp * 16 * NT * 8;
   double* sD = sD_all + warp * 16 * NT * 8;
-  const long long nrows = (long long)a.B * a.C;
+  const long long nrows = a.out_index ? a.rows : (long long)a.B * a.C;
   const long long n_strips = (nrows + 15) / 16;
   const int groups = D / 32;
   for (long long strip = (long long)blockIdx.x * HM_WARPS + warp; strip < n_strips; strip += (long long)gridDim.x * HM_WARPS) {
@@ -151,7 +153,7 @@ __global__ void __launch_bounds__(HM_WARPS * 32) heads_mma_kernel(HeadsArgs a) {
     for (int i = 0; i < 2; ++i) {
       long long r = r0 + g + 8 * i;
       if (r >= nrows) r = nrows - 1;
-      xr[i] = a.x + ((r / a.C) * a.T + a.S + (r % a.C)) * (long long)D + 8 * t4;
+      xr[i] = (a.out_index ? a.x + r * (long long)D : a.x + ((r / a.C) * a.T + a.S + (r % a.C)) * (long long)D) + 8 * t4;
     }
     // pass 1: sums of squares (a row's 32-column groups are spread over the 4 lanes of its quad)
     float ss[2] = {0.f, 0.f};
@@ -207,19 +209,20 @@ __global__ void __launch_bounds__(HM_WARPS * 32) heads_mma_kernel(HeadsArgs a) {
     for (int idx = lane; idx < 16 * NO; idx += 32) {
       const int rr = idx / NO, oo = idx % NO;
       const long long r = r0 + rr;
+      const long long orow = (a.out_index && r < nrows) ? a.out_index[r] : r;   // packed rows: the output slot this row answers
       const float mine = sC[rr * (NT * 8) + oo];
       double col;
       if (oo < a.V) {
         float lg = round_bf(round_bf(mine) * a.output_scale);
         if (a.final_logit_cap > 0.f) lg = round_bf(a.final_logit_cap * tanhf(lg / a.final_logit_cap));
         const float logp = fminf(lg, 0.f) - log1pf(expf(-fabsf(lg)));  // log_sigmoid in fp32
-        if (a.log_probs && r < nrows) a.log_probs[r * a.V + oo] = logp;
+        if (a.log_probs && r < nrows) a.log_probs[orow * a.V + oo] = logp;
         col = a.has_blend ? exp((double)logp) : 0.0;   // exp(ln p as f32 -> f64) like the client side
       } else {
         const float cl = round_bf(mine);
         const float sg = round_bf(1.0f / (1.0f + expf(-cl)));
         const float value = round_bf(sg * a.dwell_norm_scale);
-        if (a.continuous && r < nrows) a.continuous[r * a.NC + (oo - a.V)] = value;
+        if (a.continuous && r < nrows) a.continuous[orow * a.NC + (oo - a.V)] = value;
         col = (double)value;
       }
       sD[rr * (NT * 8) + oo] = col;
@@ -232,7 +235,7 @@ __global__ void __launch_bounds__(HM_WARPS * 32) heads_mma_kernel(HeadsArgs a) {
       if (a.blend.total_sum == 0.0) out = s > 0.0 ? s : 0.0;
       else if (s < 0.0) out = (s + a.blend.negative_sum) / a.blend.total_sum * 0.001;
       else out = s + 0.001;
-      a.scores[r0 + lane] = out;
+      a.scores[a.out_index ? a.out_index[r0 + lane] : r0 + lane] = out;
     }
     __syncwarp();
   }
@@ -310,7 +313,7 @@ phx_status heads_launch(const HeadsArgs& a, cudaStream_t stream, std::string& er
     for (int i = 0; i < a.blend.num_terms; ++i)
       if (a.blend.src[i] < 0 || a.blend.src[i] >= NO) { err = "heads: blend term source out of range"; return PHX_E_ARG; }
   }
-  const long long rows = (long long)a.B * a.C;
+  const long long rows = a.out_index ? a.rows : (long long)a.B * a.C;
   if (rows == 0) return PHX_OK;
   if (a.D % 32 == 0 && !(getenv("PHX_HEADS") && strcmp(getenv("PHX_HEADS"), "scalar") == 0)) {   // tensor-core path
     if (NO <= 8) return launch_heads_mma<1>(a, rows, stream, err);
