@@ -255,6 +255,37 @@ def bench_mma(a):
                               fill_tbs=tiles * 16384.0 * a.ksteps * 148 / (ms.value * 1e-3) / 1e12)))
 
 
+def bench_ragged(a):
+    """Ragged ranking batches through the blocking host-buffer call, with and without packed rows: BASELINE config 1's
+    model, --batch requests whose valid history / candidate counts are uniform in [1, S] / [1, C]."""
+    import math
+    import time
+    import x_algorithm_b200 as px
+    from oracle import phoenix_oracle as po   # synthetic weights and batches only
+    wl = dict(emb_size=512, num_layers=8, num_q_heads=8, num_kv_heads=8, key_size=64, widening_factor=4.0, history_len=128,
+              num_candidates=512, num_actions=19, num_continuous=1, num_hashes=2, table_size=1 << a.log2_rows)
+    ocfg = po.ModelConfig(**wl)
+    w = po.make_weights(ocfg, 0)
+    batch = po.make_batch(ocfg, a.batch, seed=2, ragged=True)
+    valid = int((batch.cand_post_ids != 0).sum())
+    rows = int((batch.cand_post_ids != 0).sum() + (batch.hist_post_ids != 0).sum())
+    inp = px.RankInputs(batch.hist_post_ids, batch.hist_author_ids, batch.hist_actions, batch.hist_surfaces,
+                        batch.cand_post_ids, batch.cand_author_ids)
+    for pack in (False, True):
+        eng = px.PhoenixEngine(px.PhoenixConfig(max_batch=a.batch, pack_ragged=pack, **wl), 0)
+        eng.load_weights(w)
+        eng.table_fill_synthetic(7, 1.0 / math.sqrt(512))
+        out = None
+        for i in range(a.warmup + a.iters):
+            if i == a.warmup:
+                t0 = time.perf_counter()
+            out = eng.rank(inp, out)
+        dt = (time.perf_counter() - t0) / a.iters
+        print(json.dumps(dict(op="rank_ragged", packed=pack, batch=a.batch, valid_candidates=valid, valid_rows=rows,
+                              slots=a.batch * 640, ms=dt * 1e3, valid_candidates_per_s=valid / dt)))
+        eng.close()
+
+
 def bench_value(a):
     """The value model behind the heads (phx_value_scores_device): --batch requests x --cands candidates, every gate,
     author diversity and class factors on, fuse_heads recomputed (no cached weighted score)."""
@@ -288,7 +319,7 @@ def bench_value(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gather", "topk", "attention", "retrieve", "mma", "value"])
+    ap.add_argument("op", choices=["gather", "topk", "attention", "retrieve", "mma", "value", "ragged"])
     ap.add_argument("--ksteps", type=int, default=200000, help="mma: k-steps per CTA (2000000 runs about a second)")
     ap.add_argument("--check", action="store_true")
     ap.add_argument("--no-dedup", action="store_true", help="sharded gather: send every request, not only distinct rows")
@@ -313,7 +344,7 @@ def main():
     ap.add_argument("--cands", type=int, default=1024)
     a = ap.parse_args()
     {"gather": bench_gather, "topk": bench_topk, "attention": bench_attention, "retrieve": bench_retrieve, "mma": bench_mma,
-     "value": bench_value}[a.op](a)
+     "value": bench_value, "ragged": bench_ragged}[a.op](a)
 
 
 if __name__ == "__main__":
