@@ -88,9 +88,13 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
   const int hk = h / (a.Hq / a.Hkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
-  // token row of position t of this request (plain, split or packed layout)
-  auto trow = [&](int t) -> long long { return a.pack.on() ? a.pack.row(b, t) : token_row(a.split, a.B, hist_len, T, b, t); };
+  // token row of position t of this request: in every layout (plain, split, packed) the history slots are one run of
+  // consecutive rows and the candidate slots another
   const int n_hist = hist_len < T ? hist_len : T;
+  int hrow0, crow0;   // row of t = hrow0 + t in front of n_hist, crow0 + t from there on (token rows fit 31 bits)
+  if (a.pack.on()) { hrow0 = a.pack.hist_off[b]; crow0 = (int)(a.pack.cand_base + a.pack.cand_off[b]) - n_hist; }
+  else { hrow0 = (int)token_row(a.split, a.B, hist_len, T, b, 0); crow0 = (int)token_row(a.split, a.B, hist_len, T, b, n_hist) - n_hist; }
+  auto trow = [&](int t) -> long long { return (long long)((t < n_hist ? hrow0 : crow0) + t); };
   const int n_blocks = (n_hist + KB - 1) / KB;
   const bool has_cand = (q0 + QROWS > n_hist);     // rows at or past hist_len may be candidates
 
@@ -362,9 +366,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) ranker_attention_strip_kernel(
     T = hist_len + a.pack.cand_cnt(b);
     if (q_start > 0) q_start = hist_len;
   }
-  // token row of position t of this request (plain, split or packed layout)
-  auto trow = [&](int t) -> long long { return a.pack.on() ? a.pack.row(b, t) : token_row(a.split, a.B, hist_len, T, b, t); };
+  // token row of position t of this request: in every layout (plain, split, packed) the history slots are one run of
+  // consecutive rows and the candidate slots another
   const int n_hist = hist_len < T ? hist_len : T;
+  int hrow0, crow0;   // row of t = hrow0 + t in front of n_hist, crow0 + t from there on (token rows fit 31 bits)
+  if (a.pack.on()) { hrow0 = a.pack.hist_off[b]; crow0 = (int)(a.pack.cand_base + a.pack.cand_off[b]) - n_hist; }
+  else { hrow0 = (int)token_row(a.split, a.B, hist_len, T, b, 0); crow0 = (int)token_row(a.split, a.B, hist_len, T, b, n_hist) - n_hist; }
+  auto trow = [&](int t) -> long long { return (long long)((t < n_hist ? hrow0 : crow0) + t); };
   const int n_blocks = (n_hist + KB - 1) / KB;
   const int n_tiles = (T + QROWS - 1) / QROWS;
   const bf16* qbase = a.q + (long long)h * a.q_head_stride;
