@@ -75,6 +75,10 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
   int* skey_ok = reinterpret_cast<int*>(skv + 4 * KB * LD);  // [2][KB]
   int* sall_ok = skey_ok + 2 * KB;                           // [2][2] per buffer and 32-key half: all keys valid history
   const float csc = CAP ? 1.0f : a.sm_scale * 1.4426950408889634f;
+  // programmatic dependent launch: the kernel may have been started before the one in front of it on the stream
+  // finished; wait for that one before reading what it wrote, and let the kernel behind begin its own set-up
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * QROWS;
   // rows of this request: the batch's common shape, or its own counts when the rows are packed
@@ -314,6 +318,23 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
   }
 }
 
+// launch with the attribute that lets the kernel start while its predecessor on the stream drains (the kernels wait
+// before they read global memory); PHX_PDL=0 keeps plain stream order
+template <typename Kern>
+cudaError_t launch_overlapped(Kern kern, dim3 grid, int threads, size_t smem, cudaStream_t stream, const AttnArgs& a) {
+  cudaLaunchConfig_t lc;
+  memset(&lc, 0, sizeof(lc));
+  lc.gridDim = grid; lc.blockDim = dim3(threads); lc.dynamicSmemBytes = smem; lc.stream = stream;
+  cudaLaunchAttribute at[1];
+  static const bool pdl = !(getenv("PHX_PDL") && getenv("PHX_PDL")[0] == '0');
+  if (pdl) {
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at; lc.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&lc, kern, a);
+}
+
 template <int DH, bool CAP>
 phx_status launch_dh(const AttnArgs& a, cudaStream_t stream, std::string& err) {
   constexpr int LD = DH + 8;
@@ -324,8 +345,7 @@ phx_status launch_dh(const AttnArgs& a, cudaStream_t stream, std::string& err) {
     attr_set = true;
   }
   dim3 grid((a.T + QROWS - 1) / QROWS, a.Hq, a.B);
-  ranker_attention_kernel<DH, CAP><<<grid, ATT_THREADS, smem, stream>>>(a);
-  PHX_CUDA_TRY(cudaGetLastError(), err);
+  PHX_CUDA_TRY(launch_overlapped(ranker_attention_kernel<DH, CAP>, grid, ATT_THREADS, smem, stream, a), err);
   return PHX_OK;
 }
 
@@ -356,6 +376,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) ranker_attention_strip_kernel(
   int* skey_ok = reinterpret_cast<int*>(hv_s + STRIP_HIST * 64 + ATT_WARPS * 4 * 16 * 64);   // [128]
   int* sall_ok = skey_ok + STRIP_HIST;                                                       // [4] per 32 keys
   const float csc = CAP ? 1.0f : a.sm_scale * 1.4426950408889634f;
+  // programmatic dependent launch: the kernel may have been started before the one in front of it on the stream
+  // finished; wait for that one before reading what it wrote, and let the kernel behind begin its own set-up
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const int b = blockIdx.y, h = blockIdx.x;
   const int hk = h / (a.Hq / a.Hkv);
@@ -634,8 +658,7 @@ phx_status launch_strip(const AttnArgs& a, cudaStream_t stream, std::string& err
     attr_set = true;
   }
   dim3 grid(a.Hq, a.B);
-  ranker_attention_strip_kernel<CAP><<<grid, ATT_THREADS, STRIP_SMEM, stream>>>(a);
-  PHX_CUDA_TRY(cudaGetLastError(), err);
+  PHX_CUDA_TRY(launch_overlapped(ranker_attention_strip_kernel<CAP>, grid, ATT_THREADS, STRIP_SMEM, stream, a), err);
   return PHX_OK;
 }
 

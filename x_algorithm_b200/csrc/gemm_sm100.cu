@@ -130,6 +130,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (PAIR) cluster_sync_all();   // the peer's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // Programmatic dependent launch: everything above (barriers, tensor memory, cluster hand-shake) touched no global
+  // data, so it may run while the kernel in front of this one on the stream is still finishing.  From here on the
+  // kernel reads what its predecessor wrote: wait for it (a no-op for a launch without the attribute), and let the
+  // kernel behind start its own set-up.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -450,21 +456,34 @@ phx_status launch_t(const GemmPlan& p, const GemmRope& rope, const GemmNorm& nor
   static int max_pairs = 0;
   cudaLaunchConfig_t lc;
   memset(&lc, 0, sizeof(lc));
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   lc.blockDim = dim3(gemm_threads(NG));
   lc.dynamicSmemBytes = cfg::SMEM_BYTES;
   lc.stream = stream;
+  lc.attrs = attr; lc.numAttrs = 0;
   if (PAIR) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    lc.attrs = attr; lc.numAttrs = 1;
+    attr[lc.numAttrs].id = cudaLaunchAttributeClusterDimension;
+    attr[lc.numAttrs].val.clusterDim.x = 2; attr[lc.numAttrs].val.clusterDim.y = 1; attr[lc.numAttrs].val.clusterDim.z = 1;
+    lc.numAttrs++;
+  }
+  const int attrs_for_query = lc.numAttrs;
+  // the kernel's set-up may overlap the tail of the kernel in front of it (it waits before it reads global data);
+  // PHX_PDL=0 keeps plain stream order
+  static const bool pdl = !(getenv("PHX_PDL") && getenv("PHX_PDL")[0] == '0');
+  if (pdl) {
+    attr[lc.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[lc.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+    lc.numAttrs++;
   }
   if (!attr_set) {
     PHX_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES), err);
     if (PAIR) {   // how many CTA pairs the device can hold at once (pairs need two SMs of one cluster-capable group)
       lc.gridDim = dim3(2 * (num_sms / 2));
       int n = 0;
+      const int all_attrs = lc.numAttrs;
+      lc.numAttrs = attrs_for_query;   // the occupancy query takes the cluster shape only
       PHX_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kern, &lc), err);
+      lc.numAttrs = all_attrs;
       max_pairs = n < num_sms / 2 ? n : num_sms / 2;
       if (max_pairs <= 0) { err = "gemm: the device cannot hold a CTA pair of this kernel"; return PHX_E_CUDA; }
     }
