@@ -114,6 +114,8 @@ struct GemmNorm {
 struct GemmPlan {
   CUtensorMap map_a;
   CUtensorMap map_b;
+  CUtensorMap map_b_narrow;   // W map for 128-column tiles, used when a call has too few wide tiles to fill the device
+  bool has_narrow = false;
   CUtensorMap map_c;   // output map, re-encoded when the output pointer or M changes
   CUtensorMap map_r;   // residual map, likewise
   const bf16* c_ptr = nullptr; const bf16* r_ptr = nullptr;

@@ -567,6 +567,11 @@ phx_status gemm_plan_create(GemmPlan* plan, const bf16* A, const bf16* Wt, int64
   if (s != PHX_OK) return s;
   s = make_map(&plan->map_b, Wt, N, K, plan->pair ? plan->BN / 2 : plan->BN, err);
   if (s != PHX_OK) return s;
+  if (plan->BN == 256) {   // small calls (a single request) run 128-column tiles: twice the CTAs, half the work per tile
+    s = make_map(&plan->map_b_narrow, Wt, N, K, plan->pair ? 64 : 128, err);
+    if (s != PHX_OK) return s;
+    plan->has_narrow = true;
+  }
   plan->ready = true;
   return PHX_OK;
 }
@@ -607,6 +612,17 @@ phx_status gemm_launch(GemmPlan& p, const bf16* A, bf16* C, const bf16* R, int64
     p.r_ptr = R; p.r_rows = M;
   }
   if (p.BN == 256) {
+    // latency regime: when even the 128-column tiles leave SMs idle, take them - the call's time is one tile's time
+    const long long rows_per_tile = p.pair ? 2 * BM : BM;
+    const long long narrow_tiles = ((M + rows_per_tile - 1) / rows_per_tile) * ((p.N + 127) / 128);
+    const long long slots = p.pair ? num_sms / 2 : num_sms;
+    static const bool allow = !(getenv("PHX_GEMM_TILES") && strcmp(getenv("PHX_GEMM_TILES"), "wide") == 0);
+    if (allow && p.has_narrow && narrow_tiles <= slots) {
+      GemmPlan q = p;
+      q.map_b = p.map_b_narrow; q.BN = 128;
+      return q.pair ? launch_e<128, true>(q, epilogue, rp, nm, M, err_flag, num_sms, stream, err)
+                    : launch_e<128, false>(q, epilogue, rp, nm, M, err_flag, num_sms, stream, err);
+    }
     return p.pair ? launch_e<256, true>(p, epilogue, rp, nm, M, err_flag, num_sms, stream, err)
                   : launch_e<256, false>(p, epilogue, rp, nm, M, err_flag, num_sms, stream, err);
   }
