@@ -34,6 +34,43 @@ def test_struct_layouts_match_header():
     assert C.sizeof(_lib.ModelConfig) == 17 * 4 + 5 * 4 + 4 * C.sizeof(_lib.HashFamily) + 6 * 4
     assert C.sizeof(_lib.BlendSpec) == 8 + 32 * 4 + 32 * 8 + 16 - 4 + 4   # int + pad, src, weight, two doubles
     assert C.sizeof(_lib.RankBatch) == 8 + 6 * 8 and C.sizeof(_lib.RankOut) == 24
+    # phx_value_model: 32 int sources, 30 + 9 doubles, 6 ints; phx_value_inputs: 4 ints + 9 pointers
+    assert C.sizeof(_lib.ValueModel) == 32 * 4 + 39 * 8 + 6 * 4 and C.sizeof(_lib.ValueInputs) == 4 * 4 + 9 * 8
+    assert _lib.ModelConfig.pack_ragged.offset == C.sizeof(_lib.ModelConfig) - 4
+
+
+def test_config_options_reach_the_c_struct():
+    import x_algorithm_b200 as px
+    c = px.PhoenixConfig(num_candidate_only_layers=2, compute="fp32", token_combine="project", pack_ragged=True).to_c()
+    assert (c.num_candidate_only_layers, c.compute_fp32, c.token_project, c.pack_ragged) == (2, 1, 1, 1)
+    d = px.PhoenixConfig().to_c()
+    assert (d.num_candidate_only_layers, d.compute_fp32, d.token_project, d.pack_ragged) == (0, 0, 0, 0)
+    import pytest
+    with pytest.raises(ValueError):
+        px.PhoenixConfig(compute="fp16").to_c()
+    with pytest.raises(ValueError):
+        px.PhoenixConfig(token_combine="mean").to_c()
+
+
+def test_value_model_struct_mirrors_the_weights():
+    """phx_value_model built from ValueModelWeights: sources by PhoenixScores field order, weights by term order, the
+    offset sums of the active mode (weights.rs:99-113)."""
+    import x_algorithm_b200.value_model as vm
+    wt = vm.ValueModelWeights(w=dict(favorite=2.0, reply=4.0, report=-100.0, not_dwelled=-3.0, cont_dwell_time=0.1,
+                                     video_continuation=0.5), bidirectional_follow_reply_weight_boost=1.0,
+                              enable_author_diversity=True, author_diversity_decay=0.5, author_diversity_floor=0.25, engage_bias=0.2)
+    m = vm.value_model_struct(wt, ["favorite", "report", "reply"], ["dwell_time", "home_video_continuation_secs"])
+    src = list(m.src)[:29]
+    assert src[vm.SCORE_FIELDS.index("favorite")] == 0 and src[vm.SCORE_FIELDS.index("report")] == 1
+    assert src[vm.SCORE_FIELDS.index("reply")] == 2 and src[vm.SCORE_FIELDS.index("dwell_time")] == 3
+    assert src[vm.SCORE_FIELDS.index("home_video_continuation_secs")] == 4 and src[vm.SCORE_FIELDS.index("vqv")] == -1
+    w = list(m.w)
+    assert w[vm.TERM_ORDER.index("favorite")] == 2.0 and w[vm.TERM_ORDER.index("dwell_time")] == 0.1
+    assert w[vm.TERM_ORDER.index("video_continuation")] == 0.5 and w[vm.TERM_ORDER.index("report")] == -100.0
+    assert (m.offset_total_sum, m.offset_negative_sum) == (6.0 + 103.0, 103.0)
+    import dataclasses
+    mm = vm.value_model_struct(dataclasses.replace(wt, multiplicative=True), ["favorite"], [])
+    assert (mm.offset_total_sum, mm.offset_negative_sum) == (6.0 + 0.2 + 100.0, 100.0) and mm.multiplicative == 1
 
 
 def test_config_matches_oracle_layout():
