@@ -105,6 +105,13 @@ typedef struct phx_model_config {
    * over all its slots.  Outputs of padded candidate slots are zero.  The device-pointer entry points and the
    * submit / collect pipeline run over all slots. */
   int32_t pack_ragged;
+  /* 1 = the history actions of a position are a SET: hist_actions holds a bit mask (bit v = action v, v <
+   * num_action_types <= 32; the reference's bool[B,S,V] buffer packed), and "action_table" is one [1, emb_size] vector
+   * cut into num_action_types chunks, chunk v signed by 2 a_v - 1, the row zero where no action is set
+   * (multi_hot_to_embeddings, recsys_model.py:3259-3314).  emb_size / num_action_types must be a multiple of 8.
+   * 0 = one action id per position looked up in a [num_action_types + 1, emb_size] table. */
+  int32_t action_multi_hot;
+  int32_t _pad2;
 } phx_model_config;
 
 /* Weighted blend in term-list form: xai-value-model/scoring.rs:67-73, 112-120, 282-291.

@@ -232,6 +232,7 @@ class ModelConfig:
     compute: str = "bf16"          # "bf16" | "fp32"
     num_candidate_only_layers: int = 0   # tail layers that leave the history rows frozen (transformer.py:789-871)
     token_combine: str = "sum"     # "sum" | "project": concat(rows) @ proj_mat (recsys_model.py:2163-2365)
+    action_multi_hot: bool = False  # history actions as a set per position (multi_hot_to_embeddings, recsys_model.py:3259-3314)
 
     @property
     def ffn_size(self) -> int:
@@ -278,7 +279,11 @@ def make_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02) -> Dict[str
         return bf16_round(np.float32(1.0) + rng.standard_normal(n, dtype=np.float32) * np.float32(0.05))
 
     w: Dict[str, np.ndarray] = {}
+    # multi-hot actions: one [1, D] vector cut into num_action_types chunks (recsys_model.py:3282-3294); the draw has the
+    # single-action table's shape either way so that the other parameters do not depend on the mode
     w["action_table"] = bf16_round(rng.standard_normal((cfg.num_action_types + 1, D), dtype=np.float32) / np.float32(math.sqrt(D)))
+    if cfg.action_multi_hot:
+        w["action_table"] = w["action_table"][1:2]
     w["surface_table"] = bf16_round(rng.standard_normal((cfg.num_surfaces + 1, D), dtype=np.float32) / np.float32(math.sqrt(D)))
     for l in range(cfg.num_layers):
         p = f"layer{l}."
@@ -504,7 +509,9 @@ def make_batch(cfg: ModelConfig, batch: int, seed: int = 2, zipf_s: Optional[flo
 
     b = RankBatch(
         hist_post_ids=draw((batch, S)), hist_author_ids=draw((batch, S)),
-        hist_actions=rng.integers(1, cfg.num_action_types + 1, size=(batch, S)).astype(np.int32),
+        # one action id per position, or (multi-hot) a bit set of the actions taken: bit v = action v
+        hist_actions=(rng.integers(0, 1 << cfg.num_action_types, size=(batch, S)) * (rng.random((batch, S)) < 0.9)).astype(np.int32)
+        if cfg.action_multi_hot else rng.integers(1, cfg.num_action_types + 1, size=(batch, S)).astype(np.int32),
         hist_surfaces=rng.integers(1, cfg.num_surfaces + 1, size=(batch, S)).astype(np.int32),
         cand_post_ids=draw((batch, C)), cand_author_ids=draw((batch, C)),
     )
@@ -532,7 +539,15 @@ def build_tokens(cfg: ModelConfig, w: Dict[str, np.ndarray], table_rows_fn, batc
     lay = cfg.hash_layout()
     hp, ha = lay.item_hash(batch.hist_post_ids), lay.author_hash(batch.hist_author_ids)
     cp, ca = lay.item_hash(batch.cand_post_ids), lay.author_hash(batch.cand_author_ids)
-    act = bf16_bits(w["action_table"])[np.clip(batch.hist_actions, 0, cfg.num_action_types)]
+    if cfg.action_multi_hot:
+        # multi_hot_to_embeddings (recsys_model.py:3282-3312): the vector in V chunks, chunk v signed by 2 a_v - 1, the
+        # whole row zero where no action is set; cast to the activation dtype (exact: only signs change)
+        V, D = cfg.num_action_types, cfg.emb_size
+        bits = (batch.hist_actions[..., None] >> np.arange(V)) & 1                      # [B,S,V]
+        sel = (2 * bits - 1).astype(np.float32)[..., None] * w["action_table"].reshape(V, D // V)[None, None]
+        act = bf16_bits((sel.reshape(*bits.shape[:2], D) * (bits.any(axis=-1))[..., None]).astype(np.float32))
+    else:
+        act = bf16_bits(w["action_table"])[np.clip(batch.hist_actions, 0, cfg.num_action_types)]
     srf = bf16_bits(w["surface_table"])[np.clip(batch.hist_surfaces, 0, cfg.num_surfaces)]
     hist_rows = np.concatenate([table_rows_fn(hp), table_rows_fn(ha), act[:, :, None, :], srf[:, :, None, :]], axis=2)
     cand_rows = np.concatenate([table_rows_fn(cp), table_rows_fn(ca)], axis=2)

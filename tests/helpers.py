@@ -24,7 +24,7 @@ def make_pair(max_batch=4, table_seed=7, engine_kw=None, **kw):
         rotary=ocfg.rotary, qk_norm=ocfg.qk_norm, primer_norm=ocfg.primer_norm, attn_logit_cap=ocfg.attn_logit_cap,
         attn_logit_cap_method=ocfg.attn_logit_cap_method, final_logit_cap=ocfg.final_logit_cap,
         rms_eps=ocfg.rms_eps, rope_base=float(ocfg.rope_base), dwell_norm_scale=ocfg.dwell_norm_scale,
-        num_candidate_only_layers=ocfg.num_candidate_only_layers, compute=ocfg.compute, token_combine=ocfg.token_combine, **engine_kw)
+        num_candidate_only_layers=ocfg.num_candidate_only_layers, compute=ocfg.compute, token_combine=ocfg.token_combine, action_multi_hot=ocfg.action_multi_hot, **engine_kw)
     eng = px.PhoenixEngine(pcfg, 0)
     eng.load_weights(w)
     eng.table_fill_synthetic(table_seed, amp)

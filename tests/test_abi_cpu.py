@@ -31,12 +31,12 @@ def test_library_exports_every_declared_symbol():
 def test_struct_layouts_match_header():
     from x_algorithm_b200 import _lib
     assert C.sizeof(_lib.HashFamily) == 8 * 4 + 8 * 4 + 8 + 8 + 4 + 4
-    assert C.sizeof(_lib.ModelConfig) == 17 * 4 + 5 * 4 + 4 * C.sizeof(_lib.HashFamily) + 6 * 4
+    assert C.sizeof(_lib.ModelConfig) == 17 * 4 + 5 * 4 + 4 * C.sizeof(_lib.HashFamily) + 8 * 4
     assert C.sizeof(_lib.BlendSpec) == 8 + 32 * 4 + 32 * 8 + 16 - 4 + 4   # int + pad, src, weight, two doubles
     assert C.sizeof(_lib.RankBatch) == 8 + 6 * 8 and C.sizeof(_lib.RankOut) == 24
     # phx_value_model: 32 int sources, 30 + 9 doubles, 6 ints; phx_value_inputs: 4 ints + 9 pointers
     assert C.sizeof(_lib.ValueModel) == 32 * 4 + 39 * 8 + 6 * 4 and C.sizeof(_lib.ValueInputs) == 4 * 4 + 9 * 8
-    assert _lib.ModelConfig.pack_ragged.offset == C.sizeof(_lib.ModelConfig) - 4
+    assert _lib.ModelConfig.pack_ragged.offset == C.sizeof(_lib.ModelConfig) - 12
 
 
 def test_config_options_reach_the_c_struct():

@@ -371,6 +371,29 @@ def test_packed_ragged_batches_match_unpacked(torch, monkeypatch, opts, attn):
     plain.close(); packed.close()
 
 
+@pytest.mark.parametrize("opts", [dict(), dict(token_combine="project"), dict(compute="fp32"),
+                                  dict(emb_size=256, num_q_heads=4, num_kv_heads=4, key_size=64, num_action_types=32)])
+def test_action_sets_vs_oracle(torch, monkeypatch, opts):
+    """History actions as a set per position (multi_hot_to_embeddings, recsys_model.py:3259-3314): bit masks in
+    hist_actions, one [1, D] action vector in signed chunks.  With the row sum the tokens are bit-exact."""
+    monkeypatch.setenv("PHX_DEBUG_TAPS", "1")
+    ocfg, w, rows_fn, eng = make_pair(max_batch=6, action_multi_hot=True, **opts)
+    b, taps, lp, cont, logits, spec, res = _forward_case(ocfg, w, rows_fn, eng, 6, True)
+    assert (b.hist_actions == 0).any() and (b.hist_actions > 1).any()
+    T = ocfg.seq_len
+    tokens = eng.debug_read("tokens", (6, T, ocfg.emb_size), np.uint16)
+    want = np.concatenate([taps["hist_tok"], taps["cand_tok"]], axis=1)
+    if ocfg.token_combine == "sum":
+        np.testing.assert_array_equal(tokens, want)
+    else:
+        assert rel_l2(po.bf16_from_bits(tokens), po.bf16_from_bits(want)) < 4e-3
+    valid = b.cand_post_ids != 0
+    tol = TOL_FP32 if ocfg.compute == "fp32" else TOL
+    assert rel_l2(res.log_probs[valid], lp[valid]) < tol, opts
+    assert rel_l2(res.continuous[valid], cont[valid]) < tol, opts
+    eng.close()
+
+
 def test_simt_gemm_path_matches_tcgen05(torch, monkeypatch):
     """The cross-check GEMM and the tcgen05 GEMM give the same forward (accumulation order aside)."""
     ocfg, w, rows_fn, eng = make_pair(max_batch=4)

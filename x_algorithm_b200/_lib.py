@@ -29,7 +29,7 @@ class ModelConfig(C.Structure):
         "attn_logit_cap", "final_logit_cap", "rms_eps", "rope_base", "dwell_norm_scale")] + [
         ("user", HashFamily), ("item", HashFamily), ("author", HashFamily), ("ip", HashFamily),
         ("table_world", C.c_int32), ("table_rank", C.c_int32), ("num_candidate_only_layers", C.c_int32),
-        ("compute_fp32", C.c_int32), ("token_project", C.c_int32), ("pack_ragged", C.c_int32)]
+        ("compute_fp32", C.c_int32), ("token_project", C.c_int32), ("pack_ragged", C.c_int32), ("action_multi_hot", C.c_int32), ("_pad2", C.c_int32)]
 
 
 class BlendSpec(C.Structure):

@@ -81,6 +81,7 @@ class PhoenixConfig:
     token_combine: str = "sum"  # "sum" (fp32 sum of the gathered rows) | "project" (concat(rows) @ proj_hist / proj_cand,
                                 # recsys_model.py:2163-2365)
 
+    action_multi_hot: bool = False   # hist_actions are bit sets, action_table one [1, D] vector (recsys_model.py:3259-3314)
     pack_ragged: bool = False   # run ragged host-buffer batches over their valid rows only (sequence_packing.py:317)
 
     @property
@@ -124,4 +125,5 @@ class PhoenixConfig:
             raise ValueError("token_combine must be 'sum' or 'project'")
         c.token_project = 1 if self.token_combine == "project" else 0
         c.pack_ragged = int(bool(self.pack_ragged))
+        c.action_multi_hot = int(bool(self.action_multi_hot))
         return c

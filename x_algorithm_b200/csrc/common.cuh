@@ -208,6 +208,7 @@ struct TokenBuildArgs {
   // projected tokens: when concat_hist is set the kernel only lays the gathered rows side by side -
   // concat_hist [B*S, (2H+2)*D], concat_cand [B*C, 2H*D] - and writes the segment ids
   bf16* concat_hist = nullptr; bf16* concat_cand = nullptr;
+  int action_multi_hot = 0;   // hist_actions are bit sets and action_table is one [D] vector cut into num_action_types chunks
   PackMap pack;           // packed rows: slots past a request's counts are skipped altogether
   float* x32 = nullptr;   // full-precision path: bf16(sum) * input_scale kept in fp32 here (x is then not written)
   const bf16* landing = nullptr;

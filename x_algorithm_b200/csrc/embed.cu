@@ -35,6 +35,25 @@ __device__ __forceinline__ void acc_row(float (&acc)[8], const bf16* row, int co
   acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
 }
 
+// The action row of a history token, columns col..col+7, as packed bf16.  Single action: row `act` of the table.
+// Action set (multi_hot_to_embeddings, recsys_model.py:3282-3312): the [D] vector, the chunk these columns lie in
+// signed by 2 a_v - 1 (a sign-bit flip: exact), everything zero when the set is empty.
+__device__ __forceinline__ uint4 action_chunk(const TokenBuildArgs& a, int act, int col) {
+  if (!a.action_multi_hot) return __ldg(reinterpret_cast<const uint4*>(a.action_table + (long long)act * a.D + col));
+  const unsigned live = (a.num_action_types >= 32) ? 0xffffffffu : ((1u << a.num_action_types) - 1u);
+  const unsigned bits = (unsigned)act & live;
+  if (bits == 0u) return make_uint4(0u, 0u, 0u, 0u);
+  uint4 u = __ldg(reinterpret_cast<const uint4*>(a.action_table + col));
+  const int v = col / (a.D / a.num_action_types);
+  if (!((bits >> v) & 1u)) { u.x ^= 0x80008000u; u.y ^= 0x80008000u; u.z ^= 0x80008000u; u.w ^= 0x80008000u; }
+  return u;
+}
+__device__ __forceinline__ void acc_chunk(float (&acc)[8], uint4 u) {
+  float2 a = unpack_bf2(u.x), b = unpack_bf2(u.y), c = unpack_bf2(u.z), d = unpack_bf2(u.w);
+  acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+  acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+}
+
 // One warp per token.  History token slots: post h0.., author h0.., action row, surface row;
 // candidate token slots: post h0.., author h0...  x = bf16(bf16(sum) * input_scale).
 __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
@@ -76,7 +95,7 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
   if (is_hist) {
     act = a.hist_actions[(long long)b * a.S + t];
     srf = a.hist_surfaces[(long long)b * a.S + t];
-    act = act < 0 ? 0 : (act > a.num_action_types ? a.num_action_types : act);
+    if (!a.action_multi_hot) act = act < 0 ? 0 : (act > a.num_action_types ? a.num_action_types : act);
     srf = srf < 0 ? 0 : (srf > a.num_surfaces ? a.num_surfaces : srf);
   }
   // every lane takes part in these shuffles (lanes whose column chunk lies past D skip the loop below, so a
@@ -102,8 +121,7 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
       for (int j = 0; j < 2 * PHX_MAX_HASHES; ++j)
         if (j < 2 * H) *reinterpret_cast<uint4*>(dst + (long long)j * a.D + col) = __ldg(reinterpret_cast<const uint4*>(rowp[j] + col));
       if (is_hist) {
-        *reinterpret_cast<uint4*>(dst + (long long)(2 * H) * a.D + col) =
-            __ldg(reinterpret_cast<const uint4*>(a.action_table + (long long)act * a.D + col));
+        *reinterpret_cast<uint4*>(dst + (long long)(2 * H) * a.D + col) = action_chunk(a, act, col);
         *reinterpret_cast<uint4*>(dst + (long long)(2 * H + 1) * a.D + col) =
             __ldg(reinterpret_cast<const uint4*>(a.surface_table + (long long)srf * a.D + col));
       }
@@ -117,7 +135,7 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
     for (int j = 0; j < 2 * PHX_MAX_HASHES; ++j)
       if (j < 2 * H) acc_row(acc, rowp[j], col);
     if (is_hist) {
-      acc_row(acc, a.action_table + (long long)act * a.D, col);
+      acc_chunk(acc, action_chunk(a, act, col));
       acc_row(acc, a.surface_table + (long long)srf * a.D, col);
     }
     uint4 o;

@@ -275,6 +275,10 @@ phx_status check_cfg(const phx_model_config& c, std::string& err) {
   if (c.token_project != 0 && c.token_project != 1) return bad("token_project must be 0 or 1");
   if (c.token_project && c.compute_fp32) return bad("projected tokens are not available on the full-precision path");
   if (c.pack_ragged != 0 && c.pack_ragged != 1) return bad("pack_ragged must be 0 or 1");
+  if (c.action_multi_hot != 0 && c.action_multi_hot != 1) return bad("action_multi_hot must be 0 or 1");
+  if (c.action_multi_hot && (c.num_action_types < 1 || c.num_action_types > 32 || c.emb_size % c.num_action_types != 0 ||
+                             (c.emb_size / c.num_action_types) % 8 != 0))
+    return bad("action sets need 1..32 action types and emb_size / num_action_types a multiple of 8");
   if (c.pack_ragged && c.compute_fp32) return bad("packed rows are not available on the full-precision path");
   if (c.num_candidate_only_layers < 0 || c.num_candidate_only_layers > c.num_layers) return bad("num_candidate_only_layers");
   return PHX_OK;
@@ -511,6 +515,7 @@ phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc, 
   ta.table = table_view(e);
   ta.action_table = e->action_table; ta.surface_table = e->surface_table;
   ta.num_action_types = e->cfg.num_action_types; ta.num_surfaces = e->cfg.num_surfaces;
+  ta.action_multi_hot = e->cfg.action_multi_hot;
   ta.item = to_dev(e->cfg.item, (int)oi); ta.author = to_dev(e->cfg.author, (int)oa);
   ta.B = B; ta.S = e->S; ta.C = Cc; ta.D = e->D;
   ta.input_scale = sqrtf((float)e->D);  // scaling.py:40-41
@@ -786,7 +791,7 @@ phx_status phx_load_param(phx_engine* e, const char* name, const float* host, in
     return false;
   };
   phx_status s = PHX_E_ARG;
-  if (n == "action_table") { if (!shape(e->cfg.num_action_types + 1, e->D)) return PHX_E_ARG; s = upload_bf16(e, &e->action_table, host, rows, cols, false); }
+  if (n == "action_table") { if (!shape(e->cfg.action_multi_hot ? 1 : e->cfg.num_action_types + 1, e->D)) return PHX_E_ARG; s = upload_bf16(e, &e->action_table, host, rows, cols, false); }
   else if (n == "surface_table") { if (!shape(e->cfg.num_surfaces + 1, e->D)) return PHX_E_ARG; s = upload_bf16(e, &e->surface_table, host, rows, cols, false); }
   else if (n == "final_norm") { if (!shape(1, e->D)) return PHX_E_ARG; s = upload_f32(e, &e->final_norm, host, e->D, true); }
   else if (n == "proj_hist" || n == "proj_cand") {
