@@ -371,6 +371,13 @@ phx_status phx_corpus_fill_synthetic(phx_corpus* c, uint32_t seed);
  * cuda/top_k_by_key/__init__.py:56-94).  Asynchronous on the corpus' stream. */
 phx_status phx_corpus_topk_device(phx_corpus* c, const float* users_dev, int32_t B, int32_t k, float* scores_dev,
                                   int64_t* ids_dev);
+/* Per-row eligibility of the shard (the reference's per-post masks ahead of the top-k: dataset type mask and
+ * eligibility mask, recsys_two_tower_model.py:2486-2493, 2690-2702, where a masked post's score becomes
+ * finfo(bf16).min): bit (r & 31) of host_bits[r >> 5] set = shard-local row r may be returned; ceil(rows / 32) words;
+ * NULL removes the mask.  Every later top-k call on this shard skips the other rows.  One difference from the
+ * reference: it pads a result with masked posts (at the minimum score) when fewer than k are eligible, this library
+ * refuses such a call (PHX_E_ARG).  Synchronises the shard's stream. */
+phx_status phx_corpus_set_mask(phx_corpus* c, const uint32_t* host_bits);
 /* The same top-k over rows [row_begin, row_end) of the shard only (shard-local row numbers): the reference's dataset
  * windows, where every retrieval dataset is a contiguous row range of the post table and each gets its own top-k
  * (slice_and_top_k, recsys_two_tower_model.py:2660-2686; ids come back offset by the window's start, as there).

@@ -599,6 +599,46 @@ def test_topk_dataset_windows_exact(torch, monkeypatch, impl, dim, N, windows):
     shard.close()
 
 
+@pytest.mark.parametrize("impl,dim,N", [("tc", 128, 300_000), ("tc", 64, 700_000), ("simt", 96, 300_000)])
+def test_topk_with_row_eligibility_mask(torch, monkeypatch, impl, dim, N):
+    """Per-row eligibility (the reference masks a post's score to the bf16 minimum ahead of its top-k,
+    recsys_two_tower_model.py:2486-2493): ids equal the oracle's top-k of the scores with masked rows at -inf, for a
+    dense and a sparse mask, with windows, and after the mask is lifted."""
+    from x_algorithm_b200.retrieval import CorpusShard
+    import x_algorithm_b200 as px
+    if impl == "simt":
+        monkeypatch.setenv("PHX_TOPK", "simt")
+    B, k, off = 6, 150, 5_000
+    shard = CorpusShard(N, dim, row_offset=off, max_queries=8, max_k=k)
+    shard.fill_synthetic(17)
+    corpus = po.synthetic_corpus_rows(np.arange(off, off + N), dim, 17)
+    rng = np.random.default_rng(N)
+    users = rng.standard_normal((B, dim)).astype(np.float32)
+    users /= np.linalg.norm(users, axis=1, keepdims=True)
+    tu = torch.from_numpy(users).cuda()
+    sc_all = po.corpus_scores(users, corpus).astype(np.float32)
+    scores = torch.empty((B, k), dtype=torch.float32, device="cuda"); ids = torch.empty((B, k), dtype=torch.int64, device="cuda")
+
+    def check(mask, r0, r1):
+        shard.topk_window_device(tu, B, k, r0, r1, scores, ids)
+        shard.sync()
+        sc = sc_all[:, r0:r1] if mask is None else np.where(mask[None, r0:r1], sc_all[:, r0:r1], -np.inf)
+        want_s, want_i = po.top_k(sc, k, row_offset=off + r0)
+        np.testing.assert_array_equal(ids.cpu().numpy(), want_i)
+        np.testing.assert_allclose(scores.cpu().numpy(), want_s, rtol=2.0 ** -7, atol=0)
+
+    for frac in (0.3, 0.004):
+        mask = rng.random(N) < frac
+        shard.set_mask(mask)
+        check(mask, 0, N)
+        check(mask, 1_001, N - 77)
+    with pytest.raises(px.PhoenixError):      # fewer eligible rows than k in the window
+        shard.topk_window_device(tu, B, k, 0, 2_000, scores, ids)
+    shard.set_mask(None)
+    check(None, 0, N)
+    shard.close()
+
+
 def test_sharded_gather_exchange_kernels_bit_identical(torch):
     """The device-side steps of the all-to-all exchange (bucket by owner, owner-side gather, fixed-order sum), with
     the two collectives emulated by slicing: two "ranks" on one device, each holding half of the table.  The result

@@ -80,6 +80,8 @@ struct ScanArgs {
   unsigned long long* surv;  // MODE 1: [B][cap]
   int* counts;             // MODE 1: [B]
   int cap;
+  const unsigned int* mask = nullptr;   // eligibility bits of the shard's rows (row_eligible), null = all
+  long long mask_row0 = 0;
 };
 
 // NT = n-tiles (8 users each) per warp; a CTA covers 2 * NT * 8 users x 64 corpus rows per tile
@@ -138,13 +140,15 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
       }
     }
     const long long row_a = tile * TILE_ROWS + mt * 16 + g, row_b = row_a + 8;
+    const bool ok_a = row_a < a.rows && row_eligible(a.mask, a.mask_row0, row_a);
+    const bool ok_b = row_b < a.rows && row_eligible(a.mask, a.mask_row0, row_b);
     if (MODE == 0) {
       // 16-row group maximum per user (rows past the end count as -inf)
       const long long grp = (tile / a.stride) * 4 + mt;
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
-        float m0 = fmaxf(row_a < a.rows ? round_bf(acc[j][0]) : -INFINITY, row_b < a.rows ? round_bf(acc[j][2]) : -INFINITY);
-        float m1 = fmaxf(row_a < a.rows ? round_bf(acc[j][1]) : -INFINITY, row_b < a.rows ? round_bf(acc[j][3]) : -INFINITY);
+        float m0 = fmaxf(ok_a ? round_bf(acc[j][0]) : -INFINITY, ok_b ? round_bf(acc[j][2]) : -INFINITY);
+        float m1 = fmaxf(ok_a ? round_bf(acc[j][1]) : -INFINITY, ok_b ? round_bf(acc[j][3]) : -INFINITY);
 #pragma unroll
         for (int o = 4; o < 32; o <<= 1) {
           m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
@@ -166,7 +170,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
           const float v = round_bf(acc[j][e]);
           const float p = (e & 1) ? pv.y : pv.x;
           const long long row = (e & 2) ? row_b : row_a;
-          if (v >= p && row < a.rows) {
+          if (v >= p && ((e & 2) ? ok_b : ok_a)) {
             const int u = u0 + (e & 1);
             const int slot = atomicAdd(&a.counts[u], 1);
             if (slot < a.cap)
@@ -339,6 +343,9 @@ struct phx_corpus {
   CUtensorMap map_corpus, map_users;
   CUtensorMap map_window;                    // corpus map of the last scanned window (phx_corpus_topk_window_device)
   long long win_begin = -1, win_end = -1;
+  unsigned int* mask = nullptr;              // eligibility bits of the shard's rows (phx_corpus_set_mask), null = all
+  std::vector<unsigned int> mask_host;
+  long long elig_begin = -1, elig_end = -1, elig_count = 0;   // eligible rows of the last window asked for
   cudaStream_t stream = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   std::string err;
@@ -422,7 +429,7 @@ void phx_corpus_destroy(phx_corpus* c) {
   cudaSetDevice(c->device);
   if (c->stream) cudaStreamSynchronize(c->stream);
   auto fr = [](void* p) { if (p) cudaFree(p); };
-  fr(c->data); fr(c->users_bf); fr(c->gmax); fr(c->pivot); fr(c->surv); fr(c->merge_keys); fr(c->counts); fr(c->status); fr(c->err_flag);
+  fr(c->data); fr(c->users_bf); fr(c->gmax); fr(c->pivot); fr(c->surv); fr(c->merge_keys); fr(c->counts); fr(c->status); fr(c->err_flag); fr(c->mask);
   if (c->ev0) cudaEventDestroy(c->ev0);
   if (c->ev1) cudaEventDestroy(c->ev1);
   if (c->stream) cudaStreamDestroy(c->stream);
@@ -447,6 +454,24 @@ phx_status phx_corpus_fill_synthetic(phx_corpus* c, uint32_t seed) {
   return PHX_OK;
 }
 
+phx_status phx_corpus_set_mask(phx_corpus* c, const uint32_t* host_bits) {
+  if (!c) return PHX_E_ARG;
+  cudaSetDevice(c->device);
+  PHX_CUDA_TRY(cudaStreamSynchronize(c->stream), c->err);   // no scan may be reading the old bits
+  c->elig_begin = c->elig_end = -1;
+  if (!host_bits) {
+    if (c->mask) cudaFree(c->mask);
+    c->mask = nullptr; c->mask_host.clear();
+    return PHX_OK;
+  }
+  const size_t words = (size_t)((c->rows + 31) / 32);
+  c->mask_host.assign(host_bits, host_bits + words);
+  if (c->rows & 31) c->mask_host[words - 1] &= (1u << (c->rows & 31)) - 1u;   // bits past the last row do not count
+  if (!c->mask) PHX_CUDA_TRY(cudaMalloc(&c->mask, words * 4), c->err);
+  PHX_CUDA_TRY(cudaMemcpy(c->mask, c->mask_host.data(), words * 4, cudaMemcpyHostToDevice), c->err);
+  return PHX_OK;
+}
+
 phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, int32_t B, int32_t k, int64_t row_begin,
                                          int64_t row_end, float* scores_dev, int64_t* ids_dev) {
   if (!c || !users_dev || !scores_dev || !ids_dev) return PHX_E_ARG;
@@ -456,6 +481,18 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
   const long long rows = row_end - row_begin, roff = c->row_offset + row_begin;
   const bf16* data = c->data + row_begin * (long long)c->dim;
   if (k > rows) { c->err = "topk: k exceeds the rows of the window"; return PHX_E_ARG; }
+  if (c->mask) {
+    // eligible rows of the window (counted once per window on the host copy of the mask)
+    if (c->elig_begin != row_begin || c->elig_end != row_end) {
+      long long n = 0;
+      for (long long r = row_begin; r < row_end;) {
+        if ((r & 31) == 0 && r + 32 <= row_end) { n += __builtin_popcount(c->mask_host[r >> 5]); r += 32; }
+        else { n += (c->mask_host[r >> 5] >> (r & 31)) & 1u; ++r; }
+      }
+      c->elig_begin = row_begin; c->elig_end = row_end; c->elig_count = n;
+    }
+    if (k > c->elig_count) { c->err = "topk: fewer eligible rows than k in the window"; return PHX_E_ARG; }
+  }
   cudaSetDevice(c->device);
   const CUtensorMap* map_corpus = &c->map_corpus;
   if (c->use_tc && (row_begin != 0 || row_end != c->rows)) {
@@ -479,12 +516,15 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
   ScanArgs a;
   a.corpus = data; a.users = c->users_bf; a.rows = rows; a.row_offset = roff; a.dim = c->dim; a.B = B; a.Bpad = Bpad;
   a.stride = 1; a.gmax = c->gmax; a.n_groups = 0; a.pivot = c->pivot; a.surv = c->surv; a.counts = c->counts; a.cap = c->cap;
+  a.mask = c->mask; a.mask_row0 = row_begin;
   TcScanArgs ta;
+  ta.mask = c->mask; ta.mask_row0 = row_begin;
   ta.rows = rows; ta.row_offset = roff; ta.dim = c->dim; ta.B = B; ta.stride = 1; ta.gmax = c->gmax; ta.n_groups = 0;
   ta.pivot = c->pivot; ta.surv = c->surv; ta.counts = c->counts; ta.cap = c->cap;
   const long long n_tiles = (rows + tile_rows - 1) / tile_rows;
   int j = 0;
-  if (rows > c->cap) {
+  // a window whose eligible rows all fit the survivor buffer needs no pivot: every eligible row is collected
+  if (rows > c->cap && !(c->mask && c->elig_count <= c->cap)) {
     // sample every stride-th tile so that about 48 of the wanted ~3k rows fall into the sample
     const double want = 3.0 * k;
     long long stride = (long long)(want / 48.0);

@@ -16,7 +16,17 @@ struct TcScanArgs {
   unsigned long long* surv;  // collect pass out: [B][cap] keys ordered(score) << 32 | ~global_row
   int* counts;               // [B]
   int cap;
+  // optional eligibility of the shard's rows: bit (r & 31) of mask[r >> 5] for shard-local row r = mask_row0 + row;
+  // a row whose bit is clear is skipped like a row past the end.  null = every row is eligible
+  const unsigned int* mask = nullptr;
+  long long mask_row0 = 0;
 };
+
+__device__ __forceinline__ bool row_eligible(const unsigned int* mask, long long mask_row0, long long row) {
+  if (!mask) return true;
+  const long long r = mask_row0 + row;
+  return (mask[r >> 5] >> (r & 31)) & 1u;
+}
 
 bool tc_scan_supported(int dim);
 phx_status tc_scan_make_maps(CUtensorMap* map_corpus, CUtensorMap* map_users, const bf16* corpus, long long rows, int dim,

@@ -179,7 +179,7 @@ scan_tc_kernel(const __grid_constant__ CUtensorMap map_corpus, const __grid_cons
       if (!ok) break;
       tc_fence_after();
       const long long row = tile * TC_ROWS + quad * 32 + lane;
-      const bool row_ok = row < a.rows;
+      const bool row_ok = row < a.rows && row_eligible(a.mask, a.mask_row0, row);
       const uint32_t taddr = tmem_base + acc * TC_Q + ((uint32_t)(quad * 32) << 16) + half * 128;
       if (MODE == 1) {
         // the warp's whole slice of the tile (32 rows x 128 queries) in one round trip to TMEM, then the accumulator

@@ -50,6 +50,18 @@ class CorpusShard:
         self._check(lib.phx_corpus_topk_device(self._h, int(users.data_ptr()), B, k, int(scores.data_ptr()),
                                                int(ids.data_ptr())))
 
+    def set_mask(self, eligible):
+        """Restrict every later top-k on this shard to the rows whose entry of `eligible` (bool [rows], or None to lift
+        the restriction) is true: the reference's per-post type / eligibility mask
+        (recsys_two_tower_model.py:2486-2493)."""
+        if eligible is None:
+            self._check(lib.phx_corpus_set_mask(self._h, None))
+            return
+        bits = np.packbits(np.asarray(eligible, dtype=bool), bitorder="little")
+        words = np.zeros((len(eligible) + 31) // 32 * 4, np.uint8)
+        words[:bits.size] = bits
+        self._check(lib.phx_corpus_set_mask(self._h, words.view(np.uint32).ctypes.data))
+
     def topk_window_device(self, users, B: int, k: int, row_begin: int, row_end: int, scores, ids):
         """Top-k over shard-local rows [row_begin, row_end) only: one retrieval dataset of the reference's post table
         (recsys_two_tower_model.py:2660-2686); ids are global rows as in `topk_device`."""
