@@ -39,7 +39,9 @@ def flops_per_request(c) -> dict:
     HD = c["num_q_heads"] * c["key_size"]
     QW = (c["num_q_heads"] + 2 * c["num_kv_heads"]) * c["key_size"]
     S, C = c["history_len"], c["num_candidates"]
-    L, n_tail = c["num_layers"], c.get("num_candidate_only_layers", 0)
+    # the engine always runs the last layer over the candidate rows only (its history rows are never read again), so
+    # at least one layer counts as candidate-only: the FLOPs below are the ones executed, not the dense model's
+    L, n_tail = c["num_layers"], max(c.get("num_candidate_only_layers", 0), 1)
     # a candidate-only tail layer projects QKV for every row but runs the out-projection and the FFN over the
     # candidate rows only, and its attention has no history queries
     gemm = L * 2 * T * D * QW + ((L - n_tail) * T + n_tail * C) * (2 * HD * D + 4 * D * F)

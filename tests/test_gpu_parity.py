@@ -394,6 +394,21 @@ def test_action_sets_vs_oracle(torch, monkeypatch, opts):
     eng.close()
 
 
+@pytest.mark.parametrize("opts", [dict(), dict(qk_norm=True), dict(emb_size=256, num_q_heads=4, num_kv_heads=4, key_size=64,
+                                                                  history_len=48, num_candidates=24, num_layers=3)])
+def test_last_layer_runs_candidate_rows_only_bit_identical(torch, monkeypatch, opts):
+    """The last layer's history rows are never read again, so the engine runs it over the candidate rows only: the
+    same candidate outputs, bit for bit, as with every row computed (PHX_LAST_LAYER=full)."""
+    ocfg, w, rows_fn, eng = make_pair(max_batch=5, **opts)
+    b = po.make_batch(ocfg, 5, seed=41, ragged=True)
+    got = eng.rank(to_inputs(b)); eng.close()
+    monkeypatch.setenv("PHX_LAST_LAYER", "full")
+    _, _, _, full = make_pair(max_batch=5, **opts)
+    want = full.rank(to_inputs(b)); full.close()
+    np.testing.assert_array_equal(got.log_probs, want.log_probs)
+    np.testing.assert_array_equal(got.continuous, want.continuous)
+
+
 def test_simt_gemm_path_matches_tcgen05(torch, monkeypatch):
     """The cross-check GEMM and the tcgen05 GEMM give the same forward (accumulation order aside)."""
     ocfg, w, rows_fn, eng = make_pair(max_batch=4)

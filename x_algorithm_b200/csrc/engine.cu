@@ -600,6 +600,17 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
   e->n_tail = e->C > 0 ? cfg->num_candidate_only_layers : 0;
   e->fp32 = cfg->compute_fp32 != 0;
   e->pack = cfg->pack_ragged != 0 && e->C > 0;
+  // The last layer's history rows are never read again by the ranking forward (the heads take candidate rows, and
+  // that layer's history keys / values come from its input), so it can always run as a candidate-only layer with the
+  // same candidate outputs bit for bit.  Done wherever the rows can be kept history-first at no cost: packed rows,
+  // and the plain engine in the regime its attention runs on the mma.sync kernels anyway (the tcgen05 attention
+  // kernel wants [B, T] rows).  PHX_LAST_LAYER=full keeps every row in the last layer.
+  {
+    const char* ll = getenv("PHX_LAST_LAYER");
+    const bool keep_full = ll && strcmp(ll, "full") == 0;
+    const bool mma_regime = e->dh != 128 && e->S <= 128;
+    if (e->C > 0 && !e->fp32 && !keep_full && e->n_tail == 0 && (e->pack || mma_regime)) e->n_tail = 1;
+  }
   e->split = e->n_tail > 0 && !e->fp32 && !e->pack;   // packed rows carry their own history-first order
   const long long M = e->max_tokens;
 #define TRY(x) do { phx_status _s = (x); if (_s) return fail(_s); } while (0)
