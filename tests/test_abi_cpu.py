@@ -164,3 +164,20 @@ def test_source_contract():
     out = src.run(px.Query(history=[]))
     assert [(c.post_id, c.author_id) for c in out] == [(33, 3), (11, 1)]          # row with post id 0 dropped
     assert src.run(px.Query(history=None)) == "PhoenixSource: missing retrieval_sequence"
+    assert all(c.served_type == "ForYouPhoenixRetrieval" for c in out)            # phoenix_source.rs:177-186
+    # seen posts are never returned (phoenix_source.rs:73-98); the list is taken deeper to make up for them
+    asked = []
+
+    class Deep(FakeRetriever):
+        def retrieve_for_history(self, tower, history, k):
+            asked.append(k)
+            return np.array([0.9, 0.8, 0.7], np.float32), np.array([2, 0, 1])
+
+    src = px.PhoenixSource(None, Deep(), np.array([11, 22, 33]), np.array([1, 2, 3]))
+    out = src.run(px.Query(history=[], top_k=2, seen_post_ids=[33]))
+    assert asked == [3] and [c.post_id for c in out] == [11, 22]
+    from x_algorithm_b200.plugin import served_type_for_dataset
+    assert served_type_for_dataset("home_cold") == "ForYouPhoenixRetrievalCold"
+    assert served_type_for_dataset("zero_fav") == "ForYouPhoenixRetrievalZeroFav"
+    assert served_type_for_dataset("ai_video_model_2day") == "ForYouPhoenixRetrievalAiVideo"
+    assert served_type_for_dataset("home") == "ForYouPhoenixRetrieval"

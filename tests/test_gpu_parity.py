@@ -1027,3 +1027,37 @@ def test_value_model_scorer_plugin(torch):
     np.testing.assert_allclose([r.weighted_score for r in got], want_w, rtol=2e-6, atol=1e-9)
     scorer.update_all(pcs, res)
     assert pcs[2].score is None and pcs[0].score == got[0].score
+
+
+def test_source_plugin_dataset_windows_and_exclusions(torch):
+    """PhoenixSource over dataset windows of one shard: every dataset its own top-k and served type
+    (phoenix_source.rs:140, 177-186), seen posts never returned (73-98), all equal to the oracle's top-k of the
+    window with the excluded posts masked."""
+    import x_algorithm_b200 as px
+    from x_algorithm_b200.plugin import HistoryItem
+    from x_algorithm_b200.retrieval import CorpusShard, Retriever
+    ocfg, w, rows_fn, tower = make_pair(max_batch=2, emb_size=128, num_candidates=0, history_len=32)
+    N = 40_000
+    shard = CorpusShard(N, 128, row_offset=0, max_queries=2, max_k=400)
+    shard.fill_synthetic(21)
+    post_ids = np.arange(1, N + 1, dtype=np.int64) * 7
+    author_ids = np.arange(N, dtype=np.int64) % 97 + 1
+    datasets = [("home", 0, 30_000, 50), ("home_cold", 30_000, 38_000, 20), ("zero_fav", 38_000, 40_000, 10)]
+    src = px.PhoenixSource(tower, Retriever([shard]), post_ids, author_ids, datasets=datasets)
+    rng = np.random.default_rng(3)
+    hist = [HistoryItem(int(p), int(a), int(rng.integers(1, 9)), int(rng.integers(1, 5)))
+            for p, a in zip(rng.integers(1, 1 << 40, 20), rng.integers(1, 1 << 40, 20))]
+    first = src.run(px.Query(history=hist))
+    assert [c.served_type for c in first] == (["ForYouPhoenixRetrieval"] * 50 + ["ForYouPhoenixRetrievalCold"] * 20 +
+                                              ["ForYouPhoenixRetrievalZeroFav"] * 10)
+    # oracle: the tower's own user vector against the corpus, window by window
+    users = Retriever([shard]).user_vector(tower, hist).cpu().numpy()
+    sc = po.corpus_scores(users, po.synthetic_corpus_rows(np.arange(N), 128, 21))
+    seen = [first[0].post_id, first[3].post_id, first[55].post_id, 12345]
+    got = src.run(px.Query(history=hist, seen_post_ids=seen))
+    want = []
+    for _, r0, r1, k in datasets:
+        masked = np.where(np.isin(post_ids[r0:r1], seen)[None], -np.inf, sc[:, r0:r1])
+        want += [int(post_ids[i]) for i in po.top_k(masked, k, row_offset=r0)[1][0]]
+    assert [c.post_id for c in got] == want and not set(seen) & {c.post_id for c in got}
+    shard.close(); tower.close()

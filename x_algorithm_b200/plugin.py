@@ -34,6 +34,7 @@ class Query:
     has_cached_posts: bool = False
     kill_switch: bool = False
     top_k: int = 1000
+    seen_post_ids: Optional[Sequence[int]] = None   # seen / served / impressed posts the source must not return
 
 
 @dataclass
@@ -43,6 +44,7 @@ class Candidate:
     phoenix_scores: Optional[Dict[str, float]] = None   # head name -> probability (dwell_time: seconds)
     weighted_score: Optional[float] = None
     score: Optional[float] = None
+    served_type: Optional[str] = None               # set by the source (phoenix_source.rs:177-186)
     # what the value model reads besides the scores (xai-value-model/inputs.rs:3-17, filled as in
     # home-mixer/scorers/value_model.rs:67-94)
     in_network: Optional[bool] = None
@@ -227,32 +229,75 @@ class Source:
         return self.source(query)
 
 
+# dataset type of a retrieval window -> served type of its candidates (home-mixer/sources/phoenix_source.rs:177-186)
+SERVED_TYPE_FOR_DATASET = {"home_cold": "ForYouPhoenixRetrievalCold", "zero_fav": "ForYouPhoenixRetrievalZeroFav",
+                           "ai_video_self_2day": "ForYouPhoenixRetrievalAiVideo", "ai_video_model_2day": "ForYouPhoenixRetrievalAiVideo"}
+
+
+def served_type_for_dataset(dataset: str) -> str:
+    return SERVED_TYPE_FOR_DATASET.get(dataset, "ForYouPhoenixRetrieval")
+
+
 class PhoenixSource(Source):
     """User tower + exhaustive top-k over the corpus shards of this process
     (home-mixer/sources/phoenix_source.rs:113-150).  `post_ids` / `author_ids` map corpus rows to ids
     like the reference's reply (phoenix/xrex/inference/model_runner.py:5332-5360); rows whose post id
-    is 0 are dropped (xai-recsys-engine/src/python.rs:846-864)."""
+    is 0 are dropped (xai-recsys-engine/src/python.rs:846-864).
 
-    def __init__(self, tower: PhoenixEngine, retriever, post_ids: np.ndarray, author_ids: np.ndarray):
+    `datasets`: the retrieval datasets of the post table as (dataset type, first row, end row, top-k) - each gets its
+    own top-k over its row window (the per-dataset top-k of phoenix_source.rs:140, served by slice_and_top_k,
+    recsys_two_tower_model.py:2660-2686) and its candidates the dataset's served type; without it one top-k over the
+    whole corpus.  Windows need a single-shard retriever.  Posts in `query.seen_post_ids` are never returned
+    (seen_post_exclusions, phoenix_source.rs:73-98): the top-k is taken that many entries deeper and the excluded
+    posts dropped, which equals masking them before the top-k."""
+
+    def __init__(self, tower: PhoenixEngine, retriever, post_ids: np.ndarray, author_ids: np.ndarray,
+                 datasets: Optional[Sequence[Tuple[str, int, int, int]]] = None):
         self.tower = tower
         self.retriever = retriever
         self.post_ids = post_ids
         self.author_ids = author_ids
+        self.datasets = list(datasets) if datasets else None
+        if self.datasets and len(getattr(retriever, "shards", ())) != 1:
+            raise ValueError("PhoenixSource: dataset windows need a single-shard retriever")
 
     def enable(self, query: Query) -> bool:
         return not query.has_cached_posts
 
-    def source(self, query: Query) -> Union[List[Candidate], str]:
-        if query.history is None:
-            return "PhoenixSource: missing retrieval_sequence"
-        try:
-            scores, rows = self.retriever.retrieve_for_history(self.tower, query.history, query.top_k)
-        except PhoenixError as err:
-            return f"PhoenixSource: {err}"
+    def _candidates(self, scores, rows, want: int, excluded, served: str) -> List[Candidate]:
         out = []
         for s, r in zip(scores, rows):
             pid = int(self.post_ids[r])
-            if pid == 0:
+            if pid == 0 or pid in excluded:
                 continue
-            out.append(Candidate(post_id=pid, author_id=int(self.author_ids[r]), score=float(s)))
+            out.append(Candidate(post_id=pid, author_id=int(self.author_ids[r]), score=float(s), served_type=served))
+            if len(out) == want:
+                break
         return out
+
+    def source(self, query: Query) -> Union[List[Candidate], str]:
+        if query.history is None:
+            return "PhoenixSource: missing retrieval_sequence"
+        excluded = set(int(p) for p in (query.seen_post_ids or ()))
+        try:
+            if not self.datasets:
+                depth = query.top_k + len(excluded)
+                shards = getattr(self.retriever, "shards", None)
+                if shards:
+                    depth = min(depth, min(sh.rows for sh in shards))
+                scores, rows = self.retriever.retrieve_for_history(self.tower, query.history, depth)
+                return self._candidates(scores, rows, query.top_k, excluded, served_type_for_dataset(""))
+            import torch
+            users = self.retriever.user_vector(self.tower, query.history)
+            shard = self.retriever.shards[0]
+            out: List[Candidate] = []
+            for dataset, r0, r1, k in self.datasets:
+                depth = min(k + len(excluded), r1 - r0)
+                sc = torch.empty((1, depth), dtype=torch.float32, device=users.device)
+                ids = torch.empty((1, depth), dtype=torch.int64, device=users.device)
+                shard.topk_window_device(users, 1, depth, r0, r1, sc, ids)
+                shard.sync()
+                out += self._candidates(sc[0].cpu().numpy(), ids[0].cpu().numpy(), k, excluded, served_type_for_dataset(dataset))
+            return out
+        except PhoenixError as err:
+            return f"PhoenixSource: {err}"

@@ -129,7 +129,8 @@ class Retriever:
         self.shards[0].sync()
         return out_s, out_i
 
-    def retrieve_for_history(self, tower, history, k: int):
+    def user_vector(self, tower, history):
+        """The user tower's vector of one history (list of plugin.HistoryItem): f32 [1, D] CUDA tensor."""
         import torch
         cfg = tower.cfg
         S = cfg.history_len
@@ -144,5 +145,8 @@ class Retriever:
         torch.cuda.synchronize()
         tower.user_tower_device(1, *t, users)
         tower.sync()
-        s, i = self.retrieve(users, k)
+        return users
+
+    def retrieve_for_history(self, tower, history, k: int):
+        s, i = self.retrieve(self.user_vector(tower, history), k)
         return s[0].cpu().numpy(), i[0].cpu().numpy()
