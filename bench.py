@@ -139,7 +139,7 @@ def main():
                          "device-timed steps; the host-buffer calls of the e2e leg still use peer loads)")
     ap.add_argument("--candidate-only-layers", type=int, default=0,
                     help="tail layers that update the candidate rows only (the reference's production ranker uses 2; "
-                         "BASELINE config 1 has none, so a line measured with this flag is not the headline workload)")
+                         "the headline workload has none, so a line measured with this flag is not the headline number)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 

@@ -333,7 +333,7 @@ phx_status phx_diag_mma_rate(int32_t device, int32_t pair, int32_t ksteps, int32
 /* Multi-hash id -> unified-table rows; `family`: 0 user, 1 item, 2 author, 3 ip.
  * out_dev int32 [n, num_hashes].  recsys_embedding.py:154-172, 282-331. */
 phx_status phx_hash_ids_device(phx_engine* e, int32_t family, const int64_t* ids_dev, int64_t n, int32_t* out_dev);
-/* Hash + gather + fixed-order fp32 sum -> bf16 [n, D]; the BASELINE gather-sum workload.
+/* Hash + gather + fixed-order fp32 sum -> bf16 [n, D]; the benchmark's gather-sum workload.
  * Replaces embedding_gather (emb_table.rs:330-398) + the combine. */
 phx_status phx_gather_sum_device(phx_engine* e, int32_t family, const int64_t* ids_dev, int64_t n, uint16_t* out_dev);
 /* Candidate-isolated attention on caller tensors: q,k,v,out bf16 [B,T,H,dh] (Hkv heads for k,v),

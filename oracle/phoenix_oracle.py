@@ -191,7 +191,7 @@ def gather_rows(table_bits: np.ndarray, idx: np.ndarray) -> np.ndarray:
 def gather_sum(rows_bits: np.ndarray) -> np.ndarray:
     """Combine of the gathered rows of one token: fp32 sum over the slot axis (-2) in slot
     order, one rounding to bf16.  This is the `sum` special case of the reference's combine
-    (IP hashes at recsys_model.py:1920-1923; BASELINE's gather-sum).  Returns bf16 bits."""
+    (IP hashes at recsys_model.py:1920-1923; the benchmark's gather-sum).  Returns bf16 bits."""
     rows = bf16_from_bits(rows_bits)
     acc = np.zeros(rows.shape[:-2] + rows.shape[-1:], dtype=np.float32)
     for j in range(rows.shape[-2]):  # fixed left-to-right order
@@ -917,7 +917,7 @@ def compute_value_scores(wt: ValueModelWeights, ctx: ScoringContext, cands: List
     return weighted, scores
 
 
-# The 19 discrete heads of the BASELINE workload, named after the PhoenixScores fields they
+# The 19 discrete heads of the benchmark workload, named after the PhoenixScores fields they
 # feed (home-mixer/side_effects/teacher_score_side_effect.rs:43-74), in `weighted_terms` order.
 HEAD_NAMES_19 = ["favorite", "reply", "retweet", "photo_expand", "video_open", "click", "open_link", "profile_click",
                  "vqv", "share", "share_via_dm", "share_via_copy_link", "dwell", "quote", "quoted_click",

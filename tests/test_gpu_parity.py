@@ -233,7 +233,7 @@ def test_candidate_only_tail_layers_vs_oracle(torch, monkeypatch, opts, attn):
     eng.close()
 
 
-TOL_FP32 = 1e-5   # full-precision path against the fp32 model: the bar north_star states
+TOL_FP32 = 1e-5   # full-precision path against the fp32 model: the bar set for the full-precision path
 
 
 @pytest.mark.parametrize("opts", [dict(), dict(qk_norm=True), dict(primer_norm=True),
@@ -242,7 +242,7 @@ TOL_FP32 = 1e-5   # full-precision path against the fp32 model: the bar north_st
                                   dict(emb_size=256, num_q_heads=4, num_kv_heads=4, key_size=64, history_len=48,
                                        num_candidates=24, num_layers=3)])
 def test_rank_forward_fp32_path_vs_fp32_oracle(torch, opts):
-    """BASELINE config 0 is an fp32 model: the engine's full-precision path (fp32 activations, SIMT kernels) against the
+    """The CPU-runnable benchmark configuration is an fp32 model: the engine's full-precision path (fp32 activations, SIMT kernels) against the
     oracle's fp32 mode, relative L2 below 1e-5 on the residual stream, log-probabilities and continuous head."""
     ocfg, w, rows_fn, eng = make_pair(max_batch=16, compute="fp32", **opts)
     for batch, ragged in ((16, False), (7, True)):

@@ -256,7 +256,7 @@ def bench_mma(a):
 
 
 def bench_ragged(a):
-    """Ragged ranking batches through the blocking host-buffer call, with and without packed rows: BASELINE config 1's
+    """Ragged ranking batches through the blocking host-buffer call, with and without packed rows: the headline benchmark's
     model, --batch requests whose valid history / candidate counts are uniform in [1, S] / [1, C]."""
     import math
     import time
