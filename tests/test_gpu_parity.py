@@ -409,6 +409,26 @@ def test_last_layer_runs_candidate_rows_only_bit_identical(torch, monkeypatch, o
     np.testing.assert_array_equal(got.continuous, want.continuous)
 
 
+@pytest.mark.parametrize("opts,attn", [
+    (dict(num_q_heads=4, num_kv_heads=2), None), (dict(num_q_heads=4, num_kv_heads=1, qk_norm=True), None),
+    (dict(num_q_heads=4, num_kv_heads=2, compute="fp32"), None),
+    (dict(emb_size=256, num_q_heads=4, num_kv_heads=2, key_size=64, history_len=48, num_candidates=24, num_layers=3), "strip"),
+    (dict(emb_size=256, num_q_heads=4, num_kv_heads=1, key_size=64, history_len=160, num_candidates=72, num_layers=2), None),
+    (dict(emb_size=256, num_q_heads=2, num_kv_heads=1, key_size=128, history_len=40, num_candidates=24, num_layers=2), None)])
+def test_grouped_query_attention_vs_oracle(torch, monkeypatch, opts, attn):
+    """Fewer kv heads than q heads: the merged QKV row keeps the q heads of a kv group together, [q_0..q_{g-1}, k, v]
+    (layers.py:728-736), and q head h reads kv head h // g (ranker_attention_v2.py:390)."""
+    if attn:
+        monkeypatch.setenv("PHX_ATTN", attn)
+    ocfg, w, rows_fn, eng = make_pair(max_batch=5, **opts)
+    b, taps, lp, cont, logits, spec, res = _forward_case(ocfg, w, rows_fn, eng, 5, True)
+    valid = b.cand_post_ids != 0
+    tol = TOL_FP32 if ocfg.compute == "fp32" else TOL
+    assert rel_l2(res.log_probs[valid], lp[valid]) < tol, opts
+    assert rel_l2(res.continuous[valid], cont[valid]) < tol, opts
+    eng.close()
+
+
 def test_simt_gemm_path_matches_tcgen05(torch, monkeypatch):
     """The cross-check GEMM and the tcgen05 GEMM give the same forward (accumulation order aside)."""
     ocfg, w, rows_fn, eng = make_pair(max_batch=4)

@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
     const int r = c / CH, dc = (c % CH) * 8;
     const bool ok = (q0 + r) < T;
     const long long tok = trow(ok ? q0 + r : 0);
-    cp16((uint32_t)__cvta_generic_to_shared(sq + r * LD + dc), a.q + tok * a.q_tok_stride + (long long)h * a.q_head_stride + dc, ok);
+    cp16((uint32_t)__cvta_generic_to_shared(sq + r * LD + dc), a.q + tok * a.q_tok_stride + a.q_col(h) + dc, ok);
     if (has_cand) {
       cp16((uint32_t)__cvta_generic_to_shared(sks + r * LD + dc), kbase + tok * a.k_tok_stride + dc, ok);
       cp16((uint32_t)__cvta_generic_to_shared(svs + r * LD + dc), vbase + tok * a.v_tok_stride + dc, ok);
@@ -399,7 +399,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) ranker_attention_strip_kernel(
   auto trow = [&](int t) -> long long { return (long long)((t < n_hist ? hrow0 : crow0) + t); };
   const int n_blocks = (n_hist + KB - 1) / KB;
   const int n_tiles = (T + QROWS - 1) / QROWS;
-  const bf16* qbase = a.q + (long long)h * a.q_head_stride;
+  const bf16* qbase = a.q + a.q_col(h);
   const bf16* kbase = a.k + (long long)hk * a.k_head_stride;
   const bf16* vbase = a.v + (long long)hk * a.v_head_stride;
 

@@ -693,6 +693,7 @@ phx_status launch_resident(const AttnArgs& a, int* err_flag, cudaStream_t stream
 
 bool ranker_attention_tc_supported(const AttnArgs& a) {
   if (a.dh != 64 && a.dh != 128) return false;
+  if (a.q_group > 1) return false;   // grouped q heads of a merged QKV row: the mma.sync kernels address them
   {
     const int n_hist = a.hist_len < a.T ? a.hist_len : a.T;
     if ((n_hist + 63) / 64 > TC_MAX_BLOCKS) return false;   // validity table of the CTA

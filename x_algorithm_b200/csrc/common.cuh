@@ -254,6 +254,12 @@ struct AttnArgs {
   const bf16* q; const bf16* k; const bf16* v;  // element strides below
   long long q_tok_stride, k_tok_stride, v_tok_stride;  // between consecutive tokens
   int q_head_stride, k_head_stride, v_head_stride;     // between consecutive heads
+  // grouped-query layouts where the q heads of one kv group sit together (merged QKV: [q_0..q_{g-1}, k, v] per kv
+  // head): q head h starts at (h / q_group) * q_group_stride + (h % q_group) * q_head_stride.  q_group = 1: h * q_head_stride
+  int q_group = 1, q_group_stride = 0;
+  __host__ __device__ long long q_col(int h) const {
+    return q_group <= 1 ? (long long)h * q_head_stride : (long long)(h / q_group) * q_group_stride + (long long)(h % q_group) * q_head_stride;
+  }
   bf16* out;             // [B,T,Hq,dh] dense
   const int* seg;        // [B,T]
   int B, T, Hq, Hkv, dh, hist_len;

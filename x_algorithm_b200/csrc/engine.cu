@@ -456,10 +456,11 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len, bo
     const int g = e->Hq / e->Hkv;
     aa.q = e->qkv; aa.k = e->qkv + (long long)g * e->dh; aa.v = e->qkv + (long long)(g + 1) * e->dh;
     aa.q_tok_stride = aa.k_tok_stride = aa.v_tok_stride = e->QW;
-    // q head h sits at column ((h / g) * (g + 2) + h % g) * dh; for g == 1 that is h * 3 * dh.  The kernel
-    // takes a constant head stride, so grouped-query layouts are handled by the (g + 2) * dh stride of kv
-    // heads and require g == 1 for q here.
-    aa.q_head_stride = (g + 2) * e->dh; aa.k_head_stride = (g + 2) * e->dh; aa.v_head_stride = (g + 2) * e->dh;
+    // merged QKV row: per kv head [q_0..q_{g-1}, k, v] (layers.py:728-736): q head h sits at column
+    // ((h / g) * (g + 2) + h % g) * dh, kv head j's k at (j * (g + 2) + g) * dh
+    aa.q_head_stride = (g == 1) ? (g + 2) * e->dh : e->dh;
+    aa.q_group = g; aa.q_group_stride = (g + 2) * e->dh;
+    aa.k_head_stride = (g + 2) * e->dh; aa.v_head_stride = (g + 2) * e->dh;
     aa.out = e->attn; aa.seg = e->seg; aa.B = B; aa.T = Tt; aa.Hq = e->Hq; aa.Hkv = e->Hkv; aa.dh = e->dh;
     aa.hist_len = hist_len; aa.sm_scale = sm_scale; aa.cap = c.attn_logit_cap;
     aa.cap_method = (c.attn_logit_cap > 0.f) ? c.cap_method : 0;
@@ -588,7 +589,6 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
   e->D = cfg->emb_size; e->S = cfg->history_len; e->C = cfg->num_candidates; e->T = e->S + e->C;
   e->Hq = cfg->num_q_heads; e->Hkv = cfg->num_kv_heads; e->dh = cfg->key_size; e->F = cfg->ffn_size;
   e->QW = (e->Hq + 2 * e->Hkv) * e->dh; e->HD = e->Hq * e->dh; e->V = cfg->num_actions; e->NC = cfg->num_continuous;
-  if (e->Hq != e->Hkv) { e->err = "grouped-query attention is not supported by this build (num_q_heads must equal num_kv_heads)"; return fail(PHX_E_ARG); }
   long long ou, oi, oa, oip, tot;
   region_offsets(*cfg, &ou, &oi, &oa, &oip, &tot);
   e->table_rows = tot;
