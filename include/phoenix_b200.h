@@ -371,6 +371,19 @@ phx_status phx_corpus_fill_synthetic(phx_corpus* c, uint32_t seed);
  * cuda/top_k_by_key/__init__.py:56-94).  Asynchronous on the corpus' stream. */
 phx_status phx_corpus_topk_device(phx_corpus* c, const float* users_dev, int32_t B, int32_t k, float* scores_dev,
                                   int64_t* ids_dev);
+/* The per-shard list in the form it travels in before a merge: one 64-bit key per entry, (order-preserving image of
+ * the f32 score) << 32 | ~(row as u32), sorted descending, 0 = empty slot - 8 bytes per entry in ONE all-gather instead
+ * of a score and an id array in two (recsys_two_tower_model.py:215-220 gathers both).  phx_topk_merge_keys_device
+ * merges [P,B,k] such lists into scores f32 [B,k] and rows int64 [B,k] by (score desc, row asc).  Rows must fit 32
+ * bits, as everywhere in this library. */
+phx_status phx_corpus_topk_keys_device(phx_corpus* c, const float* users_dev, int32_t B, int32_t k, uint64_t* keys_dev);
+phx_status phx_topk_merge_keys_device(phx_corpus* c, const uint64_t* keys_dev, int32_t P, int32_t B, int32_t k,
+                                      float* out_scores_dev, int64_t* out_ids_dev);
+/* Enqueue the shard's later work on `stream` (a cudaStream_t of the shard's device; NULL is the default stream)
+ * instead of its own stream, so that it orders with the caller's other work - the collective between top-k and merge -
+ * without host synchronisation; use_own != 0 returns to the shard's own stream.  The reference's ops run on the framework's stream the same way
+ * (top_k_by_key_ffi.cc:15-26). */
+phx_status phx_corpus_set_stream(phx_corpus* c, void* stream, int32_t use_own);
 /* Per-row eligibility of the shard (the reference's per-post masks ahead of the top-k: dataset type mask and
  * eligibility mask, recsys_two_tower_model.py:2486-2493, 2690-2702, where a masked post's score becomes
  * finfo(bf16).min): bit (r & 31) of host_bits[r >> 5] set = shard-local row r may be returned; ceil(rows / 32) words;

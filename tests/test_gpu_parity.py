@@ -674,6 +674,32 @@ def test_topk_with_row_eligibility_mask(torch, monkeypatch, impl, dim, N):
     shard.close()
 
 
+def test_retriever_orders_its_work_on_the_callers_stream(torch):
+    """Retriever.retrieve enqueues per-shard top-k (as 64-bit keys), the merge and anything the caller adds on torch's
+    current stream, default stream included, with no host synchronisation in between: reading the result right away
+    must give the oracle's answer, on shards large enough for a race to show."""
+    from x_algorithm_b200.retrieval import CorpusShard, Retriever
+    N, dim, k, B = 600_000, 64, 100, 8
+    shards = [CorpusShard(N // 2, dim, row_offset=0, max_queries=B, max_k=k), CorpusShard(N - N // 2, dim, row_offset=N // 2, max_queries=B, max_k=k)]
+    for sh in shards:
+        sh.fill_synthetic(23)
+    rng = np.random.default_rng(7)
+    u = rng.standard_normal((B, dim)).astype(np.float32)
+    u /= np.linalg.norm(u, axis=1, keepdims=True)
+    users = torch.from_numpy(u).cuda()
+    want_s, want_i = po.top_k(po.corpus_scores(u, po.synthetic_corpus_rows(np.arange(N), dim, 23)), k)
+    ret = Retriever(shards)
+    for stream in (torch.cuda.current_stream(), torch.cuda.Stream()):
+        with torch.cuda.stream(stream):
+            sc, ids = ret.retrieve(users, k)
+            doubled = sc * 2           # the caller's own work behind the merge, same stream
+            got_i, got_d = ids.cpu().numpy(), doubled.cpu().numpy()
+        np.testing.assert_array_equal(got_i, want_i)
+        np.testing.assert_allclose(got_d, 2 * want_s, rtol=2.0 ** -7, atol=0)
+    for sh in shards:
+        sh.sync(); sh.close()
+
+
 def test_sharded_gather_exchange_kernels_bit_identical(torch):
     """The device-side steps of the all-to-all exchange (bucket by owner, owner-side gather, fixed-order sum), with
     the two collectives emulated by slicing: two "ranks" on one device, each holding half of the table.  The result

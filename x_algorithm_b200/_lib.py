@@ -129,6 +129,9 @@ SIGNATURES = {
     "phx_corpus_fill_synthetic": (C.c_int32, [_P, C.c_uint32]),
     "phx_corpus_topk_device": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, _P, _P]),
     "phx_corpus_set_mask": (C.c_int32, [_P, _P]),
+    "phx_corpus_topk_keys_device": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, _P]),
+    "phx_topk_merge_keys_device": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, C.c_int32, _P, _P]),
+    "phx_corpus_set_stream": (C.c_int32, [_P, _P, C.c_int32]),
     "phx_corpus_topk_window_device": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, C.c_int64, C.c_int64, _P, _P]),
     "phx_topk_merge_device": (C.c_int32, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, _P, _P]),
     "phx_topk_merge_static": (C.c_int32, [C.c_int32, _P, _P, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P]),

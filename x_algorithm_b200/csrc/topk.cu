@@ -270,7 +270,9 @@ __global__ void __launch_bounds__(SEL_THREADS) pivot_kernel(const float* __restr
 __global__ void __launch_bounds__(SEL_THREADS) select_kernel(const unsigned long long* __restrict__ keys, const int* counts,
                                                              int fixed_n, int cap, int k, int kpow2,
                                                              float* __restrict__ out_scores, long long* __restrict__ out_ids,
-                                                             int* status) {
+                                                             int* status, unsigned long long* __restrict__ out_keys = nullptr) {
+  // out_keys: write the sorted 64-bit keys themselves (ordered score << 32 | ~row; 0 = empty slot) instead of
+  // (score, id) pairs - the form per-shard lists travel in before a merge
   extern __shared__ __align__(16) uint8_t selsm[];
   unsigned long long* s_keys = reinterpret_cast<unsigned long long*>(selsm);  // [kpow2]
   __shared__ int s_hist[256];
@@ -281,7 +283,10 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(const unsigned long
   if (counts && n > cap) { if (threadIdx.x == 0) atomicOr(status, 2); n = cap; }
   if (n < k) {
     if (threadIdx.x == 0) atomicOr(status, 1);
-    for (int i = threadIdx.x; i < k; i += blockDim.x) { out_scores[(size_t)u * k + i] = -INFINITY; out_ids[(size_t)u * k + i] = -1; }
+    for (int i = threadIdx.x; i < k; i += blockDim.x) {
+      if (out_keys) out_keys[(size_t)u * k + i] = 0ull;
+      else { out_scores[(size_t)u * k + i] = -INFINITY; out_ids[(size_t)u * k + i] = -1; }
+    }
     return;
   }
   const unsigned long long* ku = keys + (size_t)u * cap;
@@ -297,9 +302,20 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(const unsigned long
   bitonic_sort_desc(s_keys, kpow2);
   for (int i = threadIdx.x; i < k; i += blockDim.x) {
     const unsigned long long v = s_keys[i];
+    if (out_keys) { out_keys[(size_t)u * k + i] = v; continue; }
     out_scores[(size_t)u * k + i] = from_ordered32((uint32_t)(v >> 32));
     out_ids[(size_t)u * k + i] = (long long)(0xFFFFFFFFu - (uint32_t)(v & 0xFFFFFFFFull));
   }
+}
+
+// [P][B][k] keys -> keys[B][P*k] (the layout the select kernel reads one query's candidates in)
+__global__ void regroup_keys_kernel(const unsigned long long* __restrict__ in, int P, int B, int k, unsigned long long* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)P * B * k) return;
+  const int p = (int)(i / ((long long)B * k));
+  const int b = (int)((i / k) % B);
+  const int j = (int)(i % k);
+  out[((size_t)b * P + p) * k + j] = in[i];
 }
 
 // [P][B][k] (score, id) lists -> keys[B][P*k]
@@ -346,7 +362,9 @@ struct phx_corpus {
   unsigned int* mask = nullptr;              // eligibility bits of the shard's rows (phx_corpus_set_mask), null = all
   std::vector<unsigned int> mask_host;
   long long elig_begin = -1, elig_end = -1, elig_count = 0;   // eligible rows of the last window asked for
-  cudaStream_t stream = nullptr;
+  cudaStream_t stream = nullptr;       // the stream the shard's work is enqueued on: its own, or the caller's
+  cudaStream_t own_stream = nullptr;
+  unsigned long long* keys_out = nullptr;   // set for one call by phx_corpus_topk_keys_device
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   std::string err;
 };
@@ -394,7 +412,8 @@ phx_status phx_corpus_create(int32_t device, int64_t rows, int32_t dim, int64_t 
   if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return fail("cudaGetDeviceProperties failed");
   c->num_sms = prop.multiProcessorCount;
 #define CU(x) do { cudaError_t _e = (x); if (_e != cudaSuccess) return fail(std::string(#x) + ": " + cudaGetErrorString(_e)); } while (0)
-  CU(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+  CU(cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking));
+  c->stream = c->own_stream;
   CU(cudaEventCreate(&c->ev0)); CU(cudaEventCreate(&c->ev1));
   CU(cudaMalloc(&c->data, (size_t)rows * dim * 2));
   CU(cudaMalloc(&c->users_bf, (size_t)256 * dim * 2));
@@ -432,7 +451,7 @@ void phx_corpus_destroy(phx_corpus* c) {
   fr(c->data); fr(c->users_bf); fr(c->gmax); fr(c->pivot); fr(c->surv); fr(c->merge_keys); fr(c->counts); fr(c->status); fr(c->err_flag); fr(c->mask);
   if (c->ev0) cudaEventDestroy(c->ev0);
   if (c->ev1) cudaEventDestroy(c->ev1);
-  if (c->stream) cudaStreamDestroy(c->stream);
+  if (c->own_stream) cudaStreamDestroy(c->own_stream);
   delete c;
 }
 
@@ -474,7 +493,7 @@ phx_status phx_corpus_set_mask(phx_corpus* c, const uint32_t* host_bits) {
 
 phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, int32_t B, int32_t k, int64_t row_begin,
                                          int64_t row_end, float* scores_dev, int64_t* ids_dev) {
-  if (!c || !users_dev || !scores_dev || !ids_dev) return PHX_E_ARG;
+  if (!c || !users_dev || ((!scores_dev || !ids_dev) && !c->keys_out)) return PHX_E_ARG;
   if (B <= 0 || B > c->max_queries || k <= 0 || k > c->max_k) { c->err = "topk: B or k exceeds what the corpus was created for"; return PHX_E_CAPACITY; }
   if (row_begin < 0 || row_end > c->rows || row_begin >= row_end) { c->err = "topk: window outside the shard's rows"; return PHX_E_ARG; }
   // the window [row_begin, row_end) of the shard scanned as a corpus of its own: rows, first row and global id of row 0
@@ -553,7 +572,7 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
   }
   const int kp2 = next_pow2(k);
   select_kernel<<<B, SEL_THREADS, (size_t)kp2 * 8, c->stream>>>(c->surv, c->counts, 0, c->cap, k, kp2, scores_dev,
-                                                               (long long*)ids_dev, c->status);
+                                                               (long long*)ids_dev, c->status, c->keys_out);
   PHX_CUDA_TRY(cudaGetLastError(), c->err);
   PHX_CUDA_TRY(cudaEventRecord(c->ev1, c->stream), c->err);
   return PHX_OK;
@@ -564,6 +583,41 @@ phx_status phx_corpus_topk_device(phx_corpus* c, const float* users_dev, int32_t
   if (!c) return PHX_E_ARG;
   if (k > c->rows) { c->err = "topk: k exceeds the shard's rows"; return PHX_E_ARG; }
   return phx_corpus_topk_window_device(c, users_dev, B, k, 0, c->rows, scores_dev, ids_dev);
+}
+
+phx_status phx_corpus_topk_keys_device(phx_corpus* c, const float* users_dev, int32_t B, int32_t k, uint64_t* keys_dev) {
+  if (!c || !keys_dev) return PHX_E_ARG;
+  if (k > c->rows) { c->err = "topk: k exceeds the shard's rows"; return PHX_E_ARG; }
+  c->keys_out = (unsigned long long*)keys_dev;
+  const phx_status s = phx_corpus_topk_window_device(c, users_dev, B, k, 0, c->rows, nullptr, nullptr);
+  c->keys_out = nullptr;
+  return s;
+}
+
+phx_status phx_topk_merge_keys_device(phx_corpus* c, const uint64_t* keys_dev, int32_t P, int32_t B, int32_t k,
+                                      float* out_scores_dev, int64_t* out_ids_dev) {
+  if (!c || !keys_dev || !out_scores_dev || !out_ids_dev || P <= 0 || B <= 0 || k <= 0 || k > 4096) return PHX_E_ARG;
+  cudaSetDevice(c->device);
+  const size_t need = (size_t)P * B * k;
+  if (need > c->merge_keys_elems) {
+    if (c->merge_keys) cudaFree(c->merge_keys);
+    c->merge_keys = nullptr;
+    PHX_CUDA_TRY(cudaMalloc(&c->merge_keys, need * 8), c->err);
+    c->merge_keys_elems = need;
+  }
+  regroup_keys_kernel<<<(unsigned)((need + 255) / 256), 256, 0, c->stream>>>((const unsigned long long*)keys_dev, P, B, k, c->merge_keys);
+  PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  const int kp2 = next_pow2(k);
+  select_kernel<<<B, SEL_THREADS, (size_t)kp2 * 8, c->stream>>>(c->merge_keys, nullptr, P * k, P * k, k, kp2, out_scores_dev,
+                                                               (long long*)out_ids_dev, c->status);
+  PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  return PHX_OK;
+}
+
+phx_status phx_corpus_set_stream(phx_corpus* c, void* stream, int32_t use_own) {
+  if (!c) return PHX_E_ARG;
+  c->stream = use_own ? c->own_stream : (cudaStream_t)stream;   // a NULL caller stream is the default stream
+  return PHX_OK;
 }
 
 phx_status phx_topk_merge_device(phx_corpus* c, const float* scores_dev, const int64_t* ids_dev, int32_t P, int32_t B,

@@ -68,6 +68,20 @@ class CorpusShard:
         self._check(lib.phx_corpus_topk_window_device(self._h, int(users.data_ptr()), B, k, row_begin, row_end,
                                                       int(scores.data_ptr()), int(ids.data_ptr())))
 
+    def topk_keys_device(self, users, B: int, k: int, keys):
+        """The shard's top-k as sorted 64-bit keys int64 [B,k] (score and row in one word): the form the lists are
+        gathered in before a merge."""
+        self._check(lib.phx_corpus_topk_keys_device(self._h, int(users.data_ptr()), B, k, int(keys.data_ptr())))
+
+    def merge_keys_device(self, keys, P: int, B: int, k: int, out_scores, out_ids):
+        self._check(lib.phx_topk_merge_keys_device(self._h, int(keys.data_ptr()), P, B, k, int(out_scores.data_ptr()),
+                                                   int(out_ids.data_ptr())))
+
+    def set_stream(self, stream):
+        """Run the shard's later work on this CUDA stream (an integer handle, 0 = the default stream; None = the
+        shard's own stream)."""
+        self._check(lib.phx_corpus_set_stream(self._h, stream or None, 1 if stream is None else 0))
+
     def merge_device(self, scores, ids, P: int, B: int, k: int, out_scores, out_ids):
         self._check(lib.phx_topk_merge_device(self._h, int(scores.data_ptr()), int(ids.data_ptr()), P, B, k,
                                               int(out_scores.data_ptr()), int(out_ids.data_ptr())))
@@ -101,32 +115,27 @@ class Retriever:
         self.shards = list(shards)
 
     def retrieve(self, users, k: int):
+        """Top-k rows of the whole corpus for users f32 [B, dim] (CUDA tensor) -> (scores f32 [B,k], rows int64 [B,k]).
+        Everything is enqueued on torch's current stream - per-shard top-k as 64-bit keys, one all-gather of those
+        keys, the merge - and nothing waits on the host: the caller synchronises when it reads the result."""
         import torch
         B = users.shape[0]
         dev = users.device
         P = len(self.shards)
-        sc = torch.empty((P, B, k), dtype=torch.float32, device=dev)
-        ids = torch.empty((P, B, k), dtype=torch.int64, device=dev)
-        torch.cuda.synchronize()
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        keys = torch.empty((P, B, k), dtype=torch.int64, device=dev)
         for p, sh in enumerate(self.shards):
-            sh.topk_device(users, B, k, sc[p], ids[p])
-        for sh in self.shards:
-            sh.sync()
+            sh.set_stream(stream)
+            sh.topk_keys_device(users, B, k, keys[p])
         dist = torch.distributed
         if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
             W = dist.get_world_size()
-            gs = torch.empty((W * P, B, k), dtype=torch.float32, device=dev)
-            gi = torch.empty((W * P, B, k), dtype=torch.int64, device=dev)
-            dist.all_gather_into_tensor(gs, sc)
-            dist.all_gather_into_tensor(gi, ids)
-            sc, ids, P = gs, gi, W * P
-        if P == 1:
-            return sc[0], ids[0]
+            gk = torch.empty((W * P, B, k), dtype=torch.int64, device=dev)
+            dist.all_gather_into_tensor(gk, keys)
+            keys, P = gk, W * P
         out_s = torch.empty((B, k), dtype=torch.float32, device=dev)
         out_i = torch.empty((B, k), dtype=torch.int64, device=dev)
-        torch.cuda.synchronize()
-        self.shards[0].merge_device(sc, ids, P, B, k, out_s, out_i)
-        self.shards[0].sync()
+        self.shards[0].merge_keys_device(keys, P, B, k, out_s, out_i)
         return out_s, out_i
 
     def user_vector(self, tower, history):
@@ -149,4 +158,7 @@ class Retriever:
 
     def retrieve_for_history(self, tower, history, k: int):
         s, i = self.retrieve(self.user_vector(tower, history), k)
-        return s[0].cpu().numpy(), i[0].cpu().numpy()
+        s, i = s[0].cpu().numpy(), i[0].cpu().numpy()
+        for sh in self.shards:
+            sh.sync()      # surfaces a device-side error of the scan (bounded wait, survivor overflow) as PhoenixError
+        return s, i
