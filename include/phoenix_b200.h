@@ -102,8 +102,8 @@ typedef struct phx_model_config {
    * slots and candidates and the forward runs over those rows only, back to back (the reference serves ragged users
    * through sequence packing, phoenix/xrex/data/sequence_packing.py:317; here the packing is by rows, requests stay
    * independent).  Requests must be front-filled (padding only behind the valid slots); a batch that is not is run
-   * over all its slots.  Outputs of padded candidate slots are zero.  The device-pointer entry points and the
-   * submit / collect pipeline run over all slots. */
+   * over all its slots.  Outputs of padded candidate slots are zero.  phx_rank_forward and phx_rank_submit pack (they
+   * see the ids on the host); the device-pointer entry points run over all slots. */
   int32_t pack_ragged;
   /* 1 = the history actions of a position are a SET: hist_actions holds a bit mask (bit v = action v, v <
    * num_action_types <= 32; the reference's bool[B,S,V] buffer packed), and "action_table" is one [1, emb_size] vector

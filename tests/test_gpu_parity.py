@@ -362,6 +362,13 @@ def test_packed_ragged_batches_match_unpacked(torch, monkeypatch, opts, attn):
     lp, cont, _ = po.rank_forward(ocfg, w, rows_fn, b)
     valid = b.cand_post_ids != 0
     assert rel_l2(got.log_probs[valid], lp[valid]) < TOL
+    # two requests in flight through submit / collect: each packs by its own counts
+    packed.rank_submit(to_inputs(b), 0)
+    packed.rank_submit(to_inputs(full), 1)
+    r0, r1 = packed.rank_collect(0), packed.rank_collect(1)
+    np.testing.assert_array_equal(r0.log_probs[valid], want.log_probs[valid])
+    np.testing.assert_array_equal(r1.log_probs, plain.rank(to_inputs(full)).log_probs)
+    assert (r0.log_probs[~valid] == 0).all()
     # the device-pointer entry point of the packing engine runs every slot
     dev = _device_batch(torch, b)
     out = _device_out(torch, packed.cfg, 6)

@@ -59,6 +59,13 @@ struct Layer {
 using namespace phx;
 
 struct phx_engine {
+  struct PackState {
+    int *hist_off = nullptr, *cand_off = nullptr, *pos_rows = nullptr, *out_index = nullptr;   // device, owned
+    const int *hist_off_view = nullptr, *cand_off_view = nullptr;   // offsets living in a staging block instead
+    long long M = 0, Mh = 0;      // packed rows in all, history rows
+    int planned_batch = -1;       // batch size pos_rows / out_index were last planned for (full plan)
+    bool ragged = false;
+  };
   phx_model_config cfg;
   int device = 0;
   int num_sms = 148;
@@ -82,12 +89,6 @@ struct phx_engine {
   // packed rows (cfg.pack_ragged): every forward addresses its token rows through a PackMap; `full` covers all slots
   // of every request (device-pointer entry points, batches that are not front-filled), `ragged` the counts the
   // host-buffer call found in its batch
-  struct PackState {
-    int *hist_off = nullptr, *cand_off = nullptr, *pos_rows = nullptr, *out_index = nullptr;   // device
-    long long M = 0, Mh = 0;      // packed rows in all, history rows
-    int planned_batch = -1;       // batch size pos_rows / out_index were last planned for (full plan)
-    bool ragged = false;
-  };
   bool pack = false;
   PackState pack_full, pack_ragged;
   PackState* pack_next = nullptr;   // set by the host-buffer call for the forward it is about to enqueue
@@ -146,6 +147,8 @@ struct phx_engine {
     cudaEvent_t chunk[4] = {nullptr, nullptr, nullptr, nullptr};
     bool busy = false;
     int batch = 0;
+    PackState pack;                 // packed rows of the request in this slot (offset arrays inside the slot's block)
+    std::vector<int> pack_host;
   };
   StageSlot slots[2];
   cudaStream_t copy_stream = nullptr;
@@ -225,7 +228,11 @@ HashFamilyDev to_dev(const phx_hash_family& f, int offset) {
 
 PackMap pack_map(const phx_engine::PackState* ps) {
   PackMap m;
-  if (ps) { m.hist_off = ps->hist_off; m.cand_off = ps->cand_off; m.cand_base = ps->Mh; }
+  if (ps) {
+    m.hist_off = ps->hist_off_view ? ps->hist_off_view : ps->hist_off;
+    m.cand_off = ps->cand_off_view ? ps->cand_off_view : ps->cand_off;
+    m.cand_base = ps->Mh;
+  }
   return m;
 }
 
@@ -1126,6 +1133,30 @@ phx_status phx_rank_prefetch_device(phx_engine* e, const phx_rank_batch* bd) {
   return PHX_OK;
 }
 
+namespace {
+// Packed rows: the leading non-padding slots of every request (id 0 = padding) as exclusive prefix sums ho / co with
+// B + 1 entries.  A batch with padding in front of a valid slot is planned over all its slots.  A request keeps at
+// least one history row (a padded one when it has none), so every request has a key block.
+void plan_ragged(const phx_rank_batch* bh, size_t B, size_t S, size_t C, int* ho, int* co) {
+  bool front_filled = true;
+  ho[0] = co[0] = 0;
+  for (size_t b = 0; b < B && front_filled; ++b) {
+    const int64_t* hpid = bh->hist_post_ids + b * S;
+    const int64_t* cpid = bh->cand_post_ids + b * C;
+    size_t hc = 0, cc = 0;
+    while (hc < S && hpid[hc] != 0) ++hc;
+    while (cc < C && cpid[cc] != 0) ++cc;
+    for (size_t t = hc; t < S; ++t) if (hpid[t] != 0) front_filled = false;
+    for (size_t c = cc; c < C; ++c) if (cpid[c] != 0) front_filled = false;
+    ho[b + 1] = ho[b] + (int)(hc > 0 ? hc : 1);
+    co[b + 1] = co[b] + (int)cc;
+  }
+  if (!front_filled)
+    for (size_t b = 0; b < B; ++b) { ho[b + 1] = (int)((b + 1) * S); co[b + 1] = (int)((b + 1) * C); }
+}
+
+}  // namespace
+
 phx_status phx_rank_forward(phx_engine* e, const phx_rank_batch* bh, const phx_rank_out* oh) {
   if (!e || !bh || !oh) return PHX_E_ARG;
   if (bh->batch < 0 || bh->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
@@ -1145,35 +1176,15 @@ phx_status phx_rank_forward(phx_engine* e, const phx_rank_batch* bh, const phx_r
   bd.hist_actions = (const int32_t*)put(bh->hist_actions, B * S * 4);
   bd.hist_surfaces = (const int32_t*)put(bh->hist_surfaces, B * S * 4);
   if (e->pack) {
-    // Packed rows: the leading non-padding slots of every request (id 0 = padding).  A batch with padding in front
-    // of a valid slot is run over all its slots.  A request keeps at least one history row (a padded one when it has
-    // none), so every request has a key block.
     int* ho = e->pack_host.data();
     int* co = ho + (B + 1);
-    bool front_filled = true;
-    ho[0] = co[0] = 0;
-    for (size_t b = 0; b < B && front_filled; ++b) {
-      const int64_t* hpid = bh->hist_post_ids + b * S;
-      const int64_t* cpid = bh->cand_post_ids + b * C;
-      size_t hc = 0, cc = 0;
-      while (hc < S && hpid[hc] != 0) ++hc;
-      while (cc < C && cpid[cc] != 0) ++cc;
-      for (size_t t = hc; t < S; ++t) if (hpid[t] != 0) front_filled = false;
-      for (size_t c = cc; c < C; ++c) if (cpid[c] != 0) front_filled = false;
-      ho[b + 1] = ho[b] + (int)(hc > 0 ? hc : 1);
-      co[b + 1] = co[b] + (int)cc;
-    }
-    if (!front_filled)
-      for (size_t b = 0; b < B; ++b) { ho[b + 1] = (int)((b + 1) * S); co[b + 1] = (int)((b + 1) * C); }
+    plan_ragged(bh, B, S, C, ho, co);
     off = (off + 15) & ~(size_t)15;
-    const int* ho_dev = (const int*)put(ho, (B + 1) * 4);
-    const int* co_dev = (const int*)put(co, (B + 1) * 4);
     phx_engine::PackState& pk = e->pack_ragged;
+    pk.hist_off_view = (const int*)put(ho, (B + 1) * 4);   // the plan reads its offsets from the staged block
+    pk.cand_off_view = (const int*)put(co, (B + 1) * 4);
     pk.Mh = ho[B]; pk.M = (long long)ho[B] + co[B];
-    // the plan's offset arrays live in the engine's own buffers: copied there behind the input block
     PHX_CUDA_TRY(cudaMemcpyAsync(dp, hp, off, cudaMemcpyHostToDevice, e->stream), e->err);
-    PHX_CUDA_TRY(cudaMemcpyAsync(pk.hist_off, ho_dev, (B + 1) * 4, cudaMemcpyDeviceToDevice, e->stream), e->err);
-    PHX_CUDA_TRY(cudaMemcpyAsync(pk.cand_off, co_dev, (B + 1) * 4, cudaMemcpyDeviceToDevice, e->stream), e->err);
     e->pack_next = &pk;
   } else {
     PHX_CUDA_TRY(cudaMemcpyAsync(dp, hp, off, cudaMemcpyHostToDevice, e->stream), e->err);
@@ -1253,6 +1264,19 @@ phx_status phx_rank_submit(phx_engine* e, const phx_rank_batch* bh, int32_t slot
   bd.cand_author_ids = (const int64_t*)put(bh->cand_author_ids, B * C * 8);
   bd.hist_actions = (const int32_t*)put(bh->hist_actions, B * S * 4);
   bd.hist_surfaces = (const int32_t*)put(bh->hist_surfaces, B * S * 4);
+  if (e->pack) {   // packed rows: this request's counts travel in the slot's block, its plan shares the engine's row arrays
+    sl.pack_host.resize(2 * (B + 1));
+    int* ho = sl.pack_host.data();
+    int* co = ho + (B + 1);
+    plan_ragged(bh, B, S, C, ho, co);
+    off = (off + 15) & ~(size_t)15;
+    sl.pack.hist_off_view = (const int*)put(ho, (B + 1) * 4);
+    sl.pack.cand_off_view = (const int*)put(co, (B + 1) * 4);
+    sl.pack.pos_rows = e->pack_ragged.pos_rows; sl.pack.out_index = e->pack_ragged.out_index;
+    sl.pack.Mh = ho[B]; sl.pack.M = (long long)ho[B] + co[B];
+    sl.pack.ragged = true;
+    e->pack_next = &sl.pack;
+  }
   // inputs: on the copy stream, once the forward that last read this slot's device block is done
   PHX_CUDA_TRY(cudaStreamWaitEvent(e->copy_stream, sl.fwd_done, 0), e->err);
   PHX_CUDA_TRY(cudaMemcpyAsync(dp, hp, off, cudaMemcpyHostToDevice, e->copy_stream), e->err);

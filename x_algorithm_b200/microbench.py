@@ -281,8 +281,19 @@ def bench_ragged(a):
                 t0 = time.perf_counter()
             out = eng.rank(inp, out)
         dt = (time.perf_counter() - t0) / a.iters
+        # the same with two requests in flight (submit / collect)
+        outs = [None, None]
+        eng.rank_submit(inp, 0)
+        for i in range(a.warmup + a.iters):
+            if i == a.warmup:
+                t1 = time.perf_counter()
+            eng.rank_submit(inp, (i + 1) & 1)
+            outs[i & 1] = eng.rank_collect(i & 1, outs[i & 1])
+        eng.rank_collect((a.warmup + a.iters) & 1)
+        dp = (time.perf_counter() - t1) / a.iters
         print(json.dumps(dict(op="rank_ragged", packed=pack, batch=a.batch, valid_candidates=valid, valid_rows=rows,
-                              slots=a.batch * 640, ms=dt * 1e3, valid_candidates_per_s=valid / dt)))
+                              slots=a.batch * 640, ms=dt * 1e3, valid_candidates_per_s=valid / dt,
+                              pipelined_ms=dp * 1e3, pipelined_valid_candidates_per_s=valid / dp)))
         eng.close()
 
 
