@@ -140,6 +140,9 @@ __global__ void __launch_bounds__(HM_WARPS * 32) heads_mma_kernel(HeadsArgs a) {
     *reinterpret_cast<uint4*>(sw + n * WLD + ch * 8) = w;
   }
   for (int i = threadIdx.x; i < D; i += blockDim.x) sgain[i] = a.final_gain[i];
+  // programmatic dependent launch: the parameters above are staged while the last GEMM of the trunk drains; its
+  // output is read only from here on
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   __syncthreads();
   float* sC = sC_all + warp * 16 * NT * 8;
   double* sD = sD_all + warp * 16 * NT * 8;
@@ -253,8 +256,17 @@ phx_status launch_heads_mma(const HeadsArgs& a, long long rows, cudaStream_t str
   }
   long long blocks = ((rows + 15) / 16 + HM_WARPS - 1) / HM_WARPS;
   if (blocks > 148 * 3) blocks = 148 * 3;
-  heads_mma_kernel<NT><<<(unsigned)blocks, HM_WARPS * 32, smem, stream>>>(a);
-  PHX_CUDA_TRY(cudaGetLastError(), err);
+  cudaLaunchConfig_t lc;
+  memset(&lc, 0, sizeof(lc));
+  lc.gridDim = dim3((unsigned)blocks); lc.blockDim = dim3(HM_WARPS * 32); lc.dynamicSmemBytes = smem; lc.stream = stream;
+  cudaLaunchAttribute at[1];
+  static const bool pdl = !(getenv("PHX_PDL") && getenv("PHX_PDL")[0] == '0');
+  if (pdl) {   // start while the kernel in front drains; the kernel waits before it reads the residual stream
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at; lc.numAttrs = 1;
+  }
+  PHX_CUDA_TRY(cudaLaunchKernelEx(&lc, heads_mma_kernel<NT>, a), err);
   return PHX_OK;
 }
 
