@@ -181,3 +181,26 @@ def test_source_contract():
     assert served_type_for_dataset("zero_fav") == "ForYouPhoenixRetrievalZeroFav"
     assert served_type_for_dataset("ai_video_model_2day") == "ForYouPhoenixRetrievalAiVideo"
     assert served_type_for_dataset("home") == "ForYouPhoenixRetrieval"
+
+
+def test_value_scores_argument_errors_are_statuses():
+    """Argument checks of phx_value_scores_device come before any CUDA call: bad sizes, a missing array and a source
+    column the inputs do not have are reported as statuses with a message (no GPU needed, nothing is launched)."""
+    import ctypes as C
+    from x_algorithm_b200 import _lib
+    import x_algorithm_b200.value_model as vm
+    m = vm.value_model_struct(vm.ValueModelWeights(w=dict(favorite=1.0)), ["favorite"], ["dwell_time"])
+    inp = _lib.ValueInputs()
+    inp.batch, inp.num_candidates, inp.num_actions, inp.num_continuous = 1, 8, 1, 1
+    out = (C.c_double * 8)()
+    call = lambda i, o: _lib.lib.phx_value_scores_device(0, C.byref(m), C.byref(i), None, o, None)
+    assert call(inp, None) == 1                                   # no output array
+    assert call(inp, out) == 1 and b"log_probs missing" in _lib.lib.phx_global_error()
+    inp.num_candidates = 5000
+    assert call(inp, out) == 5 and b"4096" in _lib.lib.phx_global_error()
+    inp.num_candidates, inp.num_continuous = 8, 0
+    dummy = (C.c_float * 8)()
+    inp.log_probs = C.addressof(dummy)      # never read: the check below fails before anything is launched
+    assert call(inp, out) == 1 and b"out of range" in _lib.lib.phx_global_error()
+    inp.batch = -1
+    assert call(inp, out) == 1
