@@ -956,15 +956,19 @@ phx_status enqueue_forward(phx_engine* e, const phx_rank_batch* bd, const phx_ra
 }  // namespace
 
 phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* bd, const phx_rank_out* od) {
-  if (!e || !bd || !od) return PHX_E_ARG;
+  if (!e) return PHX_E_ARG;
+  // the plan a host-buffer call prepared for this forward is taken here, before anything can fail: it never outlives
+  // the call it was made for
+  phx_engine::PackState* const planned = e->pack_next;
+  e->pack_next = nullptr;
+  if (!bd || !od) return PHX_E_ARG;
   if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
   if (bd->batch < 0 || bd->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
   if (!params_complete(e, true) || !shards_complete(e)) return PHX_E_STATE;
   cudaSetDevice(e->device);
   const int B = bd->batch;
   e->last_batch = B; e->last_launches = 0; e->prof_used = 0;
-  e->cur_pack = e->pack ? (e->pack_next ? e->pack_next : &e->pack_full) : nullptr;
-  e->pack_next = nullptr;
+  e->cur_pack = e->pack ? (planned ? planned : &e->pack_full) : nullptr;
   if (B == 0) return PHX_OK;
   PHX_CUDA_TRY(cudaEventRecord(e->ev0, e->stream), e->err);
   phx_status s;
