@@ -57,9 +57,8 @@ __device__ __forceinline__ void acc_chunk(float (&acc)[8], uint4 u) {
 // One warp per token.  History token slots: post h0.., author h0.., action row, surface row;
 // candidate token slots: post h0.., author h0...  x = bf16(bf16(sum) * input_scale).
 __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
-  // the kernel behind this one (a GEMM launched for programmatic dependent launch) may start its set-up now; it waits
-  // for this grid to finish before it reads anything
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // (no early launch signal here: the GEMM behind this kernel would park its CTAs - registers and all - on the SMs
+  // while this bandwidth-bound kernel still needs every warp slot it can get)
   const int T = a.S + a.C;
   const long long tok = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
