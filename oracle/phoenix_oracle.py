@@ -1033,6 +1033,27 @@ def top_k(scores: np.ndarray, k: int, row_offset: int = 0):
     return out_s, out_i
 
 
+def topk_keys(scores: np.ndarray, ids: np.ndarray) -> np.ndarray:
+    """A top-k list as one unsigned 64-bit key per entry, the form the GPU path gathers the per-shard lists in: the
+    f32 score mapped to 32 bits whose unsigned order is the score order (-0 counts as +0; negative values bit-flipped,
+    the others with the sign bit set) in the high word, the bitwise complement of the row (< 2^32) in the low word,
+    so that keys descending = (score descending, row ascending), the order of `jax.lax.top_k` and of the merge
+    (recsys_two_tower_model.py:215-220)."""
+    s = np.where(scores == 0, np.float32(0.0), scores.astype(np.float32))
+    u = s.view(np.uint32).astype(np.uint64)
+    hi = np.where(u & 0x80000000, (~u) & 0xFFFFFFFF, u | 0x80000000)
+    return (hi << np.uint64(32)) | (np.uint64(0xFFFFFFFF) - ids.astype(np.uint64))
+
+
+def merge_topk_keys(shard_keys: Sequence[np.ndarray], k: int):
+    """Merge per-shard key lists [B,k] -> (scores f32 [B,k], rows int64 [B,k]): the k largest keys of each query."""
+    keys = np.concatenate(shard_keys, axis=1)
+    top = np.sort(keys, axis=1)[:, ::-1][:, :k]
+    hi = (top >> np.uint64(32)).astype(np.uint32)
+    u = np.where(hi & np.uint32(0x80000000), hi & np.uint32(0x7FFFFFFF), ~hi)
+    return u.astype(np.uint32).view(np.float32), (np.uint64(0xFFFFFFFF) - (top & np.uint64(0xFFFFFFFF))).astype(np.int64)
+
+
 def merge_top_k(shard_scores: Sequence[np.ndarray], shard_ids: Sequence[np.ndarray], k: int):
     """Merge of per-shard top-k lists (strided_dataset_top_k, recsys_two_tower_model.py:215-220):
     concatenate, re-select k by (score desc, global id asc)."""

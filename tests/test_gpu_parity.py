@@ -703,8 +703,24 @@ def test_retriever_orders_its_work_on_the_callers_stream(torch):
             got_i, got_d = ids.cpu().numpy(), doubled.cpu().numpy()
         np.testing.assert_array_equal(got_i, want_i)
         np.testing.assert_allclose(got_d, 2 * want_s, rtol=2.0 ** -7, atol=0)
+    # the per-shard list in key form decodes to the oracle's list of that shard, and the oracle's merge of the two
+    # shards' device-made keys is the global answer
+    dev_keys = []
+    for p, sh in enumerate(shards):
+        keys = torch.empty((B, k), dtype=torch.int64, device="cuda")
+        sh.set_stream(None)
+        sh.topk_keys_device(users, B, k, keys)
+        sh.sync()
+        dev_keys.append(keys.cpu().numpy().view(np.uint64))
+        lo = p * (N // 2)
+        rows = po.synthetic_corpus_rows(np.arange(lo, lo + sh.rows), dim, 23)
+        ws, wi = po.top_k(po.corpus_scores(u, rows), k, row_offset=lo)
+        ds, di = po.merge_topk_keys([dev_keys[-1]], k)
+        np.testing.assert_array_equal(di, wi)
+        np.testing.assert_allclose(ds, ws, rtol=2.0 ** -7, atol=0)
+    np.testing.assert_array_equal(po.merge_topk_keys(dev_keys, k)[1], want_i)
     for sh in shards:
-        sh.sync(); sh.close()
+        sh.close()
 
 
 def test_sharded_gather_exchange_kernels_bit_identical(torch):

@@ -368,3 +368,19 @@ def test_value_model_multiplicative_known_answer():
     stale = po.ScoringCandidate(dict(pos), weighted_score=99.0)
     assert abs(po.compute_value_scores(wt, po.ScoringContext(), [stale])[0][0] - want) < 1e-12
     assert abs(po.compute_value_scores(dataclasses.replace(wt, multiplicative=False), po.ScoringContext(), [stale])[0][0] - 99.0) < 1e-12
+
+
+def test_topk_key_form_orders_like_score_then_row():
+    """The 64-bit key of a top-k entry: descending keys = (score descending, row ascending), through negative scores,
+    signed zeros, ties and subnormals; decoding gives the score and the row back."""
+    rng = np.random.default_rng(0)
+    sc = np.concatenate([rng.standard_normal(500).astype(np.float32), np.array([0.0, -0.0, 1e-40, -1e-40, 3.5, 3.5, -2.0, -2.0], np.float32)])
+    ids = rng.permutation(len(sc)).astype(np.int64) * 7919 % (1 << 32)
+    keys = po.topk_keys(sc[None], ids[None])[0]
+    order = np.argsort(keys)[::-1]
+    want = np.lexsort((ids, -sc.astype(np.float64)))
+    zero = sc == 0                                   # +0 and -0 are one score: only the row decides between them
+    assert np.array_equal(np.where(zero[order], 0.0, sc[order]), np.where(zero[want], 0.0, sc[want]))
+    assert np.array_equal(ids[order], ids[want])
+    s2, i2 = po.merge_topk_keys([keys[None]], len(sc))
+    assert np.array_equal(i2[0], ids[want]) and np.array_equal(np.abs(s2[0]), np.abs(sc[want]))

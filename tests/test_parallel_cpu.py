@@ -58,6 +58,11 @@ def _worker(rank, world, port, q):
         ms, mi = po.merge_top_k([g.numpy() for g in gs], [g.numpy() for g in gi], k)
         ws, wi = po.top_k(po.corpus_scores(users, po.synthetic_corpus_rows(np.arange(N), 32, 3)), k)
         assert np.array_equal(mi, wi) and np.array_equal(ms, ws)
+        # the same through the one-word key form the GPU path gathers (one all-gather of 8 bytes per entry)
+        gk = [torch.empty((B, k), dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(gk, torch.from_numpy(po.topk_keys(s_loc, i_loc).view(np.int64)))
+        ks, ki = po.merge_topk_keys([g.numpy().view(np.uint64) for g in gk], k)
+        assert np.array_equal(ki, wi) and np.array_equal(ks, ws)
         # ---- data-parallel split: every request served exactly once --------------------------------------------
         served = torch.zeros(11, dtype=torch.int64)
         a, b = pl.split_batch(11, world, rank)
