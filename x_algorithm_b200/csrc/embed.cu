@@ -38,8 +38,8 @@ __device__ __forceinline__ void acc_row(float (&acc)[8], const bf16* row, int co
 // The action row of a history token, columns col..col+7, as packed bf16.  Single action: row `act` of the table.
 // Action set (multi_hot_to_embeddings, recsys_model.py:3282-3312): the [D] vector, the chunk these columns lie in
 // signed by 2 a_v - 1 (a sign-bit flip: exact), everything zero when the set is empty.
-__device__ __forceinline__ uint4 action_chunk(const TokenBuildArgs& a, int act, int col) {
-  if (!a.action_multi_hot) return __ldg(reinterpret_cast<const uint4*>(a.action_table + (long long)act * a.D + col));
+__device__ __forceinline__ uint4 action_chunk(const TokenBuildArgs& a, int act, int col, bool action_set) {
+  if (!action_set) return __ldg(reinterpret_cast<const uint4*>(a.action_table + (long long)act * a.D + col));
   const unsigned live = (a.num_action_types >= 32) ? 0xffffffffu : ((1u << a.num_action_types) - 1u);
   const unsigned bits = (unsigned)act & live;
   if (bits == 0u) return make_uint4(0u, 0u, 0u, 0u);
@@ -56,6 +56,10 @@ __device__ __forceinline__ void acc_chunk(float (&acc)[8], uint4 u) {
 
 // One warp per token.  History token slots: post h0.., author h0.., action row, surface row;
 // candidate token slots: post h0.., author h0...  x = bf16(bf16(sum) * input_scale).
+// GENERAL = false is the benchmark's path with the optional inputs and outputs compiled out (packed rows, pre-hashed
+// rows, landing buffer, projected tokens, action sets, fp32 rows, debug taps, rows-only): same arithmetic, fewer
+// instructions in a kernel that is bound by how many loads it keeps in flight.
+template <bool GENERAL>
 __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
   // (no early launch signal here: the GEMM behind this kernel would park its CTAs - registers and all - on the SMs
   // while this bandwidth-bound kernel still needs every warp slot it can get)
@@ -68,7 +72,7 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
   const int H = a.item.num_hashes;
   const long long slot = is_hist ? (long long)b * a.S + t : (long long)b * a.C + (t - a.S);
   long long orow;   // where this token's row goes
-  if (a.pack.on() && !a.rows_only) {
+  if (GENERAL && a.pack.on() && !a.rows_only) {
     // packed rows: slots past the request's counts are not built at all (one token per warp: the whole warp leaves)
     if (is_hist ? t >= a.pack.hist_cnt(b) : (t - a.S) >= a.pack.cand_cnt(b)) return;
     orow = is_hist ? (long long)a.pack.hist_off[b] + t : a.pack.cand_base + a.pack.cand_off[b] + (t - a.S);
@@ -77,7 +81,7 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
   }
   // lanes 0..H-1 hold the post rows, lanes H..2H-1 the author rows: hashed here, or taken as given
   int my_idx = 0;
-  if (a.pre_hist_post) {
+  if (GENERAL && a.pre_hist_post) {
     if (lane < H) my_idx = (is_hist ? a.pre_hist_post : a.pre_cand_post)[slot * H + lane];
     else if (lane < 2 * H) my_idx = (is_hist ? a.pre_hist_author : a.pre_cand_author)[slot * H + (lane - H)];
   } else {
@@ -89,30 +93,30 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
       my_idx = hash_one(auth_id, a.author.scales[j], a.author.biases[j], a.author);
     }
   }
-  if (a.hashes && lane < 2 * H) a.hashes[tok * (2 * H) + lane] = my_idx;
-  if (a.rows_only) return;   // uniform over the grid: the caller only wants the rows (exchange outside the kernel)
+  if (GENERAL && a.hashes && lane < 2 * H) a.hashes[tok * (2 * H) + lane] = my_idx;
+  if (GENERAL && a.rows_only) return;   // uniform over the grid: the caller only wants the rows (exchange outside the kernel)
   const int first_post_hash = __shfl_sync(0xffffffffu, my_idx, 0);
   if (lane == 0) a.seg[orow] = (first_post_hash != 0) ? (is_hist ? 1 : -1) : 0;
   int act = 0, srf = 0;
   if (is_hist) {
     act = a.hist_actions[(long long)b * a.S + t];
     srf = a.hist_surfaces[(long long)b * a.S + t];
-    if (!a.action_multi_hot) act = act < 0 ? 0 : (act > a.num_action_types ? a.num_action_types : act);
+    if (!(GENERAL && a.action_multi_hot)) act = act < 0 ? 0 : (act > a.num_action_types ? a.num_action_types : act);
     srf = srf < 0 ? 0 : (srf > a.num_surfaces ? a.num_surfaces : srf);
   }
   // every lane takes part in these shuffles (lanes whose column chunk lies past D skip the loop below, so a
   // shuffle inside the loop would leave the warp split across two different shuffle instructions)
   const bf16* rowp[2 * PHX_MAX_HASHES];
   int my_pos = 0;   // exchanged rows: where slot `lane` of this token sits in the landing buffer
-  if (a.landing && lane < 2 * H) my_pos = a.pos[tok * (2 * H) + lane];
+  if (GENERAL && a.landing && lane < 2 * H) my_pos = a.pos[tok * (2 * H) + lane];
 #pragma unroll
   for (int j = 0; j < 2 * PHX_MAX_HASHES; ++j) {
     const int jj = j < 2 * H ? j : 0;
     const int idx = __shfl_sync(0xffffffffu, my_idx, jj);
     const int ps = __shfl_sync(0xffffffffu, my_pos, jj);
-    rowp[j] = a.landing ? a.landing + (long long)ps * a.D : a.table.row_ptr(idx, a.D);
+    rowp[j] = (GENERAL && a.landing) ? a.landing + (long long)ps * a.D : a.table.row_ptr(idx, a.D);
   }
-  if (a.concat_hist) {
+  if (GENERAL && a.concat_hist) {
     // projected tokens: the gathered rows side by side - post rows, author rows, then (history) action and surface
     // rows - as one GEMM operand row (recsys_model.py:2190-2207, 2307-2316); the projection, the scaling and the row
     // statistics follow in their own launches
@@ -123,7 +127,7 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
       for (int j = 0; j < 2 * PHX_MAX_HASHES; ++j)
         if (j < 2 * H) *reinterpret_cast<uint4*>(dst + (long long)j * a.D + col) = __ldg(reinterpret_cast<const uint4*>(rowp[j] + col));
       if (is_hist) {
-        *reinterpret_cast<uint4*>(dst + (long long)(2 * H) * a.D + col) = action_chunk(a, act, col);
+        *reinterpret_cast<uint4*>(dst + (long long)(2 * H) * a.D + col) = action_chunk(a, act, col, GENERAL && a.action_multi_hot);
         *reinterpret_cast<uint4*>(dst + (long long)(2 * H + 1) * a.D + col) =
             __ldg(reinterpret_cast<const uint4*>(a.surface_table + (long long)srf * a.D + col));
       }
@@ -137,15 +141,15 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
     for (int j = 0; j < 2 * PHX_MAX_HASHES; ++j)
       if (j < 2 * H) acc_row(acc, rowp[j], col);
     if (is_hist) {
-      acc_chunk(acc, action_chunk(a, act, col));
+      acc_chunk(acc, action_chunk(a, act, col, GENERAL && a.action_multi_hot));
       acc_row(acc, a.surface_table + (long long)srf * a.D, col);
     }
     uint4 o;
-    if (a.tokens) {
+    if (GENERAL && a.tokens) {
       o.x = pack_bf2(acc[0], acc[1]); o.y = pack_bf2(acc[2], acc[3]); o.z = pack_bf2(acc[4], acc[5]); o.w = pack_bf2(acc[6], acc[7]);
       *reinterpret_cast<uint4*>(a.tokens + tok * a.D + col) = o;
     }
-    if (a.x32) {   // full-precision path: the token is the bf16 sum, its scaled value stays fp32
+    if (GENERAL && a.x32) {   // full-precision path: the token is the bf16 sum, its scaled value stays fp32
       float* dst = a.x32 + orow * a.D + col;
 #pragma unroll
       for (int i = 0; i < 8; ++i) dst[i] = round_bf(acc[i]) * a.input_scale;
@@ -318,7 +322,10 @@ phx_status build_tokens_launch(const TokenBuildArgs& a, cudaStream_t stream, std
   const long long toks = (long long)a.B * (a.S + a.C);
   if (toks == 0) return PHX_OK;
   const int warps = 8;
-  build_tokens_kernel<<<(unsigned)((toks + warps - 1) / warps), warps * 32, 0, stream>>>(a);
+  const bool general = a.pack.hist_off || a.pre_hist_post || a.landing || a.concat_hist || a.action_multi_hot || a.x32 ||
+                       a.tokens || a.hashes || a.rows_only;
+  if (general) build_tokens_kernel<true><<<(unsigned)((toks + warps - 1) / warps), warps * 32, 0, stream>>>(a);
+  else build_tokens_kernel<false><<<(unsigned)((toks + warps - 1) / warps), warps * 32, 0, stream>>>(a);
   PHX_CUDA_TRY(cudaGetLastError(), err);
   return PHX_OK;
 }
