@@ -136,6 +136,8 @@ class Retriever:
         out_s = torch.empty((B, k), dtype=torch.float32, device=dev)
         out_i = torch.empty((B, k), dtype=torch.int64, device=dev)
         self.shards[0].merge_keys_device(keys, P, B, k, out_s, out_i)
+        for sh in self.shards:
+            sh.set_stream(None)     # back to the shard's own stream: the caller's stream may not outlive this call
         return out_s, out_i
 
     def user_vector(self, tower, history):
