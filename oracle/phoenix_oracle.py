@@ -12,11 +12,15 @@ Parity pins (what this restatement has been checked against):
   * elementwise  - RoPE, RMSNorm, qkv split, segment ids, the history/candidate mask: the
                    reference functions executed with NumPy standing in for jax.numpy
                    (fixtures in tests/golden/elementwise_golden.npz);
-  * blend        - the hand-computed known-answer tests of xai-value-model/scoring.rs:498-636
-                   and following.
-  * transformer logits, attention outputs, top-k: PARITY UNPINNED - the reference ships no
-    golden outputs for them and its JAX model cannot be imported without jax/haiku; these
-    follow the cited lines only.
+  * attention    - the reference's own plain candidate-isolation attention (`attention_reference`
+                   with `_apply_cap` and `history_candidate_mask`, pallas/ranker_attention_fa3.py:
+                   1185-1236) executed the same way (fixtures in tests/golden/attention_golden.npz);
+  * value model  - every known-answer test of xai-value-model/scoring.rs:498-896 (weighted scores,
+                   author diversity, out-of-network weight, class factors, cached scores,
+                   pre-offset and multiplicative modes).
+  * transformer logits (the layers around attention taken together) and top-k: PARITY UNPINNED -
+    the reference ships no golden outputs for them and its JAX model cannot be imported without
+    jax/haiku; these follow the cited lines only.
 
 Every function cites the reference file:line it follows (paths relative to the reference
 repository root).
