@@ -240,6 +240,18 @@ phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* batch_de
  * rows were hashed from.  phx_rank_forward_hashed is the same with HOST buffers, blocking like phx_rank_forward. */
 phx_status phx_rank_forward_hashed_device(phx_engine* e, const phx_rank_batch_hashed* batch_dev, const phx_rank_out* out_dev);
 phx_status phx_rank_forward_hashed(phx_engine* e, const phx_rank_batch_hashed* batch_host, const phx_rank_out* out_host);
+/* Packed rows for callers whose batches already sit on the device (pack_ragged engines).  phx_plan_ragged is the
+ * host-side count phx_rank_forward does itself: for B requests of S history and C candidate slots (int64 post ids,
+ * 0 = padding) it writes the exclusive prefix sums hist_off / cand_off (B + 1 entries each) of every request's leading
+ * non-padding slots - at least one history row per request, all slots for every request when some request has
+ * padding in front of a valid slot; it touches no GPU.  phx_rank_forward_packed_device runs the forward over those rows:
+ * the two offset arrays in DEVICE memory, hist_rows = hist_off[B], cand_rows = cand_off[B]; outputs keep their [B, C]
+ * shape, padded slots read zero.  The role of the reference's packed serving layout (sequence_packing.py:317). */
+phx_status phx_plan_ragged(const int64_t* hist_post_ids, const int64_t* cand_post_ids, int32_t B, int32_t S, int32_t C,
+                           int32_t* hist_off, int32_t* cand_off);
+phx_status phx_rank_forward_packed_device(phx_engine* e, const phx_rank_batch* batch_dev, const int32_t* hist_off_dev,
+                                          const int32_t* cand_off_dev, int64_t hist_rows, int64_t cand_rows,
+                                          const phx_rank_out* out_dev);
 /* Build the tokens (hash -> gather-sum) of the batch that the NEXT phx_rank_forward_device call will carry, on a
  * side stream, so that the gather - which waits on other GPUs' memory when the table is row-sharded - overlaps the
  * forward that is already enqueued.  Call order per step: forward(batch i), then prefetch(batch i+1).  The next

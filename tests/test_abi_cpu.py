@@ -204,3 +204,16 @@ def test_value_scores_argument_errors_are_statuses():
     assert call(inp, out) == 1 and b"out of range" in _lib.lib.phx_global_error()
     inp.batch = -1
     assert call(inp, out) == 1
+
+
+def test_plan_ragged_offsets():
+    """The host-side plan of packed rows: leading non-padding slots per request, one history row kept for a request
+    without history, every slot for the whole batch as soon as one request has padding in front of a valid slot."""
+    from x_algorithm_b200.engine import plan_ragged
+    hp = np.array([[5, 6, 7, 0], [0, 0, 0, 0], [1, 2, 3, 4]], np.int64)
+    cp = np.array([[9, 0, 0], [8, 8, 8], [0, 0, 0]], np.int64)
+    ho, co = plan_ragged(hp, cp)
+    assert ho.tolist() == [0, 3, 4, 8] and co.tolist() == [0, 1, 4, 4]
+    cp[0] = [0, 9, 0]                                   # a hole: the batch is planned over all its slots
+    ho, co = plan_ragged(hp, cp)
+    assert ho.tolist() == [0, 4, 8, 12] and co.tolist() == [0, 3, 6, 9]

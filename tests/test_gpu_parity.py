@@ -369,6 +369,15 @@ def test_packed_ragged_batches_match_unpacked(torch, monkeypatch, opts, attn):
     np.testing.assert_array_equal(r0.log_probs[valid], want.log_probs[valid])
     np.testing.assert_array_equal(r1.log_probs, plain.rank(to_inputs(full)).log_probs)
     assert (r0.log_probs[~valid] == 0).all()
+    # device-resident batch with a plan made on the host (phx_plan_ragged + phx_rank_forward_packed_device)
+    from x_algorithm_b200.engine import plan_ragged
+    ho, co = plan_ragged(b.hist_post_ids, b.cand_post_ids)
+    dev = _device_batch(torch, b)
+    out = _device_out(torch, packed.cfg, 6)
+    packed.rank_packed_device(6, *dev, torch.from_numpy(ho).cuda(), torch.from_numpy(co).cuda(), int(ho[-1]), int(co[-1]), *out[:2])
+    packed.sync()
+    np.testing.assert_array_equal(out[0].cpu().numpy()[valid], want.log_probs[valid])
+    assert (out[0].cpu().numpy()[~valid] == 0).all()
     # the device-pointer entry point of the packing engine runs every slot
     dev = _device_batch(torch, b)
     out = _device_out(torch, packed.cfg, 6)

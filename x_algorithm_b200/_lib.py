@@ -90,6 +90,8 @@ SIGNATURES = {
     "phx_rank_collect": (C.c_int32, [_P, C.c_int32, C.POINTER(RankOut)]),
     "phx_rank_forward_device": (C.c_int32, [_P, C.POINTER(RankBatch), C.POINTER(RankOut)]),
     "phx_value_scores_device": (C.c_int32, [C.c_int32, C.POINTER(ValueModel), C.POINTER(ValueInputs), _P, _P, _P]),
+    "phx_plan_ragged": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, C.c_int32, _P, _P]),
+    "phx_rank_forward_packed_device": (C.c_int32, [_P, C.POINTER(RankBatch), _P, _P, C.c_int64, C.c_int64, C.POINTER(RankOut)]),
     "phx_rank_forward_hashed_device": (C.c_int32, [_P, C.POINTER(RankBatchHashed), C.POINTER(RankOut)]),
     "phx_rank_forward_hashed": (C.c_int32, [_P, C.POINTER(RankBatchHashed), C.POINTER(RankOut)]),
     "phx_rank_prefetch_device": (C.c_int32, [_P, C.POINTER(RankBatch)]),

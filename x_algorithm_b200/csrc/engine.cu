@@ -91,6 +91,7 @@ struct phx_engine {
   // host-buffer call found in its batch
   bool pack = false;
   PackState pack_full, pack_ragged;
+  PackState pack_device;            // plan handed over by phx_rank_forward_packed_device (offsets in the caller's memory)
   PackState* pack_next = nullptr;   // set by the host-buffer call for the forward it is about to enqueue
   PackState* cur_pack = nullptr;    // the forward being enqueued
   std::vector<int> pack_host;       // host copy of the offsets of the ragged plan
@@ -1020,7 +1021,64 @@ phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* bd, cons
   return PHX_OK;
 }
 
-// Row-sharded table with the exchange done by the host side (parallel.ShardedRanker): first the unified-table rows
+namespace {
+// Packed rows: the leading non-padding slots of every request (id 0 = padding) as exclusive prefix sums ho / co with
+// B + 1 entries.  A batch with padding in front of a valid slot is planned over all its slots.  A request keeps at
+// least one history row (a padded one when it has none), so every request has a key block.
+void plan_ragged(const phx_rank_batch* bh, size_t B, size_t S, size_t C, int* ho, int* co) {
+  bool front_filled = true;
+  ho[0] = co[0] = 0;
+  for (size_t b = 0; b < B && front_filled; ++b) {
+    const int64_t* hpid = bh->hist_post_ids + b * S;
+    const int64_t* cpid = bh->cand_post_ids + b * C;
+    size_t hc = 0, cc = 0;
+    while (hc < S && hpid[hc] != 0) ++hc;
+    while (cc < C && cpid[cc] != 0) ++cc;
+    for (size_t t = hc; t < S; ++t) if (hpid[t] != 0) front_filled = false;
+    for (size_t c = cc; c < C; ++c) if (cpid[c] != 0) front_filled = false;
+    ho[b + 1] = ho[b] + (int)(hc > 0 ? hc : 1);
+    co[b + 1] = co[b] + (int)cc;
+  }
+  if (!front_filled)
+    for (size_t b = 0; b < B; ++b) { ho[b + 1] = (int)((b + 1) * S); co[b + 1] = (int)((b + 1) * C); }
+}
+
+}  // namespace
+
+phx_status phx_plan_ragged(const int64_t* hist_post_ids, const int64_t* cand_post_ids, int32_t B, int32_t S, int32_t C,
+                           int32_t* hist_off, int32_t* cand_off) {
+  if (!hist_post_ids || !cand_post_ids || !hist_off || !cand_off || B < 0 || S <= 0 || C <= 0) {
+    set_global_error("phx_plan_ragged: bad argument");
+    return PHX_E_ARG;
+  }
+  phx_rank_batch b;
+  memset(&b, 0, sizeof(b));
+  b.batch = B; b.hist_post_ids = hist_post_ids; b.cand_post_ids = cand_post_ids;
+  plan_ragged(&b, (size_t)B, (size_t)S, (size_t)C, hist_off, cand_off);
+  return PHX_OK;
+}
+
+phx_status phx_rank_forward_packed_device(phx_engine* e, const phx_rank_batch* bd, const int32_t* hist_off_dev,
+                                          const int32_t* cand_off_dev, int64_t hist_rows, int64_t cand_rows,
+                                          const phx_rank_out* od) {
+  if (!e || !bd || !od || !hist_off_dev || !cand_off_dev) return PHX_E_ARG;
+  if (!e->pack) { e->err = "phx_rank_forward_packed_device: the engine was created without pack_ragged"; return PHX_E_ARG; }
+  const long long B = bd->batch;
+  if (B <= 0 || B > e->cfg.max_batch) { e->err = "batch must be 1..max_batch"; return PHX_E_CAPACITY; }
+  if (hist_rows < B || hist_rows > B * e->S || cand_rows < 0 || cand_rows > B * e->C) {
+    e->err = "phx_rank_forward_packed_device: row totals do not fit the batch (every request keeps at least one history row)";
+    return PHX_E_ARG;
+  }
+  phx_engine::PackState& pk = e->pack_device;
+  pk.hist_off_view = hist_off_dev; pk.cand_off_view = cand_off_dev;
+  pk.pos_rows = e->pack_ragged.pos_rows; pk.out_index = e->pack_ragged.out_index;
+  pk.Mh = hist_rows; pk.M = hist_rows + cand_rows;
+  pk.ragged = true;
+  e->pack_next = &pk;
+  return phx_rank_forward_device(e, bd, od);
+}
+
+// Row-sharded table with the exchange done by the host side (parallel.ShardedRanker)// Row-sharded table with the exchange done by the host side (parallel.ShardedRanker): first the unified-table rows
 // of every token slot, then, once their rows sit in a landing buffer, the forward from there.
 phx_status phx_rank_rows_device(phx_engine* e, const phx_rank_batch* bd, int32_t* rows_dev, void* stream) {
   if (!e || !bd || !rows_dev) return PHX_E_ARG;
@@ -1136,30 +1194,6 @@ phx_status phx_rank_prefetch_device(phx_engine* e, const phx_rank_batch* bd) {
   e->prefetch_valid = true;
   return PHX_OK;
 }
-
-namespace {
-// Packed rows: the leading non-padding slots of every request (id 0 = padding) as exclusive prefix sums ho / co with
-// B + 1 entries.  A batch with padding in front of a valid slot is planned over all its slots.  A request keeps at
-// least one history row (a padded one when it has none), so every request has a key block.
-void plan_ragged(const phx_rank_batch* bh, size_t B, size_t S, size_t C, int* ho, int* co) {
-  bool front_filled = true;
-  ho[0] = co[0] = 0;
-  for (size_t b = 0; b < B && front_filled; ++b) {
-    const int64_t* hpid = bh->hist_post_ids + b * S;
-    const int64_t* cpid = bh->cand_post_ids + b * C;
-    size_t hc = 0, cc = 0;
-    while (hc < S && hpid[hc] != 0) ++hc;
-    while (cc < C && cpid[cc] != 0) ++cc;
-    for (size_t t = hc; t < S; ++t) if (hpid[t] != 0) front_filled = false;
-    for (size_t c = cc; c < C; ++c) if (cpid[c] != 0) front_filled = false;
-    ho[b + 1] = ho[b] + (int)(hc > 0 ? hc : 1);
-    co[b + 1] = co[b] + (int)cc;
-  }
-  if (!front_filled)
-    for (size_t b = 0; b < B; ++b) { ho[b + 1] = (int)((b + 1) * S); co[b + 1] = (int)((b + 1) * C); }
-}
-
-}  // namespace
 
 phx_status phx_rank_forward(phx_engine* e, const phx_rank_batch* bh, const phx_rank_out* oh) {
   if (!e || !bh || !oh) return PHX_E_ARG;

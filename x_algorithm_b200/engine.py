@@ -200,6 +200,14 @@ class PhoenixEngine:
         o = _lib.RankOut(_ptr(lp), _ptr(cont), _ptr(sc))
         self._check(lib.phx_rank_forward_device(self._h, C.byref(b), C.byref(o)))
 
+    def rank_packed_device(self, B, hp, ha, act, srf, cp, ca, hist_off, cand_off, hist_rows: int, cand_rows: int, lp, cont, sc=None):
+        """rank_device over the valid rows only (pack_ragged engines): hist_off / cand_off are int32 CUDA tensors
+        [B + 1] as `plan_ragged` makes them, hist_rows / cand_rows their last entries."""
+        b = self._batch_struct(B, hp, ha, act, srf, cp, ca)
+        o = _lib.RankOut(_ptr(lp), _ptr(cont), _ptr(sc))
+        self._check(lib.phx_rank_forward_packed_device(self._h, C.byref(b), _ptr(hist_off), _ptr(cand_off), hist_rows,
+                                                       cand_rows, C.byref(o)))
+
     def rank_rows_device(self, B, hp, ha, act, srf, cp, ca, rows, stream=None):
         """Unified-table rows of every token slot of the batch (int32 [B, S+C, 2*num_hashes]) -> `rows`; the first
         half of a forward whose rows are exchanged between ranks (parallel.ShardedRanker)."""
@@ -298,3 +306,17 @@ def gemm(a, wt, residual=None, epilogue: int = 0, impl: int = 0, device: int = 0
     if st != 0:
         raise PhoenixError(st, lib.phx_global_error().decode())
     return c, float(ms.value)
+
+
+def plan_ragged(hist_post_ids: np.ndarray, cand_post_ids: np.ndarray):
+    """Offsets of the packed rows of a batch (host arrays int64 [B,S] / [B,C], 0 = padding): exclusive prefix sums
+    (hist_off, cand_off), int32 [B + 1] each, of every request's leading non-padding slots; at least one history row
+    per request; all slots when a request has padding in front of a valid slot.  No GPU involved."""
+    hp = np.ascontiguousarray(hist_post_ids, np.int64)
+    cp = np.ascontiguousarray(cand_post_ids, np.int64)
+    B, S = hp.shape
+    ho = np.zeros(B + 1, np.int32); co = np.zeros(B + 1, np.int32)
+    st = lib.phx_plan_ragged(hp.ctypes.data, cp.ctypes.data, B, S, cp.shape[1], ho.ctypes.data, co.ctypes.data)
+    if st != 0:
+        raise PhoenixError(st, lib.phx_global_error().decode())
+    return ho, co
