@@ -217,3 +217,41 @@ def test_plan_ragged_offsets():
     cp[0] = [0, 9, 0]                                   # a hole: the batch is planned over all its slots
     ho, co = plan_ragged(hp, cp)
     assert ho.tolist() == [0, 4, 8, 12] and co.tolist() == [0, 3, 6, 9]
+
+
+def test_pipeline_stages_order_and_error_handling():
+    """score_stage / fetch_stage keep the pipeline's rules (candidate_pipeline.rs:306-327, 497-508): disabled
+    components are skipped, scorers see the updates of the scorers before them, a scorer's failed candidates keep
+    their old values, failed and disabled sources contribute nothing."""
+    import x_algorithm_b200 as px
+    from x_algorithm_b200.plugin import Scorer, Source, score_stage, fetch_stage
+
+    class AddOne(Scorer):
+        def score(self, q, cands):
+            return [px.Candidate(score=(c.score or 0.0) + 1.0) if c.post_id != 13 else "boom" for c in cands]
+        def update(self, c, s):
+            c.score = s.score
+
+    class Double(AddOne):
+        def score(self, q, cands):
+            return [px.Candidate(score=(c.score or 0.0) * 2.0) for c in cands]
+
+    class Off(AddOne):
+        def enable(self, q):
+            return False
+
+    cands = [px.Candidate(post_id=1, score=1.0), px.Candidate(post_id=13, score=5.0)]
+    score_stage(px.Query(), cands, [AddOne(), Off(), Double()])
+    assert [c.score for c in cands] == [4.0, 10.0]          # (1 + 1) * 2; the failed one skipped AddOne only
+
+    class Src(Source):
+        def __init__(self, out, on=True):
+            self.out, self.on = out, on
+        def enable(self, q):
+            return self.on
+        def source(self, q):
+            return self.out
+
+    got = fetch_stage(px.Query(), [Src([px.Candidate(post_id=1)]), Src("PhoenixSource: down"), Src([]),
+                                   Src([px.Candidate(post_id=9)], on=False), Src([px.Candidate(post_id=2)])])
+    assert [c.post_id for c in got] == [1, 2]

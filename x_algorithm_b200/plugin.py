@@ -83,6 +83,30 @@ class Scorer:
                 self.update(c, s)
 
 
+def score_stage(query: Query, candidates: List[Candidate], scorers: Sequence[Scorer]) -> List[Candidate]:
+    """The scorer stage of the pipeline (candidate-pipeline/candidate_pipeline.rs:497-508): the enabled scorers one
+    after another over the same candidates, each one's successful results applied before the next runs - e.g.
+    [PhoenixScorer, ValueModelScorer]: probabilities first, then the value model on them."""
+    for scorer in scorers:
+        if not scorer.enable(query):
+            continue
+        scorer.update_all(candidates, scorer.run(query, candidates))
+    return candidates
+
+
+def fetch_stage(query: Query, sources: Sequence["Source"]) -> List[Candidate]:
+    """The source stage (candidate_pipeline.rs:306-327): every enabled source, failed ones (an error string) and empty
+    ones dropped, the rest concatenated in source order."""
+    out: List[Candidate] = []
+    for src in sources:
+        if not src.enable(query):
+            continue
+        got = src.run(query)
+        if not isinstance(got, str):
+            out.extend(got)
+    return out
+
+
 class PhoenixScorer(Scorer):
     """Ranks one request's candidates in chunks of the engine's candidate capacity.  Fills
     `phoenix_scores` (probabilities = exp(ln p), the client-side conversion of
