@@ -255,3 +255,42 @@ def test_pipeline_stages_order_and_error_handling():
     got = fetch_stage(px.Query(), [Src([px.Candidate(post_id=1)]), Src("PhoenixSource: down"), Src([]),
                                    Src([px.Candidate(post_id=9)], on=False), Src([px.Candidate(post_id=2)])])
     assert [c.post_id for c in got] == [1, 2]
+
+
+def test_header_compiles_as_c_and_matches_the_ctypes_structs(tmp_path):
+    """include/phoenix_b200.h is plain C (what a cgo / FFI binding would include): a probe compiled with gcc prints the
+    size of every struct and the offsets of marker fields, and they equal the ctypes mirrors of x_algorithm_b200/_lib.py."""
+    import shutil
+    import subprocess
+    from x_algorithm_b200 import _lib
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    probes = [("phx_hash_family", _lib.HashFamily, ["num_hashes"]),
+              ("phx_model_config", _lib.ModelConfig, ["user", "ip", "table_world", "num_candidate_only_layers", "compute_fp32",
+                                                      "token_project", "pack_ragged", "action_multi_hot"]),
+              ("phx_blend_spec", _lib.BlendSpec, ["src", "weight", "total_sum"]),
+              ("phx_rank_batch", _lib.RankBatch, ["hist_post_ids", "cand_author_ids"]),
+              ("phx_rank_out", _lib.RankOut, ["scores"]),
+              ("phx_value_model", _lib.ValueModel, ["w", "reply_boost", "offset_total_sum", "post_unexplored_include_oon", "multiplicative"]),
+              ("phx_value_inputs", _lib.ValueInputs, ["log_probs", "author_ids", "context"])]
+    lines = []
+    for cname, _, fields in probes:
+        lines.append(f'printf("{cname} %zu", sizeof({cname}));')
+        for f in fields:
+            lines.append(f'printf(" %zu", offsetof({cname}, {f}));')
+        lines.append('printf("\\n");')
+    src = tmp_path / "probe.c"
+    src.write_text("#include <stdio.h>\n#include <stddef.h>\n#include \"phoenix_b200.h\"\nint main(void) {\n" + "\n".join(lines) +
+                   "\nprintf(\"hashed %zu\\n\", sizeof(phx_rank_batch_hashed));\nreturn 0; }\n")
+    exe = tmp_path / "probe"
+    subprocess.run([gcc, "-std=c11", "-Wall", "-Werror", "-I", os.path.join(root, "include"), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.strip().splitlines()
+    for (cname, ct, fields), line in zip(probes, out):
+        got = line.split()
+        assert got[0] == cname
+        assert int(got[1]) == C.sizeof(ct), cname
+        for f, off in zip(fields, got[2:]):
+            assert int(off) == getattr(ct, f).offset, (cname, f)
+    assert out[-1] == f"hashed {C.sizeof(_lib.RankBatchHashed)}"
