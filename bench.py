@@ -83,23 +83,26 @@ class ClockSampler(threading.Thread):
                     reasons=sorted(self.reasons))
 
 
-def cpu_oracle_rate(n_requests: int, repeats: int = 1):
-    """candidates/s of the NumPy oracle (bf16-emulating path) on `n_requests` requests of the workload."""
+def cpu_oracle_rate(n_requests: int, repeats: int = 1, workload=None, batch=None):
+    """candidates/s of the NumPy oracle (bf16-emulating path) on `n_requests` requests of the workload (or on the
+    requests of `batch`), and the oracle's outputs for them: (rate, seconds, (log_probs, continuous, logits, scores))."""
     from oracle import phoenix_oracle as po
-    ocfg = po.ModelConfig(**WORKLOAD, compute="bf16")
+    ocfg = po.ModelConfig(**(workload or WORKLOAD), compute="bf16")
     w = po.make_weights(ocfg, WEIGHT_SEED)
     amp = 1.0 / math.sqrt(ocfg.emb_size)
     rows_fn = lambda idx: po.synthetic_table_rows(idx, ocfg.emb_size, TABLE_SEED, amp)
     spec = po.blend_spec_from_weights(po.make_blend_weights(BLEND_SEED), po.HEAD_NAMES_19, ocfg.num_actions)
-    b = po.make_batch(ocfg, n_requests, seed=ID_SEED, zipf_s=1.1)
-    best = None
+    b = batch if batch is not None else po.make_batch(ocfg, n_requests, seed=ID_SEED, zipf_s=1.1)
+    n_requests = b.cand_post_ids.shape[0]
+    best, outs = None, None
     for _ in range(repeats):
         t0 = time.perf_counter()
-        lp, cont, _ = po.rank_forward(ocfg, w, rows_fn, b)
-        po.blend_scores(spec, lp, cont)
+        lp, cont, logits = po.rank_forward(ocfg, w, rows_fn, b)
+        sc = po.blend_scores(spec, lp, cont)
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
-    return n_requests * ocfg.num_candidates / best, best
+        outs = (lp, cont, logits, sc)
+    return n_requests * ocfg.num_candidates / best, best, outs
 
 
 def run_reference(args, rank: int):
@@ -109,7 +112,7 @@ def run_reference(args, rank: int):
     n_req = 2
     times = []
     for i in range(args.warmup + args.steps):
-        rate, dt = cpu_oracle_rate(n_req)
+        rate, dt, _ = cpu_oracle_rate(n_req)
         if i >= args.warmup:
             times.append(dt)
     ms = 1e3 * float(np.mean(times))
@@ -153,7 +156,7 @@ def main():
     import torch
     import torch.distributed as dist
     import x_algorithm_b200 as px
-    from oracle import phoenix_oracle as po  # checker + cpu_baseline leg only
+    from x_algorithm_b200 import synthetic
 
     torch.cuda.set_device(local_rank)
     if world > 1:
@@ -168,18 +171,17 @@ def main():
     exchange = sharded and args.tables == "exchange"
     cfg = px.PhoenixConfig(max_batch=B, table_world=world if sharded else 1, table_rank=rank if sharded else 0, **wl)
     eng = px.PhoenixEngine(cfg, local_rank)
-    ocfg = po.ModelConfig(**wl)
-    eng.load_weights(po.make_weights(ocfg, WEIGHT_SEED))
+    eng.load_weights(synthetic.make_weights(cfg, WEIGHT_SEED))
     eng.table_fill_synthetic(TABLE_SEED, 1.0 / math.sqrt(cfg.emb_size))
     if sharded:
         from x_algorithm_b200.parallel import attach_table_shards
         attach_table_shards(eng)
-    bw = po.make_blend_weights(BLEND_SEED)
-    eng.set_blend(px.blend_spec_from_weights(px.ValueModelWeights(w=dict(bw.w)), px.HEAD_NAMES_19, cfg.num_actions))
+    bw = synthetic.make_blend_weights(px.HEAD_NAMES_19, BLEND_SEED)
+    eng.set_blend(px.blend_spec_from_weights(px.ValueModelWeights(w=bw), px.HEAD_NAMES_19, cfg.num_actions))
 
     # synthetic requests: Zipf(1.1) ids over 2^40, a different batch per rank; 4 batches rotated
     n_rot = 4
-    batches = [po.make_batch(ocfg, B, seed=ID_SEED + 1000 * rank + i, zipf_s=1.1) for i in range(n_rot)]
+    batches = [synthetic.make_batch(cfg, B, seed=ID_SEED + 1000 * rank + i, zipf_s=1.1) for i in range(n_rot)]
     dev = torch.device("cuda", local_rank)
     dbatches = [[torch.from_numpy(np.ascontiguousarray(a)).to(dev) for a in
                  (b.hist_post_ids, b.hist_author_ids, b.hist_actions, b.hist_surfaces, b.cand_post_ids, b.cand_author_ids)]
@@ -284,7 +286,8 @@ def main():
     sampler.stop_flag = True
     sampler.join(timeout=2)
 
-    # sanity: the last batch against the oracle on a couple of requests (checker, outside the timed region)
+    # the engine's answer for batch 0 through the host-buffer call, kept for the parity check below
+    check_out = eng.rank(host_in[0], None)
     t = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -327,10 +330,29 @@ def main():
         if xphase is not None:
             line["exchange_phase_ms"] = xphase
         if not args.no_cpu_baseline:
+            # The CPU oracle on the first and the last request of batch 0 (outside every timed region): its time is the
+            # CPU baseline, its logits are the checker for what the engine returned for the same two requests.
+            from oracle import phoenix_oracle as po
             cores = len(os.sched_getaffinity(0))
-            rate, dt = cpu_oracle_rate(2)
+            pick = [0, B - 1]
+            b0 = batches[0]
+            sub = po.RankBatch(*[np.ascontiguousarray(getattr(b0, f)[pick]) for f in
+                                 ("hist_post_ids", "hist_author_ids", "hist_actions", "hist_surfaces", "cand_post_ids", "cand_author_ids")])
+            rate, dt, (o_lp, o_cont, o_logits, o_sc) = cpu_oracle_rate(len(pick), workload=wl, batch=sub)
             line["cpu_baseline"] = dict(value=rate, unit="candidates/s", cores=cores, kind="port",
-                                        sample=f"2 requests x 512 candidates, one pass of the NumPy oracle ({dt:.1f} s)")
+                                        sample=f"{len(pick)} requests x {C} candidates, one pass of the NumPy oracle ({dt:.1f} s)")
+            g_lp = np.minimum(check_out.log_probs[pick].astype(np.float64), -1e-12)
+            g_logits = g_lp - np.log(-np.expm1(g_lp))
+            o_logits = o_logits.astype(np.float64)
+            dev_c = o_cont.astype(np.float64) - o_cont.astype(np.float64).mean()
+            line["parity_check"] = dict(
+                requests=pick, against="CPU oracle (bf16-emulating NumPy restatement), same seeded inputs",
+                rel_l2_logits=float(np.linalg.norm(g_logits - o_logits) / np.linalg.norm(o_logits)),
+                max_abs_logit_err=float(np.abs(g_logits - o_logits).max()), rms_logits=float(np.sqrt(np.mean(o_logits ** 2))),
+                rel_l2_continuous_mean_removed=float(np.linalg.norm(check_out.continuous[pick] - o_cont) / np.linalg.norm(dev_c)),
+                rel_l2_scores=float(np.linalg.norm(check_out.scores[pick] - o_sc) / np.linalg.norm(o_sc)),
+                tolerance=2e-2)
+            line["parity_check"]["ok"] = bool(line["parity_check"]["rel_l2_logits"] < 2e-2)
         print(json.dumps(line), flush=True)
     if ranker is not None:
         ranker.close()

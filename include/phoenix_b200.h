@@ -260,6 +260,24 @@ phx_status phx_rank_forward_packed_device(phx_engine* e, const phx_rank_batch* b
  * (phoenix/xrex/cuda/row_emb/src/row_emb_comm.hpp:228). */
 phx_status phx_rank_prefetch_device(phx_engine* e, const phx_rank_batch* batch_dev);
 phx_status phx_sync(phx_engine* e);
+/* Failure detection on the device.  Every wait inside the tcgen05 kernels (on an mbarrier that a TMA copy, an MMA
+ * commit or another warp role signals) is bounded: when the limit passes, the waiting thread raises the engine's error
+ * flag, every role drains, the kernel returns, and the next blocking call (phx_rank_forward, phx_rank_collect, phx_sync)
+ * reports PHX_E_TIMEOUT once and clears the flag; the context stays usable.  phx_set_wait_limit_us sets the limit
+ * (microseconds; 0 = the default of 2 s; synchronises the engine's stream).  phx_wait_selftest launches a one-thread
+ * kernel that waits on a barrier nothing signals and returns what phx_sync returns after it: PHX_E_TIMEOUT after
+ * about one limit when the mechanism works.  The reference leaves hangs to its serving shell (per-request deadlines,
+ * xai-recsys-engine/src/request_queue.rs:10-27); a kernel of its own that waits for ever holds the GPU. */
+phx_status phx_set_wait_limit_us(phx_engine* e, uint32_t microseconds);
+phx_status phx_wait_selftest(phx_engine* e);
+/* Which kernel variants the library's launches took, counted over the life of the process: out[i] for i < n receives the
+ * count of variant i, the return value is the number of variants; phx_dispatch_name(i) names them ("attn.strip",
+ * "attn.stream", "attn.tcgen05", "attn.resident", "gemm.pair256", "gemm.pair128", "gemm.cta256", "gemm.cta128",
+ * "gemm.simt", "scan.tcgen05", "scan.mma", "topk.exact").  A forward replayed from its CUDA graph counts nothing.  Lets a
+ * test or a monitor assert that a workload runs on the kernels meant for it.  The reference's counterpart is its
+ * attention-implementation switch being logged at start-up (phoenix/xrex/models/recsys_attention.py:18-242). */
+int32_t phx_dispatch_counts(int64_t* out, int32_t n);
+const char* phx_dispatch_name(int32_t kind);
 /* Time of the last phx_rank_forward_device / phx_user_tower_device call on the engine's stream,
  * measured with CUDA events (milliseconds). */
 phx_status phx_last_device_ms(phx_engine* e, float* ms);
@@ -331,15 +349,6 @@ phx_status phx_ipc_open(int32_t device, const uint8_t handle[PHX_IPC_HANDLE_BYTE
 phx_status phx_ipc_close(void* ptr);
 phx_status phx_ipc_free(void* ptr);
 
-/* Diagnostic: the two resources the GEMM main loop lives on, measured apart and together.  148 CTAs (pair != 0: 74
- * CTA pairs, tcgen05 cta_group::2) issue the GEMM's MMAs over fixed shared-memory tiles for `ksteps` k-steps (a
- * multiple of 8); fill_tiles_per_kstep (0..3) 16 KB TMA tiles per k-step and CTA are streamed beside them without
- * synchronisation; sync_mode 0 = one commit per 8 k-steps, 1 = one per k-step, 2 = one per k-step plus a wait on the
- * commit of four k-steps earlier.  Out: kernel time, the MMA issuer's cycles per k-step (512 = the pipe's full rate),
- * the fill thread's cycles per k-step.  No counterpart in the reference. */
-phx_status phx_diag_mma_rate(int32_t device, int32_t pair, int32_t ksteps, int32_t fill_tiles_per_kstep, int32_t sync_mode,
-                             float* ms_out, double* mma_cycles_per_kstep, double* fill_cycles_per_kstep);
-
 /* ---- stand-alone operators (micro-benchmarks and parity tests of single kernels) ------------- */
 
 /* Multi-hash id -> unified-table rows; `family`: 0 user, 1 item, 2 author, 3 ip.
@@ -375,6 +384,10 @@ phx_status phx_corpus_create(int32_t device, int64_t rows, int32_t dim, int64_t 
                              int32_t max_k, phx_corpus** out);
 void phx_corpus_destroy(phx_corpus* c);
 phx_status phx_corpus_upload(phx_corpus* c, int64_t row0, int64_t nrows, const uint16_t* host_bf16);
+/* Copy shard rows [row0, row0 + nrows) (bf16 bit patterns) into a device buffer of the shard's device; returns when
+ * the copy is done.  What an index refresh reads back to verify an upload (the reference rebuilds its post table from
+ * phoenix-rankall/ snapshots). */
+phx_status phx_corpus_read_device(phx_corpus* c, int64_t row0, int64_t nrows, uint16_t* out_dev);
 /* Synthetic L2-normalised rows, a pure function of (global row, seed). */
 phx_status phx_corpus_fill_synthetic(phx_corpus* c, uint32_t seed);
 /* Exhaustive dot-product top-k of this shard: users f32 [B,dim] (rounded to bf16 as the reference
@@ -410,7 +423,9 @@ phx_status phx_corpus_set_mask(phx_corpus* c, const uint32_t* host_bits);
 phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, int32_t B, int32_t k, int64_t row_begin,
                                          int64_t row_end, float* scores_dev, int64_t* ids_dev);
 /* Merge P per-shard lists laid out [P,B,k] into [B,k] by (score desc, id asc)
- * (strided_dataset_top_k, recsys_two_tower_model.py:215-220). */
+ * (strided_dataset_top_k, recsys_two_tower_model.py:215-220).  Ids must be below 2^32; a negative id marks an empty
+ * slot (sorted last, returned as score -inf, id -1 when the lists hold fewer than k entries); an entry with a larger
+ * id is left out and the next phx_corpus_sync reports PHX_E_ARG. */
 phx_status phx_topk_merge_device(phx_corpus* c, const float* scores_dev, const int64_t* ids_dev, int32_t P,
                                  int32_t B, int32_t k, float* out_scores_dev, int64_t* out_ids_dev);
 /* The same merge for callers that must not allocate device memory.  (No counterpart in the reference.)
@@ -428,9 +443,14 @@ phx_status phx_topk_merge_device(phx_corpus* c, const float* scores_dev, const i
  *     what must start at zero itself, but two calls whose kernels overlap on the GPU (different
  *     streams, no ordering between them) race on it; order them;
  *   - asynchronous on `stream` (a cudaStream_t, NULL = the default stream); inputs and outputs are the
- *     caller's device buffers, laid out as for phx_topk_merge_device. */
+ *     caller's device buffers, laid out as for phx_topk_merge_device;
+ *   - ids must be below 2^32 (negative = empty slot): an entry with a larger id is left out of the merge and
+ *     bit 2 of the status word is raised.  phx_topk_merge_static_status waits for `stream`, copies that word
+ *     to the host (a 4-byte copy, no allocation) and returns it in *status_out: 0 = every entry was merged;
+ *   - the calling thread's current device is the same after the call as before it. */
 phx_status phx_topk_merge_static(int32_t device, const float* scores_dev, const int64_t* ids_dev, int32_t P,
                                  int32_t B, int32_t k, float* out_scores_dev, int64_t* out_ids_dev, void* stream);
+phx_status phx_topk_merge_static_status(int32_t device, void* stream, int32_t* status_out);
 phx_status phx_corpus_sync(phx_corpus* c);
 phx_status phx_corpus_last_device_ms(phx_corpus* c, float* ms);
 const char* phx_corpus_last_error(const phx_corpus* c);

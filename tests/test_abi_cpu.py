@@ -294,3 +294,25 @@ def test_header_compiles_as_c_and_matches_the_ctypes_structs(tmp_path):
         for f, off in zip(fields, got[2:]):
             assert int(off) == getattr(ct, f).offset, (cname, f)
     assert out[-1] == f"hashed {C.sizeof(_lib.RankBatchHashed)}"
+
+
+def test_package_synthetic_generators_equal_the_oracles():
+    """Benchmarks draw weights, batches and blend weights from the package's own generators; parity tests draw them
+    from the oracle's.  Same seed -> same arrays, so that a benchmark's parity check compares like with like."""
+    import dataclasses
+    import x_algorithm_b200 as px
+    from x_algorithm_b200 import synthetic
+    from oracle import phoenix_oracle as po
+    for kw in (dict(), dict(qk_norm=True, primer_norm=True, emb_size=256, num_q_heads=4, num_kv_heads=2, key_size=64),
+               dict(token_combine="project", action_multi_hot=True)):
+        ocfg = po.ModelConfig(**kw)
+        pcfg = px.PhoenixConfig(**kw)
+        wo, wp = po.make_weights(ocfg, 3), synthetic.make_weights(pcfg, 3)
+        assert list(wo) == list(wp)
+        for k in wo:
+            np.testing.assert_array_equal(wo[k], wp[k], err_msg=k)
+        for zs, ragged in ((None, False), (1.1, True)):
+            bo, bp = po.make_batch(ocfg, 5, seed=9, zipf_s=zs, ragged=ragged), synthetic.make_batch(pcfg, 5, seed=9, zipf_s=zs, ragged=ragged)
+            for f in dataclasses.fields(bo):
+                np.testing.assert_array_equal(getattr(bo, f.name), getattr(bp, f.name), err_msg=f.name)
+    assert synthetic.make_blend_weights(px.HEAD_NAMES_19, 1) == dict(po.make_blend_weights(1).w)

@@ -96,6 +96,10 @@ SIGNATURES = {
     "phx_rank_forward_hashed": (C.c_int32, [_P, C.POINTER(RankBatchHashed), C.POINTER(RankOut)]),
     "phx_rank_prefetch_device": (C.c_int32, [_P, C.POINTER(RankBatch)]),
     "phx_sync": (C.c_int32, [_P]),
+    "phx_set_wait_limit_us": (C.c_int32, [_P, C.c_uint32]),
+    "phx_wait_selftest": (C.c_int32, [_P]),
+    "phx_dispatch_counts": (C.c_int32, [_P, C.c_int32]),
+    "phx_dispatch_name": (C.c_char_p, [C.c_int32]),
     "phx_last_device_ms": (C.c_int32, [_P, C.POINTER(C.c_float)]),
     "phx_last_launch_count": (C.c_int32, [_P, C.POINTER(C.c_int32)]),
     "phx_mark": (C.c_int32, [_P, C.c_int32]),
@@ -111,8 +115,6 @@ SIGNATURES = {
     "phx_shard_gather_push": (C.c_int32, [_P, C.c_int64, _P, C.c_int64, _P, _P, C.c_int32, C.c_int32, _P]),
     "phx_shard_dedup": (C.c_int32, [_P, C.c_int64, _P, C.c_int64, _P, _P, _P, _P]),
     "phx_shard_dedup_expand": (C.c_int32, [_P, _P, _P, C.c_int64, _P, _P]),
-    "phx_diag_mma_rate": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_float),
-                                      C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "phx_copy_async": (C.c_int32, [_P, _P, C.c_uint64, _P]),
     "phx_ipc_alloc": (C.c_int32, [C.c_int32, C.c_uint64, C.POINTER(_P), _P]),
     "phx_ipc_open": (C.c_int32, [C.c_int32, _P, C.POINTER(_P)]),
@@ -129,6 +131,7 @@ SIGNATURES = {
     "phx_corpus_destroy": (None, [_P]),
     "phx_corpus_upload": (C.c_int32, [_P, C.c_int64, C.c_int64, _P]),
     "phx_corpus_fill_synthetic": (C.c_int32, [_P, C.c_uint32]),
+    "phx_corpus_read_device": (C.c_int32, [_P, C.c_int64, C.c_int64, _P]),
     "phx_corpus_topk_device": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, _P, _P]),
     "phx_corpus_set_mask": (C.c_int32, [_P, _P]),
     "phx_corpus_topk_keys_device": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, _P]),
@@ -137,6 +140,7 @@ SIGNATURES = {
     "phx_corpus_topk_window_device": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, C.c_int64, C.c_int64, _P, _P]),
     "phx_topk_merge_device": (C.c_int32, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, _P, _P]),
     "phx_topk_merge_static": (C.c_int32, [C.c_int32, _P, _P, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P]),
+    "phx_topk_merge_static_status": (C.c_int32, [C.c_int32, _P, C.POINTER(C.c_int32)]),
     "phx_corpus_sync": (C.c_int32, [_P]),
     "phx_corpus_last_device_ms": (C.c_int32, [_P, C.POINTER(C.c_float)]),
     "phx_corpus_last_error": (C.c_char_p, [_P]),

@@ -24,8 +24,9 @@ def _sources():
 
 def _digest(path: str) -> str:
     h = hashlib.sha256()
-    for dep in [path, os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "sm100_ptx.cuh"),
-                os.path.join(HERE, "..", "include", "phoenix_b200.h")]:
+    # every header under csrc/ counts as a dependency of every source: editing one rebuilds all objects
+    headers = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
+    for dep in [path, *headers, os.path.join(HERE, "..", "include", "phoenix_b200.h")]:
         with open(dep, "rb") as f:
             h.update(f.read())
     h.update(" ".join(FLAGS).encode())

@@ -690,8 +690,10 @@ phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::
     // one CTA per (batch, head) walks the request's tiles in sequence: worth it once those CTAs fill the device,
     // while a small batch is better off with one CTA per tile (latency of a single request)
     const bool enough = (long long)a.B * a.Hq >= 148 || (force && strcmp(force, "strip") == 0);
+    if (!strip_off && enough && a.dh == 64 && n_hist <= STRIP_HIST) dispatch_note(DK_ATTN_STRIP);
     if (!strip_off && enough && a.dh == 64 && n_hist <= STRIP_HIST) return cap ? launch_strip<true>(a, stream, err) : launch_strip<false>(a, stream, err);
   }
+  dispatch_note(DK_ATTN_STREAM);
   switch (a.dh) {
     case 32: return cap ? launch_dh<32, true>(a, stream, err) : launch_dh<32, false>(a, stream, err);
     case 64: return cap ? launch_dh<64, true>(a, stream, err) : launch_dh<64, false>(a, stream, err);

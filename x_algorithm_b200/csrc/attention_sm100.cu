@@ -710,8 +710,9 @@ phx_status ranker_attention_tc_launch(const AttnArgs& a, int* err_flag, cudaStre
     const char* force = getenv("PHX_ATTN");
     const bool resident = force && strcmp(force, "resident") == 0;
     const int n_hist = a.hist_len < a.T ? a.hist_len : a.T;
-    if (resident && a.dh == 64 && n_hist <= 128 && n_hist > 0) return launch_resident(a, err_flag, stream, err);
+    if (resident && a.dh == 64 && n_hist <= 128 && n_hist > 0) { dispatch_note(DK_ATTN_RESIDENT); return launch_resident(a, err_flag, stream, err); }
   }
+  dispatch_note(DK_ATTN_TC);
   if (a.dh == 64) return cap ? launch_tc<64, true>(a, err_flag, stream, err) : launch_tc<64, false>(a, err_flag, stream, err);
   if (a.dh == 128) return cap ? launch_tc<128, true>(a, err_flag, stream, err) : launch_tc<128, false>(a, err_flag, stream, err);
   err = "attention (tcgen05): head dim must be 64 or 128";

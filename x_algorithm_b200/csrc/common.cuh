@@ -28,6 +28,24 @@ void set_global_error(const std::string& msg);
     }                                                                                            \
   } while (0)
 
+// ---- which kernel variant a launch took (host-side counters, read through phx_dispatch_counts) -------------------
+enum DispatchKind {
+  DK_ATTN_STRIP = 0,     // resident-history mma.sync kernel (head dim 64, <= 128 history keys)
+  DK_ATTN_STREAM = 1,    // streaming mma.sync kernel
+  DK_ATTN_TC = 2,        // tcgen05 / TMEM streaming kernel
+  DK_ATTN_RESIDENT = 3,  // tcgen05 / TMEM resident-history kernel
+  DK_GEMM_PAIR256 = 4,   // tcgen05 GEMM, CTA pairs, 256-column tiles
+  DK_GEMM_PAIR128 = 5,
+  DK_GEMM_CTA256 = 6,    // tcgen05 GEMM, one CTA per tile
+  DK_GEMM_CTA128 = 7,
+  DK_GEMM_SIMT = 8,
+  DK_SCAN_TC = 9,        // tcgen05 corpus scan
+  DK_SCAN_MMA = 10,      // mma.sync corpus scan
+  DK_TOPK_EXACT = 11,    // exact-threshold passes of the top-k (the sampled pivot missed)
+  DK_COUNT = 12
+};
+void dispatch_note(int kind);
+
 // ---- bf16 <-> f32 on device -------------------------------------------------------------------
 __device__ __forceinline__ float bf2f(bf16 x) { return __bfloat162float(x); }
 __device__ __forceinline__ bf16 f2bf(float x) { return __float2bfloat16_rn(x); }
@@ -277,6 +295,9 @@ struct AttnArgs {
 bool ranker_attention_tc_supported(const AttnArgs& a);
 phx_status ranker_attention_tc_launch(const AttnArgs& a, int* err_flag, cudaStream_t stream, std::string& err);
 phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::string& err);
+// One thread waits on an mbarrier that nothing ever signals, with the flag block's wait limit: the wait gives up, raises
+// the flag and the kernel returns (the bounded-wait path of every tcgen05 kernel here, exercised on its own).
+phx_status wait_selftest_launch(int* err_flag, cudaStream_t stream, std::string& err);
 
 // ---- heads + blend ------------------------------------------------------------------------------
 struct HeadsArgs {

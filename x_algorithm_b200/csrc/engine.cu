@@ -8,6 +8,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <vector>
@@ -21,6 +22,11 @@ static std::string g_err = "";
 void set_global_error(const std::string& msg) {
   std::lock_guard<std::mutex> lk(g_err_mu);
   g_err = msg;
+}
+
+static std::atomic<long long> g_dispatch[DK_COUNT];
+void dispatch_note(int kind) {
+  if (kind >= 0 && kind < DK_COUNT) g_dispatch[kind].fetch_add(1, std::memory_order_relaxed);
 }
 
 static inline uint16_t f32_to_bf16_bits(float f) {
@@ -592,7 +598,9 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
   e->use_simt_gemm = gi && strcmp(gi, "simt") == 0;
   const char* dt = getenv("PHX_DEBUG_TAPS");
   e->debug_taps = dt && dt[0] == '1';
+#ifdef PHX_DIAGNOSTICS
   { const char* sd = getenv("PHX_SYNC_DEBUG"); e->sync_debug = sd && sd[0] == '1'; }
+#endif
   { const char* g = getenv("PHX_GRAPH"); e->graphs_enabled = !(g && g[0] == '0'); }
   e->D = cfg->emb_size; e->S = cfg->history_len; e->C = cfg->num_candidates; e->T = e->S + e->C;
   e->Hq = cfg->num_q_heads; e->Hkv = cfg->num_kv_heads; e->dh = cfg->key_size; e->F = cfg->ffn_size;
@@ -684,8 +692,8 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
     TRY(dev_alloc(e, &e->tokens, (size_t)M * e->D));
     TRY(dev_alloc(e, &e->hashes, (size_t)M * 2 * cfg->item.num_hashes));
   }
-  TRY(dev_alloc(e, &e->err_flag, 1));
-  CU(cudaMemset(e->err_flag, 0, sizeof(int)));
+  TRY(dev_alloc(e, &e->err_flag, 2));   // [0] raised by a wait that ran out, [1] the wait limit in microseconds (0 = default)
+  CU(cudaMemset(e->err_flag, 0, 2 * sizeof(int)));
   // RoPE tables: angle = pos * base^(-2j/dh), positions 0..S (layers.py:52-60)
   {
     const int half = e->dh / 2, npos = e->S + 1;
@@ -719,6 +727,7 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
     TRY(gemm_plan_create(&L.p_out, e->attn, L.w_out_t, M, e->D, e->HD, e->HD <= 1024 && !cfg->primer_norm, e->err));
     TRY(gemm_plan_create(&L.p_up, e->hbuf, L.w_up_t, M, e->F, e->D, false, e->err));
     TRY(gemm_plan_create(&L.p_down, e->ffn, L.w_down_t, M, e->D, e->F, false, e->err));
+#ifdef PHX_DIAGNOSTICS
     if (getenv("PHX_GEMM_COUNTERS")) {   // diagnostics: MMA-issuer wait counters by role, summed over layers and forwards
       if (!e->gemm_counters) {
         CU(cudaMalloc(reinterpret_cast<void**>(&e->gemm_counters), 4 * 8 * sizeof(unsigned long long)));
@@ -729,6 +738,7 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
       L.p_up.counters = L.p_up_f.counters = e->gemm_counters + 16;
       L.p_down.counters = e->gemm_counters + 24;
     }
+#endif
   }
   if (e->V + e->NC > 0) TRY(dev_alloc(e, &e->unembed_t, (size_t)(e->V + e->NC) * e->D));
   // staging for the host entry point
@@ -956,6 +966,17 @@ phx_status enqueue_forward(phx_engine* e, const phx_rank_batch* bd, const phx_ra
 }
 }  // namespace
 
+namespace {
+// the six input arrays of an id batch: a null one would be dereferenced on the device (a fault on a shared GPU)
+bool batch_arrays_present(phx_engine* e, const phx_rank_batch* b, bool need_candidates, const char* who) {
+  if (b->batch <= 0) return true;   // nothing is read
+  if (b->hist_post_ids && b->hist_author_ids && b->hist_actions && b->hist_surfaces &&
+      (!need_candidates || (b->cand_post_ids && b->cand_author_ids))) return true;
+  e->err = std::string(who) + ": null input array";
+  return false;
+}
+}  // namespace
+
 phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* bd, const phx_rank_out* od) {
   if (!e) return PHX_E_ARG;
   // the plan a host-buffer call prepared for this forward is taken here, before anything can fail: it never outlives
@@ -964,6 +985,7 @@ phx_status phx_rank_forward_device(phx_engine* e, const phx_rank_batch* bd, cons
   e->pack_next = nullptr;
   if (!bd || !od) return PHX_E_ARG;
   if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
+  if (!batch_arrays_present(e, bd, true, "phx_rank_forward_device")) return PHX_E_ARG;
   if (bd->batch < 0 || bd->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
   if (!params_complete(e, true) || !shards_complete(e)) return PHX_E_STATE;
   cudaSetDevice(e->device);
@@ -1078,11 +1100,12 @@ phx_status phx_rank_forward_packed_device(phx_engine* e, const phx_rank_batch* b
   return phx_rank_forward_device(e, bd, od);
 }
 
-// Row-sharded table with the exchange done by the host side (parallel.ShardedRanker)// Row-sharded table with the exchange done by the host side (parallel.ShardedRanker): first the unified-table rows
+// Row-sharded table with the exchange done by the host side (parallel.ShardedRanker): first the unified-table rows
 // of every token slot, then, once their rows sit in a landing buffer, the forward from there.
 phx_status phx_rank_rows_device(phx_engine* e, const phx_rank_batch* bd, int32_t* rows_dev, void* stream) {
   if (!e || !bd || !rows_dev) return PHX_E_ARG;
   if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
+  if (!batch_arrays_present(e, bd, true, "phx_rank_rows_device")) return PHX_E_ARG;
   if (bd->batch <= 0 || bd->batch > e->cfg.max_batch) { e->err = "batch must be 1..max_batch"; return PHX_E_CAPACITY; }
   cudaSetDevice(e->device);
   return build_tokens(e, bd, bd->batch, e->C, nullptr, nullptr, stream ? (cudaStream_t)stream : e->stream, nullptr, rows_dev);
@@ -1092,6 +1115,7 @@ phx_status phx_rank_forward_rows_device(phx_engine* e, const phx_rank_batch* bd,
                                         const phx_rank_out* od) {
   if (!e || !bd || !od || !landing_dev || !pos_dev) return PHX_E_ARG;
   if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
+  if (!batch_arrays_present(e, bd, true, "phx_rank_forward_rows_device")) return PHX_E_ARG;
   if (bd->batch <= 0 || bd->batch > e->cfg.max_batch) { e->err = "batch must be 1..max_batch"; return PHX_E_CAPACITY; }
   if (!params_complete(e, true)) return PHX_E_STATE;
   cudaSetDevice(e->device);
@@ -1169,6 +1193,7 @@ phx_status phx_rank_forward_hashed(phx_engine* e, const phx_rank_batch_hashed* b
 phx_status phx_rank_prefetch_device(phx_engine* e, const phx_rank_batch* bd) {
   if (!e || !bd) return PHX_E_ARG;
   if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
+  if (!batch_arrays_present(e, bd, true, "phx_rank_prefetch_device")) return PHX_E_ARG;
   if (bd->batch <= 0 || bd->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
   if (e->fp32) { e->err = "token prefetch is not available on the full-precision path"; return PHX_E_ARG; }
   if (e->pack) { e->err = "token prefetch is not available on an engine that packs ragged batches"; return PHX_E_ARG; }
@@ -1198,6 +1223,7 @@ phx_status phx_rank_prefetch_device(phx_engine* e, const phx_rank_batch* bd) {
 phx_status phx_rank_forward(phx_engine* e, const phx_rank_batch* bh, const phx_rank_out* oh) {
   if (!e || !bh || !oh) return PHX_E_ARG;
   if (bh->batch < 0 || bh->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
+  if (!batch_arrays_present(e, bh, true, "phx_rank_forward")) return PHX_E_ARG;
   cudaSetDevice(e->device);
   const size_t B = bh->batch, S = e->S, C = e->C;
   if (B == 0) return PHX_OK;
@@ -1285,6 +1311,7 @@ constexpr int SLOT_CHUNKS = 4;
 phx_status phx_rank_submit(phx_engine* e, const phx_rank_batch* bh, int32_t slot) {
   if (!e || !bh || slot < 0 || slot > 1) return PHX_E_ARG;
   if (bh->batch <= 0 || bh->batch > e->cfg.max_batch) { e->err = "batch must be 1..max_batch"; return PHX_E_CAPACITY; }
+  if (!batch_arrays_present(e, bh, true, "phx_rank_submit")) return PHX_E_ARG;
   cudaSetDevice(e->device);
   phx_status s = slots_init(e);
   if (s) return s;
@@ -1368,6 +1395,34 @@ phx_status phx_sync(phx_engine* e) {
   return check_err_flag(e);
 }
 
+phx_status phx_set_wait_limit_us(phx_engine* e, uint32_t microseconds) {
+  if (!e) return PHX_E_ARG;
+  cudaSetDevice(e->device);
+  PHX_CUDA_TRY(cudaStreamSynchronize(e->stream), e->err);
+  const int v = (int)(microseconds > 0x7FFFFFFFu ? 0x7FFFFFFFu : microseconds);
+  PHX_CUDA_TRY(cudaMemcpy(e->err_flag + 1, &v, sizeof(int), cudaMemcpyHostToDevice), e->err);
+  return PHX_OK;
+}
+
+phx_status phx_wait_selftest(phx_engine* e) {
+  if (!e) return PHX_E_ARG;
+  cudaSetDevice(e->device);
+  phx_status s = wait_selftest_launch(e->err_flag, e->stream, e->err);
+  if (s) return s;
+  return phx_sync(e);
+}
+
+int32_t phx_dispatch_counts(int64_t* out, int32_t n) {
+  for (int i = 0; i < n && i < DK_COUNT; ++i) out[i] = g_dispatch[i].load(std::memory_order_relaxed);
+  return DK_COUNT;
+}
+
+const char* phx_dispatch_name(int32_t kind) {
+  static const char* names[DK_COUNT] = {"attn.strip", "attn.stream", "attn.tcgen05", "attn.resident", "gemm.pair256", "gemm.pair128",
+                                        "gemm.cta256", "gemm.cta128", "gemm.simt", "scan.tcgen05", "scan.mma", "topk.exact"};
+  return (kind >= 0 && kind < DK_COUNT) ? names[kind] : "";
+}
+
 phx_status phx_last_device_ms(phx_engine* e, float* ms) {
   if (!e || !ms) return PHX_E_ARG;
   PHX_CUDA_TRY(cudaEventSynchronize(e->ev1), e->err);
@@ -1411,11 +1466,15 @@ phx_status phx_profile_read(phx_engine* e, float* ms_by_class, int32_t* launches
       fprintf(stderr, "[phx gemm counters] %s: MMA issuer waiting for operands %.1f%%, for a free accumulator %.1f%%\n", role[r],
               100.0 * h[8 * r + 1] / (double)(h[8 * r] ? h[8 * r] : 1), 100.0 * h[8 * r + 2] / (double)(h[8 * r] ? h[8 * r] : 1));
   }
+#ifdef PHX_DIAGNOSTICS
   if (getenv("PHX_PROF_GEMM")) {   // diagnostics: GEMM time of the last forward by role
     fprintf(stderr, "[phx gemm breakdown] qkv(store) %.3f ms/%d  qkv(rope) %.3f ms/%d  up(gelu) %.3f ms/%d  out(res) %.3f ms/%d  down(res) %.3f ms/%d\n",
             sub_ms[1 + EPI_STORE], sub_n[1 + EPI_STORE], sub_ms[1 + EPI_ROPE], sub_n[1 + EPI_ROPE], sub_ms[1 + EPI_GELU],
             sub_n[1 + EPI_GELU], sub_ms[5], sub_n[5], sub_ms[6], sub_n[6]);
   }
+#else
+  (void)sub_ms; (void)sub_n;
+#endif
   return PHX_OK;
 }
 
@@ -1494,6 +1553,7 @@ phx_status phx_gather_sum_device(phx_engine* e, int32_t family, const int64_t* i
 phx_status phx_user_tower_device(phx_engine* e, const phx_rank_batch* bd, float* users_dev) {
   if (!e || !bd || !users_dev) return PHX_E_ARG;
   if (bd->batch < 0 || bd->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
+  if (!batch_arrays_present(e, bd, false, "phx_user_tower_device")) return PHX_E_ARG;
   if (!params_complete(e, false) || !shards_complete(e)) return PHX_E_STATE;
   cudaSetDevice(e->device);
   const int B = bd->batch;
@@ -1525,8 +1585,8 @@ phx_status phx_ranker_attention_device(int32_t device, const uint16_t* q, const 
   aa.out = (bf16*)out; aa.seg = seg; aa.B = B; aa.T = T; aa.Hq = Hq; aa.Hkv = Hkv; aa.dh = dh; aa.hist_len = hist_len;
   aa.sm_scale = sm_scale; aa.cap = cap; aa.cap_method = cap > 0.f ? cap_method : 0;
   int* flag = nullptr;
-  if (cudaMalloc(&flag, sizeof(int)) != cudaSuccess) { set_global_error("cudaMalloc failed"); return PHX_E_CUDA; }
-  cudaMemset(flag, 0, sizeof(int));
+  if (cudaMalloc(&flag, 2 * sizeof(int)) != cudaSuccess) { set_global_error("cudaMalloc failed"); return PHX_E_CUDA; }
+  cudaMemset(flag, 0, 2 * sizeof(int));
   aa.err_flag = flag;
   cudaEvent_t e0, e1;
   cudaEventCreate(&e0); cudaEventCreate(&e1);
@@ -1554,8 +1614,8 @@ phx_status phx_gemm_device(int32_t device, const uint16_t* A, const uint16_t* Wt
   cudaDeviceProp prop;
   cudaGetDeviceProperties(&prop, device);
   int* flag = nullptr;
-  if (cudaMalloc(&flag, sizeof(int)) != cudaSuccess) { set_global_error("cudaMalloc failed"); return PHX_E_CUDA; }
-  cudaMemset(flag, 0, sizeof(int));
+  if (cudaMalloc(&flag, 2 * sizeof(int)) != cudaSuccess) { set_global_error("cudaMalloc failed"); return PHX_E_CUDA; }
+  cudaMemset(flag, 0, 2 * sizeof(int));
   cudaEvent_t e0, e1;
   cudaEventCreate(&e0); cudaEventCreate(&e1);
   phx_status s = PHX_OK;
@@ -1567,7 +1627,9 @@ phx_status phx_gemm_device(int32_t device, const uint16_t* A, const uint16_t* Wt
   } else {
     GemmPlan plan;
     s = gemm_plan_create(&plan, (const bf16*)A, (const bf16*)Wt, M, N, K, epilogue == 1 && K <= 1024, err, impl == 2 ? 0 : -1);
+#ifdef PHX_DIAGNOSTICS
     if (getenv("PHX_GEMM_COUNTERS")) { cudaMalloc(&ctr, 64); cudaMemset(ctr, 0, 64); plan.counters = ctr; }
+#endif
     cudaEventRecord(e0, 0);
     if (s == PHX_OK && (epilogue < 0 || epilogue > 2)) { err = "phx_gemm_device: epilogue must be 0, 1 or 2"; s = PHX_E_ARG; }
     if (s == PHX_OK) s = gemm_launch(plan, (const bf16*)A, (bf16*)C, (const bf16*)R, M, epilogue, nullptr, nullptr, flag, prop.multiProcessorCount, 0, err);

@@ -618,20 +618,40 @@ phx_status gemm_launch(GemmPlan& p, const bf16* A, bf16* C, const bf16* R, int64
     const long long slots = p.pair ? num_sms / 2 : num_sms;
     static const bool allow = !(getenv("PHX_GEMM_TILES") && strcmp(getenv("PHX_GEMM_TILES"), "wide") == 0);
     if (allow && p.has_narrow && narrow_tiles <= slots) {
+      dispatch_note(p.pair ? DK_GEMM_PAIR128 : DK_GEMM_CTA128);
       GemmPlan q = p;
       q.map_b = p.map_b_narrow; q.BN = 128;
       return q.pair ? launch_e<128, true>(q, epilogue, rp, nm, M, err_flag, num_sms, stream, err)
                     : launch_e<128, false>(q, epilogue, rp, nm, M, err_flag, num_sms, stream, err);
     }
+    dispatch_note(p.pair ? DK_GEMM_PAIR256 : DK_GEMM_CTA256);
     return p.pair ? launch_e<256, true>(p, epilogue, rp, nm, M, err_flag, num_sms, stream, err)
                   : launch_e<256, false>(p, epilogue, rp, nm, M, err_flag, num_sms, stream, err);
   }
+  dispatch_note(p.pair ? DK_GEMM_PAIR128 : DK_GEMM_CTA128);
   return p.pair ? launch_e<128, true>(p, epilogue, rp, nm, M, err_flag, num_sms, stream, err)
                 : launch_e<128, false>(p, epilogue, rp, nm, M, err_flag, num_sms, stream, err);
 }
 
+namespace {
+__global__ void wait_selftest_kernel(int* err_flag) {
+  __shared__ __align__(8) unsigned long long bar;
+  const uint32_t b = smem_u32(&bar);
+  mbar_init(b, 1);
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  mbar_wait(b, 0, err_flag);   // nothing arrives: returns false once the limit has passed
+}
+}  // namespace
+
+phx_status wait_selftest_launch(int* err_flag, cudaStream_t stream, std::string& err) {
+  wait_selftest_kernel<<<1, 1, 0, stream>>>(err_flag);
+  PHX_CUDA_TRY(cudaGetLastError(), err);
+  return PHX_OK;
+}
+
 phx_status gemm_simt_launch(const bf16* A, const bf16* Wt, bf16* C, const bf16* R, int64_t M, int N, int K,
                             int epilogue, cudaStream_t stream, std::string& err) {
+  dispatch_note(DK_GEMM_SIMT);
   dim3 block(32, 32);
   dim3 grid((N + 31) / 32, (unsigned)((M + 31) / 32));
   if (grid.y > 65535) {

@@ -10,7 +10,11 @@ namespace sm100 {
 
 constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s unless the flag block carries its own limit
+// The error flag every kernel here takes is a block of two ints: [0] is raised when a bounded wait ran out, [1] is the
+// limit in microseconds (0 = the 2 s default).  A host sets [1] once (phx_set_wait_limit_us); kernels only read it on the
+// slow path of a wait.
+constexpr int ERR_FLAG_INTS = 2;
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -44,7 +48,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*err_flag != 0) return false;
       unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > WAIT_LIMIT_NS) { *err_flag = 1; __threadfence(); return false; }
+      else {
+        const unsigned int us = (unsigned int)err_flag[1];
+        const unsigned long long limit = us ? 1000ull * us : WAIT_LIMIT_NS;
+        if (now - t0 > limit) { *err_flag = 1; __threadfence(); return false; }
+      }
     }
   }
 }

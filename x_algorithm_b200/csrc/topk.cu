@@ -303,8 +303,9 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(const unsigned long
   for (int i = threadIdx.x; i < k; i += blockDim.x) {
     const unsigned long long v = s_keys[i];
     if (out_keys) { out_keys[(size_t)u * k + i] = v; continue; }
-    out_scores[(size_t)u * k + i] = from_ordered32((uint32_t)(v >> 32));
-    out_ids[(size_t)u * k + i] = (long long)(0xFFFFFFFFu - (uint32_t)(v & 0xFFFFFFFFull));
+    // key 0 is an empty slot (the lists held fewer than k entries): the same (-inf, -1) the underflow path writes
+    out_scores[(size_t)u * k + i] = v ? from_ordered32((uint32_t)(v >> 32)) : -INFINITY;
+    out_ids[(size_t)u * k + i] = v ? (long long)(0xFFFFFFFFu - (uint32_t)(v & 0xFFFFFFFFull)) : -1ll;
   }
 }
 
@@ -320,7 +321,7 @@ __global__ void regroup_keys_kernel(const unsigned long long* __restrict__ in, i
 
 // [P][B][k] (score, id) lists -> keys[B][P*k]
 __global__ void merge_keys_kernel(const float* __restrict__ scores, const long long* __restrict__ ids, int P, int B, int k,
-                                  unsigned long long* __restrict__ keys) {
+                                  unsigned long long* __restrict__ keys, int* status) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)P * B * k) return;
   const int p = (int)(i / ((long long)B * k));
@@ -328,7 +329,8 @@ __global__ void merge_keys_kernel(const float* __restrict__ scores, const long l
   const int j = (int)(i % k);
   const long long id = ids[i];
   unsigned long long key = 0ull;  // empty slot (id < 0) sorts last
-  if (id >= 0) key = ((unsigned long long)ordered32(scores[i]) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)id);
+  if (id > 0xFFFFFFFFll) atomicOr(status, 4);   // does not fit the key's 32 row bits: left out, reported
+  else if (id >= 0) key = ((unsigned long long)ordered32(scores[i]) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)id);
   keys[((size_t)b * P + p) * k + j] = key;
 }
 
@@ -427,8 +429,8 @@ phx_status phx_corpus_create(int32_t device, int64_t rows, int32_t dim, int64_t 
   CU(cudaMalloc(&c->counts, 256 * 4));
   CU(cudaMalloc(&c->status, 4));
   CU(cudaMemset(c->status, 0, 4));
-  CU(cudaMalloc(&c->err_flag, 4));
-  CU(cudaMemset(c->err_flag, 0, 4));
+  CU(cudaMalloc(&c->err_flag, 8));   // [0] flag, [1] wait limit in microseconds (0 = default)
+  CU(cudaMemset(c->err_flag, 0, 8));
 #undef CU
   {
     const char* force = getenv("PHX_TOPK");
@@ -461,6 +463,14 @@ phx_status phx_corpus_upload(phx_corpus* c, int64_t row0, int64_t nrows, const u
   if (!c || !host_bf16 || row0 < 0 || nrows < 0 || row0 + nrows > c->rows) { if (c) c->err = "phx_corpus_upload: range"; return PHX_E_ARG; }
   cudaSetDevice(c->device);
   PHX_CUDA_TRY(cudaMemcpy(c->data + row0 * c->dim, host_bf16, (size_t)nrows * c->dim * 2, cudaMemcpyHostToDevice), c->err);
+  return PHX_OK;
+}
+
+phx_status phx_corpus_read_device(phx_corpus* c, int64_t row0, int64_t nrows, uint16_t* out_dev) {
+  if (!c || !out_dev || row0 < 0 || nrows < 0 || row0 + nrows > c->rows) { if (c) c->err = "phx_corpus_read_device: range"; return PHX_E_ARG; }
+  cudaSetDevice(c->device);
+  PHX_CUDA_TRY(cudaMemcpyAsync(out_dev, c->data + row0 * c->dim, (size_t)nrows * c->dim * 2, cudaMemcpyDeviceToDevice, c->stream), c->err);
+  PHX_CUDA_TRY(cudaStreamSynchronize(c->stream), c->err);
   return PHX_OK;
 }
 
@@ -631,7 +641,7 @@ phx_status phx_topk_merge_device(phx_corpus* c, const float* scores_dev, const i
     PHX_CUDA_TRY(cudaMalloc(&c->merge_keys, need * 8), c->err);
     c->merge_keys_elems = need;
   }
-  merge_keys_kernel<<<(unsigned)((need + 255) / 256), 256, 0, c->stream>>>(scores_dev, (const long long*)ids_dev, P, B, k, c->merge_keys);
+  merge_keys_kernel<<<(unsigned)((need + 255) / 256), 256, 0, c->stream>>>(scores_dev, (const long long*)ids_dev, P, B, k, c->merge_keys, c->status);
   PHX_CUDA_TRY(cudaGetLastError(), c->err);
   const int kp2 = next_pow2(k);
   select_kernel<<<B, SEL_THREADS, (size_t)kp2 * 8, c->stream>>>(c->merge_keys, nullptr, P * k, P * k, k, kp2, out_scores_dev,
@@ -670,7 +680,31 @@ phx_status static_scratch_for(int device, StaticScratch** out, std::string& err)
   *out = &sc;
   return PHX_OK;
 }
+struct DeviceGuard {
+  int prev = -1; bool ok = false;
+  explicit DeviceGuard(int device) {
+    if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    ok = cudaSetDevice(device) == cudaSuccess;
+  }
+  ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
 }  // namespace
+
+phx_status phx_topk_merge_static_status(int32_t device, void* stream, int32_t* status_out) {
+  if (!status_out) { set_global_error("phx_topk_merge_static_status: null argument"); return PHX_E_ARG; }
+  DeviceGuard guard(device);
+  if (!guard.ok) { set_global_error("phx_topk_merge_static_status: cudaSetDevice failed"); return PHX_E_CUDA; }
+  std::string err;
+  StaticScratch* sc = nullptr;
+  phx_status s = static_scratch_for(device, &sc, err);
+  if (s) { set_global_error(err); return s; }
+  cudaError_t ce = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  int v = 0;
+  if (ce == cudaSuccess) ce = cudaMemcpy(&v, sc->status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (ce != cudaSuccess) { set_global_error(std::string("phx_topk_merge_static_status: ") + cudaGetErrorString(ce)); return PHX_E_CUDA; }
+  *status_out = v;
+  return PHX_OK;
+}
 
 phx_status phx_topk_merge_static(int32_t device, const float* scores_dev, const int64_t* ids_dev, int32_t P, int32_t B,
                                  int32_t k, float* out_scores_dev, int64_t* out_ids_dev, void* stream) {
@@ -685,7 +719,8 @@ phx_status phx_topk_merge_static(int32_t device, const float* scores_dev, const 
                      std::to_string((long long)PHX_STATIC_MERGE_MAX_KEYS) + " keys; use phx_topk_merge_device");
     return PHX_E_CAPACITY;
   }
-  if (cudaSetDevice(device) != cudaSuccess) { set_global_error("phx_topk_merge_static: cudaSetDevice failed"); return PHX_E_CUDA; }
+  DeviceGuard guard(device);   // the caller's current device is put back on return
+  if (!guard.ok) { set_global_error("phx_topk_merge_static: cudaSetDevice failed"); return PHX_E_CUDA; }
   StaticScratch* sc = nullptr;
   phx_status s = static_scratch_for(device, &sc, err);
   if (s) { set_global_error(err); return s; }
@@ -694,7 +729,7 @@ phx_status phx_topk_merge_static(int32_t device, const float* scores_dev, const 
   // [0, need) are all rewritten by the first kernel
   cudaError_t ce = cudaMemsetAsync(sc->status, 0, sizeof(int), st);
   if (ce != cudaSuccess) { set_global_error(std::string("phx_topk_merge_static: ") + cudaGetErrorString(ce)); return PHX_E_CUDA; }
-  merge_keys_kernel<<<(unsigned)((need + 255) / 256), 256, 0, st>>>(scores_dev, (const long long*)ids_dev, P, B, k, sc->keys);
+  merge_keys_kernel<<<(unsigned)((need + 255) / 256), 256, 0, st>>>(scores_dev, (const long long*)ids_dev, P, B, k, sc->keys, sc->status);
   const int kp2 = next_pow2(k);
   select_kernel<<<B, SEL_THREADS, (size_t)kp2 * 8, st>>>(sc->keys, nullptr, P * k, P * k, k, kp2, out_scores_dev,
                                                          (long long*)out_ids_dev, sc->status);
@@ -715,6 +750,11 @@ phx_status phx_corpus_sync(phx_corpus* c) {
     return PHX_E_TIMEOUT;
   }
   PHX_CUDA_TRY(cudaMemcpy(&st, c->status, 4, cudaMemcpyDeviceToHost), c->err);
+  if (st & 4) {
+    cudaMemset(c->status, 0, 4);
+    c->err = "topk merge: an id does not fit 32 bits; the entry was left out";
+    return PHX_E_ARG;
+  }
   if (st != 0) {
     cudaMemset(c->status, 0, 4);
     c->err = std::string("topk: survivor list ") + ((st & 2) ? "overflowed its capacity" : "held fewer than k rows") +

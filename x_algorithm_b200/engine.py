@@ -234,6 +234,14 @@ class PhoenixEngine:
     def sync(self):
         self._check(lib.phx_sync(self._h))
 
+    def set_wait_limit_us(self, microseconds: int):
+        """Limit of every bounded device-side wait of this engine's kernels (0 = the 2 s default)."""
+        self._check(lib.phx_set_wait_limit_us(self._h, int(microseconds)))
+
+    def wait_selftest(self):
+        """Let one device-side wait run out: raises PhoenixError(PHX_E_TIMEOUT) when the mechanism works."""
+        self._check(lib.phx_wait_selftest(self._h))
+
     def last_device_ms(self) -> float:
         ms = C.c_float()
         self._check(lib.phx_last_device_ms(self._h, C.byref(ms)))
@@ -277,6 +285,14 @@ class PhoenixEngine:
 
     def gather_sum_device(self, family: int, ids, n: int, out):
         self._check(lib.phx_gather_sum_device(self._h, family, _ptr(ids), n, _ptr(out)))
+
+
+def dispatch_counts() -> Dict[str, int]:
+    """Launch counts by kernel variant over the life of the process (phx_dispatch_counts)."""
+    n = lib.phx_dispatch_counts(None, 0)
+    buf = (C.c_int64 * n)()
+    lib.phx_dispatch_counts(buf, n)
+    return {lib.phx_dispatch_name(i).decode(): int(buf[i]) for i in range(n)}
 
 
 def ranker_attention(q, k, v, seg, hist_len: int, sm_scale: float, cap: float = -1.0, cap_method: int = 0,

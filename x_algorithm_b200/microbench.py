@@ -4,7 +4,6 @@
     torchrun --nproc-per-node N -m x_algorithm_b200.microbench gather [--exchange copy|push|a2a|peer] [--check]
     python -m x_algorithm_b200.microbench topk    [--rows 12500000] [--dim 128] [--queries 256] [--k 1000]
     torchrun --nproc-per-node N -m x_algorithm_b200.microbench retrieve [--rows 100000000] [--check]
-    python -m x_algorithm_b200.microbench mma [--ksteps 200000]
     python -m x_algorithm_b200.microbench attention [--batch 64] [--heads 16] [--dh 128] [--hist 1024] [--cands 1024]
 
 gather: the multi-hash gather-sum workload (8 tables x 2^24 rows x 256 bf16 = 64 GiB, realised as the four hash
@@ -34,13 +33,8 @@ def _peaks():
 
 
 def _zipf_ids(n, seed, s=1.1):
-    rng = np.random.Generator(np.random.PCG64(seed))
-    u = rng.random(n)
-    a, N = 1.0 - s, float(1 << 40)
-    rank = np.clip(np.floor(((N ** a - 1.0) * u + 1.0) ** (1.0 / a)).astype(np.int64), 1, (1 << 40) - 1)
-    with np.errstate(over="ignore"):
-        ids = (rank * np.int64(0x9E3779B97F4A7C15 - (1 << 64))) & np.int64((1 << 40) - 1)
-    return np.where(ids == 0, 1, ids).astype(np.int64)
+    from .synthetic import zipf_ids
+    return zipf_ids(n, np.random.Generator(np.random.PCG64(seed)), s)
 
 
 def bench_gather(a):
@@ -235,38 +229,18 @@ def bench_attention(a):
                           peak_source=src)))
 
 
-def bench_mma(a):
-    """The tcgen05 pipe and the L2 -> shared-memory fill, apart and together (the GEMM's two resources)."""
-    import ctypes as C
-    from x_algorithm_b200 import _lib
-    lib = _lib.lib
-    cases = [("pipe alone", 1, 0, 2), ("pipe + 32 KB/k-step fill (a CTA pair's 256x256 tile)", 1, 2, 2),
-             ("pipe + 16 KB/k-step fill", 1, 1, 2), ("one CTA per tile: pipe + 48 KB/k-step fill", 0, 3, 2)]
-    for name, pair, tiles, mode in cases:
-        ms, mc, fc = C.c_float(), C.c_double(), C.c_double()
-        st = lib.phx_diag_mma_rate(0, pair, a.ksteps, tiles, mode, C.byref(ms), C.byref(mc), C.byref(fc))
-        if st != 0:
-            raise _lib.PhoenixError(st, lib.phx_global_error().decode())
-        flop = 2.0 * 128 * 256 * 64 * a.ksteps * 148
-        cyc = max(mc.value, fc.value)
-        print(json.dumps(dict(op="mma_rate", case=name, ksteps=a.ksteps, ms=ms.value, mma_cycles_per_kstep=round(mc.value, 1),
-                              fill_cycles_per_kstep=round(fc.value, 1), tflops=flop / ms.value / 1e9,
-                              sm_ghz=round(cyc * a.ksteps / (ms.value * 1e-3) / 1e9, 3),
-                              fill_tbs=tiles * 16384.0 * a.ksteps * 148 / (ms.value * 1e-3) / 1e12)))
-
-
 def bench_ragged(a):
     """Ragged ranking batches through the blocking host-buffer call, with and without packed rows: the headline benchmark's
     model, --batch requests whose valid history / candidate counts are uniform in [1, S] / [1, C]."""
     import math
     import time
     import x_algorithm_b200 as px
-    from oracle import phoenix_oracle as po   # synthetic weights and batches only
+    from x_algorithm_b200 import synthetic
     wl = dict(emb_size=512, num_layers=8, num_q_heads=8, num_kv_heads=8, key_size=64, widening_factor=4.0, history_len=128,
               num_candidates=512, num_actions=19, num_continuous=1, num_hashes=2, table_size=1 << a.log2_rows)
-    ocfg = po.ModelConfig(**wl)
-    w = po.make_weights(ocfg, 0)
-    batch = po.make_batch(ocfg, a.batch, seed=2, ragged=True)
+    mcfg = px.PhoenixConfig(max_batch=a.batch, **wl)
+    w = synthetic.make_weights(mcfg, 0)
+    batch = synthetic.make_batch(mcfg, a.batch, seed=2, ragged=True)
     valid = int((batch.cand_post_ids != 0).sum())
     rows = int((batch.cand_post_ids != 0).sum() + (batch.hist_post_ids != 0).sum())
     inp = px.RankInputs(batch.hist_post_ids, batch.hist_author_ids, batch.hist_actions, batch.hist_surfaces,
@@ -330,8 +304,7 @@ def bench_value(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gather", "topk", "attention", "retrieve", "mma", "value", "ragged"])
-    ap.add_argument("--ksteps", type=int, default=200000, help="mma: k-steps per CTA (2000000 runs about a second)")
+    ap.add_argument("op", choices=["gather", "topk", "attention", "retrieve", "value", "ragged"])
     ap.add_argument("--check", action="store_true")
     ap.add_argument("--no-dedup", action="store_true", help="sharded gather: send every request, not only distinct rows")
     ap.add_argument("--exchange", choices=["copy", "push", "a2a", "peer"], default="copy",
@@ -354,7 +327,7 @@ def main():
     ap.add_argument("--hist", type=int, default=1024)
     ap.add_argument("--cands", type=int, default=1024)
     a = ap.parse_args()
-    {"gather": bench_gather, "topk": bench_topk, "attention": bench_attention, "retrieve": bench_retrieve, "mma": bench_mma,
+    {"gather": bench_gather, "topk": bench_topk, "attention": bench_attention, "retrieve": bench_retrieve,
      "value": bench_value, "ragged": bench_ragged}[a.op](a)
 
 

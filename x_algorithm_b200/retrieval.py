@@ -95,14 +95,34 @@ class CorpusShard:
         return float(ms.value)
 
 
-def merge_topk_static(scores, ids, P: int, B: int, k: int, out_scores, out_ids, device: int = 0, stream: int = 0):
+def merge_topk_static(scores, ids, P: int, B: int, k: int, out_scores, out_ids, device: "int | None" = None,
+                      stream: "int | None" = None):
     """Merge [P,B,k] per-shard lists into [B,k] without allocating device memory: the scratch is a
     fixed array inside the library (limit P*B*k <= 2,097,152).  For callers whose device memory is
-    owned by someone else.  Torch CUDA tensors; asynchronous on `stream` (0 = default stream)."""
+    owned by someone else.  Torch CUDA tensors; asynchronous on `stream` (default: torch's current
+    stream of the tensors' device, which is also the default for `device`)."""
+    import torch
+    if device is None:
+        device = scores.device.index if scores.device.index is not None else torch.cuda.current_device()
+    if stream is None:
+        stream = torch.cuda.current_stream(device).cuda_stream
     st = lib.phx_topk_merge_static(device, int(scores.data_ptr()), int(ids.data_ptr()), P, B, k,
-                                   int(out_scores.data_ptr()), int(out_ids.data_ptr()), stream)
+                                   int(out_scores.data_ptr()), int(out_ids.data_ptr()), stream or None)
     if st != 0:
         raise PhoenixError(st, lib.phx_global_error().decode())
+
+
+def merge_topk_static_status(device: int = 0, stream: "int | None" = None) -> int:
+    """Wait for `stream` and return the status word of the allocation-free merge (0 = every entry was merged, bit 2 =
+    an id did not fit 32 bits and was left out)."""
+    import torch
+    if stream is None:
+        stream = torch.cuda.current_stream(device).cuda_stream
+    v = C.c_int32()
+    st = lib.phx_topk_merge_static_status(device, stream or None, C.byref(v))
+    if st != 0:
+        raise PhoenixError(st, lib.phx_global_error().decode())
+    return int(v.value)
 
 
 class Retriever:
