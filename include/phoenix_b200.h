@@ -451,7 +451,20 @@ phx_status phx_topk_merge_device(phx_corpus* c, const float* scores_dev, const i
 phx_status phx_topk_merge_static(int32_t device, const float* scores_dev, const int64_t* ids_dev, int32_t P,
                                  int32_t B, int32_t k, float* out_scores_dev, int64_t* out_ids_dev, void* stream);
 phx_status phx_topk_merge_static_status(int32_t device, void* stream, int32_t* status_out);
+/* Wait for the shard's work and report what went wrong in it.  The fast top-k keeps the rows at or above a pivot
+ * estimated from a sample of the corpus; when a query's pivot turns out too high (fewer than k rows reach it) or too low
+ * (more rows than the survivor buffer holds: long runs of equal scores, clustered rows), the sync does that call again
+ * with exact thresholds - bisection on the 64-bit (score, row) key with one counting scan per step - into the same output
+ * buffers, so a top-k call followed by a sync always yields the exhaustive answer, as the reference's top_k does
+ * (cuda/top_k_by_key/__init__.py:56-94).  The query buffer of the call must still hold the queries.
+ * phx_corpus_finish is the same and tells in *reran_out whether the call was done again (a caller that has already
+ * passed the first answer on - an all-gather of the lists - then repeats that step).  phx_corpus_set_exact(on) makes
+ * every later top-k of the shard take the exact passes straight away (synchronous); phx_corpus_exact_runs counts the
+ * calls that took them. */
 phx_status phx_corpus_sync(phx_corpus* c);
+phx_status phx_corpus_finish(phx_corpus* c, int32_t* reran_out);
+phx_status phx_corpus_set_exact(phx_corpus* c, int32_t on);
+phx_status phx_corpus_exact_runs(phx_corpus* c, int64_t* n);
 phx_status phx_corpus_last_device_ms(phx_corpus* c, float* ms);
 const char* phx_corpus_last_error(const phx_corpus* c);
 

@@ -70,10 +70,11 @@ def test_rank_forward_headline_batch_vs_oracle(torch, monkeypatch):
     spec = po.blend_spec_from_weights(wt, po.HEAD_NAMES_19, ocfg.num_actions)
     want_s = po.blend_scores(spec, res.log_probs[pick], res.continuous[pick])
     np.testing.assert_allclose(res.scores[pick][valid], want_s[valid], rtol=1e-12, atol=1e-15)
-    # padded candidate slots of the ragged request do not disturb its valid ones: the same request alone, unpadded
-    # layout aside, gives the same bits
+    # the same ragged request alone: a batch of one takes the latency kernels (128-column GEMM tiles, streaming
+    # attention), so the bits differ, the answer does not
     alone = eng.rank(to_inputs(take_requests(b, [ragged])))
-    np.testing.assert_array_equal(alone.log_probs[0][valid[1]], res.log_probs[ragged][valid[1]])
+    assert_heads_close(alone.log_probs[0][valid[1]], alone.continuous[0][valid[1]], logits[1][valid[1]], cont[1][valid[1]], TOL,
+                       "one request")
     eng.close()
     # integer / byte stages of the same requests, bit exact (an engine that keeps its per-stage taps)
     monkeypatch.setenv("PHX_DEBUG_TAPS", "1")

@@ -172,7 +172,9 @@ def test_rank_forward_cfg0_vs_oracle(torch, ragged, monkeypatch):
     # against the fp32 path of the oracle as well
     ocfg32 = po.ModelConfig(compute="fp32")
     lp32, cont32, logits32 = po.rank_forward(ocfg32, w, rows_fn, b)
-    assert_heads_close(res.log_probs[valid], res.continuous[valid], logits32[valid], cont32[valid], TOL, "against the fp32 model")
+    # (logits only: the bf16 model rounds its dwell prediction to bf16, a step of 1/16 at values near 15, which is
+    # already 1e-2 of that head's variation; the fp32 model does not round it)
+    assert_heads_close(res.log_probs[valid], None, logits32[valid], None, TOL, "against the fp32 model")
     # blend: exact arithmetic given the engine's own head outputs (f64, same order)
     want_s = po.blend_scores(spec, res.log_probs, res.continuous)
     np.testing.assert_allclose(res.scores[valid], want_s[valid], rtol=1e-12, atol=1e-15)
@@ -708,6 +710,56 @@ def test_topk_with_row_eligibility_mask(torch, monkeypatch, impl, dim, N):
     shard.set_mask(None)
     check(None, 0, N)
     shard.close()
+
+
+@pytest.mark.parametrize("impl,dim", [("tc", 128), ("simt", 96)])
+def test_topk_is_exact_when_the_sampled_pivot_misses(torch, monkeypatch, impl, dim):
+    """Corpora the sampled pivot cannot serve: every row the same (all scores tie, far more than the survivor buffer
+    holds), and a 60,000-row block of copies of one query's direction (that query's top is one long tie).  The sync
+    after the call does it again with exact thresholds; ids equal the oracle's top-k, ties to the lower row.  And on
+    ordinary rows the exact passes, forced, give what the fast path gives."""
+    from x_algorithm_b200.retrieval import CorpusShard, Retriever
+    if impl == "simt":
+        monkeypatch.setenv("PHX_TOPK", "simt")
+    N, k, B, off = 400_000, 100, 6, 7_000
+    rng = np.random.default_rng(dim)
+    u = rng.standard_normal((B, dim)).astype(np.float32)
+    u /= np.linalg.norm(u, axis=1, keepdims=True)
+    users = torch.from_numpy(u).cuda()
+    sc = torch.empty((B, k), dtype=torch.float32, device="cuda"); ids = torch.empty((B, k), dtype=torch.int64, device="cuda")
+    sh = CorpusShard(N, dim, row_offset=off, max_queries=8, max_k=k)
+
+    def run_and_check(corpus_bits, want_reruns):
+        sh.upload(0, corpus_bits)
+        before = sh.exact_runs()
+        sh.topk_device(users, B, k, sc, ids)
+        reran = sh.finish()
+        assert reran == (want_reruns > 0) and sh.exact_runs() - before == want_reruns
+        want_s, want_i = po.top_k(po.corpus_scores(u, corpus_bits), k, row_offset=off)
+        np.testing.assert_array_equal(ids.cpu().numpy(), want_i)
+        np.testing.assert_allclose(sc.cpu().numpy(), want_s, rtol=2.0 ** -7, atol=0)
+
+    base = po.synthetic_corpus_rows(np.arange(off, off + N), dim, 29)
+    same = np.repeat(base[:1], N, axis=0)
+    run_and_check(same, 1)                                   # the k lowest rows, for every query
+    np.testing.assert_array_equal(ids.cpu().numpy(), np.tile(np.arange(off, off + k), (B, 1)))
+    block = base.copy()
+    block[300_000:360_000] = po.bf16_bits(u[0])[None, :]     # 60,000 copies of query 0's direction
+    run_and_check(block, 1)
+    assert (ids[0].cpu().numpy() == np.arange(off + 300_000, off + 300_000 + k)).all()
+    run_and_check(base, 0)                                   # ordinary rows: the fast path serves them
+    fast_i, fast_s = ids.clone(), sc.clone()
+    sh.set_exact(True)
+    sh.topk_device(users, B, k, sc, ids)
+    sh.sync()
+    sh.set_exact(False)
+    assert torch.equal(ids, fast_i) and torch.equal(sc, fast_s)
+    # through the retriever: the merged answer is exact too, the re-run replaces the shard's list before the merge
+    sh.upload(0, block)
+    got_s, got_i = Retriever([sh]).retrieve(users, k)
+    want_s, want_i = po.top_k(po.corpus_scores(u, block), k, row_offset=off)
+    np.testing.assert_array_equal(got_i.cpu().numpy(), want_i)
+    sh.close()
 
 
 def test_retriever_orders_its_work_on_the_callers_stream(torch):

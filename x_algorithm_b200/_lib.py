@@ -142,6 +142,9 @@ SIGNATURES = {
     "phx_topk_merge_static": (C.c_int32, [C.c_int32, _P, _P, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P]),
     "phx_topk_merge_static_status": (C.c_int32, [C.c_int32, _P, C.POINTER(C.c_int32)]),
     "phx_corpus_sync": (C.c_int32, [_P]),
+    "phx_corpus_finish": (C.c_int32, [_P, C.POINTER(C.c_int32)]),
+    "phx_corpus_set_exact": (C.c_int32, [_P, C.c_int32]),
+    "phx_corpus_exact_runs": (C.c_int32, [_P, C.POINTER(C.c_int64)]),
     "phx_corpus_last_device_ms": (C.c_int32, [_P, C.POINTER(C.c_float)]),
     "phx_corpus_last_error": (C.c_char_p, [_P]),
 }

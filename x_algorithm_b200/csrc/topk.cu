@@ -82,9 +82,12 @@ struct ScanArgs {
   int cap;
   const unsigned int* mask = nullptr;   // eligibility bits of the shard's rows (row_eligible), null = all
   long long mask_row0 = 0;
+  const unsigned long long* thr = nullptr;   // MODE 2 / 3: [B] threshold keys (a row counts / is kept when key >= thr[u])
 };
 
-// NT = n-tiles (8 users each) per warp; a CTA covers 2 * NT * 8 users x 64 corpus rows per tile
+// NT = n-tiles (8 users each) per warp; a CTA covers 2 * NT * 8 users x 64 corpus rows per tile.
+// MODE 0 sample pass (group maxima), 1 collect pass against a score pivot, 2 count the rows whose 64-bit key is at or
+// above a per-user threshold key, 3 collect those rows (the exact passes: no sampling, nothing estimated).
 template <int NT, int MODE>
 __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
   extern __shared__ __align__(16) uint8_t ssm[];
@@ -103,6 +106,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
   }
   if (MODE == 1)
     for (int u = threadIdx.x; u < a.Bpad; u += SCAN_THREADS) s_pivot[u] = (u < a.B) ? a.pivot[u] : INFINITY;
+  // exact passes: threshold keys and (MODE 2) this CTA's counts live behind the pivots' slot
+  unsigned long long* s_thr = reinterpret_cast<unsigned long long*>(s_pivot + a.Bpad);   // [Bpad]
+  int* s_cnt = reinterpret_cast<int*>(s_thr + a.Bpad);                                   // [Bpad]
+  if (MODE >= 2)
+    for (int u = threadIdx.x; u < a.Bpad; u += SCAN_THREADS) { s_thr[u] = (u < a.B) ? a.thr[u] : ~0ull; s_cnt[u] = 0; }
 
   const long long n_tiles = (a.rows + TILE_ROWS - 1) / TILE_ROWS;
   const long long step = (long long)gridDim.x * (MODE == 0 ? a.stride : 1);
@@ -160,6 +168,25 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
           if (u0 + 1 < a.B) a.gmax[(size_t)(u0 + 1) * a.n_groups + grp] = m1;
         }
       }
+    } else if (MODE >= 2) {
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const int u0 = (half * NT + j) * 8 + 2 * t4;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int u = u0 + (e & 1);
+          const long long row = (e & 2) ? row_b : row_a;
+          if (!((e & 2) ? ok_b : ok_a) || u >= a.B) continue;
+          const unsigned long long key = ((unsigned long long)ordered32(round_bf(acc[j][e])) << 32) |
+                                         (unsigned long long)(0xFFFFFFFFu - (uint32_t)(a.row_offset + row));
+          if (key < s_thr[u]) continue;
+          if (MODE == 2) atomicAdd(&s_cnt[u], 1);
+          else {
+            const int slot = atomicAdd(&a.counts[u], 1);
+            if (slot < a.cap) a.surv[(size_t)u * a.cap + slot] = key;
+          }
+        }
+      }
     } else {
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
@@ -183,6 +210,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
     __syncthreads();
     buf ^= 1;
   }
+  if (MODE == 2)
+    for (int u = threadIdx.x; u < a.B; u += SCAN_THREADS) if (s_cnt[u]) atomicAdd(&a.counts[u], s_cnt[u]);
 }
 
 // ---- MSB-first radix select of the k-th largest 64-bit key among n (one CTA) ------------------------
@@ -296,7 +325,9 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(const unsigned long
   __syncthreads();
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const unsigned long long v = ku[i];
-    if (v >= kth) { const int slot = atomicAdd(&s_fill, 1); if (slot < kpow2) s_keys[slot] = v; }
+    // non-empty keys are unique, so exactly k of them are >= the k-th largest; key 0 (an empty slot of a list that
+    // held fewer than k entries) repeats and is never collected: the slots it would fill are zero already
+    if (v >= kth && v != 0ull) { const int slot = atomicAdd(&s_fill, 1); if (slot < kpow2) s_keys[slot] = v; }
   }
   __syncthreads();
   bitonic_sort_desc(s_keys, kpow2);
@@ -367,6 +398,16 @@ struct phx_corpus {
   cudaStream_t stream = nullptr;       // the stream the shard's work is enqueued on: its own, or the caller's
   cudaStream_t own_stream = nullptr;
   unsigned long long* keys_out = nullptr;   // set for one call by phx_corpus_topk_keys_device
+  // exact passes (the sampled pivot missed, or phx_corpus_set_exact): per-user threshold keys found by bisection
+  bool exact = false;
+  unsigned long long* thr = nullptr;        // device [256]
+  long long exact_runs = 0;                 // calls completed through the exact passes
+  int reran = 0;                            // set by a sync that had to redo the last call exactly
+  // the last top-k call, kept so that phx_corpus_sync can redo it exactly when its status says the pivot missed
+  struct LastCall {
+    bool valid = false; const float* users = nullptr; int B = 0, k = 0; long long row_begin = 0, row_end = 0;
+    float* scores = nullptr; long long* ids = nullptr; unsigned long long* keys = nullptr;
+  } last;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   std::string err;
 };
@@ -375,7 +416,13 @@ namespace {
 
 template <int NT>
 phx_status launch_scan(phx_corpus* c, const ScanArgs& a, int mode, int grid, size_t smem) {
-  if (mode == 0) {
+  if (mode == 2) {
+    PHX_CUDA_TRY(cudaFuncSetAttribute(scan_kernel<NT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), c->err);
+    scan_kernel<NT, 2><<<grid, SCAN_THREADS, smem, c->stream>>>(a);
+  } else if (mode == 3) {
+    PHX_CUDA_TRY(cudaFuncSetAttribute(scan_kernel<NT, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), c->err);
+    scan_kernel<NT, 3><<<grid, SCAN_THREADS, smem, c->stream>>>(a);
+  } else if (mode == 0) {
     PHX_CUDA_TRY(cudaFuncSetAttribute(scan_kernel<NT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), c->err);
     scan_kernel<NT, 0><<<grid, SCAN_THREADS, smem, c->stream>>>(a);
   } else {
@@ -387,11 +434,61 @@ phx_status launch_scan(phx_corpus* c, const ScanArgs& a, int mode, int grid, siz
 }
 
 phx_status run_scan(phx_corpus* c, const ScanArgs& a, int mode, int grid) {
-  const size_t smem = ((size_t)a.Bpad + 2 * TILE_ROWS) * (a.dim + 8) * 2 + (size_t)a.Bpad * 4;
+  const size_t smem = ((size_t)a.Bpad + 2 * TILE_ROWS) * (a.dim + 8) * 2 + (size_t)a.Bpad * (4 + 8 + 4);   // + pivots, threshold keys, counts
   if (smem > 200 * 1024) { c->err = "topk: query batch x dim does not fit shared memory"; return PHX_E_CAPACITY; }
   if (a.Bpad == 16) return launch_scan<1>(c, a, mode, grid, smem);
   if (a.Bpad == 64) return launch_scan<4>(c, a, mode, grid, smem);
   return launch_scan<16>(c, a, mode, grid, smem);
+}
+
+// The top-k of a window without any estimate: per user, bisection on the 64-bit key (bf16 score, then lower row) for a
+// threshold that at least k and at most `cap` rows reach, each step one counting scan of the window; then one collect
+// scan and the usual select.  Keys are unique, so the bisection always ends (at the latest with exactly k rows), whatever
+// the scores look like: many equal scores, clustered rows, a corpus of copies.  Host-driven and synchronous between
+// steps; a few tens of scans, for the calls the sampled pivot cannot serve.
+phx_status topk_exact(phx_corpus* c, ScanArgs a, int B, int k, float* scores_dev, long long* ids_dev) {
+  dispatch_note(DK_TOPK_EXACT);
+  const long long n_tiles = (a.rows + TILE_ROWS - 1) / TILE_ROWS;
+  const int grid = (int)(n_tiles < c->num_sms * 2 ? n_tiles : c->num_sms * 2);
+  a.Bpad = B <= 16 ? 16 : (B <= 64 ? 64 : 256);
+  a.thr = c->thr;
+  users_to_bf16_kernel<<<(a.Bpad * c->dim + 255) / 256, 256, 0, c->stream>>>(c->last.users, c->users_bf, B, a.Bpad, c->dim);
+  PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  std::vector<unsigned long long> lo(B, 0ull), hi(B, ~0ull), thr(B, 0ull);   // count(key >= lo) >= k > count(key >= hi)
+  std::vector<int> cnt(B, 0);
+  std::vector<char> done(B, 0);
+  for (int it = 0; it < 66; ++it) {
+    bool all = true;
+    for (int u = 0; u < B; ++u) {
+      if (!done[u]) { thr[u] = lo[u] + (hi[u] - lo[u]) / 2; all = false; }
+    }
+    if (all) break;
+    PHX_CUDA_TRY(cudaMemcpyAsync(c->thr, thr.data(), (size_t)B * 8, cudaMemcpyHostToDevice, c->stream), c->err);
+    PHX_CUDA_TRY(cudaMemsetAsync(c->counts, 0, 256 * 4, c->stream), c->err);
+    phx_status s = run_scan(c, a, 2, grid);
+    if (s) return s;
+    PHX_CUDA_TRY(cudaMemcpyAsync(cnt.data(), c->counts, (size_t)B * 4, cudaMemcpyDeviceToHost, c->stream), c->err);
+    PHX_CUDA_TRY(cudaStreamSynchronize(c->stream), c->err);
+    for (int u = 0; u < B; ++u) {
+      if (done[u]) continue;
+      if (cnt[u] >= k) { lo[u] = thr[u]; if (cnt[u] <= c->cap) done[u] = 1; }
+      else hi[u] = thr[u];
+      if (!done[u] && hi[u] - lo[u] <= 1) { thr[u] = lo[u]; done[u] = 1; }   // lo is the k-th largest key itself
+    }
+  }
+  for (int u = 0; u < B; ++u) if (!done[u]) { c->err = "topk: the exact passes did not converge"; return PHX_E_CAPACITY; }
+  PHX_CUDA_TRY(cudaMemcpyAsync(c->thr, thr.data(), (size_t)B * 8, cudaMemcpyHostToDevice, c->stream), c->err);
+  PHX_CUDA_TRY(cudaMemsetAsync(c->counts, 0, 256 * 4, c->stream), c->err);
+  PHX_CUDA_TRY(cudaMemsetAsync(c->status, 0, 4, c->stream), c->err);
+  phx_status s = run_scan(c, a, 3, grid);
+  if (s) return s;
+  const int kp2 = next_pow2(k);
+  select_kernel<<<B, SEL_THREADS, (size_t)kp2 * 8, c->stream>>>(c->surv, c->counts, 0, c->cap, k, kp2, scores_dev, ids_dev,
+                                                               c->status, c->keys_out);
+  PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  PHX_CUDA_TRY(cudaStreamSynchronize(c->stream), c->err);   // the host vectors above were the copies' sources
+  c->exact_runs++;
+  return PHX_OK;
 }
 
 }  // namespace
@@ -429,6 +526,7 @@ phx_status phx_corpus_create(int32_t device, int64_t rows, int32_t dim, int64_t 
   CU(cudaMalloc(&c->counts, 256 * 4));
   CU(cudaMalloc(&c->status, 4));
   CU(cudaMemset(c->status, 0, 4));
+  CU(cudaMalloc(&c->thr, 256 * 8));
   CU(cudaMalloc(&c->err_flag, 8));   // [0] flag, [1] wait limit in microseconds (0 = default)
   CU(cudaMemset(c->err_flag, 0, 8));
 #undef CU
@@ -450,7 +548,7 @@ void phx_corpus_destroy(phx_corpus* c) {
   cudaSetDevice(c->device);
   if (c->stream) cudaStreamSynchronize(c->stream);
   auto fr = [](void* p) { if (p) cudaFree(p); };
-  fr(c->data); fr(c->users_bf); fr(c->gmax); fr(c->pivot); fr(c->surv); fr(c->merge_keys); fr(c->counts); fr(c->status); fr(c->err_flag); fr(c->mask);
+  fr(c->data); fr(c->users_bf); fr(c->gmax); fr(c->pivot); fr(c->surv); fr(c->merge_keys); fr(c->counts); fr(c->status); fr(c->err_flag); fr(c->mask); fr(c->thr);
   if (c->ev0) cudaEventDestroy(c->ev0);
   if (c->ev1) cudaEventDestroy(c->ev1);
   if (c->own_stream) cudaStreamDestroy(c->own_stream);
@@ -534,7 +632,19 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
     map_corpus = &c->map_window;
   }
   const int Bpad = c->use_tc ? 256 : (B <= 16 ? 16 : (B <= 64 ? 64 : 256));
+  c->last.valid = true; c->last.users = users_dev; c->last.B = B; c->last.k = k; c->last.row_begin = row_begin;
+  c->last.row_end = row_end; c->last.scores = scores_dev; c->last.ids = (long long*)ids_dev; c->last.keys = c->keys_out;
   PHX_CUDA_TRY(cudaEventRecord(c->ev0, c->stream), c->err);
+  if (c->exact) {
+    ScanArgs xa;
+    xa.corpus = data; xa.users = c->users_bf; xa.rows = rows; xa.row_offset = roff; xa.dim = c->dim; xa.B = B; xa.Bpad = Bpad;
+    xa.stride = 1; xa.gmax = c->gmax; xa.n_groups = 0; xa.pivot = c->pivot; xa.surv = c->surv; xa.counts = c->counts; xa.cap = c->cap;
+    xa.mask = c->mask; xa.mask_row0 = row_begin;
+    phx_status xs = topk_exact(c, xa, B, k, scores_dev, (long long*)ids_dev);
+    if (xs) return xs;
+    PHX_CUDA_TRY(cudaEventRecord(c->ev1, c->stream), c->err);
+    return PHX_OK;
+  }
   users_to_bf16_kernel<<<(Bpad * c->dim + 255) / 256, 256, 0, c->stream>>>(users_dev, c->users_bf, B, Bpad, c->dim);
   PHX_CUDA_TRY(cudaGetLastError(), c->err);
   PHX_CUDA_TRY(cudaMemsetAsync(c->counts, 0, 256 * 4, c->stream), c->err);
@@ -568,6 +678,7 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
     j = (int)ceil(qg * (double)a.n_groups);
     if (j < 1) j = 1;
     phx_status s;
+    dispatch_note(c->use_tc ? DK_SCAN_TC : DK_SCAN_MMA);
     if (c->use_tc) s = tc_scan_launch(*map_corpus, c->map_users, ta, 0, c->num_sms, c->err_flag, c->stream, c->err);
     else s = run_scan(c, a, 0, (int)(sampled_tiles < c->num_sms * 2 ? sampled_tiles : c->num_sms * 2));
     if (s) return s;
@@ -576,6 +687,7 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
   PHX_CUDA_TRY(cudaGetLastError(), c->err);
   {
     phx_status s;
+    dispatch_note(c->use_tc ? DK_SCAN_TC : DK_SCAN_MMA);
     if (c->use_tc) s = tc_scan_launch(*map_corpus, c->map_users, ta, 1, c->num_sms, c->err_flag, c->stream, c->err);
     else s = run_scan(c, a, 1, (int)(n_tiles < c->num_sms * 2 ? n_tiles : c->num_sms * 2));
     if (s) return s;
@@ -621,6 +733,7 @@ phx_status phx_topk_merge_keys_device(phx_corpus* c, const uint64_t* keys_dev, i
   select_kernel<<<B, SEL_THREADS, (size_t)kp2 * 8, c->stream>>>(c->merge_keys, nullptr, P * k, P * k, k, kp2, out_scores_dev,
                                                                (long long*)out_ids_dev, c->status);
   PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  PHX_CUDA_TRY(cudaEventRecord(c->ev1, c->stream), c->err);
   return PHX_OK;
 }
 
@@ -647,6 +760,7 @@ phx_status phx_topk_merge_device(phx_corpus* c, const float* scores_dev, const i
   select_kernel<<<B, SEL_THREADS, (size_t)kp2 * 8, c->stream>>>(c->merge_keys, nullptr, P * k, P * k, k, kp2, out_scores_dev,
                                                                (long long*)out_ids_dev, c->status);
   PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  PHX_CUDA_TRY(cudaEventRecord(c->ev1, c->stream), c->err);
   return PHX_OK;
 }
 
@@ -741,6 +855,9 @@ phx_status phx_topk_merge_static(int32_t device, const float* scores_dev, const 
 phx_status phx_corpus_sync(phx_corpus* c) {
   if (!c) return PHX_E_ARG;
   cudaSetDevice(c->device);
+  // the last top-k / merge may have been enqueued on a caller's stream that is no longer the current one
+  // (phx_corpus_set_stream): wait for the event recorded behind it as well
+  PHX_CUDA_TRY(cudaEventSynchronize(c->ev1), c->err);
   PHX_CUDA_TRY(cudaStreamSynchronize(c->stream), c->err);
   int st = 0, ef = 0;
   PHX_CUDA_TRY(cudaMemcpy(&ef, c->err_flag, 4, cudaMemcpyDeviceToHost), c->err);
@@ -755,12 +872,47 @@ phx_status phx_corpus_sync(phx_corpus* c) {
     c->err = "topk merge: an id does not fit 32 bits; the entry was left out";
     return PHX_E_ARG;
   }
+  if (st != 0 && c->last.valid && !c->exact) {
+    // The sampled pivot missed for some query (fewer than k rows, or more than the survivor buffer holds, reached it):
+    // the call is done again with exact thresholds, into the same output buffers, before this sync returns.  The
+    // queries must still be where the call read them.
+    cudaMemset(c->status, 0, 4);
+    c->exact = true;
+    c->keys_out = c->last.keys;
+    const phx_status xs = phx_corpus_topk_window_device(c, c->last.users, c->last.B, c->last.k, c->last.row_begin, c->last.row_end,
+                                                        c->last.scores, (int64_t*)c->last.ids);
+    c->keys_out = nullptr;
+    c->exact = false;
+    if (xs) return xs;
+    c->reran = 1;
+    PHX_CUDA_TRY(cudaMemcpy(&st, c->status, 4, cudaMemcpyDeviceToHost), c->err);
+  }
   if (st != 0) {
     cudaMemset(c->status, 0, 4);
     c->err = std::string("topk: survivor list ") + ((st & 2) ? "overflowed its capacity" : "held fewer than k rows") +
              " (pivot estimate off for this corpus); result withheld";
     return PHX_E_CAPACITY;
   }
+  return PHX_OK;
+}
+
+phx_status phx_corpus_finish(phx_corpus* c, int32_t* reran_out) {
+  if (!c) return PHX_E_ARG;
+  c->reran = 0;
+  const phx_status s = phx_corpus_sync(c);
+  if (reran_out) *reran_out = c->reran;
+  return s;
+}
+
+phx_status phx_corpus_set_exact(phx_corpus* c, int32_t on) {
+  if (!c) return PHX_E_ARG;
+  c->exact = on != 0;
+  return PHX_OK;
+}
+
+phx_status phx_corpus_exact_runs(phx_corpus* c, int64_t* n) {
+  if (!c || !n) return PHX_E_ARG;
+  *n = c->exact_runs;
   return PHX_OK;
 }
 

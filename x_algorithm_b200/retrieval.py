@@ -89,6 +89,21 @@ class CorpusShard:
     def sync(self):
         self._check(lib.phx_corpus_sync(self._h))
 
+    def finish(self) -> bool:
+        """Wait for the shard's work; True when the last top-k had to be done again with exact thresholds (its output
+        buffers then hold the exact answer)."""
+        r = C.c_int32()
+        self._check(lib.phx_corpus_finish(self._h, C.byref(r)))
+        return bool(r.value)
+
+    def set_exact(self, on: bool):
+        self._check(lib.phx_corpus_set_exact(self._h, int(bool(on))))
+
+    def exact_runs(self) -> int:
+        n = C.c_int64()
+        self._check(lib.phx_corpus_exact_runs(self._h, C.byref(n)))
+        return int(n.value)
+
     def last_device_ms(self) -> float:
         ms = C.c_float()
         self._check(lib.phx_corpus_last_device_ms(self._h, C.byref(ms)))
@@ -134,30 +149,53 @@ class Retriever:
     def __init__(self, shards: Sequence[CorpusShard]):
         self.shards = list(shards)
 
-    def retrieve(self, users, k: int):
+    def retrieve(self, users, k: int, check: bool = True):
         """Top-k rows of the whole corpus for users f32 [B, dim] (CUDA tensor) -> (scores f32 [B,k], rows int64 [B,k]).
         Everything is enqueued on torch's current stream - per-shard top-k as 64-bit keys, one all-gather of those
-        keys, the merge - and nothing waits on the host: the caller synchronises when it reads the result."""
+        keys, the merge - with no host synchronisation in between.  check=True (default) then waits for the shards and,
+        if the sampled pivot missed on any shard of any rank, takes that shard's exact list and merges again: the
+        answer is always the exhaustive top-k.  check=False returns at once; the caller owns the check
+        (CorpusShard.finish) before it trusts the result."""
         import torch
         B = users.shape[0]
         dev = users.device
         P = len(self.shards)
         stream = torch.cuda.current_stream(dev).cuda_stream
-        keys = torch.empty((P, B, k), dtype=torch.int64, device=dev)
-        for p, sh in enumerate(self.shards):
-            sh.set_stream(stream)
-            sh.topk_keys_device(users, B, k, keys[p])
         dist = torch.distributed
-        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
-            W = dist.get_world_size()
-            gk = torch.empty((W * P, B, k), dtype=torch.int64, device=dev)
-            dist.all_gather_into_tensor(gk, keys)
-            keys, P = gk, W * P
+        multi = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+        keys = torch.empty((P, B, k), dtype=torch.int64, device=dev)
         out_s = torch.empty((B, k), dtype=torch.float32, device=dev)
         out_i = torch.empty((B, k), dtype=torch.int64, device=dev)
-        self.shards[0].merge_keys_device(keys, P, B, k, out_s, out_i)
         for sh in self.shards:
-            sh.set_stream(None)     # back to the shard's own stream: the caller's stream may not outlive this call
+            sh.set_stream(stream)
+
+        def gather_and_merge():
+            all_keys, n = keys, P
+            if multi:
+                W = dist.get_world_size()
+                all_keys = torch.empty((W * P, B, k), dtype=torch.int64, device=dev)
+                dist.all_gather_into_tensor(all_keys, keys)
+                n = W * P
+            self.shards[0].merge_keys_device(all_keys, n, B, k, out_s, out_i)
+
+        try:
+            for p, sh in enumerate(self.shards):
+                sh.topk_keys_device(users, B, k, keys[p])
+            gather_and_merge()
+            if check:
+                redo = False
+                for sh in self.shards:
+                    redo = sh.finish() or redo          # an exact re-run rewrites keys[p] in place
+                if multi:
+                    flag = torch.tensor([1 if redo else 0], dtype=torch.int32, device=dev)
+                    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+                    redo = bool(flag.item())
+                if redo:
+                    gather_and_merge()
+                    self.shards[0].sync()
+        finally:
+            for sh in self.shards:
+                sh.set_stream(None)     # back to the shard's own stream: the caller's stream may not outlive this call
         return out_s, out_i
 
     def user_vector(self, tower, history):
