@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 
 from oracle import phoenix_oracle as po
+from helpers import rel_l2
 
 G = os.path.join(os.path.dirname(__file__), "golden")
 
@@ -384,3 +385,118 @@ def test_topk_key_form_orders_like_score_then_row():
     assert np.array_equal(ids[order], ids[want])
     s2, i2 = po.merge_topk_keys([keys[None]], len(sc))
     assert np.array_equal(i2[0], ids[want]) and np.array_equal(np.abs(s2[0]), np.abs(sc[want]))
+
+
+# ---- the composed model: outputs of the reference's own class bodies (tests/golden/gen_golden_model.py) -----------------
+
+def _model_golden():
+    return np.load(os.path.join(os.path.dirname(__file__), "golden", "model_golden.npz"))
+
+
+def test_scales_and_ffn_sizes_equal_the_reference_functions():
+    """ScaleConfig.input_scale / output_scale / attn_output_scale (scaling.py:40-47) and ffn_size (utils/utils.py:37-52),
+    executed from the reference source."""
+    g = _model_golden()
+    want = g["scales"]
+    got = [po.input_scale(128), po.output_scale(128), po.attn_output_scale(64), po.input_scale(512), po.output_scale(512),
+           po.attn_output_scale(32)]
+    np.testing.assert_allclose(got, want, rtol=1e-15)
+    sizes = [po.ModelConfig(emb_size=128, widening_factor=4.0).ffn_size, po.ModelConfig(emb_size=100, widening_factor=2.0).ffn_size,
+             po.ModelConfig(emb_size=512, widening_factor=4.0).ffn_size]
+    np.testing.assert_array_equal(sizes, g["ffn_sizes"])
+
+
+@pytest.mark.parametrize("name", ["plain", "gqa_qknorm", "primer"])
+def test_decoder_layers_equal_the_reference_classes(name):
+    """Two decoder layers in fp32 against the reference's DecoderLayer / MHABlock / MultiHeadAttention / DenseBlock /
+    RMSNorm / Linear executed from source (transformer.py:443-618, 160-245, 247-387; layers.py:108-357;
+    normalization.py:51-122; linear_layer.py:52-91) with its plain candidate-isolation attention: merged QKV layout,
+    qk-norm before RoPE, RoPE on positions min(t, S), attention scale and cap, residuals, primer post-norms, GELU-tanh
+    FFN.  Grouped-query heads, both cap methods."""
+    g = _model_golden()
+    B, S, C, D, Hq, Hkv, dh, F, qkn, primer, tanh_cap = (int(v) for v in g[f"{name}_dims"])
+    wf, cap = (float(v) for v in g[f"{name}_cap"])
+    x = g[f"{name}_x"]
+    T = S + C
+    seg = np.where(np.arange(T) < S, 1, -1).astype(np.int32)[None].repeat(B, 0)
+    positions = np.minimum(np.arange(T), S).astype(np.float32)[None].repeat(B, 0)
+    names = {"pre_attn_norm": "pre_attn_norm.scale", "w_qkv": "qkv.w", "w_out": "out.w", "pre_ffn_norm": "pre_ffn_norm.scale",
+             "w_up": "up_proj.w", "w_down": "down_proj.w", "q_norm": "q_norm.scale", "k_norm": "k_norm.scale",
+             "post_attn_norm": "post_attn_norm.scale", "post_ffn_norm": "post_ffn_norm.scale"}
+    w = {}
+    for l in range(2):
+        for mine, theirs in names.items():
+            key = f"{name}_l{l}_{theirs}"
+            if key in g.files:
+                w[f"layer{l}.{mine}"] = g[key]
+    for L in (1, 2):
+        cfg = po.ModelConfig(emb_size=D, num_layers=L, num_q_heads=Hq, num_kv_heads=Hkv, key_size=dh, widening_factor=wf,
+                             history_len=S, num_candidates=C, qk_norm=bool(qkn), primer_norm=bool(primer),
+                             attn_logit_cap=cap, attn_logit_cap_method="tanh" if tanh_cap else "soft_sign", compute="fp32")
+        assert cfg.ffn_size == F
+        got = po.transformer_trunk(cfg, w, x, seg, positions, po.ranker_mask(seg))
+        want = g[f"{name}_l{L - 1}_out"]
+        assert rel_l2(got, want) < 2e-5, (name, L, rel_l2(got, want))
+        assert np.abs(got - want).max() < 1e-4 * np.abs(want).max()
+
+
+def test_heads_equal_the_reference_methods():
+    """final_layer_norm -> decode / decode_continuous -> inference rescale (recsys_model.py:4792-4796, 3557-3560,
+    3756-3846, 712-733) executed from the reference source: logits before the output scale, the sigmoid (mae) dwell
+    head before and after its rescale by norm_scale = 30."""
+    g = _model_golden()
+    D, V = g["heads_unembed"].shape
+    cfg = po.ModelConfig(emb_size=D, num_actions=V, num_continuous=1, compute="fp32", dwell_norm_scale=30.0)
+    w = {"final_norm": g["heads_final_gain"], "unembed": g["heads_unembed"], "cont_unembed": g["heads_cont_unembed"][:, :1]}
+    normed = po.final_norm(cfg, w, g["heads_x"])
+    assert rel_l2(normed, g["heads_normed"]) < 2e-6
+    assert rel_l2(po.decode_logits(cfg, w, normed), g["heads_logits"]) < 2e-5
+    lp, cont, logits = po.decode_heads(cfg, w, normed)
+    assert rel_l2(logits, g["heads_logits"] * np.float32(po.output_scale(D))) < 2e-5
+    assert rel_l2(cont[..., 0], g["heads_cont_inference"][..., 0]) < 2e-5
+    assert rel_l2(cont[..., 0] / 30.0, g["heads_cont"][..., 0]) < 2e-5          # the activation before the rescale
+    np.testing.assert_allclose(np.exp(lp.astype(np.float64)), 1.0 / (1.0 + np.exp(-logits.astype(np.float64))), rtol=1e-6)
+    # the other two golden heads pin the generator's reading of the config rules: softplus stays unscaled, a binary
+    # sigmoid head is not rescaled
+    np.testing.assert_array_equal(g["heads_cont"][..., 1:], g["heads_cont_inference"][..., 1:])
+
+
+def test_user_pooling_equals_the_reference_lines():
+    """Masked mean and L2 normalisation of user_representation (recsys_two_tower_model.py:2187-2200), executed from the
+    reference source: a full user, a padded one, and one without any valid position (zeros)."""
+    g = _model_golden()
+    assert float(g["pool_eps"][0]) == 1e-12
+    got = po.pool_users(g["pool_x"], g["pool_mask"])
+    np.testing.assert_allclose(got, g["pool_out"], rtol=2e-6, atol=1e-7)
+    assert (got[2] == 0).all()
+
+
+def test_sharded_window_topk_and_merge_equal_the_reference_function():
+    """strided_dataset_top_k (recsys_two_tower_model.py:193-221) executed from the reference source on four shards with
+    an emulated all-gather: window per shard, rows outside the window at the minimum, shard-major row numbers, merge
+    with ties to the earlier list position.  Then the same answer from the pieces the GPU tests use: per-shard `top_k`
+    of the masked window and `merge_top_k` by (score desc, row asc) - the two orders agree because the shard-major
+    numbering makes 'earlier in the concatenation' and 'lower row' the same thing."""
+    g = _model_golden()
+    scores, ranges, caps, k = g["topk_scores"], g["topk_ranges"], [int(c) for c in g["topk_caps"]], int(g["topk_k"][0])
+    P, B, rows_local = scores.shape
+    res = po.strided_dataset_top_k([scores[s] for s in range(P)], ranges, caps, k)
+    for d in range(len(caps)):
+        np.testing.assert_array_equal(res[d][0], g[f"topk_rows_{d}"])
+        np.testing.assert_array_equal(res[d][1], g[f"topk_scores_{d}"])
+        # from the pieces: windows as -inf masks, ids shard-major, merge by (score desc, id asc)
+        lists_s, lists_i = [], []
+        for s in range(P):
+            start, end = (int(ranges[d, 0]) - s + P - 1) // P, (int(ranges[d, 1]) - s + P - 1) // P
+            inside = (np.arange(rows_local) >= start) & (np.arange(rows_local) < end)
+            if inside.sum() == 0:
+                continue
+            kk = min(k, int(inside.sum()))
+            sc, idx = po.top_k(np.where(inside[None], scores[s], -np.inf).astype(np.float32), kk, row_offset=s * rows_local)
+            lists_s.append(sc); lists_i.append(idx)
+        ms, mi = po.merge_top_k(lists_s, lists_i, min(k, caps[d], sum(x.shape[1] for x in lists_s)))
+        valid = g[f"topk_scores_{d}"] > np.finfo(np.float32).min       # the reference pads short windows with masked rows
+        n = int(valid[0].sum())
+        assert (valid.sum(axis=1) == n).all() and n == ms.shape[1] or n < ms.shape[1]
+        np.testing.assert_array_equal(mi[:, :n], g[f"topk_rows_{d}"][:, :n])
+        np.testing.assert_array_equal(ms[:, :n], g[f"topk_scores_{d}"][:, :n])
