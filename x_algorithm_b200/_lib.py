@@ -141,6 +141,16 @@ SIGNATURES = {
     "phx_topk_merge_device": (C.c_int32, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, _P, _P]),
     "phx_topk_merge_static": (C.c_int32, [C.c_int32, _P, _P, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P]),
     "phx_topk_merge_static_status": (C.c_int32, [C.c_int32, _P, C.POINTER(C.c_int32)]),
+    "phx_comm_unique_id": (C.c_int32, [_P]),
+    "phx_comm_create": (C.c_int32, [_P, C.c_int32, C.c_int32, C.c_int32, C.POINTER(_P)]),
+    "phx_comm_destroy": (None, [_P]),
+    "phx_comm_last_error": (C.c_char_p, [_P]),
+    "phx_comm_info": (C.c_int32, [_P, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "phx_comm_barrier": (C.c_int32, [_P, _P]),
+    "phx_retrieve_topk": (C.c_int32, [_P, _P, _P, C.c_int32, C.c_int32, _P, _P, _P]),
+    "phx_gather_sharded_setup": (C.c_int32, [_P, _P, C.c_int64, C.c_double]),
+    "phx_gather_sum_sharded": (C.c_int32, [_P, _P, C.c_int32, _P, C.c_int64, _P, _P]),
+    "phx_gather_sharded_phase_ms": (C.c_int32, [_P, C.POINTER(C.c_float)]),
     "phx_corpus_sync": (C.c_int32, [_P]),
     "phx_corpus_finish": (C.c_int32, [_P, C.POINTER(C.c_int32)]),
     "phx_corpus_set_exact": (C.c_int32, [_P, C.c_int32]),

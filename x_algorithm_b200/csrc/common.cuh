@@ -246,6 +246,10 @@ phx_status table_fill_launch(bf16* table, long long row0, long long rows, int wi
 phx_status corpus_fill_launch(bf16* rows_ptr, long long global_row0, long long rows, int dim, uint32_t seed,
                               cudaStream_t stream, std::string& err);
 
+// grouping of row requests by owning rank (shard_exchange.cu); n_dev: optional device-side request count (<= n_req)
+phx_status shard_bucket_launch(const int* rows_dev, long long n_req, const int* n_dev, long long rows_per_shard, int world,
+                               int* counts_dev, int* cursor_dev, int* send_rows_dev, int* pos_dev, cudaStream_t stream);
+
 // ---- elementwise --------------------------------------------------------------------------------
 // y = bf16(norm(x) * gain); with `res` non-null y = bf16(res + bf16(norm(x) * gain)).  y may alias x or res.
 phx_status rmsnorm_launch(const bf16* x, const float* gain, bf16* y, const bf16* res, long long rows, int D, float eps,

@@ -13,6 +13,7 @@
 #include <mutex>
 #include <vector>
 
+#include "comm.cuh"
 #include "common.cuh"
 
 namespace phx {
@@ -1657,6 +1658,178 @@ phx_status phx_gemm_device(int32_t device, const uint16_t* A, const uint16_t* Wt
   cudaEventDestroy(e0); cudaEventDestroy(e1);
   if (s) set_global_error(err);
   return s;
+}
+
+// ---- multi-hash gather-sum over the row-sharded table, exchange owned by the library -------------------------------------
+namespace {
+struct GatherWs {
+  int W = 1, H = 0, width = 0;
+  long long max_req = 0, shard_rows = 0, table_slots = 0, recv_cap = 0;
+  int *rows = nullptr, *slot = nullptr, *urows = nullptr, *upos = nullptr, *pos = nullptr, *send_rows = nullptr;
+  int *counts = nullptr, *cursor = nullptr, *nu = nullptr, *counts_all = nullptr, *recv_rows = nullptr;
+  int* counts_host = nullptr;
+  unsigned long long* table = nullptr;
+  bf16 *gathered = nullptr, *landing = nullptr;
+  bf16* peer_landing[PHX_MAX_SHARDS] = {nullptr};
+  float phase_ms[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  cudaEvent_t ev[9] = {};
+};
+
+void gather_ws_free(void* p) {
+  GatherWs* w = static_cast<GatherWs*>(p);
+  for (int r = 0; r < w->W; ++r)
+    if (w->peer_landing[r] && w->peer_landing[r] != w->landing) cudaIpcCloseMemHandle(w->peer_landing[r]);
+  for (void* q : {(void*)w->rows, (void*)w->slot, (void*)w->urows, (void*)w->upos, (void*)w->pos, (void*)w->send_rows, (void*)w->counts,
+                  (void*)w->cursor, (void*)w->nu, (void*)w->counts_all, (void*)w->recv_rows, (void*)w->table, (void*)w->gathered,
+                  (void*)w->landing})
+    if (q) cudaFree(q);
+  if (w->counts_host) cudaFreeHost(w->counts_host);
+  for (auto e : w->ev) if (e) cudaEventDestroy(e);
+  delete w;
+}
+}  // namespace
+
+phx_status phx_gather_sharded_setup(phx_comm* cm, phx_engine* e, int64_t max_ids, double recv_factor) {
+  if (!cm || !e || max_ids <= 0 || recv_factor < 1.0) { set_global_error("phx_gather_sharded_setup: bad argument"); return PHX_E_ARG; }
+  if (e->table_world != cm->world || e->table_rank != cm->rank || e->device != cm->device) {
+    cm->err = "phx_gather_sharded_setup: the engine's table_world / table_rank / device do not match the communicator";
+    return PHX_E_ARG;
+  }
+  cudaSetDevice(e->device);
+  if (cm->gather_ws) { cm->gather_ws_free(cm->gather_ws); cm->gather_ws = nullptr; }
+  GatherWs* w = new GatherWs();
+  cm->gather_ws = w; cm->gather_ws_free = gather_ws_free;
+  const int W = cm->world, H = e->cfg.item.num_hashes;
+  w->W = W; w->H = H; w->width = e->D; w->shard_rows = e->shard_rows;
+  w->max_req = (long long)max_ids * H;
+  w->table_slots = 2; while (w->table_slots < 2 * w->max_req) w->table_slots *= 2;
+  w->recv_cap = (long long)(recv_factor * (double)w->max_req) + 1;
+  const size_t nr = (size_t)w->max_req;
+#define GA(ptr, bytes) PHX_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&(ptr)), (bytes)), cm->err)
+  GA(w->rows, nr * 4); GA(w->slot, nr * 4); GA(w->urows, nr * 4); GA(w->upos, nr * 4); GA(w->pos, nr * 4); GA(w->send_rows, nr * 4);
+  GA(w->counts, 64 * 4); GA(w->cursor, 64 * 4); GA(w->nu, 4); GA(w->counts_all, ((size_t)W * W + 4) * 4);
+  GA(w->recv_rows, (size_t)w->recv_cap * 4); GA(w->table, (size_t)w->table_slots * 8);
+  GA(w->gathered, (size_t)w->recv_cap * w->width * 2); GA(w->landing, nr * w->width * 2);
+#undef GA
+  PHX_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&w->counts_host), ((size_t)W * W + 4) * 4), cm->err);
+  for (auto& ev : w->ev) PHX_CUDA_TRY(cudaEventCreate(&ev), cm->err);
+  // every rank maps every other rank's landing buffer: handles travel through one all-gather
+  w->peer_landing[cm->rank] = w->landing;
+  if (W > 1) {
+    cudaIpcMemHandle_t mine;
+    PHX_CUDA_TRY(cudaIpcGetMemHandle(&mine, w->landing), cm->err);
+    uint8_t* hbuf = nullptr;
+    PHX_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&hbuf), (size_t)(W + 1) * sizeof(mine)), cm->err);
+    PHX_CUDA_TRY(cudaMemcpy(hbuf + (size_t)W * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice), cm->err);
+    phx_status s = comm_check(cm, cm->api->AllGather(hbuf + (size_t)W * sizeof(mine), hbuf, sizeof(mine), ncclUint8, cm->comm, 0), "ncclAllGather (handles)");
+    if (s) { cudaFree(hbuf); return s; }
+    std::vector<cudaIpcMemHandle_t> all(W);
+    cudaError_t ce = cudaMemcpy(all.data(), hbuf, (size_t)W * sizeof(mine), cudaMemcpyDeviceToHost);   // waits for the collective
+    cudaFree(hbuf);
+    if (ce != cudaSuccess) { cm->err = std::string("handle exchange: ") + cudaGetErrorString(ce); return PHX_E_CUDA; }
+    for (int r = 0; r < W; ++r) {
+      if (r == cm->rank) continue;
+      void* p = nullptr;
+      PHX_CUDA_TRY(cudaIpcOpenMemHandle(&p, all[r], cudaIpcMemLazyEnablePeerAccess), cm->err);
+      w->peer_landing[r] = static_cast<bf16*>(p);
+    }
+  }
+  return phx_comm_barrier(cm, nullptr);
+}
+
+phx_status phx_gather_sum_sharded(phx_comm* cm, phx_engine* e, int32_t family, const int64_t* ids_dev, int64_t n, uint16_t* out_dev,
+                                  void* stream) {
+  if (!cm || !e || family < 0 || family > 3 || n < 0 || (n > 0 && (!ids_dev || !out_dev))) { set_global_error("phx_gather_sum_sharded: bad argument"); return PHX_E_ARG; }
+  GatherWs* w = static_cast<GatherWs*>(cm->gather_ws);
+  if (!w) { cm->err = "phx_gather_sum_sharded: call phx_gather_sharded_setup first"; return PHX_E_STATE; }
+  const int W = w->W, H = w->H, rank = cm->rank;
+  const long long nreq = n * H;
+  if (nreq > w->max_req) { cm->err = "phx_gather_sum_sharded: more ids than the set-up allowed for"; return PHX_E_CAPACITY; }
+  cudaSetDevice(e->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  long long off[5];
+  region_offsets(e->cfg, &off[0], &off[1], &off[2], &off[3], &off[4]);
+  const phx_hash_family* fams[4] = {&e->cfg.user, &e->cfg.item, &e->cfg.author, &e->cfg.ip};
+  phx_status s;
+  auto mark = [&](int i) { cudaEventRecord(w->ev[i], st); };
+  mark(0);
+  // requester: ids -> rows -> distinct rows -> grouped by owner; nothing here waits on the host
+  if ((s = hash_ids_launch(to_dev(*fams[family], (int)off[family]), (const long long*)ids_dev, n, w->rows, st, cm->err))) return s;
+  if ((s = phx_shard_dedup(w->rows, nreq, (uint64_t*)w->table, w->table_slots, w->slot, w->urows, w->nu, st))) { cm->err = phx_global_error(); return s; }
+  if ((s = shard_bucket_launch(w->urows, nreq, w->nu, w->shard_rows, W, w->counts, w->cursor, w->send_rows, w->upos, st))) { cm->err = phx_global_error(); return s; }
+  if ((s = phx_shard_dedup_expand(w->slot, (const uint64_t*)w->table, w->upos, nreq, w->pos, st))) { cm->err = phx_global_error(); return s; }
+  mark(1);
+  // every rank learns every rank's per-owner counts: one all-gather, one copy to the host, the only host wait
+  if ((s = comm_check(cm, cm->api->AllGather(w->counts, w->counts_all, W, ncclInt32, cm->comm, st), "ncclAllGather (counts)"))) return s;
+  PHX_CUDA_TRY(cudaMemcpyAsync(w->counts_host, w->counts_all, (size_t)W * W * 4, cudaMemcpyDeviceToHost, st), cm->err);
+  PHX_CUDA_TRY(cudaStreamSynchronize(st), cm->err);
+  mark(2);
+  const int* all = w->counts_host;                 // all[requester * W + owner]
+  long long send_off[PHX_MAX_SHARDS + 1], recv_off[PHX_MAX_SHARDS + 1], their_off[PHX_MAX_SHARDS];
+  send_off[0] = recv_off[0] = 0;
+  for (int p = 0; p < W; ++p) {
+    send_off[p + 1] = send_off[p] + all[rank * W + p];
+    recv_off[p + 1] = recv_off[p] + all[p * W + rank];
+    long long o = 0;
+    for (int q = 0; q < rank; ++q) o += all[p * W + q];
+    their_off[p] = o;                              // where requester p keeps the bucket of rows it asked of this rank
+  }
+  if (recv_off[W] > w->recv_cap) {
+    cm->err = "phx_gather_sum_sharded: this rank was asked for " + std::to_string(recv_off[W]) + " rows, the set-up allows " +
+              std::to_string(w->recv_cap) + " (raise recv_factor)";
+    return PHX_E_CAPACITY;
+  }
+  // row numbers to their owners
+  if ((s = comm_check(cm, cm->api->GroupStart(), "ncclGroupStart"))) return s;
+  for (int i = 1; i < W; ++i) {
+    const int to = (rank + i) % W, from = (rank - i + W) % W;
+    if (all[rank * W + to] > 0 && (s = comm_check(cm, cm->api->Send(w->send_rows + send_off[to], (size_t)all[rank * W + to], ncclInt32, to, cm->comm, st), "ncclSend (row numbers)"))) return s;
+    if (all[from * W + rank] > 0 && (s = comm_check(cm, cm->api->Recv(w->recv_rows + recv_off[from], (size_t)all[from * W + rank], ncclInt32, from, cm->comm, st), "ncclRecv (row numbers)"))) return s;
+  }
+  if ((s = comm_check(cm, cm->api->GroupEnd(), "ncclGroupEnd"))) return s;
+  if (all[rank * W + rank] > 0)
+    PHX_CUDA_TRY(cudaMemcpyAsync(w->recv_rows + recv_off[rank], w->send_rows + send_off[rank], (size_t)all[rank * W + rank] * 4, cudaMemcpyDeviceToDevice, st), cm->err);
+  mark(3);
+  // owner: per requester, gather its rows into a send block; the copy engines carry each finished block into the
+  // requester's landing buffer (one copy per peer) while the next block is gathered
+  const size_t row_bytes = (size_t)w->width * 2;
+  int used = 0;
+  for (int i = 1; i < W; ++i) {
+    const int p = (rank + i) % W;
+    const long long cnt = all[p * W + rank];
+    if (cnt == 0) continue;
+    bf16* block = w->gathered + recv_off[p] * w->width;
+    if ((s = phx_shard_gather_rows((const uint16_t*)e->table, w->shard_rows, w->recv_rows + recv_off[p], cnt, w->width, (uint16_t*)block, st))) { cm->err = phx_global_error(); return s; }
+    PHX_CUDA_TRY(cudaEventRecord(cm->ev_fork, st), cm->err);
+    cudaStream_t cs = cm->side[used % 4];
+    PHX_CUDA_TRY(cudaStreamWaitEvent(cs, cm->ev_fork, 0), cm->err);
+    PHX_CUDA_TRY(cudaMemcpyAsync(w->peer_landing[p] + their_off[p] * w->width, block, (size_t)cnt * row_bytes, cudaMemcpyDefault, cs), cm->err);
+    ++used;
+  }
+  if (all[rank * W + rank] > 0 &&
+      (s = phx_shard_gather_rows((const uint16_t*)e->table, w->shard_rows, w->recv_rows + recv_off[rank], all[rank * W + rank], w->width,
+                                 (uint16_t*)(w->landing + their_off[rank] * w->width), st))) { cm->err = phx_global_error(); return s; }
+  for (int i = 0; i < (used < 4 ? used : 4); ++i) {
+    PHX_CUDA_TRY(cudaEventRecord(cm->ev_join[i], cm->side[i]), cm->err);
+    PHX_CUDA_TRY(cudaStreamWaitEvent(st, cm->ev_join[i], 0), cm->err);
+  }
+  mark(4);
+  // every rank's copies have landed before any rank sums
+  if (W > 1 && (s = comm_check(cm, cm->api->AllReduce(cm->fence, cm->fence, 1, ncclInt32, ncclSum, cm->comm, st), "ncclAllReduce (fence)"))) return s;
+  mark(5);
+  if ((s = phx_shard_sum_rows((const uint16_t*)w->landing, w->pos, n, H, w->width, out_dev, st))) { cm->err = phx_global_error(); return s; }
+  mark(6);
+  return PHX_OK;
+}
+
+// Device time of the phases of the last phx_gather_sum_sharded call on this rank (waits for it): hash + dedup + bucket,
+// counts exchange, row numbers, owner gather + copies, fence, sum.  Six floats.
+phx_status phx_gather_sharded_phase_ms(phx_comm* cm, float* ms6) {
+  if (!cm || !ms6 || !cm->gather_ws) return PHX_E_ARG;
+  GatherWs* w = static_cast<GatherWs*>(cm->gather_ws);
+  PHX_CUDA_TRY(cudaEventSynchronize(w->ev[6]), cm->err);
+  for (int i = 0; i < 6; ++i) PHX_CUDA_TRY(cudaEventElapsedTime(&ms6[i], w->ev[i], w->ev[i + 1]), cm->err);
+  return PHX_OK;
 }
 
 }  // extern "C"

@@ -26,9 +26,12 @@ constexpr int SX_THREADS = 256;
 constexpr int SX_PER_THREAD = 8;
 constexpr int SX_MAX_WORLD = 64;
 
-__global__ void __launch_bounds__(SX_THREADS) sx_count_kernel(const int* __restrict__ rows, long long n, long long rows_per_shard,
-                                                              int world, int* __restrict__ counts) {
+// n_dev (optional): the request count lives on the device (the number of distinct rows a dedup pass found); n is then
+// its upper bound, which sizes the grid
+__global__ void __launch_bounds__(SX_THREADS) sx_count_kernel(const int* __restrict__ rows, long long n, const int* __restrict__ n_dev,
+                                                              long long rows_per_shard, int world, int* __restrict__ counts) {
   __shared__ int hist[SX_MAX_WORLD];
+  if (n_dev && *n_dev < n) n = *n_dev;
   if (threadIdx.x < world) hist[threadIdx.x] = 0;
   __syncthreads();
   const long long base = (long long)blockIdx.x * SX_THREADS * SX_PER_THREAD;
@@ -51,11 +54,12 @@ __global__ void sx_scan_kernel(const int* __restrict__ counts, int world, int* _
 
 // Each block reserves a range in every bucket for its own requests with one global atomic per owner, then places
 // them with shared-memory atomics.  The order inside a bucket is arbitrary; `pos` records it.
-__global__ void __launch_bounds__(SX_THREADS) sx_scatter_kernel(const int* __restrict__ rows, long long n, long long rows_per_shard,
-                                                                int world, int* __restrict__ cursor, int* __restrict__ send_rows,
-                                                                int* __restrict__ pos) {
+__global__ void __launch_bounds__(SX_THREADS) sx_scatter_kernel(const int* __restrict__ rows, long long n, const int* __restrict__ n_dev,
+                                                                long long rows_per_shard, int world, int* __restrict__ cursor,
+                                                                int* __restrict__ send_rows, int* __restrict__ pos) {
   __shared__ int hist[SX_MAX_WORLD];
   __shared__ int gbase[SX_MAX_WORLD];
+  if (n_dev && *n_dev < n) n = *n_dev;
   if (threadIdx.x < world) hist[threadIdx.x] = 0;
   __syncthreads();
   const long long base = (long long)blockIdx.x * SX_THREADS * SX_PER_THREAD;
@@ -208,6 +212,22 @@ phx_status check_launch(const char* what) {
 }
 
 }  // namespace
+
+phx_status shard_bucket_launch(const int* rows_dev, long long n_req, const int* n_dev, long long rows_per_shard, int world,
+                               int* counts_dev, int* cursor_dev, int* send_rows_dev, int* pos_dev, cudaStream_t st) {
+  if (!rows_dev || !counts_dev || !cursor_dev || !send_rows_dev || !pos_dev || n_req < 0 || rows_per_shard <= 0 || world < 1 ||
+      world > SX_MAX_WORLD)
+    return fail_arg("phx_shard_bucket: bad argument (world must be 1..64)");
+  if (cudaMemsetAsync(counts_dev, 0, sizeof(int32_t) * world, st) != cudaSuccess) return check_launch("phx_shard_bucket");
+  if (n_req > 0) {
+    const unsigned blocks = (unsigned)((n_req + SX_THREADS * SX_PER_THREAD - 1) / (SX_THREADS * SX_PER_THREAD));
+    sx_count_kernel<<<blocks, SX_THREADS, 0, st>>>(rows_dev, n_req, n_dev, rows_per_shard, world, counts_dev);
+    sx_scan_kernel<<<1, 32, 0, st>>>(counts_dev, world, cursor_dev);
+    sx_scatter_kernel<<<blocks, SX_THREADS, 0, st>>>(rows_dev, n_req, n_dev, rows_per_shard, world, cursor_dev, send_rows_dev, pos_dev);
+  }
+  return check_launch("phx_shard_bucket");
+}
+
 }  // namespace phx
 
 using namespace phx;
@@ -216,18 +236,8 @@ extern "C" {
 
 phx_status phx_shard_bucket(const int32_t* rows_dev, int64_t n_req, int64_t rows_per_shard, int32_t world, int32_t* counts_dev,
                             int32_t* cursor_dev, int32_t* send_rows_dev, int32_t* pos_dev, void* stream) {
-  if (!rows_dev || !counts_dev || !cursor_dev || !send_rows_dev || !pos_dev || n_req < 0 || rows_per_shard <= 0 || world < 1 ||
-      world > SX_MAX_WORLD)
-    return fail_arg("phx_shard_bucket: bad argument (world must be 1..64)");
-  cudaStream_t st = (cudaStream_t)stream;
-  if (cudaMemsetAsync(counts_dev, 0, sizeof(int32_t) * world, st) != cudaSuccess) return check_launch("phx_shard_bucket");
-  if (n_req > 0) {
-    const unsigned blocks = (unsigned)((n_req + SX_THREADS * SX_PER_THREAD - 1) / (SX_THREADS * SX_PER_THREAD));
-    sx_count_kernel<<<blocks, SX_THREADS, 0, st>>>(rows_dev, n_req, rows_per_shard, world, counts_dev);
-    sx_scan_kernel<<<1, 32, 0, st>>>(counts_dev, world, cursor_dev);
-    sx_scatter_kernel<<<blocks, SX_THREADS, 0, st>>>(rows_dev, n_req, rows_per_shard, world, cursor_dev, send_rows_dev, pos_dev);
-  }
-  return check_launch("phx_shard_bucket");
+  return shard_bucket_launch(rows_dev, n_req, nullptr, rows_per_shard, world, counts_dev, cursor_dev, send_rows_dev, pos_dev,
+                             (cudaStream_t)stream);
 }
 
 phx_status phx_shard_gather_rows(const uint16_t* shard_dev, int64_t shard_rows, const int32_t* local_rows_dev, int64_t m,

@@ -21,6 +21,7 @@
 #include <mutex>
 #include <vector>
 
+#include "comm.cuh"
 #include "common.cuh"
 #include "topk_scan.cuh"
 
@@ -366,6 +367,11 @@ __global__ void merge_keys_kernel(const float* __restrict__ scores, const long l
 }
 
 int next_pow2(int v) { int p = 1; while (p < v) p <<= 1; return p; }
+
+// one word per rank for the all-gather beside the lists: scan status in the low byte, the bounded-wait flag above it
+__global__ void pack_status_kernel(const int* status, const int* err_flag, int* out) {
+  *out = (*status & 0xFF) | ((*err_flag != 0) ? 0x100 : 0);
+}
 
 }  // namespace
 }  // namespace phx
@@ -734,6 +740,74 @@ phx_status phx_topk_merge_keys_device(phx_corpus* c, const uint64_t* keys_dev, i
                                                                (long long*)out_ids_dev, c->status);
   PHX_CUDA_TRY(cudaGetLastError(), c->err);
   PHX_CUDA_TRY(cudaEventRecord(c->ev1, c->stream), c->err);
+  return PHX_OK;
+}
+
+phx_status phx_retrieve_topk(phx_comm* cm, phx_corpus* c, const float* users_dev, int32_t B, int32_t k, float* scores_dev,
+                             int64_t* ids_dev, void* stream) {
+  if (!cm || !c || !users_dev || !scores_dev || !ids_dev) { set_global_error("phx_retrieve_topk: null argument"); return PHX_E_ARG; }
+  if (B <= 0 || B > c->max_queries || k <= 0 || k > c->max_k) { c->err = cm->err = "phx_retrieve_topk: B or k exceeds what the shard was created for"; return PHX_E_CAPACITY; }
+  if (k > c->rows) { c->err = cm->err = "phx_retrieve_topk: k exceeds the shard's rows"; return PHX_E_ARG; }
+  if (cm->device != c->device) { c->err = cm->err = "phx_retrieve_topk: communicator and shard live on different devices"; return PHX_E_ARG; }
+  cudaSetDevice(c->device);
+  const int W = cm->world;
+  const size_t per = (size_t)B * k;
+  if (per > cm->keys_cap) {
+    if (cm->keys_local) cudaFree(cm->keys_local);
+    if (cm->keys_all) cudaFree(cm->keys_all);
+    cm->keys_local = cm->keys_all = nullptr; cm->keys_cap = 0;
+    PHX_CUDA_TRY(cudaMalloc(&cm->keys_local, per * 8), cm->err);
+    PHX_CUDA_TRY(cudaMalloc(&cm->keys_all, per * 8 * W), cm->err);
+    cm->keys_cap = per;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaStream_t saved = c->stream;
+  c->stream = st;
+  struct Restore { phx_corpus* c; cudaStream_t s; ~Restore() { c->stream = s; c->keys_out = nullptr; c->exact = false; } } restore{c, saved};
+  int* my_word = cm->status_all + PHX_MAX_SHARDS;
+  auto shard_list = [&]() -> phx_status {
+    c->keys_out = cm->keys_local;
+    const phx_status s = phx_corpus_topk_window_device(c, users_dev, B, k, 0, c->rows, nullptr, nullptr);
+    c->keys_out = nullptr;
+    return s;
+  };
+  auto gather_and_merge = [&]() -> phx_status {
+    pack_status_kernel<<<1, 1, 0, st>>>(c->status, c->err_flag, my_word);
+    PHX_CUDA_TRY(cudaGetLastError(), cm->err);
+    phx_status s;
+    if ((s = comm_check(cm, cm->api->GroupStart(), "ncclGroupStart"))) return s;
+    if ((s = comm_check(cm, cm->api->AllGather(cm->keys_local, cm->keys_all, per, ncclUint64, cm->comm, st), "ncclAllGather (lists)"))) return s;
+    if ((s = comm_check(cm, cm->api->AllGather(my_word, cm->status_all, 1, ncclInt32, cm->comm, st), "ncclAllGather (status)"))) return s;
+    if ((s = comm_check(cm, cm->api->GroupEnd(), "ncclGroupEnd"))) return s;
+    if ((s = phx_topk_merge_keys_device(c, (const uint64_t*)cm->keys_all, W, B, k, scores_dev, ids_dev))) { cm->err = c->err; return s; }
+    PHX_CUDA_TRY(cudaMemcpyAsync(cm->status_host, cm->status_all, (size_t)W * sizeof(int), cudaMemcpyDeviceToHost, st), cm->err);
+    PHX_CUDA_TRY(cudaStreamSynchronize(st), cm->err);
+    return PHX_OK;
+  };
+  phx_status s;
+  if ((s = shard_list())) { cm->err = c->err; return s; }
+  if ((s = gather_and_merge())) return s;
+  int any = 0;
+  for (int r = 0; r < W; ++r) any |= cm->status_host[r];
+  if (any & 0x100) {
+    cudaMemsetAsync(c->err_flag, 0, sizeof(int), st);
+    c->err = cm->err = "phx_retrieve_topk: a bounded device-side wait ran out on some rank (scan pipeline)";
+    return PHX_E_TIMEOUT;
+  }
+  if (any & 3) {
+    // the sampled pivot missed on some shard: that shard takes the exact passes, every rank gathers and merges again
+    // (all ranks hold the same status words, so all take this branch together)
+    if (cm->status_host[cm->rank] & 3) {
+      PHX_CUDA_TRY(cudaMemsetAsync(c->status, 0, sizeof(int), st), cm->err);
+      c->exact = true;
+      s = shard_list();
+      c->exact = false;
+      if (s) { cm->err = c->err; return s; }
+    }
+    if ((s = gather_and_merge())) return s;
+    for (int r = 0; r < W; ++r)
+      if (cm->status_host[r] & 3) { c->err = cm->err = "phx_retrieve_topk: a shard's exact passes left a status behind"; return PHX_E_CAPACITY; }
+  }
   return PHX_OK;
 }
 
