@@ -127,6 +127,176 @@ def run_reference(args, rank: int):
     print(json.dumps(line), flush=True)
 
 
+def sharded_subrecords(args, rank, world, local_rank, steps, which=("gather", "retrieval", "exchange")):
+    """N > 1: the three sharded paths, each timed on the device (CUDA events, max over ranks) and checked against the
+    unsharded answer on the same GPU.  Returns a dict of sub-records for the JSON line (rank 0's copy is printed).
+      sharded_gather     multi-hash gather-sum, 8 x 2^24 x 256 bf16 tables (64 GiB) row-sharded over the ranks, 4 hashes,
+                         2^22 Zipf(1.1) ids per step split over the ranks, exchange by the library's communicator
+      sharded_retrieval  top-1000 of 256 queries over 100 M x 128 bf16 rows, row-sharded, per-shard scan + all-gather merge
+      tables_exchange    the headline ranking step over a row-sharded table, rows fetched by the bulk exchange"""
+    import torch
+    import torch.distributed as dist
+    import x_algorithm_b200 as px
+    from x_algorithm_b200 import comm as pc, synthetic
+    from x_algorithm_b200.parallel import shard_range
+    from x_algorithm_b200.retrieval import CorpusShard
+    dev = torch.device("cuda", local_rank)
+    peaks = measured_peaks()
+    box = [pc.unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    cm = pc.Communicator(box[0], rank, world, local_rank)
+    out = {}
+
+    def timed(fn, iters, warm=2):
+        """ms per call: events on torch's current stream around `iters` calls, max over ranks."""
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def all_true(flag):
+        t = torch.tensor([1.0 if flag else 0.0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t[0] > 0)
+
+    st = torch.cuda.current_stream().cuda_stream
+    # ---- sharded gather-sum ---------------------------------------------------------------------------------------
+    try:
+        if "gather" not in which:
+            raise KeyError("skipped")
+        width, hashes, log2_rows, total_ids = 256, 4, 25, 1 << 22
+        gcfg = dict(emb_size=width, num_layers=1, num_q_heads=width // 64, num_kv_heads=width // 64, key_size=64,
+                    history_len=1, num_candidates=1, max_batch=1, num_hashes=hashes, table_size=1 << log2_rows)
+        eng = px.PhoenixEngine(px.PhoenixConfig(table_world=world, table_rank=rank, **gcfg), local_rank)
+        eng.table_fill_synthetic(7, 1.0 / math.sqrt(width))
+        n = total_ids // world
+        sets = [torch.from_numpy(synthetic.zipf_ids(total_ids, np.random.Generator(np.random.PCG64(100 + i)), 1.1)
+                                 [rank * n:(rank + 1) * n].copy()).to(dev) for i in range(3)]
+        res = torch.empty((n, width), dtype=torch.int16, device=dev)
+        cm.gather_setup(eng, n, recv_factor=3.0)
+        it = [0]
+
+        def one():
+            cm.gather_sum(eng, 1 + it[0] % 2, sets[it[0] % 3], n, res, st)
+            it[0] += 1
+        ms = timed(one, 10)
+        phases = cm.gather_phase_ms()
+        last = it[0] - 1
+        whole = px.PhoenixEngine(px.PhoenixConfig(**gcfg), local_rank)
+        whole.table_fill_synthetic(7, 1.0 / math.sqrt(width))
+        want = torch.empty_like(res)
+        whole.gather_sum_device(1 + last % 2, sets[last % 3], n, want)
+        whole.sync()
+        local_ms = []
+        for _ in range(5):
+            whole.gather_sum_device(1, sets[0], n, want); whole.sync(); local_ms.append(whole.last_device_ms())
+        whole.gather_sum_device(1 + last % 2, sets[last % 3], n, want); whole.sync()
+        ok = all_true(torch.equal(res, want))
+        whole.close(); eng.close()
+        per_id = hashes * width * 2 + width * 2 + 8
+        gbs = per_id * total_ids / (ms * 1e-3) / 1e9
+        out["sharded_gather"] = dict(
+            ms=ms, ids_per_step=total_ids, table_gib=64.0, hashes=hashes, width=width, bytes_per_id=per_id,
+            achieved_gbs_aggregate=gbs, frac_of_aggregate_hbm=gbs / (peaks["hbm_gbs"] * world), matches_unsharded=ok,
+            one_gpu_share_ms=float(np.median(local_ms)),
+            note="one_gpu_share_ms = this rank's ids alone on an unsharded 64 GiB table on the same GPU (no exchange)",
+            phase_ms_rank0=dict(zip(["hash_dedup_bucket", "counts_exchange", "row_numbers", "owner_gather_copies", "fence", "sum"],
+                                    [round(x, 3) for x in phases])))
+    except Exception as e:  # a sub-record must not take the headline line down
+        out["sharded_gather"] = dict(error=repr(e))
+    # ---- sharded retrieval ----------------------------------------------------------------------------------------
+    try:
+        if "retrieval" not in which:
+            raise KeyError("skipped")
+        rows, dim, B, k = 100_000_000, 128, 256, 1000
+        lo, hi = shard_range(rows, world, rank)
+        sh = CorpusShard(hi - lo, dim, row_offset=lo, max_queries=B, max_k=k, device=local_rank)
+        sh.fill_synthetic(4)
+        u = np.random.default_rng(5).standard_normal((B, dim)).astype(np.float32)
+        u /= np.linalg.norm(u, axis=1, keepdims=True)
+        users = torch.from_numpy(u).to(dev)
+        sc = torch.empty((B, k), dtype=torch.float32, device=dev); ids = torch.empty((B, k), dtype=torch.int64, device=dev)
+        ms = timed(lambda: cm.retrieve_topk(sh, users, B, k, sc, ids, st), 10)
+        exact_runs = sh.exact_runs()
+        full = CorpusShard(rows, dim, row_offset=0, max_queries=B, max_k=k, device=local_rank)
+        full.fill_synthetic(4)
+        s2 = torch.empty_like(sc); i2 = torch.empty_like(ids)
+        full.topk_device(users, B, k, s2, i2); full.sync()
+        one_ms = []
+        for _ in range(3):
+            full.topk_device(users, B, k, s2, i2); full.sync(); one_ms.append(full.last_device_ms())
+        ok = all_true(torch.equal(ids, i2) and torch.equal(sc, s2))
+        full.close(); sh.close()
+        gbs = rows * dim * 2 / (ms * 1e-3) / 1e9
+        out["sharded_retrieval"] = dict(ms=ms, rows=rows, dim=dim, queries=B, k=k, queries_per_s=B / (ms * 1e-3),
+                                        corpus_gbs_aggregate=gbs, frac_of_aggregate_hbm=gbs / (peaks["hbm_gbs"] * world),
+                                        one_gpu_unsharded_ms=float(np.median(one_ms)), matches_unsharded=ok,
+                                        exact_reruns=exact_runs, api="phx_retrieve_topk (blocking; lists + status in one all-gather)")
+    except Exception as e:
+        out["sharded_retrieval"] = dict(error=repr(e))
+    cm.close()
+    # ---- ranking over the row-sharded table, rows exchanged in bulk ----------------------------------------------------------
+    try:
+        if "exchange" not in which:
+            raise KeyError("skipped")
+        from x_algorithm_b200.parallel import ShardedRanker
+        Bq = args.batch
+        cfg = px.PhoenixConfig(max_batch=Bq, table_world=world, table_rank=rank, **dict(WORKLOAD, table_size=1 << args.table_log2))
+        eng = px.PhoenixEngine(cfg, local_rank)
+        eng.load_weights(synthetic.make_weights(cfg, WEIGHT_SEED))
+        eng.table_fill_synthetic(TABLE_SEED, 1.0 / math.sqrt(cfg.emb_size))
+        bw = synthetic.make_blend_weights(px.HEAD_NAMES_19, BLEND_SEED)
+        eng.set_blend(px.blend_spec_from_weights(px.ValueModelWeights(w=bw), px.HEAD_NAMES_19, cfg.num_actions))
+        batches = [synthetic.make_batch(cfg, Bq, seed=ID_SEED + 1000 * rank + i, zipf_s=1.1) for i in range(4)]
+        db = [[torch.from_numpy(np.ascontiguousarray(a)).to(dev) for a in
+               (b.hist_post_ids, b.hist_author_ids, b.hist_actions, b.hist_surfaces, b.cand_post_ids, b.cand_author_ids)] for b in batches]
+        Cn, V, NC = cfg.num_candidates, cfg.num_actions, cfg.num_continuous
+        lp = torch.empty((Bq, Cn, V), dtype=torch.float32, device=dev)
+        cont = torch.empty((Bq, Cn, NC), dtype=torch.float32, device=dev)
+        scs = torch.empty((Bq, Cn), dtype=torch.float64, device=dev)
+        ranker = ShardedRanker(eng)
+
+        def step(i):
+            ranker.rank_device(Bq, *db[i % 4], lp, cont, scs)
+            ranker.prefetch(Bq, *db[(i + 1) % 4])
+        for i in range(3):
+            step(i)
+        eng.sync(); torch.cuda.synchronize(); dist.barrier()
+        eng.mark(0)
+        for i in range(steps):
+            step(i)
+        eng.mark(1)
+        eng.sync(); torch.cuda.synchronize(); dist.barrier()
+        t = torch.tensor([eng.elapsed_ms(0, 1) / steps], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        # the same batch on an engine with the whole table: bit-identical outputs
+        ranker.rank_device(Bq, *db[0], lp, cont, scs); eng.sync()
+        got = lp.clone()
+        ranker.close(); eng.close()
+        whole = px.PhoenixEngine(px.PhoenixConfig(max_batch=Bq, **dict(WORKLOAD, table_size=1 << args.table_log2)), local_rank)
+        whole.load_weights(synthetic.make_weights(cfg, WEIGHT_SEED))
+        whole.table_fill_synthetic(TABLE_SEED, 1.0 / math.sqrt(cfg.emb_size))
+        whole.rank_device(Bq, *db[0], lp, cont, None); whole.sync()
+        ok = all_true(torch.equal(got, lp))
+        whole.close()
+        out["tables_exchange"] = dict(ms_per_step=float(t[0]), value=steps and Bq * Cn * world / (float(t[0]) * 1e-3),
+                                      unit="candidates/s", matches_unsharded=ok,
+                                      note="headline step with the unified table row-sharded over the ranks; rows of batch i+1 "
+                                           "exchanged beside forward i (dedup, bucket, owner gather, copy engines over NVLink)")
+    except Exception as e:
+        out["tables_exchange"] = dict(error=repr(e))
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -136,6 +306,10 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--table-log2", type=int, default=22, help="log2 buckets per hash region (smaller for profiling captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sharded-only", default="", help="N > 1: skip the headline measurement and run only these sub-records "
+                                                       "(comma list of gather, retrieval, exchange); prints them as one JSON line")
+    ap.add_argument("--no-sharded-paths", action="store_true",
+                    help="N > 1: skip the sharded gather / retrieval / table-exchange sub-records after the headline measurement")
     ap.add_argument("--tables", default="replicated", choices=["sharded", "exchange", "replicated"],
                     help="N > 1: one full table per GPU (it fits: 17 GB); row-sharded over the ranks with per-row peer loads "
                          "over NVLink (sharded); or row-sharded with the bulk row exchange before each forward (exchange: the "
@@ -161,6 +335,12 @@ def main():
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if world > 1 and args.sharded_only:
+        sub = sharded_subrecords(args, rank, world, local_rank, args.steps, tuple(args.sharded_only.split(",")))
+        if rank == 0:
+            print(json.dumps(dict(n_gpus=world, **sub)), flush=True)
+        dist.destroy_process_group()
+        return
 
     wl = dict(WORKLOAD)
     wl["table_size"] = 1 << args.table_log2
@@ -293,6 +473,38 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms = float(t[0]), float(t[1])
 
+    sub = None
+    if world > 1 and not args.no_sharded_paths:
+        # The sharded paths are measured by a second set of processes, one per rank, each in a CUDA context of its own
+        # (this process gives its device memory back first and then only waits): they hold tables of up to 64 GiB per
+        # rank beside an unsharded copy for the check, and a benchmark that starts from a fresh context is the
+        # configuration these paths are tested in.  The children form their own process group on the next port.
+        if ranker is not None:
+            ranker.close(); ranker = None
+        eng.close(); eng = None
+        del dbatches, lp, cont, sc
+        torch.cuda.empty_cache()
+        torch.cuda.synchronize()
+        dist.barrier()
+        # (the launcher's own variables stay behind: with them a child would look for the launcher's rendezvous store
+        # on the new port instead of letting its rank 0 open one)
+        env = {k_: v_ for k_, v_ in os.environ.items() if not k_.startswith("TORCHELASTIC")}
+        env["MASTER_ADDR"] = "127.0.0.1"
+        env["MASTER_PORT"] = str(int(os.environ.get("MASTER_PORT", "29500")) + 1)
+        cmd = [sys.executable, os.path.abspath(__file__), "--gpus", str(world), "--steps", str(args.steps), "--batch", str(B),
+               "--table-log2", str(args.table_log2), "--sharded-only", "gather,retrieval,exchange"]
+        try:
+            child = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=420)
+            lines = [l for l in child.stdout.splitlines() if l.startswith("{")]
+            if rank == 0:
+                sub = json.loads(lines[-1]) if (child.returncode == 0 and lines) else \
+                    dict(sharded_paths=dict(error=f"child exit {child.returncode}: {child.stderr[-400:]}"))
+                sub.pop("n_gpus", None)
+        except Exception as e:   # the headline line is printed whatever happens to the sub-records
+            if rank == 0:
+                sub = dict(sharded_paths=dict(error=repr(e)))
+        dist.barrier()
+
     if rank == 0:
         peaks = measured_peaks()
         fl = flops_per_request(wl)
@@ -329,6 +541,8 @@ def main():
         )
         if xphase is not None:
             line["exchange_phase_ms"] = xphase
+        if sub is not None:
+            line.update(sub)
         if not args.no_cpu_baseline:
             # The CPU oracle on the first and the last request of batch 0 (outside every timed region): its time is the
             # CPU baseline, its logits are the checker for what the engine returned for the same two requests.
@@ -356,7 +570,8 @@ def main():
         print(json.dumps(line), flush=True)
     if ranker is not None:
         ranker.close()
-    eng.close()
+    if eng is not None:
+        eng.close()
     if world > 1:
         dist.destroy_process_group()
 

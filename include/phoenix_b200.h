@@ -479,7 +479,7 @@ const char* phx_corpus_last_error(const phx_corpus* c);
 typedef struct phx_comm phx_comm;
 phx_status phx_comm_unique_id(uint8_t out[PHX_COMM_ID_BYTES]);
 phx_status phx_comm_create(const uint8_t id[PHX_COMM_ID_BYTES], int32_t rank, int32_t world, int32_t device, phx_comm** out);
-void phx_comm_destroy(phx_comm* c);
+void phx_comm_destroy(phx_comm* c);   /* collective when the sharded gather was set up: ranks unmap each other's buffers first */
 const char* phx_comm_last_error(const phx_comm* c);
 phx_status phx_comm_info(const phx_comm* c, int32_t* rank, int32_t* world, int32_t* nccl_version);
 phx_status phx_comm_barrier(phx_comm* c, void* stream);

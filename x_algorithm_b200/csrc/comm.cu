@@ -99,7 +99,13 @@ void phx_comm_destroy(phx_comm* c) {
   if (!c) return;
   cudaSetDevice(c->device);
   cudaDeviceSynchronize();
-  if (c->gather_ws && c->gather_ws_free) c->gather_ws_free(c->gather_ws);
+  if (c->gather_ws && c->gather_ws_free) {
+    // memory that other ranks have mapped is freed only after every rank has unmapped it (destroy is collective)
+    c->gather_ws_free(c->gather_ws, 0);
+    if (c->comm && c->world > 1 && c->api->AllReduce(c->fence, c->fence, 1, ncclInt32, ncclSum, c->comm, nullptr) == ncclSuccess)
+      cudaStreamSynchronize(nullptr);
+    c->gather_ws_free(c->gather_ws, 1);
+  }
   if (c->keys_local) cudaFree(c->keys_local);
   if (c->keys_all) cudaFree(c->keys_all);
   if (c->status_all) cudaFree(c->status_all);

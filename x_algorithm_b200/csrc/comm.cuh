@@ -44,7 +44,7 @@ struct phx_comm {
   int* fence = nullptr;                                          // one int for ordering all-reduces
   // work spaces of the sharded paths, owned here so that they die with the communicator
   void* gather_ws = nullptr;
-  std::function<void(void*)> gather_ws_free;
+  std::function<void(void*, int)> gather_ws_free;   // (work space, step): 0 unmap peer memory, 1 free own memory
   unsigned long long* keys_local = nullptr;   // retrieval: this shard's list [B*k] + the lists of all ranks [W*B*k]
   unsigned long long* keys_all = nullptr;
   int* status_all = nullptr;                  // [W + 1]: every rank's scan status, then their OR

@@ -758,6 +758,9 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
     CU(cudaMallocHost(reinterpret_cast<void**>(&e->cont_host), rows * (e->NC > 0 ? e->NC : 1) * 4));
     CU(cudaMallocHost(reinterpret_cast<void**>(&e->score_host), rows * 8));
   }
+  // the memsets above ran on the default stream; every later launch uses the engine's own non-blocking stream, which
+  // does not order itself behind them
+  CU(cudaDeviceSynchronize());
 #undef TRY
 #undef CU
   *out = e;
@@ -1675,10 +1678,14 @@ struct GatherWs {
   cudaEvent_t ev[9] = {};
 };
 
-void gather_ws_free(void* p) {
+// step 0: unmap the peers' landing buffers; step 1 (after every rank has done step 0): free this rank's memory
+void gather_ws_free(void* p, int step) {
   GatherWs* w = static_cast<GatherWs*>(p);
-  for (int r = 0; r < w->W; ++r)
-    if (w->peer_landing[r] && w->peer_landing[r] != w->landing) cudaIpcCloseMemHandle(w->peer_landing[r]);
+  if (step == 0) {
+    for (int r = 0; r < w->W; ++r)
+      if (w->peer_landing[r] && w->peer_landing[r] != w->landing) { cudaIpcCloseMemHandle(w->peer_landing[r]); w->peer_landing[r] = nullptr; }
+    return;
+  }
   for (void* q : {(void*)w->rows, (void*)w->slot, (void*)w->urows, (void*)w->upos, (void*)w->pos, (void*)w->send_rows, (void*)w->counts,
                   (void*)w->cursor, (void*)w->nu, (void*)w->counts_all, (void*)w->recv_rows, (void*)w->table, (void*)w->gathered,
                   (void*)w->landing})
@@ -1696,7 +1703,13 @@ phx_status phx_gather_sharded_setup(phx_comm* cm, phx_engine* e, int64_t max_ids
     return PHX_E_ARG;
   }
   cudaSetDevice(e->device);
-  if (cm->gather_ws) { cm->gather_ws_free(cm->gather_ws); cm->gather_ws = nullptr; }
+  if (cm->gather_ws) {      // a second set-up: every rank unmaps, then every rank frees
+    cm->gather_ws_free(cm->gather_ws, 0);
+    phx_status bs = phx_comm_barrier(cm, nullptr);
+    if (bs) return bs;
+    cm->gather_ws_free(cm->gather_ws, 1);
+    cm->gather_ws = nullptr;
+  }
   GatherWs* w = new GatherWs();
   cm->gather_ws = w; cm->gather_ws_free = gather_ws_free;
   const int W = cm->world, H = e->cfg.item.num_hashes;
