@@ -209,7 +209,7 @@ def sharded_subrecords(args, rank, world, local_rank, steps, which=("gather", "r
             achieved_gbs_aggregate=gbs, frac_of_aggregate_hbm=gbs / (peaks["hbm_gbs"] * world), matches_unsharded=ok,
             one_gpu_share_ms=float(np.median(local_ms)),
             note="one_gpu_share_ms = this rank's ids alone on an unsharded 64 GiB table on the same GPU (no exchange)",
-            phase_ms_rank0=dict(zip(["hash_dedup_bucket", "counts_exchange", "row_numbers", "owner_gather_copies", "fence", "sum"],
+            phase_ms_rank0=dict(zip(["hash_dedup_bucket", "counts_exchange", "row_numbers", "owner_gathers", "copies_tail", "fence", "sum"],
                                     [round(x, 3) for x in phases])))
     except Exception as e:  # a sub-record must not take the headline line down
         out["sharded_gather"] = dict(error=repr(e))

@@ -504,12 +504,13 @@ phx_status phx_retrieve_topk(phx_comm* comm, phx_corpus* shard, const float* use
  * sizes the work space for max_ids ids per call; recv_factor bounds the rows one rank may be asked for in a call at
  * recv_factor * max_ids * num_hashes (PHX_E_CAPACITY beyond it, as the reference's row_emb_recv_factor).
  * phx_gather_sum_sharded (collective): this rank's ids_dev int64 [n] -> out_dev bf16 [n, emb_size], asynchronous on
- * `stream` after its one host wait.  phx_gather_sharded_phase_ms: device time of the last call's six phases on this
- * rank (requester prologue, counts exchange, row numbers, owner gather + copies, fence, sum). */
+ * `stream` after its one host wait.  phx_gather_sharded_phase_ms: device time of the last call's seven phases on this
+ * rank (requester prologue, counts exchange with the host wait, row numbers, owner-side gathers, remaining copies, fence,
+ * sum). */
 phx_status phx_gather_sharded_setup(phx_comm* comm, phx_engine* e, int64_t max_ids, double recv_factor);
 phx_status phx_gather_sum_sharded(phx_comm* comm, phx_engine* e, int32_t family, const int64_t* ids_dev, int64_t n,
                                   uint16_t* out_dev, void* stream);
-phx_status phx_gather_sharded_phase_ms(phx_comm* comm, float* ms6);
+phx_status phx_gather_sharded_phase_ms(phx_comm* comm, float* ms7);
 
 /* ---- value model after the heads (xai-value-model/scoring.rs) ---------------------------------- */
 

@@ -86,10 +86,11 @@ def test_gemm_tcgen05_vs_fp32(torch, M, N, K, epi):
 
 @pytest.mark.parametrize("dh,S,Cn,H", [(32, 32, 8, 4), (64, 128, 64, 2), (128, 96, 40, 2), (64, 200, 56, 3), (128, 300, 200, 1)])
 @pytest.mark.parametrize("cap", [(-1.0, 0), (30.0, 1), (30.0, 2)])
-@pytest.mark.parametrize("impl", ["tcgen05", "mma", "resident", "strip"])
+@pytest.mark.parametrize("impl", ["tcgen05", "mma", "resident", "strip", "pingpong"])
 def test_ranker_attention_vs_oracle(torch, monkeypatch, dh, S, Cn, H, cap, impl):
-    """tcgen05/TMEM kernels (head dim 64 / 128; dim 32 falls to mma.sync), the streaming mma.sync kernel and the
-    resident-history mma.sync kernel ("strip": head dim 64, <= 128 history keys; other shapes fall through)."""
+    """tcgen05/TMEM kernels (head dim 64 / 128; dim 32 falls to mma.sync), the streaming mma.sync kernel, the
+    resident-history mma.sync kernel ("strip": head dim 64, <= 128 history keys; other shapes fall through) and the
+    resident-history tcgen05 kernel with two softmax warpgroups ("pingpong": the same shapes)."""
     from x_algorithm_b200.engine import ranker_attention
     monkeypatch.setenv("PHX_ATTN", impl)   # "resident" applies to head dim 64 with <= 128 history keys, else tcgen05
     B, T = 3, S + Cn
@@ -118,6 +119,41 @@ def test_ranker_attention_vs_oracle(torch, monkeypatch, dh, S, Cn, H, cap, impl)
     keep = np.ones(T, bool); keep[S + 1] = False
     np.testing.assert_array_equal(got[0, keep], got2[0, keep])
     assert not np.array_equal(got[0, S + 1], got2[0, S + 1])
+
+
+@pytest.mark.parametrize("S,Cn,cap", [(128, 512, (-1.0, 0)), (100, 300, (25.0, 2)), (57, 130, (-1.0, 0))])
+def test_pingpong_attention_more_items_than_sms(torch, monkeypatch, S, Cn, cap):
+    """The persistent two-warpgroup kernel with more (batch, head) items than SMs, so that every CTA walks through
+    several items (K / V double buffer, Q ring and the alternation of the warpgroups across item boundaries): four
+    batch rows against the oracle, every row against the streaming mma.sync kernel."""
+    from x_algorithm_b200.engine import dispatch_counts, ranker_attention
+    B, H, dh = 48, 8, 64
+    T = S + Cn
+    g = torch.Generator(device="cuda").manual_seed(S + Cn)
+    q, k, v = (torch.randn(B, T, H, dh, device="cuda", generator=g).to(torch.bfloat16) for _ in range(3))
+    seg = torch.ones((B, T), dtype=torch.int32, device="cuda")
+    seg[:, S:] = -1
+    seg[1, S // 3:S] = 0; seg[1, T - 40:] = 0            # ragged history and candidates
+    seg[2, :S] = 0                                       # no history at all
+    seg[B - 1, S - 5:S] = 0; seg[B - 1, S + 3] = 0
+    sm = math.sqrt(128.0) / dh
+    monkeypatch.setenv("PHX_ATTN", "mma")
+    want_all, _ = ranker_attention(q, k, v, seg, S, sm, cap[0], cap[1])
+    monkeypatch.delenv("PHX_ATTN")
+    before = dispatch_counts()
+    out, ms = ranker_attention(q, k, v, seg, S, sm, cap[0], cap[1])       # default dispatch: 384 items >= 148
+    assert dispatch_counts()["attn.pingpong"] - before["attn.pingpong"] == 1
+    rows = [0, 1, 2, B - 1]
+    sl = lambda x: x[rows].float().cpu().numpy()
+    method = "tanh" if cap[1] == 2 else "soft_sign"
+    want = po.bf16_round(po.masked_attention(sl(q), sl(k), sl(v), po.ranker_mask(seg[rows].cpu().numpy()), sm, cap[0], method,
+                                             po._Rounder("bf16")))
+    got = sl(out)
+    assert rel_l2(got, want) < 1e-2
+    assert np.abs(got - want).max() < 0.05
+    a, b = out.float(), want_all.float()
+    assert float((a - b).norm() / b.norm()) < 5e-3
+    assert bool((out[seg == 0] == 0).all())                               # padded queries -> zeros
 
 
 @pytest.mark.parametrize("name", ["full", "ragged", "offset", "tanhcap"])
@@ -201,6 +237,8 @@ def test_rank_forward_options_vs_oracle(torch, opts):
     (dict(num_candidate_only_layers=1, primer_norm=True), None),
     (dict(num_candidate_only_layers=2, emb_size=256, num_q_heads=4, num_kv_heads=4, key_size=64, history_len=48,
           num_candidates=24, num_layers=3), "strip"),
+    (dict(num_candidate_only_layers=2, emb_size=256, num_q_heads=4, num_kv_heads=4, key_size=64, history_len=48,
+          num_candidates=300, num_layers=3), "pingpong"),
     (dict(num_candidate_only_layers=2, emb_size=256, num_q_heads=4, num_kv_heads=4, key_size=64, history_len=160,
           num_candidates=200, num_layers=3), None),
     (dict(num_candidate_only_layers=3, emb_size=128, num_q_heads=1, num_kv_heads=1, key_size=128, history_len=40,

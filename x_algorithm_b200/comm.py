@@ -70,6 +70,6 @@ class Communicator:
                                                stream or None))
 
     def gather_phase_ms(self) -> List[float]:
-        buf = (C.c_float * 6)()
+        buf = (C.c_float * 7)()
         self._check(lib.phx_gather_sharded_phase_ms(self._h, buf))
         return [float(x) for x in buf]

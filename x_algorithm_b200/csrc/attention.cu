@@ -681,6 +681,15 @@ phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::
     const bool plain = !a.split && a.q_start == 0 && !a.pack.hist_off;   // the tcgen05 kernel's tensor maps assume [B, T] token rows
     if (plain && !legacy && prefer_tc && a.err_flag && ranker_attention_tc_supported(a)) return ranker_attention_tc_launch(a, a.err_flag, stream, err);
   }
+  {
+    // Head dim 64 with a history of at most 128 keys at throughput batch sizes: the tcgen05 kernel with the history
+    // resident and two softmax warpgroups (PHX_ATTN=strip|mma keep the mma.sync kernels, PHX_ATTN=pingpong forces it).
+    const char* force = getenv("PHX_ATTN");
+    const bool forced = force && strcmp(force, "pingpong") == 0;
+    const bool enough = (long long)a.B * a.Hq >= 148;
+    if ((forced || (!force && enough)) && a.err_flag && ranker_attention_pingpong_supported(a))
+      return ranker_attention_pingpong_launch(a, a.err_flag, stream, err);
+  }
   const bool cap = a.cap_method != 0 && a.cap > 0.f;
   {
     // head dim 64 with the whole history in one shared-memory panel: the resident-history kernel

@@ -613,6 +613,340 @@ ranker_attention_resident_kernel(const __grid_constant__ CUtensorMap map_q, cons
   }
 }
 
+// ---- resident history, two softmax warpgroups (the ranking trunk's shape at throughput batch sizes) ----------------
+// Head dim 64, at most 128 history keys.  A persistent CTA (one per SM, 320 threads) walks over (batch, head) items;
+// per item the history K and V tiles are loaded once by TMA (double-buffered across items, so the next item's tiles
+// arrive while the current one is still being worked on) and every 128-row query tile of the request streams through
+// a three-deep Q ring.  Two softmax warpgroups take alternate tiles, each with its own S and O accumulators in tensor
+// memory (S0, S1 at columns 0 / 128, O0, O1 at 256 / 320) and its own P buffer in shared memory: while one warpgroup
+// exponentiates tile g, the MMA warp has already produced S of tile g+1 for the other, and P V of tile g runs under
+// the other warpgroup's softmax.  Thread = query row: the whole 128-key S row is read from tensor memory once, kept in
+// registers, and turned into P in one pass.  The candidate x candidate block is never formed: a candidate's own key
+// is one extra softmax term from a per-row dot product (its k / v rows are requested a tile ahead).  Query tiles are
+// taken from the history block and the candidate block separately, so the plain [B, T] token layout and the split
+// layout (all history rows, then all candidate rows) differ only in the tensor maps' strides; candidate-only layers
+// skip the history tiles.  All waits are bounded (sm100_ptx.cuh).
+constexpr int PP_THREADS = 320;
+constexpr int PP_NQ = 3;
+
+struct PingArgs {
+  const bf16* k; const bf16* v; bf16* out; const int* seg;
+  long long k_tok_stride, v_tok_stride;
+  int q_head_stride, k_head_stride, v_head_stride;
+  int Hq, Hkv, n_hist, n_cand, n_items;
+  long long hist_row0, hist_req_rows, cand_row0, cand_req_rows;   // token row of position 0 of request 0; rows per request
+  int skip_hist;                                                  // 1: history rows are keys only (candidate-only layer)
+  float sm_scale, cap;
+  int cap_method;
+  int* err_flag;
+};
+
+template <bool CAP>
+__global__ void __launch_bounds__(PP_THREADS, 1)
+ranker_attention_pingpong_kernel(const __grid_constant__ CUtensorMap map_qh, const __grid_constant__ CUtensorMap map_qc,
+                                 const __grid_constant__ CUtensorMap map_kh, const __grid_constant__ CUtensorMap map_vh,
+                                 PingArgs a) {
+  constexpr int DH = 64;
+  constexpr uint32_t TM_S = 0, TM_O = 256;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sKV = base;                       // 2 x (K [128 x 128 B], V [128 x 128 B])
+  const uint32_t sQ = sKV + 4 * SLAB;              // PP_NQ x [128 x 128 B]
+  const uint32_t sP = sQ + PP_NQ * SLAB;           // 2 warpgroups x 2 x [128 rows x 64 keys]
+  const uint32_t sMask = sP + 4 * SLAB;            // 2 warpgroups x 4 words
+  const uint32_t bars = sMask + 64;
+  auto kv_full = [&](int i) { return bars + 8u * i; };
+  auto kv_free = [&](int i) { return bars + 16u + 8u * i; };
+  auto q_full = [&](int i) { return bars + 32u + 8u * i; };
+  auto q_free = [&](int i) { return bars + 56u + 8u * i; };
+  auto s_full = [&](int i) { return bars + 80u + 8u * i; };
+  auto p_ready = [&](int i) { return bars + 96u + 8u * i; };
+  auto o_done = [&](int i) { return bars + 112u + 8u * i; };
+  const uint32_t tmem_slot = bars + 128;
+  uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+  uint32_t* mask_words = reinterpret_cast<uint32_t*>(smem_raw + (sMask - smem_u32(smem_raw)));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* verr = a.err_flag;
+  const int n_htiles = a.skip_hist ? 0 : (a.n_hist + QT - 1) / QT;      // 0 or 1
+  const int n_ctiles = (a.n_cand + QT - 1) / QT;
+  const int nt = n_htiles + n_ctiles;                                   // query tiles per item
+  const int my_items = ((int)blockIdx.x < a.n_items) ? (a.n_items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  const int G = my_items * nt;                                          // tiles this CTA works through
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(kv_full(i), 1); mbar_init(kv_free(i), 1); mbar_init(s_full(i), 1); mbar_init(p_ready(i), 128); mbar_init(o_done(i), 1);
+    }
+    // a Q buffer is free once S has been computed from it (commit) and the 128 threads of the warpgroup that owns the
+    // tile have read their rows for the self term
+    for (int i = 0; i < PP_NQ; ++i) { mbar_init(q_full(i), 1); mbar_init(q_free(i), 129); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int g = 0;
+      for (int li = 0; li < my_items; ++li) {
+        const int it = (int)blockIdx.x + li * (int)gridDim.x;
+        const int b = it / a.Hq, h = it % a.Hq, hk = h / (a.Hq / a.Hkv);
+        const int kb = li & 1;
+        mbar_wait(kv_free(kb), (uint32_t)(((li >> 1) & 1) ^ 1), verr);
+        mbar_expect_tx(kv_full(kb), 2 * SLAB);
+        tma_load_3d(sKV + (2 * kb) * SLAB, &map_kh, kv_full(kb), hk * a.k_head_stride, 0, b);
+        tma_load_3d(sKV + (2 * kb + 1) * SLAB, &map_vh, kv_full(kb), hk * a.v_head_stride, 0, b);
+        for (int ti = 0; ti < nt; ++ti, ++g) {
+          const int st = g % PP_NQ;
+          mbar_wait(q_free(st), (uint32_t)(((g / PP_NQ) & 1) ^ 1), verr);
+          mbar_expect_tx(q_full(st), SLAB);
+          if (ti < n_htiles) tma_load_3d(sQ + st * SLAB, &map_qh, q_full(st), h * a.q_head_stride, ti * QT, b);
+          else tma_load_3d(sQ + st * SLAB, &map_qc, q_full(st), h * a.q_head_stride, (ti - n_htiles) * QT, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(QT, 128);
+      constexpr uint32_t idesc_o = make_idesc_b_mn(QT, DH);
+      auto issue_pv = [&](int gp, int kbp, bool last_of_item) {      // O[w] = P[w] V for tile gp
+        const int w = gp & 1;
+        mbar_wait(p_ready(w), (uint32_t)((gp >> 1) & 1), verr);
+        tc_fence_after();
+        const uint32_t sV = sKV + (2 * kbp + 1) * SLAB;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t pd = make_smem_desc(sP + (2 * w + (kk >> 2)) * SLAB) + (uint64_t)((kk & 3) * 2);
+          const uint64_t vd = make_smem_desc_mn(sV + kk * 16 * 128, 128 * 128, 1024);
+          umma_bf16(tmem + TM_O + w * DH, pd, vd, idesc_o, kk != 0);
+        }
+        umma_commit(o_done(w));
+        if (last_of_item) umma_commit(kv_free(kbp));                 // every MMA that read this item's K / V is behind this point
+      };
+      int g = 0, prev_kb = 0;
+      bool prev_last = false;
+      for (int li = 0; li < my_items; ++li) {
+        const int kb = li & 1;
+        mbar_wait(kv_full(kb), (uint32_t)((li >> 1) & 1), verr);
+        for (int ti = 0; ti < nt; ++ti, ++g) {
+          const int st = g % PP_NQ, w = g & 1;
+          mbar_wait(q_full(st), (uint32_t)((g / PP_NQ) & 1), verr);
+          tc_fence_after();
+          // S[w] is free: P V of tile g - 2 was issued behind that tile's p_ready, which its warpgroup gives after
+          // it has read S
+          const uint64_t qd = make_smem_desc(sQ + st * SLAB), kd = make_smem_desc(sKV + (2 * kb) * SLAB);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_bf16(tmem + TM_S + w * 128, qd + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), idesc_s, k != 0);
+          umma_commit(s_full(w));
+          umma_commit(q_free(st));
+          if (g > 0) issue_pv(g - 1, prev_kb, prev_last);
+          prev_kb = kb; prev_last = (ti == nt - 1);
+        }
+      }
+      if (G > 0) issue_pv(G - 1, prev_kb, prev_last);
+    }
+  } else {
+    // ---------------- softmax / epilogue: warpgroup w takes the tiles g = w, w + 2, ... ----------------
+    const int w = (warp - 2) >> 2;
+    const int quad = warp & 3;                       // the tensor-memory lane quarter this warp may read
+    const int r = quad * 32 + lane;
+    const int sw = r & 7;
+    const uint32_t lane_base = ((uint32_t)(quad * 32) << 16);
+    const float csc = CAP ? 1.0f : a.sm_scale * 1.4426950408889634f;
+    const uint32_t myP = sP + (2 * w) * SLAB;
+    auto wg_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(1 + w) : "memory"); };
+
+    struct Tile { int b, h, hk, li; long long tok; int seg; bool cand; };
+    auto tile_of = [&](int g) {
+      Tile t;
+      t.li = g / nt;
+      const int ti = g - t.li * nt;
+      const int it = (int)blockIdx.x + t.li * (int)gridDim.x;
+      t.b = it / a.Hq; t.h = it % a.Hq; t.hk = t.h / (a.Hq / a.Hkv);
+      t.cand = ti >= n_htiles;
+      const int p = (t.cand ? (ti - n_htiles) : ti) * QT + r;                        // position inside the block
+      const bool in = p < (t.cand ? a.n_cand : a.n_hist);
+      t.tok = in ? (t.cand ? a.cand_row0 + (long long)t.b * a.cand_req_rows + p : a.hist_row0 + (long long)t.b * a.hist_req_rows + p) : -1;
+      t.seg = in ? a.seg[t.tok] : 0;
+      return t;
+    };
+    auto load_row = [&](const bf16* basep, long long stride, const Tile& t, int hoff, uint4 (&dst)[DH / 8]) {
+      if (t.cand && t.seg == -1) {
+        const uint4* p = reinterpret_cast<const uint4*>(basep + t.tok * stride + hoff);
+#pragma unroll
+        for (int c = 0; c < DH / 8; ++c) dst[c] = __ldg(p + c);
+      }
+    };
+    // q . k of this row against its own key, q from the (swizzled) Q buffer; every thread then lets go of the buffer
+    auto self_dot = [&](int g, const Tile& t, const uint4 (&krow)[DH / 8]) {
+      const int st = g % PP_NQ;
+      mbar_wait(q_full(st), (uint32_t)((g / PP_NQ) & 1), verr);
+      float dot = 0.f;
+      if (t.cand && t.seg == -1) {
+        float d4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < DH / 8; ++c) {
+          uint4 qa;
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(qa.x), "=r"(qa.y), "=r"(qa.z), "=r"(qa.w)
+                       : "r"(sQ + st * SLAB + r * 128 + ((uint32_t)(c ^ sw) << 4)));
+          const uint4 ka = krow[c];
+          const float2 q0f = unpack_bf2(qa.x), q1f = unpack_bf2(qa.y), q2f = unpack_bf2(qa.z), q3f = unpack_bf2(qa.w);
+          const float2 k0f = unpack_bf2(ka.x), k1f = unpack_bf2(ka.y), k2f = unpack_bf2(ka.z), k3f = unpack_bf2(ka.w);
+          d4[0] += q0f.x * k0f.x + q0f.y * k0f.y; d4[1] += q1f.x * k1f.x + q1f.y * k1f.y;
+          d4[2] += q2f.x * k2f.x + q2f.y * k2f.y; d4[3] += q3f.x * k3f.x + q3f.y * k3f.y;
+        }
+        dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+      }
+      mbar_arrive(q_free(st));
+      return CAP ? capped_log2(dot, a.sm_scale, a.cap, a.cap_method) : dot * csc;
+    };
+
+    uint4 krow[DH / 8], vrow[DH / 8];
+    uint32_t kmask[4] = {0u, 0u, 0u, 0u};
+    bool all_ok = false;
+    int mask_li = -1;
+    Tile cur, nxt;
+    float self_logit = 0.f;
+    if (w < G) {
+      cur = tile_of(w);
+      load_row(a.k, a.k_tok_stride, cur, cur.hk * a.k_head_stride, krow);
+      load_row(a.v, a.v_tok_stride, cur, cur.hk * a.v_head_stride, vrow);
+      self_logit = self_dot(w, cur, krow);
+    }
+    for (int g = w; g < G; g += 2) {
+      const uint32_t ph = (uint32_t)((g >> 1) & 1);
+      const bool more = g + 2 < G;
+      if (more) {
+        nxt = tile_of(g + 2);
+        load_row(a.k, a.k_tok_stride, nxt, nxt.hk * a.k_head_stride, krow);       // krow of this tile went into self_logit already
+      }
+      if (cur.li != mask_li) {
+        // validity of the item's history keys (the same for all of its tiles)
+        const bool ok = (r < a.n_hist) && (a.seg[a.hist_row0 + (long long)cur.b * a.hist_req_rows + r] == 1);
+        const uint32_t word = __ballot_sync(0xffffffffu, ok);
+        wg_sync();                                   // the words of the previous item have been read by every thread
+        if (lane == 0) mask_words[w * 4 + quad] = word;
+        wg_sync();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) kmask[i] = mask_words[w * 4 + i];
+        all_ok = (kmask[0] & kmask[1] & kmask[2] & kmask[3]) == 0xffffffffu;
+        mask_li = cur.li;
+      }
+
+      mbar_wait(s_full(w), ph, verr);
+      tc_fence_after();
+      float s[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32_nowait(tmem + TM_S + w * 128 + lane_base + c * 32, reinterpret_cast<uint32_t*>(s) + c * 32);
+      tmem_ld_wait();
+      if (CAP) {
+#pragma unroll
+        for (int k = 0; k < 128; ++k) s[k] = capped_log2(s[k], a.sm_scale, a.cap, a.cap_method);
+      }
+      if (!all_ok) {
+#pragma unroll
+        for (int k = 0; k < 128; ++k)
+          if (!((kmask[k >> 5] >> (k & 31)) & 1u)) s[k] = -INFINITY;
+      }
+      float bm;
+      {
+        float b4[4] = {s[0], s[1], s[2], s[3]};
+#pragma unroll
+        for (int k = 4; k + 7 < 128; k += 8) {
+          b4[0] = max3f(b4[0], s[k], s[k + 1]); b4[1] = max3f(b4[1], s[k + 2], s[k + 3]);
+          b4[2] = max3f(b4[2], s[k + 4], s[k + 5]); b4[3] = max3f(b4[3], s[k + 6], s[k + 7]);
+        }
+        bm = fmaxf(max3f(b4[0], b4[1], b4[2]), b4[3]);
+#pragma unroll
+        for (int k = 124; k < 128; ++k) bm = fmaxf(bm, s[k]);
+      }
+      float m = bm * csc;
+      const bool is_cand = cur.cand && cur.seg == -1;
+      if (is_cand) m = fmaxf(m, self_logit);           // the self key takes part in the row maximum right away
+      const float mns = (m == -INFINITY) ? 0.f : m;
+      float l;
+      {
+        const float2 c2 = make_float2(csc, csc), n2 = make_float2(-mns, -mns);
+        float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+        for (int k = 0; k < 128; k += 2) {           // packed fp32: two keys per instruction; masked keys: 2^-inf = 0
+          const float2 e = __ffma2_rn(make_float2(s[k], s[k + 1]), c2, n2);
+          s[k] = ex2f(e.x); s[k + 1] = ex2f(e.y);
+          acc2[(k >> 1) & 1] = __fadd2_rn(acc2[(k >> 1) & 1], make_float2(s[k], s[k + 1]));
+        }
+        l = (acc2[0].x + acc2[0].y) + (acc2[1].x + acc2[1].y);
+      }
+      // P (bf16) into this warpgroup's operand buffer; its previous contents were consumed by the P V product this
+      // thread waited for at the end of its previous tile
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        uint4 o;
+        o.x = pack_bf2(s[c * 8 + 0], s[c * 8 + 1]); o.y = pack_bf2(s[c * 8 + 2], s[c * 8 + 3]);
+        o.z = pack_bf2(s[c * 8 + 4], s[c * 8 + 5]); o.w = pack_bf2(s[c * 8 + 6], s[c * 8 + 7]);
+        st_shared_16(myP + (c >> 3) * SLAB + r * 128 + ((uint32_t)((c & 7) ^ sw) << 4), o);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      mbar_arrive(p_ready(w));
+
+      // while the P V product runs: the self logit of this warpgroup's next tile
+      float self_next = 0.f;
+      if (more) self_next = self_dot(g + 2, nxt, krow);
+
+      float p_self = 0.f;
+      if (is_cand) { p_self = ex2f(self_logit - mns); l += p_self; }
+      const float pr = round_bf(p_self);
+      mbar_wait(o_done(w), ph, verr);
+      tc_fence_after();
+      float o[DH];
+#pragma unroll
+      for (int c = 0; c < DH / 32; ++c) tmem_ld32_nowait(tmem + TM_O + w * DH + lane_base + c * 32, reinterpret_cast<uint32_t*>(o) + c * 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      const float inv = (l == 0.f || cur.seg == 0) ? 0.f : 1.0f / l;   // padded rows, rows with no allowed key -> zeros
+      if (cur.tok >= 0) {
+        bf16* orow = a.out + (cur.tok * a.Hq + cur.h) * DH;
+#pragma unroll
+        for (int c2 = 0; c2 < DH / 16; ++c2) {
+          uint32_t wv[8];
+#pragma unroll
+          for (int hc = 0; hc < 2; ++hc) {
+            const int c = c2 * 2 + hc;
+            if (is_cand) {
+              const float2 v0 = unpack_bf2(vrow[c].x), v1 = unpack_bf2(vrow[c].y), v2 = unpack_bf2(vrow[c].z), v3 = unpack_bf2(vrow[c].w);
+              o[c * 8 + 0] += pr * v0.x; o[c * 8 + 1] += pr * v0.y; o[c * 8 + 2] += pr * v1.x; o[c * 8 + 3] += pr * v1.y;
+              o[c * 8 + 4] += pr * v2.x; o[c * 8 + 5] += pr * v2.y; o[c * 8 + 6] += pr * v3.x; o[c * 8 + 7] += pr * v3.y;
+            }
+            wv[hc * 4 + 0] = pack_bf2(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv); wv[hc * 4 + 1] = pack_bf2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
+            wv[hc * 4 + 2] = pack_bf2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv); wv[hc * 4 + 3] = pack_bf2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
+          }
+          asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                       ::"l"(orow + c2 * 16), "r"(wv[0]), "r"(wv[1]), "r"(wv[2]), "r"(wv[3]), "r"(wv[4]), "r"(wv[5]), "r"(wv[6]), "r"(wv[7]) : "memory");
+        }
+      }
+      if (more) {
+        load_row(a.v, a.v_tok_stride, nxt, nxt.hk * a.v_head_stride, vrow);         // a whole tile to arrive
+        cur = nxt;
+        self_logit = self_next;
+      }
+    }
+  }
+
+  if (*verr != 0) __nanosleep(1000000);   // error path: let in-flight bulk copies land before the CTA retires
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
 // tensor maps are cached: the engine calls with the same buffers every layer and every step
 typedef std::tuple<const void*, long long, int, int, long long, int> MapKey;
 std::map<MapKey, CUtensorMap> g_map_cache;
@@ -631,6 +965,66 @@ phx_status cached_map3d(const CUtensorMap** out, const bf16* ptr, long long cols
     it = g_map_cache.emplace(key, m).first;
   }
   *out = &it->second;
+  return PHX_OK;
+}
+
+struct MapKey7 {
+  const void* p; long long cols, d1, d2, s1, s2; int box;
+  bool operator<(const MapKey7& o) const { return std::tie(p, cols, d1, d2, s1, s2, box) < std::tie(o.p, o.cols, o.d1, o.d2, o.s1, o.s2, o.box); }
+};
+std::map<MapKey7, CUtensorMap> g_map_cache7;
+
+// 3-D map with free strides: [d2 requests][d1 rows][cols], byte strides s1 (rows) and s2 (requests)
+phx_status cached_map3d_strided(const CUtensorMap** out, const bf16* ptr, long long cols, long long d1, long long d2,
+                                long long s1_bytes, long long s2_bytes, int box_rows, std::string& err) {
+  std::lock_guard<std::mutex> lk(g_map_mu);
+  MapKey7 key{ptr, cols, d1, d2, s1_bytes, s2_bytes, box_rows};
+  auto it = g_map_cache7.find(key);
+  if (it == g_map_cache7.end()) {
+    if (g_map_cache7.size() > 4096) g_map_cache7.clear();
+    CUtensorMap m;
+    phx_status s = make_map3d(&m, ptr, cols, d1, d2, s1_bytes, s2_bytes, box_rows, err);
+    if (s) return s;
+    it = g_map_cache7.emplace(key, m).first;
+  }
+  *out = &it->second;
+  return PHX_OK;
+}
+
+template <bool CAP>
+phx_status launch_pingpong(const AttnArgs& a, int* err_flag, int num_sms, cudaStream_t stream, std::string& err) {
+  const size_t smem = (size_t)(4 + PP_NQ + 4) * SLAB + 64 + 160 + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    PHX_CUDA_TRY(cudaFuncSetAttribute(ranker_attention_pingpong_kernel<CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), err);
+    attr_set = true;
+  }
+  const int n_hist = a.hist_len < a.T ? a.hist_len : a.T;
+  const int n_cand = a.T - n_hist;
+  PingArgs p;
+  p.k = a.k; p.v = a.v; p.out = a.out; p.seg = a.seg;
+  p.k_tok_stride = a.k_tok_stride; p.v_tok_stride = a.v_tok_stride;
+  p.q_head_stride = a.q_head_stride; p.k_head_stride = a.k_head_stride; p.v_head_stride = a.v_head_stride;
+  p.Hq = a.Hq; p.Hkv = a.Hkv; p.n_hist = n_hist; p.n_cand = n_cand; p.n_items = a.B * a.Hq;
+  p.hist_row0 = token_row(a.split, a.B, a.hist_len, a.T, 0, 0);
+  p.hist_req_rows = a.split ? a.hist_len : a.T;
+  p.cand_row0 = n_cand > 0 ? token_row(a.split, a.B, a.hist_len, a.T, 0, n_hist) : 0;
+  p.cand_req_rows = a.split ? (a.T - a.hist_len) : a.T;
+  p.skip_hist = a.q_start > 0 ? 1 : 0;
+  p.sm_scale = a.sm_scale; p.cap = a.cap; p.cap_method = a.cap_method; p.err_flag = err_flag;
+  if (p.skip_hist && n_cand == 0) return PHX_OK;
+  const CUtensorMap *mqh, *mqc, *mkh, *mvh;
+  phx_status s;
+  const long long qcols = (long long)(a.Hq - 1) * a.q_head_stride + 64, kcols = (long long)(a.Hkv - 1) * a.k_head_stride + 64,
+                  vcols = (long long)(a.Hkv - 1) * a.v_head_stride + 64;
+  if ((s = cached_map3d_strided(&mqh, a.q + p.hist_row0 * a.q_tok_stride, qcols, n_hist, a.B, a.q_tok_stride * 2, p.hist_req_rows * a.q_tok_stride * 2, QT, err))) return s;
+  if ((s = cached_map3d_strided(&mkh, a.k + p.hist_row0 * a.k_tok_stride, kcols, n_hist, a.B, a.k_tok_stride * 2, p.hist_req_rows * a.k_tok_stride * 2, 128, err))) return s;
+  if ((s = cached_map3d_strided(&mvh, a.v + p.hist_row0 * a.v_tok_stride, vcols, n_hist, a.B, a.v_tok_stride * 2, p.hist_req_rows * a.v_tok_stride * 2, 128, err))) return s;
+  mqc = mqh;
+  if (n_cand > 0 && (s = cached_map3d_strided(&mqc, a.q + p.cand_row0 * a.q_tok_stride, qcols, n_cand, a.B, a.q_tok_stride * 2, p.cand_req_rows * a.q_tok_stride * 2, QT, err))) return s;
+  const int grid = p.n_items < num_sms ? p.n_items : num_sms;
+  ranker_attention_pingpong_kernel<CAP><<<grid, PP_THREADS, smem, stream>>>(*mqh, *mqc, *mkh, *mvh, p);
+  PHX_CUDA_TRY(cudaGetLastError(), err);
   return PHX_OK;
 }
 
@@ -690,6 +1084,29 @@ phx_status launch_resident(const AttnArgs& a, int* err_flag, cudaStream_t stream
 }
 
 }  // namespace
+
+// the two-warpgroup resident-history kernel: head dim 64, 1..128 history keys, q heads not grouped, rows not packed
+bool ranker_attention_pingpong_supported(const AttnArgs& a) {
+  const int n_hist = a.hist_len < a.T ? a.hist_len : a.T;
+  if (a.dh != 64 || n_hist < 1 || n_hist > 128 || a.q_group > 1 || a.pack.hist_off || a.Hq % a.Hkv != 0) return false;
+  if (a.q_start != 0 && a.q_start != n_hist) return false;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return al(a.q) && al(a.k) && al(a.v) && al(a.out) && a.q_tok_stride % 8 == 0 && a.k_tok_stride % 8 == 0 &&
+         a.v_tok_stride % 8 == 0 && a.q_head_stride % 8 == 0 && a.k_head_stride % 8 == 0 && a.v_head_stride % 8 == 0;
+}
+
+phx_status ranker_attention_pingpong_launch(const AttnArgs& a, int* err_flag, cudaStream_t stream, std::string& err) {
+  static int num_sms = 0;
+  if (!num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (num_sms <= 0) num_sms = 148;
+  }
+  dispatch_note(DK_ATTN_PINGPONG);
+  const bool cap = a.cap_method != 0 && a.cap > 0.f;
+  return cap ? launch_pingpong<true>(a, err_flag, num_sms, stream, err) : launch_pingpong<false>(a, err_flag, num_sms, stream, err);
+}
 
 bool ranker_attention_tc_supported(const AttnArgs& a) {
   if (a.dh != 64 && a.dh != 128) return false;

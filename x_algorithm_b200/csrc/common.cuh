@@ -42,7 +42,8 @@ enum DispatchKind {
   DK_SCAN_TC = 9,        // tcgen05 corpus scan
   DK_SCAN_MMA = 10,      // mma.sync corpus scan
   DK_TOPK_EXACT = 11,    // exact-threshold passes of the top-k (the sampled pivot missed)
-  DK_COUNT = 12
+  DK_ATTN_PINGPONG = 12, // tcgen05 / TMEM resident-history kernel with two softmax warpgroups
+  DK_COUNT = 13
 };
 void dispatch_note(int kind);
 
@@ -298,6 +299,8 @@ struct AttnArgs {
 // tcgen05 / TMEM kernel for head dims 64 and 128 (attention_sm100.cu); the mma.sync kernel covers the rest
 bool ranker_attention_tc_supported(const AttnArgs& a);
 phx_status ranker_attention_tc_launch(const AttnArgs& a, int* err_flag, cudaStream_t stream, std::string& err);
+bool ranker_attention_pingpong_supported(const AttnArgs& a);
+phx_status ranker_attention_pingpong_launch(const AttnArgs& a, int* err_flag, cudaStream_t stream, std::string& err);
 phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::string& err);
 // One thread waits on an mbarrier that nothing ever signals, with the flag block's wait limit: the wait gives up, raises
 // the flag and the kernel returns (the bounded-wait path of every tcgen05 kernel here, exercised on its own).

@@ -1423,7 +1423,7 @@ int32_t phx_dispatch_counts(int64_t* out, int32_t n) {
 
 const char* phx_dispatch_name(int32_t kind) {
   static const char* names[DK_COUNT] = {"attn.strip", "attn.stream", "attn.tcgen05", "attn.resident", "gemm.pair256", "gemm.pair128",
-                                        "gemm.cta256", "gemm.cta128", "gemm.simt", "scan.tcgen05", "scan.mma", "topk.exact"};
+                                        "gemm.cta256", "gemm.cta128", "gemm.simt", "scan.tcgen05", "scan.mma", "topk.exact", "attn.pingpong"};
   return (kind >= 0 && kind < DK_COUNT) ? names[kind] : "";
 }
 
@@ -1674,7 +1674,6 @@ struct GatherWs {
   unsigned long long* table = nullptr;
   bf16 *gathered = nullptr, *landing = nullptr;
   bf16* peer_landing[PHX_MAX_SHARDS] = {nullptr};
-  float phase_ms[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   cudaEvent_t ev[9] = {};
 };
 
@@ -1822,26 +1821,27 @@ phx_status phx_gather_sum_sharded(phx_comm* cm, phx_engine* e, int32_t family, c
   if (all[rank * W + rank] > 0 &&
       (s = phx_shard_gather_rows((const uint16_t*)e->table, w->shard_rows, w->recv_rows + recv_off[rank], all[rank * W + rank], w->width,
                                  (uint16_t*)(w->landing + their_off[rank] * w->width), st))) { cm->err = phx_global_error(); return s; }
+  mark(4);
   for (int i = 0; i < (used < 4 ? used : 4); ++i) {
     PHX_CUDA_TRY(cudaEventRecord(cm->ev_join[i], cm->side[i]), cm->err);
     PHX_CUDA_TRY(cudaStreamWaitEvent(st, cm->ev_join[i], 0), cm->err);
   }
-  mark(4);
+  mark(5);
   // every rank's copies have landed before any rank sums
   if (W > 1 && (s = comm_check(cm, cm->api->AllReduce(cm->fence, cm->fence, 1, ncclInt32, ncclSum, cm->comm, st), "ncclAllReduce (fence)"))) return s;
-  mark(5);
-  if ((s = phx_shard_sum_rows((const uint16_t*)w->landing, w->pos, n, H, w->width, out_dev, st))) { cm->err = phx_global_error(); return s; }
   mark(6);
+  if ((s = phx_shard_sum_rows((const uint16_t*)w->landing, w->pos, n, H, w->width, out_dev, st))) { cm->err = phx_global_error(); return s; }
+  mark(7);
   return PHX_OK;
 }
 
 // Device time of the phases of the last phx_gather_sum_sharded call on this rank (waits for it): hash + dedup + bucket,
-// counts exchange, row numbers, owner gather + copies, fence, sum.  Six floats.
-phx_status phx_gather_sharded_phase_ms(phx_comm* cm, float* ms6) {
-  if (!cm || !ms6 || !cm->gather_ws) return PHX_E_ARG;
+// counts exchange (with the host wait), row numbers, owner-side gathers, the rest of the copies, fence, sum.  Seven floats.
+phx_status phx_gather_sharded_phase_ms(phx_comm* cm, float* ms7) {
+  if (!cm || !ms7 || !cm->gather_ws) return PHX_E_ARG;
   GatherWs* w = static_cast<GatherWs*>(cm->gather_ws);
-  PHX_CUDA_TRY(cudaEventSynchronize(w->ev[6]), cm->err);
-  for (int i = 0; i < 6; ++i) PHX_CUDA_TRY(cudaEventElapsedTime(&ms6[i], w->ev[i], w->ev[i + 1]), cm->err);
+  PHX_CUDA_TRY(cudaEventSynchronize(w->ev[7]), cm->err);
+  for (int i = 0; i < 7; ++i) PHX_CUDA_TRY(cudaEventElapsedTime(&ms7[i], w->ev[i], w->ev[i + 1]), cm->err);
   return PHX_OK;
 }
 
