@@ -139,9 +139,9 @@ def test_pingpong_attention_more_items_than_sms(torch, monkeypatch, S, Cn, cap):
     sm = math.sqrt(128.0) / dh
     monkeypatch.setenv("PHX_ATTN", "mma")
     want_all, _ = ranker_attention(q, k, v, seg, S, sm, cap[0], cap[1])
-    monkeypatch.delenv("PHX_ATTN")
+    monkeypatch.setenv("PHX_ATTN", "pingpong")
     before = dispatch_counts()
-    out, ms = ranker_attention(q, k, v, seg, S, sm, cap[0], cap[1])       # default dispatch: 384 items >= 148
+    out, ms = ranker_attention(q, k, v, seg, S, sm, cap[0], cap[1])
     assert dispatch_counts()["attn.pingpong"] - before["attn.pingpong"] == 1
     rows = [0, 1, 2, B - 1]
     sl = lambda x: x[rows].float().cpu().numpy()

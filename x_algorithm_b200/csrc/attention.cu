@@ -682,12 +682,14 @@ phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::
     if (plain && !legacy && prefer_tc && a.err_flag && ranker_attention_tc_supported(a)) return ranker_attention_tc_launch(a, a.err_flag, stream, err);
   }
   {
-    // Head dim 64 with a history of at most 128 keys at throughput batch sizes: the tcgen05 kernel with the history
-    // resident and two softmax warpgroups (PHX_ATTN=strip|mma keep the mma.sync kernels, PHX_ATTN=pingpong forces it).
+    // Head dim 64 with a history of at most 128 keys: the persistent tcgen05 kernel with the history resident and two
+    // softmax warpgroups is selected with PHX_ATTN=pingpong.  Measured on B200 at the ranking benchmark's shape it
+    // takes 2.5 ms per step against 2.1 ms for the mma.sync resident-history kernel below (its 8 softmax warps per
+    // SM leave the tensor-memory, shared-memory and global round trips of a tile exposed, where the mma.sync kernel
+    // has 16 independent warps), so the default stays with the latter.
     const char* force = getenv("PHX_ATTN");
     const bool forced = force && strcmp(force, "pingpong") == 0;
-    const bool enough = (long long)a.B * a.Hq >= 148;
-    if ((forced || (!force && enough)) && a.err_flag && ranker_attention_pingpong_supported(a))
+    if (forced && a.err_flag && ranker_attention_pingpong_supported(a))
       return ranker_attention_pingpong_launch(a, a.err_flag, stream, err);
   }
   const bool cap = a.cap_method != 0 && a.cap > 0.f;

@@ -621,12 +621,13 @@ ranker_attention_resident_kernel(const __grid_constant__ CUtensorMap map_q, cons
 // memory (S0, S1 at columns 0 / 128, O0, O1 at 256 / 320) and its own P buffer in shared memory: while one warpgroup
 // exponentiates tile g, the MMA warp has already produced S of tile g+1 for the other, and P V of tile g runs under
 // the other warpgroup's softmax.  Thread = query row: the whole 128-key S row is read from tensor memory once, kept in
-// registers, and turned into P in one pass.  The candidate x candidate block is never formed: a candidate's own key
+// registers 64 keys at a time (once for the row maximum, once for the probabilities), so the row never spills.  The
+// candidate x candidate block is never formed: a candidate's own key
 // is one extra softmax term from a per-row dot product (its k / v rows are requested a tile ahead).  Query tiles are
 // taken from the history block and the candidate block separately, so the plain [B, T] token layout and the split
 // layout (all history rows, then all candidate rows) differ only in the tensor maps' strides; candidate-only layers
 // skip the history tiles.  All waits are bounded (sm100_ptx.cuh).
-constexpr int PP_THREADS = 320;
+constexpr int PP_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2-5 softmax warpgroup 0, warps 6-9 softmax warpgroup 1
 constexpr int PP_NQ = 3;
 
 struct PingArgs {
@@ -762,7 +763,8 @@ ranker_attention_pingpong_kernel(const __grid_constant__ CUtensorMap map_qh, con
     const uint32_t myP = sP + (2 * w) * SLAB;
     auto wg_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(1 + w) : "memory"); };
 
-    struct Tile { int b, h, hk, li; long long tok; int seg; bool cand; };
+    // what a thread needs to know about its row of a tile; the two segment words are loaded a tile ahead of their use
+    struct Tile { int b, h, hk, li; long long tok; int seg, hseg; bool cand; };
     auto tile_of = [&](int g) {
       Tile t;
       t.li = g / nt;
@@ -774,10 +776,13 @@ ranker_attention_pingpong_kernel(const __grid_constant__ CUtensorMap map_qh, con
       const bool in = p < (t.cand ? a.n_cand : a.n_hist);
       t.tok = in ? (t.cand ? a.cand_row0 + (long long)t.b * a.cand_req_rows + p : a.hist_row0 + (long long)t.b * a.hist_req_rows + p) : -1;
       t.seg = in ? a.seg[t.tok] : 0;
+      t.hseg = (r < a.n_hist) ? a.seg[a.hist_row0 + (long long)t.b * a.hist_req_rows + r] : 0;   // history key r of the item
       return t;
     };
+    // a candidate row's own k / v row (requested whether or not the slot is padded: the address does not wait for the
+    // segment word)
     auto load_row = [&](const bf16* basep, long long stride, const Tile& t, int hoff, uint4 (&dst)[DH / 8]) {
-      if (t.cand && t.seg == -1) {
+      if (t.cand && t.tok >= 0) {
         const uint4* p = reinterpret_cast<const uint4*>(basep + t.tok * stride + hoff);
 #pragma unroll
         for (int c = 0; c < DH / 8; ++c) dst[c] = __ldg(p + c);
@@ -828,8 +833,7 @@ ranker_attention_pingpong_kernel(const __grid_constant__ CUtensorMap map_qh, con
       }
       if (cur.li != mask_li) {
         // validity of the item's history keys (the same for all of its tiles)
-        const bool ok = (r < a.n_hist) && (a.seg[a.hist_row0 + (long long)cur.b * a.hist_req_rows + r] == 1);
-        const uint32_t word = __ballot_sync(0xffffffffu, ok);
+        const uint32_t word = __ballot_sync(0xffffffffu, cur.hseg == 1);
         wg_sync();                                   // the words of the previous item have been read by every thread
         if (lane == 0) mask_words[w * 4 + quad] = word;
         wg_sync();
@@ -841,55 +845,64 @@ ranker_attention_pingpong_kernel(const __grid_constant__ CUtensorMap map_qh, con
 
       mbar_wait(s_full(w), ph, verr);
       tc_fence_after();
-      float s[128];
+      // one 64-key half of the S row, capped and masked, into registers
+      auto load_s_half = [&](int c, float (&sv)[64]) {
+        tmem_ld32_nowait(tmem + TM_S + w * 128 + lane_base + c * 64, reinterpret_cast<uint32_t*>(sv));
+        tmem_ld32_nowait(tmem + TM_S + w * 128 + lane_base + c * 64 + 32, reinterpret_cast<uint32_t*>(sv) + 32);
+        tmem_ld_wait();
+        if (CAP) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32_nowait(tmem + TM_S + w * 128 + lane_base + c * 32, reinterpret_cast<uint32_t*>(s) + c * 32);
-      tmem_ld_wait();
-      if (CAP) {
-#pragma unroll
-        for (int k = 0; k < 128; ++k) s[k] = capped_log2(s[k], a.sm_scale, a.cap, a.cap_method);
-      }
-      if (!all_ok) {
-#pragma unroll
-        for (int k = 0; k < 128; ++k)
-          if (!((kmask[k >> 5] >> (k & 31)) & 1u)) s[k] = -INFINITY;
-      }
-      float bm;
-      {
-        float b4[4] = {s[0], s[1], s[2], s[3]};
-#pragma unroll
-        for (int k = 4; k + 7 < 128; k += 8) {
-          b4[0] = max3f(b4[0], s[k], s[k + 1]); b4[1] = max3f(b4[1], s[k + 2], s[k + 3]);
-          b4[2] = max3f(b4[2], s[k + 4], s[k + 5]); b4[3] = max3f(b4[3], s[k + 6], s[k + 7]);
+          for (int k = 0; k < 64; ++k) sv[k] = capped_log2(sv[k], a.sm_scale, a.cap, a.cap_method);
         }
-        bm = fmaxf(max3f(b4[0], b4[1], b4[2]), b4[3]);
+        if (!all_ok) {
 #pragma unroll
-        for (int k = 124; k < 128; ++k) bm = fmaxf(bm, s[k]);
+          for (int k = 0; k < 64; ++k)
+            if (!((kmask[c * 2 + (k >> 5)] >> (k & 31)) & 1u)) sv[k] = -INFINITY;
+        }
+      };
+      // pass 1: the row maximum
+      float bm = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float sv[64];
+        load_s_half(c, sv);
+        float b4[4] = {sv[0], sv[1], sv[2], sv[3]};
+#pragma unroll
+        for (int k = 4; k + 7 < 64; k += 8) {
+          b4[0] = max3f(b4[0], sv[k], sv[k + 1]); b4[1] = max3f(b4[1], sv[k + 2], sv[k + 3]);
+          b4[2] = max3f(b4[2], sv[k + 4], sv[k + 5]); b4[3] = max3f(b4[3], sv[k + 6], sv[k + 7]);
+        }
+        bm = fmaxf(bm, fmaxf(max3f(b4[0], b4[1], b4[2]), b4[3]));
+#pragma unroll
+        for (int k = 60; k < 64; ++k) bm = fmaxf(bm, sv[k]);
       }
       float m = bm * csc;
       const bool is_cand = cur.cand && cur.seg == -1;
       if (is_cand) m = fmaxf(m, self_logit);           // the self key takes part in the row maximum right away
       const float mns = (m == -INFINITY) ? 0.f : m;
-      float l;
-      {
+      // pass 2: probabilities, row sum, P in bf16 into this warpgroup's operand buffer (its previous contents were
+      // consumed by the P V product this thread waited for at the end of its previous tile)
+      float l = 0.f;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float sv[64];
+        load_s_half(c, sv);
         const float2 c2 = make_float2(csc, csc), n2 = make_float2(-mns, -mns);
         float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-        for (int k = 0; k < 128; k += 2) {           // packed fp32: two keys per instruction; masked keys: 2^-inf = 0
-          const float2 e = __ffma2_rn(make_float2(s[k], s[k + 1]), c2, n2);
-          s[k] = ex2f(e.x); s[k + 1] = ex2f(e.y);
-          acc2[(k >> 1) & 1] = __fadd2_rn(acc2[(k >> 1) & 1], make_float2(s[k], s[k + 1]));
+        for (int k = 0; k < 64; k += 2) {            // packed fp32: two keys per instruction; masked keys: 2^-inf = 0
+          const float2 e = __ffma2_rn(make_float2(sv[k], sv[k + 1]), c2, n2);
+          sv[k] = ex2f(e.x); sv[k + 1] = ex2f(e.y);
+          acc2[(k >> 1) & 1] = __fadd2_rn(acc2[(k >> 1) & 1], make_float2(sv[k], sv[k + 1]));
         }
-        l = (acc2[0].x + acc2[0].y) + (acc2[1].x + acc2[1].y);
-      }
-      // P (bf16) into this warpgroup's operand buffer; its previous contents were consumed by the P V product this
-      // thread waited for at the end of its previous tile
+        l += (acc2[0].x + acc2[0].y) + (acc2[1].x + acc2[1].y);
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        uint4 o;
-        o.x = pack_bf2(s[c * 8 + 0], s[c * 8 + 1]); o.y = pack_bf2(s[c * 8 + 2], s[c * 8 + 3]);
-        o.z = pack_bf2(s[c * 8 + 4], s[c * 8 + 5]); o.w = pack_bf2(s[c * 8 + 6], s[c * 8 + 7]);
-        st_shared_16(myP + (c >> 3) * SLAB + r * 128 + ((uint32_t)((c & 7) ^ sw) << 4), o);
+        for (int cc = 0; cc < 8; ++cc) {
+          uint4 o;
+          o.x = pack_bf2(sv[cc * 8 + 0], sv[cc * 8 + 1]); o.y = pack_bf2(sv[cc * 8 + 2], sv[cc * 8 + 3]);
+          o.z = pack_bf2(sv[cc * 8 + 4], sv[cc * 8 + 5]); o.w = pack_bf2(sv[cc * 8 + 6], sv[cc * 8 + 7]);
+          st_shared_16(myP + c * SLAB + r * 128 + ((uint32_t)(cc ^ sw) << 4), o);
+        }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
