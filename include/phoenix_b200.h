@@ -512,6 +512,51 @@ phx_status phx_gather_sum_sharded(phx_comm* comm, phx_engine* e, int32_t family,
                                   uint16_t* out_dev, void* stream);
 phx_status phx_gather_sharded_phase_ms(phx_comm* comm, float* ms7);
 
+/* ---- serving shell: request queue and admission control -----------------------------------------------------------
+ * The duties of the reference's serving engine between its wire layer and the model runner's dispatch loop
+ * (`server.dequeue()`, model_runner.py:3026-3046), host code only.
+ *
+ * Request queue (xai-recsys-engine/src/request_queue.rs:10-155): producers push (request id, enqueue time, optional
+ * deadline) into a bounded channel (PHX_E_CAPACITY when it is full); phx_queue_dequeue moves requests into the batch
+ * under construction, hands out at most batch_size request ids in arrival order, and drops - reporting them in
+ * dropped_out, the reference's on_stale_drop - every request that has expired on the way: past its deadline, or, without
+ * a deadline, older than max_staleness_us (UINT64_MAX = never).  With batch_wait_us > 0 the call waits up to that long
+ * for the batch to fill (from an empty start: for one request), polling every millisecond.  Times are microseconds of
+ * one monotonic clock the host chooses (phx_now_us gives one); ids_out must hold batch_size entries. */
+typedef struct phx_request_queue phx_request_queue;
+uint64_t phx_now_us(void);
+phx_status phx_queue_create(int32_t batch_size, int32_t channel_size, uint64_t max_staleness_us, uint64_t batch_wait_us,
+                            phx_request_queue** out);
+void phx_queue_destroy(phx_request_queue* q);
+phx_status phx_queue_push(phx_request_queue* q, uint64_t request_id, uint64_t enqueue_time_us, uint64_t deadline_us /* 0 = none */);
+phx_status phx_queue_dequeue(phx_request_queue* q, uint64_t now_us, uint64_t* ids_out, int32_t max_out, int32_t* n_out,
+                             uint64_t* dropped_out, int32_t max_dropped, int32_t* n_dropped);
+phx_status phx_queue_stats(phx_request_queue* q, int32_t* waiting, uint64_t* total_dropped);
+
+/* Admission control (xai-recsys-engine/src/admission.rs:44-227): a request is refused at the door when the predicted
+ * time to its answer exceeds what is left of its deadline.  Two estimators: eta_model 0 ("loop") = (batches ahead +
+ * pipeline_depth) * service time + post_us, with the service time an EWMA of phx_admission_record_service_us samples;
+ * eta_model 1 ("pipeline") = queue wait + pipeline time + post_us, the pipeline time an EWMA of sojourn samples minus
+ * their queue wait.  Nothing is refused while the backlog is below one batch, without an estimate, or without a
+ * deadline (remaining_us < 0). */
+typedef struct phx_admission_config {
+  int32_t enabled;
+  int32_t eta_model;           /* 0 loop, 1 pipeline */
+  uint64_t batch_size, margin_us, post_us, fallback_budget_us, pipeline_depth;
+  double ewma_alpha;           /* outside (0, 1]: 0.2 */
+} phx_admission_config;
+typedef struct phx_admission phx_admission;
+phx_status phx_admission_create(const phx_admission_config* cfg, phx_admission** out);
+void phx_admission_destroy(phx_admission* a);
+phx_status phx_admission_set_enabled(phx_admission* a, int32_t on);
+phx_status phx_admission_reset(phx_admission* a);
+phx_status phx_admission_record_service_us(phx_admission* a, uint64_t sample_us);
+phx_status phx_admission_record_sojourn_us(phx_admission* a, uint64_t sample_us, int64_t admit_backlog);
+/* 1 and *eta_us when an estimate exists, else 0; model < 0 = the configured one */
+int32_t phx_admission_predicted_eta_us(phx_admission* a, int64_t queue_depth, int32_t model, uint64_t* eta_us);
+int32_t phx_admission_should_reject(phx_admission* a, int64_t remaining_us /* < 0 = no deadline */, int64_t queue_depth);
+phx_status phx_admission_estimates(phx_admission* a, uint64_t* service_time_us, uint64_t* pipeline_time_us);
+
 /* ---- value model after the heads (xai-value-model/scoring.rs) ---------------------------------- */
 
 /* PhoenixScores fields in declaration order (xai-value-model/phoenix_scores.rs:2-32): favorite, reply, retweet,

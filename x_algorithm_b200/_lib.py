@@ -68,6 +68,12 @@ class ValueInputs(C.Structure):  # phx_value_inputs
         "num_valid", "context")]
 
 
+class AdmissionConfig(C.Structure):   # phx_admission_config
+    _fields_ = [("enabled", C.c_int32), ("eta_model", C.c_int32), ("batch_size", C.c_uint64), ("margin_us", C.c_uint64),
+                ("post_us", C.c_uint64), ("fallback_budget_us", C.c_uint64), ("pipeline_depth", C.c_uint64),
+                ("ewma_alpha", C.c_double)]
+
+
 # every symbol include/phoenix_b200.h declares: name -> (restype, argtypes)
 _P = C.c_void_p
 SIGNATURES = {
@@ -151,6 +157,21 @@ SIGNATURES = {
     "phx_gather_sharded_setup": (C.c_int32, [_P, _P, C.c_int64, C.c_double]),
     "phx_gather_sum_sharded": (C.c_int32, [_P, _P, C.c_int32, _P, C.c_int64, _P, _P]),
     "phx_gather_sharded_phase_ms": (C.c_int32, [_P, C.POINTER(C.c_float)]),
+    "phx_now_us": (C.c_uint64, []),
+    "phx_queue_create": (C.c_int32, [C.c_int32, C.c_int32, C.c_uint64, C.c_uint64, C.POINTER(_P)]),
+    "phx_queue_destroy": (None, [_P]),
+    "phx_queue_push": (C.c_int32, [_P, C.c_uint64, C.c_uint64, C.c_uint64]),
+    "phx_queue_dequeue": (C.c_int32, [_P, C.c_uint64, _P, C.c_int32, C.POINTER(C.c_int32), _P, C.c_int32, C.POINTER(C.c_int32)]),
+    "phx_queue_stats": (C.c_int32, [_P, C.POINTER(C.c_int32), C.POINTER(C.c_uint64)]),
+    "phx_admission_create": (C.c_int32, [C.POINTER(AdmissionConfig), C.POINTER(_P)]),
+    "phx_admission_destroy": (None, [_P]),
+    "phx_admission_set_enabled": (C.c_int32, [_P, C.c_int32]),
+    "phx_admission_reset": (C.c_int32, [_P]),
+    "phx_admission_record_service_us": (C.c_int32, [_P, C.c_uint64]),
+    "phx_admission_record_sojourn_us": (C.c_int32, [_P, C.c_uint64, C.c_int64]),
+    "phx_admission_predicted_eta_us": (C.c_int32, [_P, C.c_int64, C.c_int32, C.POINTER(C.c_uint64)]),
+    "phx_admission_should_reject": (C.c_int32, [_P, C.c_int64, C.c_int64]),
+    "phx_admission_estimates": (C.c_int32, [_P, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "phx_corpus_sync": (C.c_int32, [_P]),
     "phx_corpus_finish": (C.c_int32, [_P, C.POINTER(C.c_int32)]),
     "phx_corpus_set_exact": (C.c_int32, [_P, C.c_int32]),
