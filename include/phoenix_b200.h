@@ -412,9 +412,9 @@ phx_status phx_corpus_set_stream(phx_corpus* c, void* stream, int32_t use_own);
 /* Per-row eligibility of the shard (the reference's per-post masks ahead of the top-k: dataset type mask and
  * eligibility mask, recsys_two_tower_model.py:2486-2493, 2690-2702, where a masked post's score becomes
  * finfo(bf16).min): bit (r & 31) of host_bits[r >> 5] set = shard-local row r may be returned; ceil(rows / 32) words;
- * NULL removes the mask.  Every later top-k call on this shard skips the other rows.  One difference from the
- * reference: it pads a result with masked posts (at the minimum score) when fewer than k are eligible, this library
- * refuses such a call (PHX_E_ARG).  Synchronises the shard's stream. */
+ * NULL removes the mask.  Every later top-k call on this shard skips the other rows; when a window holds fewer
+ * eligible rows than k, the list is completed with the window's first masked rows at finfo(bfloat16).min in ascending
+ * row order, which is what the reference's top-k over the masked scores returns.  Synchronises the shard's stream. */
 phx_status phx_corpus_set_mask(phx_corpus* c, const uint32_t* host_bits);
 /* The same top-k over rows [row_begin, row_end) of the shard only (shard-local row numbers): the reference's dataset
  * windows, where every retrieval dataset is a contiguous row range of the post table and each gets its own top-k
@@ -622,6 +622,52 @@ typedef struct phx_value_inputs {
  * (home-mixer/scorers/value_model.rs). */
 phx_status phx_value_scores_device(int32_t device, const phx_value_model* model, const phx_value_inputs* in,
                                    double* weighted_out, double* scores_out, void* stream);
+
+/* ---- diversity rerank behind the value model (vm-ranker/dpp.rs) --------------------------------------------------- */
+
+#define PHX_DPP_MAX_POOL 96
+#define PHX_DPP_MAX_CONTEXT 32
+
+/* DppConfig / SlidingWindow (vm-ranker/dpp.rs:14-29). */
+typedef struct phx_dpp_config {
+  int32_t top_k;               /* picks wanted, <= 96 */
+  int32_t max_selected_rank;   /* pool = this many best-scoring candidates, <= 96 */
+  int32_t greedy_order;        /* 1 = serve in pick order */
+  int32_t window_on;           /* 1 = sliding-window selection instead of the DPP kernel */
+  double theta;
+  int32_t window_size;         /* INT32_MAX = unbounded */
+  int32_t _pad;
+  double half_distance, sid_lambda;
+} phx_dpp_config;
+
+/* DppInput arrays of a batch of requests, DEVICE pointers (dpp.rs:31-38): embeddings are IEEE half bit patterns, norms
+ * as the caller computed them.  The context is the seed (if has_seed: item 0; only the seed is used without a
+ * window) followed by the history, most recent first. */
+typedef struct phx_dpp_inputs {
+  int32_t batch, num_candidates, emb_dim, num_context;
+  const double* scores;             /* [B,C] */
+  const uint16_t* embeddings;       /* [B,C,E] */
+  const double* norms;              /* [B,C] */
+  const uint8_t* missing;           /* [B,C] embedding_missing, or NULL */
+  const int32_t* l1;                /* [B,C] first-level semantic id, < 0 = none, or NULL */
+  const int32_t* num_valid;         /* [B] candidates of each request, or NULL = C */
+  const uint16_t* ctx_embeddings;   /* [B,Hc,E] */
+  const double* ctx_norms;          /* [B,Hc] */
+  const uint8_t* ctx_missing;       /* [B,Hc] or NULL */
+  const int32_t* ctx_l1;            /* [B,Hc] or NULL */
+  const int32_t* num_context_valid; /* [B] or NULL = Hc */
+  int32_t has_seed;
+  int32_t _pad;
+} phx_dpp_inputs;
+
+/* `rescore` (vm-ranker/dpp.rs:45-215) for B requests, one thread block each: out_index int32 [B, top_k] = the input
+ * index of the candidate served at each position (-1 behind the last pick), out_score f64 [B, top_k] = the score shown
+ * at that position (the picks' scores in descending order, whatever the serving order), out_count int32 [B].  Equal
+ * scores are ordered by input index where the reference's unstable sort leaves the order open; the dot product is the
+ * reference's scalar form.  On `stream` (a cudaStream_t, NULL = default stream).  Replaces the CPU rerank of
+ * vm-ranker. */
+phx_status phx_dpp_rescore_device(int32_t device, const phx_dpp_config* cfg, const phx_dpp_inputs* in, int32_t* out_index,
+                                  double* out_score, int32_t* out_count, void* stream);
 
 #ifdef __cplusplus
 }

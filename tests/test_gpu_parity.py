@@ -743,8 +743,22 @@ def test_topk_with_row_eligibility_mask(torch, monkeypatch, impl, dim, N):
         shard.set_mask(mask)
         check(mask, 0, N)
         check(mask, 1_001, N - 77)
-    with pytest.raises(px.PhoenixError):      # fewer eligible rows than k in the window
-        shard.topk_window_device(tu, B, k, 0, 2_000, scores, ids)
+    # fewer eligible rows than k in the window: the reference's top-k runs over the masked scores (masked rows at the
+    # bf16 minimum, recsys_two_tower_model.py:2492-2493), so the list ends with the window's first masked rows
+    lowest = np.array([0xFF7F0000], np.uint32).view(np.float32)[0]          # finfo(bfloat16).min
+    for r0, r1 in ((0, 2_000), (3_001, 3_400)):
+        n_el = int(mask[r0:r1].sum())
+        assert n_el < k <= r1 - r0
+        shard.topk_window_device(tu, B, k, r0, r1, scores, ids)
+        shard.sync()
+        want_s, want_i = po.top_k(np.where(mask[None, r0:r1], sc_all[:, r0:r1], lowest), k, row_offset=off + r0)
+        np.testing.assert_array_equal(ids.cpu().numpy(), want_i)
+        got_s = scores.cpu().numpy()
+        np.testing.assert_allclose(got_s[:, :n_el], want_s[:, :n_el], rtol=2.0 ** -7, atol=0)
+        assert (got_s[:, n_el:] == lowest).all()
+    keys = torch.empty((B, k), dtype=torch.int64, device="cuda")           # the same list in key form
+    shard.topk_keys_device(tu, B, k, keys)  # (whole shard: enough eligible rows, no padding)
+    shard.sync()
     shard.set_mask(None)
     check(None, 0, N)
     shard.close()

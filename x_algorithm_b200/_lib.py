@@ -68,6 +68,18 @@ class ValueInputs(C.Structure):  # phx_value_inputs
         "num_valid", "context")]
 
 
+class DppConfig(C.Structure):   # phx_dpp_config
+    _fields_ = [("top_k", C.c_int32), ("max_selected_rank", C.c_int32), ("greedy_order", C.c_int32), ("window_on", C.c_int32),
+                ("theta", C.c_double), ("window_size", C.c_int32), ("_pad", C.c_int32), ("half_distance", C.c_double),
+                ("sid_lambda", C.c_double)]
+
+
+class DppInputs(C.Structure):   # phx_dpp_inputs
+    _fields_ = [("batch", C.c_int32), ("num_candidates", C.c_int32), ("emb_dim", C.c_int32), ("num_context", C.c_int32)] + [
+        (n, C.c_void_p) for n in ("scores", "embeddings", "norms", "missing", "l1", "num_valid", "ctx_embeddings", "ctx_norms",
+                                  "ctx_missing", "ctx_l1", "num_context_valid")] + [("has_seed", C.c_int32), ("_pad", C.c_int32)]
+
+
 class AdmissionConfig(C.Structure):   # phx_admission_config
     _fields_ = [("enabled", C.c_int32), ("eta_model", C.c_int32), ("batch_size", C.c_uint64), ("margin_us", C.c_uint64),
                 ("post_us", C.c_uint64), ("fallback_budget_us", C.c_uint64), ("pipeline_depth", C.c_uint64),
@@ -172,6 +184,7 @@ SIGNATURES = {
     "phx_admission_predicted_eta_us": (C.c_int32, [_P, C.c_int64, C.c_int32, C.POINTER(C.c_uint64)]),
     "phx_admission_should_reject": (C.c_int32, [_P, C.c_int64, C.c_int64]),
     "phx_admission_estimates": (C.c_int32, [_P, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "phx_dpp_rescore_device": (C.c_int32, [C.c_int32, C.POINTER(DppConfig), C.POINTER(DppInputs), _P, _P, _P, _P]),
     "phx_corpus_sync": (C.c_int32, [_P]),
     "phx_corpus_finish": (C.c_int32, [_P, C.POINTER(C.c_int32)]),
     "phx_corpus_set_exact": (C.c_int32, [_P, C.c_int32]),

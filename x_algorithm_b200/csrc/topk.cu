@@ -300,7 +300,10 @@ __global__ void __launch_bounds__(SEL_THREADS) pivot_kernel(const float* __restr
 __global__ void __launch_bounds__(SEL_THREADS) select_kernel(const unsigned long long* __restrict__ keys, const int* counts,
                                                              int fixed_n, int cap, int k, int kpow2,
                                                              float* __restrict__ out_scores, long long* __restrict__ out_ids,
-                                                             int* status, unsigned long long* __restrict__ out_keys = nullptr) {
+                                                             int* status, unsigned long long* __restrict__ out_keys = nullptr,
+                                                             int ostride = 0) {
+  // ostride: entries per query in the output arrays when they hold more than this kernel's k (the tail is padded by
+  // the caller); 0 = k
   // out_keys: write the sorted 64-bit keys themselves (ordered score << 32 | ~row; 0 = empty slot) instead of
   // (score, id) pairs - the form per-shard lists travel in before a merge
   extern __shared__ __align__(16) uint8_t selsm[];
@@ -309,13 +312,14 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(const unsigned long
   __shared__ unsigned long long s_bcast[2];
   __shared__ int s_fill;
   const int u = blockIdx.x;
+  const size_t ob = (size_t)u * (ostride > 0 ? ostride : k);
   int n = counts ? counts[u] : fixed_n;
   if (counts && n > cap) { if (threadIdx.x == 0) atomicOr(status, 2); n = cap; }
   if (n < k) {
     if (threadIdx.x == 0) atomicOr(status, 1);
     for (int i = threadIdx.x; i < k; i += blockDim.x) {
-      if (out_keys) out_keys[(size_t)u * k + i] = 0ull;
-      else { out_scores[(size_t)u * k + i] = -INFINITY; out_ids[(size_t)u * k + i] = -1; }
+      if (out_keys) out_keys[ob + i] = 0ull;
+      else { out_scores[ob + i] = -INFINITY; out_ids[ob + i] = -1; }
     }
     return;
   }
@@ -334,10 +338,10 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(const unsigned long
   bitonic_sort_desc(s_keys, kpow2);
   for (int i = threadIdx.x; i < k; i += blockDim.x) {
     const unsigned long long v = s_keys[i];
-    if (out_keys) { out_keys[(size_t)u * k + i] = v; continue; }
+    if (out_keys) { out_keys[ob + i] = v; continue; }
     // key 0 is an empty slot (the lists held fewer than k entries): the same (-inf, -1) the underflow path writes
-    out_scores[(size_t)u * k + i] = v ? from_ordered32((uint32_t)(v >> 32)) : -INFINITY;
-    out_ids[(size_t)u * k + i] = v ? (long long)(0xFFFFFFFFu - (uint32_t)(v & 0xFFFFFFFFull)) : -1ll;
+    out_scores[ob + i] = v ? from_ordered32((uint32_t)(v >> 32)) : -INFINITY;
+    out_ids[ob + i] = v ? (long long)(0xFFFFFFFFu - (uint32_t)(v & 0xFFFFFFFFull)) : -1ll;
   }
 }
 
@@ -367,6 +371,21 @@ __global__ void merge_keys_kernel(const float* __restrict__ scores, const long l
 }
 
 int next_pow2(int v) { int p = 1; while (p < v) p <<= 1; return p; }
+
+// Fewer eligible rows than k: the reference's top-k runs over every row with the masked ones at the bf16 minimum
+// (recsys_two_tower_model.py:2492-2493), so its list ends with masked rows in ascending row order at that score.
+// pad_rows [n_pad] = the first masked rows of the window (global ids); written behind the `have` real entries.
+__global__ void pad_masked_kernel(const long long* __restrict__ pad_rows, int n_pad, int have, int k, int B,
+                                  float* __restrict__ out_scores, long long* __restrict__ out_ids,
+                                  unsigned long long* __restrict__ out_keys) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= B * n_pad) return;
+  const int u = i / n_pad, j = i % n_pad;
+  const float lowest = __uint_as_float(0xFF7F0000u);            // finfo(bfloat16).min
+  const size_t o = (size_t)u * k + have + j;
+  if (out_keys) out_keys[o] = ((unsigned long long)ordered32(lowest) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)pad_rows[j]);
+  else { out_scores[o] = lowest; out_ids[o] = pad_rows[j]; }
+}
 
 // one word per rank for the all-gather beside the lists: scan status in the low byte, the bounded-wait flag above it
 __global__ void pack_status_kernel(const int* status, const int* err_flag, int* out) {
@@ -401,6 +420,8 @@ struct phx_corpus {
   unsigned int* mask = nullptr;              // eligibility bits of the shard's rows (phx_corpus_set_mask), null = all
   std::vector<unsigned int> mask_host;
   long long elig_begin = -1, elig_end = -1, elig_count = 0;   // eligible rows of the last window asked for
+  long long* pad_rows = nullptr;             // device [max_k]: the window's first masked rows, for lists longer than its eligible rows
+  long long pad_begin = -1, pad_end = -1; int pad_have = 0;
   cudaStream_t stream = nullptr;       // the stream the shard's work is enqueued on: its own, or the caller's
   cudaStream_t own_stream = nullptr;
   unsigned long long* keys_out = nullptr;   // set for one call by phx_corpus_topk_keys_device
@@ -452,7 +473,7 @@ phx_status run_scan(phx_corpus* c, const ScanArgs& a, int mode, int grid) {
 // scan and the usual select.  Keys are unique, so the bisection always ends (at the latest with exactly k rows), whatever
 // the scores look like: many equal scores, clustered rows, a corpus of copies.  Host-driven and synchronous between
 // steps; a few tens of scans, for the calls the sampled pivot cannot serve.
-phx_status topk_exact(phx_corpus* c, ScanArgs a, int B, int k, float* scores_dev, long long* ids_dev) {
+phx_status topk_exact(phx_corpus* c, ScanArgs a, int B, int k, float* scores_dev, long long* ids_dev, int ostride = 0) {
   dispatch_note(DK_TOPK_EXACT);
   const long long n_tiles = (a.rows + TILE_ROWS - 1) / TILE_ROWS;
   const int grid = (int)(n_tiles < c->num_sms * 2 ? n_tiles : c->num_sms * 2);
@@ -490,7 +511,7 @@ phx_status topk_exact(phx_corpus* c, ScanArgs a, int B, int k, float* scores_dev
   if (s) return s;
   const int kp2 = next_pow2(k);
   select_kernel<<<B, SEL_THREADS, (size_t)kp2 * 8, c->stream>>>(c->surv, c->counts, 0, c->cap, k, kp2, scores_dev, ids_dev,
-                                                               c->status, c->keys_out);
+                                                               c->status, c->keys_out, ostride);
   PHX_CUDA_TRY(cudaGetLastError(), c->err);
   PHX_CUDA_TRY(cudaStreamSynchronize(c->stream), c->err);   // the host vectors above were the copies' sources
   c->exact_runs++;
@@ -554,7 +575,7 @@ void phx_corpus_destroy(phx_corpus* c) {
   cudaSetDevice(c->device);
   if (c->stream) cudaStreamSynchronize(c->stream);
   auto fr = [](void* p) { if (p) cudaFree(p); };
-  fr(c->data); fr(c->users_bf); fr(c->gmax); fr(c->pivot); fr(c->surv); fr(c->merge_keys); fr(c->counts); fr(c->status); fr(c->err_flag); fr(c->mask); fr(c->thr);
+  fr(c->data); fr(c->users_bf); fr(c->gmax); fr(c->pivot); fr(c->surv); fr(c->merge_keys); fr(c->counts); fr(c->status); fr(c->err_flag); fr(c->mask); fr(c->thr); fr(c->pad_rows);
   if (c->ev0) cudaEventDestroy(c->ev0);
   if (c->ev1) cudaEventDestroy(c->ev1);
   if (c->own_stream) cudaStreamDestroy(c->own_stream);
@@ -592,6 +613,7 @@ phx_status phx_corpus_set_mask(phx_corpus* c, const uint32_t* host_bits) {
   cudaSetDevice(c->device);
   PHX_CUDA_TRY(cudaStreamSynchronize(c->stream), c->err);   // no scan may be reading the old bits
   c->elig_begin = c->elig_end = -1;
+  c->pad_begin = c->pad_end = -1;
   if (!host_bits) {
     if (c->mask) cudaFree(c->mask);
     c->mask = nullptr; c->mask_host.clear();
@@ -624,7 +646,23 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
       }
       c->elig_begin = row_begin; c->elig_end = row_end; c->elig_count = n;
     }
-    if (k > c->elig_count) { c->err = "topk: fewer eligible rows than k in the window"; return PHX_E_ARG; }
+  }
+  // k_real entries come from the scan; a window with fewer eligible rows than k is completed with its first masked
+  // rows at the bf16 minimum, as the reference's top-k over masked scores does
+  const int k_real = (c->mask && k > c->elig_count) ? (int)c->elig_count : k;
+  const int n_pad = k - k_real;
+  if (n_pad > 0) {
+    if (c->pad_begin != row_begin || c->pad_end != row_end || c->pad_have < n_pad) {
+      std::vector<long long> rows_h;
+      rows_h.reserve(n_pad);
+      for (long long r = row_begin; r < row_end && (int)rows_h.size() < n_pad; ++r)
+        if (!((c->mask_host[r >> 5] >> (r & 31)) & 1u)) rows_h.push_back(c->row_offset + r);
+      if (!c->pad_rows) PHX_CUDA_TRY(cudaMalloc(&c->pad_rows, (size_t)c->max_k * sizeof(long long)), c->err);
+      cudaSetDevice(c->device);
+      PHX_CUDA_TRY(cudaMemcpyAsync(c->pad_rows, rows_h.data(), rows_h.size() * sizeof(long long), cudaMemcpyHostToDevice, c->stream), c->err);
+      PHX_CUDA_TRY(cudaStreamSynchronize(c->stream), c->err);   // rows_h goes out of scope
+      c->pad_begin = row_begin; c->pad_end = row_end; c->pad_have = n_pad;
+    }
   }
   cudaSetDevice(c->device);
   const CUtensorMap* map_corpus = &c->map_corpus;
@@ -638,6 +676,12 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
     map_corpus = &c->map_window;
   }
   const int Bpad = c->use_tc ? 256 : (B <= 16 ? 16 : (B <= 64 ? 64 : 256));
+  auto pad_tail = [&]() -> phx_status {
+    if (n_pad == 0) return PHX_OK;
+    pad_masked_kernel<<<(B * n_pad + 255) / 256, 256, 0, c->stream>>>(c->pad_rows, n_pad, k_real, k, B, scores_dev, (long long*)ids_dev, c->keys_out);
+    PHX_CUDA_TRY(cudaGetLastError(), c->err);
+    return PHX_OK;
+  };
   c->last.valid = true; c->last.users = users_dev; c->last.B = B; c->last.k = k; c->last.row_begin = row_begin;
   c->last.row_end = row_end; c->last.scores = scores_dev; c->last.ids = (long long*)ids_dev; c->last.keys = c->keys_out;
   PHX_CUDA_TRY(cudaEventRecord(c->ev0, c->stream), c->err);
@@ -646,8 +690,17 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
     xa.corpus = data; xa.users = c->users_bf; xa.rows = rows; xa.row_offset = roff; xa.dim = c->dim; xa.B = B; xa.Bpad = Bpad;
     xa.stride = 1; xa.gmax = c->gmax; xa.n_groups = 0; xa.pivot = c->pivot; xa.surv = c->surv; xa.counts = c->counts; xa.cap = c->cap;
     xa.mask = c->mask; xa.mask_row0 = row_begin;
-    phx_status xs = topk_exact(c, xa, B, k, scores_dev, (long long*)ids_dev);
-    if (xs) return xs;
+    if (k_real > 0) {
+      phx_status xs = topk_exact(c, xa, B, k_real, scores_dev, (long long*)ids_dev, k);
+      if (xs) return xs;
+    }
+    { phx_status ps = pad_tail(); if (ps) return ps; }
+    PHX_CUDA_TRY(cudaEventRecord(c->ev1, c->stream), c->err);
+    return PHX_OK;
+  }
+  if (k_real == 0) {   // nothing eligible in the window: the list is all padding
+    phx_status ps = pad_tail();
+    if (ps) return ps;
     PHX_CUDA_TRY(cudaEventRecord(c->ev1, c->stream), c->err);
     return PHX_OK;
   }
@@ -671,7 +724,7 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
   // a window whose eligible rows all fit the survivor buffer needs no pivot: every eligible row is collected
   if (rows > c->cap && !(c->mask && c->elig_count <= c->cap)) {
     // sample every stride-th tile so that about 48 of the wanted ~3k rows fall into the sample
-    const double want = 3.0 * k;
+    const double want = 3.0 * k_real;
     long long stride = (long long)(want / 48.0);
     if (stride < 1) stride = 1;
     long long sampled_tiles = (n_tiles + stride - 1) / stride;
@@ -698,10 +751,11 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
     else s = run_scan(c, a, 1, (int)(n_tiles < c->num_sms * 2 ? n_tiles : c->num_sms * 2));
     if (s) return s;
   }
-  const int kp2 = next_pow2(k);
-  select_kernel<<<B, SEL_THREADS, (size_t)kp2 * 8, c->stream>>>(c->surv, c->counts, 0, c->cap, k, kp2, scores_dev,
-                                                               (long long*)ids_dev, c->status, c->keys_out);
+  const int kp2 = next_pow2(k_real);
+  select_kernel<<<B, SEL_THREADS, (size_t)kp2 * 8, c->stream>>>(c->surv, c->counts, 0, c->cap, k_real, kp2, scores_dev,
+                                                               (long long*)ids_dev, c->status, c->keys_out, k);
   PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  { phx_status ps = pad_tail(); if (ps) return ps; }
   PHX_CUDA_TRY(cudaEventRecord(c->ev1, c->stream), c->err);
   return PHX_OK;
 }
