@@ -237,6 +237,11 @@ class ModelConfig:
     num_candidate_only_layers: int = 0   # tail layers that leave the history rows frozen (transformer.py:789-871)
     token_combine: str = "sum"     # "sum" | "project": concat(rows) @ proj_mat (recsys_model.py:2163-2365)
     action_multi_hot: bool = False  # history actions as a set per position (multi_hot_to_embeddings, recsys_model.py:3259-3314)
+    # the batch-prep buffers beyond posts and authors (xai-recsys-engine/src/python.rs:1394-1404), see rank_forward_prep
+    user_prefix: bool = False       # user token in front of the history (block_user_reduce, recsys_model.py:1889-1927)
+    cand_surface: bool = False      # product-surface row in candidate tokens (block_candidate_reduce, 2278-2365)
+    hist_continuous: tuple = ()     # ((column, norm_scale, use_log), ...) (block_history_reduce, 2249-2271)
+    hist_cont_hidden: int = 64
 
     @property
     def ffn_size(self) -> int:
@@ -310,6 +315,25 @@ def make_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02) -> Dict[str
         H2 = 2 * cfg.num_hashes
         w["proj_hist"] = bf16_round(rng.standard_normal(((H2 + 2) * D, D), dtype=np.float32) / np.float32(math.sqrt(D)))
         w["proj_cand"] = bf16_round(rng.standard_normal((H2 * D, D), dtype=np.float32) / np.float32(math.sqrt(D)))
+    return w
+
+
+def make_prep_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02) -> Dict[str, np.ndarray]:
+    """make_weights plus the parameters of the batch-prep extras, drawn from a stream of their own: "proj_user"
+    (proj_mat_1, recsys_model.py:1907-1914), a wider "proj_cand" when candidates carry a surface row (proj_mat_2,
+    2318-2326) and the two matrices of each continuous history action (1864-1884)."""
+    w = make_weights(cfg, seed, std)
+    rng = np.random.Generator(np.random.PCG64(seed + 7919))
+    D, H = cfg.emb_size, cfg.num_hashes
+    if cfg.token_combine == "project":
+        if cfg.user_prefix:
+            w["proj_user"] = bf16_round(rng.standard_normal((H * D, D), dtype=np.float32) / np.float32(math.sqrt(D)))
+        if cfg.cand_surface:
+            w["proj_cand"] = bf16_round(rng.standard_normal(((2 * H + 1) * D, D), dtype=np.float32) / np.float32(math.sqrt(D)))
+    for i in range(len(cfg.hist_continuous)):
+        w[f"hist_cont{i}.proj1"] = bf16_round(rng.standard_normal((1, cfg.hist_cont_hidden), dtype=np.float32))
+        w[f"hist_cont{i}.proj2"] = bf16_round(rng.standard_normal((cfg.hist_cont_hidden, D), dtype=np.float32)
+                                              / np.float32(math.sqrt(D * cfg.hist_cont_hidden)))
     return w
 
 
@@ -594,6 +618,147 @@ def rank_forward(cfg: ModelConfig, w: Dict[str, np.ndarray], table_rows_fn, batc
     if taps is not None:
         taps["hfin"] = hfin
     return log_probs, cont, lf
+
+
+@dataclass
+class PrepBatch:
+    """The mandatory buffers of the reference's batch-prep under its names (xai-recsys-engine/src/python.rs:1394-1404)."""
+    user_hashes: np.ndarray                  # int32 [B,Hu]   rows of the unified table, 0 = padding
+    user_ip_hashes: Optional[np.ndarray]     # int32 [B,Hip]
+    history_post_hashes: np.ndarray          # int32 [B,S,H]
+    history_auth_hashes: np.ndarray          # int32 [B,S,H]
+    history_product_surfaces: np.ndarray     # int32 [B,S]
+    history_actions: np.ndarray              # bool  [B,S,V]
+    history_continuous_actions: np.ndarray   # f32   [B,S,8]
+    candidate_post_hashes: np.ndarray        # int32 [B,C,H]
+    candidate_auth_hashes: np.ndarray        # int32 [B,C,H]
+    candidate_product_surfaces: np.ndarray   # int32 [B,C]
+
+
+def make_prep_batch(cfg: ModelConfig, batch: int, seed: int = 2, ragged: bool = False, use_ip: bool = True) -> PrepBatch:
+    """A synthetic batch in batch-prep form: make_batch's ids hashed on the host the way the featuriser does
+    (recsys_embedding.py:282-331), user and IP ids hashed by their own families, action sets as bool [B,S,V],
+    continuous actions uniform in [0, 60) with a fifth of them negative or zero (the clip of
+    normalize_continuous_value is exercised), candidate surfaces in 1..num_surfaces.  With ragged=True request 1
+    also has no user (user_hashes 0: the prefix token is padding)."""
+    assert cfg.action_multi_hot, "batch-prep hands the actions over as sets"
+    b = make_batch(cfg, batch, seed, ragged=ragged)
+    rng = np.random.Generator(np.random.PCG64(seed + 104729))
+    lay = cfg.hash_layout()
+    S, C, V = cfg.history_len, cfg.num_candidates, cfg.num_action_types
+    uid = rng.integers(1, 1 << 40, size=(batch,), dtype=np.int64)
+    ipid = rng.integers(1, 1 << 32, size=(batch,), dtype=np.int64)
+    if ragged and batch > 1:
+        uid[1] = 0
+    cont = (rng.random((batch, S, 8), dtype=np.float32) * np.float32(60.0)).astype(np.float32)
+    cont = np.where(rng.random((batch, S, 8)) < 0.2, np.float32(-1.0) * (rng.random((batch, S, 8)) < 0.5), cont).astype(np.float32)
+    csrf = rng.integers(1, cfg.num_surfaces + 1, size=(batch, C)).astype(np.int32)
+    csrf[b.cand_post_ids == 0] = 0
+    return PrepBatch(
+        user_hashes=lay.user_hash(uid).astype(np.int32),
+        user_ip_hashes=lay.ip_hash(ipid).astype(np.int32) if use_ip else None,
+        history_post_hashes=lay.item_hash(b.hist_post_ids).astype(np.int32),
+        history_auth_hashes=lay.author_hash(b.hist_author_ids).astype(np.int32),
+        history_product_surfaces=b.hist_surfaces.astype(np.int32),
+        history_actions=(((b.hist_actions[..., None] >> np.arange(V)) & 1) != 0),
+        history_continuous_actions=cont,
+        candidate_post_hashes=lay.item_hash(b.cand_post_ids).astype(np.int32),
+        candidate_auth_hashes=lay.author_hash(b.cand_author_ids).astype(np.int32),
+        candidate_product_surfaces=csrf,
+    )
+
+
+def normalize_continuous_value(values: np.ndarray, norm_scale: float, use_log: bool) -> np.ndarray:
+    """recsys_model.py:1756-1765."""
+    v = np.clip(values.astype(np.float32), np.float32(0.0), np.float32(norm_scale))
+    if use_log:
+        return (np.log1p(v) / np.log1p(np.float32(norm_scale))).astype(np.float32)
+    return (v / np.float32(norm_scale)).astype(np.float32)
+
+
+def continuous_value_embedding(values: np.ndarray, norm_scale: float, use_log: bool, proj1: np.ndarray, proj2: np.ndarray) -> np.ndarray:
+    """project_continuous_value_to_embedding (recsys_model.py:1850-1886) up to its cast: gelu(v_norm * proj1) @ proj2
+    in fp32."""
+    vn = normalize_continuous_value(values, norm_scale, use_log)
+    hidden = gelu_tanh((vn[..., None] * proj1.reshape(-1)).astype(np.float32))
+    return (hidden @ proj2).astype(np.float32)
+
+
+def build_tokens_prep(cfg: ModelConfig, w: Dict[str, np.ndarray], table_rows_fn, pb: PrepBatch, token_round=bf16_round):
+    """The input stage from batch-prep buffers: [user token |] history tokens | candidate tokens.
+    User token (block_user_reduce, recsys_model.py:1889-1927): user rows side by side @ proj_user, cast, plus the sum of
+    the IP rows; valid when the first user hash is non-zero.  History (2163-2275): as build_tokens, then one addend per
+    continuous action, each cast to the activation type before it is added.  Candidates (2278-2365): post rows, author
+    rows and, with cand_surface, the surface row.  With token_combine == "sum" the slots of a token are summed in fp32 in
+    this order with one rounding (user rows then IP rows for the user token).  `token_round` is the cast to the
+    embedding type (bf16 in serving; the identity reproduces the reference's functions run in fp32).
+    Returns (x [B,T',D] f32, padding_mask [B,T'], candidate_start)."""
+    D, V = cfg.emb_size, cfg.num_action_types
+    hp, ha = pb.history_post_hashes, pb.history_auth_hashes
+    cp, ca = pb.candidate_post_hashes, pb.candidate_auth_hashes
+    bits = pb.history_actions.astype(np.int64)                                        # [B,S,V]
+    sel = (2 * bits - 1).astype(np.float32)[..., None] * w["action_table"].reshape(V, D // V)[None, None]
+    act = bf16_bits((sel.reshape(*bits.shape[:2], D) * (bits.any(axis=-1))[..., None]).astype(np.float32))
+    stab = bf16_bits(w["surface_table"])
+    srf = stab[np.clip(pb.history_product_surfaces, 0, cfg.num_surfaces)]
+    hist_rows = np.concatenate([table_rows_fn(hp), table_rows_fn(ha), act[:, :, None, :], srf[:, :, None, :]], axis=2)
+    cand_parts = [table_rows_fn(cp), table_rows_fn(ca)]
+    if cfg.cand_surface:
+        cand_parts.append(stab[np.clip(pb.candidate_product_surfaces, 0, cfg.num_surfaces)][:, :, None, :])
+    cand_rows = np.concatenate(cand_parts, axis=2)
+
+    def proj(rows_bits, mat):
+        cat = bf16_from_bits(rows_bits).reshape(rows_bits.shape[0], rows_bits.shape[1], -1)
+        return token_round((cat @ mat).astype(np.float32))
+
+    def slot_sum(rows_bits):   # fp32, slot order, one cast
+        rows = bf16_from_bits(rows_bits)
+        acc = np.zeros(rows.shape[:-2] + rows.shape[-1:], dtype=np.float32)
+        for j in range(rows.shape[-2]):
+            acc = acc + rows[..., j, :]
+        return token_round(acc)
+
+    project = cfg.token_combine == "project"
+    if project:
+        hist_tok, cand_tok = proj(hist_rows, w["proj_hist"]), proj(cand_rows, w["proj_cand"])
+    else:
+        hist_tok, cand_tok = slot_sum(hist_rows), slot_sum(cand_rows)
+    for i, (col, scale, use_log) in enumerate(cfg.hist_continuous):
+        emb = continuous_value_embedding(pb.history_continuous_actions[:, :, col], scale, use_log,
+                                         w[f"hist_cont{i}.proj1"], w[f"hist_cont{i}.proj2"])
+        hist_tok = token_round(hist_tok + token_round(emb))
+    parts, masks = [hist_tok, cand_tok], [hp[:, :, 0] != 0, cp[:, :, 0] != 0]
+    if cfg.user_prefix:
+        urows = table_rows_fn(pb.user_hashes)[:, None]                                # [B,1,Hu,D]
+        ip = pb.user_ip_hashes
+        if project:
+            utok = proj(urows, w["proj_user"])
+            if ip is not None:
+                utok = token_round(utok + slot_sum(table_rows_fn(ip)[:, None]))
+        else:
+            utok = slot_sum(urows if ip is None else np.concatenate([urows, table_rows_fn(ip)[:, None]], axis=2))
+        parts.insert(0, utok)
+        masks.insert(0, (pb.user_hashes[:, :1] != 0))
+    tok = np.concatenate(parts, axis=1).astype(np.float32)
+    pad = np.concatenate(masks, axis=1)
+    x = tok * np.float32(math.sqrt(cfg.emb_size))
+    return x, pad, tok.shape[1] - cand_tok.shape[1]
+
+
+def rank_forward_prep(cfg: ModelConfig, w: Dict[str, np.ndarray], table_rows_fn, pb: PrepBatch, taps: Optional[dict] = None):
+    """The ranking forward over batch-prep buffers: rank_forward with build_tokens_prep as its input stage; the user
+    token is one more attended row in front (segment 1, position 0; recsys_model.py:4720-4724, 2493-2505, 6159-6167)."""
+    rnd = _Rounder(cfg.compute)
+    x, pad, cs = build_tokens_prep(cfg, w, table_rows_fn, pb)
+    if taps is not None:
+        taps["x0"] = rnd(x)
+    seg = attention_segment_ids(pad, cs)
+    T = x.shape[1]
+    idx = np.arange(T)[None, :]
+    positions = np.where(idx >= cs, cs, idx).astype(np.float32).repeat(x.shape[0], 0)
+    hfin = transformer_trunk(cfg, w, x, seg, positions, ranker_mask(seg), taps, frozen_front=cs)
+    hfin = final_norm(cfg, w, hfin)
+    return decode_heads(cfg, w, hfin[:, cs:, :])
 
 
 def input_scale(emb_size: int) -> float:

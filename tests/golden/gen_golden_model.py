@@ -109,7 +109,7 @@ def make_jax():
     for k in ("arange", "asarray", "array", "einsum", "tile", "split", "concatenate", "mean", "square", "where", "broadcast_to",
               "logical_or", "logical_not", "float32", "int32", "ndarray", "any", "exp", "inf", "log2", "abs", "tanh",
               "reshape", "dot", "ones", "zeros", "cos", "sin", "sqrt", "maximum", "minimum", "sum", "cumsum", "full",
-              "take_along_axis", "isin", "bool_", "finfo", "power", "repeat", "expand_dims"):
+              "take_along_axis", "isin", "bool_", "finfo", "power", "repeat", "expand_dims", "clip", "log1p"):
         setattr(jnp, k, getattr(np, k))
     jnp.bfloat16 = np.float32      # parameters are supplied bf16-representable; activations run in float32 here
     lax = types.SimpleNamespace(
@@ -393,6 +393,74 @@ def main(ref: str, outdir: str):
         out[f"topk_rows_{d}"] = np.asarray(res[0][d][0], np.int64)
         out[f"topk_scores_{d}"] = np.asarray(res[0][d][1], np.float32)
     out.update(topk_scores=scores, topk_ranges=ranges, topk_caps=np.array(caps, np.int64), topk_k=np.array([k], np.int64))
+
+    # ---- input stage over batch-prep buffers: block_user_reduce / block_history_reduce / block_candidate_reduce ---------
+    RM = os.path.join(X, "models/recsys_model.py")
+    # the column of the purchase-value action is an enum value of the reference's protobuf schema, which is not a Python
+    # source; block_history_reduce only compares against it (that column gets no embedding), so any column works here
+    ns["PURCHASE_VALUE_ACTION_INDEX"] = 7
+    run(cut(RM, ["normalize_continuous_value", "project_continuous_value_to_embedding", "block_user_reduce",
+                 "block_history_reduce", "block_candidate_reduce"]))
+    prng = np.random.Generator(np.random.PCG64(97))
+    Bq, Sq, Cq, Dq, Hq, Vq, HIDq = 3, 5, 4, 32, 2, 4, 64
+    keys = types.SimpleNamespace(num_user_hashes=Hq, num_ip_hashes=Hq, num_item_hashes=Hq, num_author_hashes=Hq)
+    emb = lambda *shape: bf16(prng.standard_normal(shape, dtype=np.float32) * np.float32(0.1))
+    prep = dict(
+        prep_user_rows=emb(Bq, Hq, Dq), prep_ip_rows=emb(Bq, Hq, Dq),
+        prep_user_hashes=np.array([[5, 9], [0, 0], [3, 0]], np.int32),
+        prep_hist_post_rows=emb(Bq, Sq * Hq, Dq), prep_hist_auth_rows=emb(Bq, Sq * Hq, Dq),
+        prep_hist_surface_rows=emb(Bq, Sq, Dq),
+        prep_hist_post_hashes=prng.integers(0, 3, size=(Bq, Sq, Hq)).astype(np.int32),
+        prep_hist_cont=(prng.random((Bq, Sq, 8), dtype=np.float32) * np.float32(80.0) - np.float32(10.0)),
+        prep_cand_post_rows=emb(Bq, Cq * Hq, Dq), prep_cand_auth_rows=emb(Bq, Cq * Hq, Dq),
+        prep_cand_surface_rows=emb(Bq, Cq, Dq),
+        prep_cand_post_hashes=prng.integers(0, 3, size=(Bq, Cq, Hq)).astype(np.int32),
+        prep_proj_user=emb(Hq * Dq, Dq), prep_proj_hist=emb((2 * Hq + 2) * Dq, Dq), prep_proj_cand=emb((2 * Hq + 1) * Dq, Dq),
+    )
+    # history action rows the reference's way: the action sets through multi_hot_to_embeddings
+    run(cut(RM, ["multi_hot_to_embeddings"], methods_of="RecsysAggregatedModel"))
+    ns["DTYPE_BY_NAME"] = {"float32": np.float32}
+    prep["prep_hist_actions"] = prng.random((Bq, Sq, Vq)) < 0.4
+    prep["prep_hist_actions"][0, 1] = False                                  # an empty set: the row is zero
+    prep["prep_action_vector"] = emb(1, Dq)
+    store.stack = []
+    store.params = {"history_actions_table": prep["prep_action_vector"]}
+    mh_self = types.SimpleNamespace(config=types.SimpleNamespace(fprop_dtype="float32"))
+    act_rows, _ = ns["multi_hot_to_embeddings"](mh_self, jarr(prep["prep_hist_actions"]), Vq, Dq, 1.0, "history_actions_table")
+    prep["prep_hist_action_rows"] = np.asarray(act_rows, np.float32)
+    norm = lambda scale, use_log: types.SimpleNamespace(norm_scale=scale, use_log=use_log)
+    loss = lambda idx, wt, name, nc: types.SimpleNamespace(action_index=idx, loss_weight=wt, metric_name=name, norm_config=nc)
+    # columns 0 (log) and 3 (linear) get an embedding; column 3 is listed twice (used once), column 5 has no weight,
+    # and the purchase-value column is skipped
+    losses_in = [loss(0, 1.0, "dwell", norm(30.0, True)), loss(3, 0.5, "watch", norm(60.0, False)),
+                 loss(3, 1.0, "watch_again", norm(10.0, False)), loss(5, 0.0, "unused", norm(5.0, False)),
+                 loss(7, 1.0, "purchase", norm(5.0, False))]
+    store.stack = []
+    store.params = {"proj_mat_1": prep["prep_proj_user"], "proj_mat_3": prep["prep_proj_hist"], "proj_mat_2": prep["prep_proj_cand"]}
+    for nm in ("dwell", "watch"):
+        prep[f"prep_{nm}_proj1"] = emb(1, HIDq) * np.float32(10.0)
+        prep[f"prep_{nm}_proj2"] = emb(HIDq, Dq)
+        store.params[f"{nm}_proj_proj1"], store.params[f"{nm}_proj_proj2"] = prep[f"prep_{nm}_proj1"], prep[f"prep_{nm}_proj2"]
+    lrm = lambda n: 1.0
+    u_tok, u_mask = ns["block_user_reduce"](jarr(prep["prep_user_hashes"]), jarr(prep["prep_user_rows"]), keys, lrm, 1.0,
+                                            user_ip_embeddings=jarr(prep["prep_ip_rows"]), use_ip_address=True)
+    u_tok_noip, _ = ns["block_user_reduce"](jarr(prep["prep_user_hashes"]), jarr(prep["prep_user_rows"]), keys, lrm, 1.0)
+    h_tok, h_mask = ns["block_history_reduce"](
+        jarr(prep["prep_hist_post_hashes"]), None, jarr(prep["prep_hist_post_rows"]), jarr(prep["prep_hist_auth_rows"]),
+        jarr(prep["prep_hist_surface_rows"]), jarr(prep["prep_hist_action_rows"]), keys, lrm, 1.0, True,
+        history_continuous_actions=jarr(prep["prep_hist_cont"]), fprop_dtype=np.float32, continuous_action_losses=losses_in,
+        continuous_action_hidden_dim=HIDq)
+    c_tok, c_mask = ns["block_candidate_reduce"](
+        jarr(prep["prep_cand_post_hashes"]), None, jarr(prep["prep_cand_post_rows"]), jarr(prep["prep_cand_auth_rows"]),
+        jarr(prep["prep_cand_surface_rows"]), keys, lrm, 1.0, use_product_surface=True, fprop_dtype=np.float32)
+    vals = np.array([-3.0, 0.0, 0.5, 7.0, 29.0, 30.0, 31.0, 1e6], np.float32)
+    prep.update(
+        prep_user_tok=np.asarray(u_tok, np.float32), prep_user_tok_noip=np.asarray(u_tok_noip, np.float32),
+        prep_user_mask=np.asarray(u_mask, bool), prep_hist_tok=np.asarray(h_tok, np.float32), prep_hist_mask=np.asarray(h_mask, bool),
+        prep_cand_tok=np.asarray(c_tok, np.float32), prep_cand_mask=np.asarray(c_mask, bool), prep_norm_in=vals,
+        prep_norm_log=np.asarray(ns["normalize_continuous_value"](jarr(vals), norm(30.0, True)), np.float32),
+        prep_norm_lin=np.asarray(ns["normalize_continuous_value"](jarr(vals), norm(30.0, False)), np.float32))
+    out.update(prep)
 
     np.savez_compressed(os.path.join(outdir, "model_golden.npz"), **out)
     print("wrote", os.path.join(outdir, "model_golden.npz"), len(out), "arrays")

@@ -12,7 +12,7 @@ def make_pair(max_batch=4, table_seed=7, engine_kw=None, **kw):
 
     engine_kw = engine_kw or {}     # options of the engine alone (no counterpart in the oracle's model)
     ocfg = po.ModelConfig(**kw)
-    w = po.make_weights(ocfg, 0)
+    w = po.make_prep_weights(ocfg, 0)   # make_weights plus the parameters of the batch-prep extras, when configured
     amp = 1.0 / math.sqrt(ocfg.emb_size)
     rows_fn = lambda idx: po.synthetic_table_rows(idx, ocfg.emb_size, table_seed, amp)
     pcfg = px.PhoenixConfig(
@@ -24,7 +24,9 @@ def make_pair(max_batch=4, table_seed=7, engine_kw=None, **kw):
         rotary=ocfg.rotary, qk_norm=ocfg.qk_norm, primer_norm=ocfg.primer_norm, attn_logit_cap=ocfg.attn_logit_cap,
         attn_logit_cap_method=ocfg.attn_logit_cap_method, final_logit_cap=ocfg.final_logit_cap,
         rms_eps=ocfg.rms_eps, rope_base=float(ocfg.rope_base), dwell_norm_scale=ocfg.dwell_norm_scale,
-        num_candidate_only_layers=ocfg.num_candidate_only_layers, compute=ocfg.compute, token_combine=ocfg.token_combine, action_multi_hot=ocfg.action_multi_hot, **engine_kw)
+        num_candidate_only_layers=ocfg.num_candidate_only_layers, compute=ocfg.compute, token_combine=ocfg.token_combine, action_multi_hot=ocfg.action_multi_hot,
+        user_prefix=ocfg.user_prefix, cand_surface=ocfg.cand_surface, hist_continuous=ocfg.hist_continuous,
+        hist_cont_hidden=ocfg.hist_cont_hidden, **engine_kw)
     eng = px.PhoenixEngine(pcfg, 0)
     eng.load_weights(w)
     eng.table_fill_synthetic(table_seed, amp)

@@ -31,12 +31,13 @@ def test_library_exports_every_declared_symbol():
 def test_struct_layouts_match_header():
     from x_algorithm_b200 import _lib
     assert C.sizeof(_lib.HashFamily) == 8 * 4 + 8 * 4 + 8 + 8 + 4 + 4
-    assert C.sizeof(_lib.ModelConfig) == 17 * 4 + 5 * 4 + 4 * C.sizeof(_lib.HashFamily) + 8 * 4
+    assert C.sizeof(_lib.ModelConfig) == 17 * 4 + 5 * 4 + 4 * C.sizeof(_lib.HashFamily) + (8 + 3 + 3 * 4 + 1) * 4
+    assert C.sizeof(_lib.RankBatchPrep) == 8 + 10 * 8
     assert C.sizeof(_lib.BlendSpec) == 8 + 32 * 4 + 32 * 8 + 16 - 4 + 4   # int + pad, src, weight, two doubles
     assert C.sizeof(_lib.RankBatch) == 8 + 6 * 8 and C.sizeof(_lib.RankOut) == 24
     # phx_value_model: 32 int sources, 30 + 9 doubles, 6 ints; phx_value_inputs: 4 ints + 9 pointers
     assert C.sizeof(_lib.ValueModel) == 32 * 4 + 39 * 8 + 6 * 4 and C.sizeof(_lib.ValueInputs) == 4 * 4 + 9 * 8
-    assert _lib.ModelConfig.pack_ragged.offset == C.sizeof(_lib.ModelConfig) - 12
+    assert _lib.ModelConfig.pack_ragged.offset == C.sizeof(_lib.ModelConfig) - (3 + 3 + 3 * 4 + 1) * 4
 
 
 def test_config_options_reach_the_c_struct():
@@ -50,6 +51,12 @@ def test_config_options_reach_the_c_struct():
         px.PhoenixConfig(compute="fp16").to_c()
     with pytest.raises(ValueError):
         px.PhoenixConfig(token_combine="mean").to_c()
+    p = px.PhoenixConfig(user_prefix=True, cand_surface=True, hist_continuous=((0, 30.0, True), (3, 60.0, False)), hist_cont_hidden=32).to_c()
+    assert (p.user_prefix, p.cand_surface, p.num_hist_continuous, p.hist_cont_hidden) == (1, 1, 2, 32)
+    assert list(p.hist_cont_index)[:2] == [0, 3] and list(p.hist_cont_use_log)[:2] == [1, 0] and list(p.hist_cont_norm_scale)[:2] == [30.0, 60.0]
+    assert (d.user_prefix, d.cand_surface, d.num_hist_continuous) == (0, 0, 0)
+    with pytest.raises(ValueError):
+        px.PhoenixConfig(hist_continuous=((0, 1.0, False),) * 5).to_c()
 
 
 def test_value_model_struct_mirrors_the_weights():

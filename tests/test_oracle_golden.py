@@ -500,3 +500,44 @@ def test_sharded_window_topk_and_merge_equal_the_reference_function():
         assert (valid.sum(axis=1) == n).all() and n == ms.shape[1] or n < ms.shape[1]
         np.testing.assert_array_equal(mi[:, :n], g[f"topk_rows_{d}"][:, :n])
         np.testing.assert_array_equal(ms[:, :n], g[f"topk_scores_{d}"][:, :n])
+
+
+def test_input_stage_over_batch_prep_buffers_equals_the_reference_blocks():
+    """build_tokens_prep with the cast switched off against block_user_reduce, block_history_reduce (action sets through
+    multi_hot_to_embeddings, two continuous actions, one listed twice, one without weight, the purchase column) and
+    block_candidate_reduce with the surface row, all executed from the reference's source in fp32."""
+    g = _model_golden()
+    B, S, H = g["prep_hist_post_hashes"].shape
+    C = g["prep_cand_post_hashes"].shape[1]
+    D, V = g["prep_action_vector"].shape[1], g["prep_hist_actions"].shape[2]
+    cfg = po.ModelConfig(emb_size=D, history_len=S, num_candidates=C, num_hashes=H, num_action_types=V, num_surfaces=B * (S + C),
+                         action_multi_hot=True, token_combine="project", user_prefix=True, cand_surface=True,
+                         hist_continuous=((0, 30.0, True), (3, 60.0, False)), hist_cont_hidden=g["prep_dwell_proj1"].shape[1])
+    surface_table = np.concatenate([np.zeros((1, D), np.float32), g["prep_hist_surface_rows"].reshape(-1, D),
+                                    g["prep_cand_surface_rows"].reshape(-1, D)])
+    w = {"action_table": g["prep_action_vector"], "surface_table": surface_table, "proj_user": g["prep_proj_user"],
+         "proj_hist": g["prep_proj_hist"], "proj_cand": g["prep_proj_cand"],
+         "hist_cont0.proj1": g["prep_dwell_proj1"], "hist_cont0.proj2": g["prep_dwell_proj2"],
+         "hist_cont1.proj1": g["prep_watch_proj1"], "hist_cont1.proj2": g["prep_watch_proj2"]}
+    auth_h, auth_c, ip_h = np.ones((B, S, H), np.int32), np.ones((B, C, H), np.int32), np.ones((B, H), np.int32)
+    pb = po.PrepBatch(
+        user_hashes=g["prep_user_hashes"].copy(), user_ip_hashes=ip_h, history_post_hashes=g["prep_hist_post_hashes"].copy(),
+        history_auth_hashes=auth_h, history_product_surfaces=(1 + np.arange(B * S, dtype=np.int32)).reshape(B, S),
+        history_actions=g["prep_hist_actions"], history_continuous_actions=g["prep_hist_cont"],
+        candidate_post_hashes=g["prep_cand_post_hashes"].copy(), candidate_auth_hashes=auth_c,
+        candidate_product_surfaces=(1 + B * S + np.arange(B * C, dtype=np.int32)).reshape(B, C))
+    # the fixture holds gathered rows, not a table: hand each hash array the rows the reference function was given
+    rows = {id(pb.user_hashes): g["prep_user_rows"], id(ip_h): g["prep_ip_rows"],
+            id(pb.history_post_hashes): g["prep_hist_post_rows"].reshape(B, S, H, D), id(auth_h): g["prep_hist_auth_rows"].reshape(B, S, H, D),
+            id(pb.candidate_post_hashes): g["prep_cand_post_rows"].reshape(B, C, H, D), id(auth_c): g["prep_cand_auth_rows"].reshape(B, C, H, D)}
+    x, pad, cs = po.build_tokens_prep(cfg, w, lambda idx: po.bf16_bits(rows[id(idx)]), pb, token_round=lambda v: v)
+    tok = x / np.float32(math.sqrt(D))
+    assert cs == S + 1
+    ref = np.concatenate([g["prep_user_tok"], g["prep_hist_tok"], g["prep_cand_tok"]], axis=1)
+    assert rel_l2(tok, ref) < 2e-6
+    assert np.array_equal(pad, np.concatenate([g["prep_user_mask"], g["prep_hist_mask"], g["prep_cand_mask"]], axis=1))
+    pb.user_ip_hashes = None
+    x, _, _ = po.build_tokens_prep(cfg, w, lambda idx: po.bf16_bits(rows[id(idx)]), pb, token_round=lambda v: v)
+    assert rel_l2(x[:, :1] / np.float32(math.sqrt(D)), g["prep_user_tok_noip"]) < 2e-6
+    for use_log, key in ((True, "prep_norm_log"), (False, "prep_norm_lin")):
+        np.testing.assert_allclose(po.normalize_continuous_value(g["prep_norm_in"], 30.0, use_log), g[key], rtol=1e-6, atol=1e-7)

@@ -11,6 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libphoenix_b200.so")
 
 PHX_MAX_HASHES = 4
+PHX_MAX_HIST_CONT = 4
 PHX_MAX_BLEND_TERMS = 32
 STATUS_NAMES = {0: "PHX_OK", 1: "PHX_E_ARG", 2: "PHX_E_CUDA", 3: "PHX_E_NCCL", 4: "PHX_E_TIMEOUT",
                 5: "PHX_E_CAPACITY", 6: "PHX_E_STATE"}
@@ -29,7 +30,10 @@ class ModelConfig(C.Structure):
         "attn_logit_cap", "final_logit_cap", "rms_eps", "rope_base", "dwell_norm_scale")] + [
         ("user", HashFamily), ("item", HashFamily), ("author", HashFamily), ("ip", HashFamily),
         ("table_world", C.c_int32), ("table_rank", C.c_int32), ("num_candidate_only_layers", C.c_int32),
-        ("compute_fp32", C.c_int32), ("token_project", C.c_int32), ("pack_ragged", C.c_int32), ("action_multi_hot", C.c_int32), ("_pad2", C.c_int32)]
+        ("compute_fp32", C.c_int32), ("token_project", C.c_int32), ("pack_ragged", C.c_int32), ("action_multi_hot", C.c_int32), ("user_prefix", C.c_int32),
+        ("cand_surface", C.c_int32), ("num_hist_continuous", C.c_int32), ("hist_cont_hidden", C.c_int32),
+        ("hist_cont_index", C.c_int32 * PHX_MAX_HIST_CONT), ("hist_cont_use_log", C.c_int32 * PHX_MAX_HIST_CONT),
+        ("hist_cont_norm_scale", C.c_float * PHX_MAX_HIST_CONT), ("_pad3", C.c_int32)]
 
 
 class BlendSpec(C.Structure):
@@ -41,6 +45,13 @@ class RankBatch(C.Structure):
     _fields_ = [("batch", C.c_int32), ("_pad", C.c_int32), ("hist_post_ids", C.c_void_p),
                 ("hist_author_ids", C.c_void_p), ("hist_actions", C.c_void_p), ("hist_surfaces", C.c_void_p),
                 ("cand_post_ids", C.c_void_p), ("cand_author_ids", C.c_void_p)]
+
+
+class RankBatchPrep(C.Structure):   # phx_rank_batch_prep: the reference's batch-prep buffers under its names
+    _fields_ = [("batch", C.c_int32), ("_pad", C.c_int32)] + [(n, C.c_void_p) for n in (
+        "user_hashes", "user_ip_hashes", "history_post_hashes", "history_auth_hashes", "history_product_surfaces",
+        "history_actions", "history_continuous_actions", "candidate_post_hashes", "candidate_auth_hashes",
+        "candidate_product_surfaces")]
 
 
 # phx_rank_batch_hashed: the same layout with int32 [.., H] row arrays in place of the int64 id arrays
@@ -112,6 +123,8 @@ SIGNATURES = {
     "phx_rank_forward_packed_device": (C.c_int32, [_P, C.POINTER(RankBatch), _P, _P, C.c_int64, C.c_int64, C.POINTER(RankOut)]),
     "phx_rank_forward_hashed_device": (C.c_int32, [_P, C.POINTER(RankBatchHashed), C.POINTER(RankOut)]),
     "phx_rank_forward_hashed": (C.c_int32, [_P, C.POINTER(RankBatchHashed), C.POINTER(RankOut)]),
+    "phx_rank_forward_prep_device": (C.c_int32, [_P, C.POINTER(RankBatchPrep), C.POINTER(RankOut)]),
+    "phx_rank_forward_prep": (C.c_int32, [_P, C.POINTER(RankBatchPrep), C.POINTER(RankOut)]),
     "phx_rank_prefetch_device": (C.c_int32, [_P, C.POINTER(RankBatch)]),
     "phx_sync": (C.c_int32, [_P]),
     "phx_set_wait_limit_us": (C.c_int32, [_P, C.c_uint32]),

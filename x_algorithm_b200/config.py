@@ -82,6 +82,11 @@ class PhoenixConfig:
                                 # recsys_model.py:2163-2365)
 
     action_multi_hot: bool = False   # hist_actions are bit sets, action_table one [1, D] vector (recsys_model.py:3259-3314)
+    # the reference's batch-prep buffers beyond posts and authors, served by Engine.rank_prep (python.rs:1394-1404)
+    user_prefix: bool = False        # one user token in front of the history (block_user_reduce, recsys_model.py:1889-1927)
+    cand_surface: bool = False       # candidate tokens take a product-surface row (block_candidate_reduce, 2278-2365)
+    hist_continuous: tuple = ()      # ((column, norm_scale, use_log), ...): continuous history actions (2249-2271)
+    hist_cont_hidden: int = 64
     pack_ragged: bool = False   # run ragged host-buffer batches over their valid rows only (sequence_packing.py:317)
 
     @property
@@ -126,4 +131,10 @@ class PhoenixConfig:
         c.token_project = 1 if self.token_combine == "project" else 0
         c.pack_ragged = int(bool(self.pack_ragged))
         c.action_multi_hot = int(bool(self.action_multi_hot))
+        c.user_prefix, c.cand_surface = int(bool(self.user_prefix)), int(bool(self.cand_surface))
+        if len(self.hist_continuous) > _lib.PHX_MAX_HIST_CONT:
+            raise ValueError(f"at most {_lib.PHX_MAX_HIST_CONT} continuous history actions")
+        c.num_hist_continuous, c.hist_cont_hidden = len(self.hist_continuous), int(self.hist_cont_hidden)
+        for i, (col, scale, use_log) in enumerate(self.hist_continuous):
+            c.hist_cont_index[i], c.hist_cont_norm_scale[i], c.hist_cont_use_log[i] = int(col), float(scale), int(bool(use_log))
         return c

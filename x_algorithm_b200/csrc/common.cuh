@@ -232,11 +232,28 @@ struct TokenBuildArgs {
   float* x32 = nullptr;   // full-precision path: bf16(sum) * input_scale kept in fp32 here (x is then not written)
   const bf16* landing = nullptr;
   const int* pos = nullptr;
+  // ---- batch-prep buffers beyond posts and authors (pre-hashed input only) ----
+  // P user-prefix tokens (0 or 1) in front of every request's history: S counts them, the history input arrays hold
+  // S - P slots.  User token = rows user_hashes [B,Hu] (side by side in concat_user [B, Hu*D], or summed) plus the sum of
+  // the rows user_ip_hashes [B,Hip] (NULL: none); valid when user_hashes[b,0] != 0.
+  int P = 0, Hu = 0, Hip = 0;
+  const int* user_hashes = nullptr; const int* user_ip_hashes = nullptr;
+  bf16* concat_user = nullptr;
+  const unsigned char* hist_actions_bool = nullptr;   // bool [B,S-P,num_action_types] in place of hist_actions
+  const int* cand_surfaces = nullptr;                 // [B,C]: one more candidate slot, a row of surface_table
+  // continuous history actions: token += bf16(gelu(norm(v) * w1) @ w2) per configured column of hist_cont [B,S-P,8]
+  const float* hist_cont = nullptr;
+  int n_cont = 0, cont_hidden = 0;
+  int cont_index[PHX_MAX_HIST_CONT] = {0, 0, 0, 0};
+  int cont_log[PHX_MAX_HIST_CONT] = {0, 0, 0, 0};
+  float cont_scale[PHX_MAX_HIST_CONT] = {1.f, 1.f, 1.f, 1.f};
+  const bf16* cont_w1[PHX_MAX_HIST_CONT] = {nullptr, nullptr, nullptr, nullptr};   // [hidden]
+  const bf16* cont_w2[PHX_MAX_HIST_CONT] = {nullptr, nullptr, nullptr, nullptr};   // [hidden, D]
 };
 phx_status pack_plan_launch(const PackMap& pk, int B, int S, int C, int* pos_rows, int* out_index, cudaStream_t stream,
                             std::string& err);
-phx_status finish_tokens_launch(const bf16* tok_hist, const bf16* tok_cand, const TokenBuildArgs& a, cudaStream_t stream,
-                                std::string& err);
+phx_status finish_tokens_launch(const bf16* tok_user, const bf16* tok_hist, const bf16* tok_cand, const TokenBuildArgs& a,
+                                cudaStream_t stream, std::string& err);
 phx_status build_tokens_launch(const TokenBuildArgs& a, cudaStream_t stream, std::string& err);
 phx_status hash_ids_launch(const HashFamilyDev& fam, const long long* ids, long long n, int* out, cudaStream_t stream,
                            std::string& err);

@@ -59,29 +59,68 @@ __device__ __forceinline__ void acc_chunk(float (&acc)[8], uint4 u) {
 // GENERAL = false is the benchmark's path with the optional inputs and outputs compiled out (packed rows, pre-hashed
 // rows, landing buffer, projected tokens, action sets, fp32 rows, debug taps, rows-only): same arithmetic, fewer
 // instructions in a kernel that is bound by how many loads it keeps in flight.
+// Continuous history actions (project_continuous_value_to_embedding, recsys_model.py:1850-1886).  Hidden activations
+// of every configured column for one token, gelu(norm(v) * w1), into hid[c][0..hidden): the warp's scratch.
+__device__ __forceinline__ void cont_hidden(const TokenBuildArgs& a, const float* __restrict__ vals, int lane, float (*hid)[64]) {
+  for (int c = 0; c < a.n_cont; ++c) {
+    float v = __ldg(vals + a.cont_index[c]);
+    v = fminf(fmaxf(v, 0.f), a.cont_scale[c]);                                        // normalize_continuous_value, 1756-1765
+    v = a.cont_log[c] ? log1pf(v) / log1pf(a.cont_scale[c]) : v / a.cont_scale[c];
+    for (int j = lane; j < a.cont_hidden; j += 32) hid[c][j] = gelu_tanh_f(v * __bfloat162float(a.cont_w1[c][j]));
+  }
+  __syncwarp();
+}
+// tv[0..8) (columns col..col+7 of the token, bf16-valued) += bf16(hid[c] @ w2[c]) for every configured column, one
+// rounding per addend.
+__device__ __forceinline__ void cont_add(const TokenBuildArgs& a, const float (*hid)[64], int col, float (&tv)[8]) {
+  for (int c = 0; c < a.n_cont; ++c) {
+    float e[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < a.cont_hidden; ++j) {
+      const float h = hid[c][j];
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(a.cont_w2[c] + (long long)j * a.D + col));
+      const float2 p0 = unpack_bf2(u.x), p1 = unpack_bf2(u.y), p2 = unpack_bf2(u.z), p3 = unpack_bf2(u.w);
+      e[0] = fmaf(h, p0.x, e[0]); e[1] = fmaf(h, p0.y, e[1]); e[2] = fmaf(h, p1.x, e[2]); e[3] = fmaf(h, p1.y, e[3]);
+      e[4] = fmaf(h, p2.x, e[4]); e[5] = fmaf(h, p2.y, e[5]); e[6] = fmaf(h, p3.x, e[6]); e[7] = fmaf(h, p3.y, e[7]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tv[i] = round_bf(tv[i] + round_bf(e[i]));
+  }
+}
+
 template <bool GENERAL>
-__global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
+__global__ void __launch_bounds__(256, GENERAL ? 3 : 5) build_tokens_kernel(TokenBuildArgs a) {
   // (no early launch signal here: the GEMM behind this kernel would park its CTAs - registers and all - on the SMs
   // while this bandwidth-bound kernel still needs every warp slot it can get)
+  __shared__ float hid_s[GENERAL ? 8 : 1][PHX_MAX_HIST_CONT][64];
   const int T = a.S + a.C;
   const long long tok = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (tok >= (long long)a.B * T) return;
   const int b = (int)(tok / T), t = (int)(tok % T);
-  const bool is_hist = t < a.S;
+  const int P = GENERAL ? a.P : 0;
+  const bool is_front = t < a.S;              // rows in front of the candidates: user prefix + history
+  const bool is_user = GENERAL && t < P;
+  const bool is_hist = is_front && !is_user;
+  const int Sh = a.S - P;                     // history slots of the input arrays
   const int H = a.item.num_hashes;
-  const long long slot = is_hist ? (long long)b * a.S + t : (long long)b * a.C + (t - a.S);
+  const long long slot = is_user ? (long long)b : is_hist ? (long long)b * Sh + (t - P) : (long long)b * a.C + (t - a.S);
   long long orow;   // where this token's row goes
   if (GENERAL && a.pack.on() && !a.rows_only) {
     // packed rows: slots past the request's counts are not built at all (one token per warp: the whole warp leaves)
-    if (is_hist ? t >= a.pack.hist_cnt(b) : (t - a.S) >= a.pack.cand_cnt(b)) return;
-    orow = is_hist ? (long long)a.pack.hist_off[b] + t : a.pack.cand_base + a.pack.cand_off[b] + (t - a.S);
+    if (is_front ? t >= a.pack.hist_cnt(b) : (t - a.S) >= a.pack.cand_cnt(b)) return;
+    orow = is_front ? (long long)a.pack.hist_off[b] + t : a.pack.cand_base + a.pack.cand_off[b] + (t - a.S);
   } else {
     orow = token_row(a.split, a.B, a.S, T, b, t);
   }
-  // lanes 0..H-1 hold the post rows, lanes H..2H-1 the author rows: hashed here, or taken as given
+  // lanes 0..H-1 hold the post rows, lanes H..2H-1 the author rows: hashed here, or taken as given; the user token
+  // holds its user rows in lanes 0..Hu-1 and its IP rows behind them
+  const int n_ip = (GENERAL && a.user_ip_hashes) ? a.Hip : 0;
+  const int nrow = is_user ? a.Hu + n_ip : 2 * H;
   int my_idx = 0;
-  if (GENERAL && a.pre_hist_post) {
+  if (is_user) {
+    if (lane < a.Hu) my_idx = a.user_hashes[(long long)b * a.Hu + lane];
+    else if (lane < nrow) my_idx = a.user_ip_hashes[(long long)b * a.Hip + (lane - a.Hu)];
+  } else if (GENERAL && a.pre_hist_post) {
     if (lane < H) my_idx = (is_hist ? a.pre_hist_post : a.pre_cand_post)[slot * H + lane];
     else if (lane < 2 * H) my_idx = (is_hist ? a.pre_hist_author : a.pre_cand_author)[slot * H + (lane - H)];
   } else {
@@ -95,15 +134,26 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
   }
   if (GENERAL && a.hashes && lane < 2 * H) a.hashes[tok * (2 * H) + lane] = my_idx;
   if (GENERAL && a.rows_only) return;   // uniform over the grid: the caller only wants the rows (exchange outside the kernel)
-  const int first_post_hash = __shfl_sync(0xffffffffu, my_idx, 0);
-  if (lane == 0) a.seg[orow] = (first_post_hash != 0) ? (is_hist ? 1 : -1) : 0;
+  const int first_hash = __shfl_sync(0xffffffffu, my_idx, 0);
+  if (lane == 0) a.seg[orow] = (first_hash != 0) ? (is_front ? 1 : -1) : 0;
   int act = 0, srf = 0;
   if (is_hist) {
-    act = a.hist_actions[(long long)b * a.S + t];
-    srf = a.hist_surfaces[(long long)b * a.S + t];
+    if (GENERAL && a.hist_actions_bool) {   // the action set as the batch-prep hands it over: one byte per flag
+      const unsigned char* f = a.hist_actions_bool + slot * a.num_action_types;
+      act = (int)__ballot_sync(0xffffffffu, lane < a.num_action_types && f[lane] != 0);
+    } else {
+      act = a.hist_actions[slot];
+    }
+    srf = a.hist_surfaces[slot];
     if (!(GENERAL && a.action_multi_hot)) act = act < 0 ? 0 : (act > a.num_action_types ? a.num_action_types : act);
-    srf = srf < 0 ? 0 : (srf > a.num_surfaces ? a.num_surfaces : srf);
+  } else if (GENERAL && !is_front && a.cand_surfaces) {
+    srf = a.cand_surfaces[slot];
   }
+  srf = srf < 0 ? 0 : (srf > a.num_surfaces ? a.num_surfaces : srf);
+  const bool has_srf = is_hist || (GENERAL && !is_front && a.cand_surfaces);
+  const bool has_cont = GENERAL && is_hist && a.n_cont > 0;
+  float (*hid)[64] = hid_s[GENERAL ? (threadIdx.x >> 5) : 0];
+  if (has_cont && !a.concat_hist) cont_hidden(a, a.hist_cont + slot * PHX_PREP_CONTINUOUS, lane, hid);
   // every lane takes part in these shuffles (lanes whose column chunk lies past D skip the loop below, so a
   // shuffle inside the loop would leave the warp split across two different shuffle instructions)
   const bf16* rowp[2 * PHX_MAX_HASHES];
@@ -111,26 +161,28 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
   if (GENERAL && a.landing && lane < 2 * H) my_pos = a.pos[tok * (2 * H) + lane];
 #pragma unroll
   for (int j = 0; j < 2 * PHX_MAX_HASHES; ++j) {
-    const int jj = j < 2 * H ? j : 0;
+    const int jj = j < nrow ? j : 0;
     const int idx = __shfl_sync(0xffffffffu, my_idx, jj);
     const int ps = __shfl_sync(0xffffffffu, my_pos, jj);
     rowp[j] = (GENERAL && a.landing) ? a.landing + (long long)ps * a.D : a.table.row_ptr(idx, a.D);
   }
   if (GENERAL && a.concat_hist) {
-    // projected tokens: the gathered rows side by side - post rows, author rows, then (history) action and surface
-    // rows - as one GEMM operand row (recsys_model.py:2190-2207, 2307-2316); the projection, the scaling and the row
-    // statistics follow in their own launches
-    const int nslot = 2 * H + (is_hist ? 2 : 0);
-    bf16* dst = is_hist ? a.concat_hist + slot * (long long)nslot * a.D : a.concat_cand + slot * (long long)nslot * a.D;
+    // projected tokens: the gathered rows side by side - post rows, author rows, then the action and surface rows
+    // (history) or the surface row (candidates that carry one); the user rows alone for the user token - as one GEMM
+    // operand row (recsys_model.py:1903-1918, 2190-2221, 2307-2329); the projection, the addends, the scaling and
+    // the row statistics follow in their own launches
+    const int ngat = is_user ? a.Hu : 2 * H;
+    const int nslot = ngat + (is_hist ? 2 : has_srf ? 1 : 0);
+    bf16* dst = (is_user ? a.concat_user : is_hist ? a.concat_hist : a.concat_cand) + slot * (long long)nslot * a.D;
     for (int col = lane * 8; col < a.D; col += 256) {
 #pragma unroll
       for (int j = 0; j < 2 * PHX_MAX_HASHES; ++j)
-        if (j < 2 * H) *reinterpret_cast<uint4*>(dst + (long long)j * a.D + col) = __ldg(reinterpret_cast<const uint4*>(rowp[j] + col));
-      if (is_hist) {
-        *reinterpret_cast<uint4*>(dst + (long long)(2 * H) * a.D + col) = action_chunk(a, act, col, GENERAL && a.action_multi_hot);
-        *reinterpret_cast<uint4*>(dst + (long long)(2 * H + 1) * a.D + col) =
+        if (j < ngat) *reinterpret_cast<uint4*>(dst + (long long)j * a.D + col) = __ldg(reinterpret_cast<const uint4*>(rowp[j] + col));
+      if (is_hist)
+        *reinterpret_cast<uint4*>(dst + (long long)ngat * a.D + col) = action_chunk(a, act, col, GENERAL && a.action_multi_hot);
+      if (has_srf)
+        *reinterpret_cast<uint4*>(dst + (long long)(nslot - 1) * a.D + col) =
             __ldg(reinterpret_cast<const uint4*>(a.surface_table + (long long)srf * a.D + col));
-      }
     }
     return;
   }
@@ -139,25 +191,27 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int j = 0; j < 2 * PHX_MAX_HASHES; ++j)
-      if (j < 2 * H) acc_row(acc, rowp[j], col);
-    if (is_hist) {
-      acc_chunk(acc, action_chunk(a, act, col, GENERAL && a.action_multi_hot));
-      acc_row(acc, a.surface_table + (long long)srf * a.D, col);
-    }
+      if (j < nrow) acc_row(acc, rowp[j], col);
+    if (is_hist) acc_chunk(acc, action_chunk(a, act, col, GENERAL && a.action_multi_hot));
+    if (has_srf) acc_row(acc, a.surface_table + (long long)srf * a.D, col);
+    float tv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tv[i] = round_bf(acc[i]);
+    if (has_cont) cont_add(a, hid, col, tv);
     uint4 o;
     if (GENERAL && a.tokens) {
-      o.x = pack_bf2(acc[0], acc[1]); o.y = pack_bf2(acc[2], acc[3]); o.z = pack_bf2(acc[4], acc[5]); o.w = pack_bf2(acc[6], acc[7]);
+      o.x = pack_bf2(tv[0], tv[1]); o.y = pack_bf2(tv[2], tv[3]); o.z = pack_bf2(tv[4], tv[5]); o.w = pack_bf2(tv[6], tv[7]);
       *reinterpret_cast<uint4*>(a.tokens + tok * a.D + col) = o;
     }
     if (GENERAL && a.x32) {   // full-precision path: the token is the bf16 sum, its scaled value stays fp32
       float* dst = a.x32 + orow * a.D + col;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) dst[i] = round_bf(acc[i]) * a.input_scale;
+      for (int i = 0; i < 8; ++i) dst[i] = tv[i] * a.input_scale;
       continue;
     }
     float s[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { s[i] = round_bf(round_bf(acc[i]) * a.input_scale); row_ss += s[i] * s[i]; }
+    for (int i = 0; i < 8; ++i) { s[i] = round_bf(tv[i] * a.input_scale); row_ss += s[i] * s[i]; }
     o.x = pack_bf2(s[0], s[1]); o.y = pack_bf2(s[2], s[3]); o.z = pack_bf2(s[4], s[5]); o.w = pack_bf2(s[6], s[7]);
     *reinterpret_cast<uint4*>(a.x + orow * a.D + col) = o;
   }
@@ -169,16 +223,22 @@ __global__ void __launch_bounds__(256) build_tokens_kernel(TokenBuildArgs a) {
 }
 
 // Projected tokens, last step: x = bf16(token * input_scale) at the token's row of the residual stream (plain or
-// split layout) with the row statistics of the first fused RMSNorm; tok_hist [B*S, D] and tok_cand [B*C, D] are the
-// outputs of the two projection GEMMs.  One warp per token.
-__global__ void __launch_bounds__(256) finish_tokens_kernel(const bf16* __restrict__ tok_hist, const bf16* __restrict__ tok_cand,
-                                                            TokenBuildArgs a) {
+// split layout) with the row statistics of the first fused RMSNorm; tok_user [B, D], tok_hist [B*(S-P), D] and
+// tok_cand [B*C, D] are the outputs of the projection GEMMs.  The addends of the reference's blocks that follow their
+// projection are applied here: the sum of the IP rows on the user token (recsys_model.py:1920-1923) and the
+// continuous-action embeddings on the history tokens (2249-2271).  One warp per token.
+__global__ void __launch_bounds__(256) finish_tokens_kernel(const bf16* __restrict__ tok_user, const bf16* __restrict__ tok_hist,
+                                                            const bf16* __restrict__ tok_cand, TokenBuildArgs a) {
+  __shared__ float hid_s[8][PHX_MAX_HIST_CONT][64];
   const int T = a.S + a.C;
   const long long tok = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (tok >= (long long)a.B * T) return;
   const int b = (int)(tok / T), t = (int)(tok % T);
-  const bf16* src = t < a.S ? tok_hist + ((long long)b * a.S + t) * a.D : tok_cand + ((long long)b * a.C + (t - a.S)) * a.D;
+  const int Sh = a.S - a.P;
+  const bool is_user = t < a.P, is_hist = !is_user && t < a.S;
+  const bf16* src = is_user ? tok_user + (long long)b * a.D
+                  : is_hist ? tok_hist + ((long long)b * Sh + (t - a.P)) * a.D : tok_cand + ((long long)b * a.C + (t - a.S)) * a.D;
   long long orow;
   if (a.pack.on()) {
     if (t < a.S ? t >= a.pack.hist_cnt(b) : (t - a.S) >= a.pack.cand_cnt(b)) return;
@@ -186,12 +246,24 @@ __global__ void __launch_bounds__(256) finish_tokens_kernel(const bf16* __restri
   } else {
     orow = token_row(a.split, a.B, a.S, T, b, t);
   }
+  const bool has_cont = is_hist && a.n_cont > 0;
+  const int n_ip = (is_user && a.user_ip_hashes) ? a.Hip : 0;
+  float (*hid)[64] = hid_s[threadIdx.x >> 5];
+  if (has_cont) cont_hidden(a, a.hist_cont + ((long long)b * Sh + (t - a.P)) * PHX_PREP_CONTINUOUS, lane, hid);
   float row_ss = 0.f;
   for (int col = lane * 8; col < a.D; col += 256) {
-    const uint4 u = *reinterpret_cast<const uint4*>(src + col);
-    if (a.tokens) *reinterpret_cast<uint4*>(a.tokens + tok * a.D + col) = u;
+    uint4 u = *reinterpret_cast<const uint4*>(src + col);
     const float2 p0 = unpack_bf2(u.x), p1 = unpack_bf2(u.y), p2 = unpack_bf2(u.z), p3 = unpack_bf2(u.w);
     float s[8] = {p0.x, p0.y, p1.x, p1.y, p2.x, p2.y, p3.x, p3.y};
+    if (n_ip > 0) {
+      float ip[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int j = 0; j < n_ip; ++j) acc_row(ip, a.table.row_ptr(__ldg(a.user_ip_hashes + (long long)b * a.Hip + j), a.D), col);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s[i] = round_bf(s[i] + round_bf(ip[i]));
+    }
+    if (has_cont) cont_add(a, hid, col, s);
+    if (n_ip > 0 || has_cont) { u.x = pack_bf2(s[0], s[1]); u.y = pack_bf2(s[2], s[3]); u.z = pack_bf2(s[4], s[5]); u.w = pack_bf2(s[6], s[7]); }
+    if (a.tokens) *reinterpret_cast<uint4*>(a.tokens + tok * a.D + col) = u;
 #pragma unroll
     for (int i = 0; i < 8; ++i) { s[i] = round_bf(s[i] * a.input_scale); row_ss += s[i] * s[i]; }
     uint4 o;
@@ -323,7 +395,9 @@ phx_status build_tokens_launch(const TokenBuildArgs& a, cudaStream_t stream, std
   if (toks == 0) return PHX_OK;
   const int warps = 8;
   const bool general = a.pack.hist_off || a.pre_hist_post || a.landing || a.concat_hist || a.action_multi_hot || a.x32 ||
-                       a.tokens || a.hashes || a.rows_only;
+                       a.tokens || a.hashes || a.rows_only || a.P || a.hist_actions_bool || a.cand_surfaces || a.n_cont;
+  if (a.P && (a.Hu <= 0 || a.Hu + a.Hip > 2 * PHX_MAX_HASHES || !a.user_hashes)) { err = "build_tokens: user-prefix arguments"; return PHX_E_ARG; }
+  if (a.n_cont && (a.cont_hidden <= 0 || a.cont_hidden > 64 || !a.hist_cont)) { err = "build_tokens: continuous-action arguments"; return PHX_E_ARG; }
   if (general) build_tokens_kernel<true><<<(unsigned)((toks + warps - 1) / warps), warps * 32, 0, stream>>>(a);
   else build_tokens_kernel<false><<<(unsigned)((toks + warps - 1) / warps), warps * 32, 0, stream>>>(a);
   PHX_CUDA_TRY(cudaGetLastError(), err);
@@ -339,11 +413,11 @@ phx_status pack_plan_launch(const PackMap& pk, int B, int S, int C, int* pos_row
   return PHX_OK;
 }
 
-phx_status finish_tokens_launch(const bf16* tok_hist, const bf16* tok_cand, const TokenBuildArgs& a, cudaStream_t stream,
-                                std::string& err) {
+phx_status finish_tokens_launch(const bf16* tok_user, const bf16* tok_hist, const bf16* tok_cand, const TokenBuildArgs& a,
+                                cudaStream_t stream, std::string& err) {
   const long long toks = (long long)a.B * (a.S + a.C);
   if (toks == 0) return PHX_OK;
-  finish_tokens_kernel<<<(unsigned)((toks + 7) / 8), 256, 0, stream>>>(tok_hist, tok_cand, a);
+  finish_tokens_kernel<<<(unsigned)((toks + 7) / 8), 256, 0, stream>>>(tok_user, tok_hist, tok_cand, a);
   PHX_CUDA_TRY(cudaGetLastError(), err);
   return PHX_OK;
 }

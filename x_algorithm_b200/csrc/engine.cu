@@ -108,6 +108,15 @@ struct phx_engine {
   bf16 *proj_hist_t = nullptr, *proj_cand_t = nullptr;   // [D, Kh], [D, Kc]
   bf16 *cat_hist = nullptr, *cat_cand = nullptr, *tok_proj = nullptr;   // [max_batch*S, Kh], [max_batch*C, Kc], [max_tokens, D]
   GemmPlan p_proj_hist, p_proj_cand;
+  // batch-prep buffers beyond posts and authors (cfg.user_prefix, cand_surface, num_hist_continuous): S counts the
+  // user-prefix token, Sh is the number of history slots of the input arrays
+  int P = 0, Sh = 0;
+  bool prep_extras = false;                        // any of the three: only phx_rank_forward_prep* serves the engine
+  int Ku = 0;                                      // user.num_hashes * D
+  bf16 *proj_user_t = nullptr, *cat_user = nullptr;   // [D, Ku], [max_batch, Ku]
+  GemmPlan p_proj_user;
+  bf16* cont_w1[PHX_MAX_HIST_CONT] = {nullptr, nullptr, nullptr, nullptr};
+  bf16* cont_w2[PHX_MAX_HIST_CONT] = {nullptr, nullptr, nullptr, nullptr};
   // full-precision path (cfg.compute_fp32): fp32 activations, plain row order
   bool fp32 = false;
   float *x32 = nullptr, *h32 = nullptr, *qkv32 = nullptr, *attn32 = nullptr, *ffn32 = nullptr, *tmp32 = nullptr, *hist32 = nullptr;
@@ -296,6 +305,17 @@ phx_status check_cfg(const phx_model_config& c, std::string& err) {
     return bad("action sets need 1..32 action types and emb_size / num_action_types a multiple of 8");
   if (c.pack_ragged && c.compute_fp32) return bad("packed rows are not available on the full-precision path");
   if (c.num_candidate_only_layers < 0 || c.num_candidate_only_layers > c.num_layers) return bad("num_candidate_only_layers");
+  if ((c.user_prefix != 0 && c.user_prefix != 1) || (c.cand_surface != 0 && c.cand_surface != 1)) return bad("user_prefix / cand_surface must be 0 or 1");
+  if (c.user_prefix && (c.num_candidates <= 0 || c.user.num_hashes <= 0 || c.user.num_hashes + c.ip.num_hashes > 2 * PHX_MAX_HASHES))
+    return bad("user_prefix needs a ranking engine and 1..PHX_MAX_HASHES user hashes");
+  if (c.cand_surface && c.num_candidates <= 0) return bad("cand_surface needs candidates");
+  if (c.num_hist_continuous < 0 || c.num_hist_continuous > PHX_MAX_HIST_CONT) return bad("num_hist_continuous out of range");
+  if (c.num_hist_continuous > 0 && c.hist_cont_hidden != 32 && c.hist_cont_hidden != 64) return bad("hist_cont_hidden must be 32 or 64");
+  for (int i = 0; i < c.num_hist_continuous; ++i)
+    if (c.hist_cont_index[i] < 0 || c.hist_cont_index[i] >= PHX_PREP_CONTINUOUS || !(c.hist_cont_norm_scale[i] > 0.f))
+      return bad("hist_cont_index / hist_cont_norm_scale");
+  if ((c.user_prefix || c.cand_surface || c.num_hist_continuous > 0) && (c.pack_ragged || c.table_world > 1))
+    return bad("user_prefix / cand_surface / continuous history actions are not available with packed rows or a sharded table");
   return PHX_OK;
 }
 
@@ -342,7 +362,10 @@ phx_status refresh_folded(phx_engine* e) {
 
 bool params_complete(phx_engine* e, bool need_heads) {
   std::vector<std::string> need = {"action_table", "surface_table", "final_norm"};
-  if (e->project) { need.push_back("proj_hist"); if (need_heads) need.push_back("proj_cand"); }
+  if (e->project) { need.push_back("proj_hist"); if (need_heads) need.push_back("proj_cand"); if (e->P) need.push_back("proj_user"); }
+  for (int i = 0; i < e->cfg.num_hist_continuous; ++i) {
+    need.push_back("hist_cont" + std::to_string(i) + ".proj1"); need.push_back("hist_cont" + std::to_string(i) + ".proj2");
+  }
   if (need_heads) {
     if (e->V > 0) need.push_back("unembed");
     if (e->NC > 0) need.push_back("cont_unembed");
@@ -512,17 +535,39 @@ phx_status run_trunk(phx_engine* e, int B, int Tt, int pos_cap, int hist_len, bo
   return PHX_OK;
 }
 
+// Pre-hashed input of one forward, device pointers: phx_rank_batch_hashed or phx_rank_batch_prep brought to one form.
+struct HashedIn {
+  const int *hist_post = nullptr, *hist_author = nullptr, *cand_post = nullptr, *cand_author = nullptr;
+  const int *hist_actions = nullptr, *hist_surfaces = nullptr, *cand_surfaces = nullptr;
+  const unsigned char* hist_actions_bool = nullptr;
+  const int *user_hashes = nullptr, *user_ip_hashes = nullptr;
+  const float* hist_cont = nullptr;
+};
+
 phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc, bf16* x_dst = nullptr, int* seg_dst = nullptr,
                         cudaStream_t stream = nullptr, float* ss_dst = nullptr, int* rows_out = nullptr,
-                        const bf16* landing = nullptr, const int* pos = nullptr, const phx_rank_batch_hashed* hb = nullptr) {
+                        const bf16* landing = nullptr, const int* pos = nullptr, const HashedIn* hb = nullptr) {
   long long ou, oi, oa, oip, tot;
   region_offsets(e->cfg, &ou, &oi, &oa, &oip, &tot);
   TokenBuildArgs ta;
   if (hb) {   // rows already hashed by the host's batch-prep (bd is not read)
     ta.hist_post = ta.hist_author = ta.cand_post = ta.cand_author = nullptr;
-    ta.pre_hist_post = hb->hist_post_hashes; ta.pre_hist_author = hb->hist_author_hashes;
-    ta.pre_cand_post = hb->cand_post_hashes; ta.pre_cand_author = hb->cand_author_hashes;
+    ta.pre_hist_post = hb->hist_post; ta.pre_hist_author = hb->hist_author;
+    ta.pre_cand_post = hb->cand_post; ta.pre_cand_author = hb->cand_author;
     ta.hist_actions = hb->hist_actions; ta.hist_surfaces = hb->hist_surfaces;
+    ta.hist_actions_bool = hb->hist_actions_bool;
+    if (e->cfg.cand_surface) ta.cand_surfaces = hb->cand_surfaces;
+    if (e->P) {
+      ta.P = e->P; ta.Hu = e->cfg.user.num_hashes; ta.Hip = e->cfg.ip.num_hashes;
+      ta.user_hashes = hb->user_hashes; ta.user_ip_hashes = ta.Hip > 0 ? hb->user_ip_hashes : nullptr;
+    }
+    if (e->cfg.num_hist_continuous > 0) {
+      ta.hist_cont = hb->hist_cont; ta.n_cont = e->cfg.num_hist_continuous; ta.cont_hidden = e->cfg.hist_cont_hidden;
+      for (int i = 0; i < ta.n_cont; ++i) {
+        ta.cont_index[i] = e->cfg.hist_cont_index[i]; ta.cont_log[i] = e->cfg.hist_cont_use_log[i];
+        ta.cont_scale[i] = e->cfg.hist_cont_norm_scale[i]; ta.cont_w1[i] = e->cont_w1[i]; ta.cont_w2[i] = e->cont_w2[i];
+      }
+    }
   } else {
     ta.hist_post = (const long long*)bd->hist_post_ids; ta.hist_author = (const long long*)bd->hist_author_ids;
     ta.hist_actions = bd->hist_actions; ta.hist_surfaces = bd->hist_surfaces;
@@ -547,16 +592,17 @@ phx_status build_tokens(phx_engine* e, const phx_rank_batch* bd, int B, int Cc, 
   if (e->project && !rows_out) {
     // gathered rows side by side -> two projection GEMMs -> scale, place and take the row statistics
     if (stream) { e->err = "token prefetch is not available with projected tokens"; return PHX_E_ARG; }
-    ta.concat_hist = e->cat_hist; ta.concat_cand = e->cat_cand;
+    ta.concat_hist = e->cat_hist; ta.concat_cand = e->cat_cand; ta.concat_user = e->cat_user;
     cudaStream_t st = e->stream;
     phx_status s;
     { e->last_launches++; ProfScope ps(e, KC_TOKENS); if ((s = build_tokens_launch(ta, st, e->err))) return s; }
-    bf16* tok_h = e->tok_proj; bf16* tok_c = e->tok_proj + (long long)B * e->S * e->D;
-    if ((s = do_gemm(e, e->p_proj_hist, e->cat_hist, tok_h, nullptr, (long long)B * e->S, EPI_STORE))) return s;
+    bf16* tok_u = e->tok_proj; bf16* tok_h = tok_u + (long long)B * e->P * e->D; bf16* tok_c = tok_h + (long long)B * e->Sh * e->D;
+    if (e->P && (s = do_gemm(e, e->p_proj_user, e->cat_user, tok_u, nullptr, (long long)B, EPI_STORE))) return s;
+    if ((s = do_gemm(e, e->p_proj_hist, e->cat_hist, tok_h, nullptr, (long long)B * e->Sh, EPI_STORE))) return s;
     if (Cc > 0 && (s = do_gemm(e, e->p_proj_cand, e->cat_cand, tok_c, nullptr, (long long)B * Cc, EPI_STORE))) return s;
     e->last_launches++;
     ProfScope ps(e, KC_TOKENS);
-    return finish_tokens_launch(tok_h, tok_c, ta, st, e->err);
+    return finish_tokens_launch(tok_u, tok_h, tok_c, ta, st, e->err);
   }
   if (stream) return build_tokens_launch(ta, stream, e->err);   // prefetch on the side stream: not profiled
   e->last_launches++;
@@ -603,7 +649,9 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
   { const char* sd = getenv("PHX_SYNC_DEBUG"); e->sync_debug = sd && sd[0] == '1'; }
 #endif
   { const char* g = getenv("PHX_GRAPH"); e->graphs_enabled = !(g && g[0] == '0'); }
-  e->D = cfg->emb_size; e->S = cfg->history_len; e->C = cfg->num_candidates; e->T = e->S + e->C;
+  e->P = cfg->user_prefix ? 1 : 0; e->Sh = cfg->history_len;
+  e->prep_extras = cfg->user_prefix || cfg->cand_surface || cfg->num_hist_continuous > 0;
+  e->D = cfg->emb_size; e->S = e->Sh + e->P; e->C = cfg->num_candidates; e->T = e->S + e->C;
   e->Hq = cfg->num_q_heads; e->Hkv = cfg->num_kv_heads; e->dh = cfg->key_size; e->F = cfg->ffn_size;
   e->QW = (e->Hq + 2 * e->Hkv) * e->dh; e->HD = e->Hq * e->dh; e->V = cfg->num_actions; e->NC = cfg->num_continuous;
   long long ou, oi, oa, oip, tot;
@@ -670,8 +718,14 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
   e->project = cfg->token_project != 0;
   if (e->project) {
     const int H2 = 2 * cfg->item.num_hashes;
-    e->Kh = (H2 + 2) * e->D; e->Kc = H2 * e->D;
-    const long long mh = (long long)cfg->max_batch * e->S, mc = (long long)cfg->max_batch * (e->C > 0 ? e->C : 1);
+    e->Kh = (H2 + 2) * e->D; e->Kc = (H2 + (cfg->cand_surface ? 1 : 0)) * e->D;
+    const long long mh = (long long)cfg->max_batch * e->Sh, mc = (long long)cfg->max_batch * (e->C > 0 ? e->C : 1);
+    if (e->P) {
+      e->Ku = cfg->user.num_hashes * e->D;
+      TRY(dev_alloc(e, &e->proj_user_t, (size_t)e->D * e->Ku));
+      TRY(dev_alloc(e, &e->cat_user, (size_t)cfg->max_batch * e->Ku));
+      TRY(gemm_plan_create(&e->p_proj_user, e->cat_user, e->proj_user_t, cfg->max_batch, e->D, e->Ku, false, e->err));
+    }
     TRY(dev_alloc(e, &e->proj_hist_t, (size_t)e->D * e->Kh));
     TRY(dev_alloc(e, &e->proj_cand_t, (size_t)e->D * e->Kc));
     TRY(dev_alloc(e, &e->cat_hist, (size_t)mh * e->Kh));
@@ -748,6 +802,12 @@ phx_status phx_engine_create(const phx_model_config* cfg, int32_t device, phx_en
     const size_t H = (size_t)cfg->item.num_hashes;   // raw ids (8 bytes each) or pre-hashed rows (4 bytes x H each)
     const size_t per_id = 8 > 4 * H ? 8 : 4 * H;
     e->in_stage_bytes = B * ((size_t)e->S * (2 * per_id + 4 + 4) + (size_t)e->C * 2 * per_id) + 2 * (B + 1) * 4 + 64;
+    // the batch-prep form: user and IP rows, one byte per action flag, eight continuous values per history slot, a
+    // surface per candidate; every array starts on a 16-byte boundary
+    const size_t prep_bytes = B * (4 * (size_t)(cfg->user.num_hashes + cfg->ip.num_hashes) +
+                                   (size_t)e->Sh * (8 * H + 4 + (size_t)cfg->num_action_types + 4 * PHX_PREP_CONTINUOUS) +
+                                   (size_t)e->C * (8 * H + 4)) + 10 * 16;
+    if (prep_bytes > e->in_stage_bytes) e->in_stage_bytes = prep_bytes;
     CU(cudaMalloc(&e->in_stage_dev, e->in_stage_bytes));
     CU(cudaMallocHost(&e->in_stage_host, e->in_stage_bytes));
     const size_t rows = B * (size_t)(e->C > 0 ? e->C : 1);
@@ -794,7 +854,8 @@ void phx_engine_destroy(phx_engine* e) {
   }
   fr(e->cos_tab); fr(e->sin_tab); fr(e->x); fr(e->hbuf); fr(e->qkv); fr(e->attn); fr(e->ffn); fr(e->tmp); fr(e->tokens);
   for (phx_engine::PackState* ps : {&e->pack_full, &e->pack_ragged}) { fr(ps->hist_off); fr(ps->cand_off); fr(ps->pos_rows); fr(ps->out_index); }
-  fr(e->proj_hist_t); fr(e->proj_cand_t); fr(e->cat_hist); fr(e->cat_cand); fr(e->tok_proj);
+  fr(e->proj_hist_t); fr(e->proj_cand_t); fr(e->cat_hist); fr(e->cat_cand); fr(e->tok_proj); fr(e->proj_user_t); fr(e->cat_user);
+  for (int i = 0; i < PHX_MAX_HIST_CONT; ++i) { fr(e->cont_w1[i]); fr(e->cont_w2[i]); }
   fr(e->x32); fr(e->h32); fr(e->qkv32); fr(e->attn32); fr(e->ffn32); fr(e->tmp32); fr(e->hist32);
   fr(e->x_alt); fr(e->seg_alt); fr(e->rowss_a_alt); fr(e->rowss_a); fr(e->rowss_f); fr(e->seg); fr(e->hashes); fr(e->err_flag); fr(e->in_stage_dev); fr(e->lp_dev); fr(e->cont_dev); fr(e->score_dev);
   if (e->in_stage_host) cudaFreeHost(e->in_stage_host);
@@ -832,6 +893,19 @@ phx_status phx_load_param(phx_engine* e, const char* name, const float* host, in
     const bool h = n == "proj_hist";
     if (!shape(h ? e->Kh : e->Kc, e->D)) return PHX_E_ARG;
     s = upload_bf16(e, h ? &e->proj_hist_t : &e->proj_cand_t, host, rows, cols, true);
+  }
+  else if (n == "proj_user") {
+    if (!e->project || !e->P) { e->err = "phx_load_param(proj_user): the engine was created without token_project and user_prefix"; return PHX_E_ARG; }
+    if (!shape(e->Ku, e->D)) return PHX_E_ARG;
+    s = upload_bf16(e, &e->proj_user_t, host, rows, cols, true);
+  }
+  else if (n.rfind("hist_cont", 0) == 0) {
+    const size_t dot = n.find('.');
+    const int i = dot == std::string::npos ? -1 : atoi(n.substr(9, dot - 9).c_str());
+    const std::string f = dot == std::string::npos ? "" : n.substr(dot + 1);
+    if (i < 0 || i >= e->cfg.num_hist_continuous || (f != "proj1" && f != "proj2")) { e->err = "unknown parameter " + n; return PHX_E_ARG; }
+    if (f == "proj1") { if (!shape(1, e->cfg.hist_cont_hidden)) return PHX_E_ARG; s = upload_bf16(e, &e->cont_w1[i], host, rows, cols, false); }
+    else { if (!shape(e->cfg.hist_cont_hidden, e->D)) return PHX_E_ARG; s = upload_bf16(e, &e->cont_w2[i], host, rows, cols, false); }
   }
   else if (n == "unembed" || n == "cont_unembed") {
     const bool cont = n == "cont_unembed";
@@ -933,7 +1007,7 @@ phx_status phx_set_blend(phx_engine* e, const phx_blend_spec* spec) {
 namespace {
 // the launches of one forward, in order, on the engine's stream
 phx_status enqueue_forward(phx_engine* e, const phx_rank_batch* bd, const phx_rank_out* od, int B, bool tokens_ready,
-                           const bf16* landing = nullptr, const int* pos = nullptr, const phx_rank_batch_hashed* hb = nullptr) {
+                           const bf16* landing = nullptr, const int* pos = nullptr, const HashedIn* hb = nullptr) {
   phx_status s;
   phx_engine::PackState* pk = e->cur_pack;
   if (pk && (pk->ragged || pk->planned_batch != B)) {
@@ -973,6 +1047,11 @@ phx_status enqueue_forward(phx_engine* e, const phx_rank_batch* bd, const phx_ra
 namespace {
 // the six input arrays of an id batch: a null one would be dereferenced on the device (a fault on a shared GPU)
 bool batch_arrays_present(phx_engine* e, const phx_rank_batch* b, bool need_candidates, const char* who) {
+  if (e->prep_extras) {
+    e->err = std::string(who) + ": the engine is configured for batch-prep buffers (user_prefix / cand_surface / continuous history "
+             "actions): use phx_rank_forward_prep";
+    return false;
+  }
   if (b->batch <= 0) return true;   // nothing is read
   if (b->hist_post_ids && b->hist_author_ids && b->hist_actions && b->hist_surfaces &&
       (!need_candidates || (b->cand_post_ids && b->cand_author_ids))) return true;
@@ -1137,15 +1216,11 @@ phx_status phx_rank_forward_rows_device(phx_engine* e, const phx_rank_batch* bd,
   return PHX_OK;
 }
 
-phx_status phx_rank_forward_hashed_device(phx_engine* e, const phx_rank_batch_hashed* hb, const phx_rank_out* od) {
-  if (!e || !hb || !od) return PHX_E_ARG;
-  if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
-  if (hb->batch < 0 || hb->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
-  if (!hb->hist_post_hashes || !hb->hist_author_hashes || !hb->cand_post_hashes || !hb->cand_author_hashes ||
-      !hb->hist_actions || !hb->hist_surfaces) { e->err = "phx_rank_forward_hashed: null input array"; return PHX_E_ARG; }
+namespace {
+// One forward from pre-hashed rows, asynchronous on the engine's stream.
+phx_status forward_hashed_core(phx_engine* e, const HashedIn& in, int B, const phx_rank_out* od) {
   if (!params_complete(e, true) || !shards_complete(e)) return PHX_E_STATE;
   cudaSetDevice(e->device);
-  const int B = hb->batch;
   e->last_batch = B; e->last_launches = 0; e->prof_used = 0;
   e->prefetch_valid = false;
   e->graph_key_valid = false;   // plain launches: the graph cache is keyed on id batches
@@ -1154,17 +1229,76 @@ phx_status phx_rank_forward_hashed_device(phx_engine* e, const phx_rank_batch_ha
   PHX_CUDA_TRY(cudaEventRecord(e->ev0, e->stream), e->err);
   phx_status s;
   if ((s = refresh_folded(e))) return s;
-  if ((s = enqueue_forward(e, nullptr, od, B, false, nullptr, nullptr, hb))) return s;
+  if ((s = enqueue_forward(e, nullptr, od, B, false, nullptr, nullptr, &in))) return s;
   PHX_CUDA_TRY(cudaEventRecord(e->ev1, e->stream), e->err);
   if (e->ev_done[0]) { e->done_idx ^= 1; PHX_CUDA_TRY(cudaEventRecord(e->ev_done[e->done_idx], e->stream), e->err); }
   return PHX_OK;
 }
 
+// results of the forward that was just enqueued: device -> pinned -> the caller's arrays; waits for the stream
+phx_status fetch_outputs(phx_engine* e, size_t B, const phx_rank_out* oh) {
+  const size_t rows = B * e->C;
+  if (oh->log_probs) PHX_CUDA_TRY(cudaMemcpyAsync(e->lp_host, e->lp_dev, rows * e->V * 4, cudaMemcpyDeviceToHost, e->stream), e->err);
+  if (oh->continuous) PHX_CUDA_TRY(cudaMemcpyAsync(e->cont_host, e->cont_dev, rows * e->NC * 4, cudaMemcpyDeviceToHost, e->stream), e->err);
+  if (oh->scores && e->has_blend) PHX_CUDA_TRY(cudaMemcpyAsync(e->score_host, e->score_dev, rows * 8, cudaMemcpyDeviceToHost, e->stream), e->err);
+  PHX_CUDA_TRY(cudaStreamSynchronize(e->stream), e->err);
+  if (oh->log_probs) memcpy(oh->log_probs, e->lp_host, rows * e->V * 4);
+  if (oh->continuous) memcpy(oh->continuous, e->cont_host, rows * e->NC * 4);
+  if (oh->scores && e->has_blend) memcpy(oh->scores, e->score_host, rows * 8);
+  return check_err_flag(e);
+}
+
+bool hashed_arrays_present(phx_engine* e, const phx_rank_batch_hashed* b, const char* who) {
+  if (e->prep_extras) {
+    e->err = std::string(who) + ": the engine is configured for batch-prep buffers (user_prefix / cand_surface / continuous history "
+             "actions): use phx_rank_forward_prep";
+    return false;
+  }
+  if (b->batch <= 0) return true;
+  if (b->hist_post_hashes && b->hist_author_hashes && b->cand_post_hashes && b->cand_author_hashes && b->hist_actions && b->hist_surfaces)
+    return true;
+  e->err = std::string(who) + ": null input array";
+  return false;
+}
+
+// the buffers the configuration reads must be there; the others are ignored
+bool prep_arrays_present(phx_engine* e, const phx_rank_batch_prep* b, const char* who) {
+  if (!e->cfg.action_multi_hot) { e->err = std::string(who) + ": history_actions is a set per position: the engine needs action_multi_hot = 1"; return false; }
+  if (b->batch <= 0) return true;
+  const bool ok = b->history_post_hashes && b->history_auth_hashes && b->history_product_surfaces && b->history_actions &&
+                  b->candidate_post_hashes && b->candidate_auth_hashes && (!e->P || b->user_hashes) &&
+                  (!e->cfg.cand_surface || b->candidate_product_surfaces) &&
+                  (e->cfg.num_hist_continuous == 0 || b->history_continuous_actions);
+  if (!ok) e->err = std::string(who) + ": null input array";
+  return ok;
+}
+
+HashedIn hashed_in(const phx_rank_batch_prep* b) {
+  HashedIn in;
+  in.user_hashes = b->user_hashes; in.user_ip_hashes = b->user_ip_hashes;
+  in.hist_post = b->history_post_hashes; in.hist_author = b->history_auth_hashes; in.hist_surfaces = b->history_product_surfaces;
+  in.hist_actions_bool = b->history_actions; in.hist_cont = b->history_continuous_actions;
+  in.cand_post = b->candidate_post_hashes; in.cand_author = b->candidate_auth_hashes; in.cand_surfaces = b->candidate_product_surfaces;
+  return in;
+}
+}  // namespace
+
+phx_status phx_rank_forward_hashed_device(phx_engine* e, const phx_rank_batch_hashed* hb, const phx_rank_out* od) {
+  if (!e || !hb || !od) return PHX_E_ARG;
+  if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
+  if (hb->batch < 0 || hb->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
+  if (!hashed_arrays_present(e, hb, "phx_rank_forward_hashed_device")) return PHX_E_ARG;
+  HashedIn in;
+  in.hist_post = hb->hist_post_hashes; in.hist_author = hb->hist_author_hashes; in.cand_post = hb->cand_post_hashes;
+  in.cand_author = hb->cand_author_hashes; in.hist_actions = hb->hist_actions; in.hist_surfaces = hb->hist_surfaces;
+  return forward_hashed_core(e, in, hb->batch, od);
+}
+
 phx_status phx_rank_forward_hashed(phx_engine* e, const phx_rank_batch_hashed* bh, const phx_rank_out* oh) {
   if (!e || !bh || !oh) return PHX_E_ARG;
+  if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
   if (bh->batch < 0 || bh->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
-  if (!bh->hist_post_hashes || !bh->hist_author_hashes || !bh->cand_post_hashes || !bh->cand_author_hashes ||
-      !bh->hist_actions || !bh->hist_surfaces) { e->err = "phx_rank_forward_hashed: null input array"; return PHX_E_ARG; }
+  if (!hashed_arrays_present(e, bh, "phx_rank_forward_hashed")) return PHX_E_ARG;
   cudaSetDevice(e->device);
   const size_t B = bh->batch, S = e->S, C = e->C, H = e->cfg.item.num_hashes;
   if (B == 0) return PHX_OK;
@@ -1183,15 +1317,56 @@ phx_status phx_rank_forward_hashed(phx_engine* e, const phx_rank_batch_hashed* b
   phx_rank_out od; od.log_probs = e->lp_dev; od.continuous = e->cont_dev; od.scores = e->score_dev;
   phx_status s = phx_rank_forward_hashed_device(e, &bd, &od);
   if (s) return s;
-  const size_t rows = B * C;
-  if (oh->log_probs) PHX_CUDA_TRY(cudaMemcpyAsync(e->lp_host, e->lp_dev, rows * e->V * 4, cudaMemcpyDeviceToHost, e->stream), e->err);
-  if (oh->continuous) PHX_CUDA_TRY(cudaMemcpyAsync(e->cont_host, e->cont_dev, rows * e->NC * 4, cudaMemcpyDeviceToHost, e->stream), e->err);
-  if (oh->scores && e->has_blend) PHX_CUDA_TRY(cudaMemcpyAsync(e->score_host, e->score_dev, rows * 8, cudaMemcpyDeviceToHost, e->stream), e->err);
-  PHX_CUDA_TRY(cudaStreamSynchronize(e->stream), e->err);
-  if (oh->log_probs) memcpy(oh->log_probs, e->lp_host, rows * e->V * 4);
-  if (oh->continuous) memcpy(oh->continuous, e->cont_host, rows * e->NC * 4);
-  if (oh->scores && e->has_blend) memcpy(oh->scores, e->score_host, rows * 8);
-  return check_err_flag(e);
+  return fetch_outputs(e, B, oh);
+}
+
+phx_status phx_rank_forward_prep_device(phx_engine* e, const phx_rank_batch_prep* pb, const phx_rank_out* od) {
+  if (!e || !pb || !od) return PHX_E_ARG;
+  if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
+  if (pb->batch < 0 || pb->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
+  if (!prep_arrays_present(e, pb, "phx_rank_forward_prep_device")) return PHX_E_ARG;
+  return forward_hashed_core(e, hashed_in(pb), pb->batch, od);
+}
+
+phx_status phx_rank_forward_prep(phx_engine* e, const phx_rank_batch_prep* bh, const phx_rank_out* oh) {
+  if (!e || !bh || !oh) return PHX_E_ARG;
+  if (e->C <= 0) { e->err = "engine was created without candidates"; return PHX_E_ARG; }
+  if (bh->batch < 0 || bh->batch > e->cfg.max_batch) { e->err = "batch exceeds max_batch"; return PHX_E_CAPACITY; }
+  if (!prep_arrays_present(e, bh, "phx_rank_forward_prep")) return PHX_E_ARG;
+  cudaSetDevice(e->device);
+  const size_t B = bh->batch, S = e->Sh, C = e->C, H = e->cfg.item.num_hashes, V = e->cfg.num_action_types;
+  const size_t Hu = e->cfg.user.num_hashes, Hip = e->cfg.ip.num_hashes;
+  if (B == 0) return PHX_OK;
+  uint8_t* hp = (uint8_t*)e->in_stage_host;
+  uint8_t* dp = (uint8_t*)e->in_stage_dev;
+  size_t off = 0;
+  // only what the configuration reads is copied; every array starts on a 16-byte boundary of the staging block
+  bool fits = true;
+  auto put = [&](const void* src, size_t bytes, bool wanted) -> const void* {
+    if (!wanted || !src) return nullptr;
+    if (off + bytes > e->in_stage_bytes) { fits = false; return nullptr; }
+    memcpy(hp + off, src, bytes);
+    const void* d = dp + off;
+    off = (off + bytes + 15) & ~(size_t)15;
+    return d;
+  };
+  phx_rank_batch_prep bd; memset(&bd, 0, sizeof(bd)); bd.batch = bh->batch;
+  bd.user_hashes = (const int32_t*)put(bh->user_hashes, B * Hu * 4, e->P != 0);
+  bd.user_ip_hashes = (const int32_t*)put(bh->user_ip_hashes, B * Hip * 4, e->P != 0 && Hip > 0);
+  bd.history_post_hashes = (const int32_t*)put(bh->history_post_hashes, B * S * H * 4, true);
+  bd.history_auth_hashes = (const int32_t*)put(bh->history_auth_hashes, B * S * H * 4, true);
+  bd.history_product_surfaces = (const int32_t*)put(bh->history_product_surfaces, B * S * 4, true);
+  bd.history_actions = (const uint8_t*)put(bh->history_actions, B * S * V, true);
+  bd.history_continuous_actions = (const float*)put(bh->history_continuous_actions, B * S * PHX_PREP_CONTINUOUS * 4, e->cfg.num_hist_continuous > 0);
+  bd.candidate_post_hashes = (const int32_t*)put(bh->candidate_post_hashes, B * C * H * 4, true);
+  bd.candidate_auth_hashes = (const int32_t*)put(bh->candidate_auth_hashes, B * C * H * 4, true);
+  bd.candidate_product_surfaces = (const int32_t*)put(bh->candidate_product_surfaces, B * C * 4, e->cfg.cand_surface != 0);
+  if (!fits) { e->err = "phx_rank_forward_prep: staging block too small"; return PHX_E_CAPACITY; }
+  PHX_CUDA_TRY(cudaMemcpyAsync(dp, hp, off, cudaMemcpyHostToDevice, e->stream), e->err);
+  phx_rank_out od; od.log_probs = e->lp_dev; od.continuous = e->cont_dev; od.scores = e->score_dev;
+  phx_status s = phx_rank_forward_prep_device(e, &bd, &od);
+  if (s) return s;
+  return fetch_outputs(e, B, oh);
 }
 
 phx_status phx_rank_prefetch_device(phx_engine* e, const phx_rank_batch* bd) {

@@ -161,6 +161,53 @@ class PhoenixEngine:
         o = _lib.RankOut(_ptr(lp), _ptr(cont), _ptr(sc))
         self._check(lib.phx_rank_forward_hashed_device(self._h, C.byref(b), C.byref(o)))
 
+    _PREP_FIELDS = (("user_hashes", np.int32), ("user_ip_hashes", np.int32), ("history_post_hashes", np.int32),
+                    ("history_auth_hashes", np.int32), ("history_product_surfaces", np.int32), ("history_actions", np.bool_),
+                    ("history_continuous_actions", np.float32), ("candidate_post_hashes", np.int32),
+                    ("candidate_auth_hashes", np.int32), ("candidate_product_surfaces", np.int32))
+
+    def rank_prep(self, prep) -> RankOutputs:
+        """The forward over the mandatory buffers of the reference's batch-prep, under its attribute names
+        (RankingBatchPrep, xai-recsys-engine/src/python.rs:1394-1404): `prep` is any object with those attributes as
+        host arrays - user_hashes i32 [B,Hu], user_ip_hashes i32 [B,Hip] (or None), history_post_hashes /
+        history_auth_hashes i32 [B,S,H], history_product_surfaces i32 [B,S], history_actions bool [B,S,V],
+        history_continuous_actions f32 [B,S,8], candidate_post_hashes / candidate_auth_hashes i32 [B,C,H],
+        candidate_product_surfaces i32 [B,C].  Which of them are read follows the engine's configuration."""
+        cfg = self.cfg
+        b = _lib.RankBatchPrep()
+        keep = []
+        for name, dt in self._PREP_FIELDS:
+            a = getattr(prep, name, None)
+            if a is None:
+                continue
+            a = np.ascontiguousarray(a, dt)
+            keep.append(a)
+            setattr(b, name, a.ctypes.data)
+        hp = np.asarray(prep.history_post_hashes)
+        B = hp.shape[0]
+        assert hp.shape == (B, cfg.history_len, cfg.num_hashes)
+        assert np.asarray(prep.history_actions).shape == (B, cfg.history_len, cfg.num_action_types)
+        assert np.asarray(prep.candidate_post_hashes).shape == (B, cfg.num_candidates, cfg.num_hashes)
+        b.batch = B
+        lp = np.empty((B, cfg.num_candidates, cfg.num_actions), np.float32)
+        cont = np.empty((B, cfg.num_candidates, cfg.num_continuous), np.float32)
+        sc = np.empty((B, cfg.num_candidates), np.float64) if self._has_blend else None
+        o = _lib.RankOut(_ptr(lp), _ptr(cont), _ptr(sc))
+        self._check(lib.phx_rank_forward_prep(self._h, C.byref(b), C.byref(o)))
+        return RankOutputs(lp, cont, sc)
+
+    def rank_prep_device(self, B: int, prep, lp, cont, sc=None):
+        """Same with device tensors as the attributes of `prep` (history_actions as a uint8 / bool tensor), asynchronous on
+        the engine's stream."""
+        b = _lib.RankBatchPrep()
+        b.batch = B
+        for name, _ in self._PREP_FIELDS:
+            a = getattr(prep, name, None)
+            if a is not None:
+                setattr(b, name, _ptr(a))
+        o = _lib.RankOut(_ptr(lp), _ptr(cont), _ptr(sc))
+        self._check(lib.phx_rank_forward_prep_device(self._h, C.byref(b), C.byref(o)))
+
     def rank_submit(self, inp: RankInputs, slot: int) -> None:
         """Start a host-buffer request in pipeline slot 0 or 1 and return at once (the inputs are copied before the
         call returns).  `rank_collect(slot)` delivers its results; with both slots in flight the host-side copies of
