@@ -31,6 +31,8 @@ WORKLOAD = dict(emb_size=512, num_layers=8, num_q_heads=8, num_kv_heads=8, key_s
                 history_len=128, num_candidates=512, num_actions=19, num_continuous=1, num_hashes=2,
                 table_size=1 << 22)
 BATCH = 256
+GEMM_DRAM_BYTES_PER_LAUNCH = 714.3e6          # measured (ncu), batch 256, average of the four GEMMs of a layer
+GEMM_ALGORITHMIC_BYTES_PER_LAUNCH = 756.6e6   # A + residual + result + weights of the same launches
 TABLE_SEED, WEIGHT_SEED, BLEND_SEED, ID_SEED = 7, 0, 1, 2
 
 
@@ -530,10 +532,11 @@ def main():
             gpu_launches=launches,
             roofline=dict(bound="tensor", kernel="gemm_tcgen05_kernel", achieved=gemm_tflops, peak=peaks["bf16"], unit="TFLOP/s",
                           frac=(gemm_tflops / peaks["bf16"]) if gemm_tflops else None,
-                          # DRAM read+write bytes per launch, average over the four GEMM shapes: ncu capture at
-                          # M = 40,960 rows (profiles/gemm_tcgen05_cfg1_shapes.md), scaled by rows (traffic grows with M)
-                          traffic=592e6 * (B / 256.0), traffic_unit="bytes/launch",
-                          algorithmic_bytes_per_launch=755e6 * (B / 256.0),
+                          # dram__bytes_read.sum + dram__bytes_write.sum per launch from an ncu capture of this
+                          # command at batch 256 (qkv 620.4, out 459.3, up 784.9, down 992.7 MB: their average), and
+                          # the operand + result bytes of the same four launches; both grow with the batch
+                          traffic=GEMM_DRAM_BYTES_PER_LAUNCH * (B / 256.0), traffic_unit="bytes/launch",
+                          algorithmic_bytes_per_launch=GEMM_ALGORITHMIC_BYTES_PER_LAUNCH * (B / 256.0),
                           peak_source=peaks["source"] + " (sustained bf16)", launches_per_step=gemm_n, ms_per_step=gemm_ms),
             kernel_ms_per_step={k: v[0] for k, v in prof.items()},
             clocks=sampler.summary(),
