@@ -614,25 +614,29 @@ ranker_attention_resident_kernel(const __grid_constant__ CUtensorMap map_q, cons
 }
 
 // ---- resident history, two softmax warpgroups (the ranking trunk's shape at throughput batch sizes) ----------------
-// Head dim 64, at most 128 history keys.  A persistent CTA (one per SM, 320 threads) walks over (batch, head) items;
+// Head dim 64, at most 128 history keys.  A persistent CTA (one per SM, 352 threads) walks over (batch, head) items;
 // per item the history K and V tiles are loaded once by TMA (double-buffered across items, so the next item's tiles
 // arrive while the current one is still being worked on) and every 128-row query tile of the request streams through
-// a three-deep Q ring.  Two softmax warpgroups take alternate tiles, each with its own S and O accumulators in tensor
-// memory (S0, S1 at columns 0 / 128, O0, O1 at 256 / 320) and its own P buffer in shared memory: while one warpgroup
-// exponentiates tile g, the MMA warp has already produced S of tile g+1 for the other, and P V of tile g runs under
-// the other warpgroup's softmax.  Thread = query row: the whole 128-key S row is read from tensor memory once, kept in
-// registers 64 keys at a time (once for the row maximum, once for the probabilities), so the row never spills.  The
-// candidate x candidate block is never formed: a candidate's own key
-// is one extra softmax term from a per-row dot product (its k / v rows are requested a tile ahead).  Query tiles are
-// taken from the history block and the candidate block separately, so the plain [B, T] token layout and the split
-// layout (all history rows, then all candidate rows) differ only in the tensor maps' strides; candidate-only layers
-// skip the history tiles.  All waits are bounded (sm100_ptx.cuh).
-constexpr int PP_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2-5 softmax warpgroup 0, warps 6-9 softmax warpgroup 1
+// a three-deep ring of stages.  A stage holds the tile's Q rows and, for a candidate tile, the same rows of K and V:
+// everything a tile reads from global memory arrives by bulk copies, and its output leaves the same way (the O rows
+// are staged in the stage's Q slab, which the tensor core has long finished with, and a store warp hands them to TMA
+// and releases the stage).  Two softmax warpgroups take alternate tiles, each with its own S and O accumulators in
+// tensor memory (S0, S1 at columns 0 / 128, O0, O1 at 256 / 320): while one warpgroup exponentiates tile g, the MMA
+// warp has already produced S of tile g+1 for the other, and P V of tile g runs under the other warpgroup's softmax.
+// Thread = query row: the 128-key S row is read from tensor memory 64 keys at a time, once for the row maximum and
+// once for the probabilities, which go straight back into tensor memory as bf16 pairs over the columns the row's S
+// values came from; P V takes its A operand from there (no shared-memory round trip for P).
+// The candidate x candidate block is never used as such: the tensor core forms Q Kc^T of the tile's own rows into a
+// 128-column scratch (columns 384..511) and each thread picks its diagonal element - the candidate's score against
+// its own key, one extra softmax term whose value row the thread reads from the stage.  Query tiles are taken from
+// the history block and the candidate block separately, so the plain [B, T] token layout and the split layout (all
+// history rows, then all candidate rows) differ only in the tensor maps' strides; candidate-only layers skip the
+// history tiles.  All waits are bounded (sm100_ptx.cuh).
+constexpr int PP_THREADS = 352;   // warp 0 TMA loads, warp 1 MMA, warps 2-5 / 6-9 softmax warpgroups 0 / 1, warp 10 TMA stores
 constexpr int PP_NQ = 3;
 
 struct PingArgs {
-  const bf16* k; const bf16* v; bf16* out; const int* seg;
-  long long k_tok_stride, v_tok_stride;
+  const int* seg;
   int q_head_stride, k_head_stride, v_head_stride;
   int Hq, Hkv, n_hist, n_cand, n_items;
   long long hist_row0, hist_req_rows, cand_row0, cand_req_rows;   // token row of position 0 of request 0; rows per request
@@ -642,19 +646,39 @@ struct PingArgs {
   int* err_flag;
 };
 
+// the eight tensor maps of a launch: Q / K / V / out over the history block and over the candidate block
+struct PingMaps { CUtensorMap qh, qc, kh, vh, kc, vc, oh, oc; };
+
+// D[tmem] (+)= A[tmem] * B[smem desc]: the A operand (bf16 pairs, one row per lane) comes from tensor memory
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accum)
+      : "memory");
+}
+// 32 registers per thread -> 32 lanes x 32 columns, completion left to a later tcgen05.wait::st
+__device__ __forceinline__ void tmem_st32_nowait(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
 template <bool CAP>
 __global__ void __launch_bounds__(PP_THREADS, 1)
-ranker_attention_pingpong_kernel(const __grid_constant__ CUtensorMap map_qh, const __grid_constant__ CUtensorMap map_qc,
-                                 const __grid_constant__ CUtensorMap map_kh, const __grid_constant__ CUtensorMap map_vh,
-                                 PingArgs a) {
+ranker_attention_pingpong_kernel(const __grid_constant__ PingMaps maps, PingArgs a) {
   constexpr int DH = 64;
-  constexpr uint32_t TM_S = 0, TM_O = 256;
+  constexpr uint32_t TM_S = 0, TM_O = 256, TM_D = 384;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sKV = base;                       // 2 x (K [128 x 128 B], V [128 x 128 B])
-  const uint32_t sQ = sKV + 4 * SLAB;              // PP_NQ x [128 x 128 B]
-  const uint32_t sP = sQ + PP_NQ * SLAB;           // 2 warpgroups x 2 x [128 rows x 64 keys]
-  const uint32_t sMask = sP + 4 * SLAB;            // 2 warpgroups x 4 words
+  const uint32_t sQ = sKV + 4 * SLAB;              // PP_NQ stages x (Q, Kc, Vc), each [128 x 128 B]
+  const uint32_t sMask = sQ + 3 * PP_NQ * SLAB;    // 2 warpgroups x 4 words
   const uint32_t bars = sMask + 64;
   auto kv_full = [&](int i) { return bars + 8u * i; };
   auto kv_free = [&](int i) { return bars + 16u + 8u * i; };
@@ -663,7 +687,9 @@ ranker_attention_pingpong_kernel(const __grid_constant__ CUtensorMap map_qh, con
   auto s_full = [&](int i) { return bars + 80u + 8u * i; };
   auto p_ready = [&](int i) { return bars + 96u + 8u * i; };
   auto o_done = [&](int i) { return bars + 112u + 8u * i; };
-  const uint32_t tmem_slot = bars + 128;
+  auto o_staged = [&](int i) { return bars + 128u + 8u * i; };
+  const uint32_t d_free = bars + 144u;
+  const uint32_t tmem_slot = bars + 152u;
   uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
   uint32_t* mask_words = reinterpret_cast<uint32_t*>(smem_raw + (sMask - smem_u32(smem_raw)));
 
@@ -677,11 +703,12 @@ ranker_attention_pingpong_kernel(const __grid_constant__ CUtensorMap map_qh, con
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
-      mbar_init(kv_full(i), 1); mbar_init(kv_free(i), 1); mbar_init(s_full(i), 1); mbar_init(p_ready(i), 128); mbar_init(o_done(i), 1);
+      mbar_init(kv_full(i), 1); mbar_init(kv_free(i), 1); mbar_init(s_full(i), 1); mbar_init(p_ready(i), 128);
+      mbar_init(o_done(i), 1); mbar_init(o_staged(i), 128);
     }
-    // a Q buffer is free once S has been computed from it (commit) and the 128 threads of the warpgroup that owns the
-    // tile have read their rows for the self term
-    for (int i = 0; i < PP_NQ; ++i) { mbar_init(q_full(i), 1); mbar_init(q_free(i), 129); }
+    // a stage is free again once the tile's output rows, staged in its Q slab, have been read by the store
+    for (int i = 0; i < PP_NQ; ++i) { mbar_init(q_full(i), 1); mbar_init(q_free(i), 1); }
+    mbar_init(d_free, 128);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(tmem_slot, 512);
@@ -700,14 +727,22 @@ ranker_attention_pingpong_kernel(const __grid_constant__ CUtensorMap map_qh, con
         const int kb = li & 1;
         mbar_wait(kv_free(kb), (uint32_t)(((li >> 1) & 1) ^ 1), verr);
         mbar_expect_tx(kv_full(kb), 2 * SLAB);
-        tma_load_3d(sKV + (2 * kb) * SLAB, &map_kh, kv_full(kb), hk * a.k_head_stride, 0, b);
-        tma_load_3d(sKV + (2 * kb + 1) * SLAB, &map_vh, kv_full(kb), hk * a.v_head_stride, 0, b);
+        tma_load_3d(sKV + (2 * kb) * SLAB, &maps.kh, kv_full(kb), hk * a.k_head_stride, 0, b);
+        tma_load_3d(sKV + (2 * kb + 1) * SLAB, &maps.vh, kv_full(kb), hk * a.v_head_stride, 0, b);
         for (int ti = 0; ti < nt; ++ti, ++g) {
           const int st = g % PP_NQ;
+          const uint32_t dst = sQ + 3 * st * SLAB;
           mbar_wait(q_free(st), (uint32_t)(((g / PP_NQ) & 1) ^ 1), verr);
-          mbar_expect_tx(q_full(st), SLAB);
-          if (ti < n_htiles) tma_load_3d(sQ + st * SLAB, &map_qh, q_full(st), h * a.q_head_stride, ti * QT, b);
-          else tma_load_3d(sQ + st * SLAB, &map_qc, q_full(st), h * a.q_head_stride, (ti - n_htiles) * QT, b);
+          if (ti < n_htiles) {
+            mbar_expect_tx(q_full(st), SLAB);
+            tma_load_3d(dst, &maps.qh, q_full(st), h * a.q_head_stride, ti * QT, b);
+          } else {
+            const int r0 = (ti - n_htiles) * QT;
+            mbar_expect_tx(q_full(st), 3 * SLAB);
+            tma_load_3d(dst, &maps.qc, q_full(st), h * a.q_head_stride, r0, b);
+            tma_load_3d(dst + SLAB, &maps.kc, q_full(st), hk * a.k_head_stride, r0, b);
+            tma_load_3d(dst + 2 * SLAB, &maps.vc, q_full(st), hk * a.v_head_stride, r0, b);
+          }
         }
       }
     }
@@ -716,21 +751,20 @@ ranker_attention_pingpong_kernel(const __grid_constant__ CUtensorMap map_qh, con
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(QT, 128);
       constexpr uint32_t idesc_o = make_idesc_b_mn(QT, DH);
-      auto issue_pv = [&](int gp, int kbp, bool last_of_item) {      // O[w] = P[w] V for tile gp
+      auto issue_pv = [&](int gp, int kbp, bool last_of_item) {      // O[w] = P[w] V for tile gp, P from tensor memory
         const int w = gp & 1;
         mbar_wait(p_ready(w), (uint32_t)((gp >> 1) & 1), verr);
         tc_fence_after();
         const uint32_t sV = sKV + (2 * kbp + 1) * SLAB;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint64_t pd = make_smem_desc(sP + (2 * w + (kk >> 2)) * SLAB) + (uint64_t)((kk & 3) * 2);
+        for (int kk = 0; kk < 8; ++kk) {                             // 16 keys = 8 columns of bf16 pairs per step
           const uint64_t vd = make_smem_desc_mn(sV + kk * 16 * 128, 128 * 128, 1024);
-          umma_bf16(tmem + TM_O + w * DH, pd, vd, idesc_o, kk != 0);
+          umma_bf16_ts(tmem + TM_O + w * DH, tmem + TM_S + w * 128 + kk * 8, vd, idesc_o, kk != 0);
         }
         umma_commit(o_done(w));
         if (last_of_item) umma_commit(kv_free(kbp));                 // every MMA that read this item's K / V is behind this point
       };
-      int g = 0, prev_kb = 0;
+      int g = 0, prev_kb = 0, n_d = 0;
       bool prev_last = false;
       for (int li = 0; li < my_items; ++li) {
         const int kb = li & 1;
@@ -739,18 +773,43 @@ ranker_attention_pingpong_kernel(const __grid_constant__ CUtensorMap map_qh, con
           const int st = g % PP_NQ, w = g & 1;
           mbar_wait(q_full(st), (uint32_t)((g / PP_NQ) & 1), verr);
           tc_fence_after();
-          // S[w] is free: P V of tile g - 2 was issued behind that tile's p_ready, which its warpgroup gives after
-          // it has read S
-          const uint64_t qd = make_smem_desc(sQ + st * SLAB), kd = make_smem_desc(sKV + (2 * kb) * SLAB);
+          // S[w] (and the P that overwrote part of it) is free: P V of tile g - 2 was issued before this point and the
+          // tensor core runs its instructions in order
+          const uint64_t qd = make_smem_desc(sQ + 3 * st * SLAB), kd = make_smem_desc(sKV + (2 * kb) * SLAB);
 #pragma unroll
           for (int k = 0; k < 4; ++k) umma_bf16(tmem + TM_S + w * 128, qd + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), idesc_s, k != 0);
+          if (ti >= n_htiles) {
+            // the tile's rows against their own keys; the scratch is free once the previous candidate tile's warpgroup
+            // has picked its diagonal
+            mbar_wait(d_free, (uint32_t)((n_d & 1) ^ 1), verr);
+            tc_fence_after();
+            ++n_d;
+            const uint64_t kcd = make_smem_desc(sQ + (3 * st + 1) * SLAB);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) umma_bf16(tmem + TM_D, qd + (uint64_t)(k * 2), kcd + (uint64_t)(k * 2), idesc_s, k != 0);
+          }
           umma_commit(s_full(w));
-          umma_commit(q_free(st));
           if (g > 0) issue_pv(g - 1, prev_kb, prev_last);
           prev_kb = kb; prev_last = (ti == nt - 1);
         }
       }
       if (G > 0) issue_pv(G - 1, prev_kb, prev_last);
+    }
+  } else if (warp == 10) {
+    // ---------------- store warp: staged output rows -> global memory, then the stage goes back to the producer --------
+    if (lane == 0) {
+      for (int g = 0; g < G; ++g) {
+        const int li = g / nt, ti = g - li * nt, st = g % PP_NQ, w = g & 1;
+        const int it = (int)blockIdx.x + li * (int)gridDim.x;
+        const int b = it / a.Hq, h = it % a.Hq;
+        mbar_wait(o_staged(w), (uint32_t)((g >> 1) & 1), verr);
+        if (ti < n_htiles) tma_store_3d(&maps.oh, sQ + 3 * st * SLAB, h * DH, ti * QT, b);
+        else tma_store_3d(&maps.oc, sQ + 3 * st * SLAB, h * DH, (ti - n_htiles) * QT, b);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        mbar_arrive(q_free(st));
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
   } else {
     // ---------------- softmax / epilogue: warpgroup w takes the tiles g = w, w + 2, ... ----------------
@@ -760,77 +819,36 @@ ranker_attention_pingpong_kernel(const __grid_constant__ CUtensorMap map_qh, con
     const int sw = r & 7;
     const uint32_t lane_base = ((uint32_t)(quad * 32) << 16);
     const float csc = CAP ? 1.0f : a.sm_scale * 1.4426950408889634f;
-    const uint32_t myP = sP + (2 * w) * SLAB;
     auto wg_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(1 + w) : "memory"); };
 
     // what a thread needs to know about its row of a tile; the two segment words are loaded a tile ahead of their use
-    struct Tile { int b, h, hk, li; long long tok; int seg, hseg; bool cand; };
+    struct Tile { int b, li, seg, hseg; bool cand; };
     auto tile_of = [&](int g) {
       Tile t;
       t.li = g / nt;
       const int ti = g - t.li * nt;
       const int it = (int)blockIdx.x + t.li * (int)gridDim.x;
-      t.b = it / a.Hq; t.h = it % a.Hq; t.hk = t.h / (a.Hq / a.Hkv);
+      t.b = it / a.Hq;
       t.cand = ti >= n_htiles;
       const int p = (t.cand ? (ti - n_htiles) : ti) * QT + r;                        // position inside the block
       const bool in = p < (t.cand ? a.n_cand : a.n_hist);
-      t.tok = in ? (t.cand ? a.cand_row0 + (long long)t.b * a.cand_req_rows + p : a.hist_row0 + (long long)t.b * a.hist_req_rows + p) : -1;
-      t.seg = in ? a.seg[t.tok] : 0;
+      const long long tok = t.cand ? a.cand_row0 + (long long)t.b * a.cand_req_rows + p : a.hist_row0 + (long long)t.b * a.hist_req_rows + p;
+      t.seg = in ? a.seg[tok] : 0;
       t.hseg = (r < a.n_hist) ? a.seg[a.hist_row0 + (long long)t.b * a.hist_req_rows + r] : 0;   // history key r of the item
       return t;
     };
-    // a candidate row's own k / v row (requested whether or not the slot is padded: the address does not wait for the
-    // segment word)
-    auto load_row = [&](const bf16* basep, long long stride, const Tile& t, int hoff, uint4 (&dst)[DH / 8]) {
-      if (t.cand && t.tok >= 0) {
-        const uint4* p = reinterpret_cast<const uint4*>(basep + t.tok * stride + hoff);
-#pragma unroll
-        for (int c = 0; c < DH / 8; ++c) dst[c] = __ldg(p + c);
-      }
-    };
-    // q . k of this row against its own key, q from the (swizzled) Q buffer; every thread then lets go of the buffer
-    auto self_dot = [&](int g, const Tile& t, const uint4 (&krow)[DH / 8]) {
-      const int st = g % PP_NQ;
-      mbar_wait(q_full(st), (uint32_t)((g / PP_NQ) & 1), verr);
-      float dot = 0.f;
-      if (t.cand && t.seg == -1) {
-        float d4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int c = 0; c < DH / 8; ++c) {
-          uint4 qa;
-          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(qa.x), "=r"(qa.y), "=r"(qa.z), "=r"(qa.w)
-                       : "r"(sQ + st * SLAB + r * 128 + ((uint32_t)(c ^ sw) << 4)));
-          const uint4 ka = krow[c];
-          const float2 q0f = unpack_bf2(qa.x), q1f = unpack_bf2(qa.y), q2f = unpack_bf2(qa.z), q3f = unpack_bf2(qa.w);
-          const float2 k0f = unpack_bf2(ka.x), k1f = unpack_bf2(ka.y), k2f = unpack_bf2(ka.z), k3f = unpack_bf2(ka.w);
-          d4[0] += q0f.x * k0f.x + q0f.y * k0f.y; d4[1] += q1f.x * k1f.x + q1f.y * k1f.y;
-          d4[2] += q2f.x * k2f.x + q2f.y * k2f.y; d4[3] += q3f.x * k3f.x + q3f.y * k3f.y;
-        }
-        dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
-      }
-      mbar_arrive(q_free(st));
-      return CAP ? capped_log2(dot, a.sm_scale, a.cap, a.cap_method) : dot * csc;
-    };
 
-    uint4 krow[DH / 8], vrow[DH / 8];
     uint32_t kmask[4] = {0u, 0u, 0u, 0u};
     bool all_ok = false;
     int mask_li = -1;
     Tile cur, nxt;
-    float self_logit = 0.f;
-    if (w < G) {
-      cur = tile_of(w);
-      load_row(a.k, a.k_tok_stride, cur, cur.hk * a.k_head_stride, krow);
-      load_row(a.v, a.v_tok_stride, cur, cur.hk * a.v_head_stride, vrow);
-      self_logit = self_dot(w, cur, krow);
-    }
+    if (w < G) cur = tile_of(w);
     for (int g = w; g < G; g += 2) {
       const uint32_t ph = (uint32_t)((g >> 1) & 1);
+      const int st = g % PP_NQ;
+      const uint32_t stage = sQ + 3 * st * SLAB;
       const bool more = g + 2 < G;
-      if (more) {
-        nxt = tile_of(g + 2);
-        load_row(a.k, a.k_tok_stride, nxt, nxt.hk * a.k_head_stride, krow);       // krow of this tile went into self_logit already
-      }
+      if (more) nxt = tile_of(g + 2);
       if (cur.li != mask_li) {
         // validity of the item's history keys (the same for all of its tiles)
         const uint32_t word = __ballot_sync(0xffffffffu, cur.hseg == 1);
@@ -845,6 +863,19 @@ ranker_attention_pingpong_kernel(const __grid_constant__ CUtensorMap map_qh, con
 
       mbar_wait(s_full(w), ph, verr);
       tc_fence_after();
+      const bool is_cand = cur.cand && cur.seg == -1;
+      // the row's score against its own key: element r of row r of the scratch (this warp's 32 x 32 diagonal block)
+      float self_logit = 0.f;
+      if (cur.cand) {                                // uniform over the tile
+        float dv[32];
+        tmem_ld32(tmem + TM_D + lane_base + quad * 32, reinterpret_cast<uint32_t*>(dv));
+        tc_fence_before();
+        mbar_arrive(d_free);
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) dot = (lane == i) ? dv[i] : dot;
+        self_logit = CAP ? capped_log2(dot, a.sm_scale, a.cap, a.cap_method) : dot * csc;
+      }
       // one 64-key half of the S row, capped and masked, into registers
       auto load_s_half = [&](int c, float (&sv)[64]) {
         tmem_ld32_nowait(tmem + TM_S + w * 128 + lane_base + c * 64, reinterpret_cast<uint32_t*>(sv));
@@ -877,11 +908,10 @@ ranker_attention_pingpong_kernel(const __grid_constant__ CUtensorMap map_qh, con
         for (int k = 60; k < 64; ++k) bm = fmaxf(bm, sv[k]);
       }
       float m = bm * csc;
-      const bool is_cand = cur.cand && cur.seg == -1;
       if (is_cand) m = fmaxf(m, self_logit);           // the self key takes part in the row maximum right away
       const float mns = (m == -INFINITY) ? 0.f : m;
-      // pass 2: probabilities, row sum, P in bf16 into this warpgroup's operand buffer (its previous contents were
-      // consumed by the P V product this thread waited for at the end of its previous tile)
+      // pass 2: probabilities, row sum, P as bf16 pairs back into tensor memory: half c of the row (64 keys) lands in
+      // the 32 columns c * 32.. of the row's own S block - columns whose S values this thread has already consumed
       float l = 0.f;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -889,31 +919,34 @@ ranker_attention_pingpong_kernel(const __grid_constant__ CUtensorMap map_qh, con
         load_s_half(c, sv);
         const float2 c2 = make_float2(csc, csc), n2 = make_float2(-mns, -mns);
         float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+        uint32_t pw[32];
 #pragma unroll
         for (int k = 0; k < 64; k += 2) {            // packed fp32: two keys per instruction; masked keys: 2^-inf = 0
           const float2 e = __ffma2_rn(make_float2(sv[k], sv[k + 1]), c2, n2);
-          sv[k] = ex2f(e.x); sv[k + 1] = ex2f(e.y);
-          acc2[(k >> 1) & 1] = __fadd2_rn(acc2[(k >> 1) & 1], make_float2(sv[k], sv[k + 1]));
+          const float e0 = ex2f(e.x), e1 = ex2f(e.y);
+          acc2[(k >> 1) & 1] = __fadd2_rn(acc2[(k >> 1) & 1], make_float2(e0, e1));
+          pw[k >> 1] = pack_bf2(e0, e1);
         }
         l += (acc2[0].x + acc2[0].y) + (acc2[1].x + acc2[1].y);
-#pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {
-          uint4 o;
-          o.x = pack_bf2(sv[cc * 8 + 0], sv[cc * 8 + 1]); o.y = pack_bf2(sv[cc * 8 + 2], sv[cc * 8 + 3]);
-          o.z = pack_bf2(sv[cc * 8 + 4], sv[cc * 8 + 5]); o.w = pack_bf2(sv[cc * 8 + 6], sv[cc * 8 + 7]);
-          st_shared_16(myP + c * SLAB + r * 128 + ((uint32_t)(cc ^ sw) << 4), o);
-        }
+        tmem_st32_nowait(tmem + TM_S + w * 128 + lane_base + c * 32, pw);
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       tc_fence_before();
       mbar_arrive(p_ready(w));
 
-      // while the P V product runs: the self logit of this warpgroup's next tile
-      float self_next = 0.f;
-      if (more) self_next = self_dot(g + 2, nxt, krow);
-
+      // while the P V product runs: the row's own value row out of the stage (128-byte swizzle: chunk c of row r sits
+      // at chunk c ^ (r & 7))
+      uint4 vrow[DH / 8];
       float p_self = 0.f;
-      if (is_cand) { p_self = ex2f(self_logit - mns); l += p_self; }
+      if (is_cand) {
+        mbar_wait(q_full(st), (uint32_t)((g / PP_NQ) & 1), verr);   // long complete (S came from this stage): orders the reads below behind the bulk copies
+#pragma unroll
+        for (int c = 0; c < DH / 8; ++c)
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(vrow[c].x), "=r"(vrow[c].y), "=r"(vrow[c].z), "=r"(vrow[c].w)
+                       : "r"(stage + 2 * SLAB + r * 128 + ((uint32_t)(c ^ sw) << 4)));
+        p_self = ex2f(self_logit - mns);
+        l += p_self;
+      }
       const float pr = round_bf(p_self);
       mbar_wait(o_done(w), ph, verr);
       tc_fence_after();
@@ -923,31 +956,23 @@ ranker_attention_pingpong_kernel(const __grid_constant__ CUtensorMap map_qh, con
       tmem_ld_wait();
       tc_fence_before();
       const float inv = (l == 0.f || cur.seg == 0) ? 0.f : 1.0f / l;   // padded rows, rows with no allowed key -> zeros
-      if (cur.tok >= 0) {
-        bf16* orow = a.out + (cur.tok * a.Hq + cur.h) * DH;
+      // the output row goes into the stage's Q slab (same swizzle), from where the store warp sends the tile out; rows
+      // past the end of the block are clipped by the copy
 #pragma unroll
-        for (int c2 = 0; c2 < DH / 16; ++c2) {
-          uint32_t wv[8];
-#pragma unroll
-          for (int hc = 0; hc < 2; ++hc) {
-            const int c = c2 * 2 + hc;
-            if (is_cand) {
-              const float2 v0 = unpack_bf2(vrow[c].x), v1 = unpack_bf2(vrow[c].y), v2 = unpack_bf2(vrow[c].z), v3 = unpack_bf2(vrow[c].w);
-              o[c * 8 + 0] += pr * v0.x; o[c * 8 + 1] += pr * v0.y; o[c * 8 + 2] += pr * v1.x; o[c * 8 + 3] += pr * v1.y;
-              o[c * 8 + 4] += pr * v2.x; o[c * 8 + 5] += pr * v2.y; o[c * 8 + 6] += pr * v3.x; o[c * 8 + 7] += pr * v3.y;
-            }
-            wv[hc * 4 + 0] = pack_bf2(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv); wv[hc * 4 + 1] = pack_bf2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
-            wv[hc * 4 + 2] = pack_bf2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv); wv[hc * 4 + 3] = pack_bf2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
-          }
-          asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
-                       ::"l"(orow + c2 * 16), "r"(wv[0]), "r"(wv[1]), "r"(wv[2]), "r"(wv[3]), "r"(wv[4]), "r"(wv[5]), "r"(wv[6]), "r"(wv[7]) : "memory");
+      for (int c = 0; c < DH / 8; ++c) {
+        if (is_cand) {
+          const float2 v0 = unpack_bf2(vrow[c].x), v1 = unpack_bf2(vrow[c].y), v2 = unpack_bf2(vrow[c].z), v3 = unpack_bf2(vrow[c].w);
+          o[c * 8 + 0] += pr * v0.x; o[c * 8 + 1] += pr * v0.y; o[c * 8 + 2] += pr * v1.x; o[c * 8 + 3] += pr * v1.y;
+          o[c * 8 + 4] += pr * v2.x; o[c * 8 + 5] += pr * v2.y; o[c * 8 + 6] += pr * v3.x; o[c * 8 + 7] += pr * v3.y;
         }
+        uint4 ov;
+        ov.x = pack_bf2(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv); ov.y = pack_bf2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
+        ov.z = pack_bf2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv); ov.w = pack_bf2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
+        st_shared_16(stage + r * 128 + ((uint32_t)(c ^ sw) << 4), ov);
       }
-      if (more) {
-        load_row(a.v, a.v_tok_stride, nxt, nxt.hk * a.v_head_stride, vrow);         // a whole tile to arrive
-        cur = nxt;
-        self_logit = self_next;
-      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(o_staged(w));
+      if (more) cur = nxt;
     }
   }
 
@@ -981,32 +1006,9 @@ phx_status cached_map3d(const CUtensorMap** out, const bf16* ptr, long long cols
   return PHX_OK;
 }
 
-struct MapKey7 {
-  const void* p; long long cols, d1, d2, s1, s2; int box;
-  bool operator<(const MapKey7& o) const { return std::tie(p, cols, d1, d2, s1, s2, box) < std::tie(o.p, o.cols, o.d1, o.d2, o.s1, o.s2, o.box); }
-};
-std::map<MapKey7, CUtensorMap> g_map_cache7;
-
-// 3-D map with free strides: [d2 requests][d1 rows][cols], byte strides s1 (rows) and s2 (requests)
-phx_status cached_map3d_strided(const CUtensorMap** out, const bf16* ptr, long long cols, long long d1, long long d2,
-                                long long s1_bytes, long long s2_bytes, int box_rows, std::string& err) {
-  std::lock_guard<std::mutex> lk(g_map_mu);
-  MapKey7 key{ptr, cols, d1, d2, s1_bytes, s2_bytes, box_rows};
-  auto it = g_map_cache7.find(key);
-  if (it == g_map_cache7.end()) {
-    if (g_map_cache7.size() > 4096) g_map_cache7.clear();
-    CUtensorMap m;
-    phx_status s = make_map3d(&m, ptr, cols, d1, d2, s1_bytes, s2_bytes, box_rows, err);
-    if (s) return s;
-    it = g_map_cache7.emplace(key, m).first;
-  }
-  *out = &it->second;
-  return PHX_OK;
-}
-
 template <bool CAP>
 phx_status launch_pingpong(const AttnArgs& a, int* err_flag, int num_sms, cudaStream_t stream, std::string& err) {
-  const size_t smem = (size_t)(4 + PP_NQ + 4) * SLAB + 64 + 160 + 1024;
+  const size_t smem = (size_t)(4 + 3 * PP_NQ) * SLAB + 64 + 192 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
     PHX_CUDA_TRY(cudaFuncSetAttribute(ranker_attention_pingpong_kernel<CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), err);
@@ -1015,8 +1017,7 @@ phx_status launch_pingpong(const AttnArgs& a, int* err_flag, int num_sms, cudaSt
   const int n_hist = a.hist_len < a.T ? a.hist_len : a.T;
   const int n_cand = a.T - n_hist;
   PingArgs p;
-  p.k = a.k; p.v = a.v; p.out = a.out; p.seg = a.seg;
-  p.k_tok_stride = a.k_tok_stride; p.v_tok_stride = a.v_tok_stride;
+  p.seg = a.seg;
   p.q_head_stride = a.q_head_stride; p.k_head_stride = a.k_head_stride; p.v_head_stride = a.v_head_stride;
   p.Hq = a.Hq; p.Hkv = a.Hkv; p.n_hist = n_hist; p.n_cand = n_cand; p.n_items = a.B * a.Hq;
   p.hist_row0 = token_row(a.split, a.B, a.hist_len, a.T, 0, 0);
@@ -1026,17 +1027,49 @@ phx_status launch_pingpong(const AttnArgs& a, int* err_flag, int num_sms, cudaSt
   p.skip_hist = a.q_start > 0 ? 1 : 0;
   p.sm_scale = a.sm_scale; p.cap = a.cap; p.cap_method = a.cap_method; p.err_flag = err_flag;
   if (p.skip_hist && n_cand == 0) return PHX_OK;
-  const CUtensorMap *mqh, *mqc, *mkh, *mvh;
-  phx_status s;
-  const long long qcols = (long long)(a.Hq - 1) * a.q_head_stride + 64, kcols = (long long)(a.Hkv - 1) * a.k_head_stride + 64,
-                  vcols = (long long)(a.Hkv - 1) * a.v_head_stride + 64;
-  if ((s = cached_map3d_strided(&mqh, a.q + p.hist_row0 * a.q_tok_stride, qcols, n_hist, a.B, a.q_tok_stride * 2, p.hist_req_rows * a.q_tok_stride * 2, QT, err))) return s;
-  if ((s = cached_map3d_strided(&mkh, a.k + p.hist_row0 * a.k_tok_stride, kcols, n_hist, a.B, a.k_tok_stride * 2, p.hist_req_rows * a.k_tok_stride * 2, 128, err))) return s;
-  if ((s = cached_map3d_strided(&mvh, a.v + p.hist_row0 * a.v_tok_stride, vcols, n_hist, a.B, a.v_tok_stride * 2, p.hist_req_rows * a.v_tok_stride * 2, 128, err))) return s;
-  mqc = mqh;
-  if (n_cand > 0 && (s = cached_map3d_strided(&mqc, a.q + p.cand_row0 * a.q_tok_stride, qcols, n_cand, a.B, a.q_tok_stride * 2, p.cand_req_rows * a.q_tok_stride * 2, QT, err))) return s;
+  // eight maps per launch: the engine calls with the same buffers every layer and every step, so they are cached whole
+  struct Key {
+    const void *q, *k, *v, *o; long long qs, ks, vs, h0, hr, c0, cr; int qh, kh, vh, Hq, Hkv, nh, nc, B;
+    bool operator<(const Key& x) const {
+      return std::tie(q, k, v, o, qs, ks, vs, h0, hr, c0, cr, qh, kh, vh, Hq, Hkv, nh, nc, B) <
+             std::tie(x.q, x.k, x.v, x.o, x.qs, x.ks, x.vs, x.h0, x.hr, x.c0, x.cr, x.qh, x.kh, x.vh, x.Hq, x.Hkv, x.nh, x.nc, x.B);
+    }
+  };
+  static std::map<Key, PingMaps> cache;
+  static std::mutex mu;
+  const Key key{a.q, a.k, a.v, a.out, a.q_tok_stride, a.k_tok_stride, a.v_tok_stride, p.hist_row0, p.hist_req_rows, p.cand_row0,
+                p.cand_req_rows, a.q_head_stride, a.k_head_stride, a.v_head_stride, a.Hq, a.Hkv, n_hist, n_cand, a.B};
+  PingMaps pm;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+      if (cache.size() > 1024) cache.clear();
+      PingMaps m;
+      phx_status s;
+      const long long qcols = (long long)(a.Hq - 1) * a.q_head_stride + 64, kcols = (long long)(a.Hkv - 1) * a.k_head_stride + 64,
+                      vcols = (long long)(a.Hkv - 1) * a.v_head_stride + 64, ocols = (long long)a.Hq * 64;
+      const long long ostr = ocols;   // output rows are dense: [token][head][64]
+      auto mk = [&](CUtensorMap* dst, const bf16* ptr, long long cols, long long rows, long long tok_stride, long long req_rows) {
+        return sm100::make_map3d(dst, ptr, cols, rows, a.B, tok_stride * 2, req_rows * tok_stride * 2, 128, err);
+      };
+      if ((s = mk(&m.qh, a.q + p.hist_row0 * a.q_tok_stride, qcols, n_hist, a.q_tok_stride, p.hist_req_rows))) return s;
+      if ((s = mk(&m.kh, a.k + p.hist_row0 * a.k_tok_stride, kcols, n_hist, a.k_tok_stride, p.hist_req_rows))) return s;
+      if ((s = mk(&m.vh, a.v + p.hist_row0 * a.v_tok_stride, vcols, n_hist, a.v_tok_stride, p.hist_req_rows))) return s;
+      if ((s = mk(&m.oh, a.out + p.hist_row0 * ostr, ocols, n_hist, ostr, p.hist_req_rows))) return s;
+      m.qc = m.qh; m.kc = m.kh; m.vc = m.vh; m.oc = m.oh;
+      if (n_cand > 0) {
+        if ((s = mk(&m.qc, a.q + p.cand_row0 * a.q_tok_stride, qcols, n_cand, a.q_tok_stride, p.cand_req_rows))) return s;
+        if ((s = mk(&m.kc, a.k + p.cand_row0 * a.k_tok_stride, kcols, n_cand, a.k_tok_stride, p.cand_req_rows))) return s;
+        if ((s = mk(&m.vc, a.v + p.cand_row0 * a.v_tok_stride, vcols, n_cand, a.v_tok_stride, p.cand_req_rows))) return s;
+        if ((s = mk(&m.oc, a.out + p.cand_row0 * ostr, ocols, n_cand, ostr, p.cand_req_rows))) return s;
+      }
+      it = cache.emplace(key, m).first;
+    }
+    pm = it->second;
+  }
   const int grid = p.n_items < num_sms ? p.n_items : num_sms;
-  ranker_attention_pingpong_kernel<CAP><<<grid, PP_THREADS, smem, stream>>>(*mqh, *mqc, *mkh, *mvh, p);
+  ranker_attention_pingpong_kernel<CAP><<<grid, PP_THREADS, smem, stream>>>(pm, p);
   PHX_CUDA_TRY(cudaGetLastError(), err);
   return PHX_OK;
 }
