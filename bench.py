@@ -149,20 +149,26 @@ def sharded_subrecords(args, rank, world, local_rank, steps, which=("gather", "r
     cm = pc.Communicator(box[0], rank, world, local_rank)
     out = {}
 
-    def timed(fn, iters, warm=2):
-        """ms per call: events on torch's current stream around `iters` calls, max over ranks."""
+    per_call = {}
+
+    def timed(fn, iters, warm=2, name=None):
+        """ms per call: events on torch's current stream around `iters` calls, max over ranks.  With `name`, the
+        duration of every single call (max over ranks) is kept in per_call[name] as well."""
         for _ in range(warm):
             fn()
         torch.cuda.synchronize()
         dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(iters):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
+        ev[0].record()
+        for i in range(iters):
             fn()
-        e1.record()
+            ev[i + 1].record()
         torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device=dev)
+        t = torch.tensor([ev[0].elapsed_time(ev[iters]) / iters] + [ev[i].elapsed_time(ev[i + 1]) for i in range(iters)],
+                         dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if name:
+            per_call[name] = [round(float(x), 3) for x in t[1:]]
         return float(t[0])
 
     def all_true(flag):
@@ -190,8 +196,10 @@ def sharded_subrecords(args, rank, world, local_rank, steps, which=("gather", "r
         def one():
             cm.gather_sum(eng, 1 + it[0] % 2, sets[it[0] % 3], n, res, st)
             it[0] += 1
-        ms = timed(one, 10)
+        ms = timed(one, 10, name="gather")
         phases = cm.gather_phase_ms()
+        ph_all = [None] * world
+        dist.all_gather_object(ph_all, [round(float(x), 3) for x in phases])
         last = it[0] - 1
         whole = px.PhoenixEngine(px.PhoenixConfig(**gcfg), local_rank)
         whole.table_fill_synthetic(7, 1.0 / math.sqrt(width))
@@ -212,7 +220,8 @@ def sharded_subrecords(args, rank, world, local_rank, steps, which=("gather", "r
             one_gpu_share_ms=float(np.median(local_ms)),
             note="one_gpu_share_ms = this rank's ids alone on an unsharded 64 GiB table on the same GPU (no exchange)",
             phase_ms_rank0=dict(zip(["hash_dedup_bucket", "counts_exchange", "row_numbers", "owner_gathers", "copies_tail", "fence", "sum"],
-                                    [round(x, 3) for x in phases])))
+                                    [round(x, 3) for x in phases])),
+            ms_per_call=per_call["gather"], phase_ms_last_call_by_rank=ph_all)
     except Exception as e:  # a sub-record must not take the headline line down
         out["sharded_gather"] = dict(error=repr(e))
     # ---- sharded retrieval ----------------------------------------------------------------------------------------

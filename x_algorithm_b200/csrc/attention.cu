@@ -672,10 +672,9 @@ phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::
     const char* force = getenv("PHX_ATTN");
     const bool legacy = force && strcmp(force, "mma") == 0;
     const bool forced_tc = force && (strcmp(force, "tcgen05") == 0 || strcmp(force, "resident") == 0);
-    // Measured on B200: with a history of one key block (<= 128 keys at head dim 64) a tile's tensor work is ~0.1 us
-    // and the tcgen05 pipeline's hand-offs between its warps dominate, so the mma.sync kernel (16 independent warps
-    // per SM) is faster there (2.4 vs 2.6-2.9 ms per step at B=256, S=128, C=512); longer histories and head dim 128
-    // go to the tcgen05 kernel (2.0 vs 4.6 ms at 1024 + 1024 tokens, 16 heads x 128).
+    // Histories longer than one key block (128 keys at head dim 64) and head dim 128 go to the streaming tcgen05
+    // kernel (measured on B200: 1.5 vs 4.6 ms for the mma.sync kernel at 1024 + 1024 tokens, 16 heads x 128); a
+    // history of one key block is the resident-history kernels' case further down.
     const int n_hist = a.hist_len < a.T ? a.hist_len : a.T;
     const bool prefer_tc = forced_tc || a.dh == 128 || n_hist > 128;
     const bool plain = !a.split && a.q_start == 0 && !a.pack.hist_off;   // the tcgen05 kernel's tensor maps assume [B, T] token rows
@@ -683,13 +682,15 @@ phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::
   }
   {
     // Head dim 64 with a history of at most 128 keys: the persistent tcgen05 kernel with the history resident and two
-    // softmax warpgroups is selected with PHX_ATTN=pingpong.  Measured on B200 at the ranking benchmark's shape it
-    // takes 2.5 ms per step against 2.1 ms for the mma.sync resident-history kernel below (its 8 softmax warps per
-    // SM leave the tensor-memory, shared-memory and global round trips of a tile exposed, where the mma.sync kernel
-    // has 16 independent warps), so the default stays with the latter.
+    // softmax warpgroups, once there is an item (batch, head) for every SM.  Measured on B200 at the ranking
+    // benchmark's shape (B=256, S=128, C=512, 8 heads): 0.154 ms per layer against 0.216 ms for the mma.sync
+    // resident-history kernel below (1.48 against 2.02 ms per step inside the forward), and 0.053 against 0.069 ms at
+    // B=64; every byte it touches moves by bulk copies.  PHX_ATTN=strip keeps the mma.sync kernel, PHX_ATTN=pingpong
+    // takes this one at any batch size.
     const char* force = getenv("PHX_ATTN");
     const bool forced = force && strcmp(force, "pingpong") == 0;
-    if (forced && a.err_flag && ranker_attention_pingpong_supported(a))
+    const bool fills = !force && (long long)a.B * a.Hq >= 148;
+    if ((forced || fills) && a.err_flag && ranker_attention_pingpong_supported(a))
       return ranker_attention_pingpong_launch(a, a.err_flag, stream, err);
   }
   const bool cap = a.cap_method != 0 && a.cap > 0.f;
