@@ -191,12 +191,16 @@ def sharded_subrecords(args, rank, world, local_rank, steps, which=("gather", "r
                                  [rank * n:(rank + 1) * n].copy()).to(dev) for i in range(3)]
         res = torch.empty((n, width), dtype=torch.int16, device=dev)
         cm.gather_setup(eng, n, recv_factor=3.0)
+        # a step's ids belong to the four features of the unified table in equal parts (the benchmark's "8 tables" are
+        # regions of one row-sharded table here): lookups spread over every shard, as a batch's features do
+        fams = [0, 1, 2, 3]
+        cnts = [n // 4] * 3 + [n - 3 * (n // 4)]
         it = [0]
 
         def one():
-            cm.gather_sum(eng, 1 + it[0] % 2, sets[it[0] % 3], n, res, st)
+            cm.gather_sum_multi(eng, fams, cnts, sets[it[0] % 3], res, st)
             it[0] += 1
-        ms = timed(one, 10, name="gather")
+        ms = timed(one, 10, warm=6, name="gather")   # the warm-up calls also let NCCL finish setting up its send / recv channels
         phases = cm.gather_phase_ms()
         ph_all = [None] * world
         dist.all_gather_object(ph_all, [round(float(x), 3) for x in phases])
@@ -204,12 +208,18 @@ def sharded_subrecords(args, rank, world, local_rank, steps, which=("gather", "r
         whole = px.PhoenixEngine(px.PhoenixConfig(**gcfg), local_rank)
         whole.table_fill_synthetic(7, 1.0 / math.sqrt(width))
         want = torch.empty_like(res)
-        whole.gather_sum_device(1 + last % 2, sets[last % 3], n, want)
-        whole.sync()
-        local_ms = []
-        for _ in range(5):
-            whole.gather_sum_device(1, sets[0], n, want); whole.sync(); local_ms.append(whole.last_device_ms())
-        whole.gather_sum_device(1 + last % 2, sets[last % 3], n, want); whole.sync()
+
+        def unsharded(ids_t, timed_ms=False):
+            at, tot = 0, 0.0
+            for f, c in zip(fams, cnts):
+                whole.gather_sum_device(f, ids_t[at:at + c], c, want[at:at + c])
+                if timed_ms:
+                    whole.sync(); tot += whole.last_device_ms()
+                at += c
+            return tot
+        unsharded(sets[0]); whole.sync()
+        local_ms = [unsharded(sets[0], True) for _ in range(5)]
+        unsharded(sets[last % 3]); whole.sync()
         ok = all_true(torch.equal(res, want))
         whole.close(); eng.close()
         per_id = hashes * width * 2 + width * 2 + 8

@@ -567,6 +567,13 @@ phx_status phx_retrieve_topk(phx_comm* comm, phx_corpus* shard, const float* use
 phx_status phx_gather_sharded_setup(phx_comm* comm, phx_engine* e, int64_t max_ids, double recv_factor);
 phx_status phx_gather_sum_sharded(phx_comm* comm, phx_engine* e, int32_t family, const int64_t* ids_dev, int64_t n,
                                   uint16_t* out_dev, void* stream);
+/* The same for ids of several features in one call: ids_dev holds nseg runs back to back, run i = seg_count[i] ids of
+ * hash family seg_family[i] (0 user, 1 item, 2 author, 3 ip; every family used must have the engine's item hash count).
+ * One exchange serves all runs, so lookups that spread over the table's regions - the reference gathers every
+ * feature of a batch in one row_emb call - load every owner alike; a single-family call sends all of its requests
+ * to the one or two ranks that hold that region.  out_dev: [sum of seg_count, emb_size] in id order. */
+phx_status phx_gather_sum_sharded_multi(phx_comm* comm, phx_engine* e, int32_t nseg, const int32_t* seg_family,
+                                        const int64_t* seg_count, const int64_t* ids_dev, uint16_t* out_dev, void* stream);
 phx_status phx_gather_sharded_phase_ms(phx_comm* comm, float* ms7);
 
 /* ---- serving shell: request queue and admission control -----------------------------------------------------------

@@ -62,7 +62,14 @@ def _rank_main(rank, world, id_bytes, out_q):
             out = torch.empty((N_IDS, W_EMB), dtype=torch.int16, device=dev)
             cm.gather_sum(eng, 1 + call, d_ids, N_IDS, out)
             torch.cuda.synchronize()
-            gathered.append((my, out))
+            gathered.append((my, out, [1 + call], [N_IDS]))
+        # a third call with runs of all four features in one exchange (one run empty)
+        fams, cnts = [3, 0, 2, 1, 2], [N_IDS // 4, N_IDS // 8, 0, N_IDS // 2, N_IDS - N_IDS // 4 - N_IDS // 8 - N_IDS // 2]
+        my = zipf_ids(N_IDS, np.random.Generator(np.random.PCG64(300 + rank)), 1.1)
+        out = torch.empty((N_IDS, W_EMB), dtype=torch.int16, device=dev)
+        cm.gather_sum_multi(eng, fams, cnts, torch.from_numpy(my).to(dev), out)
+        torch.cuda.synchronize()
+        gathered.append((my, out, fams, cnts))
         phases = cm.gather_phase_ms()
         ok, msg = True, ""
         # every rank checks its own answers against an unsharded shard / table on its own GPU
@@ -75,9 +82,13 @@ def _rank_main(rank, world, id_bytes, out_q):
             ok, msg = False, "sharded retrieval differs from the unsharded scan"
         full.close()
         whole = _engine(px, 1, 0, rank)
-        for call, (my, out) in enumerate(gathered):
+        for call, (my, out, fams, cnts) in enumerate(gathered):
             want = torch.empty_like(out)
-            whole.gather_sum_device(1 + call, torch.from_numpy(my).to(dev), N_IDS, want)
+            d_my, at = torch.from_numpy(my).to(dev), 0
+            for f, c in zip(fams, cnts):
+                if c:
+                    whole.gather_sum_device(f, d_my[at:at + c], c, want[at:at + c])
+                at += c
             whole.sync()
             if not torch.equal(out, want):
                 ok, msg = False, f"sharded gather-sum (call {call}) differs from the unsharded table"
@@ -133,6 +144,7 @@ def test_communicator_argument_checks():
     assert lib.phx_comm_create(idb, 0, 17, 0, C.byref(h)) == 1           # more ranks than shards the library supports
     assert lib.phx_retrieve_topk(None, None, None, 1, 1, None, None, None) == 1
     assert lib.phx_gather_sum_sharded(None, None, 0, None, 0, None, None) == 1
+    assert lib.phx_gather_sum_sharded_multi(None, None, 1, None, None, None, None, None) == 1
     assert lib.phx_gather_sharded_setup(None, None, 10, 2.0) == 1
     assert lib.phx_comm_barrier(None, None) == 1
     assert b"null" in lib.phx_global_error() or b"bad argument" in lib.phx_global_error()

@@ -181,6 +181,7 @@ SIGNATURES = {
     "phx_retrieve_topk": (C.c_int32, [_P, _P, _P, C.c_int32, C.c_int32, _P, _P, _P]),
     "phx_gather_sharded_setup": (C.c_int32, [_P, _P, C.c_int64, C.c_double]),
     "phx_gather_sum_sharded": (C.c_int32, [_P, _P, C.c_int32, _P, C.c_int64, _P, _P]),
+    "phx_gather_sum_sharded_multi": (C.c_int32, [_P, _P, C.c_int32, _P, _P, _P, _P, _P]),
     "phx_gather_sharded_phase_ms": (C.c_int32, [_P, C.POINTER(C.c_float)]),
     "phx_now_us": (C.c_uint64, []),
     "phx_queue_create": (C.c_int32, [C.c_int32, C.c_int32, C.c_uint64, C.c_uint64, C.POINTER(_P)]),

@@ -69,6 +69,16 @@ class Communicator:
         self._check(lib.phx_gather_sum_sharded(self._h, engine._h, family, int(ids.data_ptr()), n, int(out.data_ptr()),
                                                stream or None))
 
+    def gather_sum_multi(self, engine, families, counts, ids, out, stream: int = 0):
+        """The same for several features in one exchange: ids holds the runs back to back, run i = counts[i] ids of hash
+        family families[i] (0 user, 1 item, 2 author, 3 ip).  Lookups that spread over the table's regions load every
+        owner alike."""
+        m = len(families)
+        fam = (C.c_int32 * m)(*[int(f) for f in families])
+        cnt = (C.c_int64 * m)(*[int(c) for c in counts])
+        self._check(lib.phx_gather_sum_sharded_multi(self._h, engine._h, m, fam, cnt, int(ids.data_ptr()), int(out.data_ptr()),
+                                                     stream or None))
+
     def gather_phase_ms(self) -> List[float]:
         buf = (C.c_float * 7)()
         self._check(lib.phx_gather_sharded_phase_ms(self._h, buf))

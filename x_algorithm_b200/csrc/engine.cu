@@ -1926,7 +1926,22 @@ phx_status phx_gather_sharded_setup(phx_comm* cm, phx_engine* e, int64_t max_ids
 
 phx_status phx_gather_sum_sharded(phx_comm* cm, phx_engine* e, int32_t family, const int64_t* ids_dev, int64_t n, uint16_t* out_dev,
                                   void* stream) {
-  if (!cm || !e || family < 0 || family > 3 || n < 0 || (n > 0 && (!ids_dev || !out_dev))) { set_global_error("phx_gather_sum_sharded: bad argument"); return PHX_E_ARG; }
+  return phx_gather_sum_sharded_multi(cm, e, 1, &family, &n, ids_dev, out_dev, stream);
+}
+
+phx_status phx_gather_sum_sharded_multi(phx_comm* cm, phx_engine* e, int32_t nseg, const int32_t* seg_family, const int64_t* seg_count,
+                                        const int64_t* ids_dev, uint16_t* out_dev, void* stream) {
+  if (!cm || !e || nseg < 1 || nseg > 16 || !seg_family || !seg_count) { set_global_error("phx_gather_sum_sharded: bad argument"); return PHX_E_ARG; }
+  int64_t n = 0;
+  const phx_hash_family* fams[4] = {&e->cfg.user, &e->cfg.item, &e->cfg.author, &e->cfg.ip};
+  for (int i = 0; i < nseg; ++i) {
+    if (seg_family[i] < 0 || seg_family[i] > 3 || seg_count[i] < 0) { set_global_error("phx_gather_sum_sharded: bad family or count"); return PHX_E_ARG; }
+    if (seg_count[i] > 0 && fams[seg_family[i]]->num_hashes != e->cfg.item.num_hashes) {
+      set_global_error("phx_gather_sum_sharded: every family of a call must have the engine's item hash count"); return PHX_E_ARG;
+    }
+    n += seg_count[i];
+  }
+  if (n > 0 && (!ids_dev || !out_dev)) { set_global_error("phx_gather_sum_sharded: bad argument"); return PHX_E_ARG; }
   GatherWs* w = static_cast<GatherWs*>(cm->gather_ws);
   if (!w) { cm->err = "phx_gather_sum_sharded: call phx_gather_sharded_setup first"; return PHX_E_STATE; }
   const int W = w->W, H = w->H, rank = cm->rank;
@@ -1936,12 +1951,20 @@ phx_status phx_gather_sum_sharded(phx_comm* cm, phx_engine* e, int32_t family, c
   cudaStream_t st = (cudaStream_t)stream;
   long long off[5];
   region_offsets(e->cfg, &off[0], &off[1], &off[2], &off[3], &off[4]);
-  const phx_hash_family* fams[4] = {&e->cfg.user, &e->cfg.item, &e->cfg.author, &e->cfg.ip};
   phx_status s;
   auto mark = [&](int i) { cudaEventRecord(w->ev[i], st); };
   mark(0);
-  // requester: ids -> rows -> distinct rows -> grouped by owner; nothing here waits on the host
-  if ((s = hash_ids_launch(to_dev(*fams[family], (int)off[family]), (const long long*)ids_dev, n, w->rows, st, cm->err))) return s;
+  // requester: ids -> rows (run by run, each with its family's constants and region) -> distinct rows -> grouped by
+  // owner; nothing here waits on the host
+  {
+    int64_t at = 0;
+    for (int i = 0; i < nseg; ++i) {
+      const int f = seg_family[i];
+      if (seg_count[i] > 0 &&
+          (s = hash_ids_launch(to_dev(*fams[f], (int)off[f]), (const long long*)ids_dev + at, seg_count[i], w->rows + at * H, st, cm->err))) return s;
+      at += seg_count[i];
+    }
+  }
   if ((s = phx_shard_dedup(w->rows, nreq, (uint64_t*)w->table, w->table_slots, w->slot, w->urows, w->nu, st))) { cm->err = phx_global_error(); return s; }
   if ((s = shard_bucket_launch(w->urows, nreq, w->nu, w->shard_rows, W, w->counts, w->cursor, w->send_rows, w->upos, st))) { cm->err = phx_global_error(); return s; }
   if ((s = phx_shard_dedup_expand(w->slot, (const uint64_t*)w->table, w->upos, nreq, w->pos, st))) { cm->err = phx_global_error(); return s; }
