@@ -669,6 +669,27 @@ __device__ __forceinline__ void tmem_st32_nowait(uint32_t taddr, const uint32_t*
       : "memory");
 }
 
+// 16 registers per thread -> 32 lanes x 16 columns
+__device__ __forceinline__ void tmem_st16_nowait(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// Wait for the tensor-memory loads in flight.  The 32 registers of the load that is about to be used are operands of
+// the statement, so that no use of them can be scheduled in front of it (another load may have been issued since and
+// other work done in between: the wait is the only thing that orders the registers' arrival).
+__device__ __forceinline__ void tmem_ld_wait_on(float (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+f"(r[0]), "+f"(r[1]), "+f"(r[2]), "+f"(r[3]), "+f"(r[4]), "+f"(r[5]), "+f"(r[6]), "+f"(r[7]),
+                 "+f"(r[8]), "+f"(r[9]), "+f"(r[10]), "+f"(r[11]), "+f"(r[12]), "+f"(r[13]), "+f"(r[14]), "+f"(r[15]),
+                 "+f"(r[16]), "+f"(r[17]), "+f"(r[18]), "+f"(r[19]), "+f"(r[20]), "+f"(r[21]), "+f"(r[22]), "+f"(r[23]),
+                 "+f"(r[24]), "+f"(r[25]), "+f"(r[26]), "+f"(r[27]), "+f"(r[28]), "+f"(r[29]), "+f"(r[30]), "+f"(r[31])
+               :: "memory");
+}
+
 template <bool CAP>
 __global__ void __launch_bounds__(PP_THREADS, 1)
 ranker_attention_pingpong_kernel(const __grid_constant__ PingMaps maps, PingArgs a) {
@@ -821,34 +842,39 @@ ranker_attention_pingpong_kernel(const __grid_constant__ PingMaps maps, PingArgs
     const float csc = CAP ? 1.0f : a.sm_scale * 1.4426950408889634f;
     auto wg_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(1 + w) : "memory"); };
 
-    // what a thread needs to know about its row of a tile; the two segment words are loaded a tile ahead of their use
-    struct Tile { int b, li, seg, hseg; bool cand; };
-    auto tile_of = [&](int g) {
+    // what a thread needs to know about its row of a tile; the two segment words are loaded a tile ahead of their use.
+    // (li, ti) = item and tile inside the item, advanced two tiles at a time (no division per tile)
+    struct Tile { int li, ti, seg, hseg; bool cand; };
+    auto tile_at = [&](int li, int ti) {
       Tile t;
-      t.li = g / nt;
-      const int ti = g - t.li * nt;
-      const int it = (int)blockIdx.x + t.li * (int)gridDim.x;
-      t.b = it / a.Hq;
+      t.li = li; t.ti = ti;
+      const int it = (int)blockIdx.x + li * (int)gridDim.x;
+      const int b = it / a.Hq;
       t.cand = ti >= n_htiles;
       const int p = (t.cand ? (ti - n_htiles) : ti) * QT + r;                        // position inside the block
       const bool in = p < (t.cand ? a.n_cand : a.n_hist);
-      const long long tok = t.cand ? a.cand_row0 + (long long)t.b * a.cand_req_rows + p : a.hist_row0 + (long long)t.b * a.hist_req_rows + p;
+      const long long tok = t.cand ? a.cand_row0 + (long long)b * a.cand_req_rows + p : a.hist_row0 + (long long)b * a.hist_req_rows + p;
       t.seg = in ? a.seg[tok] : 0;
-      t.hseg = (r < a.n_hist) ? a.seg[a.hist_row0 + (long long)t.b * a.hist_req_rows + r] : 0;   // history key r of the item
+      t.hseg = (r < a.n_hist) ? a.seg[a.hist_row0 + (long long)b * a.hist_req_rows + r] : 0;   // history key r of the item
       return t;
+    };
+    auto tile_after = [&](const Tile& c) {         // two tiles further on
+      int li = c.li, ti = c.ti + 2;
+      while (ti >= nt) { ti -= nt; ++li; }
+      return tile_at(li, ti);
     };
 
     uint32_t kmask[4] = {0u, 0u, 0u, 0u};
     bool all_ok = false;
     int mask_li = -1;
     Tile cur, nxt;
-    if (w < G) cur = tile_of(w);
+    if (w < G) cur = tile_at(w / nt, w % nt);
     for (int g = w; g < G; g += 2) {
       const uint32_t ph = (uint32_t)((g >> 1) & 1);
       const int st = g % PP_NQ;
       const uint32_t stage = sQ + 3 * st * SLAB;
       const bool more = g + 2 < G;
-      if (more) nxt = tile_of(g + 2);
+      if (more) nxt = tile_after(cur);
       if (cur.li != mask_li) {
         // validity of the item's history keys (the same for all of its tiles)
         const uint32_t word = __ballot_sync(0xffffffffu, cur.hseg == 1);
@@ -876,59 +902,81 @@ ranker_attention_pingpong_kernel(const __grid_constant__ PingMaps maps, PingArgs
         for (int i = 0; i < 32; ++i) dot = (lane == i) ? dv[i] : dot;
         self_logit = CAP ? capped_log2(dot, a.sm_scale, a.cap, a.cap_method) : dot * csc;
       }
-      // one 64-key half of the S row, capped and masked, into registers
-      auto load_s_half = [&](int c, float (&sv)[64]) {
-        tmem_ld32_nowait(tmem + TM_S + w * 128 + lane_base + c * 64, reinterpret_cast<uint32_t*>(sv));
-        tmem_ld32_nowait(tmem + TM_S + w * 128 + lane_base + c * 64 + 32, reinterpret_cast<uint32_t*>(sv) + 32);
-        tmem_ld_wait();
+      // The 128-key S row in four chunks of 32 columns, two register buffers: the load of the next chunk is in flight
+      // while the current one is worked on.  Two passes (row maximum, then probabilities), each a rolled loop over
+      // two pairs of chunks so that the code of a pass stays small.
+      const uint32_t s_base = tmem + TM_S + w * 128 + lane_base;
+      float sa[32], sb[32];
+      auto fix = [&](float (&sv)[32], int c) {       // logit cap and key validity of chunk c
         if (CAP) {
 #pragma unroll
-          for (int k = 0; k < 64; ++k) sv[k] = capped_log2(sv[k], a.sm_scale, a.cap, a.cap_method);
+          for (int k = 0; k < 32; ++k) sv[k] = capped_log2(sv[k], a.sm_scale, a.cap, a.cap_method);
         }
         if (!all_ok) {
+          const uint32_t km = c == 0 ? kmask[0] : c == 1 ? kmask[1] : c == 2 ? kmask[2] : kmask[3];
 #pragma unroll
-          for (int k = 0; k < 64; ++k)
-            if (!((kmask[c * 2 + (k >> 5)] >> (k & 31)) & 1u)) sv[k] = -INFINITY;
+          for (int k = 0; k < 32; ++k)
+            if (!((km >> k) & 1u)) sv[k] = -INFINITY;
         }
       };
-      // pass 1: the row maximum
-      float bm = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        float sv[64];
-        load_s_half(c, sv);
+      auto chunk_max = [&](const float (&sv)[32]) {
         float b4[4] = {sv[0], sv[1], sv[2], sv[3]};
 #pragma unroll
-        for (int k = 4; k + 7 < 64; k += 8) {
+        for (int k = 4; k + 7 < 32; k += 8) {
           b4[0] = max3f(b4[0], sv[k], sv[k + 1]); b4[1] = max3f(b4[1], sv[k + 2], sv[k + 3]);
           b4[2] = max3f(b4[2], sv[k + 4], sv[k + 5]); b4[3] = max3f(b4[3], sv[k + 6], sv[k + 7]);
         }
-        bm = fmaxf(bm, fmaxf(max3f(b4[0], b4[1], b4[2]), b4[3]));
-#pragma unroll
-        for (int k = 60; k < 64; ++k) bm = fmaxf(bm, sv[k]);
+        b4[0] = max3f(b4[0], sv[28], sv[29]); b4[1] = max3f(b4[1], sv[30], sv[31]);
+        return fmaxf(max3f(b4[0], b4[1], b4[2]), b4[3]);
+      };
+      // pass 1: the row maximum
+      float bm = -INFINITY;
+      tmem_ld32_nowait(s_base, reinterpret_cast<uint32_t*>(sa));
+      tmem_ld_wait_on(sa);
+#pragma unroll 1
+      for (int cp = 0; cp < 2; ++cp) {
+        tmem_ld32_nowait(s_base + (2 * cp + 1) * 32, reinterpret_cast<uint32_t*>(sb));
+        fix(sa, 2 * cp);
+        bm = fmaxf(bm, chunk_max(sa));
+        tmem_ld_wait_on(sb);
+        if (cp == 0) tmem_ld32_nowait(s_base + 64, reinterpret_cast<uint32_t*>(sa));
+        fix(sb, 2 * cp + 1);
+        bm = fmaxf(bm, chunk_max(sb));
+        if (cp == 0) tmem_ld_wait_on(sa);
       }
       float m = bm * csc;
       if (is_cand) m = fmaxf(m, self_logit);           // the self key takes part in the row maximum right away
       const float mns = (m == -INFINITY) ? 0.f : m;
-      // pass 2: probabilities, row sum, P as bf16 pairs back into tensor memory: half c of the row (64 keys) lands in
-      // the 32 columns c * 32.. of the row's own S block - columns whose S values this thread has already consumed
+      // pass 2: probabilities, row sum, P as bf16 pairs back into tensor memory: chunk c of the row (32 keys) lands in
+      // the 16 columns c * 16.. of the row's own S block - columns whose S values this thread has already in registers
+      // or consumed (the chunk in flight lies further right)
       float l = 0.f;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        float sv[64];
-        load_s_half(c, sv);
-        const float2 c2 = make_float2(csc, csc), n2 = make_float2(-mns, -mns);
+      const float2 c2 = make_float2(csc, csc), n2 = make_float2(-mns, -mns);
+      auto exp_chunk = [&](float (&sv)[32], int c) {
         float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-        uint32_t pw[32];
+        uint32_t pw[16];
 #pragma unroll
-        for (int k = 0; k < 64; k += 2) {            // packed fp32: two keys per instruction; masked keys: 2^-inf = 0
+        for (int k = 0; k < 32; k += 2) {            // packed fp32: two keys per instruction; masked keys: 2^-inf = 0
           const float2 e = __ffma2_rn(make_float2(sv[k], sv[k + 1]), c2, n2);
           const float e0 = ex2f(e.x), e1 = ex2f(e.y);
           acc2[(k >> 1) & 1] = __fadd2_rn(acc2[(k >> 1) & 1], make_float2(e0, e1));
           pw[k >> 1] = pack_bf2(e0, e1);
         }
         l += (acc2[0].x + acc2[0].y) + (acc2[1].x + acc2[1].y);
-        tmem_st32_nowait(tmem + TM_S + w * 128 + lane_base + c * 32, pw);
+        tmem_st16_nowait(s_base + c * 16, pw);
+      };
+      tmem_ld32_nowait(s_base, reinterpret_cast<uint32_t*>(sa));
+      tmem_ld_wait_on(sa);
+#pragma unroll 1
+      for (int cp = 0; cp < 2; ++cp) {
+        tmem_ld32_nowait(s_base + (2 * cp + 1) * 32, reinterpret_cast<uint32_t*>(sb));
+        fix(sa, 2 * cp);
+        exp_chunk(sa, 2 * cp);
+        tmem_ld_wait_on(sb);
+        if (cp == 0) tmem_ld32_nowait(s_base + 64, reinterpret_cast<uint32_t*>(sa));
+        fix(sb, 2 * cp + 1);
+        exp_chunk(sb, 2 * cp + 1);
+        if (cp == 0) tmem_ld_wait_on(sa);
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       tc_fence_before();
