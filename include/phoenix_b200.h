@@ -447,6 +447,19 @@ phx_status phx_corpus_upload(phx_corpus* c, int64_t row0, int64_t nrows, const u
 phx_status phx_corpus_read_device(phx_corpus* c, int64_t row0, int64_t nrows, uint16_t* out_dev);
 /* Synthetic L2-normalised rows, a pure function of (global row, seed). */
 phx_status phx_corpus_fill_synthetic(phx_corpus* c, uint32_t seed);
+/* int8 form of the shard (the reference's post_q8 / post_scales table, recsys_two_tower_model.py:2518-2533): rows as
+ * int8 [rows, dim] with one float scale per row; a call scores
+ *   bf16((float(int32 dot of the int8 query with the int8 row) * query_scale) * row_scale)
+ * where the query is quantised per call: query_scale = max(max|u| / 127, 1e-12), q = clip(round_half_even(u /
+ * query_scale), -127, 127) (2523-2526).  Integer dot products are exact, so scores and ids are bit-exact against the
+ * reference arithmetic.  dim must be a multiple of 32.  phx_corpus_upload_int8 takes the table as the host has it;
+ * phx_corpus_quantize_int8 derives it on the device from the resident bf16 rows with the same rule as the queries
+ * (benchmarks, tests).  phx_corpus_set_int8(1) makes every later top-k of the shard (windows, masks, keys, exact
+ * passes, phx_retrieve_topk) score with the int8 form; it reads half the bytes per row. */
+phx_status phx_corpus_upload_int8(phx_corpus* c, int64_t row0, int64_t nrows, const int8_t* host_q8, const float* host_scales);
+phx_status phx_corpus_quantize_int8(phx_corpus* c);
+phx_status phx_corpus_set_int8(phx_corpus* c, int32_t on);
+phx_status phx_corpus_read_int8_device(phx_corpus* c, int64_t row0, int64_t nrows, int8_t* q8_dev, float* scales_dev);
 /* Exhaustive dot-product top-k of this shard: users f32 [B,dim] (rounded to bf16 as the reference
  * does), scores bf16-rounded f32 [B,k], ids int64 [B,k] global rows, ordered by (score desc,
  * id asc).  Replaces compute_top_k + top_k_by_key (recsys_two_tower_model.py:2455-2516,

@@ -1231,6 +1231,25 @@ def corpus_scores(users: np.ndarray, corpus_bits: np.ndarray) -> np.ndarray:
     return bf16_round(u @ bf16_from_bits(corpus_bits).T)
 
 
+def quantize_int8(x: np.ndarray):
+    """Symmetric per-row int8 form: scale = max(max|x| / 127, 1e-12), q = clip(round_half_even(x / scale), -127, 127)
+    (the query side of the reference's int8 scoring, recsys_two_tower_model.py:2523-2526; the same rule stands in for
+    the offline quantisation of the post table in tests and benchmarks).  Returns (int8 [n, d], float32 [n])."""
+    xf = np.asarray(x, np.float32)
+    sc = np.maximum(np.max(np.abs(xf), axis=1) / np.float32(127.0), np.float32(1e-12)).astype(np.float32)
+    q = np.clip(np.round(xf / sc[:, None]), -127, 127).astype(np.int8)
+    return q, sc
+
+
+def int8_corpus_scores(users: np.ndarray, post_q8: np.ndarray, post_scales: np.ndarray) -> np.ndarray:
+    """_int8_dot_scores (recsys_two_tower_model.py:2519-2533): the queries quantised per call, int32 dot products with
+    the int8 rows, (float(dot) * query scale) * row scale in float32, cast to bf16.  Returns float32 [B, rows] holding
+    bf16 values."""
+    uq, us = quantize_int8(users)
+    acc = uq.astype(np.int32) @ post_q8.astype(np.int32).T
+    return bf16_round((acc.astype(np.float32) * us[:, None]) * np.asarray(post_scales, np.float32)[None, :])
+
+
 def top_k(scores: np.ndarray, k: int, row_offset: int = 0):
     """Definitional top-k = `jax.lax.top_k` (cuda/top_k_by_key/__init__.py:78-80): scores
     descending, ties broken by the lower index.  Returns (scores [B,k] f32, ids [B,k] int64)."""

@@ -541,3 +541,30 @@ def test_input_stage_over_batch_prep_buffers_equals_the_reference_blocks():
     assert rel_l2(x[:, :1] / np.float32(math.sqrt(D)), g["prep_user_tok_noip"]) < 2e-6
     for use_log, key in ((True, "prep_norm_log"), (False, "prep_norm_lin")):
         np.testing.assert_allclose(po.normalize_continuous_value(g["prep_norm_in"], 30.0, use_log), g[key], rtol=1e-6, atol=1e-7)
+
+
+def test_int8_corpus_scoring_restates_the_reference_lines():
+    """quantize_int8 / int8_corpus_scores (recsys_two_tower_model.py:2519-2533): scale max|x| / 127 floored at 1e-12,
+    round half to even, clip at +-127; int32 dot, (dot * query scale) * row scale in float32, cast to bf16."""
+    x = np.array([[127.0, 0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 63.5],      # scale exactly 1: halves go to the even neighbour
+                  [0.0] * 8,                                           # nothing to scale by: the floor, all zeros
+                  [-254.0, 1.0, 3.0, 5.0, 253.9, 0.0, 0.0, 0.0]], np.float32)
+    q, sc = po.quantize_int8(x)
+    assert sc[0] == 1.0 and list(q[0]) == [127, 0, 2, 2, 0, -2, -2, 64]
+    assert sc[1] == np.float32(1e-12) and not q[1].any()
+    assert sc[2] == np.float32(2.0) and list(q[2]) == [-127, 0, 2, 2, 127, 0, 0, 0]
+    r = np.random.default_rng(0)
+    posts = r.standard_normal((200, 64)).astype(np.float32)
+    posts /= np.linalg.norm(posts, axis=1, keepdims=True)
+    users = r.standard_normal((4, 64)).astype(np.float32)
+    users /= np.linalg.norm(users, axis=1, keepdims=True)
+    pq, ps = po.quantize_int8(posts)
+    got = po.int8_corpus_scores(users, pq, ps)
+    uq, us = po.quantize_int8(users)
+    want = np.empty_like(got)
+    for b in range(4):                                                   # the same arithmetic one element at a time
+        for n in range(200):
+            dot = int(np.dot(uq[b].astype(np.int64), pq[n].astype(np.int64)))
+            want[b, n] = po.bf16_round(np.array([np.float32(np.float32(dot) * us[b]) * ps[n]], np.float32))[0]
+    assert np.array_equal(got, want)
+    assert np.abs(got - users @ posts.T).max() < 0.02                    # and it approximates the float scores

@@ -162,6 +162,10 @@ SIGNATURES = {
     "phx_corpus_destroy": (None, [_P]),
     "phx_corpus_upload": (C.c_int32, [_P, C.c_int64, C.c_int64, _P]),
     "phx_corpus_fill_synthetic": (C.c_int32, [_P, C.c_uint32]),
+    "phx_corpus_upload_int8": (C.c_int32, [_P, C.c_int64, C.c_int64, _P, _P]),
+    "phx_corpus_quantize_int8": (C.c_int32, [_P]),
+    "phx_corpus_set_int8": (C.c_int32, [_P, C.c_int32]),
+    "phx_corpus_read_int8_device": (C.c_int32, [_P, C.c_int64, C.c_int64, _P, _P]),
     "phx_corpus_read_device": (C.c_int32, [_P, C.c_int64, C.c_int64, _P]),
     "phx_corpus_topk_device": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, _P, _P]),
     "phx_corpus_set_mask": (C.c_int32, [_P, _P]),

@@ -67,6 +67,47 @@ struct AttnTcArgs {
   int* err_flag;
 };
 
+// D[tmem] (+)= A[tmem] * B[smem desc]: the A operand (bf16 pairs, one row per lane) comes from tensor memory
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accum)
+      : "memory");
+}
+// 32 registers per thread -> 32 lanes x 32 columns, completion left to a later tcgen05.wait::st
+__device__ __forceinline__ void tmem_st32_nowait(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+// 16 registers per thread -> 32 lanes x 16 columns
+__device__ __forceinline__ void tmem_st16_nowait(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// Wait for the tensor-memory loads in flight.  The 32 registers of the load that is about to be used are operands of
+// the statement, so that no use of them can be scheduled in front of it (another load may have been issued since and
+// other work done in between: the wait is the only thing that orders the registers' arrival).
+__device__ __forceinline__ void tmem_ld_wait_on(float (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+f"(r[0]), "+f"(r[1]), "+f"(r[2]), "+f"(r[3]), "+f"(r[4]), "+f"(r[5]), "+f"(r[6]), "+f"(r[7]),
+                 "+f"(r[8]), "+f"(r[9]), "+f"(r[10]), "+f"(r[11]), "+f"(r[12]), "+f"(r[13]), "+f"(r[14]), "+f"(r[15]),
+                 "+f"(r[16]), "+f"(r[17]), "+f"(r[18]), "+f"(r[19]), "+f"(r[20]), "+f"(r[21]), "+f"(r[22]), "+f"(r[23]),
+                 "+f"(r[24]), "+f"(r[25]), "+f"(r[26]), "+f"(r[27]), "+f"(r[28]), "+f"(r[29]), "+f"(r[30]), "+f"(r[31])
+               :: "memory");
+}
+
 template <int DH, bool CAP>
 __global__ void __launch_bounds__(A_THREADS, 2)
 ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -84,12 +125,12 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sQ = base;                               // DCH x [128 x 128 B]; reused to stage the output
   const uint32_t sK = sQ + DCH * SLAB;                    // NSB x DCH x [KBLK x 128 B]
-  const uint32_t sV = sK + NSB * DCH * KBLK * 128;        // DCH x [KBLK x 128 B]
-  const uint32_t sP = sV + DCH * KBLK * 128;              // PCH x [128 x 128 B]
-  const uint32_t sMask = sP + PCH * SLAB;                 // [TC_MAX_BLOCKS][4] key-validity words
+  const uint32_t sV = sK + NSB * DCH * KBLK * 128;        // 2 x DCH x [KBLK x 128 B]
+  const uint32_t sMask = sV + 2 * DCH * KBLK * 128;       // [TC_MAX_BLOCKS][4] key-validity words
   const uint32_t bars = sMask + TC_MAX_BLOCKS * 16;
-  const uint32_t q_full = bars, v_full = bars + 8, v_empty = bars + 16, p_ready = bars + 24, o_done = bars + 32,
-                 tmem_slot = bars + 88;
+  const uint32_t q_full = bars, p_ready = bars + 24, o_done = bars + 32, tmem_slot = bars + 88;
+  auto v_full = [&](int i) { return bars + (i ? 96u : 8u); };
+  auto v_empty = [&](int i) { return bars + (i ? 104u : 16u); };
   auto k_full = [&](int i) { return bars + 40u + 8u * i; };
   auto k_empty = [&](int i) { return bars + 56u + 8u * i; };
   auto s_full = [&](int i) { return bars + 72u + 8u * i; };
@@ -105,8 +146,8 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   volatile int* verr = a.err_flag;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1); mbar_init(v_full, 1); mbar_init(v_empty, 1); mbar_init(p_ready, 128); mbar_init(o_done, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(k_full(i), 1); mbar_init(k_empty(i), 1); mbar_init(s_full(i), 1); }
+    mbar_init(q_full, 1); mbar_init(p_ready, 128); mbar_init(o_done, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(k_full(i), 1); mbar_init(k_empty(i), 1); mbar_init(s_full(i), 1); mbar_init(v_full(i), 1); mbar_init(v_empty(i), 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(tmem_slot, 256);
@@ -131,9 +172,11 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       for (int j = 0; j < n_blocks; ++j) {
         const uint32_t ph = (uint32_t)(j & 1);
         if (j + NSB - 1 < n_blocks) load_k(j + NSB - 1);
-        mbar_wait(v_empty, ph ^ 1, verr);
-        mbar_expect_tx(v_full, DCH * KBLK * 128);
-        for (int c = 0; c < DCH; ++c) tma_load_3d(sV + c * KBLK * 128, &map_v, v_full, hk * a.v_head_stride + c * 64, j * KBLK, b);
+        const int vb = j & 1;                           // V is double-buffered: block j + 1 arrives under P V of block j
+        mbar_wait(v_empty(vb), (uint32_t)((j >> 1) & 1) ^ 1u, verr);
+        mbar_expect_tx(v_full(vb), DCH * KBLK * 128);
+        for (int c = 0; c < DCH; ++c)
+          tma_load_3d(sV + (vb * DCH + c) * KBLK * 128, &map_v, v_full(vb), hk * a.v_head_stride + c * 64, j * KBLK, b);
       }
     }
   } else if (warp == 1) {
@@ -160,16 +203,18 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         const uint32_t ph = (uint32_t)(j & 1);
         // the S buffer of block j + NSB - 1 was last read by the softmax of block j - 1, whose P has been awaited below
         if (j + NSB - 1 < n_blocks) issue_s(j + NSB - 1);
+        const int vb = j & 1;
         mbar_wait(p_ready, ph, verr);
-        mbar_wait(v_full, ph, verr);
+        mbar_wait(v_full(vb), (uint32_t)((j >> 1) & 1), verr);
         tc_fence_after();
+        // P sits in tensor memory, as bf16 pairs over the first KBLK / 2 columns of the S buffer it was computed from
+        // (16 keys = 8 columns per step); that buffer is overwritten by S of block j + NSB, issued after this product
 #pragma unroll
         for (int kk = 0; kk < KBLK / 16; ++kk) {
-          const uint64_t pd = make_smem_desc(sP + (kk >> 2) * SLAB) + (uint64_t)((kk & 3) * 2);
-          const uint64_t vd = make_smem_desc_mn(sV + kk * 16 * 128, KBLK * 128, 1024);
-          umma_bf16(tmem + TM_O, pd, vd, idesc_o, (j | kk) != 0);
+          const uint64_t vd = make_smem_desc_mn(sV + vb * DCH * KBLK * 128 + kk * 16 * 128, KBLK * 128, 1024);
+          umma_bf16_ts(tmem + TM_O, tmem + TM_S + (j % NSB) * KBLK + kk * 8, vd, idesc_o, (j | kk) != 0);
         }
-        umma_commit(v_empty);
+        umma_commit(v_empty(vb));
         umma_commit(o_done);
       }
     }
@@ -270,15 +315,16 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           }
         }
       }
-      // P (bf16) into the swizzled K-major slabs the second MMA reads
+      // P (bf16 pairs) back into tensor memory, over the first KBLK / 2 columns of this block's S buffer (the whole
+      // row of S is in registers by now): the second MMA takes its A operand from there
+      {
+        uint32_t pw[KBLK / 2];
 #pragma unroll
-      for (int c = 0; c < KBLK / 8; ++c) {
-        uint4 o;
-        o.x = pack_bf2(s[c * 8 + 0], s[c * 8 + 1]); o.y = pack_bf2(s[c * 8 + 2], s[c * 8 + 3]);
-        o.z = pack_bf2(s[c * 8 + 4], s[c * 8 + 5]); o.w = pack_bf2(s[c * 8 + 6], s[c * 8 + 7]);
-        st_shared_16(sP + (c >> 3) * SLAB + r * 128 + ((uint32_t)((c & 7) ^ sw) << 4), o);
+        for (int k = 0; k < KBLK / 2; ++k) pw[k] = pack_bf2(s[2 * k], s[2 * k + 1]);
+#pragma unroll
+        for (int c = 0; c < KBLK / 64; ++c) tmem_st32_nowait(tmem + TM_S + (j % NSB) * KBLK + lane_base + c * 32, pw + c * 32);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       mbar_arrive(p_ready);
     }
@@ -648,47 +694,6 @@ struct PingArgs {
 
 // the eight tensor maps of a launch: Q / K / V / out over the history block and over the candidate block
 struct PingMaps { CUtensorMap qh, qc, kh, vh, kc, vc, oh, oc; };
-
-// D[tmem] (+)= A[tmem] * B[smem desc]: the A operand (bf16 pairs, one row per lane) comes from tensor memory
-__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
-      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accum)
-      : "memory");
-}
-// 32 registers per thread -> 32 lanes x 32 columns, completion left to a later tcgen05.wait::st
-__device__ __forceinline__ void tmem_st32_nowait(uint32_t taddr, const uint32_t* r) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-
-// 16 registers per thread -> 32 lanes x 16 columns
-__device__ __forceinline__ void tmem_st16_nowait(uint32_t taddr, const uint32_t* r) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
-// Wait for the tensor-memory loads in flight.  The 32 registers of the load that is about to be used are operands of
-// the statement, so that no use of them can be scheduled in front of it (another load may have been issued since and
-// other work done in between: the wait is the only thing that orders the registers' arrival).
-__device__ __forceinline__ void tmem_ld_wait_on(float (&r)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+f"(r[0]), "+f"(r[1]), "+f"(r[2]), "+f"(r[3]), "+f"(r[4]), "+f"(r[5]), "+f"(r[6]), "+f"(r[7]),
-                 "+f"(r[8]), "+f"(r[9]), "+f"(r[10]), "+f"(r[11]), "+f"(r[12]), "+f"(r[13]), "+f"(r[14]), "+f"(r[15]),
-                 "+f"(r[16]), "+f"(r[17]), "+f"(r[18]), "+f"(r[19]), "+f"(r[20]), "+f"(r[21]), "+f"(r[22]), "+f"(r[23]),
-                 "+f"(r[24]), "+f"(r[25]), "+f"(r[26]), "+f"(r[27]), "+f"(r[28]), "+f"(r[29]), "+f"(r[30]), "+f"(r[31])
-               :: "memory");
-}
 
 template <bool CAP>
 __global__ void __launch_bounds__(PP_THREADS, 1)
@@ -1127,7 +1132,7 @@ phx_status launch_tc(const AttnArgs& a, int* err_flag, cudaStream_t stream, std:
   constexpr int KBLK = (DH == 64) ? 128 : 64;
   constexpr int DCH = DH / 64, PCH = KBLK / 64;
   constexpr int NSB = (KBLK <= 64) ? 2 : 1;   // K buffers, as in the kernel
-  const size_t smem = (size_t)DCH * SLAB + (NSB + 1) * (size_t)DCH * KBLK * 128 + (size_t)PCH * SLAB + TC_MAX_BLOCKS * 16 + 128 + 1024;
+  const size_t smem = (size_t)DCH * SLAB + (NSB + 2) * (size_t)DCH * KBLK * 128 + TC_MAX_BLOCKS * 16 + 128 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
     PHX_CUDA_TRY(cudaFuncSetAttribute(ranker_attention_tc_kernel<DH, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), err);

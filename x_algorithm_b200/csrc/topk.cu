@@ -68,9 +68,44 @@ __global__ void users_to_bf16_kernel(const float* __restrict__ users, bf16* __re
   out[i] = (b < B) ? f2bf(users[i]) : f2bf(0.f);
 }
 
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ void mma_16832_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Symmetric int8 form of one vector per warp: scale = max(max|x| / 127, 1e-12), q = clip(round_half_even(x / scale),
+// -127, 127) - the query side of the reference's int8 scoring (recsys_two_tower_model.py:2523-2526).  Rows past
+// n_valid are zero with scale 0.
+template <typename Tin>
+__global__ void quantize_rows_int8_kernel(const Tin* __restrict__ in, long long n_valid, long long n_rows, int dim,
+                                          signed char* __restrict__ out, float* __restrict__ scale) {
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= n_rows) return;
+  if (row >= n_valid) {
+    for (int d = lane; d < dim; d += 32) out[row * dim + d] = 0;
+    if (lane == 0) scale[row] = 0.f;
+    return;
+  }
+  float mx = 0.f;
+  for (int d = lane; d < dim; d += 32) mx = fmaxf(mx, fabsf(to_f32(in[row * dim + d])));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  const float sc = fmaxf(mx / 127.0f, 1e-12f);
+  for (int d = lane; d < dim; d += 32) {
+    const float q = fminf(fmaxf(rintf(to_f32(in[row * dim + d]) / sc), -127.f), 127.f);
+    out[row * dim + d] = (signed char)(int)q;
+  }
+  if (lane == 0) scale[row] = sc;
+}
+
 struct ScanArgs {
-  const bf16* corpus;      // [rows, dim]
-  const bf16* users;       // [Bpad, dim] bf16
+  const bf16* corpus;      // [rows, dim] bf16, or (i8) [rows, dim] int8
+  const bf16* users;       // [Bpad, dim] bf16, or (i8) int8
   long long rows;
   long long row_offset;    // global id of local row 0
   int dim, B, Bpad;
@@ -84,26 +119,33 @@ struct ScanArgs {
   const unsigned int* mask = nullptr;   // eligibility bits of the shard's rows (row_eligible), null = all
   long long mask_row0 = 0;
   const unsigned long long* thr = nullptr;   // MODE 2 / 3: [B] threshold keys (a row counts / is kept when key >= thr[u])
+  // int8 corpus (recsys_two_tower_model.py:2518-2533): score = bf16((float(int32 dot) * user_scale[u]) * row_scale[row])
+  int i8 = 0;
+  const float* user_scale = nullptr;   // [Bpad]
+  const float* row_scale = nullptr;    // [rows] of the scanned window
 };
 
 // NT = n-tiles (8 users each) per warp; a CTA covers 2 * NT * 8 users x 64 corpus rows per tile.
 // MODE 0 sample pass (group maxima), 1 collect pass against a score pivot, 2 count the rows whose 64-bit key is at or
 // above a per-user threshold key, 3 collect those rows (the exact passes: no sampling, nothing estimated).
-template <int NT, int MODE>
+// I8: corpus and queries are int8; every load below moves 16-bit units, so an int8 row is dim / 2 of them and one
+// m16n8k32 s8 MMA consumes the bytes one m16n8k16 bf16 MMA would (the fragments' byte layouts coincide).
+template <int NT, int MODE, bool I8>
 __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
   extern __shared__ __align__(16) uint8_t ssm[];
-  const int LD = a.dim + 8;
+  const int dimw = I8 ? a.dim / 2 : a.dim;   // 16-bit units per row
+  const int LD = dimw + 8;
   bf16* s_users = reinterpret_cast<bf16*>(ssm);                    // [Bpad][LD]
   bf16* s_tile = s_users + (size_t)a.Bpad * LD;                    // [2][TILE_ROWS][LD]
   float* s_pivot = reinterpret_cast<float*>(s_tile + 2 * TILE_ROWS * LD);  // [Bpad]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int mt = warp & 3, half = warp >> 2;
-  const int chunks_per_row = a.dim / 8;
+  const int chunks_per_row = dimw / 8;
 
   for (int c = threadIdx.x; c < a.Bpad * chunks_per_row; c += SCAN_THREADS) {
     const int r = c / chunks_per_row, dc = (c % chunks_per_row) * 8;
-    *reinterpret_cast<uint4*>(&s_users[r * LD + dc]) = *reinterpret_cast<const uint4*>(a.users + (size_t)r * a.dim + dc);
+    *reinterpret_cast<uint4*>(&s_users[r * LD + dc]) = *reinterpret_cast<const uint4*>(a.users + (size_t)r * dimw + dc);
   }
   if (MODE == 1)
     for (int u = threadIdx.x; u < a.Bpad; u += SCAN_THREADS) s_pivot[u] = (u < a.B) ? a.pivot[u] : INFINITY;
@@ -112,6 +154,9 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
   int* s_cnt = reinterpret_cast<int*>(s_thr + a.Bpad);                                   // [Bpad]
   if (MODE >= 2)
     for (int u = threadIdx.x; u < a.Bpad; u += SCAN_THREADS) { s_thr[u] = (u < a.B) ? a.thr[u] : ~0ull; s_cnt[u] = 0; }
+  float* s_us = reinterpret_cast<float*>(s_cnt + a.Bpad);                                // [Bpad] query scales (int8)
+  if (I8)
+    for (int u = threadIdx.x; u < a.Bpad; u += SCAN_THREADS) s_us[u] = a.user_scale[u];
 
   const long long n_tiles = (a.rows + TILE_ROWS - 1) / TILE_ROWS;
   const long long step = (long long)gridDim.x * (MODE == 0 ? a.stride : 1);
@@ -123,7 +168,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
     for (int c = threadIdx.x; c < TILE_ROWS * chunks_per_row; c += SCAN_THREADS) {
       const int r = c / chunks_per_row, dc = (c % chunks_per_row) * 8;
       const bool ok = (r0 + r) < a.rows;
-      const bf16* src = a.corpus + (size_t)(ok ? (r0 + r) : 0) * a.dim + dc;
+      const bf16* src = a.corpus + (size_t)(ok ? (r0 + r) : 0) * dimw + dc;
       cp_async16((uint32_t)__cvta_generic_to_shared(dst + r * LD + dc), src, ok);
     }
     cp_async_commit();
@@ -137,20 +182,35 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
     __syncthreads();
     const bf16* tl = s_tile + (size_t)buf * TILE_ROWS * LD;
     float acc[NT][4];
+    int acci[I8 ? NT : 1][4];
 #pragma unroll
-    for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
-    for (int ks = 0; ks < a.dim / 16; ++ks) {
+    for (int j = 0; j < NT; ++j) {
+      acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+      if (I8) { acci[j][0] = acci[j][1] = acci[j][2] = acci[j][3] = 0; }
+    }
+    for (int ks = 0; ks < dimw / 16; ++ks) {
       uint32_t af[4];
       ldmatrix_x4(af, (uint32_t)__cvta_generic_to_shared(tl + (mt * 16 + (lane & 15)) * LD + ks * 16 + ((lane >> 4) << 3)));
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
         const bf16* up = s_users + ((half * NT + j) * 8 + g) * LD + ks * 16 + 2 * t4;
-        mma_16816(acc[j], af, *reinterpret_cast<const uint32_t*>(up), *reinterpret_cast<const uint32_t*>(up + 8));
+        if (I8) mma_16832_s8(acci[I8 ? j : 0], af, *reinterpret_cast<const uint32_t*>(up), *reinterpret_cast<const uint32_t*>(up + 8));
+        else mma_16816(acc[j], af, *reinterpret_cast<const uint32_t*>(up), *reinterpret_cast<const uint32_t*>(up + 8));
       }
     }
     const long long row_a = tile * TILE_ROWS + mt * 16 + g, row_b = row_a + 8;
     const bool ok_a = row_a < a.rows && row_eligible(a.mask, a.mask_row0, row_a);
     const bool ok_b = row_b < a.rows && row_eligible(a.mask, a.mask_row0, row_b);
+    if (I8) {   // (float(dot) * query scale) * row scale, in that order, the cast to bf16 follows below
+      const float rs_a = row_a < a.rows ? __ldg(a.row_scale + row_a) : 0.f, rs_b = row_b < a.rows ? __ldg(a.row_scale + row_b) : 0.f;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const int u0 = (half * NT + j) * 8 + 2 * t4;
+        const float us0 = s_us[u0], us1 = s_us[u0 + 1];
+        acc[j][0] = ((float)acci[I8 ? j : 0][0] * us0) * rs_a; acc[j][1] = ((float)acci[I8 ? j : 0][1] * us1) * rs_a;
+        acc[j][2] = ((float)acci[I8 ? j : 0][2] * us0) * rs_b; acc[j][3] = ((float)acci[I8 ? j : 0][3] * us1) * rs_b;
+      }
+    }
     if (MODE == 0) {
       // 16-row group maximum per user (rows past the end count as -inf)
       const long long grp = (tile / a.stride) * 4 + mt;
@@ -414,6 +474,11 @@ struct phx_corpus {
   int* status = nullptr;
   int* err_flag = nullptr;       // raised by a bounded device-side wait that ran out
   bool use_tc = false;           // tcgen05 scan (dim 64 / 128), else the mma.sync scan
+  // int8 form of the corpus (phx_corpus_upload_int8 / phx_corpus_quantize_int8) and whether calls score with it
+  signed char* q8 = nullptr;     // [rows, dim]
+  float* row_scale = nullptr;    // [rows]
+  float* user_scale = nullptr;   // [256]
+  bool int8 = false;
   CUtensorMap map_corpus, map_users;
   CUtensorMap map_window;                    // corpus map of the last scanned window (phx_corpus_topk_window_device)
   long long win_begin = -1, win_end = -1;
@@ -441,31 +506,48 @@ struct phx_corpus {
 
 namespace {
 
-template <int NT>
+template <int NT, bool I8>
 phx_status launch_scan(phx_corpus* c, const ScanArgs& a, int mode, int grid, size_t smem) {
   if (mode == 2) {
-    PHX_CUDA_TRY(cudaFuncSetAttribute(scan_kernel<NT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), c->err);
-    scan_kernel<NT, 2><<<grid, SCAN_THREADS, smem, c->stream>>>(a);
+    PHX_CUDA_TRY(cudaFuncSetAttribute(scan_kernel<NT, 2, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), c->err);
+    scan_kernel<NT, 2, I8><<<grid, SCAN_THREADS, smem, c->stream>>>(a);
   } else if (mode == 3) {
-    PHX_CUDA_TRY(cudaFuncSetAttribute(scan_kernel<NT, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), c->err);
-    scan_kernel<NT, 3><<<grid, SCAN_THREADS, smem, c->stream>>>(a);
+    PHX_CUDA_TRY(cudaFuncSetAttribute(scan_kernel<NT, 3, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), c->err);
+    scan_kernel<NT, 3, I8><<<grid, SCAN_THREADS, smem, c->stream>>>(a);
   } else if (mode == 0) {
-    PHX_CUDA_TRY(cudaFuncSetAttribute(scan_kernel<NT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), c->err);
-    scan_kernel<NT, 0><<<grid, SCAN_THREADS, smem, c->stream>>>(a);
+    PHX_CUDA_TRY(cudaFuncSetAttribute(scan_kernel<NT, 0, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), c->err);
+    scan_kernel<NT, 0, I8><<<grid, SCAN_THREADS, smem, c->stream>>>(a);
   } else {
-    PHX_CUDA_TRY(cudaFuncSetAttribute(scan_kernel<NT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), c->err);
-    scan_kernel<NT, 1><<<grid, SCAN_THREADS, smem, c->stream>>>(a);
+    PHX_CUDA_TRY(cudaFuncSetAttribute(scan_kernel<NT, 1, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), c->err);
+    scan_kernel<NT, 1, I8><<<grid, SCAN_THREADS, smem, c->stream>>>(a);
   }
   PHX_CUDA_TRY(cudaGetLastError(), c->err);
   return PHX_OK;
 }
 
 phx_status run_scan(phx_corpus* c, const ScanArgs& a, int mode, int grid) {
-  const size_t smem = ((size_t)a.Bpad + 2 * TILE_ROWS) * (a.dim + 8) * 2 + (size_t)a.Bpad * (4 + 8 + 4);   // + pivots, threshold keys, counts
+  const int dimw = a.i8 ? a.dim / 2 : a.dim;
+  const size_t smem = ((size_t)a.Bpad + 2 * TILE_ROWS) * (dimw + 8) * 2 + (size_t)a.Bpad * (4 + 8 + 4 + 4);   // + pivots, threshold keys, counts, query scales
   if (smem > 200 * 1024) { c->err = "topk: query batch x dim does not fit shared memory"; return PHX_E_CAPACITY; }
-  if (a.Bpad == 16) return launch_scan<1>(c, a, mode, grid, smem);
-  if (a.Bpad == 64) return launch_scan<4>(c, a, mode, grid, smem);
-  return launch_scan<16>(c, a, mode, grid, smem);
+  if (a.i8) {
+    if (a.Bpad == 16) return launch_scan<1, true>(c, a, mode, grid, smem);
+    if (a.Bpad == 64) return launch_scan<4, true>(c, a, mode, grid, smem);
+    return launch_scan<16, true>(c, a, mode, grid, smem);
+  }
+  if (a.Bpad == 16) return launch_scan<1, false>(c, a, mode, grid, smem);
+  if (a.Bpad == 64) return launch_scan<4, false>(c, a, mode, grid, smem);
+  return launch_scan<16, false>(c, a, mode, grid, smem);
+}
+
+// queries into the form the scan in use reads: bf16, or int8 with one scale per query
+phx_status convert_users(phx_corpus* c, const float* users_dev, int B, int Bpad) {
+  if (c->int8) {
+    quantize_rows_int8_kernel<float><<<(Bpad + 7) / 8, 256, 0, c->stream>>>(users_dev, B, Bpad, c->dim, reinterpret_cast<signed char*>(c->users_bf), c->user_scale);
+  } else {
+    users_to_bf16_kernel<<<(Bpad * c->dim + 255) / 256, 256, 0, c->stream>>>(users_dev, c->users_bf, B, Bpad, c->dim);
+  }
+  PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  return PHX_OK;
 }
 
 // The top-k of a window without any estimate: per user, bisection on the 64-bit key (bf16 score, then lower row) for a
@@ -479,8 +561,7 @@ phx_status topk_exact(phx_corpus* c, ScanArgs a, int B, int k, float* scores_dev
   const int grid = (int)(n_tiles < c->num_sms * 2 ? n_tiles : c->num_sms * 2);
   a.Bpad = B <= 16 ? 16 : (B <= 64 ? 64 : 256);
   a.thr = c->thr;
-  users_to_bf16_kernel<<<(a.Bpad * c->dim + 255) / 256, 256, 0, c->stream>>>(c->last.users, c->users_bf, B, a.Bpad, c->dim);
-  PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  { phx_status cs = convert_users(c, c->last.users, B, a.Bpad); if (cs) return cs; }
   std::vector<unsigned long long> lo(B, 0ull), hi(B, ~0ull), thr(B, 0ull);   // count(key >= lo) >= k > count(key >= hi)
   std::vector<int> cnt(B, 0);
   std::vector<char> done(B, 0);
@@ -575,7 +656,7 @@ void phx_corpus_destroy(phx_corpus* c) {
   cudaSetDevice(c->device);
   if (c->stream) cudaStreamSynchronize(c->stream);
   auto fr = [](void* p) { if (p) cudaFree(p); };
-  fr(c->data); fr(c->users_bf); fr(c->gmax); fr(c->pivot); fr(c->surv); fr(c->merge_keys); fr(c->counts); fr(c->status); fr(c->err_flag); fr(c->mask); fr(c->thr); fr(c->pad_rows);
+  fr(c->data); fr(c->users_bf); fr(c->gmax); fr(c->pivot); fr(c->surv); fr(c->merge_keys); fr(c->counts); fr(c->status); fr(c->err_flag); fr(c->mask); fr(c->thr); fr(c->pad_rows); fr(c->q8); fr(c->row_scale); fr(c->user_scale);
   if (c->ev0) cudaEventDestroy(c->ev0);
   if (c->ev1) cudaEventDestroy(c->ev1);
   if (c->own_stream) cudaStreamDestroy(c->own_stream);
@@ -608,6 +689,56 @@ phx_status phx_corpus_fill_synthetic(phx_corpus* c, uint32_t seed) {
   return PHX_OK;
 }
 
+namespace {
+phx_status ensure_int8_buffers(phx_corpus* c) {
+  if (c->dim % 32 != 0) { c->err = "int8 corpus: dim must be a multiple of 32"; return PHX_E_ARG; }
+  if (!c->q8) PHX_CUDA_TRY(cudaMalloc(&c->q8, (size_t)c->rows * c->dim), c->err);
+  if (!c->row_scale) PHX_CUDA_TRY(cudaMalloc(&c->row_scale, (size_t)c->rows * 4), c->err);
+  if (!c->user_scale) PHX_CUDA_TRY(cudaMalloc(&c->user_scale, 256 * 4), c->err);
+  return PHX_OK;
+}
+}  // namespace
+
+phx_status phx_corpus_upload_int8(phx_corpus* c, int64_t row0, int64_t nrows, const int8_t* host_q8, const float* host_scales) {
+  if (!c || !host_q8 || !host_scales || row0 < 0 || nrows < 0 || row0 + nrows > c->rows) { if (c) c->err = "phx_corpus_upload_int8: range"; return PHX_E_ARG; }
+  cudaSetDevice(c->device);
+  phx_status s = ensure_int8_buffers(c);
+  if (s) return s;
+  PHX_CUDA_TRY(cudaMemcpy(c->q8 + row0 * c->dim, host_q8, (size_t)nrows * c->dim, cudaMemcpyHostToDevice), c->err);
+  PHX_CUDA_TRY(cudaMemcpy(c->row_scale + row0, host_scales, (size_t)nrows * 4, cudaMemcpyHostToDevice), c->err);
+  return PHX_OK;
+}
+
+phx_status phx_corpus_quantize_int8(phx_corpus* c) {
+  if (!c) return PHX_E_ARG;
+  cudaSetDevice(c->device);
+  phx_status s = ensure_int8_buffers(c);
+  if (s) return s;
+  quantize_rows_int8_kernel<bf16><<<(unsigned)((c->rows + 7) / 8), 256, 0, c->stream>>>(c->data, c->rows, c->rows, c->dim, c->q8, c->row_scale);
+  PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  PHX_CUDA_TRY(cudaStreamSynchronize(c->stream), c->err);
+  return PHX_OK;
+}
+
+phx_status phx_corpus_set_int8(phx_corpus* c, int32_t on) {
+  if (!c) return PHX_E_ARG;
+  if (on && !c->q8) { c->err = "phx_corpus_set_int8: no int8 rows (phx_corpus_upload_int8 / phx_corpus_quantize_int8)"; return PHX_E_STATE; }
+  cudaSetDevice(c->device);
+  PHX_CUDA_TRY(cudaStreamSynchronize(c->stream), c->err);
+  c->int8 = on != 0;
+  c->last.valid = false;
+  return PHX_OK;
+}
+
+phx_status phx_corpus_read_int8_device(phx_corpus* c, int64_t row0, int64_t nrows, int8_t* q8_dev, float* scales_dev) {
+  if (!c || !q8_dev || !scales_dev || !c->q8 || row0 < 0 || nrows < 0 || row0 + nrows > c->rows) { if (c) c->err = "phx_corpus_read_int8_device: range or no int8 rows"; return PHX_E_ARG; }
+  cudaSetDevice(c->device);
+  PHX_CUDA_TRY(cudaMemcpyAsync(q8_dev, c->q8 + row0 * c->dim, (size_t)nrows * c->dim, cudaMemcpyDeviceToDevice, c->stream), c->err);
+  PHX_CUDA_TRY(cudaMemcpyAsync(scales_dev, c->row_scale + row0, (size_t)nrows * 4, cudaMemcpyDeviceToDevice, c->stream), c->err);
+  PHX_CUDA_TRY(cudaStreamSynchronize(c->stream), c->err);
+  return PHX_OK;
+}
+
 phx_status phx_corpus_set_mask(phx_corpus* c, const uint32_t* host_bits) {
   if (!c) return PHX_E_ARG;
   cudaSetDevice(c->device);
@@ -634,7 +765,8 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
   if (row_begin < 0 || row_end > c->rows || row_begin >= row_end) { c->err = "topk: window outside the shard's rows"; return PHX_E_ARG; }
   // the window [row_begin, row_end) of the shard scanned as a corpus of its own: rows, first row and global id of row 0
   const long long rows = row_end - row_begin, roff = c->row_offset + row_begin;
-  const bf16* data = c->data + row_begin * (long long)c->dim;
+  const bool tc = c->use_tc && !c->int8;   // the int8 corpus is scanned by the mma.sync kernel
+  const bf16* data = c->int8 ? reinterpret_cast<const bf16*>(c->q8 + row_begin * (long long)c->dim) : c->data + row_begin * (long long)c->dim;
   if (k > rows) { c->err = "topk: k exceeds the rows of the window"; return PHX_E_ARG; }
   if (c->mask) {
     // eligible rows of the window (counted once per window on the host copy of the mask)
@@ -666,7 +798,7 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
   }
   cudaSetDevice(c->device);
   const CUtensorMap* map_corpus = &c->map_corpus;
-  if (c->use_tc && (row_begin != 0 || row_end != c->rows)) {
+  if (tc && (row_begin != 0 || row_end != c->rows)) {
     if (c->win_begin != row_begin || c->win_end != row_end) {
       CUtensorMap users_unused;
       phx_status ms = tc_scan_make_maps(&c->map_window, &users_unused, data, rows, c->dim, c->users_bf, c->err);
@@ -675,7 +807,7 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
     }
     map_corpus = &c->map_window;
   }
-  const int Bpad = c->use_tc ? 256 : (B <= 16 ? 16 : (B <= 64 ? 64 : 256));
+  const int Bpad = tc ? 256 : (B <= 16 ? 16 : (B <= 64 ? 64 : 256));
   auto pad_tail = [&]() -> phx_status {
     if (n_pad == 0) return PHX_OK;
     pad_masked_kernel<<<(B * n_pad + 255) / 256, 256, 0, c->stream>>>(c->pad_rows, n_pad, k_real, k, B, scores_dev, (long long*)ids_dev, c->keys_out);
@@ -690,6 +822,7 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
     xa.corpus = data; xa.users = c->users_bf; xa.rows = rows; xa.row_offset = roff; xa.dim = c->dim; xa.B = B; xa.Bpad = Bpad;
     xa.stride = 1; xa.gmax = c->gmax; xa.n_groups = 0; xa.pivot = c->pivot; xa.surv = c->surv; xa.counts = c->counts; xa.cap = c->cap;
     xa.mask = c->mask; xa.mask_row0 = row_begin;
+    xa.i8 = c->int8 ? 1 : 0; xa.user_scale = c->user_scale; xa.row_scale = c->int8 ? c->row_scale + row_begin : nullptr;
     if (k_real > 0) {
       phx_status xs = topk_exact(c, xa, B, k_real, scores_dev, (long long*)ids_dev, k);
       if (xs) return xs;
@@ -704,17 +837,17 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
     PHX_CUDA_TRY(cudaEventRecord(c->ev1, c->stream), c->err);
     return PHX_OK;
   }
-  users_to_bf16_kernel<<<(Bpad * c->dim + 255) / 256, 256, 0, c->stream>>>(users_dev, c->users_bf, B, Bpad, c->dim);
-  PHX_CUDA_TRY(cudaGetLastError(), c->err);
+  { phx_status cs = convert_users(c, users_dev, B, Bpad); if (cs) return cs; }
   PHX_CUDA_TRY(cudaMemsetAsync(c->counts, 0, 256 * 4, c->stream), c->err);
 
   // geometry of the scan in use: tile rows, rows per maximum group
-  const int tile_rows = c->use_tc ? 128 : TILE_ROWS;
-  const double group_rows = c->use_tc ? 32.0 : 16.0;
+  const int tile_rows = tc ? 128 : TILE_ROWS;
+  const double group_rows = tc ? 32.0 : 16.0;
   ScanArgs a;
   a.corpus = data; a.users = c->users_bf; a.rows = rows; a.row_offset = roff; a.dim = c->dim; a.B = B; a.Bpad = Bpad;
   a.stride = 1; a.gmax = c->gmax; a.n_groups = 0; a.pivot = c->pivot; a.surv = c->surv; a.counts = c->counts; a.cap = c->cap;
   a.mask = c->mask; a.mask_row0 = row_begin;
+  a.i8 = c->int8 ? 1 : 0; a.user_scale = c->user_scale; a.row_scale = c->int8 ? c->row_scale + row_begin : nullptr;
   TcScanArgs ta;
   ta.mask = c->mask; ta.mask_row0 = row_begin;
   ta.rows = rows; ta.row_offset = roff; ta.dim = c->dim; ta.B = B; ta.stride = 1; ta.gmax = c->gmax; ta.n_groups = 0;
@@ -737,8 +870,8 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
     j = (int)ceil(qg * (double)a.n_groups);
     if (j < 1) j = 1;
     phx_status s;
-    dispatch_note(c->use_tc ? DK_SCAN_TC : DK_SCAN_MMA);
-    if (c->use_tc) s = tc_scan_launch(*map_corpus, c->map_users, ta, 0, c->num_sms, c->err_flag, c->stream, c->err);
+    dispatch_note(tc ? DK_SCAN_TC : DK_SCAN_MMA);
+    if (tc) s = tc_scan_launch(*map_corpus, c->map_users, ta, 0, c->num_sms, c->err_flag, c->stream, c->err);
     else s = run_scan(c, a, 0, (int)(sampled_tiles < c->num_sms * 2 ? sampled_tiles : c->num_sms * 2));
     if (s) return s;
   }
@@ -746,8 +879,8 @@ phx_status phx_corpus_topk_window_device(phx_corpus* c, const float* users_dev, 
   PHX_CUDA_TRY(cudaGetLastError(), c->err);
   {
     phx_status s;
-    dispatch_note(c->use_tc ? DK_SCAN_TC : DK_SCAN_MMA);
-    if (c->use_tc) s = tc_scan_launch(*map_corpus, c->map_users, ta, 1, c->num_sms, c->err_flag, c->stream, c->err);
+    dispatch_note(tc ? DK_SCAN_TC : DK_SCAN_MMA);
+    if (tc) s = tc_scan_launch(*map_corpus, c->map_users, ta, 1, c->num_sms, c->err_flag, c->stream, c->err);
     else s = run_scan(c, a, 1, (int)(n_tiles < c->num_sms * 2 ? n_tiles : c->num_sms * 2));
     if (s) return s;
   }

@@ -129,6 +129,9 @@ def bench_topk(a):
     hbm, tf, src = _peaks()
     sh = CorpusShard(a.rows, a.dim, row_offset=0, max_queries=a.queries, max_k=a.k)
     sh.fill_synthetic(4)
+    if a.int8:                      # the int8 form of the same rows, derived on the device; scores come from it
+        sh.quantize_int8()
+        sh.set_int8(True)
     rng = np.random.default_rng(5)
     u = rng.standard_normal((a.queries, a.dim)).astype(np.float32)
     u /= np.linalg.norm(u, axis=1, keepdims=True)
@@ -143,9 +146,10 @@ def bench_topk(a):
         if it >= a.warmup:
             times.append(sh.last_device_ms())
     ms = float(np.median(times))
-    gbs = a.rows * a.dim * 2 / (ms * 1e-3) / 1e9
+    row_bytes = a.dim + 4 if a.int8 else a.dim * 2      # int8 row + its scale, or bf16 row
+    gbs = a.rows * row_bytes / (ms * 1e-3) / 1e9
     tfl = 2.0 * a.queries * a.dim * a.rows / (ms * 1e-3) / 1e12
-    print(json.dumps(dict(op="corpus_topk", rows=a.rows, dim=a.dim, queries=a.queries, k=a.k, ms=ms, achieved_gbs=gbs,
+    print(json.dumps(dict(op="corpus_topk_int8" if a.int8 else "corpus_topk", rows=a.rows, dim=a.dim, queries=a.queries, k=a.k, ms=ms, achieved_gbs=gbs,
                           peak_gbs=hbm, frac=gbs / hbm, tflops=tfl, peak_source=src)))
     sh.close()
 
@@ -306,6 +310,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["gather", "topk", "attention", "retrieve", "value", "ragged"])
     ap.add_argument("--check", action="store_true")
+    ap.add_argument("--int8", action="store_true", help="topk: score with the int8 form of the corpus")
     ap.add_argument("--no-dedup", action="store_true", help="sharded gather: send every request, not only distinct rows")
     ap.add_argument("--exchange", choices=["copy", "push", "a2a", "peer"], default="copy",
                     help="gather on >1 GPU: owner-side gather + copy-engine transfer into the requester's buffer (copy), "

@@ -45,6 +45,24 @@ class CorpusShard:
     def fill_synthetic(self, seed: int):
         self._check(lib.phx_corpus_fill_synthetic(self._h, seed))
 
+    def upload_int8(self, row0: int, q8: np.ndarray, scales: np.ndarray):
+        """The int8 form of rows [row0, row0 + n): q8 int8 [n, dim], scales f32 [n] (the reference's post_q8 /
+        post_scales, recsys_two_tower_model.py:2518-2533)."""
+        q = np.ascontiguousarray(q8, dtype=np.int8); sc = np.ascontiguousarray(scales, dtype=np.float32)
+        assert q.shape == (sc.shape[0], self.dim)
+        self._check(lib.phx_corpus_upload_int8(self._h, row0, q.shape[0], q.ctypes.data, sc.ctypes.data))
+
+    def quantize_int8(self):
+        """Derive the int8 form from the resident bf16 rows on the device (scale = max|row| / 127)."""
+        self._check(lib.phx_corpus_quantize_int8(self._h))
+
+    def set_int8(self, on: bool):
+        """Score every later top-k with the int8 form (half the bytes per row)."""
+        self._check(lib.phx_corpus_set_int8(self._h, int(bool(on))))
+
+    def read_int8_device(self, row0: int, nrows: int, q8, scales):
+        self._check(lib.phx_corpus_read_int8_device(self._h, row0, nrows, int(q8.data_ptr()), int(scales.data_ptr())))
+
     def topk_device(self, users, B: int, k: int, scores, ids):
         """users f32 [B,dim], scores f32 [B,k], ids int64 [B,k]: torch CUDA tensors; asynchronous."""
         self._check(lib.phx_corpus_topk_device(self._h, int(users.data_ptr()), B, k, int(scores.data_ptr()),
