@@ -594,6 +594,23 @@ def test_engine_errors_are_statuses(torch):
     with pytest.raises(px.PhoenixError) as ei:          # batch beyond capacity
         eng.rank(to_inputs(po.make_batch(ocfg, 3)))
     assert ei.value.status == 5
+    # a missing input array is an argument error on every id-path entry point, never a read through a null pointer
+    import ctypes as C
+    from x_algorithm_b200 import _lib
+    b2 = po.make_batch(ocfg, 2)
+    arrs = [np.ascontiguousarray(a) for a in (b2.hist_post_ids, b2.hist_author_ids, b2.hist_actions.astype(np.int32),
+                                              b2.hist_surfaces.astype(np.int32), b2.cand_post_ids, b2.cand_author_ids)]
+    lp = np.empty((2, ocfg.num_candidates, ocfg.num_actions), np.float32)
+    cont = np.empty((2, ocfg.num_candidates, ocfg.num_continuous), np.float32)
+    o = _lib.RankOut(lp.ctypes.data, cont.ctypes.data, None)
+    for missing in range(6):
+        ptrs = [a.ctypes.data for a in arrs]
+        ptrs[missing] = None
+        rb = _lib.RankBatch(2, 0, *ptrs)
+        assert _lib.lib.phx_rank_forward(eng._h, C.byref(rb), C.byref(o)) == 1
+        assert b"null input array" in _lib.lib.phx_last_error(eng._h)
+        assert _lib.lib.phx_rank_forward_device(eng._h, C.byref(rb), C.byref(o)) == 1
+        assert _lib.lib.phx_rank_submit(eng._h, C.byref(rb), 0) == 1
     out = eng.rank(to_inputs(po.make_batch(ocfg, 2)))   # the engine stays usable after errors
     assert np.isfinite(out.log_probs).all()
     eng.close()
