@@ -85,9 +85,10 @@ class ClockSampler(threading.Thread):
                     reasons=sorted(self.reasons))
 
 
-def cpu_oracle_rate(n_requests: int, repeats: int = 1, workload=None, batch=None):
+def cpu_oracle_rate(n_requests: int, repeats: int = 1, workload=None, batch=None, warmup: int = 0):
     """candidates/s of the NumPy oracle (bf16-emulating path) on `n_requests` requests of the workload (or on the
-    requests of `batch`), and the oracle's outputs for them: (rate, seconds, (log_probs, continuous, logits, scores))."""
+    requests of `batch`), and the oracle's outputs for them: (rate, seconds, (log_probs, continuous, logits, scores));
+    seconds = median of `repeats` passes after `warmup` untimed ones."""
     from oracle import phoenix_oracle as po
     ocfg = po.ModelConfig(**(workload or WORKLOAD), compute="bf16")
     w = po.make_weights(ocfg, WEIGHT_SEED)
@@ -96,15 +97,16 @@ def cpu_oracle_rate(n_requests: int, repeats: int = 1, workload=None, batch=None
     spec = po.blend_spec_from_weights(po.make_blend_weights(BLEND_SEED), po.HEAD_NAMES_19, ocfg.num_actions)
     b = batch if batch is not None else po.make_batch(ocfg, n_requests, seed=ID_SEED, zipf_s=1.1)
     n_requests = b.cand_post_ids.shape[0]
-    best, outs = None, None
-    for _ in range(repeats):
+    times, outs = [], None
+    for i in range(warmup + repeats):
         t0 = time.perf_counter()
         lp, cont, logits = po.rank_forward(ocfg, w, rows_fn, b)
         sc = po.blend_scores(spec, lp, cont)
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
         outs = (lp, cont, logits, sc)
-    return n_requests * ocfg.num_candidates / best, best, outs
+    dt = float(np.median(times))
+    return n_requests * ocfg.num_candidates / dt, dt, outs
 
 
 def run_reference(args, rank: int):
@@ -574,9 +576,10 @@ def main():
             b0 = batches[0]
             sub = po.RankBatch(*[np.ascontiguousarray(getattr(b0, f)[pick]) for f in
                                  ("hist_post_ids", "hist_author_ids", "hist_actions", "hist_surfaces", "cand_post_ids", "cand_author_ids")])
-            rate, dt, (o_lp, o_cont, o_logits, o_sc) = cpu_oracle_rate(len(pick), workload=wl, batch=sub)
+            rate, dt, (o_lp, o_cont, o_logits, o_sc) = cpu_oracle_rate(len(pick), repeats=5, workload=wl, batch=sub, warmup=1)
             line["cpu_baseline"] = dict(value=rate, unit="candidates/s", cores=cores, kind="port",
-                                        sample=f"{len(pick)} requests x {C} candidates, one pass of the NumPy oracle ({dt:.1f} s)")
+                                        sample=f"{len(pick)} requests x {C} candidates, median of 5 passes of the NumPy oracle "
+                                               f"after 1 warm-up ({dt:.1f} s per pass)")
             g_lp = np.minimum(check_out.log_probs[pick].astype(np.float64), -1e-12)
             g_logits = g_lp - np.log(-np.expm1(g_lp))
             o_logits = o_logits.astype(np.float64)
