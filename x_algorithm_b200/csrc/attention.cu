@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(ATT_THREADS) ranker_attention_kernel(AttnArgs 
   constexpr int KSTEPS = DH / 16;     // k-steps of Q K^T
   constexpr int DT = DH / 8;          // output n-tiles
   constexpr int CH = DH / 8;          // 16-byte chunks per row
-  extern __shared__ __align__(16) uint8_t asm_raw[];
+  extern __shared__ __align__(128) uint8_t asm_raw[];
   bf16* sq = reinterpret_cast<bf16*>(asm_raw);     // [QROWS][LD]  Q tile, later the output tile
   bf16* sks = sq + QROWS * LD;                     // [QROWS][LD]  K rows of the tile's own tokens
   bf16* svs = sks + QROWS * LD;                    // [QROWS][LD]  V rows of the tile's own tokens
@@ -683,8 +683,8 @@ phx_status ranker_attention_launch(const AttnArgs& a, cudaStream_t stream, std::
   {
     // Head dim 64 with a history of at most 128 keys: the persistent tcgen05 kernel with the history resident and two
     // softmax warpgroups, once there is an item (batch, head) for every SM.  Measured on B200 at the ranking
-    // benchmark's shape (B=256, S=128, C=512, 8 heads): 0.154 ms per layer against 0.216 ms for the mma.sync
-    // resident-history kernel below (1.48 against 2.02 ms per step inside the forward), and 0.053 against 0.069 ms at
+    // benchmark's shape (B=256, S=128, C=512, 8 heads): 0.140 ms per layer against 0.206 ms for the mma.sync
+    // resident-history kernel below (1.2-1.4 against 2.0 ms per step inside the forward), and 0.051 against 0.067 ms at
     // B=64; every byte it touches moves by bulk copies.  PHX_ATTN=strip keeps the mma.sync kernel, PHX_ATTN=pingpong
     // takes this one at any batch size.
     const char* force = getenv("PHX_ATTN");

@@ -115,7 +115,6 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                            AttnTcArgs a) {
   constexpr int KBLK = (DH == 64) ? 128 : 64;   // keys per block (keeps shared memory at 80 KB: two CTAs per SM)
   constexpr int DCH = DH / 64;                  // 64-column chunks of the head dim
-  constexpr int PCH = KBLK / 64;                // 64-key slabs of P
   // S is double-buffered in TMEM (and K in shared memory): S of block j+1 is computed while the softmax warps are
   // still on block j, so the tensor pipe and the softmax overlap inside one CTA.  KBLK <= 64 or two S buffers of
   // 128 columns would not fit next to O in the CTA's 256 columns; at head dim 64 (KBLK 128) S stays single.
@@ -170,7 +169,6 @@ ranker_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       };
       for (int j = 0; j < NSB - 1 && j < n_blocks; ++j) load_k(j);
       for (int j = 0; j < n_blocks; ++j) {
-        const uint32_t ph = (uint32_t)(j & 1);
         if (j + NSB - 1 < n_blocks) load_k(j + NSB - 1);
         const int vb = j & 1;                           // V is double-buffered: block j + 1 arrives under P V of block j
         mbar_wait(v_empty(vb), (uint32_t)((j >> 1) & 1) ^ 1u, verr);
@@ -1130,7 +1128,7 @@ phx_status launch_pingpong(const AttnArgs& a, int* err_flag, int num_sms, cudaSt
 template <int DH, bool CAP>
 phx_status launch_tc(const AttnArgs& a, int* err_flag, cudaStream_t stream, std::string& err) {
   constexpr int KBLK = (DH == 64) ? 128 : 64;
-  constexpr int DCH = DH / 64, PCH = KBLK / 64;
+  constexpr int DCH = DH / 64;
   constexpr int NSB = (KBLK <= 64) ? 2 : 1;   // K buffers, as in the kernel
   const size_t smem = (size_t)DCH * SLAB + (NSB + 2) * (size_t)DCH * KBLK * 128 + TC_MAX_BLOCKS * 16 + 128 + 1024;
   static bool attr_set = false;
