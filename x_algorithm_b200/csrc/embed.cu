@@ -96,7 +96,9 @@ __global__ void __launch_bounds__(256, GENERAL ? 3 : 5) build_tokens_kernel(Toke
   const long long tok = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (tok >= (long long)a.B * T) return;
-  const int b = (int)(tok / T), t = (int)(tok % T);
+  // request and slot by 32-bit division (the launcher refuses B * T >= 2^31): a 64-bit '/' and '%' here cost more
+  // instructions than the rest of the warp's prologue
+  const int b = (int)((unsigned)tok / (unsigned)T), t = (int)((unsigned)tok - (unsigned)b * (unsigned)T);
   const int P = GENERAL ? a.P : 0;
   const bool is_front = t < a.S;              // rows in front of the candidates: user prefix + history
   const bool is_user = GENERAL && t < P;
@@ -234,7 +236,9 @@ __global__ void __launch_bounds__(256) finish_tokens_kernel(const bf16* __restri
   const long long tok = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (tok >= (long long)a.B * T) return;
-  const int b = (int)(tok / T), t = (int)(tok % T);
+  // request and slot by 32-bit division (the launcher refuses B * T >= 2^31): a 64-bit '/' and '%' here cost more
+  // instructions than the rest of the warp's prologue
+  const int b = (int)((unsigned)tok / (unsigned)T), t = (int)((unsigned)tok - (unsigned)b * (unsigned)T);
   const int Sh = a.S - a.P;
   const bool is_user = t < a.P, is_hist = !is_user && t < a.S;
   const bf16* src = is_user ? tok_user + (long long)b * a.D
@@ -393,6 +397,7 @@ phx_status build_tokens_launch(const TokenBuildArgs& a, cudaStream_t stream, std
   }
   const long long toks = (long long)a.B * (a.S + a.C);
   if (toks == 0) return PHX_OK;
+  if (toks >= (1ll << 31)) { err = "build_tokens: more than 2^31 tokens in one call"; return PHX_E_CAPACITY; }
   const int warps = 8;
   const bool general = a.pack.hist_off || a.pre_hist_post || a.landing || a.concat_hist || a.action_multi_hot || a.x32 ||
                        a.tokens || a.hashes || a.rows_only || a.P || a.hist_actions_bool || a.cand_surfaces || a.n_cont;
@@ -417,6 +422,7 @@ phx_status finish_tokens_launch(const bf16* tok_user, const bf16* tok_hist, cons
                                 cudaStream_t stream, std::string& err) {
   const long long toks = (long long)a.B * (a.S + a.C);
   if (toks == 0) return PHX_OK;
+  if (toks >= (1ll << 31)) { err = "finish_tokens: more than 2^31 tokens in one call"; return PHX_E_CAPACITY; }
   finish_tokens_kernel<<<(unsigned)((toks + 7) / 8), 256, 0, stream>>>(tok_user, tok_hist, tok_cand, a);
   PHX_CUDA_TRY(cudaGetLastError(), err);
   return PHX_OK;
