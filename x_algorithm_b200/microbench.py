@@ -233,6 +233,37 @@ def bench_attention(a):
                           peak_source=src)))
 
 
+def bench_gemm(a):
+    """The four GEMM shapes of a cfg1 layer at the full M (plain store epilogue), this library's kernel beside
+    torch.matmul (cuBLAS) on the same operands: a comparison line, not a path of the engine."""
+    import torch
+    from x_algorithm_b200.engine import gemm
+    M = a.rows_m
+    torch.manual_seed(0)
+    for name, N, K in (("qkv", 1536, 512), ("out", 512, 512), ("up", 2048, 512), ("down", 512, 2048)):
+        x = (torch.randn(M, K, device="cuda") * 0.05).to(torch.bfloat16)
+        wt = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)      # [N, K], K-major, as the engine stores weights
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        for _ in range(a.warmup):
+            torch.matmul(x, wt.t(), out=out)
+        torch.cuda.synchronize()
+        lib_ms = []
+        for _ in range(a.iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); torch.matmul(x, wt.t(), out=out); e1.record(); torch.cuda.synchronize()
+            lib_ms.append(e0.elapsed_time(e1))
+        ours_ms = []
+        for i in range(a.warmup + a.iters):
+            c, ms = gemm(x, wt, None, 0, 0)
+            if i >= a.warmup:
+                ours_ms.append(ms)
+        fl = 2.0 * M * N * K
+        t_lib, t_ours = float(np.median(lib_ms)), float(np.median(ours_ms))
+        print(json.dumps(dict(op="gemm", shape=name, M=M, N=N, K=K, ms=t_ours, tflops=fl / t_ours / 1e9, cublas_ms=t_lib,
+                              cublas_tflops=fl / t_lib / 1e9, ratio_to_cublas=t_lib / t_ours,
+                              max_abs_diff=float((c.float() - out.float()).abs().max()))))
+
+
 def bench_ragged(a):
     """Ragged ranking batches through the blocking host-buffer call, with and without packed rows: the headline benchmark's
     model, --batch requests whose valid history / candidate counts are uniform in [1, S] / [1, C]."""
@@ -308,9 +339,10 @@ def bench_value(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gather", "topk", "attention", "retrieve", "value", "ragged"])
+    ap.add_argument("op", choices=["gather", "topk", "attention", "retrieve", "value", "ragged", "gemm"])
     ap.add_argument("--check", action="store_true")
     ap.add_argument("--int8", action="store_true", help="topk: score with the int8 form of the corpus")
+    ap.add_argument("--rows-m", type=int, default=163840, help="gemm: rows of the activation matrix")
     ap.add_argument("--no-dedup", action="store_true", help="sharded gather: send every request, not only distinct rows")
     ap.add_argument("--exchange", choices=["copy", "push", "a2a", "peer"], default="copy",
                     help="gather on >1 GPU: owner-side gather + copy-engine transfer into the requester's buffer (copy), "
@@ -333,7 +365,7 @@ def main():
     ap.add_argument("--cands", type=int, default=1024)
     a = ap.parse_args()
     {"gather": bench_gather, "topk": bench_topk, "attention": bench_attention, "retrieve": bench_retrieve,
-     "value": bench_value, "ragged": bench_ragged}[a.op](a)
+     "value": bench_value, "ragged": bench_ragged, "gemm": bench_gemm}[a.op](a)
 
 
 if __name__ == "__main__":
